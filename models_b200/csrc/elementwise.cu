@@ -1,0 +1,254 @@
+// Row-wise and element-wise kernels of the decoder: embedding gather, residual add fused with
+// RMSNorm, rotary position encoding fused with the cache write, the gated activation and bias add.
+// Each is instantiated for float and bfloat16 storage; all arithmetic is float.
+//
+// Formulas follow integrallis/models (paths inside that project):
+//   RMSNorm    backend-java/.../ops/TensorOps.java:45-58
+//   rotation   backend-java/.../ops/TensorOps.java:1474-1486 (pair rotation), RotaryTable.java:177-186
+//   SwiGLU     backend-java/.../ops/TensorOps.java:1407-1425
+//   cache write after rotation, values unrotated: backend-java/.../llama/LlamaForwardPass.java:1070-1086
+#include "common.cuh"
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+// ------------------------------------------------------------------------------------ embedding
+
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                                    float* __restrict__ out, int width, int vocab, float scale) {
+    const int row = blockIdx.x;
+    int token = tokens[row];
+    token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);  // ids are validated on the host
+    const TW* src = table + (size_t)token * width;
+    float* dst = out + (size_t)row * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) dst[d] = Num<TW>::load(src + d) * scale;
+}
+
+// ------------------------------------------------------------------------------------ add + RMSNorm
+
+// One block per output row.  x is the float residual stream.  With `delta` the sum x + delta is
+// formed in float; it is written back to x when write_x is set.  `rows` (optional) picks input rows.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                   const float* __restrict__ weight, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int width, float eps, int write_x) {
+    extern __shared__ float row_cache[];  // the row, width floats
+    __shared__ float scratch[32];
+    const int out_row = blockIdx.x;
+    const int in_row = rows ? rows[out_row] : out_row;
+    float* xr = x + (size_t)in_row * width;
+    const TD* dr = delta ? delta + (size_t)in_row * width : nullptr;
+    float sum_sq = 0.0f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float v = xr[d];
+        if (dr) {
+            v += Num<TD>::load(dr + d);
+            if (write_x) xr[d] = v;
+        }
+        row_cache[d] = v;
+        sum_sq += v * v;
+    }
+    sum_sq = block_sum(sum_sq, scratch);
+    const float rms = sqrtf(sum_sq / (float)width + eps);
+    const float scale = 1.0f / rms;
+    TO* o = out + (size_t)out_row * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) Num<TO>::store(o + d, row_cache[d] * scale * weight[d]);
+}
+
+// ------------------------------------------------------------------------------------ rotary + cache
+
+// grid (tokens, heads + 2*kv_heads).  Query heads are rotated in place; key heads are rotated and
+// written to the cache; value heads are copied to the cache.  slot_mapping[t] is the flat position
+// (page * page_size + offset) of token t in this layer's pools, or < 0 for a row that is padding.
+template <typename T>
+__global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                        const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                        T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                        const int* __restrict__ slot_mapping, int heads, int kv_heads, int head_dim,
+                                        int rotary_dim, int interleaved, int page_size, int write_cache) {
+    const int t = blockIdx.x;
+    const int h = blockIdx.y;
+    T* vec = qkv + (size_t)t * row_stride + (size_t)h * head_dim;
+    const bool is_query = h < heads;
+    const bool is_key = !is_query && h < heads + kv_heads;
+    T* dst = nullptr;
+    if (!is_query) {
+        if (!write_cache) return;
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const int kvh = is_key ? h - heads : h - heads - kv_heads;
+        const size_t page = slot / page_size, offset = slot % page_size;
+        dst = (is_key ? k_pool : v_pool) + ((page * kv_heads + kvh) * page_size + offset) * head_dim;
+    }
+    if (is_query || is_key) {
+        const int pairs = rotary_dim / 2;
+        const int pos = positions[t];
+        const float* c = cos_table + (size_t)pos * pairs;
+        const float* s = sin_table + (size_t)pos * pairs;
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+            const int i0 = interleaved ? 2 * i : i;
+            const int i1 = interleaved ? 2 * i + 1 : i + pairs;
+            const float x0 = Num<T>::load(vec + i0), x1 = Num<T>::load(vec + i1);
+            const float r0 = x0 * c[i] - x1 * s[i];
+            const float r1 = x0 * s[i] + x1 * c[i];
+            if (is_query) {
+                Num<T>::store(vec + i0, r0);
+                Num<T>::store(vec + i1, r1);
+            } else {
+                Num<T>::store(dst + i0, r0);
+                Num<T>::store(dst + i1, r1);
+            }
+        }
+        if (is_key)
+            for (int d = rotary_dim + threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = vec[d];
+    } else {
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = vec[d];
+    }
+}
+
+// ------------------------------------------------------------------------------------ gated activation
+
+// gate_up: [rows, 2*width] with the gate in columns [0, width) and up in [width, 2*width).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const size_t row = i / width, col = i % width;
+        const float g = Num<T>::load(gate_up + row * 2 * width + col);
+        const float u = Num<T>::load(gate_up + row * 2 * width + width + col);
+        const float silu = g / (1.0f + expf(-g));
+        Num<T>::store(out + i, silu * u);
+    }
+}
+
+template <typename T>
+__global__ void bias_add_kernel(T* __restrict__ x, const float* __restrict__ bias, int width, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+        Num<T>::store(x + i, Num<T>::load(x + i) + bias[i % width]);
+}
+
+// x (float residual) += delta
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t total) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
+        x[i] += Num<TD>::load(delta + i);
+}
+
+inline int grid_for(size_t total, int block) {
+    size_t blocks = (total + block - 1) / block;
+    return (int)(blocks > 148 * 16 ? 148 * 16 : (blocks ? blocks : 1));
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int rows, int width,
+                              int vocab, float scale, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || vocab <= 0) return fail("embed_gather: width %d and vocab %d must be positive", width, vocab);
+    const int block = width >= 1024 ? 256 : 128;
+    if (table_dtype == MB_F32)
+        embed_gather_kernel<float><<<rows, block, 0, stream>>>((const float*)table, tokens, out, width, vocab, scale);
+    else if (table_dtype == MB_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<rows, block, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, width, vocab, scale);
+    else
+        return fail("embed_gather: unknown dtype code %d", table_dtype);
+    return check_launch("embed_gather");
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
+                              int out_rows, int width, float eps, int write_x, cudaStream_t stream) {
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return fail("add_rmsnorm: a row of %d floats does not fit shared memory (limit 51200)", width);
+    auto kernel = add_rmsnorm_kernel<TD, TO>;
+    if (smem > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("add_rmsnorm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+    }
+    const int block = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    kernel<<<out_rows, block, smem, stream>>>(x, (const TD*)delta, weight, (TO*)out, rows, width, eps, write_x);
+    return check_launch("add_rmsnorm");
+}
+
+// delta may be null (then delta_dtype is ignored).  out_dtype selects the storage of `out`.
+MB_EXPORT int mb_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* weight, void* out,
+                             int out_dtype, const int* rows, int out_rows, int width, float eps, int write_x,
+                             cudaStream_t stream) {
+    if (out_rows <= 0) return 0;
+    if (width <= 0) return fail("add_rmsnorm: width %d must be positive", width);
+    if (!delta) delta_dtype = out_dtype;
+    if (delta_dtype == MB_F32 && out_dtype == MB_F32)
+        return launch_add_rmsnorm<float, float>(x, delta, weight, out, rows, out_rows, width, eps, write_x, stream);
+    if (delta_dtype == MB_BF16 && out_dtype == MB_BF16)
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, weight, out, rows, out_rows, width, eps, write_x, stream);
+    if (delta_dtype == MB_F32 && out_dtype == MB_BF16)
+        return launch_add_rmsnorm<float, __nv_bfloat16>(x, delta, weight, out, rows, out_rows, width, eps, write_x, stream);
+    if (delta_dtype == MB_BF16 && out_dtype == MB_F32)
+        return launch_add_rmsnorm<__nv_bfloat16, float>(x, delta, weight, out, rows, out_rows, width, eps, write_x, stream);
+    return fail("add_rmsnorm: unknown dtype codes %d, %d", delta_dtype, out_dtype);
+}
+
+MB_EXPORT int mb_rope_cache_write(void* qkv, int dtype, int row_stride, const int* positions, const float* cos_table,
+                                  const float* sin_table, void* k_pool, void* v_pool, const int* slot_mapping,
+                                  int tokens, int heads, int kv_heads, int head_dim, int rotary_dim, int interleaved,
+                                  int page_size, int write_cache, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+        return fail("rope_cache_write: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    if (rotary_dim > 0 && (!cos_table || !sin_table || !positions))
+        return fail("rope_cache_write: a rotation needs positions and cos/sin tables");
+    if (write_cache && (!k_pool || !v_pool || !slot_mapping || page_size <= 0))
+        return fail("rope_cache_write: a cache write needs pools, a slot mapping and a page size");
+    const dim3 grid(tokens, write_cache ? heads + 2 * kv_heads : heads);
+    const int block = head_dim >= 128 ? 64 : 32;
+    if (dtype == MB_F32)
+        rope_cache_write_kernel<float><<<grid, block, 0, stream>>>((float*)qkv, row_stride, positions, cos_table, sin_table,
+            (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, rotary_dim, interleaved, page_size, write_cache);
+    else if (dtype == MB_BF16)
+        rope_cache_write_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>((__nv_bfloat16*)qkv, row_stride, positions, cos_table, sin_table,
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim, rotary_dim, interleaved, page_size, write_cache);
+    else
+        return fail("rope_cache_write: unknown dtype code %d", dtype);
+    return check_launch("rope_cache_write");
+}
+
+MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int dtype, int rows, int width, cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    if (total == 0) return 0;
+    if (dtype == MB_F32)
+        swiglu_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, width, total);
+    else if (dtype == MB_BF16)
+        swiglu_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total);
+    else
+        return fail("swiglu: unknown dtype code %d", dtype);
+    return check_launch("swiglu");
+}
+
+MB_EXPORT int mb_bias_add(void* x, int dtype, const float* bias, int rows, int width, cudaStream_t stream) {
+    const size_t total = (size_t)rows * width;
+    if (total == 0) return 0;
+    if (dtype == MB_F32)
+        bias_add_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((float*)x, bias, width, total);
+    else if (dtype == MB_BF16)
+        bias_add_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>((__nv_bfloat16*)x, bias, width, total);
+    else
+        return fail("bias_add: unknown dtype code %d", dtype);
+    return check_launch("bias_add");
+}
+
+MB_EXPORT int mb_residual_add(float* x, const void* delta, int delta_dtype, size_t total, cudaStream_t stream) {
+    if (total == 0) return 0;
+    if (delta_dtype == MB_F32)
+        residual_add_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>(x, (const float*)delta, total);
+    else if (delta_dtype == MB_BF16)
+        residual_add_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>(x, (const __nv_bfloat16*)delta, total);
+    else
+        return fail("residual_add: unknown dtype code %d", delta_dtype);
+    return check_launch("residual_add");
+}

@@ -1,0 +1,395 @@
+// Next-token selection on the device: greedy argmax and the sampling pipeline of
+// integrallis/models (models-runtime/.../Sampler.java:37-151,174-205,244-252):
+//   repetition penalty once per earlier occurrence (positive logit / r, otherwise * r),
+//   divide by the temperature, softmax over the whole vocabulary (max subtracted, exp, / sum),
+//   the k most probable tokens with ties going to the lower id, the shortest prefix of these (most
+//   probable first) whose mass reaches top_p, crossing token included, then an inverse-CDF draw
+//   r = u * kept mass.  Temperature 0 is argmax, first maximum wins.
+// The uniform u comes from Philox4x32-10 keyed by the request's seed, with the request's draw
+// counter as the counter, 24 random bits as Java's Random.nextFloat() uses; the stream is
+// reproducible but not the Java generator's.
+//
+// One block of 1024 threads per row.  `work` is caller-provided scratch of rows * vocab floats
+// and `counts` rows * vocab ints (only touched by rows whose penalty is > 1).
+#include "common.cuh"
+
+#include <math_constants.h>
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int kThreads = 1024;
+constexpr int kMaxSorted = 1024;
+
+struct Best {
+    float value;
+    int index;
+};
+
+__device__ __forceinline__ Best better(Best a, Best b) {
+    // greater value wins; equal values: the lower index (first maximum wins)
+    if (b.value > a.value || (b.value == a.value && b.index < a.index)) return b;
+    return a;
+}
+
+__device__ Best block_best(Best mine, Best* scratch /* 32 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        Best other;
+        other.value = __shfl_xor_sync(0xffffffffu, mine.value, offset);
+        other.index = __shfl_xor_sync(0xffffffffu, mine.index, offset);
+        mine = better(mine, other);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = mine;
+    __syncthreads();
+    Best total = scratch[lane < (int)(blockDim.x >> 5) ? lane : 0];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        Best other;
+        other.value = __shfl_xor_sync(0xffffffffu, total.value, offset);
+        other.index = __shfl_xor_sync(0xffffffffu, total.index, offset);
+        total = better(total, other);
+    }
+    return total;
+}
+
+// Exclusive prefix sum of a 0/1 flag over the block (thread order); *total gets the block's sum.
+__device__ int block_flag_scan(bool flag, int* warp_totals /* 32 */, int* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+    const int in_warp = __popc(ballot & ((1u << lane) - 1u));
+    __syncthreads();
+    if (lane == 0) warp_totals[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, all = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+        const int t = warp_totals[w];
+        if (w < warp) before += t;
+        all += t;
+    }
+    *total = all;
+    return before + in_warp;
+}
+
+// Inclusive prefix sum of floats over the block in thread order (a fixed order of additions).
+__device__ float block_float_scan(float v, float* warp_totals /* 32 */, float* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, v, offset);
+        if (lane >= offset) v += up;
+    }
+    __syncthreads();
+    if (lane == 31) warp_totals[warp] = v;
+    __syncthreads();
+    float before = 0.0f, all = 0.0f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+        const float t = warp_totals[w];
+        if (w < warp) before += t;
+        all += t;
+    }
+    *total = all;
+    return before + v;
+}
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t (&k)[2]) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+    const uint32_t n0 = hi1 ^ c[1] ^ k[0], n1 = lo1, n2 = hi0 ^ c[3] ^ k[1], n3 = lo0;
+    c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+    k[0] += 0x9E3779B9u;
+    k[1] += 0xBB67AE85u;
+}
+
+__device__ float philox_uniform(unsigned long long seed, unsigned long long counter) {
+    uint32_t c[4] = {(uint32_t)counter, (uint32_t)(counter >> 32), 0u, 0u};
+    uint32_t k[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)};
+#pragma unroll
+    for (int round = 0; round < 10; ++round) philox_round(c, k);
+    return (float)(c[0] >> 8) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(kThreads)
+argmax_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, int* __restrict__ out) {
+    __shared__ Best scratch[32];
+    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    Best mine = {-CUDART_INF_F, 0x7fffffff};
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > mine.value) mine = {v, i};  // ascending i per thread: the first maximum stays
+    }
+    const Best best = block_best(mine, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = best.index == 0x7fffffff ? 0 : best.index;
+}
+
+__global__ void __launch_bounds__(kThreads)
+sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, float* __restrict__ work,
+                   int* __restrict__ counts, const float* __restrict__ temperature, const int* __restrict__ top_k,
+                   const float* __restrict__ top_p, const float* __restrict__ penalty,
+                   const int* __restrict__ history, int history_stride, const int* __restrict__ history_len,
+                   const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
+                   const float* __restrict__ uniforms, int* __restrict__ out) {
+    __shared__ Best best_scratch[32];
+    __shared__ float float_scratch[32];
+    __shared__ int int_scratch[32];
+    __shared__ int histogram[256];
+    __shared__ float sorted_p[kMaxSorted];
+    __shared__ int sorted_id[kMaxSorted];
+    __shared__ int shared_int[4];
+
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)r * row_stride;
+    float* w = work + (size_t)r * vocab;
+    const float temp = temperature[r];
+    const float pen = penalty[r];
+    const bool penalised = pen > 1.0f && history && history_len[r] > 0;
+
+    if (penalised) {
+        int* cnt = counts + (size_t)r * vocab;
+        for (int i = tid; i < vocab; i += kThreads) cnt[i] = 0;
+        __syncthreads();
+        const int* h = history + (size_t)r * history_stride;
+        for (int j = tid; j < history_len[r]; j += kThreads) {
+            const int token = h[j];
+            if (token >= 0 && token < vocab) atomicAdd(&cnt[token], 1);
+        }
+        __syncthreads();
+    }
+
+    // adjusted logits, and their first maximum
+    Best mine = {-CUDART_INF_F, 0x7fffffff};
+    for (int i = tid; i < vocab; i += kThreads) {
+        float v = row[i];
+        if (penalised) {
+            const int c = counts[(size_t)r * vocab + i];
+            for (int n = 0; n < c; ++n) v = v > 0.0f ? v / pen : v * pen;
+        }
+        if (temp > 0.0f) v = v / temp;
+        w[i] = v;
+        if (v > mine.value) mine = {v, i};
+    }
+    const Best top = block_best(mine, best_scratch);
+    if (temp <= 0.0f) {
+        if (tid == 0) out[r] = top.index == 0x7fffffff ? 0 : top.index;
+        return;
+    }
+
+    // softmax over the whole vocabulary
+    float local = 0.0f;
+    for (int i = tid; i < vocab; i += kThreads) {
+        const float e = expf(w[i] - top.value);
+        w[i] = e;
+        local += e;
+    }
+    const float sum = block_sum(local, float_scratch);
+    for (int i = tid; i < vocab; i += kThreads) w[i] = w[i] / sum;
+    __syncthreads();
+
+    const float u = uniforms ? uniforms[r] : philox_uniform(seeds[r], counters[r]);
+    int k = top_k[r];
+    if (k <= 0 || k > vocab) k = vocab;
+    const float nucleus = top_p[r];
+
+    // k-th largest probability by radix select over the float bit patterns (all are >= 0)
+    uint32_t kth_bits = 0;
+    int need_ties = 0, tie_count = 0;
+    if (k < vocab) {
+        uint32_t prefix = 0, mask = 0;
+        int remaining = k;
+        for (int pass = 3; pass >= 0; --pass) {
+            const int shift = pass * 8;
+            if (tid < 256) histogram[tid] = 0;
+            __syncthreads();
+            for (int i = tid; i < vocab; i += kThreads) {
+                const uint32_t key = __float_as_uint(w[i]);
+                if ((key & mask) == prefix) atomicAdd(&histogram[(key >> shift) & 255u], 1);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int cumulative = 0, digit = 0;
+                for (int b = 255; b >= 0; --b) {
+                    if (cumulative + histogram[b] >= remaining) {
+                        digit = b;
+                        break;
+                    }
+                    cumulative += histogram[b];
+                }
+                shared_int[0] = digit;
+                shared_int[1] = remaining - cumulative;
+                shared_int[2] = histogram[digit];
+            }
+            __syncthreads();
+            prefix |= (uint32_t)shared_int[0] << shift;
+            mask |= 255u << shift;
+            remaining = shared_int[1];
+            tie_count = shared_int[2];
+            __syncthreads();
+        }
+        kth_bits = prefix;
+        need_ties = remaining;
+    }
+
+    if (k <= kMaxSorted) {
+        // gather the k candidates, sort them (probability descending, id ascending), walk them
+        if (tid == 0) shared_int[3] = 0;
+        for (int i = tid; i < kMaxSorted; i += kThreads) {
+            sorted_p[i] = -1.0f;
+            sorted_id[i] = 0x7fffffff;
+        }
+        __syncthreads();
+        const bool all_ties = (k == vocab) || tie_count == need_ties;
+        for (int i = tid; i < vocab; i += kThreads) {
+            const uint32_t key = __float_as_uint(w[i]);
+            if (k == vocab || key > kth_bits || (all_ties && key == kth_bits)) {
+                const int at = atomicAdd(&shared_int[3], 1);
+                sorted_p[at] = w[i];
+                sorted_id[at] = i;
+            }
+        }
+        __syncthreads();
+        if (!all_ties) {
+            // more tokens tie at the k-th probability than fit: the lower ids go in
+            int taken = 0;
+            const int base_count = shared_int[3];
+            for (int base = 0; base < vocab && taken < need_ties; base += kThreads) {
+                const int i = base + tid;
+                const bool tie = i < vocab && __float_as_uint(w[i]) == kth_bits;
+                int chunk_total;
+                const int rank = taken + block_flag_scan(tie, int_scratch, &chunk_total);
+                if (tie && rank < need_ties) {
+                    sorted_p[base_count + rank] = w[i];
+                    sorted_id[base_count + rank] = i;
+                }
+                taken += chunk_total;
+            }
+            __syncthreads();
+        }
+        // bitonic sort of kMaxSorted entries
+        for (int size = 2; size <= kMaxSorted; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const int partner = tid ^ stride;
+                if (partner > tid) {
+                    const bool descending_block = (tid & size) == 0;
+                    const float pa = sorted_p[tid], pb = sorted_p[partner];
+                    const int ia = sorted_id[tid], ib = sorted_id[partner];
+                    const bool a_first = pa > pb || (pa == pb && ia < ib);
+                    if (a_first != descending_block) {
+                        sorted_p[tid] = pb; sorted_p[partner] = pa;
+                        sorted_id[tid] = ib; sorted_id[partner] = ia;
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        if (tid == 0) {
+            float cumulative = 0.0f;
+            int cutoff = k;
+            for (int i = 0; i < k; ++i) {
+                cumulative += sorted_p[i];
+                if (cumulative >= nucleus) {
+                    cutoff = i + 1;
+                    break;
+                }
+            }
+            float total = 0.0f;
+            for (int i = 0; i < cutoff; ++i) total += sorted_p[i];
+            const float target = u * total;
+            float acc = 0.0f;
+            int pick = sorted_id[cutoff - 1];
+            for (int i = 0; i < cutoff; ++i) {
+                acc += sorted_p[i];
+                if (acc >= target) {
+                    pick = sorted_id[i];
+                    break;
+                }
+            }
+            out[r] = pick;
+        }
+        return;
+    }
+
+    // More than kMaxSorted candidates (the host admits this only with top_p == 1): the draw walks
+    // the kept tokens in id order, which draws from the same distribution.
+    float kept_local = 0.0f;
+    {
+        // ties at the k-th probability: the first need_ties ids are kept; find the id bound
+        int tie_bound = vocab;  // ids < tie_bound that tie are kept
+        if (k < vocab && tie_count != need_ties) {
+            int taken = 0;
+            tie_bound = 0;
+            for (int base = 0; base < vocab && taken < need_ties; base += kThreads) {
+                const int i = base + tid;
+                const bool tie = i < vocab && __float_as_uint(w[i]) == kth_bits;
+                int chunk_total;
+                const int rank = taken + block_flag_scan(tie, int_scratch, &chunk_total);
+                if (tie && rank == need_ties - 1) shared_int[3] = i + 1;
+                taken += chunk_total;
+            }
+            __syncthreads();
+            tie_bound = shared_int[3];
+        }
+        for (int i = tid; i < vocab; i += kThreads) {
+            const uint32_t key = __float_as_uint(w[i]);
+            const bool kept = k == vocab || key > kth_bits || (key == kth_bits && i < tie_bound);
+            if (!kept) w[i] = 0.0f;
+            kept_local += w[i];
+        }
+    }
+    const float total = block_sum(kept_local, float_scratch);
+    const float target = u * total;
+    if (tid == 0) {
+        shared_int[1] = 0x7fffffff;  // lowest id whose running mass reaches the target
+        shared_int[2] = -1;          // highest kept id, taken if rounding leaves the target unreached
+    }
+    __syncthreads();
+    int last_kept = -1;
+    for (int i = tid; i < vocab; i += kThreads)
+        if (w[i] > 0.0f) last_kept = i;
+    if (last_kept >= 0) atomicMax(&shared_int[2], last_kept);
+    float running = 0.0f;
+    for (int base = 0; base < vocab; base += kThreads) {
+        const int i = base + tid;
+        const float v = i < vocab ? w[i] : 0.0f;
+        float chunk_total;
+        const float inclusive = running + block_float_scan(v, float_scratch, &chunk_total);
+        if (v > 0.0f && inclusive >= target) atomicMin(&shared_int[1], i);
+        running += chunk_total;  // the same value in every thread
+        if (running >= target) break;
+    }
+    __syncthreads();
+    if (tid == 0) out[r] = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_argmax_rows(const float* logits, int row_stride, int rows, int vocab, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || row_stride < vocab) return fail("argmax_rows: vocab %d, row stride %d", vocab, row_stride);
+    argmax_rows_kernel<<<rows, kThreads, 0, stream>>>(logits, row_stride, vocab, out);
+    return check_launch("argmax_rows");
+}
+
+// Per-row arrays live on the device.  `uniforms` (optional) overrides the generator, for tests.
+// The host guarantees top_p == 1 for rows whose candidate count (top_k, or the vocabulary when
+// top_k <= 0) exceeds `mb_sample_max_sorted()`.
+MB_EXPORT int mb_sample_rows(const float* logits, int row_stride, int rows, int vocab, float* work, int* counts,
+                             const float* temperature, const int* top_k, const float* top_p, const float* penalty,
+                             const int* history, int history_stride, const int* history_len,
+                             const unsigned long long* seeds, const unsigned long long* counters,
+                             const float* uniforms, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || row_stride < vocab) return fail("sample_rows: vocab %d, row stride %d", vocab, row_stride);
+    if (!work) return fail("sample_rows: needs rows * vocab floats of scratch");
+    if (!uniforms && (!seeds || !counters)) return fail("sample_rows: needs seeds and counters, or uniforms");
+    sample_rows_kernel<<<rows, kThreads, 0, stream>>>(logits, row_stride, vocab, work, counts, temperature, top_k, top_p,
+                                                      penalty, history, history_stride, history_len, seeds, counters,
+                                                      uniforms, out);
+    return check_launch("sample_rows");
+}
+
+MB_EXPORT int mb_sample_max_sorted() { return kMaxSorted; }

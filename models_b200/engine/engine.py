@@ -1,0 +1,155 @@
+"""The engine: a model on one GPU, its cache, and the one step function everything drives.
+
+`step(entries)` runs exactly the tokens it is given, as one batch, on top of what earlier steps
+left in the cache, and returns the logits at the wanted places.  The requests of a step either all
+start (their prompts, of unequal lengths, in one step) or all go on by one token; nothing in the
+code needs that distinction -- a step may also bring several tokens to a sequence that already
+holds some -- it only decides which attention kernel is the fast one.
+
+integrallis/models has the pieces separately: whole-prompt prefill of one sequence
+(backend-java/.../llama/LlamaForwardPass.java:351-370), one token for each of several sessions
+(:471-481,709-723), logits for chosen rows only (Head.LOGITS/NONE, :984-991), and checks before any
+state changes (:933-960, :1008-1014).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import CacheFull, KvCache, StateArea
+from ..config.specs import ModelSpec
+from ..parts import RunContext, Runtime
+from .batch import StepBatch, build_step_batch
+from .model import DecoderModel
+
+
+class StepError(ValueError):
+    """A step that was refused; nothing changed."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError(
+            "models_b200 runs its own CUDA kernels and has no CPU path: a CUDA device is required "
+            f"(asked for {device}, torch.cuda.is_available() is {torch.cuda.is_available()})")
+    return device
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype: str = "bfloat16",
+                 max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0"):
+        self.device = require_cuda(device)
+        torch.cuda.set_device(self.device)
+        self.spec = spec
+        page_tokens = -(-max_tokens // 64) * 64
+        self.runtime = Runtime(self.device, dtype, max_positions=min(spec.max_positions, page_tokens))
+        self.model = DecoderModel(spec, self.runtime)
+        self.model.load(tensors)
+        cache_from = [entry.cache_from for entry in spec.schedule]
+        self.cache = KvCache(self.model.kv_requests(), cache_from, max_tokens, max_slots)
+        dtype_t = self.runtime.compute_dtype
+        self.cache_elements = self.cache.allocate_storage(
+            lambda shape: torch.zeros(shape, dtype=dtype_t, device=self.device))
+        self.state = StateArea(
+            self.model.state_requests(), self.cache.max_slots,
+            lambda shape, dt: torch.zeros(shape, dtype=dt, device=self.device))
+        self.runs: List[RunContext] = []
+        for run, entry in enumerate(spec.schedule):
+            ctx = RunContext(run=run, writes_cache=entry.cache_from is None, state=self.state.of_run(run))
+            if run in self.cache.run_location:
+                ctx.group, ctx.k_pool, ctx.v_pool = self.cache.pools(run)
+            self.runs.append(ctx)
+        self.steps = 0
+
+    # ------------------------------------------------------------------ slots
+
+    def open_slot(self) -> int:
+        slot = self.cache.open_slot()
+        self.state.reset(slot)
+        return slot
+
+    def release_slot(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    def rewind(self, slot: int, length: int) -> None:
+        if self.state.tensors:
+            raise StepError("a model with per-sequence state cannot rewind: state is not a length that can be cut")
+        self.cache.rewind(slot, length)
+
+    # ------------------------------------------------------------------ the step
+
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        vocab = self.spec.vocab_size
+        limit = self.runtime.max_positions
+        for e in entries:
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if e.slot not in self.cache.lengths:
+                raise StepError(f"slot {e.slot} is not open")
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"slot {e.slot}: a step must bring at least one token")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside the {n} tokens of this step")
+            if self.cache.lengths[e.slot] + n > limit:
+                raise StepError(
+                    f"slot {e.slot}: {self.cache.lengths[e.slot]} + {n} positions exceed the limit of {limit} "
+                    "(the model's max positions, or the size the cache was made for)")
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Appends each entry's tokens to its slot and returns float32 logits [wanted, vocab] in the
+        order of the entries and of their `want` lists (None if nothing is wanted).  A refused step
+        (StepError, CacheFull) leaves every slot as it was."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self.validate(entries)
+        appends = [(e.slot, len(e.tokens)) for e in entries]
+        self.cache.append(appends)
+        batch = build_step_batch(self.cache, [(e.slot, e.tokens, e.want) for e in entries], self.device,
+                                 state_pad_row=self.cache.max_slots)
+        logits = self.model.forward(batch, self.runs)
+        self.cache.commit(appends)
+        self.steps += 1
+        return logits
+
+    # ------------------------------------------------------------------ facts
+
+    def diagnostics(self) -> Dict[str, object]:
+        props = torch.cuda.get_device_properties(self.device)
+        element = 2 if self.runtime.mode == "bfloat16" else 4
+        from ..kernels.build import loaded_libraries
+
+        return {
+            "device": props.name,
+            "multiprocessors": props.multi_processor_count,
+            "dtype": self.runtime.mode,
+            "architecture": self.spec.architecture,
+            "cache_groups": len(self.cache.groups),
+            "cache_pages": self.cache.num_pages,
+            "page_size": self.cache.page_size,
+            "cache_bytes": self.cache_elements * element,
+            "state_bytes": self.state.bytes,
+            "max_positions": self.runtime.max_positions,
+            "kernel_libraries": loaded_libraries(),
+        }

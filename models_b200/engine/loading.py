@@ -1,0 +1,42 @@
+"""From a model folder (or a configuration and a seed) to an engine on the GPU.
+
+The order mirrors integrallis/models' load path: read the configuration, pick the architecture
+from the registry, look the tensors up by name, size the cache, build the model
+(backend-java/.../PureJavaBackend.java:128-273).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+from ..config import load_config
+from ..weights import load_tensors, random_tensors
+from .engine import Engine, require_cuda
+from .model import parameter_requests
+
+
+def engine_from_folder(folder, dtype: str = "bfloat16", max_tokens: int = 4096, max_slots: Optional[int] = None,
+                       device="cuda:0") -> Engine:
+    require_cuda(device)
+    config = load_config(folder)
+    spec = config.model_spec()
+    tensors = load_tensors(folder, parameter_requests(spec))
+    engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device)
+    engine.config = config
+    return engine
+
+
+def engine_from_config(config, seed: int, dtype: str = "bfloat16", max_tokens: int = 4096,
+                       max_slots: Optional[int] = None, device="cuda:0", std: float = 0.02,
+                       gain_std: float = 0.1) -> Engine:
+    """Random weights drawn on the device (values differ from the ones `write_random_model` draws
+    on the host for the same seed)."""
+    import torch
+
+    device = require_cuda(device)
+    spec = config.model_spec()
+    store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    tensors = random_tensors(parameter_requests(spec), seed, std, gain_std, store, device)
+    engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device)
+    engine.config = config
+    return engine

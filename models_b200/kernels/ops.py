@@ -1,0 +1,259 @@
+"""Python faces of the CUDA launchers: shape and dtype checks, then one C call on the current stream.
+
+There is no CPU path and no library stand-in: a tensor that is not on a CUDA device, or a kernel
+library that cannot be built, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+_F32, _BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 storage, got {dtype}")
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError(
+                "models_b200 kernels run on a CUDA device only (got a tensor on "
+                f"{t.device}); there is no CPU path")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _run(lib, status: int):
+    if status != 0:
+        raise KernelError(lib.mb_last_error().decode("utf-8", "replace"))
+
+
+def _int32(t: Optional[torch.Tensor], name: str):
+    if t is not None and (t.dtype != torch.int32 or not t.is_contiguous()):
+        raise KernelError(f"{name} must be a contiguous int32 tensor, got {t.dtype}")
+
+
+# ------------------------------------------------------------------------------------ libraries
+
+def elementwise():
+    return load_library("mb_elementwise", ["elementwise.cu"])
+
+
+def attention_rows():
+    return load_library("mb_attention_rows", ["attention_rows.cu"])
+
+
+def gemm32():
+    return load_library("mb_gemm_f32", ["gemm_f32.cu"])
+
+
+def sampling():
+    return load_library("mb_sampling", ["sampling.cu"])
+
+
+# ------------------------------------------------------------------------------------ element-wise
+
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Rows of `table` ([vocab, width]) picked by `tokens` (int32), as the float residual stream."""
+    _cuda(table, tokens)
+    _int32(tokens, "tokens")
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("embedding table must be a contiguous [vocab, width] matrix")
+    rows, (vocab, width) = tokens.numel(), table.shape
+    out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
+    lib = elementwise()
+    _run(lib, lib.mb_embed_gather(_p(table), _code(table.dtype), _p(tokens), _p(out), rows, width, vocab,
+                                  ctypes.c_float(scale), _stream()))
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, write_x: bool = True) -> torch.Tensor:
+    """x (float residual, [T, width]) += delta, then RMSNorm with `weight` (float).  With `rows`
+    only those rows are normalised (and x is left alone).  Returns the normalised rows."""
+    _cuda(x, delta, weight, rows)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("the residual stream must be a contiguous float32 [rows, width] tensor")
+    width = x.shape[1]
+    if weight.dtype != torch.float32 or weight.numel() != width:
+        raise KernelError(f"norm weight must be float32 of {width} elements, got {weight.dtype} of {weight.numel()}")
+    if delta is not None and (delta.shape != x.shape or not delta.is_contiguous()):
+        raise KernelError(f"delta {tuple(delta.shape)} must match the residual stream {tuple(x.shape)}")
+    _int32(rows, "rows")
+    out_rows = rows.numel() if rows is not None else x.shape[0]
+    out = torch.empty((out_rows, width), dtype=out_dtype, device=x.device)
+    lib = elementwise()
+    _run(lib, lib.mb_add_rmsnorm(_p(x), _p(delta), _code(delta.dtype) if delta is not None else 0, _p(weight), _p(out),
+                                 _code(out_dtype), _p(rows), out_rows, width, ctypes.c_float(eps),
+                                 1 if (write_x and rows is None) else 0, _stream()))
+    return out
+
+
+def rope_cache_write(qkv: torch.Tensor, positions: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                     sin: Optional[torch.Tensor], k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                     slot_mapping: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
+                     interleaved: bool, page_size: int, write_cache: bool) -> None:
+    """Rotates the query heads of `qkv` ([T, (heads + 2*kv_heads) * head_dim]) in place; rotates the
+    key heads and copies the value heads into the pools at `slot_mapping`."""
+    _cuda(qkv, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    if qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("qkv must be a [tokens, columns] tensor with unit column stride")
+    need = (heads + (2 * kv_heads if write_cache else 0)) * head_dim
+    if qkv.shape[1] < need:
+        raise KernelError(f"qkv rows have {qkv.shape[1]} columns, {need} are needed")
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    if rotary_dim > 0:
+        if cos is None or sin is None or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+            raise KernelError("rotation needs float32 cos/sin tables")
+        if cos.shape[-1] != rotary_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError(f"cos/sin tables must be contiguous [positions, {rotary_dim // 2}]")
+    if write_cache and (k_pool.dtype != qkv.dtype or v_pool.dtype != qkv.dtype):
+        raise KernelError(f"cache pools ({k_pool.dtype}) must have the dtype of qkv ({qkv.dtype})")
+    lib = elementwise()
+    _run(lib, lib.mb_rope_cache_write(_p(qkv), _code(qkv.dtype), qkv.stride(0), _p(positions), _p(cos), _p(sin),
+                                      _p(k_pool), _p(v_pool), _p(slot_mapping), qkv.shape[0], heads, kv_heads,
+                                      head_dim, rotary_dim, 1 if interleaved else 0, page_size,
+                                      1 if write_cache else 0, _stream()))
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for a [rows, 2*width] tensor whose first half of columns is the gate."""
+    _cuda(gate_up)
+    if gate_up.dim() != 2 or not gate_up.is_contiguous() or gate_up.shape[1] % 2:
+        raise KernelError("gate_up must be a contiguous [rows, 2*width] tensor")
+    rows, width = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, width), dtype=gate_up.dtype, device=gate_up.device)
+    lib = elementwise()
+    _run(lib, lib.mb_swiglu(_p(gate_up), _p(out), _code(gate_up.dtype), rows, width, _stream()))
+    return out
+
+
+def bias_add(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    _cuda(x, bias)
+    if not x.is_contiguous() or bias.dtype != torch.float32 or bias.numel() != x.shape[-1]:
+        raise KernelError("bias_add needs a contiguous x and a float32 bias of x's width")
+    lib = elementwise()
+    _run(lib, lib.mb_bias_add(_p(x), _code(x.dtype), _p(bias), x.numel() // x.shape[-1], x.shape[-1], _stream()))
+    return x
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    _cuda(x, delta)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not delta.is_contiguous() or delta.shape != x.shape:
+        raise KernelError("residual_add needs a contiguous float32 x and a delta of the same shape")
+    lib = elementwise()
+    _run(lib, lib.mb_residual_add(_p(x), _p(delta), _code(delta.dtype), ctypes.c_size_t(x.numel()), _stream()))
+    return x
+
+
+# ------------------------------------------------------------------------------------ attention
+
+def paged_attention_rows(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                         block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int,
+                         heads: int, kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> None:
+    """q: [T, >= heads*head_dim] (may be a column slice of a wider tensor); out: [T, heads*head_dim].
+    Pools: [pages, kv_heads, page_size, head_dim]."""
+    _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens)
+    _int32(block_table, "block_table")
+    _int32(cu_q, "cu_q")
+    _int32(kv_lens, "kv_lens")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("q and out need unit column stride")
+    if k_pool.dim() != 4 or k_pool.shape[1] != kv_heads or k_pool.shape[3] != head_dim or not k_pool.is_contiguous():
+        raise KernelError(f"k_pool must be contiguous [pages, {kv_heads}, page_size, {head_dim}], got {tuple(k_pool.shape)}")
+    if v_pool.shape != k_pool.shape or not v_pool.is_contiguous():
+        raise KernelError("v_pool must match k_pool")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype):
+        raise KernelError("q, out and the pools must share one dtype")
+    sequences = kv_lens.numel()
+    lib = attention_rows()
+    _run(lib, lib.mb_paged_attention_rows(_p(q), q.stride(0), _p(out), out.stride(0), _code(q.dtype), _p(k_pool),
+                                          _p(v_pool), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens),
+                                          sequences, max_q_len, heads, kv_heads, head_dim, k_pool.shape[2],
+                                          window or 0, ctypes.c_float(scale), _stream()))
+
+
+# ------------------------------------------------------------------------------------ matrix products
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, row_invariant: bool = True) -> torch.Tensor:
+    """a [m, k] . w[n, k]^T in true 32-bit arithmetic."""
+    _cuda(a, w)
+    if a.dtype != torch.float32 or w.dtype != torch.float32:
+        raise KernelError(f"gemm_f32 takes float32 operands, got {a.dtype} and {w.dtype}")
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or a.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError(f"gemm_f32: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not fit")
+    m, k = a.shape
+    n = w.shape[0]
+    c = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    lib = gemm32()
+    _run(lib, lib.mb_gemm_f32(_p(a), a.stride(0), _p(w), w.stride(0), _p(c), n, m, n, k, 1 if row_invariant else 0,
+                              _stream()))
+    return c
+
+
+# ------------------------------------------------------------------------------------ sampling
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("argmax_rows takes float32 [rows, vocab] logits")
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    lib = sampling()
+    _run(lib, lib.mb_argmax_rows(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out), _stream()))
+    return out
+
+
+def sample_max_sorted() -> int:
+    return int(sampling().mb_sample_max_sorted())
+
+
+def sample_rows(logits: torch.Tensor, work: torch.Tensor, counts: Optional[torch.Tensor], temperature: torch.Tensor,
+                top_k: torch.Tensor, top_p: torch.Tensor, penalty: torch.Tensor, history: Optional[torch.Tensor],
+                history_len: Optional[torch.Tensor], seeds: Optional[torch.Tensor], counters: Optional[torch.Tensor],
+                uniforms: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _cuda(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters, uniforms)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample_rows takes float32 [rows, vocab] logits")
+    rows, vocab = logits.shape
+    if work.dtype != torch.float32 or work.numel() < rows * vocab:
+        raise KernelError("sample_rows needs rows*vocab floats of scratch")
+    if counts is not None and (counts.dtype != torch.int32 or counts.numel() < rows * vocab):
+        raise KernelError("sample_rows needs rows*vocab int32 counters for the repetition penalty")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("penalty", penalty, torch.float32)):
+        if t.dtype != dt or t.numel() < rows:
+            raise KernelError(f"{name} must hold {rows} values of {dt}")
+    _int32(history, "history")
+    _int32(history_len, "history_len")
+    if history is not None and counts is None:
+        raise KernelError("a token history needs the counters scratch")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    lib = sampling()
+    _run(lib, lib.mb_sample_rows(_p(logits), logits.stride(0), rows, vocab, _p(work), _p(counts), _p(temperature),
+                                 _p(top_k), _p(top_p), _p(penalty), _p(history),
+                                 history.stride(0) if history is not None else 0, _p(history_len), _p(seeds),
+                                 _p(counters), _p(uniforms), _p(out), _stream()))
+    return out

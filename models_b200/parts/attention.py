@@ -1,0 +1,102 @@
+"""Grouped-query attention over the paged cache (the Llama mixer).
+
+q = Wq.xn, k = Wk.xn, v = Wv.xn (optional biases); rotation of every query and key head; keys and
+values stored at the token's position; per head softmax(q.K * scale) . V over the visible positions
+with kvHead = head / (heads / kv_heads); then Wo (integrallis/models,
+backend-java/.../llama/LlamaForwardPass.java:1061-1138,1543-1593).  q, k and v are one matrix
+product over the row-concatenated weights, which is how the reference groups them at execution
+time (tripleMatmulDispatch, backend-java/.../llama/LlamaForwardPass.java:1044-1059).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.kv_cache import KvRequest
+from ..kernels import ops
+from ..weights.loader import ParamRequest
+from .base import Mixer, RunContext
+from .linear import linear
+from .registry import build_part, register_part
+
+
+class AttentionMixer(Mixer):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} heads are no multiple of {spec.num_kv_heads} kv heads")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError(f"attention window must be positive, got {spec.window}")
+        self.q_width = spec.num_heads * spec.head_dim
+        self.kv_width = spec.num_kv_heads * spec.head_dim
+        self.position = None
+        if spec.position is not None:
+            if spec.position.rotary_dim > spec.head_dim:
+                raise ValueError(f"rotary_dim {spec.position.rotary_dim} exceeds head_dim {spec.head_dim}")
+            key = ("position", spec.position, runtime.max_positions)
+            if key not in runtime.shared:
+                runtime.shared[key] = build_part("position", spec.position, runtime)
+            self.position = runtime.shared[key]
+
+    def parameters(self):
+        s, n = self.spec, self.spec.weights
+        out = [
+            ParamRequest(n["q"], (self.q_width, s.hidden_size)),
+            ParamRequest(n["k"], (self.kv_width, s.hidden_size)),
+            ParamRequest(n["v"], (self.kv_width, s.hidden_size)),
+            ParamRequest(n["o"], (s.hidden_size, self.q_width)),
+        ]
+        if s.bias:
+            out += [
+                ParamRequest(n["q_bias"], (self.q_width,), "bias"),
+                ParamRequest(n["k_bias"], (self.kv_width,), "bias"),
+                ParamRequest(n["v_bias"], (self.kv_width,), "bias"),
+                ParamRequest(n["o_bias"], (s.hidden_size,), "bias"),
+            ]
+        return out
+
+    def load(self, tensors):
+        n, rt = self.spec.weights, self.runtime
+        q, k, v = (rt.matrix(tensors[n[r]]) for r in ("q", "k", "v"))
+        if not (q.dtype == k.dtype == v.dtype):
+            q, k, v = q.float(), k.float(), v.float()
+        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        self.w_q = self.w_qkv[: self.q_width]
+        self.w_o = rt.matrix(tensors[n["o"]])
+        self.b_qkv = self.b_o = None
+        if self.spec.bias:
+            self.b_qkv = torch.cat([rt.vector(tensors[n[r]]) for r in ("q_bias", "k_bias", "v_bias")]).contiguous()
+            self.b_q = self.b_qkv[: self.q_width].contiguous()
+            self.b_o = rt.vector(tensors[n["o_bias"]])
+
+    def kv_request(self):
+        return KvRequest(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:
+        s, dtype = self.spec, self.runtime.compute_dtype
+        if run.k_pool is None:
+            raise RuntimeError("the attention mixer needs cache pools; its run has none")
+        writes = run.writes_cache
+        qkv = linear(xn, self.w_qkv if writes else self.w_q, dtype)
+        if self.b_qkv is not None:
+            ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
+        group = batch.groups[run.group]
+        pos = self.position
+        ops.rope_cache_write(
+            qkv, batch.positions, pos.cos if pos else None, pos.sin if pos else None, run.k_pool, run.v_pool,
+            group.slot_mapping, s.num_heads, s.num_kv_heads, s.head_dim, pos.rotary_dim if pos else 0,
+            pos.interleaved if pos else False, run.k_pool.shape[2], writes)
+        attended = torch.empty((xn.shape[0], self.q_width), dtype=dtype, device=xn.device)
+        self.attend(qkv, attended, batch, group, run)
+        delta = linear(attended, self.w_o, dtype)
+        if self.b_o is not None:
+            ops.bias_add(delta, self.b_o)
+        return delta
+
+    def attend(self, qkv, attended, batch, group, run):
+        s = self.spec
+        ops.paged_attention_rows(qkv, attended, run.k_pool, run.v_pool, group.block_table, batch.cu_q, batch.kv_lens,
+                                 batch.max_q_len, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+
+
+register_part("mixer", "attention", AttentionMixer)

@@ -1,0 +1,42 @@
+"""Arrangement of a layer's parts.  "prenorm": x += mixer(norm(x)); x += feed_forward(norm(x))
+(integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1028-1182).
+
+The residual stream x stays in float32.  A block does not add its last result into x itself: it
+returns it as the pending delta, and whoever normalises next (the following block, or the final
+norm) adds it in the same kernel that normalises.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .base import Part, RunContext
+from .registry import build_part, register_part
+
+
+class PreNormBlock(Part):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
+        self.mixer = build_part("mixer", spec.mixer, runtime)
+        self.feed_forward_norm = build_part("norm", spec.feed_forward_norm, runtime)
+        self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime)
+        self.parts = [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def parameters(self):
+        return [p for part in self.parts for p in part.parameters()]
+
+    def load(self, tensors):
+        for part in self.parts:
+            part.load(tensors)
+
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], batch, run: RunContext) -> torch.Tensor:
+        xn = self.mixer_norm.forward(x, pending)
+        mixed = self.mixer.forward(xn, batch, run)
+        xn = self.feed_forward_norm.forward(x, mixed)
+        return self.feed_forward.forward(xn)
+
+
+register_part("block", "prenorm", PreNormBlock)

@@ -1,0 +1,63 @@
+"""Dense gated feed-forward: down(silu(gate(xn)) * up(xn)) (integrallis/models,
+backend-java/.../llama/LlamaForwardPass.java:1150-1178; silu(z) = z / (1 + exp(-z)),
+backend-java/.../ops/TensorOps.java:1407-1425).  gate and up are one product over row-concatenated
+weights, as the reference pairs them (dualMatmulDispatch,
+backend-java/.../llama/LlamaForwardPass.java:1153-1164).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import ParamRequest
+from .base import Part
+from .linear import linear
+from .registry import register_part
+
+
+class GatedFeedForward(Part):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if spec.activation != "silu":
+            raise ValueError(f"gated feed-forward activation {spec.activation!r} is not built (known: silu)")
+
+    def parameters(self):
+        s, n = self.spec, self.spec.weights
+        out = [
+            ParamRequest(n["gate"], (s.intermediate_size, s.hidden_size)),
+            ParamRequest(n["up"], (s.intermediate_size, s.hidden_size)),
+            ParamRequest(n["down"], (s.hidden_size, s.intermediate_size)),
+        ]
+        if s.bias:
+            out += [
+                ParamRequest(n["gate_bias"], (s.intermediate_size,), "bias"),
+                ParamRequest(n["up_bias"], (s.intermediate_size,), "bias"),
+                ParamRequest(n["down_bias"], (s.hidden_size,), "bias"),
+            ]
+        return out
+
+    def load(self, tensors):
+        n, rt = self.spec.weights, self.runtime
+        gate, up = rt.matrix(tensors[n["gate"]]), rt.matrix(tensors[n["up"]])
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = rt.matrix(tensors[n["down"]])
+        self.b_gate_up = self.b_down = None
+        if self.spec.bias:
+            self.b_gate_up = torch.cat([rt.vector(tensors[n["gate_bias"]]), rt.vector(tensors[n["up_bias"]])]).contiguous()
+            self.b_down = rt.vector(tensors[n["down_bias"]])
+
+    def forward(self, xn: torch.Tensor) -> torch.Tensor:
+        dtype = self.runtime.compute_dtype
+        gate_up = linear(xn, self.w_gate_up, dtype)
+        if self.b_gate_up is not None:
+            ops.bias_add(gate_up, self.b_gate_up)
+        delta = linear(ops.swiglu(gate_up), self.w_down, dtype)
+        if self.b_down is not None:
+            ops.bias_add(delta, self.b_down)
+        return delta
+
+
+register_part("feed_forward", "gated", GatedFeedForward)

@@ -1,0 +1,29 @@
+"""Matrix products y = x . W^T for row-major W [out, in] (integrallis/models,
+backend-java/.../ops/TensorOps.java:61-63), chosen by the weight's storage.
+
+bfloat16 weights: a library product (bfloat16 inputs, float accumulation), the place where the
+reference too calls a library (its matmul is VectorUtil.batchDotProduct of an external artifact).
+float32 weights: this package's own true-32-bit kernel, in both modes -- a matrix stored in 32-bit is
+multiplied in 32-bit.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    if not x.is_cuda:
+        raise ops.KernelError("models_b200 runs on a CUDA device only; there is no CPU path")
+    if weight.dtype == torch.float32:
+        a = x if x.dtype == torch.float32 else x.float()
+        out = ops.gemm_f32(a, weight)
+        return out if out_dtype == torch.float32 else out.to(out_dtype)
+    if weight.dtype != torch.bfloat16:
+        raise ops.KernelError(f"matrices are bfloat16 or float32, got {weight.dtype}")
+    a = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    if out_dtype == torch.float32:
+        return torch.mm(a, weight.t(), out_dtype=torch.float32)
+    return torch.mm(a, weight.t())

@@ -1,0 +1,242 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes that are
+not the engine's: widths and vocabularies that are no power of two, head sizes in steps of 16,
+odd numbers of heads and groups, rows that do not fill a tile."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-6 if dtype == torch.float32 else 1e-2
+
+
+def close(actual, expected, dtype, scale=None):
+    actual, expected = actual.double().cpu(), expected.double().cpu()
+    bound = tol(dtype) * (scale if scale is not None else float(expected.abs().max().clamp_min(1e-30)))
+    worst = float((actual - expected).abs().max())
+    assert worst <= bound, f"max abs error {worst} > {bound}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(cuda_device, dtype):
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(203, 72, generator=g).to(dtype)
+    tokens = torch.tensor([0, 202, 5, 5, 17], dtype=torch.int32)
+    out = ops.embed_gather(table.cuda(), tokens.cuda(), scale=1.5)
+    assert out.dtype == torch.float32
+    close(out, table.float()[tokens.long()] * 1.5, torch.float32)
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 2048, 5000])
+def test_add_rmsnorm(cuda_device, out_dtype, width):
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(7, width, generator=g) * 3
+    delta = (torch.randn(7, width, generator=g)).to(out_dtype)
+    weight = 1 + 0.1 * torch.randn(width, generator=g)
+    eps = 3e-6
+    xd = x.cuda()
+    out = ops.add_rmsnorm(xd, delta.cuda(), weight.cuda(), eps, out_dtype)
+    summed = x + delta.float()
+    close(xd, summed, torch.float32)
+    close(out, plain_llama.rms_norm(summed, weight, eps), out_dtype)
+    # without a delta, on chosen rows, x untouched
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    before = xd.clone()
+    out = ops.add_rmsnorm(xd, None, weight.cuda(), eps, out_dtype, rows=rows.cuda())
+    assert torch.equal(before, xd)
+    close(out, plain_llama.rms_norm(summed[rows.long()], weight, eps), out_dtype)
+    # a delta on chosen rows is added for the norm only
+    out = ops.add_rmsnorm(xd, delta.cuda(), weight.cuda(), eps, out_dtype, rows=rows.cuda())
+    assert torch.equal(before, xd)
+    close(out, plain_llama.rms_norm((summed + delta.float())[rows.long()], weight, eps), out_dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 72, 40), (5, 203, 136), (70, 130, 97), (130, 64, 256)])
+def test_gemm_f32(cuda_device, dtype, m, n, k):
+    from models_b200.kernels import ops
+
+    if dtype != torch.float32:
+        pytest.skip("the 32-bit product takes float32 only")
+    g = torch.Generator().manual_seed(2)
+    a, w = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g)
+    expected = (a.double() @ w.double().t())
+    for invariant in (True, False):
+        out = ops.gemm_f32(a.cuda(), w.cuda(), row_invariant=invariant)
+        close(out, expected, torch.float32, scale=float(expected.abs().max()) * 4)
+    # a row's result does not depend on the other rows of the call
+    alone = ops.gemm_f32(a[:1].cuda(), w.cuda(), row_invariant=True)
+    together = ops.gemm_f32(a.cuda(), w.cuda(), row_invariant=True)
+    assert torch.equal(alone[0], together[0])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_bias(cuda_device, dtype):
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(3)
+    gate_up = (torch.randn(5, 2 * 136, generator=g) * 4).to(dtype)
+    out = ops.swiglu(gate_up.cuda())
+    f = gate_up.float()
+    close(out, plain_llama.swiglu(f[:, :136], f[:, 136:]), dtype)
+    x = torch.randn(5, 203, generator=g).to(dtype)
+    bias = torch.randn(203, generator=g)
+    got = ops.bias_add(x.cuda().clone(), bias.cuda())
+    close(got, x.float() + bias, dtype)
+
+
+def _pools(pages, kv_heads, page_size, head_dim, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    k = (torch.randn(pages, kv_heads, page_size, head_dim, generator=g)).to(dtype)
+    v = (torch.randn(pages, kv_heads, page_size, head_dim, generator=g)).to(dtype)
+    return k, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+@pytest.mark.parametrize("head_dim,rotary_dim", [(16, 16), (48, 48), (64, 32)])
+def test_rope_cache_write(cuda_device, dtype, pairing, head_dim, rotary_dim):
+    from models_b200.kernels import ops
+
+    heads, kv_heads, page = 3, 2, 64
+    tokens = 9
+    g = torch.Generator().manual_seed(4)
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(tokens, width + 8, generator=g).to(dtype)  # wider rows: the stride is honoured
+    positions = torch.tensor([0, 1, 2, 63, 64, 65, 130, 7, 8], dtype=torch.int32)
+    freqs = plain_llama.rope_pair_frequencies(rotary_dim, 12345.0)
+    cos, sin = plain_llama.rope_cos_sin(torch.arange(200), freqs, None)
+    pages = 5
+    k_pool, v_pool = _pools(pages, kv_heads, page, head_dim, dtype, 5)
+    slot_mapping = torch.tensor([64 * 1 + 0, 64 * 1 + 1, 64 * 1 + 2, 64 * 1 + 63, 64 * 3 + 0, 64 * 3 + 1, 64 * 4 + 2, -1,
+                                 64 * 2 + 8], dtype=torch.int32)
+    qkv_d, k_d, v_d = qkv.cuda(), k_pool.cuda(), v_pool.cuda()
+    view = qkv_d[:, :width]
+    ops.rope_cache_write(view, positions.cuda(), cos.cuda(), sin.cuda(), k_d, v_d, slot_mapping.cuda(), heads, kv_heads,
+                         head_dim, rotary_dim, pairing == "interleaved", page, True)
+
+    def rotate(x, pos):  # x [T, h, hd] float
+        c, s = cos[pos.long()], sin[pos.long()]
+        if pairing == "half":
+            return plain_llama.rope_rotate_split_half(x, c, s)
+        pairs = rotary_dim // 2
+        x0, x1 = x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2]
+        r0, r1 = x0 * c[:, None, :] - x1 * s[:, None, :], x0 * s[:, None, :] + x1 * c[:, None, :]
+        out = x.clone()
+        out[..., 0:rotary_dim:2], out[..., 1:rotary_dim:2] = r0, r1
+        return out
+
+    f = qkv.float()[:, :width]
+    q = f[:, : heads * head_dim].reshape(tokens, heads, head_dim)
+    k = f[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(tokens, kv_heads, head_dim)
+    v = f[:, (heads + kv_heads) * head_dim:].reshape(tokens, kv_heads, head_dim)
+    close(qkv_d[:, : heads * head_dim], rotate(q, positions).reshape(tokens, -1), dtype)
+    assert torch.equal(qkv_d[:, width:].cpu(), qkv[:, width:])  # columns beyond the heads are untouched
+    ek, ev = k_pool.float().clone(), v_pool.float().clone()
+    rk = rotate(k, positions)
+    for t in range(tokens):
+        s = int(slot_mapping[t])
+        if s < 0:
+            continue
+        ek[s // page, :, s % page, :] = rk[t]
+        ev[s // page, :, s % page, :] = v[t]
+    close(k_d, ek, dtype)
+    close(v_d, ev, dtype)
+
+
+def _reference_attention(q, k_pool, v_pool, block_table, q_lens, kv_lens, heads, kv_heads, head_dim, window, scale):
+    """q [T, heads*hd] float; whole-sequence plain attention per sequence, keys gathered from the pages."""
+    page = k_pool.shape[2]
+    out = torch.zeros(q.shape[0], heads * head_dim)
+    row = 0
+    for b, (n, total) in enumerate(zip(q_lens, kv_lens)):
+        pos = torch.arange(total)
+        pages = block_table[b][pos // page].long()
+        k = k_pool.float()[pages, :, pos % page, :]  # [total, kv, hd]
+        v = v_pool.float()[pages, :, pos % page, :]
+        qfull = torch.zeros(total, heads, head_dim)
+        qfull[total - n:] = q[row:row + n].reshape(n, heads, head_dim)
+        full = plain_llama.causal_gqa_attention(qfull * (scale * math.sqrt(head_dim)), k, v, window)
+        out[row:row + n] = full[total - n:]
+        row += n
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (3, 1, 32, None), (6, 3, 48, None),
+                                                            (8, 2, 128, None), (5, 5, 80, 37), (4, 1, 64, 64)])
+def test_paged_attention_rows(cuda_device, dtype, heads, kv_heads, head_dim, window):
+    from models_b200.kernels import ops
+
+    page = 64
+    q_lens = [1, 70, 5, 1]
+    kv_lens = [1, 70, 133, 200]
+    pages_needed = [-(-n // page) for n in kv_lens]
+    total_pages = sum(pages_needed) + 1
+    k_pool, v_pool = _pools(total_pages, kv_heads, page, head_dim, dtype, 6)
+    order = torch.randperm(total_pages - 1, generator=torch.Generator().manual_seed(7)) + 1
+    block_table = torch.zeros(len(q_lens), max(pages_needed), dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages_needed):
+        block_table[b, :n] = order[at:at + n].int()
+        at += n
+    T = sum(q_lens)
+    g = torch.Generator().manual_seed(8)
+    q = torch.randn(T, heads * head_dim + 16, generator=g).to(dtype)
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
+    scale = 0.7 / math.sqrt(head_dim)
+    ops.paged_attention_rows(q.cuda()[:, : heads * head_dim], out, k_pool.cuda(), v_pool.cuda(), block_table.cuda(),
+                             cu_q.cuda(), torch.tensor(kv_lens, dtype=torch.int32).cuda(), max(q_lens), heads, kv_heads,
+                             head_dim, window, scale)
+    expected = _reference_attention(q.float()[:, : heads * head_dim], k_pool, v_pool, block_table, q_lens, kv_lens, heads,
+                                    kv_heads, head_dim, window, scale)
+    close(out, expected, dtype)
+
+
+def test_attention_finds_one_far_key(cuda_device):
+    """One key among hundreds is made to stand out; the output must be that key's value row."""
+    from models_b200.kernels import ops
+
+    heads, kv_heads, head_dim, page = 2, 1, 32, 64
+    total = 300
+    for far in (0, 63, 64, 191, 299):
+        k_pool = torch.zeros(6, kv_heads, page, head_dim)
+        v_pool = torch.randn(6, kv_heads, page, head_dim, generator=torch.Generator().manual_seed(far))
+        table = torch.tensor([[5, 2, 4, 1, 3]], dtype=torch.int32)
+        k_pool[table[0, far // page], 0, far % page, :] = 10.0
+        q = torch.ones(1, heads * head_dim)
+        out = torch.zeros(1, heads * head_dim, device="cuda")
+        ops.paged_attention_rows(q.cuda(), out, k_pool.cuda(), v_pool.cuda(), table.cuda(),
+                                 torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                                 torch.tensor([total], dtype=torch.int32).cuda(), 1, heads, kv_heads, head_dim, None, 1.0)
+        expected = v_pool[table[0, far // page], 0, far % page, :]
+        for h in range(heads):
+            assert torch.allclose(out[0, h * head_dim:(h + 1) * head_dim].cpu(), expected, atol=1e-5), far
+
+
+def test_argmax_first_maximum(cuda_device):
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(5, 5003, generator=g)
+    logits[1, 4000] = logits[1, 77] = 50.0  # a tie: the lower id wins
+    logits[2, 0] = 60.0
+    logits[3, 5002] = 60.0
+    got = ops.argmax_rows(logits.cuda()).cpu().tolist()
+    assert got == [plain_llama.plain_argmax(row) for row in logits]
+    assert got[1] == 77
