@@ -41,37 +41,58 @@ class StepBatch:
     host_slots: Tuple[int, ...]
 
 
-def build_step_batch(cache, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]], device,
-                     pad_sequences: int = 0, blocks: int = 0, state_pad_row: int = 0) -> StepBatch:
-    """entries: (slot, new tokens, wanted places among them).  The cache must already have room
-    (KvCache.append); lengths are still the ones before the step.  `pad_sequences` > len(entries)
-    appends one-token padding sequences; `blocks` fixes the page-table width (0: as needed)."""
+@dataclass(frozen=True)
+class StepLayout:
+    """Where the parts of a step lie in its one int32 buffer."""
+
+    sequences: int
+    tokens: int
+    wanted: int
+    blocks: int
+    groups: int
+
+    @property
+    def sizes(self):
+        B, T = self.sequences, self.tokens
+        return [T, T, B + 1, B, B, self.wanted] + [B * self.blocks, T] * self.groups
+
+    @property
+    def offsets(self):
+        return np.concatenate([[0], np.cumsum(self.sizes)]).astype(np.int64)
+
+    @property
+    def total(self) -> int:
+        return int(sum(self.sizes))
+
+
+def plan_layout(cache, entries, pad_sequences: int = 0, blocks: int = 0) -> StepLayout:
     B = max(len(entries), pad_sequences)
-    q_lens = [len(tokens) for _, tokens, _ in entries] + [1] * (B - len(entries))
-    T = sum(q_lens)
-    page = cache.page_size
-    n_groups = len(cache.groups)
+    T = sum(len(tokens) for _, tokens, _ in entries) + (B - len(entries))
     need_blocks = 1
     for slot, tokens, _ in entries:
-        need_blocks = max(need_blocks, -(-(cache.lengths[slot] + len(tokens)) // page))
+        need_blocks = max(need_blocks, -(-(cache.lengths[slot] + len(tokens)) // cache.page_size))
     if blocks and blocks < need_blocks:
         raise ValueError(f"page table of {blocks} blocks is too narrow, the step needs {need_blocks}")
-    width = blocks or need_blocks
     R = sum(len(want) for _, _, want in entries)
+    return StepLayout(B, T, R, blocks or need_blocks, len(cache.groups))
 
-    # one int32 buffer: tokens | positions | cu_q | kv_lens | slots | want_rows | per group (table, mapping)
-    sizes = [T, T, B + 1, B, B, R] + [B * width, T] * n_groups
-    offsets = np.concatenate([[0], np.cumsum(sizes)])
-    buf = np.zeros(int(offsets[-1]), dtype=np.int32)
+
+def pack_step(cache, entries, layout: StepLayout, buf: np.ndarray, state_pad_row: int = 0):
+    """Fills `buf` (int32, layout.total long) for the step; returns (q_lens, max_kv_len)."""
+    B, T, width, n_groups = layout.sequences, layout.tokens, layout.blocks, layout.groups
+    offsets = layout.offsets
+    buf[:] = 0
     tokens_a, positions_a, cu_q_a, kv_lens_a, slots_a, want_a = (buf[offsets[i]:offsets[i + 1]] for i in range(6))
     tables = [buf[offsets[6 + 2 * g]:offsets[7 + 2 * g]].reshape(B, width) for g in range(n_groups)]
     mappings = [buf[offsets[7 + 2 * g]:offsets[8 + 2 * g]] for g in range(n_groups)]
-
+    page = cache.page_size
+    q_lens = []
     row = 0
     wanted = 0
     max_kv = 1
     for b, (slot, tokens, want) in enumerate(entries):
         n = len(tokens)
+        q_lens.append(n)
         start = cache.lengths[slot]
         tokens_a[row:row + n] = tokens
         pos = np.arange(start, start + n, dtype=np.int32)
@@ -89,6 +110,7 @@ def build_step_batch(cache, entries: Sequence[Tuple[int, Sequence[int], Sequence
             mappings[g][row:row + n] = table[pos // page] * page + pos % page
         row += n
     for b in range(len(entries), B):  # padding sequences
+        q_lens.append(1)
         cu_q_a[b] = row
         kv_lens_a[b] = 1
         slots_a[b] = state_pad_row
@@ -96,16 +118,32 @@ def build_step_batch(cache, entries: Sequence[Tuple[int, Sequence[int], Sequence
             mappings[g][row] = -1
         row += 1
     cu_q_a[B] = row
+    return q_lens, max_kv
 
+
+def batch_from_buffer(dev: torch.Tensor, layout: StepLayout, q_lens, max_kv: int, host_slots) -> StepBatch:
+    offsets = layout.offsets
+    part = [dev[int(offsets[i]):int(offsets[i + 1])] for i in range(len(layout.sizes))]
+    B, width = layout.sequences, layout.blocks
+    groups = [GroupBatch(part[6 + 2 * g].view(B, width), part[7 + 2 * g]) for g in range(layout.groups)]
+    return StepBatch(
+        tokens=part[0], positions=part[1], cu_q=part[2], kv_lens=part[3], slots=part[4],
+        want_rows=part[5] if layout.wanted else None, groups=groups, num_sequences=B, num_tokens=layout.tokens,
+        num_wanted=layout.wanted, max_q_len=max(q_lens), max_kv_len=max_kv, q_lens=tuple(q_lens),
+        host_slots=tuple(host_slots))
+
+
+def build_step_batch(cache, entries: Sequence[Tuple[int, Sequence[int], Sequence[int]]], device,
+                     pad_sequences: int = 0, blocks: int = 0, state_pad_row: int = 0) -> StepBatch:
+    """entries: (slot, new tokens, wanted places among them).  The cache must already have room
+    (KvCache.append); lengths are still the ones before the step.  `pad_sequences` > len(entries)
+    appends one-token padding sequences; `blocks` fixes the page-table width (0: as needed)."""
+    layout = plan_layout(cache, entries, pad_sequences, blocks)
+    buf = np.zeros(layout.total, dtype=np.int32)
+    q_lens, max_kv = pack_step(cache, entries, layout, buf, state_pad_row)
     host = torch.from_numpy(buf)
     if torch.device(device).type == "cuda":
         dev = host.pin_memory().to(device, non_blocking=True)
     else:
         dev = host.to(device)
-    part = [dev[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
-    groups = [GroupBatch(part[6 + 2 * g].view(B, width), part[7 + 2 * g]) for g in range(n_groups)]
-    return StepBatch(
-        tokens=part[0], positions=part[1], cu_q=part[2], kv_lens=part[3], slots=part[4],
-        want_rows=part[5] if R else None, groups=groups, num_sequences=B, num_tokens=T, num_wanted=R,
-        max_q_len=max(q_lens), max_kv_len=max_kv, q_lens=tuple(q_lens),
-        host_slots=tuple(slot for slot, _, _ in entries))
+    return batch_from_buffer(dev, layout, q_lens, max_kv, [slot for slot, _, _ in entries])

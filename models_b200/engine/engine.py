@@ -48,12 +48,16 @@ def require_cuda(device) -> torch.device:
 
 class Engine:
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype: str = "bfloat16",
-                 max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0"):
+                 max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0",
+                 max_sequence: Optional[int] = None):
         self.device = require_cuda(device)
         torch.cuda.set_device(self.device)
         self.spec = spec
         page_tokens = -(-max_tokens // 64) * 64
-        self.runtime = Runtime(self.device, dtype, max_positions=min(spec.max_positions, page_tokens))
+        longest = min(spec.max_positions, page_tokens)
+        if max_sequence is not None:
+            longest = min(longest, max(1, max_sequence))
+        self.runtime = Runtime(self.device, dtype, max_positions=longest)
         self.model = DecoderModel(spec, self.runtime)
         self.model.load(tensors)
         cache_from = [entry.cache_from for entry in spec.schedule]
@@ -71,6 +75,15 @@ class Engine:
                 ctx.group, ctx.k_pool, ctx.v_pool = self.cache.pools(run)
             self.runs.append(ctx)
         self.steps = 0
+        self.decode_graphs = None
+
+    def enable_decode_graphs(self, max_batch: int, max_sequence: Optional[int] = None) -> None:
+        """Captures decode steps of up to `max_batch` sequences of up to `max_sequence` positions
+        as CUDA graphs (lazily, one per batch size of a ladder)."""
+        from .decode_graph import DecodeGraphs
+
+        longest = min(max_sequence or self.runtime.max_positions, self.runtime.max_positions)
+        self.decode_graphs = DecodeGraphs(self, max_batch, -(-longest // self.cache.page_size))
 
     # ------------------------------------------------------------------ slots
 
@@ -129,6 +142,24 @@ class Engine:
         batch = build_step_batch(self.cache, [(e.slot, e.tokens, e.want) for e in entries], self.device,
                                  state_pad_row=self.cache.max_slots)
         logits = self.model.forward(batch, self.runs)
+        self.cache.commit(appends)
+        self.steps += 1
+        return logits
+
+    def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
+        """One more token for each slot; logits [len(slots), vocab] for these tokens.  The same as
+        `step` with single-token entries that each want place 0, replayed from a CUDA graph when
+        graphs are enabled and the batch fits them.  The result is overwritten by the next decode."""
+        entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        graphs = self.decode_graphs
+        if graphs is None or len(entries) > graphs.max_batch:
+            return self.step(entries)
+        self.validate(entries)
+        if any(-(-(self.cache.lengths[e.slot] + 1) // self.cache.page_size) > graphs.blocks for e in entries):
+            return self.step(entries)
+        appends = [(e.slot, 1) for e in entries]
+        self.cache.append(appends)
+        logits = graphs.step([(e.slot, e.tokens, e.want) for e in entries])
         self.cache.commit(appends)
         self.steps += 1
         return logits

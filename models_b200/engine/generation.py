@@ -1,0 +1,175 @@
+"""The generation loop above the step function: batches of unequal prompts, stop tokens, sequences
+that end earlier, and as many batches one after another as there are requests.
+
+Per request it follows integrallis/models' loop (models-runtime/.../GenerationLoop.java:250-279):
+sample from the last logits; an end-of-generation token ends the request and is neither emitted
+nor counted (:263-265); otherwise the token is emitted; when it was the last one allowed, the
+request ends without running the model again (:273-275); else the token goes through the model.
+An empty prompt is refused (:148-151).  Usage counts prompt and emitted tokens (:198-199).
+
+The reference serves one request at a time; batching is this library's own: requests that fit
+start together in one prefill step and decode together, a finished request gives its slot back at
+once, and no request joins a batch that has started.  The loop only decides; it talks to the model
+through a small `Stepper`, so its decisions can be tested with a scripted one.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Iterable, List, Optional, Protocol, Sequence
+
+from ..sampling.options import SamplingOptions
+from ..sampling.sampler import RequestSampling
+
+
+@dataclass(frozen=True)
+class GenerationUsage:
+    """Exact token counts of one request (models-api/.../GenerationUsage.java:19-34)."""
+
+    prompt_tokens: int
+    completion_tokens: int
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int]
+    usage: GenerationUsage
+    finish_reason: str  # "stop": an end-of-generation token was sampled; "length": max_tokens or the context ran out
+
+
+class Stepper(Protocol):
+    """What the loop needs of a model."""
+
+    page_size: int
+    capacity_tokens: int  # positions the cache holds, in whole pages
+    max_positions: int  # longest sequence
+
+    def open_slot(self) -> int: ...
+
+    def release_slot(self, slot: int) -> None: ...
+
+    def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]): ...
+
+    def decode(self, slots: Sequence[int], tokens: Sequence[int]): ...
+
+    def sample(self, logits, requests: Sequence[RequestSampling]) -> List[int]: ...
+
+    def check_options(self, options: SamplingOptions) -> None: ...
+
+
+@dataclass
+class _Live:
+    index: int
+    prompt: List[int]
+    sampling: RequestSampling
+    limit: int  # most tokens this request may emit
+    slot: int = -1
+    tokens: List[int] = field(default_factory=list)
+    last: int = -1
+
+
+class GenerationLoop:
+    def __init__(self, stepper: Stepper, max_batch: int, stop_token_ids: Iterable[int] = ()):
+        if max_batch <= 0:
+            raise ValueError(f"max_batch must be positive, got {max_batch}")
+        self.stepper = stepper
+        self.max_batch = max_batch
+        self.stop_token_ids = frozenset(int(t) for t in stop_token_ids)
+
+    # ------------------------------------------------------------------ planning
+
+    def _pages(self, tokens: int) -> int:
+        page = self.stepper.page_size
+        return -(-tokens // page)
+
+    def plan_batches(self, prompts: Sequence[Sequence[int]], limits: Sequence[int]) -> List[List[int]]:
+        """Request indices batch by batch, in order: a batch takes requests while there are at most
+        max_batch of them and the cache can hold every one of them at its longest."""
+        budget = self.stepper.capacity_tokens // self.stepper.page_size
+        batches: List[List[int]] = []
+        current: List[int] = []
+        used = 0
+        for i, (prompt, limit) in enumerate(zip(prompts, limits)):
+            need = self._pages(len(prompt) + limit - 1)
+            if need > budget:
+                raise ValueError(
+                    f"request {i}: {len(prompt)} prompt tokens plus {limit} generated need {need} cache pages, "
+                    f"the cache has {budget}")
+            if current and (len(current) == self.max_batch or used + need > budget):
+                batches.append(current)
+                current, used = [], 0
+            current.append(i)
+            used += need
+        if current:
+            batches.append(current)
+        return batches
+
+    # ------------------------------------------------------------------ running
+
+    def run(self, prompts: Sequence[Sequence[int]], options: Sequence[SamplingOptions] | SamplingOptions,
+            on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
+        """Generates for every prompt; results keep the order of the prompts.
+        `on_token(request index, token)` is called for each emitted token, in order per request."""
+        if isinstance(options, SamplingOptions):
+            options = [options] * len(prompts)
+        if len(options) != len(prompts):
+            raise ValueError(f"{len(prompts)} prompts but {len(options)} sampling options")
+        prompts = [[int(t) for t in p] for p in prompts]
+        limits = []
+        for i, (p, o) in enumerate(zip(prompts, options)):
+            if len(p) == 0:
+                raise ValueError("prompt must not be empty" if len(prompts) == 1 else f"prompt {i} must not be empty")
+            if len(p) > self.stepper.max_positions:
+                raise ValueError(f"prompt {i} has {len(p)} tokens, the context holds {self.stepper.max_positions}")
+            self.stepper.check_options(o)
+            # the last emitted token is never fed back, so a sequence needs prompt + limit - 1 positions
+            limits.append(min(o.max_tokens, self.stepper.max_positions - len(p) + 1))
+        results: List[Optional[GenerationResult]] = [None] * len(prompts)
+        for batch in self.plan_batches(prompts, limits):
+            self._run_batch([_Live(i, prompts[i], RequestSampling(options[i], prompts[i]), limits[i]) for i in batch],
+                            results, on_token)
+        return results  # type: ignore[return-value]
+
+    def _finish(self, request: _Live, reason: str, results) -> None:
+        self.stepper.release_slot(request.slot)
+        request.slot = -1
+        results[request.index] = GenerationResult(
+            request.tokens, GenerationUsage(len(request.prompt), len(request.tokens)), reason)
+
+    def _run_batch(self, live: List[_Live], results, on_token) -> None:
+        stepper = self.stepper
+        try:
+            for r in live:
+                r.slot = stepper.open_slot()
+            logits = stepper.prefill([r.slot for r in live], [r.prompt for r in live])
+            while live:
+                sampled = stepper.sample(logits, [r.sampling for r in live])
+                going: List[_Live] = []
+                for r, token in zip(live, sampled):
+                    token = int(token)
+                    stops = self.stop_token_ids | set(r.sampling.options.stop_token_ids)
+                    if token in stops:
+                        self._finish(r, "stop", results)
+                        continue
+                    r.tokens.append(token)
+                    if r.sampling.history is not None:
+                        r.sampling.history.append(token)
+                    if on_token is not None:
+                        on_token(r.index, token)
+                    if len(r.tokens) >= r.limit:
+                        self._finish(r, "length", results)
+                        continue
+                    r.last = token
+                    going.append(r)
+                live = going
+                if live:
+                    logits = stepper.decode([r.slot for r in live], [r.last for r in live])
+        except BaseException:
+            for r in live:
+                if r.slot >= 0:
+                    try:
+                        stepper.release_slot(r.slot)
+                    except Exception:
+                        pass
+                    r.slot = -1
+            raise

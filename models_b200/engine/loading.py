@@ -16,19 +16,19 @@ from .model import parameter_requests
 
 
 def engine_from_folder(folder, dtype: str = "bfloat16", max_tokens: int = 4096, max_slots: Optional[int] = None,
-                       device="cuda:0") -> Engine:
+                       device="cuda:0", max_sequence: Optional[int] = None) -> Engine:
     require_cuda(device)
     config = load_config(folder)
     spec = config.model_spec()
     tensors = load_tensors(folder, parameter_requests(spec))
-    engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device)
+    engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device, max_sequence)
     engine.config = config
     return engine
 
 
 def engine_from_config(config, seed: int, dtype: str = "bfloat16", max_tokens: int = 4096,
                        max_slots: Optional[int] = None, device="cuda:0", std: float = 0.02,
-                       gain_std: float = 0.1) -> Engine:
+                       gain_std: float = 0.1, max_sequence: Optional[int] = None) -> Engine:
     """Random weights drawn on the device (values differ from the ones `write_random_model` draws
     on the host for the same seed)."""
     import torch
@@ -37,6 +37,6 @@ def engine_from_config(config, seed: int, dtype: str = "bfloat16", max_tokens: i
     spec = config.model_spec()
     store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
     tensors = random_tensors(parameter_requests(spec), seed, std, gain_std, store, device)
-    engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device)
+    engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device, max_sequence)
     engine.config = config
     return engine

@@ -1,0 +1,116 @@
+"""The cache's bookkeeping (no GPU): no slot or page lost, held twice or freed twice."""
+
+import random
+
+import pytest
+
+from models_b200.cache import CacheFull, FreeList, KvCache, KvRequest
+
+
+def test_free_list_never_hands_an_id_out_twice():
+    pool = FreeList(5, first=1, what="page")
+    taken = [pool.take() for _ in range(5)]
+    assert sorted(taken) == [1, 2, 3, 4, 5]
+    with pytest.raises(CacheFull):
+        pool.take()
+    pool.give_back(3)
+    with pytest.raises(ValueError, match="twice"):
+        pool.give_back(3)
+    with pytest.raises(ValueError):
+        pool.give_back(99)
+    assert pool.take() == 3  # a released id is the next one handed out
+    pool.check()
+
+
+def _cache(max_tokens=640, window=None, max_slots=None):
+    full = KvRequest(2, 16, None)
+    requests = [full, full, KvRequest(2, 16, window) if window else full]
+    return KvCache(requests, [None, None, None], max_tokens, max_slots)
+
+
+def test_groups_by_need_and_storage_shapes():
+    cache = _cache(window=100)
+    assert len(cache.groups) == 2
+    assert cache.groups[0].runs == [0, 1] and cache.groups[1].runs == [2]
+    shapes = []
+    cache.allocate_storage(lambda shape: shapes.append(shape) or shape)
+    assert shapes == [(2, 2, 11, 2, 64, 16), (1, 2, 11, 2, 64, 16)]  # 10 pages and the spare page 0
+    shared = KvCache([KvRequest(2, 16), KvRequest(2, 16)], [None, 0], 128)
+    assert shared.run_location[1] == shared.run_location[0] and shared.groups[0].runs == [0]
+    with pytest.raises(ValueError, match="kv heads"):
+        KvCache([KvRequest(2, 16), KvRequest(4, 16)], [None, 0], 128)
+
+
+def test_append_commit_release_and_refusals():
+    cache = _cache(max_tokens=256)  # 4 pages
+    a, b = cache.open_slot(), cache.open_slot()
+    cache.append([(a, 65), (b, 1)])
+    cache.commit([(a, 65), (b, 1)])
+    assert cache.length(a) == 65 and len(cache.groups[0].tables[a]) == 2
+    with pytest.raises(CacheFull):
+        cache.append([(a, 64), (b, 64)])  # needs 1 + 1 more pages... a: 129 -> 3 pages, b: 65 -> 2: 5 > 4
+    cache.check()
+    assert cache.length(a) == 65 and len(cache.groups[0].tables[a]) == 2  # a refused step changes nothing
+    with pytest.raises(ValueError, match="twice"):
+        cache.append([(a, 1), (a, 1)])
+    with pytest.raises(KeyError):
+        cache.append([(7, 1)])
+    cache.release(a)
+    with pytest.raises(KeyError):
+        cache.release(a)
+    c = cache.open_slot()
+    assert c == a and cache.length(c) == 0  # the slot is used again, empty
+    cache.append([(c, 128)])
+    cache.commit([(c, 128)])
+    cache.check()
+
+
+def test_window_group_gives_pages_back_and_rewind_knows():
+    cache = _cache(max_tokens=64 * 20, window=70)
+    s = cache.open_slot()
+    cache.append([(s, 300)])
+    cache.commit([(s, 300)])
+    full, windowed = cache.groups
+    assert [p >= 0 for p in full.tables[s]] == [True] * 5
+    # next query is at 300 and sees keys >= 231: blocks 0..2 (positions < 192) are dead
+    assert [p >= 0 for p in windowed.tables[s]] == [False, False, False, True, True]
+    cache.check()
+    with pytest.raises(ValueError, match="window"):
+        cache.rewind(s, 200)
+    cache.rewind(s, 290)
+    assert cache.length(s) == 290
+    cache.release(s)
+    cache.check()
+    assert windowed.pages.held == 0 and full.pages.held == 0
+
+
+def test_random_schedule_of_batches_loses_nothing():
+    rng = random.Random(0)
+    cache = _cache(max_tokens=64 * 40, window=90, max_slots=6)
+    live = {}
+    for _ in range(600):
+        action = rng.random()
+        if action < 0.25 and cache.slots.free:
+            live[cache.open_slot()] = 0
+        elif action < 0.8 and live:
+            chosen = rng.sample(sorted(live), rng.randint(1, len(live)))
+            appends = [(s, rng.choice([1, 1, 1, 5, 64, 130])) for s in chosen]
+            try:
+                cache.append(appends)
+            except CacheFull:
+                before = dict(cache.lengths)
+                assert before == {s: live[s] for s in live}
+                continue
+            cache.commit(appends)
+            for s, n in appends:
+                live[s] += n
+        elif live:
+            s = rng.choice(sorted(live))
+            cache.release(s)
+            del live[s]
+        cache.check()
+        assert {s: cache.length(s) for s in live} == live
+    for s in list(live):
+        cache.release(s)
+    cache.check()
+    assert cache.slots.held == 0 and all(g.pages.held == 0 for g in cache.groups)

@@ -1,0 +1,222 @@
+"""Generation through the Python entry point, sampling kernels, CUDA-graph decode, long decoding."""
+
+import numpy as np
+import pytest
+import torch
+
+from plain import plain_llama
+from tiny import TINY, TOLERANCE, make_folder, plain_logits, random_tokens, scaled_error
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen_models")
+    # larger weights than N(0, 0.02) so that logits are spread and greedy choices are not near-ties
+    return {name: make_folder(raw, seed=21 + i, tmp_path=root, std=0.08) for i, (name, raw) in enumerate(TINY.items())}
+
+
+def plain_greedy(folder, prompt, max_tokens, stop_ids=()):
+    """Greedy generation with the plain implementation; also the smallest top-2 margin met."""
+    config, weights = plain_llama.read_model_folder(folder)
+    tokens, out, margins = list(prompt), [], []
+    for _ in range(max_tokens):
+        logits = plain_llama.forward(config, weights, tokens)[-1]
+        top2 = torch.topk(logits, 2).values
+        margins.append(float(top2[0] - top2[1]))
+        nxt = plain_llama.plain_argmax(logits)
+        if nxt in stop_ids:
+            break
+        out.append(nxt)
+        tokens.append(nxt)
+    return out, margins
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(cuda_device, folders, name, dtype):
+    import models_b200
+    from models_b200 import SamplingOptions
+
+    raw = TINY[name]
+    model = models_b200.load_model(folders[name], dtype=dtype, max_batch=4, context=128)
+    prompts = [random_tokens(raw["vocab_size"], n, 30 + n) for n in (3, 17, 1, 40, 9)]
+    options = SamplingOptions(temperature=0.0, max_tokens=12)
+    results = model.generate_batch(prompts, options)  # five requests, batches of four: slots are used again
+    for prompt, result in zip(prompts, results):
+        expected, margins = plain_greedy(folders[name], prompt, 12, model.engine.spec.stop_token_ids)
+        got = result.tokens
+        if dtype == "float32":
+            assert got == expected
+        else:
+            # bfloat16 may pick the other token only where the plain top-2 margin is within rounding
+            for i, (g, e) in enumerate(zip(got, expected)):
+                if g != e:
+                    assert margins[i] < 0.05, (i, margins[i])
+                    break
+        assert result.usage.prompt_tokens == len(prompt)
+    alone = model.generate(prompts[1], options)
+    if dtype == "float32":
+        assert alone == results[1].tokens  # batch or alone: the same tokens
+    streamed = []
+    done = []
+    model.generate(prompts[1], options, models_b200.CallbackStream(streamed.append, done.append, done.append))
+    assert streamed == alone and len(done) == 1 and done[0].completion_tokens == len(alone)
+    assert list(model.stream(prompts[1], options)) == alone
+    errors = []
+    model.generate([], options, models_b200.CallbackStream(on_error=errors.append))
+    assert len(errors) == 1 and "empty" in str(errors[0])
+    model.engine.cache.check()
+    assert model.engine.cache.slots.held == 0
+    model.close()
+    model.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_with_graphs_matches_plain(cuda_device, folders, dtype):
+    """Three prompt tokens, then 200 tokens one at a time across several cache pages, in a batch with
+    a second sequence that ends early; decode steps replay CUDA graphs."""
+    import models_b200
+
+    name = "B"
+    vocab = TINY[name]["vocab_size"]
+    model = models_b200.load_model(folders[name], dtype=dtype, max_batch=2, context=256)
+    engine = model.engine
+    a, b = random_tokens(vocab, 203, 1), random_tokens(vocab, 40, 2)
+    ea, eb = plain_logits(folders[name], a), plain_logits(folders[name], b)
+    sa, sb = engine.open_slot(), engine.open_slot()
+    from models_b200.engine import StepEntry
+
+    out = engine.step([StepEntry(sa, a[:3], [2]), StepEntry(sb, b[:10], [9])])
+    assert scaled_error(out[0], ea[2]) < TOLERANCE[dtype] and scaled_error(out[1], eb[9]) < TOLERANCE[dtype]
+    for i in range(200):
+        if i < 30:
+            out = engine.decode([sa, sb], [a[3 + i], b[10 + i]])
+            assert scaled_error(out[1], eb[10 + i]) < TOLERANCE[dtype], ("b", i)
+            if i == 29:
+                engine.release_slot(sb)
+        else:
+            out = engine.decode([sa], [a[3 + i]])
+        assert scaled_error(out[0], ea[3 + i]) < TOLERANCE[dtype], ("a", i)
+    assert engine.decode_graphs is not None and set(engine.decode_graphs.captured) == {1, 2}
+    engine.release_slot(sa)
+    engine.cache.check()
+
+
+def test_graph_and_eager_decode_agree(cuda_device, folders):
+    import models_b200
+    from models_b200.engine import StepEntry
+
+    name = "A"
+    vocab = TINY[name]["vocab_size"]
+    tokens = [random_tokens(vocab, 30, s) for s in range(3)]
+    outs = []
+    for graphs in (True, False):
+        model = models_b200.load_model(folders[name], dtype="bfloat16", max_batch=4, context=128, cuda_graphs=graphs)
+        engine = model.engine
+        slots = [engine.open_slot() for _ in tokens]
+        engine.step([StepEntry(s, t[:20], []) for s, t in zip(slots, tokens)])
+        rows = []
+        for i in range(20, 30):
+            rows.append(engine.decode(slots, [t[i] for t in tokens]).clone())
+        outs.append(torch.stack(rows))
+    assert torch.equal(outs[0], outs[1])  # three live rows in a graph of four: padding changes nothing
+
+
+def expected_draw(logits, previous, options, u):
+    ids, probs = plain_llama.plain_candidates(logits, previous, options.temperature, options.top_k, options.top_p,
+                                              options.repetition_penalty)
+    total = np.float32(0)
+    for p in probs:
+        total += np.float32(p)
+    target = np.float32(u) * total
+    acc = np.float32(0)
+    for i, p in zip(ids, probs):
+        acc += np.float32(p)
+        if acc >= target:
+            return i, ids
+    return ids[-1], ids
+
+
+@pytest.mark.parametrize("vocab", [203, 5003])
+def test_sampling_kernel_follows_the_reference_pipeline(cuda_device, vocab):
+    from models_b200.sampling import BatchSampler, RequestSampling, SamplingOptions, philox_uniform
+
+    g = torch.Generator().manual_seed(vocab)
+    sampler = BatchSampler(vocab, "cuda:0")
+    cases = [
+        SamplingOptions(temperature=1.0, top_k=40, top_p=0.9, seed=1),
+        SamplingOptions(temperature=0.7, top_k=5, top_p=1.0, seed=2),
+        SamplingOptions(temperature=1.3, top_k=1000, top_p=0.5, seed=3),
+        SamplingOptions(temperature=0.0, repetition_penalty=1.5, seed=4),
+        SamplingOptions(temperature=0.9, top_k=vocab, top_p=1.0, seed=5),
+        SamplingOptions(temperature=1.0, top_k=12, top_p=0.8, repetition_penalty=1.3, seed=6),
+        SamplingOptions(temperature=0.0, seed=7),
+    ]
+    prompt = [int(t) for t in torch.randint(0, vocab, (25,), generator=g)] + [3, 3, 3]
+    requests = [RequestSampling(o, prompt) for o in cases]
+    for step in range(6):
+        logits = torch.randn(len(cases), vocab, generator=g) * 3
+        logits[:, 3] = 6.0  # a likely token that the history penalises three times
+        logits[0, 10] = logits[0, 11] = logits[0, 12] = 5.0  # ties inside the top-k
+        draws = [r.draws for r in requests]
+        got = sampler.sample(logits.cuda(), requests).tolist()
+        for row, (o, r) in enumerate(zip(cases, requests)):
+            if o.temperature == 0.0:
+                adjusted = logits[row].clone()
+                if o.repetition_penalty > 1.0:
+                    for t in r.history:
+                        adjusted[t] = adjusted[t] / o.repetition_penalty if adjusted[t] > 0 else adjusted[t] * o.repetition_penalty
+                assert got[row] == plain_llama.plain_argmax(adjusted), (step, row)
+                continue
+            u = philox_uniform(r.seed, draws[row])
+            want, ids = expected_draw(logits[row].numpy(), r.history or [], o, u)
+            if min(o.top_k, vocab) > 1024:
+                assert got[row] in ids, (step, row)  # drawn in id order: same distribution, other token
+            else:
+                assert got[row] == want, (step, row, got[row], want)
+        BatchSampler.record(requests, got)
+    with pytest.raises(ValueError, match="top_p"):
+        BatchSampler(5003, "cuda:0").check(SamplingOptions(top_k=2000, top_p=0.9))
+
+
+def test_sampling_is_reproducible_and_follows_the_distribution(cuda_device):
+    import models_b200
+    from models_b200.sampling import BatchSampler, RequestSampling, SamplingOptions
+
+    vocab = 64
+    logits = torch.zeros(1, vocab)
+    logits[0, :4] = torch.tensor([2.0, 1.0, 0.0, -1.0])
+    logits[0, 4:] = -30.0
+    sampler = BatchSampler(vocab, "cuda:0")
+    device_logits = logits.cuda()
+
+    def run(seed, top_k):
+        request = RequestSampling(SamplingOptions(temperature=1.0, top_k=top_k, top_p=1.0, seed=seed), [0])
+        return [sampler.sample(device_logits, [request]).item() for _ in range(400)]
+
+    first = run(11, 4)
+    assert first == run(11, 4) and first != run(12, 4)
+    expected = torch.softmax(logits[0, :4], 0)
+    for top_k in (4, 64):
+        draws = run(13, top_k)
+        counts = torch.bincount(torch.tensor(draws), minlength=vocab)[:4].float() / len(draws)
+        assert float((counts - expected).abs().max()) < 0.08, (top_k, counts)
+
+
+def test_temperature_generation_through_the_entry_point(cuda_device, folders):
+    import models_b200
+    from models_b200 import SamplingOptions
+
+    # float32: a row's logits are bit-identical alone and in a batch, so the draws are too
+    model = models_b200.load_model(folders["B"], dtype="float32", max_batch=4, context=128)
+    prompts = [[1, 2, 3], [9] * 20, [4]]
+    options = SamplingOptions(temperature=0.8, top_k=20, top_p=0.95, max_tokens=10, seed=5, repetition_penalty=1.1)
+    a = model.generate_batch(prompts, options)
+    b = model.generate_batch(prompts, options)
+    assert [r.tokens for r in a] == [r.tokens for r in b]  # same seed, same tokens
+    c = model.generate_batch(prompts, SamplingOptions(temperature=0.8, top_k=20, top_p=0.95, max_tokens=10, seed=6))
+    assert [r.tokens for r in a] != [r.tokens for r in c]
+    assert all(0 <= t < 320 for r in a for t in r.tokens)
+    assert model.generate_batch([[1, 2, 3]], options)[0].tokens == a[0].tokens  # alone or in a batch

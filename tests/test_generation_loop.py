@@ -1,0 +1,142 @@
+"""The generation loop's decisions, with a scripted stepper in place of a model (no GPU).
+The rules are integrallis/models' (models-runtime/.../GenerationLoop.java:250-279; its own tests:
+models-runtime/src/test/.../GenerationLoopTest.java:92-133,189-236)."""
+
+import pytest
+
+from models_b200.engine.generation import GenerationLoop
+from models_b200.sampling import SamplingOptions
+
+
+class ScriptedStepper:
+    """Each request 'generates' the tokens of its script, found by its prompt's first id."""
+
+    page_size = 64
+    max_positions = 4096
+
+    def __init__(self, scripts, capacity_tokens=64 * 64, max_slots=64):
+        self.scripts = scripts
+        self.capacity_tokens = capacity_tokens
+        self.free = list(range(max_slots - 1, -1, -1))
+        self.held = {}  # slot -> [script key, tokens seen]
+        self.calls = []
+
+    def open_slot(self):
+        slot = self.free.pop()
+        self.held[slot] = None
+        return slot
+
+    def release_slot(self, slot):
+        assert slot in self.held, "released twice"
+        del self.held[slot]
+        self.free.append(slot)
+
+    def check_options(self, options):
+        pass
+
+    def prefill(self, slots, prompts):
+        self.calls.append(("prefill", list(slots), [list(p) for p in prompts]))
+        for s, p in zip(slots, prompts):
+            self.held[s] = [p[0], 0]
+        return list(slots)
+
+    def decode(self, slots, tokens):
+        self.calls.append(("decode", list(slots), list(tokens)))
+        for s, t in zip(slots, tokens):
+            key, n = self.held[s]
+            assert t == self.scripts[key][n], "the token fed back is the one sampled"
+            self.held[s][1] += 1
+        return list(slots)
+
+    def sample(self, logits, requests):
+        return [self.scripts[self.held[s][0]][self.held[s][1]] for s in logits]
+
+
+EOS = 99
+
+
+def test_stops_at_eos_without_emitting_it_and_counts_usage():
+    stepper = ScriptedStepper({1: [10, 11, 12, EOS, 13]})
+    loop = GenerationLoop(stepper, 4, [EOS])
+    result = loop.run([[1, 2, 3]], SamplingOptions(temperature=0.0, max_tokens=50))[0]
+    assert result.tokens == [10, 11, 12] and result.finish_reason == "stop"
+    assert (result.usage.prompt_tokens, result.usage.completion_tokens) == (3, 3)
+    assert [c[0] for c in stepper.calls] == ["prefill", "decode", "decode", "decode"]
+    assert not stepper.held
+
+
+def test_max_tokens_and_the_last_token_is_not_fed_back():
+    stepper = ScriptedStepper({1: [10, 11, 12, 13, 14]})
+    result = GenerationLoop(stepper, 4, [EOS]).run([[1]], SamplingOptions(temperature=0.0, max_tokens=3))[0]
+    assert result.tokens == [10, 11, 12] and result.finish_reason == "length"
+    assert [c[0] for c in stepper.calls] == ["prefill", "decode", "decode"]  # 3 tokens, 2 model runs after prefill
+
+
+def test_any_stop_id_ends_and_request_stop_ids_add_to_the_models():
+    stepper = ScriptedStepper({1: [10, 55, 11], 2: [10, 77, 11]})
+    loop = GenerationLoop(stepper, 4, [55])
+    a, b = loop.run([[1], [2]], [SamplingOptions(temperature=0.0), SamplingOptions(temperature=0.0, stop_token_ids=(77,))])
+    assert a.tokens == [10] and b.tokens == [10] and a.finish_reason == b.finish_reason == "stop"
+
+
+def test_unequal_prompts_start_together_and_shorter_requests_end_earlier():
+    scripts = {1: [10, EOS], 2: [20, 21, 22, 23, EOS], 3: [30, 31, EOS]}
+    stepper = ScriptedStepper(scripts)
+    streamed = []
+    results = GenerationLoop(stepper, 8, [EOS]).run(
+        [[1, 0, 0, 0, 0], [2], [3, 0]], SamplingOptions(temperature=0.0, max_tokens=10),
+        on_token=lambda i, t: streamed.append((i, t)))
+    assert [r.tokens for r in results] == [[10], [20, 21, 22, 23], [30, 31]]
+    kinds = [(c[0], len(c[1])) for c in stepper.calls]
+    assert kinds == [("prefill", 3), ("decode", 3), ("decode", 2), ("decode", 1), ("decode", 1)]
+    assert [t for i, t in streamed if i == 1] == [20, 21, 22, 23]  # in token order per request
+    assert not stepper.held
+
+
+def test_batches_follow_one_another_and_slots_are_used_again():
+    scripts = {i: [100 + i, EOS] for i in range(1, 8)}
+    stepper = ScriptedStepper(scripts, max_slots=3)
+    results = GenerationLoop(stepper, 3, [EOS]).run([[i] for i in range(1, 8)], SamplingOptions(temperature=0.0))
+    assert [r.tokens for r in results] == [[100 + i] for i in range(1, 8)]
+    prefills = [c for c in stepper.calls if c[0] == "prefill"]
+    assert [len(c[1]) for c in prefills] == [3, 3, 1]
+    assert all(set(c[1]) <= {0, 1, 2} for c in prefills)
+
+
+def test_cache_budget_splits_batches_and_refuses_what_never_fits():
+    stepper = ScriptedStepper({1: [5] * 200, 2: [6] * 200}, capacity_tokens=4 * 64)
+    loop = GenerationLoop(stepper, 8, [EOS])
+    # each request may grow to 100 + 100 - 1 positions = 4 pages: one per batch
+    assert loop.plan_batches([[1] * 100, [2] * 100], [100, 100]) == [[0], [1]]
+    assert loop.plan_batches([[1] * 10, [2] * 10], [100, 100]) == [[0, 1]]
+    with pytest.raises(ValueError, match="cache pages"):
+        loop.run([[1] * 300], SamplingOptions(temperature=0.0, max_tokens=10))
+
+
+def test_empty_prompt_and_mismatched_options_are_refused_before_anything_runs():
+    stepper = ScriptedStepper({})
+    loop = GenerationLoop(stepper, 2, [EOS])
+    with pytest.raises(ValueError, match="prompt must not be empty"):
+        loop.run([[]], SamplingOptions())
+    with pytest.raises(ValueError, match="2 prompts but 1"):
+        loop.run([[1], [2]], [SamplingOptions()])
+    assert stepper.calls == []
+
+
+def test_context_limit_caps_the_generated_tokens():
+    stepper = ScriptedStepper({1: list(range(10, 40))})
+    stepper.max_positions = 8
+    result = GenerationLoop(stepper, 2, [EOS]).run([[1, 0, 0, 0, 0]], SamplingOptions(temperature=0.0, max_tokens=20))[0]
+    # positions 5, 6, 7 take three generated tokens; the fourth is sampled but never stored
+    assert len(result.tokens) == 4 and result.finish_reason == "length"
+
+
+def test_a_failing_step_gives_the_slots_back():
+    class Failing(ScriptedStepper):
+        def decode(self, slots, tokens):
+            raise RuntimeError("boom")
+
+    stepper = Failing({1: [10, 11], 2: [20, 21]})
+    with pytest.raises(RuntimeError, match="boom"):
+        GenerationLoop(stepper, 4, [EOS]).run([[1], [2]], SamplingOptions(temperature=0.0))
+    assert not stepper.held

@@ -1,0 +1,298 @@
+"""Each part alone, models put together from specs that no architecture here uses (a window in one
+layer only, a layer named twice, a run that reads another run's cache), and a toy mixer with state
+of its own that is defined here and registered without touching the package."""
+
+import math
+
+import pytest
+import torch
+
+from plain import plain_llama as P
+from tiny import TOLERANCE, scaled_error
+
+pytestmark = pytest.mark.gpu
+
+
+def _specs(hidden=80, heads=4, kv_heads=2, head_dim=16, inter=136, vocab=203, windows=(None, 24), theta=5000.0,
+           eps=2e-6, schedule=None):
+    from models_b200.config.specs import (AttentionSpec, BlockSpec, EmbeddingSpec, GatedFeedForwardSpec, HeadSpec, ModelSpec,
+                                          NormSpec, RopeSpec, ScheduleEntry)
+
+    rope = RopeSpec(rotary_dim=head_dim, theta=theta, pairing="half")
+    layers = []
+    for i, window in enumerate(windows):
+        p = f"layers.{i}."
+        layers.append(BlockSpec(
+            mixer=AttentionSpec(hidden, heads, kv_heads, head_dim, 1.0 / math.sqrt(head_dim), rope, window, False,
+                                {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"}),
+            feed_forward=GatedFeedForwardSpec(hidden, inter, "silu", False, {"gate": p + "gate", "up": p + "up", "down": p + "down"}),
+            mixer_norm=NormSpec(hidden, eps, {"weight": p + "norm1"}),
+            feed_forward_norm=NormSpec(hidden, eps, {"weight": p + "norm2"})))
+    schedule = schedule or [ScheduleEntry(i) for i in range(len(layers))]
+    return ModelSpec("test-only", vocab, hidden, 512, EmbeddingSpec(vocab, hidden, 1.0, {"weight": "embed"}), tuple(layers),
+                     tuple(schedule), NormSpec(hidden, eps, {"weight": "final_norm"}), HeadSpec(vocab, hidden, False, {"weight": "head"}))
+
+
+def _plain_forward(spec, tensors, tokens):
+    """The plain functions put together the way `spec` says, whole sequence, float32."""
+    w = {k: v.float() for k, v in tensors.items()}
+    T = len(tokens)
+    x = P.embed(w["embed"], torch.tensor(tokens))
+    kv_of_run = {}
+    for run, entry in enumerate(spec.schedule):
+        layer = spec.layers[entry.layer]
+        m, names = layer.mixer, layer.mixer.weights
+        xn = P.rms_norm(x, w[layer.mixer_norm.weights["weight"]], layer.mixer_norm.eps)
+        freqs = P.rope_pair_frequencies(m.position.rotary_dim, m.position.theta)
+        cos, sin = P.rope_cos_sin(torch.arange(T), freqs, None)
+        q = P.rope_rotate_split_half(P.linear(xn, w[names["q"]]).reshape(T, m.num_heads, m.head_dim), cos, sin)
+        if entry.cache_from is None:
+            k = P.rope_rotate_split_half(P.linear(xn, w[names["k"]]).reshape(T, m.num_kv_heads, m.head_dim), cos, sin)
+            v = P.linear(xn, w[names["v"]]).reshape(T, m.num_kv_heads, m.head_dim)
+            kv_of_run[run] = (k, v)
+        else:
+            k, v = kv_of_run[entry.cache_from]
+        x = x + P.linear(P.causal_gqa_attention(q, k, v, m.window), w[names["o"]])
+        f = layer.feed_forward.weights
+        xn = P.rms_norm(x, w[layer.feed_forward_norm.weights["weight"]], layer.feed_forward_norm.eps)
+        x = x + P.feed_forward(xn, w[f["gate"]], w[f["up"]], w[f["down"]])
+    return P.linear(P.rms_norm(x, w["final_norm"], spec.final_norm.eps), w["head"])
+
+
+def _engine(spec, dtype, seed=1, max_tokens=1024):
+    from models_b200.engine import Engine, parameter_requests
+    from models_b200.weights import random_tensors
+
+    tensors = random_tensors(parameter_requests(spec), seed, std=0.05)
+    return Engine(spec, tensors, dtype, max_tokens), tensors
+
+
+def _tokens(n, vocab, seed):
+    return [int(t) for t in torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed))]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_different_mixers_in_different_layers(cuda_device, dtype):
+    """Layer 0 sees all keys, layer 1 a window of 24: two cache groups, each with storage of its own;
+    whole prompts, then token by token across the window's edge and across pages."""
+    from models_b200.engine import StepEntry
+
+    spec = _specs(windows=(None, 24))
+    engine, tensors = _engine(spec, dtype)
+    assert len(engine.cache.groups) == 2
+    tokens = _tokens(150, spec.vocab_size, 0)
+    expected = _plain_forward(spec, tensors, tokens)
+    slot = engine.open_slot()
+    out = engine.step([StepEntry(slot, tokens[:100], list(range(100)))])
+    assert scaled_error(out, expected[:100]) < TOLERANCE[dtype]
+    for i in range(100, 150):
+        out = engine.step([StepEntry(slot, [tokens[i]], [0])])
+        assert scaled_error(out[0], expected[i]) < TOLERANCE[dtype], i
+    full, windowed = engine.cache.groups
+    assert sum(p >= 0 for p in full.tables[slot]) == 3 and sum(p >= 0 for p in windowed.tables[slot]) == 2
+    engine.release_slot(slot)
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_names_a_layer_twice_and_shares_a_cache(cuda_device, dtype):
+    from models_b200.config.specs import ScheduleEntry
+    from models_b200.engine import StepEntry
+
+    schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_from=1)]
+    spec = _specs(windows=(None, None), schedule=schedule, heads=3, kv_heads=1, head_dim=32, hidden=96)
+    engine, tensors = _engine(spec, dtype, seed=2)
+    assert engine.cache.groups[0].runs == [0, 1, 2]  # run 3 owns no storage
+    a, b = _tokens(70, spec.vocab_size, 1), _tokens(9, spec.vocab_size, 2)
+    ea, eb = _plain_forward(spec, tensors, a), _plain_forward(spec, tensors, b)
+    sa, sb = engine.open_slot(), engine.open_slot()
+    out = engine.step([StepEntry(sa, a[:60], [0, 59]), StepEntry(sb, b[:5], [4])])
+    assert scaled_error(out[0], ea[0]) < TOLERANCE[dtype] and scaled_error(out[1], ea[59]) < TOLERANCE[dtype]
+    assert scaled_error(out[2], eb[4]) < TOLERANCE[dtype]
+    for i in range(4):
+        out = engine.step([StepEntry(sa, [a[60 + i]], [0]), StepEntry(sb, [b[5 + i]], [0])])
+        assert scaled_error(out[0], ea[60 + i]) < TOLERANCE[dtype] and scaled_error(out[1], eb[5 + i]) < TOLERANCE[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_parts_alone(cuda_device, dtype):
+    """Norm, position tables, feed-forward and the attention mixer, each built from its spec alone."""
+    from models_b200.cache import KvCache
+    from models_b200.config.specs import RopeScalingSpec, RopeSpec
+    from models_b200.engine.batch import build_step_batch
+    from models_b200.parts import RunContext, Runtime, build_part
+    from models_b200.weights import random_tensors
+
+    runtime = Runtime(torch.device("cuda:0"), dtype, max_positions=300)
+    compute = runtime.compute_dtype
+    spec = _specs(windows=(None,), hidden=72, heads=6, kv_heads=2, head_dim=48, inter=200)
+    layer = spec.layers[0]
+    tol = TOLERANCE[dtype]
+    g = torch.Generator().manual_seed(5)
+
+    # norm (with the add that precedes it)
+    norm = build_part("norm", layer.mixer_norm, runtime)
+    tensors = random_tensors({r.name: r for r in norm.parameters()}, 1)
+    norm.load(tensors)
+    x = torch.randn(9, 72, generator=g)
+    delta = torch.randn(9, 72, generator=g).to(compute)
+    xd = x.cuda()
+    out = norm.forward(xd, delta.cuda())
+    gain = tensors["layers.0.norm1"].float()
+    assert scaled_error(out, P.rms_norm(x + delta.float(), gain, layer.mixer_norm.eps)) < tol
+    assert scaled_error(xd, x + delta.float()) < 1e-6
+
+    # position tables: llama3 scaling, linear scaling, plain
+    for scaling in (None, RopeScalingSpec("linear", 4.0), RopeScalingSpec("llama3", 8.0, 1.0, 4.0, 64)):
+        rope = build_part("position", RopeSpec(32, 500000.0, "half", scaling), runtime)
+        freqs = P.rope_pair_frequencies(32, 500000.0)
+        divisors, scale = None, 1.0
+        if scaling is not None and scaling.kind == "llama3":
+            divisors = P.llama3_pair_divisors(freqs, 8.0, 1.0, 4.0, 64)
+        if scaling is not None and scaling.kind == "linear":
+            scale = 0.25
+        cos, sin = P.rope_cos_sin(torch.arange(300), freqs, divisors, scale)
+        assert torch.equal(rope.cos.cpu(), cos) and torch.equal(rope.sin.cpu(), sin)
+
+    # feed-forward
+    ffn = build_part("feed_forward", layer.feed_forward, runtime)
+    tensors = random_tensors({r.name: r for r in ffn.parameters()}, 2, std=0.1)
+    ffn.load(tensors)
+    xn = torch.randn(9, 72, generator=g).to(compute)
+    w = {k: v.float() for k, v in tensors.items()}
+    expected = P.feed_forward(xn.float(), w["layers.0.gate"], w["layers.0.up"], w["layers.0.down"])
+    assert scaled_error(ffn.forward(xn.cuda()), expected) < tol
+
+    # attention mixer over a cache of its own: a prompt of 70, then 3 single tokens
+    mixer = build_part("mixer", layer.mixer, runtime)
+    tensors = random_tensors({r.name: r for r in mixer.parameters()}, 3, std=0.1)
+    mixer.load(tensors)
+    w = {k: v.float() for k, v in tensors.items()}
+    cache = KvCache([mixer.kv_request()], [None], 256)
+    cache.allocate_storage(lambda shape: torch.zeros(shape, dtype=compute, device="cuda:0"))
+    group, k_pool, v_pool = cache.pools(0)
+    run = RunContext(0, group, k_pool, v_pool, True, None)
+    slot = cache.open_slot()
+    T = 73
+    xn = torch.randn(T, 72, generator=g).to(compute)
+    m = layer.mixer
+    cos, sin = P.rope_cos_sin(torch.arange(T), P.rope_pair_frequencies(48, m.position.theta), None)
+    q = P.rope_rotate_split_half(P.linear(xn.float(), w["layers.0.q"]).reshape(T, 6, 48), cos, sin)
+    k = P.rope_rotate_split_half(P.linear(xn.float(), w["layers.0.k"]).reshape(T, 2, 48), cos, sin)
+    v = P.linear(xn.float(), w["layers.0.v"]).reshape(T, 2, 48)
+    expected = P.linear(P.causal_gqa_attention(q, k, v), w["layers.0.o"])
+    rows = []
+    for begin, end in ((0, 70), (70, 71), (71, 72), (72, 73)):
+        cache.append([(slot, end - begin)])
+        batch = build_step_batch(cache, [(slot, [0] * (end - begin), [])], "cuda:0")
+        rows.append(mixer.forward(xn[begin:end].cuda(), batch, run))
+        cache.commit([(slot, end - begin)])
+    assert scaled_error(torch.cat(rows), expected) < tol
+
+
+class RunningMeanMixer:
+    """A toy mixer with state of its own and no keys or values: it returns, for every token, the mean
+    of all inputs of its sequence so far, times a learned gain.  Per sequence it keeps the running sum
+    and the count in the state area.  It exists only in this test."""
+
+    def __init__(self, spec, runtime):
+        self.spec, self.runtime = spec, runtime
+
+    def parameters(self):
+        from models_b200.weights import ParamRequest
+
+        return [ParamRequest(self.spec.weights["gain"], (self.spec.hidden_size,), "gain")]
+
+    def load(self, tensors):
+        self.gain = self.runtime.vector(tensors[self.spec.weights["gain"]])
+
+    def kv_request(self):
+        return None
+
+    def state_request(self):
+        from models_b200.cache import StateRequest
+
+        return StateRequest((self.spec.hidden_size + 1,), torch.float32)
+
+    def forward(self, xn, batch, run):
+        out = torch.empty_like(xn)
+        slots = batch.slots.tolist()
+        cu = batch.cu_q.tolist()
+        for b in range(batch.num_sequences):
+            state = run.state[slots[b]]
+            rows = xn[cu[b]:cu[b + 1]].float()
+            sums = state[:-1] + rows.cumsum(0)
+            counts = state[-1] + torch.arange(1, rows.shape[0] + 1, device=xn.device)
+            out[cu[b]:cu[b + 1]] = (sums / counts[:, None] * self.gain).to(xn.dtype)
+            state[:-1] = sums[-1]
+            state[-1] = counts[-1]
+        return out
+
+
+def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(cuda_device):
+    from dataclasses import dataclass, field
+
+    from models_b200.config.specs import BlockSpec, ModelSpec, ScheduleEntry
+    from models_b200.engine import StepEntry
+    from models_b200.parts import register_part, unregister_part
+
+    @dataclass(frozen=True)
+    class RunningMeanSpec:
+        hidden_size: int
+        weights: dict = field(default_factory=dict, hash=False, compare=False)
+        kind: str = "test_running_mean"
+
+    register_part("mixer", "test_running_mean", RunningMeanMixer)
+    try:
+        base = _specs(windows=(None, None))
+        toy = BlockSpec(RunningMeanSpec(base.hidden_size, {"gain": "layers.1.mean_gain"}), base.layers[1].feed_forward,
+                        base.layers[1].mixer_norm, base.layers[1].feed_forward_norm)
+        spec = ModelSpec(base.architecture, base.vocab_size, base.hidden_size, base.max_positions, base.embedding,
+                         (base.layers[0], toy), (ScheduleEntry(0), ScheduleEntry(1)), base.final_norm, base.head)
+        engine, tensors = _engine(spec, "float32", seed=4, max_tokens=512)
+        assert engine.state.of_run(1).shape == (engine.cache.max_slots + 1, base.hidden_size + 1)
+        assert engine.state.of_run(0) is None and len(engine.cache.groups) == 1
+
+        def plain(tokens):
+            w = {k: v.float() for k, v in tensors.items()}
+            T = len(tokens)
+            x = P.embed(w["embed"], torch.tensor(tokens))
+            l0 = spec.layers[0]
+            m = l0.mixer
+            xn = P.rms_norm(x, w["layers.0.norm1"], l0.mixer_norm.eps)
+            cos, sin = P.rope_cos_sin(torch.arange(T), P.rope_pair_frequencies(m.head_dim, m.position.theta), None)
+            q = P.rope_rotate_split_half(P.linear(xn, w["layers.0.q"]).reshape(T, m.num_heads, m.head_dim), cos, sin)
+            k = P.rope_rotate_split_half(P.linear(xn, w["layers.0.k"]).reshape(T, m.num_kv_heads, m.head_dim), cos, sin)
+            v = P.linear(xn, w["layers.0.v"]).reshape(T, m.num_kv_heads, m.head_dim)
+            x = x + P.linear(P.causal_gqa_attention(q, k, v), w["layers.0.o"])
+            x = x + P.feed_forward(P.rms_norm(x, w["layers.0.norm2"], l0.feed_forward_norm.eps), w["layers.0.gate"],
+                                   w["layers.0.up"], w["layers.0.down"])
+            xn = P.rms_norm(x, w["layers.1.norm1"], toy.mixer_norm.eps)
+            x = x + xn.cumsum(0) / torch.arange(1, T + 1)[:, None] * w["layers.1.mean_gain"]
+            x = x + P.feed_forward(P.rms_norm(x, w["layers.1.norm2"], toy.feed_forward_norm.eps), w["layers.1.gate"],
+                                   w["layers.1.up"], w["layers.1.down"])
+            return P.linear(P.rms_norm(x, w["final_norm"], spec.final_norm.eps), w["head"])
+
+        for round_index in range(2):  # the second round takes the first one's slots: the state starts at zero again
+            a, b = _tokens(20, spec.vocab_size, 10 + round_index), _tokens(7, spec.vocab_size, 20 + round_index)
+            ea, eb = plain(a), plain(b)
+            sa, sb = engine.open_slot(), engine.open_slot()
+            out = engine.step([StepEntry(sa, a[:12], [11]), StepEntry(sb, b[:3], [2])])
+            assert scaled_error(out[0], ea[11]) < 1e-4 and scaled_error(out[1], eb[2]) < 1e-4
+            for i in range(4):
+                out = engine.step([StepEntry(sa, [a[12 + i]], [0]), StepEntry(sb, [b[3 + i]], [0])])
+                assert scaled_error(out[0], ea[12 + i]) < 1e-4 and scaled_error(out[1], eb[3 + i]) < 1e-4
+            engine.release_slot(sa)
+            engine.release_slot(sb)
+    finally:
+        unregister_part("mixer", "test_running_mean")
+
+
+def test_missing_kind_and_cpu_tensors_fail_loudly(cuda_device):
+    from models_b200.kernels import ops
+    from models_b200.parts import Runtime, build_part
+
+    with pytest.raises(ValueError, match="no mixer of kind 'nope'"):
+        build_part("mixer", type("S", (), {"kind": "nope"})(), Runtime(torch.device("cuda:0"), "float32"))
+    with pytest.raises(ops.KernelError, match="no CPU path"):
+        ops.swiglu(torch.zeros(2, 4))
