@@ -14,6 +14,7 @@ from typing import Dict, List, Sequence
 import numpy as np
 import torch
 
+from ..kernels import ops
 from .batch import StepLayout, batch_from_buffer, pack_step
 
 
@@ -46,8 +47,11 @@ class _Captured:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize(engine.device)
         self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
         with torch.cuda.graph(self.graph, pool=pool, stream=stream):
             self.logits = engine.model.forward(self.batch, engine.runs)
+        self.kernels = ops.launch_count() - before  # this package's kernels inside one replay
+        ops.add_launches(-self.kernels)  # a capture launches nothing
 
 
 class DecodeGraphs:
@@ -76,4 +80,5 @@ class DecodeGraphs:
         pack_step(engine.cache, entries, captured.layout, captured.host_np, engine.cache.max_slots)
         captured.dev.copy_(captured.host, non_blocking=True)
         captured.graph.replay()
+        ops.add_launches(captured.kernels)
         return captured.logits[: len(entries)]

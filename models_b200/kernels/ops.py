@@ -44,9 +44,22 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Launches of this package's own kernels so far (graph replays count the kernels they hold)."""
+    return _launches[0]
+
+
+def add_launches(n: int) -> None:
+    _launches[0] += n
+
+
 def _run(lib, status: int):
     if status != 0:
         raise KernelError(lib.mb_last_error().decode("utf-8", "replace"))
+    _launches[0] += 1
 
 
 def _int32(t: Optional[torch.Tensor], name: str):
