@@ -1,0 +1,537 @@
+// Causal grouped-query attention over the paged cache on the tensor cores (bfloat16 storage,
+// float accumulation and softmax), compiled for one head size: -DMB_HEAD_DIM=<multiple of 16>.
+//
+// Two kernels share the tile machinery:
+//   * decode: one new token per sequence.  The query heads that share a kv head form the rows of
+//     one 16-row MMA tile, so keys and values are read once for the whole group.  A sequence's keys
+//     are split over several blocks; partial results (running maximum, sum, unnormalised output)
+//     go to scratch memory and a small kernel combines them.
+//   * prefill: any number of new tokens per sequence.  A block takes 64 consecutive query tokens of
+//     one head (16 per warp) and walks the visible key tiles.
+// A tile is the 64 positions of one cache page of one kv head: [64][head_dim], contiguous in the
+// pool.  Tiles are brought to shared memory with cp.async, two stages deep, into rows padded by
+// 16 bytes so that ldmatrix reads are conflict-free.
+//
+// Formula: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1543-1670 (kvHead =
+// head / group; dot first, then scale; only positions <= the query's are read; with a window of n
+// only the n positions that end at the query) and backend-java/.../ops/TensorOps.java:1247-1279
+// (softmax), here in its running form.  Probabilities are rounded to bfloat16 for the P.V product.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+#ifndef MB_HEAD_DIM
+#error "compile with -DMB_HEAD_DIM=<head size>"
+#endif
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int HD = MB_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
+constexpr int kTile = 64;                 // keys per tile, one cache page
+constexpr int kRowBytes = HD * 2 + 16;    // padded shared-memory row
+constexpr int kTileBytes = kTile * kRowBytes;
+constexpr int kChunks = HD / 8;           // 16-byte pieces of a row
+constexpr int kKSteps = HD / 16;
+constexpr int kThreads = 128;
+constexpr int kQRowsDecode = 16;
+constexpr int kQRowsPrefill = 64;
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One page of one kv head -> a padded tile in shared memory (all threads of the block).
+__device__ __forceinline__ void load_tile(uint32_t dst, const bf16* __restrict__ pool, size_t page, int kv_head,
+                                          int kv_heads) {
+    const bf16* src = pool + (page * kv_heads + kv_head) * (size_t)(kTile * HD);
+    for (int i = threadIdx.x; i < kTile * kChunks; i += kThreads) {
+        const int row = i / kChunks, chunk = i % kChunks;
+        cp_async16(dst + row * kRowBytes + chunk * 16, src + row * HD + chunk * 8);
+    }
+}
+
+// Rows of queries -> padded rows in shared memory; rows >= valid are zero.
+__device__ __forceinline__ void load_queries(unsigned char* dst, const bf16* __restrict__ q_first_row, size_t row_stride,
+                                             int rows, int valid) {
+    for (int i = threadIdx.x; i < rows * kChunks; i += kThreads) {
+        const int row = i / kChunks, chunk = i % kChunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < valid) v = *reinterpret_cast<const uint4*>(q_first_row + (size_t)row * row_stride + chunk * 8);
+        *reinterpret_cast<uint4*>(dst + row * kRowBytes + chunk * 16) = v;
+    }
+}
+
+// Query fragments of one warp's 16 rows for every 16-wide step over the head.
+__device__ __forceinline__ void load_q_fragments(uint32_t (&a)[kKSteps][4], uint32_t q_rows_base) {
+    const int lane = threadIdx.x & 31;
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) ldmatrix_x4(a[ks], q_rows_base + row * kRowBytes + (ks * 2 + (lane >> 4)) * 16);
+}
+
+// S[16 x 16 keys] for keys key0..key0+15 of a tile: two 8-key accumulators.
+__device__ __forceinline__ void scores_16_keys(float (&s)[2][4], const uint32_t (&a)[kKSteps][4], uint32_t k_tile, int key0) {
+    const int lane = threadIdx.x & 31;
+    const int key = key0 + (lane & 7) + ((lane >> 4) & 1) * 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[0][i] = s[1][i] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+        uint32_t b[4];
+        ldmatrix_x4(b, k_tile + key * kRowBytes + (ks * 2 + ((lane >> 3) & 1)) * 16);
+        mma_bf16(s[0], a[ks], b[0], b[1]);
+        mma_bf16(s[1], a[ks], b[2], b[3]);
+    }
+}
+
+// O[16 x HD] += P[16 x 16 keys] . V[16 keys x HD]
+__device__ __forceinline__ void accumulate_16_keys(float (&o)[HD / 8][4], const uint32_t (&p)[4], uint32_t v_tile, int key0) {
+    const int lane = threadIdx.x & 31;
+    const int key = key0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_tile + key * kRowBytes + (dp * 2 + (lane >> 4)) * 16);
+        mma_bf16(o[2 * dp], p, b[0], b[1]);
+        mma_bf16(o[2 * dp + 1], p, b[2], b[3]);
+    }
+}
+
+__device__ __forceinline__ float quad_max(float v) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// ------------------------------------------------------------------------------------------ decode
+
+// grid (splits, kv_heads * head_chunks, sequences).  Rows of the MMA tile are the (up to 16) query
+// heads of one kv head; each of the 4 warps takes 16 of a tile's 64 keys.
+__global__ void __launch_bounds__(kThreads)
+decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out, int out_row_stride,
+                        const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                        const int* __restrict__ kv_lens, int heads, int kv_heads, int head_chunks, int window,
+                        float scale, int splits, float* __restrict__ partial_o, float* __restrict__ partial_ml) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char* q_smem = smem;                                 // 16 rows
+    unsigned char* stage_smem = smem + kQRowsDecode * kRowBytes;  // 2 stages x (K tile, V tile)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
+    const int split = blockIdx.x, seq = blockIdx.z;
+    const int kv_head = blockIdx.y / head_chunks, chunk = blockIdx.y % head_chunks;
+    const int group = heads / kv_heads;
+    const int head0 = kv_head * group + chunk * 16;
+    const int rows_here = min(16, group - chunk * 16);
+    const int q_row = cu_q[seq];
+    const int kv_len = kv_lens[seq];
+    const int pos = kv_len - 1;
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first_tile = first / kTile;
+    const int tiles = (kv_len + kTile - 1) / kTile - first_tile;
+    const int per_split = (tiles + splits - 1) / splits;
+    const int t_begin = first_tile + split * per_split;
+    const int t_end = min(t_begin + per_split, first_tile + tiles);
+
+    if (t_begin >= t_end) {  // nothing for this split: an empty partial
+        if (threadIdx.x < rows_here) {
+            float* ml = partial_ml + ((size_t)(seq * heads + head0 + threadIdx.x) * splits + split) * 2;
+            ml[0] = -CUDART_INF_F;
+            ml[1] = 0.0f;
+        }
+        return;
+    }
+
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const uint32_t stage_base = smem_u32(stage_smem);
+    load_tile(stage_base, k_pool, table[t_begin], kv_head, kv_heads);
+    load_tile(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads);
+    cp_async_commit();
+    load_queries(q_smem, q + (size_t)q_row * q_row_stride + (size_t)head0 * HD, HD, kQRowsDecode, rows_here);
+    __syncthreads();
+    uint32_t a[kKSteps][4];
+    load_q_fragments(a, smem_u32(q_smem));
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end) {
+            const uint32_t next = stage_base + (stage ^ 1) * 2 * kTileBytes;
+            load_tile(next, k_pool, table[t + 1], kv_head, kv_heads);
+            load_tile(next + kTileBytes, v_pool, table[t + 1], kv_head, kv_heads);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t k_tile = stage_base + stage * 2 * kTileBytes, v_tile = k_tile + kTileBytes;
+        const int key0 = warp * 16;
+        const int abs0 = t * kTile + key0;
+        if (abs0 <= pos && abs0 + 15 >= first) {  // this warp's 16 keys hold something visible
+            float s[2][4];
+            scores_16_keys(s, a, k_tile, key0);
+            float tile_max = -CUDART_INF_F;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = abs0 + nt * 8 + tid4 * 2 + (i & 1);
+                    s[nt][i] = (key >= first && key <= pos) ? s[nt][i] * scale : -CUDART_INF_F;
+                }
+            // one token: both rows of a lane see the same keys, so one maximum test serves the mask
+            float row_max[2] = {fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])),
+                                fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]))};
+            uint32_t p[4];
+            float probs[2][4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                tile_max = quad_max(row_max[r]);
+                const float new_max = fmaxf(run_max[r], tile_max);  // finite: a visible key exists
+                const float correction = expf(run_max[r] - new_max);
+                run_max[r] = new_max;
+                float local = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const float e = expf(s[nt][2 * r + c] - new_max);
+                        probs[nt][2 * r + c] = e;
+                        local += e;
+                    }
+                run_sum[r] = run_sum[r] * correction + local;
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i) {
+                    o[i][2 * r] *= correction;
+                    o[i][2 * r + 1] *= correction;
+                }
+            }
+            p[0] = pack_bf16(probs[0][0], probs[0][1]);
+            p[1] = pack_bf16(probs[0][2], probs[0][3]);
+            p[2] = pack_bf16(probs[1][0], probs[1][1]);
+            p[3] = pack_bf16(probs[1][2], probs[1][3]);
+            accumulate_16_keys(o, p, v_tile, key0);
+        }
+        __syncthreads();  // the stage is free for the load after next
+    }
+    run_sum[0] = quad_sum(run_sum[0]);
+    run_sum[1] = quad_sum(run_sum[1]);
+
+    // merge the four warps' partial results through shared memory (the stages are free now)
+    float* merge_o = reinterpret_cast<float*>(stage_smem);         // [4 warps][16 rows][HD]
+    float* merge_ml = merge_o + 4 * 16 * HD;                        // [4 warps][16 rows][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = group_id + 8 * r;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            float* dst = merge_o + ((size_t)(warp * 16 + row)) * HD + i * 8 + tid4 * 2;
+            dst[0] = o[i][2 * r];
+            dst[1] = o[i][2 * r + 1];
+        }
+        if (tid4 == 0) {
+            merge_ml[(warp * 16 + row) * 2] = run_max[r];
+            merge_ml[(warp * 16 + row) * 2 + 1] = run_sum[r];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows_here * HD; i += kThreads) {
+        const int row = i / HD, d = i % HD;
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
+        float total = 0.0f, value = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float weight = expf(merge_ml[(w * 16 + row) * 2] - m);  // exp(-inf) = 0 for a warp that saw nothing
+            total += merge_ml[(w * 16 + row) * 2 + 1] * weight;
+            value += merge_o[(size_t)(w * 16 + row) * HD + d] * weight;
+        }
+        const int head = head0 + row;
+        if (splits == 1) {
+            out[(size_t)q_row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(value * (1.0f / total));
+        } else {
+            const size_t slot = (size_t)(seq * heads + head) * splits + split;
+            partial_o[slot * HD + d] = value;
+            if (d == 0) {
+                partial_ml[slot * 2] = m;
+                partial_ml[slot * 2 + 1] = total;
+            }
+        }
+    }
+}
+
+// grid (heads, sequences), HD threads... one thread per output coordinate (strided).
+__global__ void combine_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                                      bf16* __restrict__ out, int out_row_stride, const int* __restrict__ cu_q,
+                                      int heads, int splits) {
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const size_t base = (size_t)(seq * heads + head) * splits;
+    float m = -CUDART_INF_F;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, partial_ml[(base + s) * 2]);
+    float total = 0.0f;
+    for (int s = 0; s < splits; ++s) total += partial_ml[(base + s) * 2 + 1] * expf(partial_ml[(base + s) * 2] - m);
+    const float inv = 1.0f / total;
+    const int row = cu_q[seq];
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float value = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float weight = expf(partial_ml[(base + s) * 2] - m);
+            if (weight > 0.0f) value += partial_o[(base + s) * HD + d] * weight;  // an empty split wrote no output
+        }
+        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(value * inv);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ prefill
+
+// grid (query tiles of 64 tokens, heads, sequences); warp w owns tokens 16w..16w+15 of the tile.
+__global__ void __launch_bounds__(kThreads)
+prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out, int out_row_stride,
+                         const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
+                         const int* __restrict__ kv_lens, int heads, int kv_heads, int window, float scale) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    unsigned char* q_smem = smem;                                  // 64 rows
+    unsigned char* stage_smem = smem + kQRowsPrefill * kRowBytes;  // 2 stages x (K tile, V tile)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int kv_head = head / (heads / kv_heads);
+    const int q_begin = cu_q[seq];
+    const int q_len = cu_q[seq + 1] - q_begin;
+    const int q_tile = gridDim.x - 1 - blockIdx.x;  // the tiles with the most keys start first
+    const int t0 = q_tile * kQRowsPrefill;
+    if (t0 >= q_len) return;
+    const int valid = min(kQRowsPrefill, q_len - t0);
+    const int kv_len = kv_lens[seq];
+    const int pos0 = kv_len - q_len + t0;  // position of the tile's first token
+    const int last_pos = pos0 + valid - 1;
+    const int first_needed = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int t_begin = first_needed / kTile, t_end = last_pos / kTile + 1;
+
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const uint32_t stage_base = smem_u32(stage_smem);
+    load_tile(stage_base, k_pool, table[t_begin], kv_head, kv_heads);
+    load_tile(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads);
+    cp_async_commit();
+    load_queries(q_smem, q + (size_t)(q_begin + t0) * q_row_stride + (size_t)head * HD, q_row_stride, kQRowsPrefill, valid);
+    __syncthreads();
+    uint32_t a[kKSteps][4];
+    load_q_fragments(a, smem_u32(q_smem) + warp * 16 * kRowBytes);
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+    // this lane's two rows: positions, and the first position each sees
+    int row_pos[2], row_first[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + group_id + 8 * r;
+        row_pos[r] = row < valid ? pos0 + row : -1;  // a row beyond the sequence sees nothing
+        row_first[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
+    }
+    const int warp_last = min(pos0 + warp * 16 + 15, last_pos);        // highest position among the warp's rows
+    const int warp_first_pos = pos0 + warp * 16;                        // lowest
+    const int warp_first_key = (window > 0 && warp_first_pos - window + 1 > 0) ? warp_first_pos - window + 1 : 0;
+    const bool warp_has_rows = warp * 16 < valid;
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int stage = (t - t_begin) & 1;
+        if (t + 1 < t_end) {
+            const uint32_t next = stage_base + (stage ^ 1) * 2 * kTileBytes;
+            load_tile(next, k_pool, table[t + 1], kv_head, kv_heads);
+            load_tile(next + kTileBytes, v_pool, table[t + 1], kv_head, kv_heads);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t k_tile = stage_base + stage * 2 * kTileBytes, v_tile = k_tile + kTileBytes;
+        const int key_base = t * kTile;
+        if (warp_has_rows && key_base <= warp_last && key_base + kTile - 1 >= warp_first_key) {
+            // every key of the tile is visible to every row of the warp: no mask needed
+            const bool full = key_base + kTile - 1 <= warp_first_pos && key_base >= ((window > 0) ? max(0, warp_last - window + 1) : 0)
+                              && warp * 16 + 15 < valid;
+#pragma unroll
+            for (int part = 0; part < kTile / 16; ++part) {
+                const int key0 = part * 16;
+                const int abs0 = key_base + key0;
+                if (abs0 > warp_last || abs0 + 15 < warp_first_key) continue;  // uniform across the warp
+                float s[2][4];
+                scores_16_keys(s, a, k_tile, key0);
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int key = abs0 + nt * 8 + tid4 * 2 + (i & 1);
+                        const int r = i >> 1;
+                        const bool visible = full || (key <= row_pos[r] && key >= row_first[r]);
+                        s[nt][i] = visible ? s[nt][i] * scale : -CUDART_INF_F;
+                    }
+                uint32_t p[4];
+                float probs[2][4];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const float part_max = quad_max(fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1])));
+                    const float new_max = fmaxf(run_max[r], part_max);
+                    // a row that has seen nothing yet keeps -inf; subtract 0 then so that exp gives 0, not NaN
+                    const float safe_max = new_max == -CUDART_INF_F ? 0.0f : new_max;
+                    const float correction = expf(run_max[r] - safe_max);
+                    run_max[r] = new_max;
+                    float local = 0.0f;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+                            const float e = expf(s[nt][2 * r + c] - safe_max);
+                            probs[nt][2 * r + c] = e;
+                            local += e;
+                        }
+                    run_sum[r] = run_sum[r] * correction + local;
+#pragma unroll
+                    for (int i = 0; i < HD / 8; ++i) {
+                        o[i][2 * r] *= correction;
+                        o[i][2 * r + 1] *= correction;
+                    }
+                }
+                p[0] = pack_bf16(probs[0][0], probs[0][1]);
+                p[1] = pack_bf16(probs[0][2], probs[0][3]);
+                p[2] = pack_bf16(probs[1][0], probs[1][1]);
+                p[3] = pack_bf16(probs[1][2], probs[1][3]);
+                accumulate_16_keys(o, p, v_tile, key0);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + group_id + 8 * r;
+        const float total = quad_sum(run_sum[r]);
+        if (row >= valid) continue;
+        const float inv = 1.0f / total;
+        bf16* dst = out + (size_t)(q_begin + t0 + row) * out_row_stride + (size_t)head * HD;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i)
+            *reinterpret_cast<uint32_t*>(dst + i * 8 + tid4 * 2) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+}
+
+constexpr size_t decode_smem() {
+    const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 4 * (size_t)kTileBytes;
+    const size_t merge = (size_t)kQRowsDecode * kRowBytes + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+    return tiles > merge ? tiles : merge;
+}
+constexpr size_t prefill_smem() { return (size_t)kQRowsPrefill * kRowBytes + 4 * (size_t)kTileBytes; }
+
+static int check_common(const char* what, int heads, int kv_heads, int page_size, int q_row_stride, int out_row_stride,
+                        const void* q, const void* out) {
+    if (kv_heads <= 0 || heads % kv_heads) return fail("%s: %d heads are no multiple of %d kv heads", what, heads, kv_heads);
+    if (page_size != kTile) return fail("%s: the cache page must hold %d positions, got %d", what, kTile, page_size);
+    if (q_row_stride % 8 || out_row_stride % 2 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3))
+        return fail("%s: query rows must start on 16-byte boundaries (row stride %d elements)", what, q_row_stride);
+    return 0;
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_attention_head_dim() { return HD; }
+
+// Scratch floats a decode call with `splits` > 1 needs: partial outputs and (maximum, sum) pairs.
+MB_EXPORT size_t mb_decode_scratch_floats(int sequences, int heads, int splits) {
+    return splits > 1 ? (size_t)sequences * heads * splits * (HD + 2) : 0;
+}
+
+MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_pool,
+                                  const void* v_pool, const int* block_table, int max_blocks, const int* cu_q,
+                                  const int* kv_lens, int sequences, int heads, int kv_heads, int page_size, int window,
+                                  float scale, int splits, float* scratch, cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (int status = check_common("decode_attention", heads, kv_heads, page_size, q_row_stride, out_row_stride, q, out)) return status;
+    if (splits < 1) return fail("decode_attention: splits %d must be at least 1", splits);
+    if (splits > 1 && !scratch) return fail("decode_attention: %d splits need scratch memory", splits);
+    const int group = heads / kv_heads;
+    const int head_chunks = (group + 15) / 16;
+    if (sequences > 65535 || kv_heads * head_chunks > 65535) return fail("decode_attention: grid too large");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
+        if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(), cudaGetErrorString(status));
+        configured = true;
+    }
+    float* partial_o = scratch;
+    float* partial_ml = scratch ? scratch + (size_t)sequences * heads * splits * HD : nullptr;
+    const dim3 grid(splits, kv_heads * head_chunks, sequences);
+    decode_attention_kernel<<<grid, kThreads, decode_smem(), stream>>>(
+        (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
+        max_blocks, cu_q, kv_lens, heads, kv_heads, head_chunks, window, scale, splits, partial_o, partial_ml);
+    if (int status = check_launch("decode_attention")) return status;
+    if (splits > 1) {
+        combine_splits_kernel<<<dim3(heads, sequences), HD < 64 ? 32 : 64, 0, stream>>>(partial_o, partial_ml, (bf16*)out,
+                                                                                   out_row_stride, cu_q, heads, splits);
+        return check_launch("combine_splits");
+    }
+    return 0;
+}
+
+MB_EXPORT int mb_prefill_attention(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_pool,
+                                   const void* v_pool, const int* block_table, int max_blocks, const int* cu_q,
+                                   const int* kv_lens, int sequences, int max_q_len, int heads, int kv_heads,
+                                   int page_size, int window, float scale, cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0) return 0;
+    if (int status = check_common("prefill_attention", heads, kv_heads, page_size, q_row_stride, out_row_stride, q, out)) return status;
+    if (sequences > 65535 || heads > 65535) return fail("prefill_attention: grid too large");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem());
+        if (status != cudaSuccess) return fail("prefill_attention: cannot reserve %zu bytes of shared memory: %s", prefill_smem(), cudaGetErrorString(status));
+        configured = true;
+    }
+    const dim3 grid((max_q_len + kQRowsPrefill - 1) / kQRowsPrefill, heads, sequences);
+    prefill_attention_kernel<<<grid, kThreads, prefill_smem(), stream>>>(
+        (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
+        max_blocks, cu_q, kv_lens, heads, kv_heads, window, scale);
+    return check_launch("prefill_attention");
+}

@@ -77,6 +77,15 @@ def attention_rows():
     return load_library("mb_attention_rows", ["attention_rows.cu"])
 
 
+def attention_tc(head_dim: int):
+    """The tensor-core attention kernels, compiled for this head size at first use."""
+    return load_library("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": int(head_dim)})
+
+
+def attention_tc_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size == 64
+
+
 def gemm32():
     return load_library("mb_gemm_f32", ["gemm_f32.cu"])
 
@@ -206,6 +215,58 @@ def paged_attention_rows(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
                                           _p(v_pool), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens),
                                           sequences, max_q_len, heads, kv_heads, head_dim, k_pool.shape[2],
                                           window or 0, ctypes.c_float(scale), _stream()))
+
+
+def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim):
+    _cuda(q, out, k_pool, v_pool, block_table, cu_q, kv_lens)
+    _int32(block_table, "block_table")
+    _int32(cu_q, "cu_q")
+    _int32(kv_lens, "kv_lens")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("q and out need unit column stride")
+    if k_pool.dim() != 4 or k_pool.shape[1] != kv_heads or k_pool.shape[3] != head_dim or not k_pool.is_contiguous():
+        raise KernelError(f"k_pool must be contiguous [pages, {kv_heads}, page_size, {head_dim}], got {tuple(k_pool.shape)}")
+    if v_pool.shape != k_pool.shape or not v_pool.is_contiguous():
+        raise KernelError("v_pool must match k_pool")
+    if not (q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16):
+        raise KernelError("the tensor-core attention kernels take bfloat16 q, out and pools")
+
+
+def decode_splits(sequences: int, heads: int, kv_heads: int, max_blocks: int, multiprocessors: int = 148) -> int:
+    """How many blocks share one sequence's keys: enough to fill the GPU about four times over, at
+    most 16, at most one per cache page."""
+    base = sequences * kv_heads * (-(-(heads // kv_heads) // 16))
+    return max(1, min(16, max_blocks, (4 * multiprocessors) // max(1, base)))
+
+
+def decode_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                     block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, heads: int, kv_heads: int,
+                     head_dim: int, window: Optional[int], scale: float, splits: int) -> None:
+    """One query token per sequence (row cu_q[s] of q) against its cached keys and values."""
+    _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim)
+    sequences = kv_lens.numel()
+    lib = attention_tc(head_dim)
+    lib.mb_decode_scratch_floats.restype = ctypes.c_size_t
+    need = lib.mb_decode_scratch_floats(sequences, heads, splits)
+    scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    _run(lib, lib.mb_decode_attention(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(v_pool),
+                                      _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens), sequences, heads,
+                                      kv_heads, k_pool.shape[2], window or 0, ctypes.c_float(scale), splits,
+                                      _p(scratch), _stream()))
+    if splits > 1:
+        _launches[0] += 1  # the combine kernel
+
+
+def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                      block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
+                      kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> None:
+    """Any number of new tokens per sequence; their keys and values are already in the cache."""
+    _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim)
+    lib = attention_tc(head_dim)
+    _run(lib, lib.mb_prefill_attention(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(v_pool),
+                                       _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens), kv_lens.numel(),
+                                       max_q_len, heads, kv_heads, k_pool.shape[2], window or 0, ctypes.c_float(scale),
+                                       _stream()))
 
 
 # ------------------------------------------------------------------------------------ matrix products

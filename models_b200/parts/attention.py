@@ -94,9 +94,18 @@ class AttentionMixer(Mixer):
         return delta
 
     def attend(self, qkv, attended, batch, group, run):
+        """Tensor-core kernels where they apply (bfloat16, head size a multiple of 16, pages of 64);
+        otherwise the plain-arithmetic kernel, which takes every size and is the 32-bit path's."""
         s = self.spec
-        ops.paged_attention_rows(qkv, attended, run.k_pool, run.v_pool, group.block_table, batch.cu_q, batch.kv_lens,
-                                 batch.max_q_len, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+        args = (qkv, attended, run.k_pool, run.v_pool, group.block_table, batch.cu_q, batch.kv_lens)
+        if ops.attention_tc_takes(qkv.dtype, s.head_dim, run.k_pool.shape[2]):
+            if batch.max_q_len == 1:
+                splits = ops.decode_splits(batch.num_sequences, s.num_heads, s.num_kv_heads, group.block_table.shape[1])
+                ops.decode_attention(*args, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale, splits)
+            else:
+                ops.prefill_attention(*args, batch.max_q_len, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
+            return
+        ops.paged_attention_rows(*args, batch.max_q_len, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)
 
 
 register_part("mixer", "attention", AttentionMixer)

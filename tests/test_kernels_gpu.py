@@ -208,6 +208,85 @@ def test_paged_attention_rows(cuda_device, dtype, heads, kv_heads, head_dim, win
     close(out, expected, dtype)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (3, 1, 32, None), (6, 3, 48, None),
+                                                            (32, 8, 64, None), (8, 2, 128, None), (5, 5, 80, 37),
+                                                            (4, 1, 64, 64), (40, 2, 64, None), (2, 1, 256, 100)])
+def test_tensor_core_attention(cuda_device, heads, kv_heads, head_dim, window):
+    """Prefill (unequal new-token counts on top of unequal cached lengths) and decode (one token each,
+    with 1, 3 and 16 splits of the keys) against the plain attention."""
+    from models_b200.kernels import ops
+
+    dtype, page = torch.bfloat16, 64
+    for q_lens, kv_lens in (([1, 70, 5, 64, 130], [1, 70, 133, 200, 130]), ([1, 1, 1, 1], [1, 64, 65, 300])):
+        pages_needed = [-(-n // page) for n in kv_lens]
+        total_pages = sum(pages_needed) + 1
+        k_pool, v_pool = _pools(total_pages, kv_heads, page, head_dim, dtype, 6)
+        order = torch.randperm(total_pages - 1, generator=torch.Generator().manual_seed(7)) + 1
+        block_table = torch.zeros(len(q_lens), max(pages_needed) + 2, dtype=torch.int32)
+        at = 0
+        for b, n in enumerate(pages_needed):
+            block_table[b, :n] = order[at:at + n].int()
+            at += n
+        T = sum(q_lens)
+        q = torch.randn(T, heads * head_dim + 16, generator=torch.Generator().manual_seed(8)).to(dtype)
+        cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+        scale = 0.7 / math.sqrt(head_dim)
+        expected = _reference_attention(q.float()[:, : heads * head_dim], k_pool, v_pool, block_table, q_lens, kv_lens,
+                                        heads, kv_heads, head_dim, window, scale)
+        common = (k_pool.cuda(), v_pool.cuda(), block_table.cuda(), cu_q.cuda(), torch.tensor(kv_lens, dtype=torch.int32).cuda())
+        qd = q.cuda()[:, : heads * head_dim]
+        if max(q_lens) > 1:
+            out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
+            ops.prefill_attention(qd, out, *common, max(q_lens), heads, kv_heads, head_dim, window, scale)
+            close(out, expected, dtype)
+        else:
+            for splits in (1, 3, 16):
+                out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
+                ops.decode_attention(qd, out, *common, heads, kv_heads, head_dim, window, scale, splits)
+                close(out, expected, dtype)
+
+
+def test_window_edge_and_stale_pages_do_not_leak(cuda_device):
+    """The key just outside the window, the positions beyond a sequence's length in its last page, and
+    a page that belongs to nobody are all made to attract the query; none may be seen."""
+    from models_b200.kernels import ops
+
+    heads, kv_heads, head_dim, page, window = 4, 1, 64, 64, 50
+    kv_len = 150
+    loud = 30.0
+    k_pool = torch.zeros(5, kv_heads, page, head_dim)
+    v_pool = torch.zeros(5, kv_heads, page, head_dim)
+    k_pool[:] = loud  # every key attracts ...
+    v_pool[:] = 1000.0  # ... and would wreck the output
+    table = torch.tensor([[2, 4, 1, 0]], dtype=torch.int32)
+    first = kv_len - window  # the decode query sits at 149 and sees 100..149
+    for p in range(first, kv_len):  # the visible keys are quiet and carry the value 1
+        k_pool[table[0, p // page], 0, p % page, :] = 0.0
+        v_pool[table[0, p // page], 0, p % page, :] = 1.0
+    q = torch.ones(1, heads * head_dim)
+    for dtype in (torch.bfloat16, torch.float32):
+        args = (k_pool.to(dtype).cuda(), v_pool.to(dtype).cuda(), table.cuda(), torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                torch.tensor([kv_len], dtype=torch.int32).cuda())
+        out = torch.zeros(1, heads * head_dim, dtype=dtype, device="cuda")
+        ops.paged_attention_rows(q.to(dtype).cuda(), out, *args, 1, heads, kv_heads, head_dim, window, 1.0)
+        assert torch.allclose(out.float().cpu(), torch.ones(1, heads * head_dim)), dtype
+        if dtype == torch.bfloat16:
+            for splits in (1, 2, 4):
+                out = torch.zeros(1, heads * head_dim, dtype=dtype, device="cuda")
+                ops.decode_attention(q.to(dtype).cuda(), out, *args, heads, kv_heads, head_dim, window, 1.0, splits)
+                assert torch.allclose(out.float().cpu(), torch.ones(1, heads * head_dim)), splits
+            # prefill of the last 3 tokens: each sees its own 50 positions; make 97..99 quiet for them
+            for p in range(first - 2, first):
+                k_pool[table[0, p // page], 0, p % page, :] = 0.0
+                v_pool[table[0, p // page], 0, p % page, :] = 1.0
+            args = (k_pool.to(dtype).cuda(), v_pool.to(dtype).cuda()) + args[2:3] + (
+                torch.tensor([0, 3], dtype=torch.int32).cuda(), args[4])
+            out = torch.zeros(3, heads * head_dim, dtype=dtype, device="cuda")
+            ops.prefill_attention(q.to(dtype).cuda().expand(3, -1).contiguous(), out, *args, 3, heads, kv_heads, head_dim,
+                                  window, 1.0)
+            assert torch.allclose(out.float().cpu(), torch.ones(3, heads * head_dim))
+
+
 def test_attention_finds_one_far_key(cuda_device):
     """One key among hundreds is made to stand out; the output must be that key's value row."""
     from models_b200.kernels import ops
@@ -227,6 +306,14 @@ def test_attention_finds_one_far_key(cuda_device):
         expected = v_pool[table[0, far // page], 0, far % page, :]
         for h in range(heads):
             assert torch.allclose(out[0, h * head_dim:(h + 1) * head_dim].cpu(), expected, atol=1e-5), far
+        for splits in (1, 5):
+            out16 = torch.zeros(1, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+            ops.decode_attention(q.bfloat16().cuda(), out16, k_pool.bfloat16().cuda(), v_pool.bfloat16().cuda(), table.cuda(),
+                                 torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                                 torch.tensor([total], dtype=torch.int32).cuda(), heads, kv_heads, head_dim, None, 1.0, splits)
+            for h in range(heads):
+                assert torch.allclose(out16[0, h * head_dim:(h + 1) * head_dim].float().cpu(), expected.bfloat16().float(),
+                                      atol=1e-2), (far, splits)
 
 
 def test_argmax_first_maximum(cuda_device):
