@@ -236,6 +236,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=LLAMA_3_2_1B["num_hidden_layers"])
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
+    parser.add_argument("--only-prefill", action="store_true",
+                        help="run the 2,048-token prefill alone and print its figures (for profiling)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -253,6 +255,10 @@ def main() -> int:
     config = dict(LLAMA_3_2_1B, num_hidden_layers=args.layers)
     peak = peaks()
     model = make_model(config, max(64, args.batch))
+    if args.only_prefill:
+        ms = device_prefill(model, PREFILL_TOKENS, repeats=1)
+        print(json.dumps({"prefill_ms": ms, "tokens": PREFILL_TOKENS}))
+        return 0
     main_run = device_decode(model, args.batch, args.steps, warmup, sample_clocks=True)
     e2e = e2e_decode(model, args.batch, args.steps, warmup)
     bytes_per_step = decode_bytes(config, args.layers, main_run["kv_tokens_per_step"])
