@@ -535,3 +535,59 @@ MB_EXPORT int mb_prefill_attention(const void* q, int q_row_stride, void* out, i
         max_blocks, cu_q, kv_lens, heads, kv_heads, window, scale);
     return check_launch("prefill_attention");
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention that allocates nothing (declared in attention_tc.h; integrallis/models has no
+// counterpart of it).
+//
+// mb_decode_attention() takes its scratch from the caller, and the Python face of this library gets
+// it from the framework's allocator.  A plain C or C++ host that runs these kernels by itself may
+// not be able to do that: one that handed all device memory to an arena of its own when it started,
+// or one that serves requests in a loop in which cudaMalloc -- which can fail once memory is
+// committed, and synchronises the device -- must not appear.  For such a caller the partial results
+// of the split keys live in the file-scope array below instead.  It is part of the library's image:
+// every GPU that loads this library holds kStaticScratchFloats * 4 bytes for it until the process
+// exits.
+//
+// The array's name is usable in device code only; host code sees a stand-in for it, not a device
+// address.  So the entry point asks the runtime for the address once per device, with that device
+// current (cudaGetSymbolAddress), keeps it, and hands it to the kernels.  The first call on a
+// device does this set-up; make that first call outside any stream capture.
+//
+// Every call uses the same array, and it keeps what the last call left.  Nothing in it has to be
+// zero at the start: each block writes its (maximum, sum) pair, and a partial output is read only
+// where that pair says the block saw keys.  Two calls that overlap on the GPU (different streams,
+// no ordering between them) race on the array; order them.
+constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats];
+static float* g_static_scratch_address[kMaxDevices] = {nullptr};
+
+MB_EXPORT size_t mb_decode_attention_static_capacity() { return kStaticScratchFloats; }
+
+MB_EXPORT int mb_decode_attention_static(const void* q, int q_row_stride, void* out, int out_row_stride,
+                                         const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
+                                         const int* cu_q, const int* kv_lens, int sequences, int heads, int kv_heads,
+                                         int page_size, int window, float scale, int splits, cudaStream_t stream) {
+    if (sequences <= 0) return 0;
+    if (splits < 1) return fail("decode_attention_static: splits %d must be at least 1", splits);
+    const size_t need = mb_decode_scratch_floats(sequences, heads, splits);
+    if (need > kStaticScratchFloats)
+        return fail("decode_attention_static: %d sequences x %d heads x %d splits need %zu floats of scratch, the built-in "
+                    "array holds %zu; use fewer splits or mb_decode_attention with scratch of your own",
+                    sequences, heads, splits, need, (size_t)kStaticScratchFloats);
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return fail("decode_attention_static: cudaGetDevice: %s", cudaGetErrorString(status));
+    if (device < 0 || device >= kMaxDevices) return fail("decode_attention_static: device %d is outside 0..%d", device, kMaxDevices - 1);
+    if (!g_static_scratch_address[device]) {
+        float* address = nullptr;
+        status = cudaGetSymbolAddress((void**)&address, g_static_decode_scratch);
+        if (status != cudaSuccess || !address)
+            return fail("decode_attention_static: cudaGetSymbolAddress on device %d: %s", device, cudaGetErrorString(status));
+        g_static_scratch_address[device] = address;
+    }
+    return mb_decode_attention(q, q_row_stride, out, out_row_stride, k_pool, v_pool, block_table, max_blocks, cu_q, kv_lens,
+                               sequences, heads, kv_heads, page_size, window, scale, splits,
+                               splits > 1 ? g_static_scratch_address[device] : nullptr, stream);
+}
