@@ -78,9 +78,14 @@ class DecoderModel:
         for run, entry in zip(runs, self.spec.schedule):
             pending = self.blocks[entry.layer].forward(x, pending, batch, run)
             if self.observer is not None:
-                self.observer(run.run, x + pending.float())
+                self.observer(run.run, x + pending.float() if pending is not None else x.clone())
         if batch.num_wanted == 0:
             return None
+        if (pending is None and self.runtime.mode == "bfloat16" and getattr(self.final_norm, "foldable", False)
+                and ops.skinny_takes(self.head_weight, batch.num_wanted, with_norm=True)):
+            # few wanted rows: gather, final norm and output product in one kernel
+            return ops.skinny_gemm(self.head_weight, ops.EPI_F32, xf=x, gain=self.final_norm.weight,
+                                   eps=self.final_norm.spec.eps, rows=batch.want_rows)
         xn = self.final_norm.forward(x, pending, rows=batch.want_rows)
         return linear(xn, self.head_weight, torch.float32)
 

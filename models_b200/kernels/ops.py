@@ -287,6 +287,68 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, row_invariant: bool = True) -> to
     return c
 
 
+SKINNY_ROWS, SKINNY_NORM_ROWS = 32, 16
+EPI_BF16, EPI_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+
+
+def skinny():
+    return load_library("mb_skinny_gemm", ["skinny_gemm.cu"])
+
+
+def skinny_takes(weight: torch.Tensor, rows: int, with_norm: bool = False) -> bool:
+    """Whether the decode matrix product takes this weight with this many activation rows."""
+    return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.stride(1) == 1 and weight.shape[1] % 8 == 0
+            and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
+            and 0 < rows <= (SKINNY_NORM_ROWS if with_norm else SKINNY_ROWS))
+
+
+_multiprocessors = {}
+
+
+def _sm_count(device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _multiprocessors:
+        _multiprocessors[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _multiprocessors[index]
+
+
+def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] = None, xf: Optional[torch.Tensor] = None,
+                gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Few activation rows times weight^T ([n, k] bfloat16).  Activations: `x` (bfloat16 [rows, k]), or
+    `xf` (the float32 residual rows, optionally gathered by `rows`) normalised on the fly with `gain`
+    and `eps`.  Epilogues: EPI_BF16 / EPI_F32 store [rows, n]; EPI_RESIDUAL adds into `out` (float32
+    [rows, n]); EPI_SWIGLU takes weight = [gate rows; up rows] and stores silu(gate) * up [rows, n/2]."""
+    _cuda(weight, x, xf, gain, rows, out)
+    n, k = weight.shape
+    norm = gain is not None
+    if norm:
+        if xf is None or xf.dtype != torch.float32 or xf.stride(1) != 1 or xf.shape[1] != k:
+            raise KernelError("the norm prologue needs float32 rows of the weight's width")
+        if gain.dtype != torch.float32 or gain.numel() != k:
+            raise KernelError("the norm gain must be float32 of the weight's width")
+        _int32(rows, "rows")
+        batch = rows.numel() if rows is not None else xf.shape[0]
+    else:
+        if x is None or x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.shape[1] != k:
+            raise KernelError("activations must be bfloat16 rows of the weight's width")
+        batch = x.shape[0]
+    if not skinny_takes(weight, batch, norm):
+        raise KernelError(f"skinny_gemm does not take a {tuple(weight.shape)} {weight.dtype} weight with {batch} rows")
+    out_cols = n // 2 if epilogue == EPI_SWIGLU else n
+    if epilogue == EPI_RESIDUAL:
+        if out is None or out.dtype != torch.float32 or out.shape != (batch, n) or out.stride(1) != 1:
+            raise KernelError("the residual epilogue adds into a float32 [rows, n] tensor")
+    elif out is None:
+        out = torch.empty((batch, out_cols), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16,
+                          device=weight.device)
+    lib = skinny()
+    _run(lib, lib.mb_skinny_gemm(_p(weight), weight.stride(0), n, k, batch, _p(x), x.stride(0) if x is not None else 0,
+                                 _p(xf), xf.stride(0) if xf is not None else 0, _p(gain), ctypes.c_float(eps), _p(rows),
+                                 _p(out), out.stride(0), epilogue, _sm_count(weight.device), _stream()))
+    return out
+
+
 # ------------------------------------------------------------------------------------ sampling
 
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:

@@ -72,26 +72,45 @@ class AttentionMixer(Mixer):
     def kv_request(self):
         return KvRequest(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def folds(self, rows: int, norm) -> bool:
+        """Whether `forward_residual` applies: bfloat16 weights, few rows, no biases, a foldable norm."""
+        return (self.b_qkv is None and self.b_o is None and getattr(norm, "foldable", False)
+                and ops.skinny_takes(self.w_qkv, rows, with_norm=True) and ops.skinny_takes(self.w_o, rows))
+
+    def forward_residual(self, x: torch.Tensor, norm, batch, run: RunContext) -> None:
+        """x += Wo . attention(rotate(Wqkv . norm(x))): the norm rides in the q/k/v product, the
+        residual add in the output product."""
+        writes = run.writes_cache
+        qkv = ops.skinny_gemm(self.w_qkv if writes else self.w_q, ops.EPI_BF16, xf=x, gain=norm.weight, eps=norm.spec.eps)
+        attended = self._rotate_store_attend(qkv, batch, run)
+        ops.skinny_gemm(self.w_o, ops.EPI_RESIDUAL, x=attended, out=x)
+
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:
-        s, dtype = self.spec, self.runtime.compute_dtype
-        if run.k_pool is None:
-            raise RuntimeError("the attention mixer needs cache pools; its run has none")
+        dtype = self.runtime.compute_dtype
         writes = run.writes_cache
         qkv = linear(xn, self.w_qkv if writes else self.w_q, dtype)
         if self.b_qkv is not None:
             ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
+        attended = self._rotate_store_attend(qkv, batch, run)
+        delta = linear(attended, self.w_o, dtype)
+        if self.b_o is not None:
+            ops.bias_add(delta, self.b_o)
+        return delta
+
+    def _rotate_store_attend(self, qkv: torch.Tensor, batch, run: RunContext) -> torch.Tensor:
+        s, dtype = self.spec, self.runtime.compute_dtype
+        if run.k_pool is None:
+            raise RuntimeError("the attention mixer needs cache pools; its run has none")
+        writes = run.writes_cache
         group = batch.groups[run.group]
         pos = self.position
         ops.rope_cache_write(
             qkv, batch.positions, pos.cos if pos else None, pos.sin if pos else None, run.k_pool, run.v_pool,
             group.slot_mapping, s.num_heads, s.num_kv_heads, s.head_dim, pos.rotary_dim if pos else 0,
             pos.interleaved if pos else False, run.k_pool.shape[2], writes)
-        attended = torch.empty((xn.shape[0], self.q_width), dtype=dtype, device=xn.device)
+        attended = torch.empty((qkv.shape[0], self.q_width), dtype=dtype, device=qkv.device)
         self.attend(qkv, attended, batch, group, run)
-        delta = linear(attended, self.w_o, dtype)
-        if self.b_o is not None:
-            ops.bias_add(delta, self.b_o)
-        return delta
+        return attended
 
     def attend(self, qkv, attended, batch, group, run):
         """Tensor-core kernels where they apply (bfloat16, head size a multiple of 16, pages of 64);

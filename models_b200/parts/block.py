@@ -12,6 +12,7 @@ from typing import Optional
 
 import torch
 
+from ..kernels import ops
 from .base import Part, RunContext
 from .registry import build_part, register_part
 
@@ -32,7 +33,19 @@ class PreNormBlock(Part):
         for part in self.parts:
             part.load(tensors)
 
-    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], batch, run: RunContext) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], batch, run: RunContext) -> Optional[torch.Tensor]:
+        rows = x.shape[0]
+        mixer_folds = getattr(self.mixer, "folds", None)
+        ffn_folds = getattr(self.feed_forward, "folds", None)
+        if (self.runtime.mode == "bfloat16" and mixer_folds and ffn_folds and mixer_folds(rows, self.mixer_norm)
+                and ffn_folds(rows, self.feed_forward_norm)):
+            # few rows (decode): norms ride in the products that follow them and residual adds in the
+            # products that precede them, so nothing stays pending
+            if pending is not None:
+                ops.residual_add(x, pending)
+            self.mixer.forward_residual(x, self.mixer_norm, batch, run)
+            self.feed_forward.forward_residual(x, self.feed_forward_norm)
+            return None
         xn = self.mixer_norm.forward(x, pending)
         mixed = self.mixer.forward(xn, batch, run)
         xn = self.feed_forward_norm.forward(x, mixed)

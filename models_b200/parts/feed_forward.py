@@ -49,8 +49,25 @@ class GatedFeedForward(Part):
             self.b_gate_up = torch.cat([rt.vector(tensors[n["gate_bias"]]), rt.vector(tensors[n["up_bias"]])]).contiguous()
             self.b_down = rt.vector(tensors[n["down_bias"]])
 
+    def folds(self, rows: int, norm) -> bool:
+        """Whether `forward_residual` applies: bfloat16 weights, few rows, no biases, a foldable norm."""
+        return (self.b_gate_up is None and self.b_down is None and getattr(norm, "foldable", False)
+                and ops.skinny_takes(self.w_gate_up, rows, with_norm=True) and ops.skinny_takes(self.w_down, rows))
+
+    def forward_residual(self, x: torch.Tensor, norm) -> None:
+        """x += down(silu(gate(norm(x))) * up(norm(x))) in two kernels: norm, gate/up product and
+        activation in one, the down product and the residual add in the other."""
+        hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, xf=x, gain=norm.weight, eps=norm.spec.eps)
+        ops.skinny_gemm(self.w_down, ops.EPI_RESIDUAL, x=hidden, out=x)
+
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
+        if self.b_gate_up is None and ops.skinny_takes(self.w_gate_up, xn.shape[0]) and xn.dtype == torch.bfloat16:
+            hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, x=xn)
+            delta = linear(hidden, self.w_down, dtype)
+            if self.b_down is not None:
+                ops.bias_add(delta, self.b_down)
+            return delta
         gate_up = linear(xn, self.w_gate_up, dtype)
         if self.b_gate_up is not None:
             ops.bias_add(gate_up, self.b_gate_up)

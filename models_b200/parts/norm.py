@@ -17,6 +17,9 @@ from .registry import register_part
 
 
 class RmsNorm(Part):
+    # a consumer may fold this norm into its own kernel: it reads `weight` and `spec.eps`
+    foldable = True
+
     def parameters(self):
         return [ParamRequest(self.spec.weights["weight"], (self.spec.size,), "gain")]
 

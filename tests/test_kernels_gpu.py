@@ -65,13 +65,10 @@ def test_add_rmsnorm(cuda_device, out_dtype, width):
     close(out, plain_llama.rms_norm((summed + delta.float())[rows.long()], weight, eps), out_dtype)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,n,k", [(1, 72, 40), (5, 203, 136), (70, 130, 97), (130, 64, 256)])
-def test_gemm_f32(cuda_device, dtype, m, n, k):
+def test_gemm_f32(cuda_device, m, n, k):
     from models_b200.kernels import ops
 
-    if dtype != torch.float32:
-        pytest.skip("the 32-bit product takes float32 only")
     g = torch.Generator().manual_seed(2)
     a, w = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g)
     expected = (a.double() @ w.double().t())
@@ -327,3 +324,52 @@ def test_argmax_first_maximum(cuda_device):
     got = ops.argmax_rows(logits.cuda()).cpu().tolist()
     assert got == [plain_llama.plain_argmax(row) for row in logits]
     assert got[1] == 77
+
+
+@pytest.mark.parametrize("batch", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(48, 64), (203, 136), (3072, 2048), (130, 8192)])
+def test_skinny_gemm_all_prologues_and_epilogues(cuda_device, batch, n, k):
+    """The decode matrix product against float64: plain, with the folded RMSNorm (and a row gather),
+    with the residual add, and with the gated activation, at widths that do not fill its tiles."""
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(batch * 1000 + n)
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    x = torch.randn(batch, k, generator=g).bfloat16()
+    wd, xd = w.cuda(), x.cuda()
+    exact = x.double() @ w.double().t()
+    scale = float(exact.abs().max())
+    out = ops.skinny_gemm(wd, ops.EPI_F32, x=xd)
+    assert float((out.double().cpu() - exact).abs().max()) < 2e-5 * scale * math.sqrt(k)
+    out = ops.skinny_gemm(wd, ops.EPI_BF16, x=xd)
+    assert out.dtype == torch.bfloat16 and float((out.double().cpu() - exact).abs().max()) < 1e-2 * scale
+    residual = torch.randn(batch, n, generator=g)
+    rd = residual.cuda()
+    ops.skinny_gemm(wd, ops.EPI_RESIDUAL, x=xd, out=rd)
+    assert float((rd.double().cpu() - (residual.double() + exact)).abs().max()) < 2e-5 * (scale + 4) * math.sqrt(k)
+    if n % 2 == 0:
+        gated = ops.skinny_gemm(wd, ops.EPI_SWIGLU, x=xd)
+        want = plain_llama.swiglu(exact[:, : n // 2], exact[:, n // 2:])
+        assert gated.shape == (batch, n // 2)
+        assert float((gated.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+    if batch <= 16:
+        rows_total = batch + 3
+        xf = torch.randn(rows_total, k, generator=g) * 2
+        gain = 1 + 0.1 * torch.randn(k, generator=g)
+        pick = torch.randperm(rows_total, generator=g)[:batch].int()
+        eps = 1e-5
+        normed = plain_llama.rms_norm(xf.double(), gain.double(), eps)[pick.long()]
+        want = normed @ w.double().t()
+        got = ops.skinny_gemm(wd, ops.EPI_F32, xf=xf.cuda(), gain=gain.cuda(), eps=eps, rows=pick.cuda())
+        # the normalised rows are rounded to bfloat16 before the product
+        assert float((got.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+        if n % 2 == 0:
+            got = ops.skinny_gemm(wd, ops.EPI_SWIGLU, xf=xf.cuda()[:batch].contiguous(), gain=gain.cuda(), eps=eps)
+            full = plain_llama.rms_norm(xf.double()[:batch], gain.double(), eps) @ w.double().t()
+            want = plain_llama.swiglu(full[:, : n // 2], full[:, n // 2:])
+            assert float((got.double().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max())
+    else:
+        with pytest.raises(ops.KernelError):
+            ops.skinny_gemm(wd, ops.EPI_F32, xf=x.float().cuda(), gain=torch.ones(k).cuda(), eps=1e-5)
+    with pytest.raises(ops.KernelError):
+        ops.skinny_gemm(wd, ops.EPI_F32, x=torch.zeros(33, k, dtype=torch.bfloat16, device="cuda"))
