@@ -254,7 +254,7 @@ def main() -> int:
 
     config = dict(LLAMA_3_2_1B, num_hidden_layers=args.layers)
     peak = peaks()
-    model = make_model(config, max(64, args.batch))
+    model = make_model(config, args.batch if (args.no_points or args.only_prefill) else max(64, args.batch))
     if args.only_prefill:
         ms = device_prefill(model, PREFILL_TOKENS, repeats=1)
         print(json.dumps({"prefill_ms": ms, "tokens": PREFILL_TOKENS}))
