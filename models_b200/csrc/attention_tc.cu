@@ -18,6 +18,7 @@
 // (softmax), here in its running form.  Probabilities are rounded to bfloat16 for the P.V product.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 #ifndef MB_HEAD_DIM
@@ -143,12 +144,18 @@ __device__ __forceinline__ float quad_sum(float v) {
 
 // grid (splits, kv_heads * head_chunks, sequences).  Rows of the MMA tile are the (up to 16) query
 // heads of one kv head; each of the 4 warps takes 16 of a tile's 64 keys.
+// kCluster: the `splits` blocks of one (sequence, kv head) form a thread-block cluster and combine
+// their partial results in the first block's shared memory (distributed shared memory) instead of
+// going through scratch memory and a second kernel; splits <= 8 then.
+template <bool kCluster>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out, int out_row_stride,
                         const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                         const int* __restrict__ kv_lens, int heads, int kv_heads, int head_chunks, int window,
                         float scale, int splits, float* __restrict__ partial_o, float* __restrict__ partial_ml) {
+    grid_launch_dependents();
+    grid_dependency_wait();  // the newest keys and values come from the kernel before this one
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* q_smem = smem;                                 // 16 rows
     unsigned char* stage_smem = smem + kQRowsDecode * kRowBytes;  // 2 stages x (K tile, V tile)
@@ -168,7 +175,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     const int t_begin = first_tile + split * per_split;
     const int t_end = min(t_begin + per_split, first_tile + tiles);
 
-    if (t_begin >= t_end) {  // nothing for this split: an empty partial
+    const bool empty = t_begin >= t_end;  // nothing for this split
+    if (empty && !kCluster) {  // an empty partial
         if (threadIdx.x < rows_here) {
             float* ml = partial_ml + ((size_t)(seq * heads + head0 + threadIdx.x) * splits + split) * 2;
             ml[0] = -CUDART_INF_F;
@@ -177,6 +185,11 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
         return;
     }
 
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+    if (!empty) {
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t stage_base = smem_u32(stage_smem);
     load_tile(stage_base, k_pool, table[t_begin], kv_head, kv_heads);
@@ -186,11 +199,6 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     __syncthreads();
     uint32_t a[kKSteps][4];
     load_q_fragments(a, smem_u32(q_smem));
-
-    float o[HD / 8][4];
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) & 1;
@@ -253,12 +261,15 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
         }
         __syncthreads();  // the stage is free for the load after next
     }
+    }  // !empty
     run_sum[0] = quad_sum(run_sum[0]);
     run_sum[1] = quad_sum(run_sum[1]);
 
     // merge the four warps' partial results through shared memory (the stages are free now)
     float* merge_o = reinterpret_cast<float*>(stage_smem);         // [4 warps][16 rows][HD]
     float* merge_ml = merge_o + 4 * 16 * HD;                        // [4 warps][16 rows][2]
+    float* block_o = merge_ml + 4 * 16 * 2;                         // [16 rows][HD]   (cluster: this block's result)
+    float* block_ml = block_o + 16 * HD;                            // [16 rows][2]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = group_id + 8 * r;
@@ -280,14 +291,22 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
 #pragma unroll
         for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
         float total = 0.0f, value = 0.0f;
+        if (m != -CUDART_INF_F) {
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float weight = expf(merge_ml[(w * 16 + row) * 2] - m);  // exp(-inf) = 0 for a warp that saw nothing
-            total += merge_ml[(w * 16 + row) * 2 + 1] * weight;
-            value += merge_o[(size_t)(w * 16 + row) * HD + d] * weight;
+            for (int w = 0; w < 4; ++w) {
+                const float weight = expf(merge_ml[(w * 16 + row) * 2] - m);  // exp(-inf) = 0 for a warp that saw nothing
+                total += merge_ml[(w * 16 + row) * 2 + 1] * weight;
+                value += merge_o[(size_t)(w * 16 + row) * HD + d] * weight;
+            }
         }
         const int head = head0 + row;
-        if (splits == 1) {
+        if (kCluster) {
+            block_o[row * HD + d] = value;
+            if (d == 0) {
+                block_ml[row * 2] = m;
+                block_ml[row * 2 + 1] = total;
+            }
+        } else if (splits == 1) {
             out[(size_t)q_row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(value * (1.0f / total));
         } else {
             const size_t slot = (size_t)(seq * heads + head) * splits + split;
@@ -298,12 +317,37 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
             }
         }
     }
+    if (kCluster) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (cluster.block_rank() == 0) {
+            for (int i = threadIdx.x; i < rows_here * HD; i += kThreads) {
+                const int row = i / HD, d = i % HD;
+                float m = -CUDART_INF_F;
+                for (int r = 0; r < splits; ++r) m = fmaxf(m, cluster.map_shared_rank(block_ml, r)[row * 2]);
+                float total = 0.0f, value = 0.0f;
+                for (int r = 0; r < splits; ++r) {
+                    const float* ml = cluster.map_shared_rank(block_ml, r);
+                    const float weight = expf(ml[row * 2] - m);  // 0 for a block that saw nothing
+                    if (weight > 0.0f) {
+                        total += ml[row * 2 + 1] * weight;
+                        value += cluster.map_shared_rank(block_o, r)[row * HD + d] * weight;
+                    }
+                }
+                out[(size_t)q_row * out_row_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(value * (1.0f / total));
+            }
+        }
+        cluster.sync();  // the other blocks' shared memory has been read; they may leave
+    }
 }
 
 // grid (heads, sequences), HD threads... one thread per output coordinate (strided).
 __global__ void combine_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                       bf16* __restrict__ out, int out_row_stride, const int* __restrict__ cu_q,
                                       int heads, int splits) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int head = blockIdx.x, seq = blockIdx.y;
     const size_t base = (size_t)(seq * heads + head) * splits;
     float m = -CUDART_INF_F;
@@ -330,6 +374,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
                          const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                          const int* __restrict__ kv_lens, int heads, int kv_heads, int window, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* q_smem = smem;                                  // 64 rows
     unsigned char* stage_smem = smem + kQRowsPrefill * kRowBytes;  // 2 stages x (K tile, V tile)
@@ -459,7 +505,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
 
 constexpr size_t decode_smem() {
     const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 4 * (size_t)kTileBytes;
-    const size_t merge = (size_t)kQRowsDecode * kRowBytes + (4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+    const size_t merge = (size_t)kQRowsDecode * kRowBytes + (4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
 constexpr size_t prefill_smem() { return (size_t)kQRowsPrefill * kRowBytes + 4 * (size_t)kTileBytes; }
@@ -491,28 +537,53 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     if (sequences <= 0) return 0;
     if (int status = check_common("decode_attention", heads, kv_heads, page_size, q_row_stride, out_row_stride, q, out)) return status;
     if (splits < 1) return fail("decode_attention: splits %d must be at least 1", splits);
-    if (splits > 1 && !scratch) return fail("decode_attention: %d splits need scratch memory", splits);
     const int group = heads / kv_heads;
     const int head_chunks = (group + 15) / 16;
     if (sequences > 65535 || kv_heads * head_chunks > 65535) return fail("decode_attention: grid too large");
     static bool configured = false;
     if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
+        cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(decode_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
         if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(), cudaGetErrorString(status));
         configured = true;
     }
+    const dim3 grid(splits, kv_heads * head_chunks, sequences);
+    if (splits > 1 && !scratch) {
+        // no scratch given: the splits of a sequence meet inside a thread-block cluster
+        if (splits > 8) return fail("decode_attention: %d splits without scratch memory exceed the cluster limit of 8", splits);
+        cudaLaunchConfig_t config = {};
+        config.gridDim = grid;
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = decode_smem();
+        config.stream = stream;
+        cudaLaunchAttribute attribute[2];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = splits;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = 2;
+        cudaError_t status = cudaLaunchKernelEx(&config, decode_attention_kernel<true>, (const bf16*)q, q_row_stride, (bf16*)out,
+                                                out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks,
+                                                cu_q, kv_lens, heads, kv_heads, head_chunks, window, scale, splits,
+                                                (float*)nullptr, (float*)nullptr);
+        if (status != cudaSuccess) return fail("decode_attention: launch failed: %s", cudaGetErrorString(status));
+        return check_launch("decode_attention");
+    }
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)sequences * heads * splits * HD : nullptr;
-    const dim3 grid(splits, kv_heads * head_chunks, sequences);
-    decode_attention_kernel<<<grid, kThreads, decode_smem(), stream>>>(
-        (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-        max_blocks, cu_q, kv_lens, heads, kv_heads, head_chunks, window, scale, splits, partial_o, partial_ml);
-    if (int status = check_launch("decode_attention")) return status;
-    if (splits > 1) {
-        combine_splits_kernel<<<dim3(heads, sequences), HD < 64 ? 32 : 64, 0, stream>>>(partial_o, partial_ml, (bf16*)out,
-                                                                                   out_row_stride, cu_q, heads, splits);
-        return check_launch("combine_splits");
-    }
+    if (int status = launch_dependent("decode_attention", decode_attention_kernel<false>, grid, dim3(kThreads), decode_smem(), stream, true,
+                                      (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool,
+                                      (const bf16*)v_pool, block_table, max_blocks, cu_q, kv_lens, heads, kv_heads, head_chunks,
+                                      window, scale, splits, partial_o, partial_ml))
+        return status;
+    if (splits > 1)
+        return launch_dependent("combine_splits", combine_splits_kernel, dim3(heads, sequences), dim3(HD < 64 ? 32 : 64), 0, stream,
+                                true, (const float*)partial_o, (const float*)partial_ml, (bf16*)out, out_row_stride, cu_q, heads,
+                                splits);
     return 0;
 }
 
@@ -530,10 +601,9 @@ MB_EXPORT int mb_prefill_attention(const void* q, int q_row_stride, void* out, i
         configured = true;
     }
     const dim3 grid((max_q_len + kQRowsPrefill - 1) / kQRowsPrefill, heads, sequences);
-    prefill_attention_kernel<<<grid, kThreads, prefill_smem(), stream>>>(
-        (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-        max_blocks, cu_q, kv_lens, heads, kv_heads, window, scale);
-    return check_launch("prefill_attention");
+    return launch_dependent("prefill_attention", prefill_attention_kernel, grid, dim3(kThreads), prefill_smem(), stream, true,
+                            (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
+                            block_table, max_blocks, cu_q, kv_lens, heads, kv_heads, window, scale);
 }
 
 // ------------------------------------------------------------------------------------------------

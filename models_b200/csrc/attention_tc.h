@@ -16,7 +16,10 @@ int mb_attention_head_dim(void);
 /* Floats of scratch a decode call with `splits` > 1 needs (0 for one split). */
 size_t mb_decode_scratch_floats(int sequences, int heads, int splits);
 
-/* One query token per sequence against its cached keys and values; scratch from the caller. */
+/* One query token per sequence against its cached keys and values.  With splits > 1 the partial
+ * results of the split keys go through `scratch` (mb_decode_scratch_floats floats, from the caller)
+ * and a second kernel; with scratch == NULL and splits <= 8 the blocks of a sequence form a
+ * thread-block cluster and combine in shared memory instead. */
 int mb_decode_attention(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_pool,
                         const void* v_pool, const int* block_table, int max_blocks, const int* cu_q, const int* kv_lens,
                         int sequences, int heads, int kv_heads, int page_size, int window, float scale, int splits,

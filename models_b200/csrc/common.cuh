@@ -114,6 +114,30 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
     return total;
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_dependent() may start while the
+// kernel before it in the stream is still draining; everything it does before grid_dependency_wait()
+// must not touch what that kernel writes.  Without such a launch both calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+inline int launch_dependent(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, bool dependent, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = dependent ? 1 : 0;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+    if (status != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(status));
+    return check_launch(what);
+}
+
 }  // namespace mb
 
 #define MB_DEFINE_LAST_ERROR() \

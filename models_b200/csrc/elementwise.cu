@@ -18,6 +18,8 @@ namespace mb {
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ out, int width, int vocab, float scale) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int row = blockIdx.x;
     int token = tokens[row];
     token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);  // ids are validated on the host
@@ -34,6 +36,8 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                    const float* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps, int write_x) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     extern __shared__ float row_cache[];  // the row, width floats
     __shared__ float scratch[32];
     const int out_row = blockIdx.x;
@@ -68,6 +72,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride, con
                                         T* __restrict__ k_pool, T* __restrict__ v_pool,
                                         const int* __restrict__ slot_mapping, int heads, int kv_heads, int head_dim,
                                         int rotary_dim, int interleaved, int page_size, int write_cache) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int t = blockIdx.x;
     const int h = blockIdx.y;
     T* vec = qkv + (size_t)t * row_stride + (size_t)h * head_dim;
@@ -113,6 +119,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride, con
 // gate_up: [rows, 2*width] with the gate in columns [0, width) and up in [width, 2*width).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const size_t row = i / width, col = i % width;
@@ -125,6 +133,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 
 template <typename T>
 __global__ void bias_add_kernel(T* __restrict__ x, const float* __restrict__ bias, int width, size_t total) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
         Num<T>::store(x + i, Num<T>::load(x + i) + bias[i % width]);
@@ -133,6 +143,8 @@ __global__ void bias_add_kernel(T* __restrict__ x, const float* __restrict__ bia
 // x (float residual) += delta
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t total) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride)
         x[i] += Num<TD>::load(delta + i);
@@ -152,6 +164,7 @@ MB_EXPORT int mb_embed_gather(const void* table, int table_dtype, const int* tok
     if (rows <= 0) return 0;
     if (width <= 0 || vocab <= 0) return fail("embed_gather: width %d and vocab %d must be positive", width, vocab);
     const int block = width >= 1024 ? 256 : 128;
+    // the first kernel of a step follows a copy, not a kernel: an ordinary launch
     if (table_dtype == MB_F32)
         embed_gather_kernel<float><<<rows, block, 0, stream>>>((const float*)table, tokens, out, width, vocab, scale);
     else if (table_dtype == MB_BF16)
@@ -172,8 +185,8 @@ static int launch_add_rmsnorm(float* x, const void* delta, const float* weight, 
         if (status != cudaSuccess) return fail("add_rmsnorm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
     }
     const int block = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
-    kernel<<<out_rows, block, smem, stream>>>(x, (const TD*)delta, weight, (TO*)out, rows, width, eps, write_x);
-    return check_launch("add_rmsnorm");
+    return launch_dependent("add_rmsnorm", kernel, dim3(out_rows), dim3(block), smem, stream, true, x, (const TD*)delta, weight,
+                            (TO*)out, rows, width, eps, write_x);
 }
 
 // delta may be null (then delta_dtype is ignored).  out_dtype selects the storage of `out`.
@@ -208,14 +221,15 @@ MB_EXPORT int mb_rope_cache_write(void* qkv, int dtype, int row_stride, const in
     const dim3 grid(tokens, write_cache ? heads + 2 * kv_heads : heads);
     const int block = head_dim >= 128 ? 64 : 32;
     if (dtype == MB_F32)
-        rope_cache_write_kernel<float><<<grid, block, 0, stream>>>((float*)qkv, row_stride, positions, cos_table, sin_table,
-            (float*)k_pool, (float*)v_pool, slot_mapping, heads, kv_heads, head_dim, rotary_dim, interleaved, page_size, write_cache);
-    else if (dtype == MB_BF16)
-        rope_cache_write_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>((__nv_bfloat16*)qkv, row_stride, positions, cos_table, sin_table,
-            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim, rotary_dim, interleaved, page_size, write_cache);
-    else
-        return fail("rope_cache_write: unknown dtype code %d", dtype);
-    return check_launch("rope_cache_write");
+        return launch_dependent("rope_cache_write", rope_cache_write_kernel<float>, grid, dim3(block), 0, stream, true, (float*)qkv,
+                                row_stride, positions, cos_table, sin_table, (float*)k_pool, (float*)v_pool, slot_mapping, heads,
+                                kv_heads, head_dim, rotary_dim, interleaved, page_size, write_cache);
+    if (dtype == MB_BF16)
+        return launch_dependent("rope_cache_write", rope_cache_write_kernel<__nv_bfloat16>, grid, dim3(block), 0, stream, true,
+                                (__nv_bfloat16*)qkv, row_stride, positions, cos_table, sin_table, (__nv_bfloat16*)k_pool,
+                                (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim, rotary_dim, interleaved, page_size,
+                                write_cache);
+    return fail("rope_cache_write: unknown dtype code %d", dtype);
 }
 
 MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int dtype, int rows, int width, cudaStream_t stream) {

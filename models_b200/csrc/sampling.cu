@@ -13,6 +13,7 @@
 // and `counts` rows * vocab ints (only touched by rows whose penalty is > 1).
 #include "common.cuh"
 
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 MB_DEFINE_LAST_ERROR()
@@ -112,17 +113,36 @@ __device__ float philox_uniform(unsigned long long seed, unsigned long long coun
     return (float)(c[0] >> 8) * (1.0f / 16777216.0f);
 }
 
+constexpr int kArgmaxBlocks = 8;  // blocks of a cluster that share one row
+
+// grid (kArgmaxBlocks, rows), clusters of kArgmaxBlocks along x: each block scans an eighth of the
+// row, the first block of the cluster picks among the eight candidates (distributed shared memory).
 __global__ void __launch_bounds__(kThreads)
 argmax_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, int* __restrict__ out) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    namespace cg = cooperative_groups;
     __shared__ Best scratch[32];
-    const float* row = logits + (size_t)blockIdx.x * row_stride;
+    __shared__ Best block_result;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int part = cluster.block_rank();
+    const float* row = logits + (size_t)blockIdx.y * row_stride;
+    const int per_block = (vocab + kArgmaxBlocks - 1) / kArgmaxBlocks;
+    const int begin = part * per_block, end = min(vocab, begin + per_block);
     Best mine = {-CUDART_INF_F, 0x7fffffff};
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         const float v = row[i];
         if (v > mine.value) mine = {v, i};  // ascending i per thread: the first maximum stays
     }
     const Best best = block_best(mine, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = best.index == 0x7fffffff ? 0 : best.index;
+    if (threadIdx.x == 0) block_result = best;
+    cluster.sync();
+    if (part == 0 && threadIdx.x == 0) {
+        Best total = block_result;
+        for (int r = 1; r < kArgmaxBlocks; ++r) total = better(total, *cluster.map_shared_rank(&block_result, r));
+        out[blockIdx.y] = total.index == 0x7fffffff ? 0 : total.index;
+    }
+    cluster.sync();
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -370,7 +390,22 @@ using namespace mb;
 MB_EXPORT int mb_argmax_rows(const float* logits, int row_stride, int rows, int vocab, int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || row_stride < vocab) return fail("argmax_rows: vocab %d, row stride %d", vocab, row_stride);
-    argmax_rows_kernel<<<rows, kThreads, 0, stream>>>(logits, row_stride, vocab, out);
+    if (rows > 65535) return fail("argmax_rows: %d rows exceed the grid limit 65535", rows);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(kArgmaxBlocks, rows);
+    config.blockDim = dim3(kThreads);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = kArgmaxBlocks;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 2;
+    cudaError_t status = cudaLaunchKernelEx(&config, argmax_rows_kernel, logits, row_stride, vocab, out);
+    if (status != cudaSuccess) return fail("argmax_rows: launch failed: %s", cudaGetErrorString(status));
     return check_launch("argmax_rows");
 }
 

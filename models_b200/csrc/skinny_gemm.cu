@@ -1,23 +1,44 @@
 // Matrix products for decode: few activation rows (one per live sequence, up to 32) against a large
-// bfloat16 weight matrix W[N, K] that is read exactly once, straight from global memory into
-// tensor-core fragments.  The work is bound by the weight stream, so everything around the product
-// is folded into the same kernel:
+// bfloat16 weight matrix W[N, K] that is read exactly once.  The work is bound by the weight stream,
+// so everything around the product is folded into the same kernel:
 //   prologue  NORM: the activations are the float32 residual rows; RMSNorm (gain, epsilon) is applied
-//             on the fly -- the rows are multiplied by the gain while they are loaded, their sums of
+//             on the fly -- the rows are multiplied by the gain while they are staged, their sums of
 //             squares are gathered by the same loads, and 1/rms scales the accumulators at the end
 //             (sumSq/size + eps, sqrt, 1/rms: integrallis/models, backend-java/.../ops/TensorOps.java:45-58).
 //   epilogue  BF16 / F32: store.  RESIDUAL: add into the float32 residual stream
 //             (x = x + W.h, backend-java/.../llama/LlamaForwardPass.java:1131-1138,1172-1178).
-//             SWIGLU: the block computes a gate tile and the matching up tile and stores
-//             silu(gate) * up (backend-java/.../ops/TensorOps.java:1407-1425).
+//             SWIGLU: the 16 rows of a tile are 8 gate rows and the 8 up rows that match them, and
+//             silu(gate) * up is stored (backend-java/.../ops/TensorOps.java:1407-1425).
+//             ROPE: W is [q heads; k heads; v heads]; the 16 rows of a tile are 8 coordinates of a head
+//             and their rotation partners half a head further; query and key pairs are rotated by the
+//             token's position (x0' = x0*c - x1*s, x1' = x0*s + x1*c, backend-java/.../ops/TensorOps.java:1481-1486),
+//             queries go to the query buffer, keys and values straight into the paged cache
+//             (backend-java/.../llama/LlamaForwardPass.java:1070-1086).
 //
-// Layout of the work: a block owns 16 weight rows (two such tiles, `pair_offset` rows apart, for
-// SWIGLU); its warps split K.  A warp walks its K slice 64 columns at a time.  In an
-// m16n8k16 MMA the weights are the 16-row operand and up to 8 activation rows the 8-column one.  The
-// order of k inside an MMA is free as long as both operands agree, so each lane loads 16-byte
-// pieces: columns [k0 + 16*tid4, +16) of weight rows groupID and groupID+8, and the same columns of
-// activation row groupID.  Partial sums of the warps are added in warp order in shared memory.
+// Layout of the work.  A block of four warps owns 16 weight rows at a time and walks a sequence of
+// such row tiles; its warps split the
+// block's part of K.  Each warp streams its rows with cp.async through a private four-stage ring in
+// shared memory, 64 columns per stage, and the stages run on across row tiles, so loads stay in flight
+// from the first tile to the last.  The activations of the block's part of K are staged once, as
+// bfloat16, in shared memory.  At the end of a row tile the warps' partial sums are added in warp
+// order.  When a matrix has too few row tiles to occupy the GPU, K is also split over the blocks of a
+// thread-block cluster (up to 8); their partial sums meet in the shared memory of the cluster's first
+// block (distributed shared memory) and are added there in block order, so no result depends on
+// timing.
+//
+// The kernel is launched as a programmatic dependent of the kernel before it: its blocks may start
+// while that kernel drains, and they fill their weight rings (weights are never written) before they
+// wait for it (griddepcontrol.wait) and touch the activations.
+//
+// In an m16n8k16 MMA the weights are the 16-row operand and 8 activation rows the 8-column one.  The
+// order of k inside an MMA is free as long as both operands agree, so every lane works on 16-byte
+// pieces: of a 64-column step, lane (groupID, tid4) takes columns [8*tid4, +8) and [32 + 8*tid4, +8)
+// of weight rows groupID and groupID+8 and of activation row groupID.
 #include "common.cuh"
+
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
 
 MB_DEFINE_LAST_ERROR()
 
@@ -26,7 +47,12 @@ namespace mb {
 using bf16 = __nv_bfloat16;
 
 enum { PRO_NONE = 0, PRO_NORM = 1 };
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE = 4 };
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kDepth = 4;   // stages of the weight ring
+constexpr int kStep = 64;   // columns per stage
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -34,16 +60,23 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-__device__ __forceinline__ uint4 load_weights(const bf16* p) {
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
-    // streamed once: do not keep in L1
-    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
-
+__device__ __forceinline__ void sts128_zero(uint32_t addr) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(addr), "r"(0u) : "memory");
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -63,179 +96,308 @@ struct SkinnyArgs {
     float* out_f32;       // EPI_F32 output, or the residual stream for EPI_RESIDUAL
     int ld_out;
     int pair_offset;      // EPI_SWIGLU: the up tile starts pair_offset rows after the gate tile
-    int k_per_warp;       // multiple of 64
+    int k_split;          // blocks of a cluster that share K
+    int k_unit;           // columns per block, a multiple of 256
+    int k_warp;           // columns per warp, a multiple of 64
+    int clusters;         // clusters (of k_split blocks) in the grid; each walks row tiles cluster, cluster + clusters, ...
+    int dependent;        // launch as a programmatic dependent of the kernel before it
+    // EPI_ROPE
+    int heads, kv_heads, head_dim, page_size;
+    const int* positions;     // [batch]
+    const int* slot_mapping;  // [batch] flat cache position, < 0: do not store
+    const float* cos_table;   // [positions][head_dim / 2]
+    const float* sin_table;
+    bf16* k_pool;             // [pages][kv_heads][page_size][head_dim]
+    bf16* v_pool;
 };
 
-// NT: tiles of 8 activation rows.  TILES: 1, or 2 for paired row tiles.
-template <int NT, int PRO, int EPI>
-__global__ void __launch_bounds__(512)
-skinny_gemm_kernel(const SkinnyArgs args) {
-    constexpr int TILES = EPI == EPI_SWIGLU ? 2 : 1;
-    extern __shared__ float reduce_smem[];  // [warps][TILES][16][NT*8] then [warps][NT*8] sums of squares
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int group_id = lane >> 2, tid4 = lane & 3;
-    const int n0 = blockIdx.x * 16;
-    const int k_begin = warp * args.k_per_warp;
-    const int k_end = min(args.k, k_begin + args.k_per_warp);
+// Shared memory of a block, in bytes from the start:
+//   activations  [NT*8 rows][k_unit*2 + 64]          (row stride = 64 mod 128 keeps 8-lane phases conflict-free)
+//   ring         [4 warps][kDepth][2 halves][2 pieces][32 lanes][16]
+//   partial      [2 buffers][4 warps][16][NT*8] floats, then sums of squares [NT*8], [4][NT*8]
+template <int NT, int EPI>
+struct SmemPlan {
+    static constexpr int COLS = NT * 8;
+    static constexpr int kStageBytes = 4 * 32 * 16;
+    static constexpr int kPartialFloats = kWarps * 16 * COLS;
+    static __host__ __device__ int x_stride(int k_unit) { return k_unit * 2 + 64; }
+    static __host__ __device__ int ring_offset(int k_unit) { return COLS * x_stride(k_unit); }
+    static __host__ __device__ int partial_offset(int k_unit) { return ring_offset(k_unit) + kWarps * kDepth * kStageBytes; }
+    static __host__ __device__ int total(int k_unit) {
+        return partial_offset(k_unit) + (2 * kPartialFloats + COLS + kWarps * COLS) * (int)sizeof(float);
+    }
+};
 
-    // weight rows of this lane (clamped: rows beyond N are computed and dropped)
-    const bf16* w_rows[TILES][2];
-#pragma unroll
-    for (int t = 0; t < TILES; ++t)
+template <int NT, int PRO, int EPI>
+__global__ void __launch_bounds__(kThreads)
+skinny_gemm_kernel(const SkinnyArgs args) {
+    using Plan = SmemPlan<NT, EPI>;
+    constexpr int COLS = Plan::COLS;
+    constexpr bool kPaired = EPI == EPI_SWIGLU || EPI == EPI_ROPE;  // MMA rows 8..15 are the partners of rows 0..7
+    constexpr int kTileRows = kPaired ? 8 : 16;  // output rows (or pairs) per tile
+    extern __shared__ __align__(128) unsigned char smem[];
+    const uint32_t smem_base = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group_id = lane >> 2, tid4 = lane & 3;
+    const int rank = args.k_split > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int cluster_id = blockIdx.x / args.k_split, clusters = gridDim.x / args.k_split;
+    const int rows_total = EPI == EPI_SWIGLU ? args.pair_offset : (EPI == EPI_ROPE ? args.n / 2 : args.n);  // rows, or pairs
+    const int tiles_total = (rows_total + kTileRows - 1) / kTileRows;
+    const int tiles_mine = cluster_id < tiles_total ? (tiles_total - cluster_id + clusters - 1) / clusters : 0;
+    // K: the block's part, then this warp's slice of it
+    const int part_begin = rank * args.k_unit;
+    const int part_end = min(args.k, part_begin + args.k_unit);
+    const int k_begin = min(part_end, part_begin + warp * args.k_warp);
+    const int k_end = min(part_end, k_begin + args.k_warp);
+    const int steps = (k_end - k_begin + kStep - 1) / kStep;
+    const int stages_total = tiles_mine * steps;
+
+    // ---- weights: this lane's pieces of each stage go to ring[stage][half][piece][lane]
+    const uint32_t ring = smem_base + Plan::ring_offset(args.k_unit) + warp * kDepth * Plan::kStageBytes;
+    auto issue = [&](int stage_index) {
+        const int tile = cluster_id + (stage_index / steps) * clusters, step = stage_index % steps;
+        const uint32_t stage = ring + (stage_index % kDepth) * Plan::kStageBytes;
+        const int kc = k_begin + step * kStep + 8 * tid4;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int row = min(args.n - 1 + t * args.pair_offset, n0 + t * args.pair_offset + group_id + 8 * h);
-            w_rows[t][h] = args.w + (size_t)row * args.ldw;
-        }
-    // activation rows of this lane: batch index nt*8 + group_id
-    const bf16* x_rows[NT];
-    const float* xf_rows[NT];
-    bool x_live[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int b = nt * 8 + group_id;
-        x_live[nt] = b < args.batch;
-        const int src = x_live[nt] ? (args.rows ? args.rows[b] : b) : 0;
-        x_rows[nt] = PRO == PRO_NONE ? args.x + (size_t)src * args.ldx : nullptr;
-        xf_rows[nt] = PRO == PRO_NORM ? args.xf + (size_t)src * args.ldxf : nullptr;
-    }
-
-    float acc[TILES][NT][4];
-#pragma unroll
-    for (int t = 0; t < TILES; ++t)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) acc[t][nt][0] = acc[t][nt][1] = acc[t][nt][2] = acc[t][nt][3] = 0.0f;
-    float sum_sq[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) sum_sq[nt] = 0.0f;
-
-    // weights are fetched one step ahead of the products that use them
-    uint4 wv_next[TILES][2][2];
-    auto fetch = [&](int k0) {
-        const int kc = k0 + 16 * tid4;  // two 16-byte pieces per row: columns k0 + 16*tid4 + {0, 8}
-#pragma unroll
-        for (int t = 0; t < TILES; ++t)
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    wv_next[t][h][c] = (kc + 8 * c < k_end) ? load_weights(w_rows[t][h] + kc + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
-    };
-    if (k_begin < k_end) fetch(k_begin);
-    for (int k0 = k_begin; k0 < k_end; k0 += 64) {
-        const int kc = k0 + 16 * tid4;
-        uint4 wv[TILES][2][2];
-#pragma unroll
-        for (int t = 0; t < TILES; ++t)
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int c = 0; c < 2; ++c) wv[t][h][c] = wv_next[t][h][c];
-        if (k0 + 64 < k_end) fetch(k0 + 64);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            uint4 xv[2];
+            // MMA rows groupID and groupID+8: 16 consecutive weight rows, or 8 gate rows and their 8 up rows
+            int row;
+            if (EPI == EPI_SWIGLU) {
+                row = min(rows_total - 1, tile * 8 + group_id) + h * args.pair_offset;
+            } else if (EPI == EPI_ROPE) {  // tile = (head, eighth of its first half); partner half a head further
+                const int tiles_per_head = args.head_dim / 16;
+                row = (tile / tiles_per_head) * args.head_dim + (tile % tiles_per_head) * 8 + group_id + h * (args.head_dim / 2);
+            } else {
+                row = min(rows_total - 1, tile * 16 + group_id + 8 * h);
+            }
+            const bf16* w_row = args.w + (size_t)row * args.ldw;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const int kk = kc + 8 * c;
-                xv[c] = make_uint4(0u, 0u, 0u, 0u);
-                if (kk < k_end && x_live[nt]) {
-                    if (PRO == PRO_NONE) {
-                        xv[c] = *reinterpret_cast<const uint4*>(x_rows[nt] + kk);
-                    } else {
-                        const float4 a = *reinterpret_cast<const float4*>(xf_rows[nt] + kk);
-                        const float4 b = *reinterpret_cast<const float4*>(xf_rows[nt] + kk + 4);
-                        const float4 ga = *reinterpret_cast<const float4*>(args.gain + kk);
-                        const float4 gb = *reinterpret_cast<const float4*>(args.gain + kk + 4);
-                        sum_sq[nt] += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
-                        xv[c] = make_uint4(pack2(a.x * ga.x, a.y * ga.y), pack2(a.z * ga.z, a.w * ga.w),
-                                           pack2(b.x * gb.x, b.y * gb.y), pack2(b.z * gb.z, b.w * gb.w));
+                const int kk = kc + 32 * c;
+                const uint32_t dst = stage + ((h * 2 + c) * 32 + lane) * 16;
+                if (kk < k_end) cp_async16(dst, w_row + kk);
+                else sts128_zero(dst);
+            }
+        }
+    };
+    grid_launch_dependents();  // the next kernel's blocks may be scheduled as this one's leave
+    for (int s = 0; s < kDepth - 1; ++s) {
+        if (s < stages_total) issue(s);
+        cp_async_commit();
+    }
+    grid_dependency_wait();  // from here on the results of the kernel before this one are visible
+
+    // ---- activations of this block's part of K -> shared memory, bfloat16
+    const int x_stride = Plan::x_stride(args.k_unit);
+    float* partial = reinterpret_cast<float*>(smem + Plan::partial_offset(args.k_unit));  // two buffers
+    float* sq_total = partial + 2 * Plan::kPartialFloats;  // [COLS]
+    float* sq_warp = sq_total + COLS;                      // [kWarps][COLS]
+    const int chunks = (part_end - part_begin + 7) / 8;
+    const int chunks_padded = args.k_unit / 8;  // the last steps may read past the part: zeros there
+    for (int b = 0; b < COLS; ++b) {
+        const int live_chunks = b < args.batch ? max(chunks, 0) : 0;
+        for (int c = live_chunks + threadIdx.x; c < chunks_padded; c += kThreads) sts128_zero(smem_base + b * x_stride + c * 16);
+    }
+    if (PRO == PRO_NONE) {
+        for (int b = 0; b < args.batch; ++b) {
+            const bf16* src = args.x + (size_t)b * args.ldx + part_begin;
+            for (int c = threadIdx.x; c < chunks; c += kThreads) cp_async16(smem_base + b * x_stride + c * 16, src + c * 8);
+        }
+    } else {
+#pragma unroll
+        for (int b0 = 0; b0 < COLS; b0 += 8) {  // eight rows at a time: all their loads are issued before any is used
+            if (b0 >= args.batch) break;
+            const float* src[8];
+            float ss[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int b = b0 + j;
+                src[j] = args.xf + (size_t)(b < args.batch ? (args.rows ? args.rows[b] : b) : 0) * args.ldxf + part_begin;
+                ss[j] = 0.0f;
+            }
+            for (int c = threadIdx.x; c < chunks; c += kThreads) {
+                const float4 ga = *reinterpret_cast<const float4*>(args.gain + part_begin + c * 8);
+                const float4 gd = *reinterpret_cast<const float4*>(args.gain + part_begin + c * 8 + 4);
+                float4 a[8], d[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (b0 + j < args.batch) {
+                        a[j] = *reinterpret_cast<const float4*>(src[j] + c * 8);
+                        d[j] = *reinterpret_cast<const float4*>(src[j] + c * 8 + 4);
                     }
-                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (b0 + j < args.batch) {
+                        ss[j] += a[j].x * a[j].x + a[j].y * a[j].y + a[j].z * a[j].z + a[j].w * a[j].w + d[j].x * d[j].x +
+                                 d[j].y * d[j].y + d[j].z * d[j].z + d[j].w * d[j].w;
+                        *reinterpret_cast<uint4*>(smem + (b0 + j) * x_stride + c * 16) =
+                            make_uint4(pack2(a[j].x * ga.x, a[j].y * ga.y), pack2(a[j].z * ga.z, a[j].w * ga.w),
+                                       pack2(d[j].x * gd.x, d[j].y * gd.y), pack2(d[j].z * gd.z, d[j].w * gd.w));
+                    }
             }
 #pragma unroll
-            for (int t = 0; t < TILES; ++t) {
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    mma_bf16(acc[t][nt], wv[t][0][c].x, wv[t][1][c].x, wv[t][0][c].y, wv[t][1][c].y, xv[c].x, xv[c].y);
-                    mma_bf16(acc[t][nt], wv[t][0][c].z, wv[t][1][c].z, wv[t][0][c].w, wv[t][1][c].w, xv[c].z, xv[c].w);
-                }
+            for (int j = 0; j < 8; ++j) {
+                const float total = warp_sum(ss[j]);
+                if (lane == 0) sq_warp[warp * COLS + b0 + j] = total;
             }
         }
     }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    if (PRO == PRO_NORM && threadIdx.x < COLS) {
+        float s = 0.0f;
+        if (threadIdx.x < (args.batch + 7) / 8 * 8)
+            for (int w = 0; w < kWarps; ++w) s += sq_warp[w * COLS + threadIdx.x];
+        sq_total[threadIdx.x] = s;
+    }
+    bool sq_gathered = args.k_split == 1;
 
-    // partial results of the warps -> shared memory
-    constexpr int COLS = NT * 8;
-    float* part = reduce_smem + (size_t)warp * TILES * 16 * COLS;
+    // ---- row tile after row tile; the ring keeps running across them
+    const uint32_t x_lane = smem_base + group_id * x_stride + ((k_begin - part_begin) + 8 * tid4) * 2;
+    int stage_index = 0;
+    for (int local = 0; local < tiles_mine; ++local) {
+        const int tile = cluster_id + local * clusters;
+        float acc[NT][4];
 #pragma unroll
-    for (int t = 0; t < TILES; ++t)
+        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+        for (int step = 0; step < steps; ++step, ++stage_index) {
+            if (stage_index + kDepth - 1 < stages_total) issue(stage_index + kDepth - 1);
+            cp_async_commit();
+            cp_async_wait<kDepth - 1>();  // this lane's pieces of the stage have landed; nobody else reads them
+            const uint32_t stage = ring + (stage_index % kDepth) * Plan::kStageBytes;
+            uint4 wv[2][2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) wv[h][c] = lds128(stage + ((h * 2 + c) * 32 + lane) * 16);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint4 xv = lds128(x_lane + nt * 8 * x_stride + (step * kStep + 32 * c) * 2);
+                    mma_bf16(acc[nt], wv[0][c].x, wv[1][c].x, wv[0][c].y, wv[1][c].y, xv.x, xv.y);
+                    mma_bf16(acc[nt], wv[0][c].z, wv[1][c].z, wv[0][c].w, wv[1][c].w, xv.z, xv.w);
+                }
+            }
+        }
+
+        // the warps' partial sums of this row tile: c0,c1 = (MMA row groupID, activation rows 2*tid4, +1); c2,c3 = row +8
+        float* mine = partial + (local & 1) * Plan::kPartialFloats;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int row = group_id + 8 * (i >> 1), col = nt * 8 + tid4 * 2 + (i & 1);
-                part[(t * 16 + row) * COLS + col] = acc[t][nt][i];
+            for (int i = 0; i < 4; ++i)
+                mine[(warp * 16 + group_id + 8 * (i >> 1)) * COLS + nt * 8 + tid4 * 2 + (i & 1)] = acc[nt][i];
+        if (args.k_split > 1) {
+            cg::this_cluster().sync();
+            if (rank != 0) continue;
+            if (PRO == PRO_NORM && !sq_gathered) {
+                if (threadIdx.x < COLS) {
+                    float s = 0.0f;
+                    for (int r = 0; r < args.k_split; ++r) s += cg::this_cluster().map_shared_rank(sq_total, r)[threadIdx.x];
+                    sq_warp[threadIdx.x] = s;  // the whole row's sum of squares
+                }
+                __syncthreads();
+                sq_total = sq_warp;
+                sq_gathered = true;
             }
-    float* sq = reduce_smem + (size_t)warps * TILES * 16 * COLS;
-    if (PRO == PRO_NORM) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            float s = sum_sq[nt];
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if (tid4 == 0) sq[warp * COLS + nt * 8 + group_id] = s;
+        } else {
+            __syncthreads();
+        }
+        for (int i = threadIdx.x; i < kTileRows * COLS; i += kThreads) {
+            const int row_in_tile = i % kTileRows, col = i / kTileRows;  // neighbouring threads store neighbouring output columns
+            const int row = tile * kTileRows + row_in_tile;
+            if (row >= rows_total || col >= args.batch) continue;
+            float value = 0.0f, second = 0.0f;  // second: the up row that matches a gate row
+            for (int r = 0; r < args.k_split; ++r) {
+                const float* from = args.k_split > 1 ? cg::this_cluster().map_shared_rank(mine, r) : mine;
+                for (int w = 0; w < kWarps; ++w) {
+                    value += from[(w * 16 + row_in_tile) * COLS + col];
+                    if (kPaired) second += from[(w * 16 + row_in_tile + 8) * COLS + col];
+                }
+            }
+            if (PRO == PRO_NORM) {
+                const float inv_rms = 1.0f / sqrtf(sq_total[col] / (float)args.k + args.eps);
+                value *= inv_rms;
+                second *= inv_rms;
+            }
+            const size_t at = (size_t)col * args.ld_out + row;
+            if (EPI == EPI_BF16) args.out_bf16[at] = __float2bfloat16_rn(value);
+            if (EPI == EPI_F32) args.out_f32[at] = value;
+            if (EPI == EPI_RESIDUAL) args.out_f32[at] += value;
+            if (EPI == EPI_SWIGLU) args.out_bf16[at] = __float2bfloat16_rn(value / (1.0f + expf(-value)) * second);
+            if (EPI == EPI_ROPE) {
+                const int tiles_per_head = args.head_dim / 16, half = args.head_dim / 2;
+                const int head = tile / tiles_per_head, d0 = (tile % tiles_per_head) * 8 + row_in_tile;
+                // queries and keys pass through bfloat16 before the rotation, as they do when the product stores them
+                float x0 = __bfloat162float(__float2bfloat16_rn(value)), x1 = __bfloat162float(__float2bfloat16_rn(second));
+                if (head < args.heads + args.kv_heads) {
+                    const size_t at_table = (size_t)args.positions[col] * half + d0;
+                    const float c = args.cos_table[at_table], sn = args.sin_table[at_table];
+                    const float r0 = x0 * c - x1 * sn, r1 = x0 * sn + x1 * c;
+                    x0 = r0;
+                    x1 = r1;
+                }
+                if (head < args.heads) {
+                    bf16* q = args.out_bf16 + (size_t)col * args.ld_out + (size_t)head * args.head_dim;
+                    q[d0] = __float2bfloat16_rn(x0);
+                    q[d0 + half] = __float2bfloat16_rn(x1);
+                } else {
+                    const int slot = args.slot_mapping[col];
+                    if (slot >= 0) {
+                        const bool is_key = head < args.heads + args.kv_heads;
+                        const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
+                        const size_t page = slot / args.page_size, offset = slot % args.page_size;
+                        bf16* dst = (is_key ? args.k_pool : args.v_pool) +
+                                    ((page * args.kv_heads + kv_head) * args.page_size + offset) * args.head_dim;
+                        dst[d0] = __float2bfloat16_rn(x0);
+                        dst[d0 + half] = __float2bfloat16_rn(x1);
+                    }
+                }
+            }
         }
     }
-    __syncthreads();
-
-    for (int i = threadIdx.x; i < 16 * COLS; i += blockDim.x) {
-        const int col = i / 16, row = i % 16;  // row fastest: neighbouring threads store neighbouring columns of the output
-        if (col >= args.batch || n0 + row >= args.n) continue;
-        float value[TILES];
-#pragma unroll
-        for (int t = 0; t < TILES; ++t) {
-            float s = 0.0f;
-            for (int w = 0; w < warps; ++w) s += reduce_smem[((size_t)w * TILES + t) * 16 * COLS + row * COLS + col];
-            value[t] = s;
-        }
-        if (PRO == PRO_NORM) {
-            float s = 0.0f;
-            for (int w = 0; w < warps; ++w) s += sq[w * COLS + col];
-            const float inv_rms = 1.0f / sqrtf(s / (float)args.k + args.eps);
-#pragma unroll
-            for (int t = 0; t < TILES; ++t) value[t] *= inv_rms;
-        }
-        const size_t at = (size_t)col * args.ld_out + n0 + row;
-        if (EPI == EPI_BF16) args.out_bf16[at] = __float2bfloat16_rn(value[0]);
-        if (EPI == EPI_F32) args.out_f32[at] = value[0];
-        if (EPI == EPI_RESIDUAL) args.out_f32[at] += value[0];
-        if (EPI == EPI_SWIGLU) {
-            const float g = value[0], u = value[TILES - 1];
-            args.out_bf16[at] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-        }
-    }
+    // a cluster's blocks leave together: the first block reads the others' shared memory until the end
+    if (args.k_split > 1) cg::this_cluster().sync();
 }
 
 template <int NT, int PRO, int EPI>
-static int launch(const SkinnyArgs& args, int warps, cudaStream_t stream) {
-    constexpr int TILES = EPI == EPI_SWIGLU ? 2 : 1;
-    const size_t smem = ((size_t)warps * TILES * 16 * NT * 8 + (size_t)warps * NT * 8) * sizeof(float);
+static int launch(const SkinnyArgs& args, cudaStream_t stream) {
+    using Plan = SmemPlan<NT, EPI>;
+    const int smem = Plan::total(args.k_unit);
     auto kernel = skinny_gemm_kernel<NT, PRO, EPI>;
-    if (smem > 48 * 1024) {
-        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (status != cudaSuccess) return fail("skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+    static int reserved = 0;
+    if (smem > reserved) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (status != cudaSuccess) return fail("skinny_gemm: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(status));
+        reserved = smem;
     }
-    const int rows = EPI == EPI_SWIGLU ? args.pair_offset : args.n;
-    kernel<<<(rows + 15) / 16, warps * 32, smem, stream>>>(args);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(args.clusters * args.k_split);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = args.k_split;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = args.dependent ? 2 : 1;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, args);
+    if (status != cudaSuccess) return fail("skinny_gemm: launch failed: %s", cudaGetErrorString(status));
     return check_launch("skinny_gemm");
 }
 
 template <int PRO, int EPI>
-static int launch_nt(const SkinnyArgs& args, int warps, cudaStream_t stream) {
-    if (args.batch <= 8) return launch<1, PRO, EPI>(args, warps, stream);
-    if (args.batch <= 16) return launch<2, PRO, EPI>(args, warps, stream);
+static int launch_nt(const SkinnyArgs& args, cudaStream_t stream) {
+    if (args.batch <= 8) return launch<1, PRO, EPI>(args, stream);
+    if (args.batch <= 16) return launch<2, PRO, EPI>(args, stream);
     if (PRO == PRO_NORM) return fail("skinny_gemm: the norm prologue takes at most 16 rows, got %d", args.batch);
-    if (args.batch <= 32) return launch<4, PRO_NONE, EPI>(args, warps, stream);
+    if (args.batch <= 32) return launch<4, PRO_NONE, EPI>(args, stream);
     return fail("skinny_gemm: takes at most 32 activation rows, got %d", args.batch);
 }
 
@@ -249,9 +411,9 @@ MB_EXPORT int mb_skinny_max_rows(int with_norm) { return with_norm ? 16 : 32; }
 // else xf (float32 rows, optionally picked by `rows`) normalised with `gain` and `eps`.
 // epilogue 0: out bfloat16 [batch, n]; 1: out float32; 2: out float32 += ; 3: w holds gate rows
 // [0, n/2) and up rows [n/2, n), out bfloat16 [batch, n/2] = silu(gate) * up.
-MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, const float* xf,
-                             int ldxf, const float* gain, float eps, const int* rows, void* out, int ld_out,
-                             int epilogue, int multiprocessors, cudaStream_t stream) {
+static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, const float* xf,
+                       int ldxf, const float* gain, float eps, const int* rows, void* out, int ld_out,
+                       int epilogue, int multiprocessors, int dependent, SkinnyArgs args, cudaStream_t stream) {
     if (batch <= 0 || n <= 0) return 0;
     if (batch > 32) return fail("skinny_gemm: takes at most 32 activation rows, got %d", batch);
     if (k <= 0 || k % 8 || ldw % 8) return fail("skinny_gemm: k (%d) and the weight row stride (%d) must be multiples of 8", k, ldw);
@@ -261,19 +423,41 @@ MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, co
         return fail("skinny_gemm: the norm prologue needs 16-byte aligned float rows and gain");
     if (!norm && (!x || ldx % 8 || ((uintptr_t)x & 15))) return fail("skinny_gemm: activations need 16-byte aligned bfloat16 rows");
     if (epilogue == EPI_SWIGLU && n % 2) return fail("skinny_gemm: the gated epilogue needs an even number of weight rows, got %d", n);
-    SkinnyArgs args{};
     args.w = (const bf16*)w; args.ldw = ldw; args.n = n; args.k = k; args.batch = batch;
     args.x = (const bf16*)x; args.ldx = ldx; args.xf = xf; args.ldxf = ldxf; args.gain = gain; args.eps = eps; args.rows = rows;
     args.out_bf16 = (bf16*)out; args.out_f32 = (float*)out; args.ld_out = ld_out;
     args.pair_offset = epilogue == EPI_SWIGLU ? n / 2 : 0;
+    args.dependent = dependent;
     if (epilogue == EPI_SWIGLU) args.n = n / 2;
-    // warps per block: enough blocks x warps to keep every multiprocessor streaming, K slices of >= 128
-    const int tiles = (args.n + 15) / 16;
-    int warps = 1;
-    while (warps < 16 && tiles * warps < multiprocessors * 16 && k / (warps * 2) >= 128) warps *= 2;
-    args.k_per_warp = ((k + warps - 1) / warps + 63) / 64 * 64;
+    // Planning.  A block's shared memory holds its activations (rows x k_unit bfloat16), the warps' rings
+    // and the partial sums; as many blocks as fit stay resident per multiprocessor (at most four).
+    // With fewer row tiles than resident blocks, K is split over a cluster (a warp keeps at least 256
+    // columns); with more, blocks walk several row tiles.
+    const int rows_total = (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE) ? n / 2 : n;
+    const int tiles = (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE) ? (rows_total + 7) / 8 : (rows_total + 15) / 16;
+    const int cols = batch <= 8 ? 8 : (batch <= 16 ? 16 : 32);
+    auto smem_for = [&](int split) {
+        const int k_unit = ((k + split - 1) / split + 255) / 256 * 256;
+        return (size_t)cols * (k_unit * 2 + 64) + (size_t)kWarps * kDepth * 2048 +
+               (size_t)(2 * kWarps * 16 * cols + (1 + kWarps) * cols) * sizeof(float);
+    };
+    auto resident_for = [&](int split) {
+        const size_t per_sm = 220 * 1024 / smem_for(split);
+        return multiprocessors * (int)(per_sm > 4 ? 4 : per_sm);
+    };
+    int split = 1;
+    while (split < 8 && smem_for(split) > 200 * 1024) split *= 2;
+    while (split < 8 && tiles * split * 2 <= resident_for(split * 2) && k / (split * 2) >= 256 * kWarps) split *= 2;
+    if (smem_for(split) > 200 * 1024)
+        return fail("skinny_gemm: %d activation rows of %d columns do not fit shared memory", batch, k);
+    args.k_split = split;
+    args.k_unit = ((k + split - 1) / split + 255) / 256 * 256;
+    args.k_warp = args.k_unit / kWarps;
+    const int resident_clusters = resident_for(split) / split;
+    args.clusters = tiles < resident_clusters ? tiles : resident_clusters;
+    if (args.clusters < 1) args.clusters = 1;
 #define MB_CASE(PRO, EPI) \
-    if ((norm ? PRO_NORM : PRO_NONE) == PRO && epilogue == EPI) return launch_nt<PRO, EPI>(args, warps, stream);
+    if ((norm ? PRO_NORM : PRO_NONE) == PRO && epilogue == EPI) return launch_nt<PRO, EPI>(args, stream);
     MB_CASE(PRO_NONE, EPI_BF16)
     MB_CASE(PRO_NONE, EPI_F32)
     MB_CASE(PRO_NONE, EPI_RESIDUAL)
@@ -281,6 +465,36 @@ MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, co
     MB_CASE(PRO_NORM, EPI_F32)
     MB_CASE(PRO_NORM, EPI_SWIGLU)
     MB_CASE(PRO_NONE, EPI_SWIGLU)
+    MB_CASE(PRO_NORM, EPI_ROPE)
+    MB_CASE(PRO_NONE, EPI_ROPE)
 #undef MB_CASE
     return fail("skinny_gemm: no kernel for prologue %d with epilogue %d", norm ? 1 : 0, epilogue);
+}
+
+// `dependent` != 0 launches the kernel as a programmatic dependent of the kernel before it in the stream.
+MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, const float* xf,
+                             int ldxf, const float* gain, float eps, const int* rows, void* out, int ld_out,
+                             int epilogue, int multiprocessors, int dependent, cudaStream_t stream) {
+    if (epilogue == EPI_ROPE) return fail("skinny_gemm: the rotary epilogue has an entry point of its own");
+    return skinny_gemm(w, ldw, n, k, batch, x, ldx, xf, ldxf, gain, eps, rows, out, ld_out, epilogue, multiprocessors, dependent,
+                       SkinnyArgs{}, stream);
+}
+
+// The q/k/v product of an attention layer with rotation and cache write folded in.  w: [(heads + 2 *
+// kv_heads) * head_dim, k]; rotation over the whole head with split-half pairs; q_out: bfloat16
+// [batch, heads * head_dim] (row stride ld_q); keys and values go to the pools at slot_mapping.
+MB_EXPORT int mb_skinny_qkv_rope(const void* w, int ldw, int k, int batch, const void* x, int ldx, const float* xf, int ldxf,
+                                 const float* gain, float eps, void* q_out, int ld_q, int heads, int kv_heads, int head_dim,
+                                 const int* positions, const float* cos_table, const float* sin_table, void* k_pool,
+                                 void* v_pool, const int* slot_mapping, int page_size, int multiprocessors, int dependent,
+                                 cudaStream_t stream) {
+    if (head_dim <= 0 || head_dim % 16) return fail("skinny_qkv_rope: head_dim %d must be a multiple of 16", head_dim);
+    if (!positions || !cos_table || !sin_table || !k_pool || !v_pool || !slot_mapping || page_size <= 0)
+        return fail("skinny_qkv_rope: needs positions, cos/sin tables, cache pools, a slot mapping and a page size");
+    SkinnyArgs args{};
+    args.heads = heads; args.kv_heads = kv_heads; args.head_dim = head_dim; args.page_size = page_size;
+    args.positions = positions; args.slot_mapping = slot_mapping; args.cos_table = cos_table; args.sin_table = sin_table;
+    args.k_pool = (bf16*)k_pool; args.v_pool = (bf16*)v_pool;
+    return skinny_gemm(w, ldw, (heads + 2 * kv_heads) * head_dim, k, batch, x, ldx, xf, ldxf, gain, eps, nullptr, q_out, ld_q,
+                       EPI_ROPE, multiprocessors, dependent, args, stream);
 }

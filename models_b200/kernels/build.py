@@ -35,6 +35,7 @@ class KernelBuildError(RuntimeError):
 
 
 _loaded: Dict[str, ctypes.CDLL] = {}
+_by_request: Dict[tuple, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
 
@@ -139,10 +140,15 @@ def build_library(name: str, sources: Sequence[str], defines: Mapping[str, objec
 def load_library(name: str, sources: Sequence[str], defines: Mapping[str, object] | None = None,
                  extra_flags: Sequence[str] = ()) -> ctypes.CDLL:
     """The loaded library (compiled first if needed).  Raises KernelBuildError; never falls back."""
+    quick = (name, tuple(sources), tuple(sorted((defines or {}).items())), tuple(extra_flags))
+    lib = _by_request.get(quick)  # the common case: no hashing of sources on the way to a launch
+    if lib is not None:
+        return lib
     out, _ = library_path(name, sources, defines, extra_flags)
     key = str(out)
     with _lock:
         if key in _loaded:
+            _by_request[quick] = _loaded[key]
             return _loaded[key]
         path = build_library(name, sources, defines, extra_flags)
         try:
@@ -151,6 +157,7 @@ def load_library(name: str, sources: Sequence[str], defines: Mapping[str, object
             raise KernelBuildError(f"cannot load {path}: {error}") from error
         lib.mb_last_error.restype = ctypes.c_char_p
         _loaded[key] = lib
+        _by_request[quick] = lib
         return lib
 
 

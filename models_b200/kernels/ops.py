@@ -233,27 +233,34 @@ def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, h
 
 
 def decode_splits(sequences: int, heads: int, kv_heads: int, max_blocks: int, multiprocessors: int = 148) -> int:
-    """How many blocks share one sequence's keys: enough to fill the GPU about four times over, at
-    most 16, at most one per cache page."""
+    """How many blocks share one sequence's keys: a power of two that fills the GPU about four times
+    over, at most 8 (they form one thread-block cluster), at most one per cache page."""
     base = sequences * kv_heads * (-(-(heads // kv_heads) // 16))
-    return max(1, min(16, max_blocks, (4 * multiprocessors) // max(1, base)))
+    limit = max(1, min(8, max_blocks, (4 * multiprocessors) // max(1, base)))
+    splits = 1
+    while splits * 2 <= limit:
+        splits *= 2
+    return splits
 
 
 def decode_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                      block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, heads: int, kv_heads: int,
-                     head_dim: int, window: Optional[int], scale: float, splits: int) -> None:
-    """One query token per sequence (row cu_q[s] of q) against its cached keys and values."""
+                     head_dim: int, window: Optional[int], scale: float, splits: int, use_scratch: bool = False) -> None:
+    """One query token per sequence (row cu_q[s] of q) against its cached keys and values.  The keys
+    of a sequence are split over `splits` blocks; 2, 4 or 8 of them combine inside a thread-block
+    cluster, other counts (or use_scratch) through scratch memory and a second kernel."""
     _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim)
     sequences = kv_lens.numel()
     lib = attention_tc(head_dim)
-    lib.mb_decode_scratch_floats.restype = ctypes.c_size_t
-    need = lib.mb_decode_scratch_floats(sequences, heads, splits)
-    scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    scratch = None
+    if splits > 1 and (use_scratch or splits not in (2, 4, 8)):
+        lib.mb_decode_scratch_floats.restype = ctypes.c_size_t
+        scratch = torch.empty((lib.mb_decode_scratch_floats(sequences, heads, splits),), dtype=torch.float32, device=q.device)
     _run(lib, lib.mb_decode_attention(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(v_pool),
                                       _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens), sequences, heads,
                                       kv_heads, k_pool.shape[2], window or 0, ctypes.c_float(scale), splits,
                                       _p(scratch), _stream()))
-    if splits > 1:
+    if scratch is not None:
         _launches[0] += 1  # the combine kernel
 
 
@@ -345,8 +352,36 @@ def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] =
     lib = skinny()
     _run(lib, lib.mb_skinny_gemm(_p(weight), weight.stride(0), n, k, batch, _p(x), x.stride(0) if x is not None else 0,
                                  _p(xf), xf.stride(0) if xf is not None else 0, _p(gain), ctypes.c_float(eps), _p(rows),
-                                 _p(out), out.stride(0), epilogue, _sm_count(weight.device), _stream()))
+                                 _p(out), out.stride(0), epilogue, _sm_count(weight.device), 1, _stream()))
     return out
+
+
+def skinny_qkv_rope(weight: torch.Tensor, xf: torch.Tensor, gain: torch.Tensor, eps: float, heads: int, kv_heads: int,
+                    head_dim: int, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
+                    v_pool: torch.Tensor, slot_mapping: torch.Tensor) -> torch.Tensor:
+    """The q/k/v product of an attention layer on few rows with everything around it folded in: RMSNorm
+    of the float32 residual rows `xf` before it, rotation of queries and keys (split-half pairs over
+    the whole head) and the paged cache write of keys and values after it.  Returns the rotated
+    queries, bfloat16 [rows, heads * head_dim]."""
+    _cuda(weight, xf, gain, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    batch, k = xf.shape
+    if weight.shape != ((heads + 2 * kv_heads) * head_dim, k) or not skinny_takes(weight, batch, True):
+        raise KernelError(f"skinny_qkv_rope does not take a {tuple(weight.shape)} {weight.dtype} weight with {batch} rows")
+    if xf.dtype != torch.float32 or xf.stride(1) != 1 or gain.dtype != torch.float32 or gain.numel() != k:
+        raise KernelError("skinny_qkv_rope needs float32 residual rows and gain")
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    if cos.dtype != torch.float32 or cos.shape[-1] != head_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous():
+        raise KernelError(f"cos/sin tables must be contiguous float32 [positions, {head_dim // 2}]")
+    if k_pool.dtype != torch.bfloat16 or k_pool.shape != v_pool.shape or k_pool.shape[1] != kv_heads or k_pool.shape[3] != head_dim:
+        raise KernelError("cache pools must be bfloat16 [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((batch, heads * head_dim), dtype=torch.bfloat16, device=weight.device)
+    lib = skinny()
+    _run(lib, lib.mb_skinny_qkv_rope(_p(weight), weight.stride(0), k, batch, None, 0, _p(xf), xf.stride(0), _p(gain),
+                                     ctypes.c_float(eps), _p(q), q.stride(0), heads, kv_heads, head_dim, _p(positions),
+                                     _p(cos), _p(sin), _p(k_pool), _p(v_pool), _p(slot_mapping), k_pool.shape[2],
+                                     _sm_count(weight.device), 1, _stream()))
+    return q
 
 
 # ------------------------------------------------------------------------------------ sampling

@@ -80,9 +80,18 @@ class AttentionMixer(Mixer):
     def forward_residual(self, x: torch.Tensor, norm, batch, run: RunContext) -> None:
         """x += Wo . attention(rotate(Wqkv . norm(x))): the norm rides in the q/k/v product, the
         residual add in the output product."""
-        writes = run.writes_cache
-        qkv = ops.skinny_gemm(self.w_qkv if writes else self.w_q, ops.EPI_BF16, xf=x, gain=norm.weight, eps=norm.spec.eps)
-        attended = self._rotate_store_attend(qkv, batch, run)
+        writes, s, pos = run.writes_cache, self.spec, self.position
+        if (writes and pos is not None and pos.rotary_dim == s.head_dim and not pos.interleaved and s.head_dim % 16 == 0
+                and run.k_pool is not None and run.k_pool.dtype == torch.bfloat16):
+            # rotation and cache write ride in the q/k/v product too
+            group = batch.groups[run.group]
+            q = ops.skinny_qkv_rope(self.w_qkv, x, norm.weight, norm.spec.eps, s.num_heads, s.num_kv_heads, s.head_dim,
+                                    batch.positions, pos.cos, pos.sin, run.k_pool, run.v_pool, group.slot_mapping)
+            attended = torch.empty((q.shape[0], self.q_width), dtype=q.dtype, device=q.device)
+            self.attend(q, attended, batch, group, run)
+        else:
+            qkv = ops.skinny_gemm(self.w_qkv if writes else self.w_q, ops.EPI_BF16, xf=x, gain=norm.weight, eps=norm.spec.eps)
+            attended = self._rotate_store_attend(qkv, batch, run)
         ops.skinny_gemm(self.w_o, ops.EPI_RESIDUAL, x=attended, out=x)
 
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:

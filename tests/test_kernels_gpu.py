@@ -237,9 +237,9 @@ def test_tensor_core_attention(cuda_device, heads, kv_heads, head_dim, window):
             ops.prefill_attention(qd, out, *common, max(q_lens), heads, kv_heads, head_dim, window, scale)
             close(out, expected, dtype)
         else:
-            for splits in (1, 3, 16):
+            for splits, use_scratch in ((1, False), (2, False), (4, False), (8, False), (3, False), (16, False), (4, True)):
                 out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
-                ops.decode_attention(qd, out, *common, heads, kv_heads, head_dim, window, scale, splits)
+                ops.decode_attention(qd, out, *common, heads, kv_heads, head_dim, window, scale, splits, use_scratch)
                 close(out, expected, dtype)
 
 
@@ -373,3 +373,48 @@ def test_skinny_gemm_all_prologues_and_epilogues(cuda_device, batch, n, k):
             ops.skinny_gemm(wd, ops.EPI_F32, xf=x.float().cuda(), gain=torch.ones(k).cuda(), eps=1e-5)
     with pytest.raises(ops.KernelError):
         ops.skinny_gemm(wd, ops.EPI_F32, x=torch.zeros(33, k, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("batch", [1, 5, 16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 8, 64, 2048), (6, 3, 48, 72)])
+def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads, kv_heads, head_dim, hidden):
+    """The folded decode kernel (norm, q/k/v product, rotation, cache write) against the plain parts."""
+    from models_b200.kernels import ops
+
+    page = 64
+    g = torch.Generator().manual_seed(batch + head_dim)
+    n = (heads + 2 * kv_heads) * head_dim
+    w = (torch.randn(n, hidden, generator=g) * 0.05).bfloat16()
+    xf = torch.randn(batch, hidden, generator=g) * 2
+    gain = 1 + 0.1 * torch.randn(hidden, generator=g)
+    eps = 1e-5
+    positions = torch.randint(0, 300, (batch,), generator=g).int()
+    cos, sin = plain_llama.rope_cos_sin(torch.arange(300), plain_llama.rope_pair_frequencies(head_dim, 50000.0), None)
+    pages = batch + 2
+    k_pool, v_pool = _pools(pages, kv_heads, page, head_dim, torch.bfloat16, 3)
+    slots = (torch.randperm(pages - 1, generator=g)[:batch] + 1) * page + torch.randint(0, page, (batch,), generator=g)
+    slots = slots.int()
+    if batch > 1:
+        slots[1] = -1  # a padding row stores nothing
+    kd, vd = k_pool.cuda(), v_pool.cuda()
+    q = ops.skinny_qkv_rope(w.cuda(), xf.cuda(), gain.cuda(), eps, heads, kv_heads, head_dim, positions.cuda(), cos.cuda(),
+                            sin.cuda(), kd, vd, slots.cuda())
+    qkv = plain_llama.rms_norm(xf, gain, eps) @ w.float().t()
+    c, s_ = cos[positions.long()], sin[positions.long()]
+    want_q = plain_llama.rope_rotate_split_half(qkv[:, : heads * head_dim].reshape(batch, heads, head_dim), c, s_)
+    want_k = plain_llama.rope_rotate_split_half(
+        qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(batch, kv_heads, head_dim), c, s_)
+    want_v = qkv[:, (heads + kv_heads) * head_dim:].reshape(batch, kv_heads, head_dim)
+    scale = float(qkv.abs().max())
+    assert float((q.float().cpu() - want_q.reshape(batch, -1)).abs().max()) < 2e-2 * scale
+    ek, ev = k_pool.float().clone(), v_pool.float().clone()
+    for b in range(batch):
+        slot = int(slots[b])
+        if slot >= 0:
+            ek[slot // page, :, slot % page, :] = want_k[b]
+            ev[slot // page, :, slot % page, :] = want_v[b]
+    assert float((kd.float().cpu() - ek).abs().max()) < 2e-2 * max(scale, 4.0)
+    assert float((vd.float().cpu() - ev).abs().max()) < 2e-2 * max(scale, 4.0)
+    untouched = torch.ones(pages, dtype=torch.bool)
+    untouched[[int(x) // page for x in slots if x >= 0]] = False
+    assert torch.equal(kd.cpu()[untouched], k_pool[untouched])  # pages of other sequences are left alone
