@@ -61,6 +61,52 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     for (int d = threadIdx.x; d < width; d += blockDim.x) Num<TO>::store(o + d, row_cache[d] * scale * weight[d]);
 }
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                       __uint_as_float(raw.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
+// The same with four elements per thread and step; width a multiple of 4, rows 16-byte aligned.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                        const float* __restrict__ weight, TO* __restrict__ out,
+                                        const int* __restrict__ rows, int width, float eps, int write_x) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    extern __shared__ float row_cache[];
+    __shared__ float scratch[32];
+    const int out_row = blockIdx.x;
+    const int in_row = rows ? rows[out_row] : out_row;
+    float* xr = x + (size_t)in_row * width;
+    const TD* dr = delta ? delta + (size_t)in_row * width : nullptr;
+    float sum_sq = 0.0f;
+    for (int d = threadIdx.x * 4; d < width; d += blockDim.x * 4) {
+        float4 v = load4(xr + d);
+        if (dr) {
+            const float4 e = load4(dr + d);
+            v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+            if (write_x) store4(xr + d, v);
+        }
+        store4(row_cache + d, v);
+        sum_sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    sum_sq = block_sum(sum_sq, scratch);
+    const float rms = sqrtf(sum_sq / (float)width + eps);
+    const float scale = 1.0f / rms;
+    TO* o = out + (size_t)out_row * width;
+    for (int d = threadIdx.x * 4; d < width; d += blockDim.x * 4) {
+        const float4 v = load4(row_cache + d), w = load4(weight + d);
+        store4(o + d, make_float4(v.x * scale * w.x, v.y * scale * w.y, v.z * scale * w.z, v.w * scale * w.w));
+    }
+}
+
 // ------------------------------------------------------------------------------------ rotary + cache
 
 // grid (tokens, heads + 2*kv_heads).  Query heads are rotated in place; key heads are rotated and
@@ -114,6 +160,59 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int row_stride, con
     }
 }
 
+// The common case -- split-half pairs over the whole head, head size a multiple of 16 -- eight
+// elements per thread: grid (tokens), a block walks the (head, eighth-of-a-half) items of its token.
+template <typename T>
+__global__ void rope_cache_write_vec8_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                             const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+                                             T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                             const int* __restrict__ slot_mapping, int heads, int kv_heads, int head_dim,
+                                             int page_size, int write_cache) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int half = head_dim / 2, pieces = half / 8;  // pieces of 8 pairs per head
+    const int pos = positions[t];
+    const float* c = cos_table + (size_t)pos * half;
+    const float* s = sin_table + (size_t)pos * half;
+    const int slot = write_cache ? slot_mapping[t] : -1;
+    const size_t page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot % page_size : 0;
+    T* row = qkv + (size_t)t * row_stride;
+    const int rotated_heads = write_cache ? heads + kv_heads : heads;
+    const int rotate_items = rotated_heads * pieces;
+    const int copy_items = write_cache ? kv_heads * (head_dim / 8) : 0;
+    for (int item = threadIdx.x; item < rotate_items + copy_items; item += blockDim.x) {
+        if (item < rotate_items) {
+            const int h = item / pieces, piece = item % pieces;
+            T* vec = row + (size_t)h * head_dim + piece * 8;
+            float x0[8], x1[8], cs[8], sn[8], r0[8], r1[8];
+            load8(vec, x0);
+            load8(vec + half, x1);
+            load8(c + piece * 8, cs);
+            load8(s + piece * 8, sn);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                r0[i] = x0[i] * cs[i] - x1[i] * sn[i];
+                r1[i] = x0[i] * sn[i] + x1[i] * cs[i];
+            }
+            T* dst = vec;
+            if (h >= heads) {
+                if (slot < 0) continue;
+                dst = k_pool + ((page * kv_heads + (h - heads)) * page_size + offset) * head_dim + piece * 8;
+            }
+            store8(dst, r0);
+            store8(dst + half, r1);
+        } else {
+            if (slot < 0) continue;
+            const int copy = item - rotate_items;
+            const int h = copy / (head_dim / 8), piece = copy % (head_dim / 8);
+            float v[8];
+            load8(row + (size_t)(heads + kv_heads + h) * head_dim + piece * 8, v);
+            store8(v_pool + ((page * kv_heads + h) * page_size + offset) * head_dim + piece * 8, v);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------ gated activation
 
 // gate_up: [rows, 2*width] with the gate in columns [0, width) and up in [width, 2*width).
@@ -128,6 +227,24 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
         const float u = Num<T>::load(gate_up + row * 2 * width + width + col);
         const float silu = g / (1.0f + expf(-g));
         Num<T>::store(out + i, silu * u);
+    }
+}
+
+// Eight elements per thread; width a multiple of 8, rows 16-byte (bf16) or 32-byte (float) aligned.
+template <typename T>
+__global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total8) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const int per_row = width / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += stride) {
+        const size_t row = i / per_row, col = (i % per_row) * 8;
+        float g[8], u[8], r[8];
+        load8(gate_up + row * 2 * width + col, g);
+        load8(gate_up + row * 2 * width + width + col, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+        store8(out + row * width + col, r);
     }
 }
 
@@ -185,6 +302,17 @@ static int launch_add_rmsnorm(float* x, const void* delta, const float* weight, 
         if (status != cudaSuccess) return fail("add_rmsnorm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
     }
     const int block = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+    const bool aligned = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)delta & 7) && !((uintptr_t)weight & 15) &&
+                         !((uintptr_t)out & 7);
+    if (aligned) {
+        auto vec = add_rmsnorm_vec4_kernel<TD, TO>;
+        if (smem > 48 * 1024) {
+            cudaError_t status = cudaFuncSetAttribute(vec, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (status != cudaSuccess) return fail("add_rmsnorm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+        }
+        return launch_dependent("add_rmsnorm", vec, dim3(out_rows), dim3(block), smem, stream, true, x, (const TD*)delta, weight,
+                                (TO*)out, rows, width, eps, write_x);
+    }
     return launch_dependent("add_rmsnorm", kernel, dim3(out_rows), dim3(block), smem, stream, true, x, (const TD*)delta, weight,
                             (TO*)out, rows, width, eps, write_x);
 }
@@ -218,6 +346,23 @@ MB_EXPORT int mb_rope_cache_write(void* qkv, int dtype, int row_stride, const in
         return fail("rope_cache_write: a rotation needs positions and cos/sin tables");
     if (write_cache && (!k_pool || !v_pool || !slot_mapping || page_size <= 0))
         return fail("rope_cache_write: a cache write needs pools, a slot mapping and a page size");
+    const bool wide = !interleaved && rotary_dim == head_dim && head_dim % 16 == 0 && row_stride % 8 == 0 &&
+                      !((uintptr_t)qkv & 31) && !((uintptr_t)k_pool & 31) && !((uintptr_t)v_pool & 31) &&
+                      !((uintptr_t)cos_table & 31) && !((uintptr_t)sin_table & 31);
+    if (wide) {
+        const int items = (heads + kv_heads) * (head_dim / 16) + kv_heads * (head_dim / 8);
+        const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        if (dtype == MB_F32)
+            return launch_dependent("rope_cache_write", rope_cache_write_vec8_kernel<float>, dim3(tokens), dim3(threads), 0, stream,
+                                    true, (float*)qkv, row_stride, positions, cos_table, sin_table, (float*)k_pool, (float*)v_pool,
+                                    slot_mapping, heads, kv_heads, head_dim, page_size, write_cache);
+        if (dtype == MB_BF16)
+            return launch_dependent("rope_cache_write", rope_cache_write_vec8_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0,
+                                    stream, true, (__nv_bfloat16*)qkv, row_stride, positions, cos_table, sin_table,
+                                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slot_mapping, heads, kv_heads, head_dim,
+                                    page_size, write_cache);
+        return fail("rope_cache_write: unknown dtype code %d", dtype);
+    }
     const dim3 grid(tokens, write_cache ? heads + 2 * kv_heads : heads);
     const int block = head_dim >= 128 ? 64 : 32;
     if (dtype == MB_F32)
@@ -235,6 +380,18 @@ MB_EXPORT int mb_rope_cache_write(void* qkv, int dtype, int row_stride, const in
 MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int dtype, int rows, int width, cudaStream_t stream) {
     const size_t total = (size_t)rows * width;
     if (total == 0) return 0;
+    if (width % 8 == 0 && !((uintptr_t)gate_up & 31) && !((uintptr_t)out & 31)) {
+        const size_t total8 = total / 8;
+        const size_t blocks = (total8 + 255) / 256;
+        const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
+        if (dtype == MB_F32)
+            return launch_dependent("swiglu", swiglu_vec8_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)gate_up,
+                                    (float*)out, width, total8);
+        if (dtype == MB_BF16)
+            return launch_dependent("swiglu", swiglu_vec8_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
+                                    (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total8);
+        return fail("swiglu: unknown dtype code %d", dtype);
+    }
     if (dtype == MB_F32)
         swiglu_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, width, total);
     else if (dtype == MB_BF16)

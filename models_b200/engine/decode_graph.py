@@ -19,6 +19,7 @@ from .batch import StepLayout, batch_from_buffer, pack_step
 
 
 def ladder(max_batch: int) -> List[int]:
+    """Powers of two up to max_batch (and max_batch itself): the batch sizes that are captured."""
     sizes, b = [], 1
     while b < max_batch:
         sizes.append(b)
@@ -37,6 +38,8 @@ class _Captured:
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
         # a first layout that is valid to run: every row is padding
         pack_step(cache, [], self.layout, self.host_np, cache.max_slots)
+        offsets = [int(o) for o in self.layout.offsets]
+        self.host_np[offsets[5]:offsets[6]] = np.arange(size, dtype=np.int32)  # every row's logits, row by row
         self.dev.copy_(self.host)
         self.batch = batch_from_buffer(self.dev, self.layout, [1] * size, 1, [])
         stream = torch.cuda.Stream(device=engine.device)
@@ -52,6 +55,52 @@ class _Captured:
             self.logits = engine.model.forward(self.batch, engine.runs)
         self.kernels = ops.launch_count() - before  # this package's kernels inside one replay
         ops.add_launches(-self.kernels)  # a capture launches nothing
+        # views of the pinned buffer, for the quick per-step update
+        off = [int(o) for o in self.layout.offsets]
+        n = self.host_np
+        self.tokens_h, self.positions_h = n[off[0]:off[1]], n[off[1]:off[2]]
+        self.kv_lens_h, self.slots_h = n[off[3]:off[4]], n[off[4]:off[5]]
+        groups = len(cache.groups)
+        self.tables_h = [n[off[6 + 2 * g]:off[7 + 2 * g]].reshape(size, blocks) for g in range(groups)]
+        self.mappings_h = [n[off[7 + 2 * g]:off[8 + 2 * g]] for g in range(groups)]
+        self.row_owner = [(-1, -1)] * size  # (slot, blocks written) of each row of the page tables
+        self.live = 0
+
+    def update(self, cache, slots: Sequence[int], tokens: Sequence[int]) -> None:
+        """The indices of one decode step, written in place: one token per slot, appended at each
+        slot's length.  Page-table rows are rewritten only when a sequence moved in or gained a page."""
+        live, page = len(slots), cache.page_size
+        pad_row = cache.max_slots
+        lengths = [cache.lengths[s] for s in slots]
+        self.tokens_h[:live] = tokens
+        self.positions_h[:live] = lengths
+        self.kv_lens_h[:live] = lengths
+        self.kv_lens_h[:live] += 1
+        self.slots_h[:live] = slots
+        if live < self.live:  # rows that fell out of the batch become padding
+            self.tokens_h[live:self.live] = 0
+            self.positions_h[live:self.live] = 0
+            self.kv_lens_h[live:self.live] = 1
+            self.slots_h[live:self.live] = pad_row
+            for g in range(len(self.tables_h)):
+                self.tables_h[g][live:self.live] = 0
+                self.mappings_h[g][live:self.live] = -1
+            for b in range(live, self.live):
+                self.row_owner[b] = (-1, -1)
+        self.live = live
+        for b, slot in enumerate(slots):
+            length = lengths[b]
+            block, offset = length // page, length % page
+            blocks_held = len(cache.groups[0].tables[slot]) if cache.groups else 0  # the same in every group
+            refresh = self.row_owner[b] != (slot, blocks_held)
+            self.row_owner[b] = (slot, blocks_held)
+            for g, group in enumerate(cache.groups):
+                table = group.tables[slot]
+                self.mappings_h[g][b] = table[block] * page + offset
+                if refresh:  # pages a window group gave back are never read: their stale ids may stay
+                    row = self.tables_h[g][b]
+                    row[:len(table)] = [p if p >= 0 else 0 for p in table]
+                    row[len(table):] = 0
 
 
 class DecodeGraphs:
@@ -77,7 +126,7 @@ class DecodeGraphs:
         captured = self.captured.get(size)
         if captured is None:
             captured = self.captured[size] = _Captured(engine, size, self.blocks, self.pool)
-        pack_step(engine.cache, entries, captured.layout, captured.host_np, engine.cache.max_slots)
+        captured.update(engine.cache, [e[0] for e in entries], [e[1][0] for e in entries])
         captured.dev.copy_(captured.host, non_blocking=True)
         captured.graph.replay()
         ops.add_launches(captured.kernels)

@@ -232,11 +232,15 @@ def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, h
         raise KernelError("the tensor-core attention kernels take bfloat16 q, out and pools")
 
 
-def decode_splits(sequences: int, heads: int, kv_heads: int, max_blocks: int, multiprocessors: int = 148) -> int:
+def decode_splits(sequences: int, heads: int, kv_heads: int, multiprocessors: int = 148) -> int:
     """How many blocks share one sequence's keys: a power of two that fills the GPU about four times
-    over, at most 8 (they form one thread-block cluster), at most one per cache page."""
-    base = sequences * kv_heads * (-(-(heads // kv_heads) // 16))
-    limit = max(1, min(8, max_blocks, (4 * multiprocessors) // max(1, base)))
+    over, at most 8 (they form one thread-block cluster).  It depends on the batch size rounded up
+    to a power of two only, so a batch padded to such a size is split like the unpadded one."""
+    rounded = 1
+    while rounded < sequences:
+        rounded *= 2
+    base = rounded * kv_heads * (-(-(heads // kv_heads) // 16))
+    limit = max(1, min(8, (4 * multiprocessors) // max(1, base)))
     splits = 1
     while splits * 2 <= limit:
         splits *= 2
