@@ -416,6 +416,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
         row_pos[r] = row < valid ? pos0 + row : -1;  // a row beyond the sequence sees nothing
         row_first[r] = (window > 0 && row_pos[r] - window + 1 > 0) ? row_pos[r] - window + 1 : 0;
     }
+    const float scale_log2 = scale * 1.4426950408889634f;
     const int warp_last = min(pos0 + warp * 16 + 15, last_pos);        // highest position among the warp's rows
     const int warp_first_pos = pos0 + warp * 16;                        // lowest
     const int warp_first_key = (window > 0 && warp_first_pos - window + 1 > 0) ? warp_first_pos - window + 1 : 0;
@@ -439,53 +440,60 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
             // every key of the tile is visible to every row of the warp: no mask needed
             const bool full = key_base + kTile - 1 <= warp_first_pos && key_base >= ((window > 0) ? max(0, warp_last - window + 1) : 0)
                               && warp * 16 + 15 < valid;
+            // scores of the whole tile first, so that the running maximum moves once per 64 keys
+            float s[kTile / 8][4];
 #pragma unroll
             for (int part = 0; part < kTile / 16; ++part) {
-                const int key0 = part * 16;
-                const int abs0 = key_base + key0;
-                if (abs0 > warp_last || abs0 + 15 < warp_first_key) continue;  // uniform across the warp
-                float s[2][4];
-                scores_16_keys(s, a, k_tile, key0);
+                float two[2][4];
+                scores_16_keys(two, a, k_tile, part * 16);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int key = abs0 + nt * 8 + tid4 * 2 + (i & 1);
-                        const int r = i >> 1;
-                        const bool visible = full || (key <= row_pos[r] && key >= row_first[r]);
-                        s[nt][i] = visible ? s[nt][i] * scale : -CUDART_INF_F;
-                    }
-                uint32_t p[4];
-                float probs[2][4];
-#pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    const float part_max = quad_max(fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1])));
-                    const float new_max = fmaxf(run_max[r], part_max);
-                    // a row that has seen nothing yet keeps -inf; subtract 0 then so that exp gives 0, not NaN
-                    const float safe_max = new_max == -CUDART_INF_F ? 0.0f : new_max;
-                    const float correction = expf(run_max[r] - safe_max);
-                    run_max[r] = new_max;
-                    float local = 0.0f;
-#pragma unroll
-                    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            const float e = expf(s[nt][2 * r + c] - safe_max);
-                            probs[nt][2 * r + c] = e;
-                            local += e;
-                        }
-                    run_sum[r] = run_sum[r] * correction + local;
-#pragma unroll
-                    for (int i = 0; i < HD / 8; ++i) {
-                        o[i][2 * r] *= correction;
-                        o[i][2 * r + 1] *= correction;
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    s[2 * part][i] = two[0][i];
+                    s[2 * part + 1][i] = two[1][i];
                 }
-                p[0] = pack_bf16(probs[0][0], probs[0][1]);
-                p[1] = pack_bf16(probs[0][2], probs[0][3]);
-                p[2] = pack_bf16(probs[1][0], probs[1][1]);
-                p[3] = pack_bf16(probs[1][2], probs[1][3]);
-                accumulate_16_keys(o, p, v_tile, key0);
+            }
+            float part_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int nt = 0; nt < kTile / 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int key = key_base + nt * 8 + tid4 * 2 + (i & 1);
+                    const int r = i >> 1;
+                    const bool visible = full || (key <= row_pos[r] && key >= row_first[r]);
+                    s[nt][i] = visible ? s[nt][i] * scale_log2 : -CUDART_INF_F;  // in units of log2(e): exp(x) = exp2(x log2 e)
+                    part_max[r] = fmaxf(part_max[r], s[nt][i]);
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float new_max = fmaxf(run_max[r], quad_max(part_max[r]));
+                // a row that has seen nothing yet keeps -inf; subtract 0 then so that exp gives 0, not NaN
+                const float safe_max = new_max == -CUDART_INF_F ? 0.0f : new_max;
+                const float correction = exp2f(run_max[r] - safe_max);
+                run_max[r] = new_max;
+                float local = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < kTile / 8; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const float e = exp2f(s[nt][2 * r + c] - safe_max);
+                        s[nt][2 * r + c] = e;
+                        local += e;
+                    }
+                run_sum[r] = run_sum[r] * correction + local;
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i) {
+                    o[i][2 * r] *= correction;
+                    o[i][2 * r + 1] *= correction;
+                }
+            }
+#pragma unroll
+            for (int part = 0; part < kTile / 16; ++part) {
+                uint32_t p[4];
+                p[0] = pack_bf16(s[2 * part][0], s[2 * part][1]);
+                p[1] = pack_bf16(s[2 * part][2], s[2 * part][3]);
+                p[2] = pack_bf16(s[2 * part + 1][0], s[2 * part + 1][1]);
+                p[3] = pack_bf16(s[2 * part + 1][2], s[2 * part + 1][3]);
+                accumulate_16_keys(o, p, v_tile, part * 16);
             }
         }
         __syncthreads();
@@ -565,7 +573,7 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
         attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attribute[1].val.programmaticStreamSerializationAllowed = 1;
         config.attrs = attribute;
-        config.numAttrs = 2;
+        config.numAttrs = dependent_launches_allowed() ? 2 : 1;
         cudaError_t status = cudaLaunchKernelEx(&config, decode_attention_kernel<true>, (const bf16*)q, q_row_stride, (bf16*)out,
                                                 out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks,
                                                 cu_q, kv_lens, heads, kv_heads, head_chunks, window, scale, splits,

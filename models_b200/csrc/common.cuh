@@ -7,6 +7,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define MB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -120,6 +121,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// MODELS_B200_NO_PDL=1 in the environment turns every programmatic dependent launch into an ordinary
+// one (a switch for debugging launch-order problems).
+inline bool dependent_launches_allowed() {
+    static const bool allowed = getenv("MODELS_B200_NO_PDL") == nullptr;
+    return allowed;
+}
+
 template <typename... KernelArgs, typename... Args>
 inline int launch_dependent(const char* what, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
                             cudaStream_t stream, bool dependent, Args... args) {
@@ -132,7 +140,7 @@ inline int launch_dependent(const char* what, void (*kernel)(KernelArgs...), dim
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = dependent ? 1 : 0;
+    config.numAttrs = (dependent && dependent_launches_allowed()) ? 1 : 0;
     cudaError_t status = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
     if (status != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(status));
     return check_launch(what);

@@ -1,0 +1,387 @@
+// Prefill matrix products on the fifth-generation tensor cores: C[M, N] = A[M, K] . W[N, K]^T with
+// bfloat16 operands and float accumulation, for many activation rows (a whole prompt).
+//
+//   * Operand tiles travel by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a four-stage ring of
+//     shared memory: 128 rows of A and 256 rows of W, 64 columns of K per stage.
+//   * One thread issues tcgen05.mma (M = 128, N = 256, K = 16, operands from shared-memory
+//     descriptors); the accumulator lives in tensor memory, 256 columns, double-buffered, so the
+//     epilogue of one tile overlaps the products of the next.
+//   * Four epilogue warps read the accumulator back with tcgen05.ld and finish the layer's arithmetic
+//     in registers: store as bfloat16 / float, add into the float32 residual stream, or -- when W
+//     holds gate rows and up rows -- silu(gate) * up, so the gated activation never passes through
+//     memory.  (x = x + W.h: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1131-1138,
+//     1172-1178; SwiGLU: backend-java/.../ops/TensorOps.java:1407-1425.)
+//   * Blocks are persistent (one per multiprocessor) and walk the output tiles with the row tile
+//     index running fastest, so neighbouring blocks share a weight tile through L2.
+//
+// Every wait on an mbarrier is bounded: after about two seconds a role gives up, records where in
+// g_gemm_status and leaves its loop; all roles then meet at the final barrier, tensor memory is
+// freed and the kernel returns.  mb_gemm_tc_status() reads the record.
+#include "common.cuh"
+
+#include <cuda.h>
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+using bf16 = __nv_bfloat16;
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+
+constexpr int kBlockM = 128, kBlockN = 256, kBlockK = 64, kStages = 4;
+constexpr int kTileABytes = kBlockM * kBlockK * 2;      // 16 KB
+constexpr int kBoxBBytes = 128 * kBlockK * 2;           // 16 KB, two boxes per stage
+constexpr int kStageBytes = kTileABytes + 2 * kBoxBBytes;
+constexpr int kThreads = 192;                           // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr int kAccumulatorColumns = 256, kTmemColumns = 512;
+constexpr long long kWaitCycles = 4000000000LL;         // about two seconds
+
+__device__ int g_gemm_status = 0;  // 0: fine; else 1 + (role << 8) of the first wait that gave up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait: false (and a record) when the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > kWaitCycles) {
+            atomicCAS(&g_gemm_status, 0, 1 + (role << 8));
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_descriptor(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address
+    desc |= (uint64_t)1 << 16;                        // leading byte offset (unused with this swizzle)
+    desc |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: 8 rows x 128 bytes
+    desc |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    desc |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return desc;
+}
+// bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = 256
+constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstruction), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct GemmArgs {
+    int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
+    int up_row_offset;    // EPI_SWIGLU: first up row of W
+    void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream
+    int ld_out;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmArgs args) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment of the tiles is what the swizzle and the descriptors assume
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t barriers[2 * kStages + 4];
+    __shared__ uint32_t tmem_base_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t full_bar = smem_u32(&barriers[0]), empty_bar = smem_u32(&barriers[kStages]);
+    const uint32_t acc_full_bar = smem_u32(&barriers[2 * kStages]), acc_empty_bar = smem_u32(&barriers[2 * kStages + 2]);
+
+    // columns of output per tile: 256, or 128 gate/up pairs
+    constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : 256;
+    const int m_tiles = (args.m + kBlockM - 1) / kBlockM;
+    const int n_tiles = (args.n + kOutCols - 1) / kOutCols;
+    const int tiles = m_tiles * n_tiles;
+    const int k_blocks = (args.k + kBlockK - 1) / kBlockK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full_bar + 8 * a, 1);
+            mbar_init(acc_empty_bar + 8 * a, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // one warp allocates all 512 columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    grid_launch_dependents();
+    grid_dependency_wait();  // the activations come from the kernel before this one
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 1;  // the first pass over the ring finds every stage free
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * kBlockM, n_tile = tile / m_tiles;
+                const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * 256;
+                const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * 256 + 128;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
+                    const uint32_t dst = smem_u32(smem) + stage * kStageBytes;
+                    mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
+                    tma_load_2d(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
+                    tma_load_2d(dst + kTileABytes, &map_w, kb * kBlockK, w_row0, full_bar + 8 * stage);
+                    tma_load_2d(dst + kTileABytes + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * stage);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 1;  // both accumulators start free
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                if (!(ok = mbar_wait(acc_empty_bar + 8 * acc, acc_phase, 2))) break;
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * kAccumulatorColumns;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!(ok = mbar_wait(full_bar + 8 * stage, phase, 3))) break;
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(smem) + stage * kStageBytes;
+                    const uint64_t a_desc = umma_descriptor(a_addr), b_desc = umma_descriptor(a_addr + kTileABytes);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockK / 16; ++ks)  // 32 bytes further along K per step: +2 in the address field
+                        umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, (kb > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(empty_bar + 8 * stage);  // the stage is free once these products have read it
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                umma_commit(acc_full_bar + 8 * acc);  // the accumulator is complete once all products are
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: 4 warps, one TMEM lane quarter each
+        const int quarter = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile % m_tiles) * kBlockM, n_tile = tile / m_tiles;
+            ok = mbar_wait(acc_full_bar + 8 * acc, acc_phase, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * kAccumulatorColumns + ((uint32_t)(quarter * 32) << 16);
+            const int n0 = n_tile * kOutCols;
+#pragma unroll 1
+            for (int c = 0; c < kOutCols; c += 32) {
+                float v[32];
+                tmem_load_32(taddr + c, v);
+                if (EPI == EPI_SWIGLU) {
+                    float u[32];
+                    tmem_load_32(taddr + 128 + c, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                }
+                if (row < args.m) {
+                    const int col = n0 + c;
+                    if (EPI == EPI_BF16 || EPI == EPI_SWIGLU) {
+                        bf16* dst = reinterpret_cast<bf16*>(args.out) + (size_t)row * args.ld_out + col;
+                        if (col + 32 <= args.n) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                float piece[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) piece[j] = v[i + j];
+                                store8(dst + i, piece);
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col + i < args.n; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+                        }
+                    } else {
+                        float* dst = reinterpret_cast<float*>(args.out) + (size_t)row * args.ld_out + col;
+                        if (col + 32 <= args.n) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                if (EPI == EPI_RESIDUAL) {
+                                    const float4 x = *reinterpret_cast<const float4*>(dst + i);
+                                    o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + i) = o;
+                            }
+                        } else {
+                            for (int i = 0; i < 32 && col + i < args.n; ++i) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    // every role has left its loop (done, or after a bounded wait gave up): free tensor memory
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)entry;
+    }
+    return fn;
+}
+
+// A row-major bfloat16 matrix [rows, k] (row stride ld elements) as a TMA map with boxes of 128 rows x 64 columns.
+static int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return fail("gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, 128};
+    const cuuint32_t element_strides[2] = {1, 1};
+    CUresult status = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) return fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)status);
+    return 0;
+}
+
+template <int EPI>
+static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, cudaStream_t stream) {
+    constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : 256;
+    const size_t smem = (size_t)kStages * kStageBytes + 1024;
+    auto kernel = gemm_tcgen05_kernel<EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
+        configured = true;
+    }
+    const int tiles = ((args.m + kBlockM - 1) / kBlockM) * ((args.n + kOutCols - 1) / kOutCols);
+    const int grid = tiles < multiprocessors ? tiles : multiprocessors;
+    return launch_dependent("gemm_tcgen05", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_a, map_w, args);
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+// a: bfloat16 [m, k] (row stride lda); w: bfloat16 [n_w, k] (row stride ldw).
+// epilogue 0: out bfloat16 [m, n_w]; 1: out float32 [m, n_w]; 2: out float32 [m, n_w] += ; 3: w holds gate
+// rows [0, n_w/2) and up rows [n_w/2, n_w): out bfloat16 [m, n_w/2] = silu(gate) * up.
+MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ld_out, int m, int n_w, int k,
+                              int epilogue, int multiprocessors, cudaStream_t stream) {
+    if (m <= 0 || n_w <= 0) return 0;
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8) return fail("gemm_tcgen05: k (%d) and the row strides (%d, %d) must be multiples of 8", k, lda, ldw);
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return fail("gemm_tcgen05: operands must start on 16-byte boundaries");
+    if (epilogue == EPI_SWIGLU && n_w % 2) return fail("gemm_tcgen05: the gated epilogue needs an even number of weight rows, got %d", n_w);
+    const int n = epilogue == EPI_SWIGLU ? n_w / 2 : n_w;
+    const bool wide_out = epilogue == EPI_F32 || epilogue == EPI_RESIDUAL;
+    if (((uintptr_t)out & 15) || ld_out % (wide_out ? 4 : 8)) return fail("gemm_tcgen05: output rows must start on 16-byte boundaries");
+    CUtensorMap map_a, map_w;
+    if (int status = make_map(&map_a, a, m, k, lda)) return status;
+    if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
+    GemmArgs args{m, n, k, n, out, ld_out};
+    switch (epilogue) {
+        case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, stream);
+        case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, stream);
+        case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(map_a, map_w, args, multiprocessors, stream);
+        case EPI_SWIGLU: return launch<EPI_SWIGLU>(map_a, map_w, args, multiprocessors, stream);
+    }
+    return fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+}
+
+// 0 when no wait ever gave up; else 1 + (role << 8): 1 producer, 2 MMA (accumulator), 3 MMA (operands), 4 epilogue.
+MB_EXPORT int mb_gemm_tc_status() {
+    int status = 0;
+    if (cudaMemcpyFromSymbol(&status, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    return status;
+}

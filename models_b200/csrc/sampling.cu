@@ -403,7 +403,7 @@ MB_EXPORT int mb_argmax_rows(const float* logits, int row_stride, int rows, int 
     attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = 2;
+    config.numAttrs = dependent_launches_allowed() ? 2 : 1;
     cudaError_t status = cudaLaunchKernelEx(&config, argmax_rows_kernel, logits, row_stride, vocab, out);
     if (status != cudaSuccess) return fail("argmax_rows: launch failed: %s", cudaGetErrorString(status));
     return check_launch("argmax_rows");

@@ -386,7 +386,7 @@ static int launch(const SkinnyArgs& args, cudaStream_t stream) {
     attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = args.dependent ? 2 : 1;
+    config.numAttrs = (args.dependent && dependent_launches_allowed()) ? 2 : 1;
     cudaError_t status = cudaLaunchKernelEx(&config, kernel, args);
     if (status != cudaSuccess) return fail("skinny_gemm: launch failed: %s", cudaGetErrorString(status));
     return check_launch("skinny_gemm");

@@ -33,7 +33,7 @@ class _Captured:
         self.size = size
         cache = engine.cache
         self.layout = StepLayout(size, size, size, blocks, len(cache.groups))
-        self.host = torch.zeros(self.layout.total, dtype=torch.int32).pin_memory()
+        self.host = torch.zeros(self.layout.total, dtype=torch.int32)  # the step's indices, kept up to date in place
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
         # a first layout that is valid to run: every row is padding
@@ -65,6 +65,18 @@ class _Captured:
         self.mappings_h = [n[off[7 + 2 * g]:off[8 + 2 * g]] for g in range(groups)]
         self.row_owner = [(-1, -1)] * size  # (slot, blocks written) of each row of the page tables
         self.live = 0
+        self.staging = [(torch.zeros_like(self.host).pin_memory(), torch.cuda.Event()) for _ in range(4)]
+        self.staging_next = 0
+
+    def upload(self) -> None:
+        """Copies the indices to the device through a small ring of pinned buffers: the copy is
+        asynchronous, so the buffer it reads must not be rewritten before it has run."""
+        staging, event = self.staging[self.staging_next]
+        self.staging_next = (self.staging_next + 1) % len(self.staging)
+        event.synchronize()  # returns at once unless the host is several steps ahead of the GPU
+        staging.copy_(self.host)
+        self.dev.copy_(staging, non_blocking=True)
+        event.record()
 
     def update(self, cache, slots: Sequence[int], tokens: Sequence[int]) -> None:
         """The indices of one decode step, written in place: one token per slot, appended at each
@@ -127,7 +139,7 @@ class DecodeGraphs:
         if captured is None:
             captured = self.captured[size] = _Captured(engine, size, self.blocks, self.pool)
         captured.update(engine.cache, [e[0] for e in entries], [e[1][0] for e in entries])
-        captured.dev.copy_(captured.host, non_blocking=True)
+        captured.upload()
         captured.graph.replay()
         ops.add_launches(captured.kernels)
         return captured.logits[: len(entries)]

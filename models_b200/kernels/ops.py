@@ -388,6 +388,51 @@ def skinny_qkv_rope(weight: torch.Tensor, xf: torch.Tensor, gain: torch.Tensor, 
     return q
 
 
+def gemm_tc():
+    return load_library("mb_gemm_tcgen05", ["gemm_tcgen05.cu"])
+
+
+TCGEN05_MIN_ROWS = 128  # one row tile of the kernel; fewer rows leave most of it empty
+
+
+def gemm_tcgen05_takes(weight: torch.Tensor, epilogue: int = EPI_BF16, rows: Optional[int] = None) -> bool:
+    """Whether the tcgen05 matrix product takes this weight (and, if given, pays off for so many rows)."""
+    n = weight.shape[0] // 2 if epilogue == EPI_SWIGLU else weight.shape[0]
+    if rows is not None and rows < TCGEN05_MIN_ROWS:
+        return False
+    return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.stride(1) == 1 and weight.shape[1] % 8 == 0
+            and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0 and n % 8 == 0
+            and (epilogue != EPI_SWIGLU or weight.shape[0] % 2 == 0))
+
+
+def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [m, k] . weight[n, k]^T on the tcgen05 tensor cores (bfloat16 in, float accumulation).
+    Epilogues as for skinny_gemm: EPI_BF16 / EPI_F32 store, EPI_RESIDUAL adds into `out` (float32
+    [m, n]), EPI_SWIGLU stores silu(gate) * up for weight = [gate rows; up rows]."""
+    _cuda(a, weight, out)
+    if a.dtype != torch.bfloat16 or a.dim() != 2 or a.stride(1) != 1 or a.shape[1] != weight.shape[1]:
+        raise KernelError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit the weight {tuple(weight.shape)}")
+    if not gemm_tcgen05_takes(weight, epilogue) or a.stride(0) % 8 or a.data_ptr() % 16:
+        raise KernelError(f"gemm_tcgen05 does not take a {tuple(weight.shape)} {weight.dtype} weight")
+    m, k = a.shape
+    n_w = weight.shape[0]
+    n = n_w // 2 if epilogue == EPI_SWIGLU else n_w
+    if epilogue == EPI_RESIDUAL:
+        if out is None or out.dtype != torch.float32 or out.shape != (m, n) or out.stride(1) != 1:
+            raise KernelError("the residual epilogue adds into a float32 [m, n] tensor")
+    elif out is None:
+        out = torch.empty((m, n), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=a.device)
+    lib = gemm_tc()
+    _run(lib, lib.mb_gemm_tcgen05(_p(a), a.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), m, n_w, k,
+                                  epilogue, _sm_count(a.device), _stream()))
+    return out
+
+
+def gemm_tcgen05_status() -> int:
+    """0 unless a bounded wait inside the kernel ever gave up (then it names the role)."""
+    return int(gemm_tc().mb_gemm_tc_status())
+
+
 # ------------------------------------------------------------------------------------ sampling
 
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:

@@ -94,6 +94,20 @@ class AttentionMixer(Mixer):
             attended = self._rotate_store_attend(qkv, batch, run)
         ops.skinny_gemm(self.w_o, ops.EPI_RESIDUAL, x=attended, out=x)
 
+    def adds(self, xn: torch.Tensor) -> bool:
+        """Whether `forward_into` applies (any number of rows): a bfloat16 output matrix the tcgen05
+        kernel takes, no output bias."""
+        return self.b_o is None and xn.dtype == torch.bfloat16 and ops.gemm_tcgen05_takes(self.w_o, rows=xn.shape[0])
+
+    def forward_into(self, x: torch.Tensor, xn: torch.Tensor, batch, run: RunContext) -> None:
+        """x += Wo . attention(...): the residual add rides in the output product."""
+        writes = run.writes_cache
+        qkv = linear(xn, self.w_qkv if writes else self.w_q, self.runtime.compute_dtype)
+        if self.b_qkv is not None:
+            ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
+        attended = self._rotate_store_attend(qkv, batch, run)
+        ops.gemm_tcgen05(attended, self.w_o, ops.EPI_RESIDUAL, out=x)
+
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
         writes = run.writes_cache

@@ -47,8 +47,17 @@ class PreNormBlock(Part):
             self.feed_forward.forward_residual(x, self.feed_forward_norm)
             return None
         xn = self.mixer_norm.forward(x, pending)
-        mixed = self.mixer.forward(xn, batch, run)
+        mixer_adds = getattr(self.mixer, "adds", None)
+        if mixer_adds and mixer_adds(xn):
+            self.mixer.forward_into(x, xn, batch, run)  # the residual add rides in the mixer's last product
+            mixed = None
+        else:
+            mixed = self.mixer.forward(xn, batch, run)
         xn = self.feed_forward_norm.forward(x, mixed)
+        ffn_adds = getattr(self.feed_forward, "adds", None)
+        if ffn_adds and ffn_adds(xn):
+            self.feed_forward.forward_into(x, xn)
+            return None
         return self.feed_forward.forward(xn)
 
 

@@ -60,6 +60,19 @@ class GatedFeedForward(Part):
         hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, xf=x, gain=norm.weight, eps=norm.spec.eps)
         ops.skinny_gemm(self.w_down, ops.EPI_RESIDUAL, x=hidden, out=x)
 
+    def adds(self, xn: torch.Tensor) -> bool:
+        """Whether `forward_into` applies (any number of rows): bfloat16 weights the tensor-core kernels
+        take, no biases."""
+        return (self.b_gate_up is None and self.b_down is None and xn.dtype == torch.bfloat16
+                and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, xn.shape[0])
+                and ops.gemm_tcgen05_takes(self.w_down, rows=xn.shape[0]))
+
+    def forward_into(self, x: torch.Tensor, xn: torch.Tensor) -> None:
+        """x += down(silu(gate(xn)) * up(xn)): the activation rides in the gate/up product, the residual
+        add in the down product; neither the gate/up matrix nor the down result passes through memory."""
+        hidden = ops.gemm_tcgen05(xn, self.w_gate_up, ops.EPI_SWIGLU)
+        ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
         if self.b_gate_up is None and ops.skinny_takes(self.w_gate_up, xn.shape[0]) and xn.dtype == torch.bfloat16:
@@ -68,10 +81,15 @@ class GatedFeedForward(Part):
             if self.b_down is not None:
                 ops.bias_add(delta, self.b_down)
             return delta
-        gate_up = linear(xn, self.w_gate_up, dtype)
-        if self.b_gate_up is not None:
-            ops.bias_add(gate_up, self.b_gate_up)
-        delta = linear(ops.swiglu(gate_up), self.w_down, dtype)
+        if (self.b_gate_up is None and xn.dtype == torch.bfloat16
+                and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, xn.shape[0])):
+            hidden = ops.gemm_tcgen05(xn, self.w_gate_up, ops.EPI_SWIGLU)
+        else:
+            gate_up = linear(xn, self.w_gate_up, dtype)
+            if self.b_gate_up is not None:
+                ops.bias_add(gate_up, self.b_gate_up)
+            hidden = ops.swiglu(gate_up)
+        delta = linear(hidden, self.w_down, dtype)
         if self.b_down is not None:
             ops.bias_add(delta, self.b_down)
         return delta

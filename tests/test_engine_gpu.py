@@ -31,10 +31,11 @@ def folders(tmp_path_factory):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_whole_prompt_every_position(cuda_device, folders, name, dtype):
+    # 1 and 7 tokens take the decode kernels, 70 the library product, 128 and more the tcgen05 product
     from models_b200.engine import StepEntry
 
     engine = _engine(folders[name], dtype)
-    for n, seed in ((1, 1), (7, 2), (70, 3)):
+    for n, seed in ((1, 1), (7, 2), (70, 3), ({"A": 128, "B": 200, "C": 300}[name], 4)):
         tokens = random_tokens(TINY[name]["vocab_size"], n, seed)
         slot = engine.open_slot()
         logits = engine.step([StepEntry(slot, tokens, list(range(n)))])

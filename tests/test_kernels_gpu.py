@@ -418,3 +418,36 @@ def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads
     untouched = torch.ones(pages, dtype=torch.bool)
     untouched[[int(x) // page for x in slots if x >= 0]] = False
     assert torch.equal(kd.cpu()[untouched], k_pool[untouched])  # pages of other sequences are left alone
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (70, 144, 136), (300, 272, 200), (1, 512, 2048), (513, 1040, 328)])
+def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
+    """The prefill matrix product (TMA, tcgen05.mma, accumulator in tensor memory) against float64,
+    at sizes that do not fill its 128 x 256 x 64 tiles; no bounded wait may have given up."""
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    exact = a.double() @ w.double().t()
+    scale = float(exact.abs().max())
+    out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_F32)
+    assert float((out.double().cpu() - exact).abs().max()) < 2e-5 * scale * math.sqrt(k)
+    out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_BF16)
+    assert out.dtype == torch.bfloat16 and float((out.double().cpu() - exact).abs().max()) < 1e-2 * scale
+    residual = torch.randn(m, n, generator=g)
+    rd = residual.cuda()
+    ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_RESIDUAL, out=rd)
+    assert float((rd.double().cpu() - (residual.double() + exact)).abs().max()) < 2e-5 * (scale + 4) * math.sqrt(k)
+    gated = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_SWIGLU)
+    want = plain_llama.swiglu(exact[:, : n // 2], exact[:, n // 2:])
+    assert gated.shape == (m, n // 2)
+    assert float((gated.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+    # a strided view of wider activations is taken as it is
+    wide = torch.randn(m, k + 24, generator=g).bfloat16().cuda()
+    out = ops.gemm_tcgen05(wide[:, 8:8 + k], w.cuda(), ops.EPI_F32)
+    want = wide[:, 8:8 + k].double().cpu() @ w.double().t()
+    assert float((out.double().cpu() - want).abs().max()) < 2e-5 * float(want.abs().max()) * math.sqrt(k)
+    assert ops.gemm_tcgen05_status() == 0
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05(a.cuda(), torch.zeros(n + 4, k, dtype=torch.bfloat16, device="cuda"), ops.EPI_BF16)
