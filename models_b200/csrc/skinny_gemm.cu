@@ -51,8 +51,16 @@ enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE = 4
 
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-constexpr int kDepth = 4;   // stages of the weight ring
-constexpr int kStep = 64;   // columns per stage
+#ifndef MB_SKINNY_DEPTH
+#define MB_SKINNY_DEPTH 4
+#endif
+#ifndef MB_SKINNY_STEP
+#define MB_SKINNY_STEP 128
+#endif
+constexpr int kDepth = MB_SKINNY_DEPTH;  // stages of the weight ring
+constexpr int kStep = MB_SKINNY_STEP;    // columns per stage: 32 per piece, a lane takes 8 of each piece
+constexpr int kPieces = kStep / 32;
+static_assert(kStep % 32 == 0 && kPieces >= 1 && kDepth >= 2, "a stage is a whole number of 32-column pieces");
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -97,8 +105,8 @@ struct SkinnyArgs {
     int ld_out;
     int pair_offset;      // EPI_SWIGLU: the up tile starts pair_offset rows after the gate tile
     int k_split;          // blocks of a cluster that share K
-    int k_unit;           // columns per block, a multiple of 256
-    int k_warp;           // columns per warp, a multiple of 64
+    int k_unit;           // columns per block, a multiple of 4 * kStep
+    int k_warp;           // columns per warp, a multiple of kStep
     int clusters;         // clusters (of k_split blocks) in the grid; each walks row tiles cluster, cluster + clusters, ...
     int dependent;        // launch as a programmatic dependent of the kernel before it
     // EPI_ROPE
@@ -113,12 +121,12 @@ struct SkinnyArgs {
 
 // Shared memory of a block, in bytes from the start:
 //   activations  [NT*8 rows][k_unit*2 + 64]          (row stride = 64 mod 128 keeps 8-lane phases conflict-free)
-//   ring         [4 warps][kDepth][2 halves][2 pieces][32 lanes][16]
+//   ring         [4 warps][kDepth][2 halves][kPieces][32 lanes][16]
 //   partial      [2 buffers][4 warps][16][NT*8] floats, then sums of squares [NT*8], [4][NT*8]
 template <int NT, int EPI>
 struct SmemPlan {
     static constexpr int COLS = NT * 8;
-    static constexpr int kStageBytes = 4 * 32 * 16;
+    static constexpr int kStageBytes = 2 * kPieces * 32 * 16;
     static constexpr int kPartialFloats = kWarps * 16 * COLS;
     static __host__ __device__ int x_stride(int k_unit) { return k_unit * 2 + 64; }
     static __host__ __device__ int ring_offset(int k_unit) { return COLS * x_stride(k_unit); }
@@ -172,9 +180,9 @@ skinny_gemm_kernel(const SkinnyArgs args) {
             }
             const bf16* w_row = args.w + (size_t)row * args.ldw;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < kPieces; ++c) {
                 const int kk = kc + 32 * c;
-                const uint32_t dst = stage + ((h * 2 + c) * 32 + lane) * 16;
+                const uint32_t dst = stage + ((h * kPieces + c) * 32 + lane) * 16;
                 if (kk < k_end) cp_async16(dst, w_row + kk);
                 else sts128_zero(dst);
             }
@@ -266,15 +274,15 @@ skinny_gemm_kernel(const SkinnyArgs args) {
             cp_async_commit();
             cp_async_wait<kDepth - 1>();  // this lane's pieces of the stage have landed; nobody else reads them
             const uint32_t stage = ring + (stage_index % kDepth) * Plan::kStageBytes;
-            uint4 wv[2][2];
+            uint4 wv[2][kPieces];
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int c = 0; c < 2; ++c) wv[h][c] = lds128(stage + ((h * 2 + c) * 32 + lane) * 16);
+                for (int c = 0; c < kPieces; ++c) wv[h][c] = lds128(stage + ((h * kPieces + c) * 32 + lane) * 16);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < kPieces; ++c) {
                     const uint4 xv = lds128(x_lane + nt * 8 * x_stride + (step * kStep + 32 * c) * 2);
                     mma_bf16(acc[nt], wv[0][c].x, wv[1][c].x, wv[0][c].y, wv[1][c].y, xv.x, xv.y);
                     mma_bf16(acc[nt], wv[0][c].z, wv[1][c].z, wv[0][c].w, wv[1][c].w, xv.z, xv.w);
@@ -437,8 +445,8 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     const int tiles = (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE) ? (rows_total + 7) / 8 : (rows_total + 15) / 16;
     const int cols = batch <= 8 ? 8 : (batch <= 16 ? 16 : 32);
     auto smem_for = [&](int split) {
-        const int k_unit = ((k + split - 1) / split + 255) / 256 * 256;
-        return (size_t)cols * (k_unit * 2 + 64) + (size_t)kWarps * kDepth * 2048 +
+        const int k_unit = ((k + split - 1) / split + kWarps * kStep - 1) / (kWarps * kStep) * (kWarps * kStep);
+        return (size_t)cols * (k_unit * 2 + 64) + (size_t)kWarps * kDepth * (2 * kPieces * 512) +
                (size_t)(2 * kWarps * 16 * cols + (1 + kWarps) * cols) * sizeof(float);
     };
     auto resident_for = [&](int split) {
@@ -451,7 +459,7 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     if (smem_for(split) > 200 * 1024)
         return fail("skinny_gemm: %d activation rows of %d columns do not fit shared memory", batch, k);
     args.k_split = split;
-    args.k_unit = ((k + split - 1) / split + 255) / 256 * 256;
+    args.k_unit = ((k + split - 1) / split + kWarps * kStep - 1) / (kWarps * kStep) * (kWarps * kStep);
     args.k_warp = args.k_unit / kWarps;
     const int resident_clusters = resident_for(split) / split;
     args.clusters = tiles < resident_clusters ? tiles : resident_clusters;

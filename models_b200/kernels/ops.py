@@ -7,6 +7,7 @@ library that cannot be built, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -303,7 +304,13 @@ EPI_BF16, EPI_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 
 
 def skinny():
-    return load_library("mb_skinny_gemm", ["skinny_gemm.cu"])
+    return load_library("mb_skinny_gemm", ["skinny_gemm.cu"], _skinny_defines)
+
+
+# tuning knob for experiments: MODELS_B200_SKINNY="DEPTH=6,STEP=128" rebuilds the decode product with
+# another ring depth / stage width
+_skinny_defines = {"MB_SKINNY_" + k: int(v) for k, v in
+                   (item.split("=") for item in os.environ.get("MODELS_B200_SKINNY", "").split(",") if item)}
 
 
 def skinny_takes(weight: torch.Tensor, rows: int, with_norm: bool = False) -> bool:
