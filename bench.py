@@ -161,7 +161,7 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False):
     logits = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
     tokens = ops.argmax_rows(logits).tolist()
     for _ in range(warmup):
-        tokens = ops.argmax_rows(engine.decode(slots, tokens)).tolist()
+        tokens = engine.greedy_tokens(engine.decode(slots, tokens)).tolist()
     sampler = ClockSampler() if sample_clocks else None
     if sampler:
         sampler.start()
@@ -172,7 +172,7 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False):
     start.record()
     for _ in range(steps):
         kv_total += sum(engine.length(s) + 1 for s in slots)
-        tokens = ops.argmax_rows(engine.decode(slots, tokens)).tolist()
+        tokens = engine.greedy_tokens(engine.decode(slots, tokens)).tolist()
     end.record()
     torch.cuda.synchronize()
     seconds = start.elapsed_time(end) / 1e3

@@ -46,13 +46,14 @@ class _Captured:
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             for _ in range(2):  # warm-up outside the capture: libraries load, attributes are set
-                engine.model.forward(self.batch, engine.runs)
+                ops.argmax_rows(engine.model.forward(self.batch, engine.runs))
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize(engine.device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(self.graph, pool=pool, stream=stream):
             self.logits = engine.model.forward(self.batch, engine.runs)
+            self.argmax = ops.argmax_rows(self.logits)  # greedy choice of every row, for callers that want only that
         self.kernels = ops.launch_count() - before  # this package's kernels inside one replay
         ops.add_launches(-self.kernels)  # a capture launches nothing
         # views of the pinned buffer, for the quick per-step update
@@ -122,6 +123,7 @@ class DecodeGraphs:
         self.blocks = blocks
         self.sizes = ladder(max_batch)
         self.captured: Dict[int, _Captured] = {}
+        self.last_argmax = None  # first maximum of every row of the last step's logits (device, int32)
         self.pool = torch.cuda.graph_pool_handle()
 
     def rung(self, n: int) -> int:
@@ -142,4 +144,5 @@ class DecodeGraphs:
         captured.upload()
         captured.graph.replay()
         ops.add_launches(captured.kernels)
+        self.last_argmax = captured.argmax[: len(entries)]
         return captured.logits[: len(entries)]

@@ -76,6 +76,8 @@ class Engine:
             self.runs.append(ctx)
         self.steps = 0
         self.decode_graphs = None
+        self.last_argmax = None
+        self._last_logits = None
 
     def enable_decode_graphs(self, max_batch: int, max_sequence: Optional[int] = None) -> None:
         """Captures decode steps of up to `max_batch` sequences of up to `max_sequence` positions
@@ -152,6 +154,7 @@ class Engine:
         graphs are enabled and the batch fits them.  The result is overwritten by the next decode."""
         entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
         graphs = self.decode_graphs
+        self.last_argmax = None
         if graphs is None or len(entries) > graphs.max_batch:
             return self.step(entries)
         self.validate(entries)
@@ -160,9 +163,20 @@ class Engine:
         appends = [(e.slot, 1) for e in entries]
         self.cache.append(appends)
         logits = graphs.step([(e.slot, e.tokens, e.want) for e in entries])
+        self.last_argmax = graphs.last_argmax  # the graph holds the greedy choice too
+        self._last_logits = logits
         self.cache.commit(appends)
         self.steps += 1
         return logits
+
+    def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
+        """First maximum of every row of `logits` (device, int32): taken from the decode graph when
+        `logits` is what the last `decode` returned, else computed."""
+        from ..kernels import ops
+
+        if self.last_argmax is not None and logits is self._last_logits:
+            return self.last_argmax
+        return ops.argmax_rows(logits)
 
     # ------------------------------------------------------------------ facts
 

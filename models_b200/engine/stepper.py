@@ -36,4 +36,4 @@ class EngineStepper:
         return self.engine.decode(slots, tokens)
 
     def sample(self, logits: torch.Tensor, requests: Sequence[RequestSampling]) -> List[int]:
-        return self.sampler.sample(logits, requests).tolist()
+        return self.sampler.sample(logits, requests, self.engine.greedy_tokens).tolist()

@@ -45,15 +45,16 @@ class BatchSampler:
                 f"{self._max_sorted} of them: use top_k <= {self._max_sorted}, or top_p = 1 (got top_k "
                 f"{options.top_k}, top_p {options.top_p})")
 
-    def sample(self, logits: torch.Tensor, requests: Sequence[RequestSampling]) -> torch.Tensor:
+    def sample(self, logits: torch.Tensor, requests: Sequence[RequestSampling], greedy=None) -> torch.Tensor:
         """logits: float32 [len(requests), vocab] on the device.  Returns int32 token ids on the
-        device, one per request, and advances the draw counters."""
+        device, one per request, and advances the draw counters.  `greedy(logits)`, if given,
+        supplies the argmax of every row (the decode graph computes it along with the logits)."""
         rows = len(requests)
         if logits.shape[0] < rows or logits.shape[1] != self.vocab:
             raise ValueError(f"logits {tuple(logits.shape)} do not fit {rows} requests of vocabulary {self.vocab}")
-        logits = logits[:rows]
         if all(r.options.greedy for r in requests):
-            return ops.argmax_rows(logits)
+            return greedy(logits)[:rows] if greedy is not None else ops.argmax_rows(logits[:rows])
+        logits = logits[:rows]
         temperature = torch.tensor([r.options.temperature for r in requests], dtype=torch.float32)
         top_k = torch.tensor([min(r.options.top_k, self.vocab) for r in requests], dtype=torch.int32)
         top_p = torch.tensor([r.options.top_p for r in requests], dtype=torch.float32)
