@@ -57,6 +57,10 @@ constexpr int kThreads = kWarps * 32;
 #ifndef MB_SKINNY_STEP
 #define MB_SKINNY_STEP 128
 #endif
+#ifndef MB_SKINNY_RESIDENT
+#define MB_SKINNY_RESIDENT 4
+#endif
+constexpr int kMaxResident = MB_SKINNY_RESIDENT;  // most blocks per multiprocessor the planner counts on
 constexpr int kDepth = MB_SKINNY_DEPTH;  // stages of the weight ring
 constexpr int kStep = MB_SKINNY_STEP;    // columns per stage: 32 per piece, a lane takes 8 of each piece
 constexpr int kPieces = kStep / 32;
@@ -451,7 +455,7 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     };
     auto resident_for = [&](int split) {
         const size_t per_sm = 220 * 1024 / smem_for(split);
-        return multiprocessors * (int)(per_sm > 4 ? 4 : per_sm);
+        return multiprocessors * (int)(per_sm > kMaxResident ? kMaxResident : per_sm);
     };
     int split = 1;
     while (split < 8 && smem_for(split) > 200 * 1024) split *= 2;
