@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from tiny import TINY, TOLERANCE, make_folder, plain_logits, random_tokens, scaled_error
+from tiny import MID, TINY, TOLERANCE, make_folder, plain_logits, random_tokens, scaled_error
 
 pytestmark = pytest.mark.gpu
 
@@ -133,3 +133,48 @@ def test_trace_run_program(cuda_device, folders, dtype, tmp_path):
         assert scaled_error(got[0], ea[30 + i]) < TOLERANCE[dtype], i
         if i < 4:
             assert scaled_error(got[1], eb[5 + i]) < TOLERANCE[dtype], i
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_mid_size_models_all_ways(cuda_device, tmp_path, name, dtype):
+    """At sizes where the tensor-core kernels run their real tilings: a whole prompt of 300 (tcgen05
+    products, tiled prefill attention), the same prompt cut at 200 with the rest one by one (decode
+    products with K split over clusters, cluster-combined attention), and an unequal batch."""
+    from models_b200.engine import StepEntry
+    from models_b200.kernels import ops
+
+    raw = MID[name]
+    folder = make_folder(raw, seed=31, tmp_path=tmp_path, std=0.03)
+    engine = _engine(folder, dtype, max_tokens=2048)
+    vocab = raw["vocab_size"]
+    a, b, c = random_tokens(vocab, 300, 1), random_tokens(vocab, 140, 2), random_tokens(vocab, 17, 3)
+    ea, eb, ec = (plain_logits(folder, t) for t in (a, b, c))
+    tol = TOLERANCE[dtype]
+    slot = engine.open_slot()
+    out = engine.step([StepEntry(slot, a, [0, 63, 64, 150, 299])])
+    for row, place in enumerate([0, 63, 64, 150, 299]):
+        assert scaled_error(out[row], ea[place]) < tol, ("whole", place)
+    engine.release_slot(slot)
+    slot = engine.open_slot()
+    out = engine.step([StepEntry(slot, a[:200], [199])])
+    assert scaled_error(out[0], ea[199]) < tol
+    for i in range(200, 232):
+        out = engine.step([StepEntry(slot, [a[i]], [0])])
+        assert scaled_error(out[0], ea[i]) < tol, ("one by one", i)
+    engine.release_slot(slot)
+    slots = [engine.open_slot() for _ in range(3)]
+    out = engine.step([StepEntry(slots[0], a[:130], [129]), StepEntry(slots[1], b[:129], [0, 128]), StepEntry(slots[2], c[:5], [4])])
+    for row, (expected, place) in enumerate(((ea, 129), (eb, 0), (eb, 128), (ec, 4))):
+        assert scaled_error(out[row], expected[place]) < tol, ("batch prefill", row)
+    for i in range(11):
+        live = [(slots[0], a, 130), (slots[1], b, 129)] + ([(slots[2], c, 5)] if i < 9 else [])
+        out = engine.decode([s for s, _, _ in live], [t[p + i] for _, t, p in live])
+        for row, (_, t, p) in enumerate(live):
+            expected = {id(a): ea, id(b): eb, id(c): ec}[id(t)]
+            assert scaled_error(out[row], expected[p + i]) < tol, ("batch decode", i, row)
+        if i == 8:
+            engine.release_slot(slots[2])
+    if dtype == "bfloat16":
+        assert ops.gemm_tcgen05_status() == 0
+    engine.cache.check()

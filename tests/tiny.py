@@ -81,7 +81,48 @@ TINY_C = {
     "hidden_act": "silu",
 }
 
+# Not tiny in shape: sizes at which the tensor-core kernels run their real tilings (head size 64 and
+# 128, four query heads per kv head, widths of several tiles, K split over clusters), still small
+# enough for the plain implementation.
+MID_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 2,
+    "hidden_size": 512,
+    "num_attention_heads": 8,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "intermediate_size": 1408,
+    "vocab_size": 1000,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 1024,
+    "hidden_act": "silu",
+}
+
+MID_E = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "num_hidden_layers": 2,
+    "hidden_size": 768,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 6,
+    "head_dim": 128,
+    "intermediate_size": 2048,
+    "vocab_size": 1203,
+    "rope_theta": 10000.0,
+    "rope_scaling": None,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 512,
+    "hidden_act": "silu",
+}
+
 TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+MID = {"D": MID_D, "E": MID_E}
 
 
 def make_folder(raw_config: dict, seed: int, tmp_path, std: float = 0.02, gain_std: float = 0.1,
