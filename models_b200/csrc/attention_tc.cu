@@ -131,6 +131,14 @@ __device__ __forceinline__ void accumulate_16_keys(float (&o)[HD / 8][4], const 
     }
 }
 
+// 2^x by the special-function unit (about two units in the last place; the probabilities it feeds are
+// rounded to bfloat16 afterwards).  2^-inf = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float quad_max(float v) {
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
     return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -452,30 +460,38 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
                     s[2 * part + 1][i] = two[1][i];
                 }
             }
+            // scores stay raw; the scale (times log2 e) is folded into the exponent: 2^(s*c - m*c)
             float part_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
+            if (full) {
 #pragma unroll
-            for (int nt = 0; nt < kTile / 8; ++nt)
+                for (int nt = 0; nt < kTile / 8; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int key = key_base + nt * 8 + tid4 * 2 + (i & 1);
-                    const int r = i >> 1;
-                    const bool visible = full || (key <= row_pos[r] && key >= row_first[r]);
-                    s[nt][i] = visible ? s[nt][i] * scale_log2 : -CUDART_INF_F;  // in units of log2(e): exp(x) = exp2(x log2 e)
-                    part_max[r] = fmaxf(part_max[r], s[nt][i]);
-                }
+                    for (int i = 0; i < 4; ++i) part_max[i >> 1] = fmaxf(part_max[i >> 1], s[nt][i]);
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < kTile / 8; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int key = key_base + nt * 8 + tid4 * 2 + (i & 1);
+                        const int r = i >> 1;
+                        if (!(key <= row_pos[r] && key >= row_first[r])) s[nt][i] = -CUDART_INF_F;
+                        part_max[r] = fmaxf(part_max[r], s[nt][i]);
+                    }
+            }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                const float new_max = fmaxf(run_max[r], quad_max(part_max[r]));
-                // a row that has seen nothing yet keeps -inf; subtract 0 then so that exp gives 0, not NaN
+                const float new_max = fmaxf(run_max[r], quad_max(part_max[r]));  // in raw score units
+                // a row that has seen nothing yet keeps -inf; subtract 0 then so that the exponent is -inf, not NaN
                 const float safe_max = new_max == -CUDART_INF_F ? 0.0f : new_max;
-                const float correction = exp2f(run_max[r] - safe_max);
+                const float correction = fast_exp2((run_max[r] - safe_max) * scale_log2);
+                const float offset = -safe_max * scale_log2;
                 run_max[r] = new_max;
                 float local = 0.0f;
 #pragma unroll
                 for (int nt = 0; nt < kTile / 8; ++nt)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        const float e = exp2f(s[nt][2 * r + c] - safe_max);
+                        const float e = fast_exp2(fmaf(s[nt][2 * r + c], scale_log2, offset));
                         s[nt][2 * r + c] = e;
                         local += e;
                     }
