@@ -220,3 +220,43 @@ def test_temperature_generation_through_the_entry_point(cuda_device, folders):
     assert [r.tokens for r in a] != [r.tokens for r in c]
     assert all(0 <= t < 320 for r in a for t in r.tokens)
     assert model.generate_batch([[1, 2, 3]], options)[0].tokens == a[0].tokens  # alone or in a batch
+
+
+def test_command_line_generate_and_profiles(cuda_device, folders, tmp_path):
+    """`python -m models_b200 ...` as a user types it: generate (greedy, two prompts from a file), a
+    random model folder, and the decode / sessions profiles."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(*args):
+        proc = subprocess.run([sys.executable, "-m", "models_b200", *args], cwd=root, capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        return proc.stdout
+
+    prompts = tmp_path / "prompts.txt"
+    prompts.write_text("1 2 3 4\n9,8,7\n")
+    report = json.loads(run("generate", "--model", str(folders["B"]), "--prompt-file", str(prompts), "--max-tokens", "6",
+                            "--temperature", "0", "--dtype", "float32", "--context", "128"))
+    assert len(report["results"]) == 2
+    for prompt, result in zip(([1, 2, 3, 4], [9, 8, 7]), report["results"]):
+        expected, _ = plain_greedy(folders["B"], prompt, 6, (5, 7))
+        assert result["tokens"] == expected and result["prompt_tokens"] == len(prompt)
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(TINY["A"]))
+    made = run("random-model", "--config", str(config), "--seed", "4", "--output", str(tmp_path / "made")).strip()
+    assert sorted(os.listdir(made)) == ["config.json", "model.safetensors"]
+    out = json.loads(run("profile-decode", "--model", made, "--prompt-tokens", "20", "--measure-tokens", "8", "--context", "128"))
+    assert out["measured_tokens"] == 8 and out["decode_tokens_per_second"] > 0
+    out = json.loads(run("profile-sessions", "--model", made, "--prompt-tokens", "10", "--concurrency", "3", "--measure-steps",
+                         "4", "--context", "128"))
+    assert out["aggregate_tokens_per_second"] > 0
+    out = json.loads(run("profile-prefill", "--config", str(config), "--random-seed", "1", "--prompt-tokens", "100",
+                         "--context", "128", "--iterations", "2"))
+    assert out["prompt_tokens"] == 100
+    bad = subprocess.run([sys.executable, "-m", "models_b200", "generate", "--model", made, "--bogus", "1"], cwd=root,
+                         capture_output=True, text=True)
+    assert bad.returncode == 2 and "unknown option: --bogus" in bad.stderr
