@@ -17,110 +17,21 @@
 // Every wait on an mbarrier is bounded: after about two seconds a role gives up, records where in
 // g_gemm_status and leaves its loop; all roles then meet at the final barrier, tensor memory is
 // freed and the kernel returns.  mb_gemm_tc_status() reads the record.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 MB_DEFINE_LAST_ERROR()
 
 namespace mb {
 
-using bf16 = __nv_bfloat16;
-
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
 
-constexpr int kBlockM = 128, kBlockN = 256, kBlockK = 64, kStages = 4;
+constexpr int kBlockM = 128, kBlockN = 256, kStages = 4;
+constexpr uint32_t kInstruction = instruction_descriptor(kBlockM, kBlockN);
 constexpr int kTileABytes = kBlockM * kBlockK * 2;      // 16 KB
 constexpr int kBoxBBytes = 128 * kBlockK * 2;           // 16 KB, two boxes per stage
 constexpr int kStageBytes = kTileABytes + 2 * kBoxBBytes;
 constexpr int kThreads = 192;                           // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
 constexpr int kAccumulatorColumns = 256, kTmemColumns = 512;
-constexpr long long kWaitCycles = 4000000000LL;         // about two seconds
-
-__device__ int g_gemm_status = 0;  // 0: fine; else 1 + (role << 8) of the first wait that gave up
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-// Bounded wait: false (and a record) when the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int role) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - start > kWaitCycles) {
-            atomicCAS(&g_gemm_status, 0, 1 + (role << 8));
-            return false;
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_descriptor(uint32_t smem_addr) {
-    uint64_t desc = 0;
-    desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address
-    desc |= (uint64_t)1 << 16;                        // leading byte offset (unused with this swizzle)
-    desc |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: 8 rows x 128 bytes
-    desc |= (uint64_t)1 << 46;                        // descriptor version of this architecture
-    desc |= (uint64_t)2 << 61;                        // 128-byte swizzle
-    return desc;
-}
-// bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = 256
-constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstruction), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 struct GemmArgs {
     int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
@@ -211,7 +122,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint64_t a_desc = umma_descriptor(a_addr), b_desc = umma_descriptor(a_addr + kTileABytes);
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 16; ++ks)  // 32 bytes further along K per step: +2 in the address field
-                        umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, (kb > 0 || ks > 0) ? 1u : 0u);
+                        umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(empty_bar + 8 * stage);  // the stage is free once these products have read it
                     if (++stage == kStages) {
                         stage = 0;
@@ -301,37 +212,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
     }
-}
-
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* entry = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
-            result == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiled)entry;
-    }
-    return fn;
-}
-
-// A row-major bfloat16 matrix [rows, k] (row stride ld elements) as a TMA map with boxes of 128 rows x 64 columns.
-static int make_map(CUtensorMap* map, const void* base, int rows, int k, int ld) {
-    EncodeTiled encode = encode_tiled();
-    if (!encode) return fail("gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, 128};
-    const cuuint32_t element_strides[2] = {1, 1};
-    CUresult status = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
-                             element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (status != CUDA_SUCCESS) return fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)status);
-    return 0;
 }
 
 template <int EPI>

@@ -12,6 +12,7 @@ LIBRARIES = [
     ("mb_sampling", ["sampling.cu"], {}),
     ("mb_skinny_gemm", ["skinny_gemm.cu"], {}),
     ("mb_gemm_tcgen05", ["gemm_tcgen05.cu"], {}),
+    ("mb_wide_gemm_tcgen05", ["wide_gemm_tcgen05.cu"], {}),
     # the tensor-core attention is compiled per head size when a model first needs it; these are
     # the sizes of the benchmark models and of the tests
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 16}),

@@ -399,14 +399,21 @@ def gemm_tc():
     return load_library("mb_gemm_tcgen05", ["gemm_tcgen05.cu"])
 
 
-TCGEN05_MIN_ROWS = 128  # one row tile of the kernel; fewer rows leave most of it empty
+TCGEN05_MIN_ROWS = 33  # fewer rows take the narrow decode product
+WIDE_ROWS = 128  # most activation rows of the wide decode product
 
 
 def gemm_tcgen05_takes(weight: torch.Tensor, epilogue: int = EPI_BF16, rows: Optional[int] = None) -> bool:
-    """Whether the tcgen05 matrix product takes this weight (and, if given, pays off for so many rows)."""
+    """Whether a tcgen05 matrix product takes this weight and, if `rows` is given, pays off for so
+    many rows: above 128 the prefill form; from 33 to 128 the wide decode form, and that only for
+    matrices with a row tile per multiprocessor (with fewer it would have to split K, and a library
+    product is quicker there)."""
     n = weight.shape[0] // 2 if epilogue == EPI_SWIGLU else weight.shape[0]
-    if rows is not None and rows < TCGEN05_MIN_ROWS:
-        return False
+    if rows is not None:
+        if rows < TCGEN05_MIN_ROWS:
+            return False
+        if rows <= WIDE_ROWS and n < 128 * _sm_count(weight.device):
+            return False
     return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.stride(1) == 1 and weight.shape[1] % 8 == 0
             and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0 and n % 8 == 0
             and (epilogue != EPI_SWIGLU or weight.shape[0] % 2 == 0))
@@ -435,9 +442,56 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16
     return out
 
 
+def wide_gemm_lib():
+    return load_library("mb_wide_gemm_tcgen05", ["wide_gemm_tcgen05.cu"])
+
+
+_tickets = {}
+
+
+def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Up to 128 activation rows times weight^T on the tcgen05 tensor cores with the weights as the
+    128-row operand (decode at wide batches).  Epilogues as for skinny_gemm."""
+    _cuda(x, weight, out)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != weight.shape[1] or x.shape[0] > WIDE_ROWS:
+        raise KernelError(f"wide_gemm: activations {tuple(x.shape)} {x.dtype} do not fit the weight {tuple(weight.shape)}")
+    if not gemm_tcgen05_takes(weight, epilogue) or x.stride(0) % 8 or x.data_ptr() % 16:
+        raise KernelError(f"wide_gemm does not take a {tuple(weight.shape)} {weight.dtype} weight")
+    batch, k = x.shape
+    n_w = weight.shape[0]
+    n = n_w // 2 if epilogue == EPI_SWIGLU else n_w
+    if epilogue == EPI_RESIDUAL:
+        if out is None or out.dtype != torch.float32 or out.shape != (batch, n) or out.stride(1) != 1:
+            raise KernelError("the residual epilogue adds into a float32 [rows, n] tensor")
+    elif out is None:
+        out = torch.empty((batch, n), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=x.device)
+    lib = wide_gemm_lib()
+    sms = _sm_count(x.device)
+    need_partial, need_tickets = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    lib.mb_wide_gemm_scratch(n_w, k, batch, epilogue, sms, ctypes.byref(need_partial), ctypes.byref(need_tickets))
+    partial = tickets = None
+    if need_partial.value:
+        partial = torch.empty((need_partial.value,), dtype=torch.float32, device=x.device)
+        key = x.device.index if x.device.index is not None else torch.cuda.current_device()
+        tickets = _tickets.get(key)
+        if tickets is None or tickets.numel() < need_tickets.value:
+            # zero once; every launch leaves the tickets at zero
+            tickets = _tickets[key] = torch.zeros((max(4096, need_tickets.value),), dtype=torch.int32, device=x.device)
+    _run(lib, lib.mb_wide_gemm(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), batch, n_w, k,
+                               epilogue, _p(partial), _p(tickets), sms, _stream()))
+    return out
+
+
+def tensor_core_gemm(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The tcgen05 product for this many rows: up to 128 the wide decode form, above the prefill form."""
+    if a.shape[0] <= WIDE_ROWS:
+        return wide_gemm(a, weight, epilogue, out)
+    return gemm_tcgen05(a, weight, epilogue, out)
+
+
 def gemm_tcgen05_status() -> int:
-    """0 unless a bounded wait inside the kernel ever gave up (then it names the role)."""
-    return int(gemm_tc().mb_gemm_tc_status())
+    """0 unless a bounded wait inside a tcgen05 kernel ever gave up (then it names the role)."""
+    return int(gemm_tc().mb_gemm_tc_status()) or int(wide_gemm_lib().mb_wide_gemm_status())
 
 
 # ------------------------------------------------------------------------------------ sampling

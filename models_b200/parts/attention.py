@@ -106,7 +106,7 @@ class AttentionMixer(Mixer):
         if self.b_qkv is not None:
             ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
         attended = self._rotate_store_attend(qkv, batch, run)
-        ops.gemm_tcgen05(attended, self.w_o, ops.EPI_RESIDUAL, out=x)
+        ops.tensor_core_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x)
 
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:
         dtype = self.runtime.compute_dtype

@@ -70,8 +70,8 @@ class GatedFeedForward(Part):
     def forward_into(self, x: torch.Tensor, xn: torch.Tensor) -> None:
         """x += down(silu(gate(xn)) * up(xn)): the activation rides in the gate/up product, the residual
         add in the down product; neither the gate/up matrix nor the down result passes through memory."""
-        hidden = ops.gemm_tcgen05(xn, self.w_gate_up, ops.EPI_SWIGLU)
-        ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+        hidden = ops.tensor_core_gemm(xn, self.w_gate_up, ops.EPI_SWIGLU)
+        ops.tensor_core_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
@@ -83,7 +83,7 @@ class GatedFeedForward(Part):
             return delta
         if (self.b_gate_up is None and xn.dtype == torch.bfloat16
                 and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, xn.shape[0])):
-            hidden = ops.gemm_tcgen05(xn, self.w_gate_up, ops.EPI_SWIGLU)
+            hidden = ops.tensor_core_gemm(xn, self.w_gate_up, ops.EPI_SWIGLU)
         else:
             gate_up = linear(xn, self.w_gate_up, dtype)
             if self.b_gate_up is not None:

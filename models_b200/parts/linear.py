@@ -1,8 +1,9 @@
 """Matrix products y = x . W^T for row-major W [out, in] (integrallis/models,
 backend-java/.../ops/TensorOps.java:61-63), chosen by the weight's storage.
 
-bfloat16 weights: with few activation rows (decode) this package's own weight-streaming kernel
-(csrc/skinny_gemm.cu); with many rows (prefill) its tcgen05 kernel (csrc/gemm_tcgen05.cu).  Widths
+bfloat16 weights: with up to 32 activation rows (decode) this package's own weight-streaming kernel
+(csrc/skinny_gemm.cu); with 33 to 128 rows its tcgen05 kernel with the weights as the 128-row operand
+(csrc/wide_gemm_tcgen05.cu); with more rows (prefill) its tcgen05 kernel csrc/gemm_tcgen05.cu.  Widths
 that are no multiple of 8 fall to a library product (bfloat16 inputs, float accumulation), the place
 where the reference too calls a library (its matmul is VectorUtil.batchDotProduct of an external
 artifact).
@@ -33,8 +34,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> tor
         return ops.skinny_gemm(weight, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16, x=a)
     if (ops.gemm_tcgen05_takes(weight, rows=a.shape[0]) and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
             and out_dtype in (torch.bfloat16, torch.float32)):
-        # prefill: many rows, this package's tcgen05 kernel
-        return ops.gemm_tcgen05(a, weight, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
+        # many rows: this package's tcgen05 kernels (wide decode form up to 128 rows, prefill form above)
+        return ops.tensor_core_gemm(a, weight, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16)
     if out_dtype == torch.float32:
         return torch.mm(a, weight.t(), out_dtype=torch.float32)
     return torch.mm(a, weight.t())

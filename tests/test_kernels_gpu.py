@@ -451,3 +451,32 @@ def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
     assert ops.gemm_tcgen05_status() == 0
     with pytest.raises(ops.KernelError):
         ops.gemm_tcgen05(a.cuda(), torch.zeros(n + 4, k, dtype=torch.bfloat16, device="cuda"), ops.EPI_BF16)
+
+
+@pytest.mark.parametrize("batch", [33, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(144, 136), (2048, 2048), (272, 8192), (1040, 328)])
+def test_wide_decode_gemm_all_epilogues(cuda_device, batch, n, k):
+    """The wide decode product (weights as the 128-row tcgen05 operand, K split with tickets) against
+    float64; a second call must find its tickets reset and give the same bits."""
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(batch + n + k)
+    a = torch.randn(batch, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    ad, wd = a.cuda(), w.cuda()
+    exact = a.double() @ w.double().t()
+    scale = float(exact.abs().max())
+    out = ops.wide_gemm(ad, wd, ops.EPI_F32)
+    assert float((out.double().cpu() - exact).abs().max()) < 2e-5 * scale * math.sqrt(k)
+    assert torch.equal(out, ops.wide_gemm(ad, wd, ops.EPI_F32))
+    out = ops.wide_gemm(ad, wd, ops.EPI_BF16)
+    assert out.dtype == torch.bfloat16 and float((out.double().cpu() - exact).abs().max()) < 1e-2 * scale
+    residual = torch.randn(batch, n, generator=g)
+    rd = residual.cuda()
+    ops.wide_gemm(ad, wd, ops.EPI_RESIDUAL, out=rd)
+    assert float((rd.double().cpu() - (residual.double() + exact)).abs().max()) < 2e-5 * (scale + 4) * math.sqrt(k)
+    gated = ops.wide_gemm(ad, wd, ops.EPI_SWIGLU)
+    want = plain_llama.swiglu(exact[:, : n // 2], exact[:, n // 2:])
+    assert gated.shape == (batch, n // 2)
+    assert float((gated.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+    assert ops.gemm_tcgen05_status() == 0
