@@ -148,20 +148,28 @@ def random_prompts(n, length, vocab, seed):
 
 
 def device_decode(model, batch, steps, warmup, sample_clocks=False):
-    """K decode steps of `batch` sequences after 512-token prompts, greedy, timed on the device."""
+    """K decode steps of `batch` sequences after 512-token prompts, greedy, timed on the device.
+    As in generation, a step is queued with the ids of the step before it still on the device, and
+    the host reads every step's ids while the next step runs."""
     import torch
 
-    from models_b200.engine import StepEntry
+    from models_b200 import SamplingOptions
+    from models_b200.engine.stepper import EngineStepper
     from models_b200.kernels import ops
+    from models_b200.sampling.sampler import RequestSampling
 
     engine = model.engine
     vocab = engine.spec.vocab_size
     prompts = random_prompts(batch, PROMPT_TOKENS, vocab, 1)
-    slots = [engine.open_slot() for _ in range(batch)]
-    logits = engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
-    tokens = ops.argmax_rows(logits).tolist()
+    stepper = EngineStepper(engine)
+    greedy = [RequestSampling(SamplingOptions(temperature=0.0), p) for p in prompts]
+    rows = list(range(batch))
+    slots = [stepper.open_slot() for _ in range(batch)]
+    pending = stepper.sample_start(stepper.prefill(slots, prompts), greedy)
     for _ in range(warmup):
-        tokens = engine.greedy_tokens(engine.decode(slots, tokens)).tolist()
+        logits = stepper.decode_pending(slots, pending, rows)
+        pending.result()
+        pending = stepper.sample_start(logits, greedy)
     sampler = ClockSampler() if sample_clocks else None
     if sampler:
         sampler.start()
@@ -172,7 +180,9 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False):
     start.record()
     for _ in range(steps):
         kv_total += sum(engine.length(s) + 1 for s in slots)
-        tokens = engine.greedy_tokens(engine.decode(slots, tokens)).tolist()
+        logits = stepper.decode_pending(slots, pending, rows)
+        pending.result()
+        pending = stepper.sample_start(logits, greedy)
     end.record()
     torch.cuda.synchronize()
     seconds = start.elapsed_time(end) / 1e3
@@ -201,7 +211,10 @@ def e2e_decode(model, batch, steps, warmup):
     model.generate_batch(prompts, SamplingOptions(temperature=0.0, max_tokens=steps + 1), on_token=on_token)
     seconds = stamps[-1] - stamps[0]
     graphs = model.engine.decode_graphs
-    h2d = 4 * graphs.captured[graphs.rung(batch)].layout.total if graphs and graphs.captured else 0
+    h2d = 0  # the step's indices; the ids themselves stay on the device
+    if graphs and graphs.captured:
+        layout = graphs.captured[graphs.rung(batch)].layout
+        h2d = 4 * (layout.total - layout.tokens)
     return {"tokens_per_second": batch * (len(stamps) - 1) / seconds, "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": 4 * batch}
 

@@ -9,7 +9,7 @@ point at the cache's spare page and store nothing, so padding changes no result.
 
 from __future__ import annotations
 
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -69,23 +69,28 @@ class _Captured:
         self.staging = [(torch.zeros_like(self.host).pin_memory(), torch.cuda.Event()) for _ in range(4)]
         self.staging_next = 0
 
-    def upload(self) -> None:
+    def upload(self, skip_tokens: bool = False) -> None:
         """Copies the indices to the device through a small ring of pinned buffers: the copy is
-        asynchronous, so the buffer it reads must not be rewritten before it has run."""
+        asynchronous, so the buffer it reads must not be rewritten before it has run.  With
+        `skip_tokens` the token ids (the first part of the buffer) are left as they are on the device:
+        the sampler has written them there."""
         staging, event = self.staging[self.staging_next]
         self.staging_next = (self.staging_next + 1) % len(self.staging)
         event.synchronize()  # returns at once unless the host is several steps ahead of the GPU
         staging.copy_(self.host)
-        self.dev.copy_(staging, non_blocking=True)
+        first = self.layout.tokens if skip_tokens else 0
+        self.dev[first:].copy_(staging[first:], non_blocking=True)
         event.record()
 
-    def update(self, cache, slots: Sequence[int], tokens: Sequence[int]) -> None:
+    def update(self, cache, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
         """The indices of one decode step, written in place: one token per slot, appended at each
-        slot's length.  Page-table rows are rewritten only when a sequence moved in or gained a page."""
+        slot's length.  Page-table rows are rewritten only when a sequence moved in or gained a page.
+        `tokens` None: the token ids are already on the device."""
         live, page = len(slots), cache.page_size
         pad_row = cache.max_slots
         lengths = [cache.lengths[s] for s in slots]
-        self.tokens_h[:live] = tokens
+        if tokens is not None:
+            self.tokens_h[:live] = tokens
         self.positions_h[:live] = lengths
         self.kv_lens_h[:live] = lengths
         self.kv_lens_h[:live] += 1
@@ -132,16 +137,23 @@ class DecodeGraphs:
                 return size
         raise ValueError(f"a decode batch of {n} exceeds the largest captured size {self.max_batch}")
 
-    def step(self, entries: Sequence) -> torch.Tensor:
+    def step(self, entries: Sequence, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """entries: (slot, [token], [0]) each; the cache already has room.  Returns logits
-        [len(entries), vocab]; they live in the graph's output buffer until the next replay."""
+        [len(entries), vocab]; they live in the graph's output buffer until the next replay.
+        `device_tokens` (int32 [len(entries)], on the device) replaces the entries' token ids: the
+        step then needs nothing from the host that depends on the step before it."""
         engine = self.engine
         size = self.rung(len(entries))
         captured = self.captured.get(size)
         if captured is None:
             captured = self.captured[size] = _Captured(engine, size, self.blocks, self.pool)
-        captured.update(engine.cache, [e[0] for e in entries], [e[1][0] for e in entries])
-        captured.upload()
+        if device_tokens is None:
+            captured.update(engine.cache, [e[0] for e in entries], [e[1][0] for e in entries])
+            captured.upload()
+        else:
+            captured.update(engine.cache, [e[0] for e in entries], None)
+            captured.upload(skip_tokens=True)
+            captured.batch.tokens[: len(entries)].copy_(device_tokens)
         captured.graph.replay()
         ops.add_launches(captured.kernels)
         self.last_argmax = captured.argmax[: len(entries)]

@@ -169,6 +169,26 @@ class Engine:
         self.steps += 1
         return logits
 
+    def decode_device_tokens(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """`decode` with the token ids still on the device (int32 [len(slots)], what a sampler just
+        wrote): the step is queued without waiting for them, so the host can prepare it while the
+        step before it runs.  Without decode graphs (or beyond their sizes) the ids are fetched and
+        the step runs as `decode` does."""
+        graphs = self.decode_graphs
+        if (graphs is None or len(slots) > graphs.max_batch or
+                any(-(-(self.cache.lengths[s] + 1) // self.cache.page_size) > graphs.blocks for s in slots)):
+            return self.decode(slots, tokens.tolist())
+        entries = [StepEntry(s, [0], [0]) for s in slots]  # ids come from the device; a sampler's ids are in range
+        self.validate(entries)
+        appends = [(s, 1) for s in slots]
+        self.cache.append(appends)
+        logits = graphs.step([(e.slot, e.tokens, e.want) for e in entries], device_tokens=tokens)
+        self.last_argmax = graphs.last_argmax
+        self._last_logits = logits
+        self.cache.commit(appends)
+        self.steps += 1
+        return logits
+
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
         """First maximum of every row of `logits` (device, int32): taken from the decode graph when
         `logits` is what the last `decode` returned, else computed."""

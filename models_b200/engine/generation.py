@@ -136,32 +136,72 @@ class GenerationLoop:
         results[request.index] = GenerationResult(
             request.tokens, GenerationUsage(len(request.prompt), len(request.tokens)), reason)
 
+    def _take(self, r: _Live, token: int, results, on_token) -> bool:
+        """What the reference's loop does with one sampled token; True if the request goes on."""
+        stops = self.stop_token_ids | set(r.sampling.options.stop_token_ids)
+        if token in stops:
+            self._finish(r, "stop", results)
+            return False
+        r.tokens.append(token)
+        if r.sampling.history is not None:
+            r.sampling.history.append(token)
+        if on_token is not None:
+            on_token(r.index, token)
+        if len(r.tokens) >= r.limit:
+            self._finish(r, "length", results)
+            return False
+        r.last = token
+        return True
+
+    def _run_batch_pipelined(self, live: List[_Live], results, on_token) -> None:
+        """The same decisions, one step ahead of the ids: the next decode step is queued for every
+        request that has room for another token before the last ids have reached the host, with
+        the ids taken on the device.  A request whose pending token turns out to be a stop token
+        has then been stepped once more than needed; that step's row is dropped, nothing of it is
+        emitted, and the slot goes back as always.  The rows of such a step are sampled with the
+        others (their ids are never read).  Tokens, order and counts are those of the unpipelined loop."""
+        stepper = self.stepper
+        rows: List[Optional[_Live]] = list(live)  # aligned with the rows of `pending`; None: finished
+        try:
+            for r in live:
+                r.slot = stepper.open_slot()
+            logits = stepper.prefill([r.slot for r in live], [r.prompt for r in live])
+            pending = stepper.sample_start(logits, [r.sampling for r in live])
+            samplings = [r.sampling for r in live]
+            while any(r is not None for r in rows):
+                ahead = [i for i, r in enumerate(rows) if r is not None and len(r.tokens) + 1 < r.limit]
+                next_logits = None
+                if ahead:
+                    next_logits = stepper.decode_pending([rows[i].slot for i in ahead], pending, ahead)
+                tokens = pending.result()
+                for i, r in enumerate(rows):
+                    if r is not None and not self._take(r, int(tokens[i]), results, on_token):
+                        rows[i] = None
+                samplings = [samplings[i] for i in ahead]
+                rows = [rows[i] for i in ahead]
+                if any(r is not None for r in rows):
+                    pending = stepper.sample_start(next_logits, samplings)
+        except BaseException:
+            for r in live:
+                if r.slot >= 0:
+                    try:
+                        stepper.release_slot(r.slot)
+                    except Exception:
+                        pass
+                    r.slot = -1
+            raise
+
     def _run_batch(self, live: List[_Live], results, on_token) -> None:
         stepper = self.stepper
+        if hasattr(stepper, "decode_pending") and hasattr(stepper, "sample_start"):
+            return self._run_batch_pipelined(live, results, on_token)
         try:
             for r in live:
                 r.slot = stepper.open_slot()
             logits = stepper.prefill([r.slot for r in live], [r.prompt for r in live])
             while live:
                 sampled = stepper.sample(logits, [r.sampling for r in live])
-                going: List[_Live] = []
-                for r, token in zip(live, sampled):
-                    token = int(token)
-                    stops = self.stop_token_ids | set(r.sampling.options.stop_token_ids)
-                    if token in stops:
-                        self._finish(r, "stop", results)
-                        continue
-                    r.tokens.append(token)
-                    if r.sampling.history is not None:
-                        r.sampling.history.append(token)
-                    if on_token is not None:
-                        on_token(r.index, token)
-                    if len(r.tokens) >= r.limit:
-                        self._finish(r, "length", results)
-                        continue
-                    r.last = token
-                    going.append(r)
-                live = going
+                live = [r for r, token in zip(live, sampled) if self._take(r, int(token), results, on_token)]
                 if live:
                     logits = stepper.decode([r.slot for r in live], [r.last for r in live])
         except BaseException:

@@ -19,6 +19,8 @@ class EngineStepper:
         self.page_size = engine.cache.page_size
         self.capacity_tokens = engine.cache.num_pages * engine.cache.page_size
         self.max_positions = engine.runtime.max_positions
+        self._pinned = [(torch.empty((256,), dtype=torch.int32).pin_memory(), torch.cuda.Event()) for _ in range(4)]
+        self._pinned_next = 0
 
     def open_slot(self) -> int:
         return self.engine.open_slot()
@@ -37,3 +39,39 @@ class EngineStepper:
 
     def sample(self, logits: torch.Tensor, requests: Sequence[RequestSampling]) -> List[int]:
         return self.sampler.sample(logits, requests, self.engine.greedy_tokens).tolist()
+
+    # -- the same in two halves, so that the next step can be queued before the ids reach the host
+
+    def sample_start(self, logits: torch.Tensor, requests: Sequence[RequestSampling]) -> "PendingTokens":
+        """Launches the sampling and the copy of the ids to the host; returns at once."""
+        tokens = self.sampler.sample(logits, requests, self.engine.greedy_tokens)
+        host, event = self._pinned[self._pinned_next]
+        self._pinned_next = (self._pinned_next + 1) % len(self._pinned)
+        if host.numel() < tokens.numel():
+            host = torch.empty((max(256, tokens.numel()),), dtype=torch.int32).pin_memory()
+            self._pinned[(self._pinned_next - 1) % len(self._pinned)] = (host, event)
+        event.synchronize()  # the copy that last used this buffer (several steps ago) is done
+        host[: tokens.numel()].copy_(tokens, non_blocking=True)
+        event.record()
+        return PendingTokens(tokens, host, event, tokens.numel())
+
+    def decode_pending(self, slots: Sequence[int], pending: "PendingTokens", rows: Sequence[int]) -> torch.Tensor:
+        """One more token for each slot, the token being row rows[i] of `pending` -- taken on the device."""
+        tokens = pending.device
+        if list(rows) != list(range(pending.count)):
+            tokens = tokens[torch.tensor(list(rows), dtype=torch.long, device=tokens.device)]
+        return self.engine.decode_device_tokens(slots, tokens)
+
+
+class PendingTokens:
+    """Sampled ids that are on the device and on their way to the host."""
+
+    def __init__(self, device: torch.Tensor, host: torch.Tensor, event, count: int):
+        self.device, self._host, self._event, self.count = device, host, event, count
+        self._values = None
+
+    def result(self) -> List[int]:
+        if self._values is None:
+            self._event.synchronize()
+            self._values = self._host[: self.count].tolist()
+        return self._values

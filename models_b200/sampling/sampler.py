@@ -32,6 +32,8 @@ class BatchSampler:
         self.vocab = vocab_size
         self.device = torch.device(device)
         self._max_sorted = None
+        self._staging = None
+        self._staging_next = 0
 
     def check(self, options: SamplingOptions) -> None:
         """Refuses what the kernel cannot do exactly, before any step runs."""
@@ -55,12 +57,7 @@ class BatchSampler:
         if all(r.options.greedy for r in requests):
             return greedy(logits)[:rows] if greedy is not None else ops.argmax_rows(logits[:rows])
         logits = logits[:rows]
-        temperature = torch.tensor([r.options.temperature for r in requests], dtype=torch.float32)
-        top_k = torch.tensor([min(r.options.top_k, self.vocab) for r in requests], dtype=torch.int32)
-        top_p = torch.tensor([r.options.top_p for r in requests], dtype=torch.float32)
-        penalty = torch.tensor([r.options.repetition_penalty for r in requests], dtype=torch.float32)
-        seeds = torch.tensor([r.seed for r in requests], dtype=torch.int64)
-        counters = torch.tensor([r.draws for r in requests], dtype=torch.int64)
+        temperature, top_k, top_p, penalty, seeds, counters = self._parameters(requests)
         history = history_len = counts = None
         if any(r.history is not None for r in requests):
             longest = max(len(r.history) if r.history is not None else 0 for r in requests)
@@ -73,13 +70,39 @@ class BatchSampler:
             history, history_len = host.to(self.device), lens.to(self.device)
             counts = torch.empty((rows, self.vocab), dtype=torch.int32, device=self.device)
         work = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.device)
-        d = self.device
-        out = ops.sample_rows(logits, work, counts, temperature.to(d), top_k.to(d), top_p.to(d), penalty.to(d), history,
-                              history_len, seeds.to(d), counters.to(d))
+        out = ops.sample_rows(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters)
         for r in requests:
             if r.options.temperature > 0.0:
                 r.draws += 1
         return out
+
+    def _parameters(self, requests: Sequence[RequestSampling]):
+        """The per-row options on the device, sent as one asynchronous copy from pinned memory (a
+        copy from ordinary memory would wait for every step that is still queued)."""
+        rows = len(requests)
+        if self._staging is None or self._staging[0][0].numel() < 32 * rows:
+            size = 32 * max(64, rows)
+            self._staging = [(torch.empty((size,), dtype=torch.uint8).pin_memory(), torch.cuda.Event()) for _ in range(4)]
+        host, event = self._staging[self._staging_next]
+        self._staging_next = (self._staging_next + 1) % len(self._staging)
+        event.synchronize()  # the copy that last read this buffer, four calls ago
+        device = torch.empty((32 * rows,), dtype=torch.uint8, device=self.device)
+
+        def views(buffer):
+            floats = buffer[: 12 * rows].view(torch.float32).view(3, rows)
+            ints = buffer[12 * rows: 16 * rows].view(torch.int32)
+            longs = buffer[16 * rows: 32 * rows].view(torch.int64).view(2, rows)
+            return floats, ints, longs
+
+        floats, ints, longs = views(host)
+        floats.copy_(torch.tensor([[r.options.temperature for r in requests], [r.options.top_p for r in requests],
+                                   [r.options.repetition_penalty for r in requests]], dtype=torch.float32))
+        ints.copy_(torch.tensor([min(r.options.top_k, self.vocab) for r in requests], dtype=torch.int32))
+        longs.copy_(torch.tensor([[r.seed for r in requests], [r.draws for r in requests]], dtype=torch.int64))
+        device.copy_(host[: 32 * rows], non_blocking=True)
+        event.record()
+        floats, ints, longs = views(device)
+        return floats[0], ints, floats[1], floats[2], longs[0], longs[1]
 
     @staticmethod
     def record(requests: Sequence[RequestSampling], tokens: Sequence[int]) -> None:

@@ -260,3 +260,45 @@ def test_command_line_generate_and_profiles(cuda_device, folders, tmp_path):
     bad = subprocess.run([sys.executable, "-m", "models_b200", "generate", "--model", made, "--bogus", "1"], cwd=root,
                          capture_output=True, text=True)
     assert bad.returncode == 2 and "unknown option: --bogus" in bad.stderr
+
+
+class OneAtATime:
+    """An engine stepper without the step-ahead interface: the loop then waits for every step's ids."""
+
+    def __init__(self, stepper):
+        self._stepper = stepper
+        self.page_size, self.capacity_tokens, self.max_positions = stepper.page_size, stepper.capacity_tokens, stepper.max_positions
+        for name in ("open_slot", "release_slot", "check_options", "prefill", "decode", "sample"):
+            setattr(self, name, getattr(stepper, name))
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stepping_ahead_of_the_sampled_ids_changes_no_token(cuda_device, folders, dtype, graphs):
+    """The loop queues the next decode step before the last ids have reached the host.  The tokens,
+    the finish reasons and the slots are those of the loop that waits, for greedy and for seeded
+    sampling, with requests that stop early (a stop id chosen among the tokens they produce)."""
+    import models_b200
+    from models_b200 import SamplingOptions
+    from models_b200.engine.generation import GenerationLoop
+
+    raw = TINY["B"]
+    model = models_b200.load_model(folders["B"], dtype=dtype, max_batch=4, context=128, cuda_graphs=graphs)
+    prompts = [random_tokens(raw["vocab_size"], n, 70 + n) for n in (5, 1, 23, 12, 2, 31)]
+    waiting = GenerationLoop(OneAtATime(model._stepper), 4, model.engine.spec.stop_token_ids)
+    for base in (SamplingOptions(temperature=0.0, max_tokens=24),
+                 SamplingOptions(temperature=0.9, top_k=30, top_p=0.9, max_tokens=24, seed=11),
+                 SamplingOptions(temperature=0.7, top_k=12, top_p=1.0, max_tokens=24, seed=3, repetition_penalty=1.2)):
+        free_run = waiting.run(prompts, base)
+        # stop ids that occur: the 4th token of one request, the 9th of another; and unequal limits
+        stops = (free_run[0].tokens[3], free_run[2].tokens[8])
+        options = [SamplingOptions(temperature=base.temperature, top_k=base.top_k, top_p=base.top_p, seed=base.seed,
+                                   repetition_penalty=base.repetition_penalty, max_tokens=limit, stop_token_ids=stops)
+                   for limit in (24, 3, 24, 1, 17, 10)]
+        expected = waiting.run(prompts, options)
+        got = model.generate_batch(prompts, options)
+        assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in expected]
+        assert any(r.finish_reason == "stop" for r in got)
+        model.engine.cache.check()
+        assert model.engine.cache.slots.held == 0
+    model.close()

@@ -140,3 +140,67 @@ def test_a_failing_step_gives_the_slots_back():
     with pytest.raises(RuntimeError, match="boom"):
         GenerationLoop(stepper, 4, [EOS]).run([[1], [2]], SamplingOptions(temperature=0.0))
     assert not stepper.held
+
+
+class AheadStepper(ScriptedStepper):
+    """The same scripted model with the two-halves interface: ids that are 'still on the device'
+    until result() is called, and a decode step that takes them from there."""
+
+    class Pending:
+        def __init__(self, values, log):
+            self.values, self.log, self.count = values, log, len(values)
+
+        def result(self):
+            self.log.append(("result",))
+            return self.values
+
+    def sample_start(self, logits, requests):
+        # rows of requests that have just ended may still be among the logits; their ids are never read
+        values = [self.scripts[self.held[s][0]][self.held[s][1]] if s in self.held else -1 for s in logits]
+        return self.Pending(values, self.calls)
+
+    def decode_pending(self, slots, pending, rows):
+        return self.decode(slots, [pending.values[i] for i in rows])
+
+    def decode(self, slots, tokens):
+        # a step ahead may carry a stop token for a request that is about to end: the script allows it
+        self.calls.append(("decode", list(slots), list(tokens)))
+        for s, t in zip(slots, tokens):
+            key, n = self.held[s]
+            assert t == self.scripts[key][n], "the token fed back is the one sampled"
+            self.held[s][1] += 1
+        return list(slots)
+
+
+def test_the_loop_that_runs_a_step_ahead_decides_the_same():
+    scripts = {1: [10, 11, 12, EOS, 13], 2: [20, EOS, 5, 5, 5, 5, 5], 3: [30, 31, 32, 33, 34, 35, 36], 4: [EOS, 1, 1, 1],
+               5: [50, 51, 77, 52, 53, 54, 55]}
+    prompts = [[1, 7], [2], [3, 3, 3], [4], [5, 5]]
+    options = [SamplingOptions(temperature=0.0, max_tokens=6), SamplingOptions(temperature=0.0, max_tokens=6),
+               SamplingOptions(temperature=0.0, max_tokens=4), SamplingOptions(temperature=0.0, max_tokens=1),
+               SamplingOptions(temperature=0.0, max_tokens=6, stop_token_ids=(77,))]
+    seen = {}
+    for kind in (ScriptedStepper, AheadStepper):
+        stepper = kind(scripts)
+        emitted = []
+        results = GenerationLoop(stepper, 3, [EOS]).run(prompts, options, on_token=lambda i, t: emitted.append((i, t)))
+        seen[kind] = ([(r.tokens, r.finish_reason, r.usage.prompt_tokens, r.usage.completion_tokens) for r in results], emitted)
+        assert not stepper.held and len(stepper.free) == 64 and len(set(stepper.free)) == 64
+    assert seen[ScriptedStepper] == seen[AheadStepper]
+    assert [r[0] for r in seen[AheadStepper][0]] == [[10, 11, 12], [20], [30, 31, 32, 33], [], [50, 51]]
+    # the step ahead is queued before the ids are read, and never for a request at its limit
+    calls = AheadStepper(scripts)
+    GenerationLoop(calls, 3, [EOS]).run([[3, 3, 3]], SamplingOptions(temperature=0.0, max_tokens=3))
+    kinds = [c[0] for c in calls.calls]
+    assert kinds == ["prefill", "decode", "result", "decode", "result", "result"]
+
+
+def test_a_failing_step_ahead_gives_the_slots_back():
+    class Failing(AheadStepper):
+        def decode_pending(self, slots, pending, rows):
+            raise RuntimeError("boom")
+
+    stepper = Failing({1: [10, 11], 2: [20, 21]})
+    with pytest.raises(RuntimeError, match="boom"):
+        GenerationLoop(stepper, 4, [EOS]).run([[1], [2]], SamplingOptions(temperature=0.0))
+    assert not stepper.held
