@@ -1,0 +1,373 @@
+// Prefill attention on the fifth-generation tensor cores: causal grouped-query attention of many new
+// tokens over the paged cache, bfloat16 storage, float accumulation and softmax.  Compiled for one
+// head size: -DMB_HEAD_DIM=64 or 128.
+//
+// A block takes 128 consecutive query tokens of one head and walks the visible cache pages (64 keys
+// each).  Its six warps have three roles:
+//   * warp 0, one thread: TMA.  The query tile once, then per page the key tile and the value tile
+//     ([64 keys][head size], contiguous in the pool) into a ring of shared-memory stages, 128-byte
+//     swizzle.
+//   * warp 1, one thread: tcgen05.mma.  S = Q . K^T (M = 128, N = 64 keys, K = head size) into one of
+//     two score buffers in tensor memory, then O_page = P . V (M = 128, N = head size, K = 64 keys,
+//     V read as an MN-major operand) into one of two output buffers.  The scores of page t + 1 are
+//     issued before the softmax of page t has finished, so the tensor cores and the softmax overlap.
+//   * warps 2..5, one thread per query row: the running softmax.  A thread reads its row of scores
+//     with tcgen05.ld, masks, takes the maximum, exponentiates (special-function exp2 with the scale
+//     folded into the exponent), writes the probabilities as bfloat16 into shared memory in the
+//     swizzled layout the next product expects, and folds the finished O_page of the page before
+//     into its float accumulator (O = (O + O_page) * correction).  No shuffles: a row never leaves
+//     its thread.
+//
+// Formula: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1543-1670 (kvHead = head /
+// group; dot first, then scale; only positions <= the query's are read; with a window of n only the n
+// positions that end at the query) and backend-java/.../ops/TensorOps.java:1247-1279 (softmax), in its
+// running form.  Probabilities are rounded to bfloat16 for the P . V product.
+//
+// Every mbarrier wait is bounded (about two seconds); a role that gives up records where, all roles
+// meet at the final barrier, tensor memory is freed and the kernel returns.
+// mb_prefill_attention_tc_status() reads the record.
+#include "tcgen05.cuh"
+
+#include <math_constants.h>
+
+#ifndef MB_HEAD_DIM
+#error "compile with -DMB_HEAD_DIM=64 or 128"
+#endif
+
+MB_DEFINE_LAST_ERROR()
+
+namespace mb {
+
+constexpr int HD = MB_HEAD_DIM;
+static_assert(HD == 64 || HD == 128, "this kernel is built for head sizes 64 and 128");
+constexpr int kQRows = 128;               // query tokens per block
+constexpr int kKeys = 64;                 // keys per step: one cache page
+constexpr int kBoxes = HD / 64;           // 64-column TMA boxes per row of a tile
+constexpr int kQBoxBytes = kQRows * 128;  // [128 rows][64 columns]
+constexpr int kQBytes = kBoxes * kQBoxBytes;
+constexpr int kKVBoxBytes = kKeys * 128;  // [64 keys][64 columns]
+constexpr int kKVTileBytes = kBoxes * kKVBoxBytes;
+constexpr int kStageBytes = 2 * kKVTileBytes;  // keys, then values
+constexpr int kStages = HD == 64 ? 3 : 2;
+constexpr int kPBytes = kQRows * kKeys * 2;    // probabilities of one page, bfloat16
+constexpr int kThreads = 192;
+constexpr int kScoreColumns = 64;
+constexpr int kTmemUsed = 2 * kScoreColumns + 2 * HD;
+constexpr int kTmemColumns = kTmemUsed <= 256 ? 256 : 512;
+constexpr size_t kSmemBytes = (size_t)kQBytes + (size_t)kStages * kStageBytes + 2 * (size_t)kPBytes + 1024;
+
+constexpr uint32_t kScoreInstruction = instruction_descriptor(kQRows, kKeys);
+constexpr uint32_t kOutputInstruction = instruction_descriptor(kQRows, HD) | (1u << 16);  // B is MN-major
+
+// MN-major operand with 128-byte swizzle: 64 elements of the MN extent are contiguous (one 128-byte
+// row per step of K), 8-row groups along K are 1024 bytes apart, and further 64-element blocks of
+// the MN extent are `block_bytes` apart.
+__device__ __forceinline__ uint64_t umma_descriptor_mn(uint32_t smem_addr, uint32_t block_bytes) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    desc |= (uint64_t)(block_bytes >> 4) << 16;  // leading byte offset
+    desc |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
+
+__device__ __forceinline__ void tmem_load_32_raw(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttentionArgs {
+    bf16* out;
+    int out_row_stride;
+    const int* block_table;
+    int max_blocks;
+    const int* cu_q;
+    const int* kv_lens;
+    int heads, kv_heads, window;
+    float scale;
+};
+
+// roles in the status record: 1 TMA (stage free), 2 MMA (queries), 3 MMA (keys), 4 MMA (probabilities),
+// 5 softmax (scores), 6 softmax (output of a page)
+__global__ void __launch_bounds__(kThreads, HD == 64 ? 2 : 1)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, const AttentionArgs args) {
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_begin = args.cu_q[seq], q_len = args.cu_q[seq + 1] - q_begin;  // written before the step, by a copy
+    const int q_tile = gridDim.x - 1 - blockIdx.x;  // the tiles with the most keys start first
+    const int t0 = q_tile * kQRows;
+    if (t0 >= q_len) return;
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t barriers[2 * kStages + 7];
+    __shared__ uint32_t tmem_base_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t q_smem = smem_u32(smem);
+    const uint32_t stage_smem = q_smem + kQBytes;
+    const uint32_t p_smem = stage_smem + kStages * kStageBytes;
+    const uint32_t kv_full = smem_u32(&barriers[0]), kv_empty = smem_u32(&barriers[kStages]);
+    const uint32_t q_full = smem_u32(&barriers[2 * kStages]);
+    const uint32_t s_full = smem_u32(&barriers[2 * kStages + 1]);  // two
+    const uint32_t p_full = smem_u32(&barriers[2 * kStages + 3]);  // two
+    const uint32_t o_full = smem_u32(&barriers[2 * kStages + 5]);  // two
+
+    const int valid = min(kQRows, q_len - t0);
+    const int kv_len = args.kv_lens[seq];
+    const int pos0 = kv_len - q_len + t0;  // position of the tile's first token
+    const int last_pos = pos0 + valid - 1;
+    const int window = args.window;
+    const int first_needed = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int t_begin = first_needed / kKeys, t_end = last_pos / kKeys + 1;
+    const int pages = t_end - t_begin;
+    const int kv_head = head / (args.heads / args.kv_heads);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(kv_full + 8 * s, 1);
+            mbar_init(kv_empty + 8 * s, 1);
+        }
+        mbar_init(q_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_full + 8 * b, 1);
+            mbar_init(p_full + 8 * b, 4);  // one arrival per softmax warp
+            mbar_init(o_full + 8 * b, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t tmem_scores = tmem_base, tmem_output = tmem_base + 2 * kScoreColumns;
+    grid_launch_dependents();
+    grid_dependency_wait();  // queries, and the newest keys and values, come from the kernel before this one
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, kQBytes);
+#pragma unroll
+            for (int b = 0; b < kBoxes; ++b) tma_load_2d(q_smem + b * kQBoxBytes, &map_q, head * HD + b * 64, q_begin + t0, q_full);
+            const int* table = args.block_table + (size_t)seq * args.max_blocks;
+            for (int t = 0; t < pages; ++t) {
+                const int stage = t % kStages;
+                if (!mbar_wait(kv_empty + 8 * stage, ((t / kStages) & 1) ^ 1, 1)) break;
+                const int row = (table[t_begin + t] * args.kv_heads + kv_head) * kKeys;
+                const uint32_t dst = stage_smem + stage * kStageBytes;
+                mbar_expect_tx(kv_full + 8 * stage, kStageBytes);
+#pragma unroll
+                for (int b = 0; b < kBoxes; ++b) {
+                    tma_load_2d(dst + b * kKVBoxBytes, &map_k, b * 64, row, kv_full + 8 * stage);
+                    tma_load_2d(dst + kKVTileBytes + b * kKVBoxBytes, &map_v, b * 64, row, kv_full + 8 * stage);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            auto issue_scores = [&](int t) {  // S[t % 2] = Q . K(t)^T
+                const uint32_t k_tile = stage_smem + (t % kStages) * kStageBytes;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t a_desc = umma_descriptor(q_smem + (ks / 4) * kQBoxBytes) + 2 * (ks % 4);
+                    const uint64_t b_desc = umma_descriptor(k_tile + (ks / 4) * kKVBoxBytes) + 2 * (ks % 4);
+                    umma(tmem_scores + (t & 1) * kScoreColumns, a_desc, b_desc, kScoreInstruction, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full + 8 * (t & 1));
+            };
+            bool ok = mbar_wait(q_full, 0, 2) && mbar_wait(kv_full, 0, 3);
+            if (ok) {
+                tcgen05_fence_after();
+                issue_scores(0);
+            }
+            for (int t = 0; t < pages && ok; ++t) {
+                if (t + 1 < pages) {
+                    if (!(ok = mbar_wait(kv_full + 8 * ((t + 1) % kStages), ((t + 1) / kStages) & 1, 3))) break;
+                    tcgen05_fence_after();
+                    issue_scores(t + 1);
+                }
+                if (!(ok = mbar_wait(p_full + 8 * (t & 1), (t >> 1) & 1, 4))) break;
+                tcgen05_fence_after();
+                const uint32_t v_tile = stage_smem + (t % kStages) * kStageBytes + kKVTileBytes;
+                const uint32_t p_tile = p_smem + (t & 1) * kPBytes;
+#pragma unroll
+                for (int j = 0; j < kKeys / 16; ++j)  // 16 keys per instruction: 32 bytes along a row of P, 16 rows of V
+                    umma(tmem_output + (t & 1) * HD, umma_descriptor(p_tile) + 2 * j,
+                         umma_descriptor_mn(v_tile + j * 16 * 128, kKVBoxBytes), kOutputInstruction, j > 0 ? 1u : 0u);
+                umma_commit(o_full + 8 * (t & 1));
+                umma_commit(kv_empty + 8 * (t % kStages));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax: one thread per query row
+        const int quarter = warp & 3;  // the quarter of the tensor-memory lanes this warp may read
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int row_pos = row < valid ? pos0 + row : -1;  // a row beyond the sequence sees nothing
+        const int row_first = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
+        const float scale_log2 = args.scale * 1.4426950408889634f;
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o[i] = 0.0f;
+        float run_max = -CUDART_INF_F, run_sum = 0.0f;
+        bool ok = true;
+        auto fold = [&](int t, float factor) {  // o = (o + O_page(t)) * factor
+            ok = mbar_wait(o_full + 8 * (t & 1), (t >> 1) & 1, 6);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            tcgen05_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t r[32];
+                tmem_load_32_raw(tmem_output + (t & 1) * HD + lane_base + c, r);
+                tmem_wait_loads();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c + i] = (o[c + i] + __uint_as_float(r[i])) * factor;
+            }
+        };
+        for (int t = 0; t < pages; ++t) {
+            ok = mbar_wait(s_full + 8 * (t & 1), (t >> 1) & 1, 5);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            uint32_t s[kKeys];
+            tmem_load_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base, &s[0]);
+            tmem_load_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base + 32, &s[32]);
+            tmem_wait_loads();
+            const int key_base = (t_begin + t) * kKeys;
+            float page_max = -CUDART_INF_F;
+            if (key_base + kKeys - 1 <= row_pos && key_base >= row_first) {  // the whole page is visible to this row
+#pragma unroll
+                for (int i = 0; i < kKeys; ++i) page_max = fmaxf(page_max, __uint_as_float(s[i]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < kKeys; ++i) {
+                    const int key = key_base + i;
+                    if (!(key <= row_pos && key >= row_first)) s[i] = __float_as_uint(-CUDART_INF_F);
+                    page_max = fmaxf(page_max, __uint_as_float(s[i]));
+                }
+            }
+            // scores stay raw; the scale (times log2 e) is folded into the exponent: 2^(s*c - m*c)
+            const float new_max = fmaxf(run_max, page_max);
+            // a row that has seen nothing yet keeps -inf; subtract 0 then so that the exponent is -inf, not NaN
+            const float safe_max = new_max == -CUDART_INF_F ? 0.0f : new_max;
+            const float correction = fast_exp2((run_max - safe_max) * scale_log2);
+            const float offset = -safe_max * scale_log2;
+            run_max = new_max;
+            float local = 0.0f;
+            const uint32_t p_row = p_smem + (t & 1) * kPBytes + row * 128;
+#pragma unroll
+            for (int c = 0; c < kKeys / 8; ++c) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    e[i] = fast_exp2(fmaf(__uint_as_float(s[c * 8 + i]), scale_log2, offset));
+                    local += e[i];
+                }
+                // 16-byte piece c of the row goes to piece c ^ (row % 8): the 128-byte swizzle
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c ^ (row & 7)) << 4)),
+                             "r"(pack_bf16(e[0], e[1])), "r"(pack_bf16(e[2], e[3])), "r"(pack_bf16(e[4], e[5])),
+                             "r"(pack_bf16(e[6], e[7]))
+                             : "memory");
+            }
+            run_sum = run_sum * correction + local;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what was just stored
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 8 * (t & 1));
+            if (t > 0) {
+                fold(t - 1, correction);
+                if (!ok) break;
+            }
+        }
+        if (ok) fold(pages - 1, 1.0f);
+        if (ok && row < valid) {
+            const float inv = 1.0f / run_sum;
+            bf16* dst = args.out + (size_t)(q_begin + t0 + row) * args.out_row_stride + (size_t)head * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                float piece[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) piece[j] = o[i + j] * inv;
+                store8(dst + i, piece);
+            }
+        }
+    }
+
+    // every role has left its loop (done, or after a bounded wait gave up): free tensor memory
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+    }
+}
+
+}  // namespace mb
+
+using namespace mb;
+
+MB_EXPORT int mb_prefill_attention_tc_head_dim() { return HD; }
+
+// q: bfloat16 rows (row stride q_row_stride) of total_rows tokens, head h at columns [h * HD, +HD); out likewise.
+// k_pool, v_pool: bfloat16 [pages][kv_heads][64][HD].  block_table: int32 [sequences][max_blocks];
+// cu_q: int32 [sequences + 1]; kv_lens: int32 [sequences] (the new tokens included).
+MB_EXPORT int mb_prefill_attention_tcgen05(const void* q, int q_row_stride, int total_rows, void* out, int out_row_stride,
+                                           const void* k_pool, const void* v_pool, int pool_pages, const int* block_table,
+                                           int max_blocks, const int* cu_q, const int* kv_lens, int sequences, int max_q_len,
+                                           int heads, int kv_heads, int page_size, int window, float scale,
+                                           cudaStream_t stream) {
+    if (sequences <= 0 || max_q_len <= 0) return 0;
+    if (kv_heads <= 0 || heads % kv_heads) return fail("prefill_attention_tcgen05: %d heads are no multiple of %d kv heads", heads, kv_heads);
+    if (page_size != kKeys) return fail("prefill_attention_tcgen05: the cache page must hold %d positions, got %d", kKeys, page_size);
+    if (q_row_stride % 8 || out_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
+        return fail("prefill_attention_tcgen05: query and output rows must start on 16-byte boundaries");
+    if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15)) return fail("prefill_attention_tcgen05: the cache pools must start on 16-byte boundaries");
+    if (sequences > 65535 || heads > 65535) return fail("prefill_attention_tcgen05: grid too large");
+    if ((long long)pool_pages * kv_heads * kKeys > 0x7fffffffLL) return fail("prefill_attention_tcgen05: the cache pool has too many rows for one map");
+    CUtensorMap map_q, map_k, map_v;
+    if (int status = make_map(&map_q, q, total_rows, heads * HD, q_row_stride, kQRows)) return status;
+    if (int status = make_map(&map_k, k_pool, pool_pages * kv_heads * kKeys, HD, HD, kKeys)) return status;
+    if (int status = make_map(&map_v, v_pool, pool_pages * kv_heads * kKeys, HD, HD, kKeys)) return status;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t status = cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (status != cudaSuccess)
+            return fail("prefill_attention_tcgen05: cannot reserve %zu bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(status));
+        configured = true;
+    }
+    AttentionArgs args{(bf16*)out, out_row_stride, block_table, max_blocks, cu_q, kv_lens, heads, kv_heads, window, scale};
+    const dim3 grid((max_q_len + kQRows - 1) / kQRows, heads, sequences);
+    return launch_dependent("prefill_attention_tcgen05", prefill_attention_tcgen05_kernel, grid, dim3(kThreads), kSmemBytes, stream,
+                            true, map_q, map_k, map_v, args);
+}
+
+// 0 when no wait ever gave up; else 1 + (role << 8).
+MB_EXPORT int mb_prefill_attention_tc_status() {
+    int status = 0;
+    if (cudaMemcpyFromSymbol(&status, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    return status;
+}

@@ -20,6 +20,8 @@ LIBRARIES = [
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 48}),
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 64}),
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 128}),
+    ("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": 64}),
+    ("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": 128}),
 ]
 
 

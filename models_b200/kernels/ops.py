@@ -87,6 +87,20 @@ def attention_tc_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> boo
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256 and page_size == 64
 
 
+def prefill_attention_tc(head_dim: int):
+    """The tcgen05 prefill attention, compiled for this head size (64 or 128) at first use."""
+    return load_library("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": int(head_dim)})
+
+
+TCGEN05_ATTENTION_MIN_ROWS = 33  # shorter steps go to the mma.sync kernel, whose blocks take 64 query rows
+
+
+def prefill_attention_tcgen05_takes(q: torch.Tensor, out: torch.Tensor, head_dim: int, max_q_len: int) -> bool:
+    """Head sizes 64 and 128, steps of more than a few tokens, rows that TMA and 16-byte stores can address."""
+    return (head_dim in (64, 128) and max_q_len >= TCGEN05_ATTENTION_MIN_ROWS and q.stride(0) % 8 == 0
+            and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
 def gemm32():
     return load_library("mb_gemm_f32", ["gemm_f32.cu"])
 
@@ -271,9 +285,22 @@ def decode_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
 
 def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                       block_table: torch.Tensor, cu_q: torch.Tensor, kv_lens: torch.Tensor, max_q_len: int, heads: int,
-                      kv_heads: int, head_dim: int, window: Optional[int], scale: float) -> None:
-    """Any number of new tokens per sequence; their keys and values are already in the cache."""
+                      kv_heads: int, head_dim: int, window: Optional[int], scale: float, kernel: Optional[str] = None) -> None:
+    """Any number of new tokens per sequence; their keys and values are already in the cache.
+    `kernel`: None picks the tcgen05 kernel where it applies, else the mma.sync one; "tcgen05" or
+    "mma" asks for one of them."""
     _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, head_dim)
+    if kernel not in (None, "tcgen05", "mma"):
+        raise KernelError(f"prefill_attention: unknown kernel {kernel!r}")
+    if kernel == "tcgen05" or (kernel is None and prefill_attention_tcgen05_takes(q, out, head_dim, max_q_len)):
+        if head_dim not in (64, 128):
+            raise KernelError(f"the tcgen05 prefill attention is built for head sizes 64 and 128, got {head_dim}")
+        lib = prefill_attention_tc(head_dim)
+        _run(lib, lib.mb_prefill_attention_tcgen05(
+            _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pool), _p(v_pool), k_pool.shape[0],
+            _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens), kv_lens.numel(), max_q_len, heads, kv_heads,
+            k_pool.shape[2], window or 0, ctypes.c_float(scale), _stream()))
+        return
     lib = attention_tc(head_dim)
     _run(lib, lib.mb_prefill_attention(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_pool), _p(v_pool),
                                        _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_lens), kv_lens.numel(),
@@ -487,6 +514,11 @@ def tensor_core_gemm(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_
     if a.shape[0] <= WIDE_ROWS:
         return wide_gemm(a, weight, epilogue, out)
     return gemm_tcgen05(a, weight, epilogue, out)
+
+
+def prefill_attention_tcgen05_status(head_dim: int) -> int:
+    """0 unless a bounded wait inside the tcgen05 prefill attention ever gave up (1 + (role << 8))."""
+    return int(prefill_attention_tc(head_dim).mb_prefill_attention_tc_status())
 
 
 def gemm_tcgen05_status() -> int:

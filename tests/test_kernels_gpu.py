@@ -233,14 +233,77 @@ def test_tensor_core_attention(cuda_device, heads, kv_heads, head_dim, window):
         common = (k_pool.cuda(), v_pool.cuda(), block_table.cuda(), cu_q.cuda(), torch.tensor(kv_lens, dtype=torch.int32).cuda())
         qd = q.cuda()[:, : heads * head_dim]
         if max(q_lens) > 1:
-            out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
-            ops.prefill_attention(qd, out, *common, max(q_lens), heads, kv_heads, head_dim, window, scale)
-            close(out, expected, dtype)
+            for kernel in ("mma", "tcgen05") if head_dim in (64, 128) else ("mma",):
+                out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
+                ops.prefill_attention(qd, out, *common, max(q_lens), heads, kv_heads, head_dim, window, scale, kernel=kernel)
+                close(out, expected, dtype)
         else:
             for splits, use_scratch in ((1, False), (2, False), (4, False), (8, False), (3, False), (16, False), (4, True)):
                 out = torch.zeros(T, heads * head_dim, dtype=dtype, device="cuda")
                 ops.decode_attention(qd, out, *common, heads, kv_heads, head_dim, window, scale, splits, use_scratch)
                 close(out, expected, dtype)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(8, 2, 64, None), (3, 3, 128, None), (4, 1, 64, 100),
+                                                            (2, 1, 128, 257), (12, 4, 64, 64)])
+def test_tcgen05_prefill_attention(cuda_device, heads, kv_heads, head_dim, window):
+    """The tcgen05 kernel alone at sizes that turn its rings over several times: many pages per
+    block, several 128-row blocks per sequence, new tokens on top of cached ones, a sequence of one
+    token beside long ones, pages scattered over the pool."""
+    from models_b200.kernels import ops
+
+    dtype, page = torch.bfloat16, 64
+    q_lens = [300, 1, 129, 700, 64, 128]
+    kv_lens = [300, 50, 500, 700, 449, 128]
+    pages_needed = [-(-n // page) for n in kv_lens]
+    total_pages = sum(pages_needed) + 3
+    k_pool, v_pool = _pools(total_pages, kv_heads, page, head_dim, dtype, 16)
+    order = torch.randperm(total_pages - 1, generator=torch.Generator().manual_seed(17)) + 1
+    block_table = torch.zeros(len(q_lens), max(pages_needed) + 1, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages_needed):
+        block_table[b, :n] = order[at:at + n].int()
+        at += n
+    T = sum(q_lens)
+    q = torch.randn(T, heads * head_dim + 24, generator=torch.Generator().manual_seed(18)).to(dtype)
+    cu_q = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32)
+    scale = 1.3 / math.sqrt(head_dim)
+    expected = _reference_attention(q.float()[:, : heads * head_dim], k_pool, v_pool, block_table, q_lens, kv_lens,
+                                    heads, kv_heads, head_dim, window, scale)
+    out = torch.full((T, heads * head_dim), 7.0, dtype=dtype, device="cuda")
+    ops.prefill_attention(q.cuda()[:, : heads * head_dim], out, k_pool.cuda(), v_pool.cuda(), block_table.cuda(), cu_q.cuda(),
+                          torch.tensor(kv_lens, dtype=torch.int32).cuda(), max(q_lens), heads, kv_heads, head_dim, window,
+                          scale, kernel="tcgen05")
+    torch.cuda.synchronize()
+    assert ops.prefill_attention_tcgen05_status(head_dim) == 0
+    close(out, expected, dtype)
+
+
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_tcgen05_prefill_attention_finds_one_far_key(cuda_device, head_dim):
+    """One key among 600 stands out.  Every query row at or after it must return that key's value
+    row; every row before it sees equal scores and must return the mean of the values it can see."""
+    from models_b200.kernels import ops
+
+    heads, kv_heads, page, total, new = 2, 1, 64, 600, 250
+    for far in (0, 349, 350, 383, 384, 511, 599):
+        k_pool = torch.zeros(11, kv_heads, page, head_dim)
+        v_pool = torch.randn(11, kv_heads, page, head_dim, generator=torch.Generator().manual_seed(far))
+        table = torch.tensor([[5, 2, 10, 1, 3, 9, 7, 4, 8, 6]], dtype=torch.int32)
+        k_pool[table[0, far // page], 0, far % page, :] = 10.0
+        q = torch.ones(new, heads * head_dim).bfloat16()
+        out = torch.zeros(new, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+        ops.prefill_attention(q.cuda(), out, k_pool.bfloat16().cuda(), v_pool.bfloat16().cuda(), table.cuda(),
+                              torch.tensor([0, new], dtype=torch.int32).cuda(), torch.tensor([total], dtype=torch.int32).cuda(),
+                              new, heads, kv_heads, head_dim, None, 1.0, kernel="tcgen05")
+        values = v_pool.bfloat16().float()
+        flat = torch.stack([values[table[0, p // page], 0, p % page, :] for p in range(total)])  # [total, hd]
+        for row in range(new):
+            pos = total - new + row
+            want = flat[far] if pos >= far else flat[: pos + 1].mean(dim=0)
+            for h in range(heads):
+                got = out[row, h * head_dim:(h + 1) * head_dim].float().cpu()
+                assert torch.allclose(got, want, atol=2e-2), (far, row, h, float((got - want).abs().max()))
 
 
 def test_window_edge_and_stale_pages_do_not_leak(cuda_device):
