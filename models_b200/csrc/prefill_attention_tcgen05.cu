@@ -8,15 +8,18 @@
 //     ([64 keys][head size], contiguous in the pool) into a ring of shared-memory stages, 128-byte
 //     swizzle.
 //   * warp 1, one thread: tcgen05.mma.  S = Q . K^T (M = 128, N = 64 keys, K = head size) into one of
-//     two score buffers in tensor memory, then O_page = P . V (M = 128, N = head size, K = 64 keys,
-//     V read as an MN-major operand) into one of two output buffers.  The scores of page t + 1 are
-//     issued before the softmax of page t has finished, so the tensor cores and the softmax overlap.
+//     two score buffers in tensor memory, then O += P . V (M = 128, N = head size, K = 64 keys,
+//     V read as an MN-major operand) into the output accumulator, which stays in tensor memory over
+//     all pages.  The scores of page t + 1 are issued before the softmax of page t has finished, so
+//     the tensor cores and the softmax overlap.
 //   * warps 2..5, one thread per query row: the running softmax.  A thread reads its row of scores
 //     with tcgen05.ld, masks, takes the maximum, exponentiates (special-function exp2 with the scale
-//     folded into the exponent), writes the probabilities as bfloat16 into shared memory in the
-//     swizzled layout the next product expects, and folds the finished O_page of the page before
-//     into its float accumulator (O = (O + O_page) * correction).  No shuffles: a row never leaves
-//     its thread.
+//     folded into the exponent, two floats per instruction around it) and writes the probabilities
+//     as bfloat16 pairs over its scores in tensor memory (tcgen05.st), from where the next product
+//     takes them as its A operand: they never pass through shared memory.  The base of
+//     the exponents follows the running maximum lazily; only when it moves is the accumulator read
+//     back, rescaled and stored again (tcgen05.ld / tcgen05.st).  At the end the thread divides its
+//     row by the sum and stores it.  No shuffles: a row never leaves its thread.
 //
 // Formula: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1543-1670 (kvHead = head /
 // group; dot first, then scale; only positions <= the query's are read; with a window of n only the n
@@ -48,13 +51,18 @@ constexpr int kQBytes = kBoxes * kQBoxBytes;
 constexpr int kKVBoxBytes = kKeys * 128;  // [64 keys][64 columns]
 constexpr int kKVTileBytes = kBoxes * kKVBoxBytes;
 constexpr int kStageBytes = 2 * kKVTileBytes;  // keys, then values
-constexpr int kStages = HD == 64 ? 3 : 2;
-constexpr int kPBytes = kQRows * kKeys * 2;    // probabilities of one page, bfloat16
+constexpr int kStages = HD == 64 ? 4 : 2;
+constexpr int kPColumns = kKeys / 2;           // probabilities of one page: bfloat16 pairs in 32-bit columns
 constexpr int kThreads = 192;
 constexpr int kScoreColumns = 64;
-constexpr int kTmemUsed = 2 * kScoreColumns + 2 * HD;
-constexpr int kTmemColumns = kTmemUsed <= 256 ? 256 : 512;
-constexpr size_t kSmemBytes = (size_t)kQBytes + (size_t)kStages * kStageBytes + 2 * (size_t)kPBytes + 1024;
+constexpr int kTmemColumns = 256;  // two score buffers and the output: 2 * 64 + HD
+static_assert(2 * kScoreColumns + HD <= kTmemColumns, "tensor memory budget");
+#ifndef MB_IDLE_NS
+#define MB_IDLE_NS 100
+#endif
+constexpr unsigned kIdleNanoseconds = MB_IDLE_NS;
+constexpr float kSlack = 8.0f;     // how far (in the exponent) the maximum may run ahead of the base
+constexpr size_t kSmemBytes = (size_t)kQBytes + (size_t)kStages * kStageBytes + 1024;
 
 constexpr uint32_t kScoreInstruction = instruction_descriptor(kQRows, kKeys);
 constexpr uint32_t kOutputInstruction = instruction_descriptor(kQRows, HD) | (1u << 16);  // B is MN-major
@@ -83,6 +91,37 @@ __device__ __forceinline__ void tmem_load_32_raw(uint32_t taddr, uint32_t* r) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store_32_raw(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_stores() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// two floats in one 64-bit register, and arithmetic on both at once
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -92,6 +131,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// The wait of a single-thread role: it sleeps between polls, so that it does not take issue slots
+// from the softmax warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, int role) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(kIdleNanoseconds);
+        if (clock64() - start > kWaitCycles) {
+            atomicCAS(&g_gemm_status, 0, 1 + (role << 8));
+            return false;
+        }
+    }
+    return true;
+}
+
+// tcgen05.mma with the 128 x 16 A operand in tensor memory (lane = row, two bfloat16 per 32-bit column)
+__device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t instruction, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(instruction), "r"(accumulate)
+        : "memory");
 }
 
 struct AttentionArgs {
@@ -107,7 +171,7 @@ struct AttentionArgs {
 
 // roles in the status record: 1 TMA (stage free), 2 MMA (queries), 3 MMA (keys), 4 MMA (probabilities),
 // 5 softmax (scores), 6 softmax (output of a page)
-__global__ void __launch_bounds__(kThreads, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const AttentionArgs args) {
     const int seq = blockIdx.z, head = blockIdx.y;
@@ -123,7 +187,6 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_smem = smem_u32(smem);
     const uint32_t stage_smem = q_smem + kQBytes;
-    const uint32_t p_smem = stage_smem + kStages * kStageBytes;
     const uint32_t kv_full = smem_u32(&barriers[0]), kv_empty = smem_u32(&barriers[kStages]);
     const uint32_t q_full = smem_u32(&barriers[2 * kStages]);
     const uint32_t s_full = smem_u32(&barriers[2 * kStages + 1]);  // two
@@ -161,7 +224,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    const uint32_t tmem_scores = tmem_base, tmem_output = tmem_base + 2 * kScoreColumns;
+    const uint32_t tmem_scores = tmem_base, tmem_output = tmem_base + 2 * kScoreColumns;  // output: one buffer, all pages
     grid_launch_dependents();
     grid_dependency_wait();  // queries, and the newest keys and values, come from the kernel before this one
 
@@ -174,7 +237,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int* table = args.block_table + (size_t)seq * args.max_blocks;
             for (int t = 0; t < pages; ++t) {
                 const int stage = t % kStages;
-                if (!mbar_wait(kv_empty + 8 * stage, ((t / kStages) & 1) ^ 1, 1)) break;
+                if (!mbar_wait_idle(kv_empty + 8 * stage, ((t / kStages) & 1) ^ 1, 1)) break;
                 const int row = (table[t_begin + t] * args.kv_heads + kv_head) * kKeys;
                 const uint32_t dst = stage_smem + stage * kStageBytes;
                 mbar_expect_tx(kv_full + 8 * stage, kStageBytes);
@@ -198,25 +261,25 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 }
                 umma_commit(s_full + 8 * (t & 1));
             };
-            bool ok = mbar_wait(q_full, 0, 2) && mbar_wait(kv_full, 0, 3);
+            bool ok = mbar_wait_idle(q_full, 0, 2) && mbar_wait_idle(kv_full, 0, 3);
             if (ok) {
                 tcgen05_fence_after();
                 issue_scores(0);
             }
             for (int t = 0; t < pages && ok; ++t) {
                 if (t + 1 < pages) {
-                    if (!(ok = mbar_wait(kv_full + 8 * ((t + 1) % kStages), ((t + 1) / kStages) & 1, 3))) break;
+                    if (!(ok = mbar_wait_idle(kv_full + 8 * ((t + 1) % kStages), ((t + 1) / kStages) & 1, 3))) break;
                     tcgen05_fence_after();
                     issue_scores(t + 1);
                 }
-                if (!(ok = mbar_wait(p_full + 8 * (t & 1), (t >> 1) & 1, 4))) break;
+                if (!(ok = mbar_wait_idle(p_full + 8 * (t & 1), (t >> 1) & 1, 4))) break;
                 tcgen05_fence_after();
                 const uint32_t v_tile = stage_smem + (t % kStages) * kStageBytes + kKVTileBytes;
-                const uint32_t p_tile = p_smem + (t & 1) * kPBytes;
+                const uint32_t p_tile = tmem_scores + (t & 1) * kScoreColumns;  // the probabilities lie over the scores they came from
 #pragma unroll
-                for (int j = 0; j < kKeys / 16; ++j)  // 16 keys per instruction: 32 bytes along a row of P, 16 rows of V
-                    umma(tmem_output + (t & 1) * HD, umma_descriptor(p_tile) + 2 * j,
-                         umma_descriptor_mn(v_tile + j * 16 * 128, kKVBoxBytes), kOutputInstruction, j > 0 ? 1u : 0u);
+                for (int j = 0; j < kKeys / 16; ++j)  // 16 keys per instruction: 8 columns of P, 16 rows of V
+                    umma_a_tmem(tmem_output, p_tile + 8 * j, umma_descriptor_mn(v_tile + j * 16 * 128, kKVBoxBytes),
+                                kOutputInstruction, (t > 0 || j > 0) ? 1u : 0u);
                 umma_commit(o_full + 8 * (t & 1));
                 umma_commit(kv_empty + 8 * (t % kStages));
             }
@@ -229,25 +292,14 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int row_pos = row < valid ? pos0 + row : -1;  // a row beyond the sequence sees nothing
         const int row_first = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
         const float scale_log2 = args.scale * 1.4426950408889634f;
-        float o[HD];
-#pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.0f;
-        float run_max = -CUDART_INF_F, run_sum = 0.0f;
+        const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+        // `base` is the score the exponents are taken against.  It follows the running maximum lazily:
+        // it moves (and the output so far is rescaled) only when the maximum has grown by more than
+        // kSlack in the exponent, so most pages cost no pass over the output.  Until then the
+        // probabilities of later pages may exceed 1, by at most 2^kSlack; sum and output share the base,
+        // so their quotient is the same.
+        float base = -CUDART_INF_F, run_sum = 0.0f;
         bool ok = true;
-        auto fold = [&](int t, float factor) {  // o = (o + O_page(t)) * factor
-            ok = mbar_wait(o_full + 8 * (t & 1), (t >> 1) & 1, 6);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) return;
-            tcgen05_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t r[32];
-                tmem_load_32_raw(tmem_output + (t & 1) * HD + lane_base + c, r);
-                tmem_wait_loads();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c + i] = (o[c + i] + __uint_as_float(r[i])) * factor;
-            }
-        };
         for (int t = 0; t < pages; ++t) {
             ok = mbar_wait(s_full + 8 * (t & 1), (t >> 1) & 1, 5);
             ok = __all_sync(0xffffffffu, ok);
@@ -258,61 +310,103 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tmem_load_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base + 32, &s[32]);
             tmem_wait_loads();
             const int key_base = (t_begin + t) * kKeys;
-            float page_max = -CUDART_INF_F;
-            if (key_base + kKeys - 1 <= row_pos && key_base >= row_first) {  // the whole page is visible to this row
-#pragma unroll
-                for (int i = 0; i < kKeys; ++i) page_max = fmaxf(page_max, __uint_as_float(s[i]));
-            } else {
+            if (!(key_base + kKeys - 1 <= row_pos && key_base >= row_first)) {  // not the whole page is visible to this row
 #pragma unroll
                 for (int i = 0; i < kKeys; ++i) {
                     const int key = key_base + i;
                     if (!(key <= row_pos && key >= row_first)) s[i] = __float_as_uint(-CUDART_INF_F);
-                    page_max = fmaxf(page_max, __uint_as_float(s[i]));
                 }
             }
-            // scores stay raw; the scale (times log2 e) is folded into the exponent: 2^(s*c - m*c)
-            const float new_max = fmaxf(run_max, page_max);
+            float part[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) part[i] = __uint_as_float(s[i]);
+#pragma unroll
+            for (int i = 8; i < kKeys; ++i) part[i & 7] = fmaxf(part[i & 7], __uint_as_float(s[i]));
+            const float page_max = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])),
+                                         fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
+            // scores stay raw; the scale (times log2 e) is folded into the exponent: 2^(s*c - base*c)
+            float factor = 1.0f;
+            if (base == -CUDART_INF_F) {
+                base = page_max;  // nothing accumulated so far (or still nothing visible)
+            } else if ((page_max - base) * scale_log2 > kSlack) {
+                factor = fast_exp2((base - page_max) * scale_log2);
+                base = page_max;
+            }
+            if (__any_sync(0xffffffffu, factor != 1.0f)) {
+                // the output so far moves to the new base; the product of the page before must have landed
+                ok = mbar_wait(o_full + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, 6);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+                run_sum *= factor;
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t r[32];
+                    tmem_load_32_raw(tmem_output + lane_base + c, r);
+                    tmem_wait_loads();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+                    tmem_store_32_raw(tmem_output + lane_base + c, r);
+                }
+                tmem_wait_stores();
+            }
             // a row that has seen nothing yet keeps -inf; subtract 0 then so that the exponent is -inf, not NaN
-            const float safe_max = new_max == -CUDART_INF_F ? 0.0f : new_max;
-            const float correction = fast_exp2((run_max - safe_max) * scale_log2);
-            const float offset = -safe_max * scale_log2;
-            run_max = new_max;
-            float local = 0.0f;
-            const uint32_t p_row = p_smem + (t & 1) * kPBytes + row * 128;
+            const float offset = base == -CUDART_INF_F ? 0.0f : -base * scale_log2;
+            const uint64_t offset2 = pack_f32x2(offset, offset);
+            uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};  // eight partial sums, two per register pair
+            uint32_t packed[kPColumns];
 #pragma unroll
             for (int c = 0; c < kKeys / 8; ++c) {
-                float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    e[i] = fast_exp2(fmaf(__uint_as_float(s[c * 8 + i]), scale_log2, offset));
-                    local += e[i];
+                for (int i = 0; i < 4; ++i) {
+                    float x0, x1;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c * 8 + 2 * i]), __uint_as_float(s[c * 8 + 2 * i + 1])),
+                                           scale2, offset2), x0, x1);
+#if defined(MB_PROBE_NO_EXP)
+                    const float e0 = x0 * 1e-3f, e1 = x1 * 1e-3f;
+#elif defined(MB_PROBE_HALF_EXP)
+                    const float e0 = fast_exp2(x0), e1 = x1 * 1e-3f;
+#else
+                    const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+#endif
+                    sums[i] = add_f32x2(sums[i], pack_f32x2(e0, e1));
+                    packed[c * 4 + i] = pack_bf16(e0, e1);
                 }
-                // 16-byte piece c of the row goes to piece c ^ (row % 8): the 128-byte swizzle
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c ^ (row & 7)) << 4)),
-                             "r"(pack_bf16(e[0], e[1])), "r"(pack_bf16(e[2], e[3])), "r"(pack_bf16(e[4], e[5])),
-                             "r"(pack_bf16(e[6], e[7]))
-                             : "memory");
             }
-            run_sum = run_sum * correction + local;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads what was just stored
+            // the row's probabilities go where its scores were: the next product takes them from tensor memory
+            tmem_store_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base, packed);
+            tmem_wait_stores();
+            {
+                float lo, hi;
+                unpack_f32x2(add_f32x2(add_f32x2(sums[0], sums[1]), add_f32x2(sums[2], sums[3])), lo, hi);
+                run_sum += lo + hi;
+            }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * (t & 1));
-            if (t > 0) {
-                fold(t - 1, correction);
-                if (!ok) break;
-            }
         }
-        if (ok) fold(pages - 1, 1.0f);
-        if (ok && row < valid) {
+        if (ok) {
+            ok = mbar_wait(o_full + 8 * ((pages - 1) & 1), ((pages - 1) >> 1) & 1, 6);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tcgen05_fence_after();
             const float inv = 1.0f / run_sum;
             bf16* dst = args.out + (size_t)(q_begin + t0 + row) * args.out_row_stride + (size_t)head * HD;
 #pragma unroll
-            for (int i = 0; i < HD; i += 8) {
-                float piece[8];
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t r[32];
+                tmem_load_32_raw(tmem_output + lane_base + c, r);
+                tmem_wait_loads();
+                if (row < valid) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) piece[j] = o[i + j] * inv;
-                store8(dst + i, piece);
+                    for (int i = 0; i < 32; i += 8) {
+                        float piece[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) piece[j] = __uint_as_float(r[i + j]) * inv;
+                        store8(dst + c + i, piece);
+                    }
+                }
             }
         }
     }
