@@ -5,8 +5,8 @@
 // A block takes 128 consecutive query tokens of one head and walks the visible cache pages (64 keys
 // each).  Its six warps have three roles:
 //   * warp 0, one thread: TMA.  The query tile once, then per page the key tile and the value tile
-//     ([64 keys][head size], contiguous in the pool) into a ring of shared-memory stages, 128-byte
-//     swizzle.
+//     ([64 keys][head size], contiguous in the pool) into two rings of shared-memory stages (keys,
+//     values), 128-byte swizzle.
 //   * warp 1, one thread: tcgen05.mma.  S = Q . K^T (M = 128, N = 64 keys, K = head size) into one of
 //     two score buffers in tensor memory, then O += P . V (M = 128, N = head size, K = 64 keys,
 //     V read as an MN-major operand) into the output accumulator, which stays in tensor memory over
@@ -50,19 +50,14 @@ constexpr int kQBoxBytes = kQRows * 128;  // [128 rows][64 columns]
 constexpr int kQBytes = kBoxes * kQBoxBytes;
 constexpr int kKVBoxBytes = kKeys * 128;  // [64 keys][64 columns]
 constexpr int kKVTileBytes = kBoxes * kKVBoxBytes;
-constexpr int kStageBytes = 2 * kKVTileBytes;  // keys, then values
-constexpr int kStages = HD == 64 ? 4 : 2;
+constexpr int kStages = HD == 64 ? 3 : 2;      // of the key ring and of the value ring, each
 constexpr int kPColumns = kKeys / 2;           // probabilities of one page: bfloat16 pairs in 32-bit columns
 constexpr int kThreads = 192;
 constexpr int kScoreColumns = 64;
 constexpr int kTmemColumns = 256;  // two score buffers and the output: 2 * 64 + HD
 static_assert(2 * kScoreColumns + HD <= kTmemColumns, "tensor memory budget");
-#ifndef MB_IDLE_NS
-#define MB_IDLE_NS 100
-#endif
-constexpr unsigned kIdleNanoseconds = MB_IDLE_NS;
 constexpr float kSlack = 8.0f;     // how far (in the exponent) the maximum may run ahead of the base
-constexpr size_t kSmemBytes = (size_t)kQBytes + (size_t)kStages * kStageBytes + 1024;
+constexpr size_t kSmemBytes = (size_t)kQBytes + 2 * (size_t)kStages * kKVTileBytes + 1024;
 
 constexpr uint32_t kScoreInstruction = instruction_descriptor(kQRows, kKeys);
 constexpr uint32_t kOutputInstruction = instruction_descriptor(kQRows, HD) | (1u << 16);  // B is MN-major
@@ -133,21 +128,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// The wait of a single-thread role: it sleeps between polls, so that it does not take issue slots
-// from the softmax warps that share its scheduler.
-__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, int role) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        __nanosleep(kIdleNanoseconds);
-        if (clock64() - start > kWaitCycles) {
-            atomicCAS(&g_gemm_status, 0, 1 + (role << 8));
-            return false;
-        }
-    }
-    return true;
-}
-
 // tcgen05.mma with the 128 x 16 A operand in tensor memory (lane = row, two bfloat16 per 32-bit column)
 __device__ __forceinline__ void umma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t instruction, uint32_t accumulate) {
     asm volatile(
@@ -174,24 +154,29 @@ struct AttentionArgs {
 __global__ void __launch_bounds__(kThreads, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const AttentionArgs args) {
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // blocks start in the order of their index: all heads of the query tile with the most keys first, then
+    // the next tile, so that the long blocks are under way early and the short ones fill the end
+    const int seq = blockIdx.z, head = blockIdx.x;
     const int q_begin = args.cu_q[seq], q_len = args.cu_q[seq + 1] - q_begin;  // written before the step, by a copy
-    const int q_tile = gridDim.x - 1 - blockIdx.x;  // the tiles with the most keys start first
+    const int q_tile = gridDim.y - 1 - blockIdx.y;
     const int t0 = q_tile * kQRows;
     if (t0 >= q_len) return;
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t barriers[2 * kStages + 7];
+    __shared__ __align__(8) uint64_t barriers[4 * kStages + 7];
     __shared__ uint32_t tmem_base_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t q_smem = smem_u32(smem);
-    const uint32_t stage_smem = q_smem + kQBytes;
-    const uint32_t kv_full = smem_u32(&barriers[0]), kv_empty = smem_u32(&barriers[kStages]);
-    const uint32_t q_full = smem_u32(&barriers[2 * kStages]);
-    const uint32_t s_full = smem_u32(&barriers[2 * kStages + 1]);  // two
-    const uint32_t p_full = smem_u32(&barriers[2 * kStages + 3]);  // two
-    const uint32_t o_full = smem_u32(&barriers[2 * kStages + 5]);  // two
+    // keys and values have rings of their own: a key tile is free as soon as its scores are computed,
+    // a value tile only after the softmax of its page, and the next keys must not wait for that
+    const uint32_t k_smem = q_smem + kQBytes, v_smem = k_smem + kStages * kKVTileBytes;
+    const uint32_t k_full = smem_u32(&barriers[0]), k_empty = smem_u32(&barriers[kStages]);
+    const uint32_t v_full = smem_u32(&barriers[2 * kStages]), v_empty = smem_u32(&barriers[3 * kStages]);
+    const uint32_t q_full = smem_u32(&barriers[4 * kStages]);
+    const uint32_t s_full = smem_u32(&barriers[4 * kStages + 1]);  // two
+    const uint32_t p_full = smem_u32(&barriers[4 * kStages + 3]);  // two
+    const uint32_t o_full = smem_u32(&barriers[4 * kStages + 5]);  // two
 
     const int valid = min(kQRows, q_len - t0);
     const int kv_len = args.kv_lens[seq];
@@ -205,8 +190,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(kv_full + 8 * s, 1);
-            mbar_init(kv_empty + 8 * s, 1);
+            mbar_init(k_full + 8 * s, 1);
+            mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1);
+            mbar_init(v_empty + 8 * s, 1);
         }
         mbar_init(q_full, 1);
         for (int b = 0; b < 2; ++b) {
@@ -237,22 +224,25 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int* table = args.block_table + (size_t)seq * args.max_blocks;
             for (int t = 0; t < pages; ++t) {
                 const int stage = t % kStages;
-                if (!mbar_wait_idle(kv_empty + 8 * stage, ((t / kStages) & 1) ^ 1, 1)) break;
+                const uint32_t free_parity = ((t / kStages) & 1) ^ 1;
                 const int row = (table[t_begin + t] * args.kv_heads + kv_head) * kKeys;
-                const uint32_t dst = stage_smem + stage * kStageBytes;
-                mbar_expect_tx(kv_full + 8 * stage, kStageBytes);
+                if (!mbar_wait(k_empty + 8 * stage, free_parity, 1)) break;
+                mbar_expect_tx(k_full + 8 * stage, kKVTileBytes);
 #pragma unroll
-                for (int b = 0; b < kBoxes; ++b) {
-                    tma_load_2d(dst + b * kKVBoxBytes, &map_k, b * 64, row, kv_full + 8 * stage);
-                    tma_load_2d(dst + kKVTileBytes + b * kKVBoxBytes, &map_v, b * 64, row, kv_full + 8 * stage);
-                }
+                for (int b = 0; b < kBoxes; ++b)
+                    tma_load_2d(k_smem + stage * kKVTileBytes + b * kKVBoxBytes, &map_k, b * 64, row, k_full + 8 * stage);
+                if (!mbar_wait(v_empty + 8 * stage, free_parity, 1)) break;
+                mbar_expect_tx(v_full + 8 * stage, kKVTileBytes);
+#pragma unroll
+                for (int b = 0; b < kBoxes; ++b)
+                    tma_load_2d(v_smem + stage * kKVTileBytes + b * kKVBoxBytes, &map_v, b * 64, row, v_full + 8 * stage);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             auto issue_scores = [&](int t) {  // S[t % 2] = Q . K(t)^T
-                const uint32_t k_tile = stage_smem + (t % kStages) * kStageBytes;
+                const uint32_t k_tile = k_smem + (t % kStages) * kKVTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     const uint64_t a_desc = umma_descriptor(q_smem + (ks / 4) * kQBoxBytes) + 2 * (ks % 4);
@@ -260,28 +250,30 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     umma(tmem_scores + (t & 1) * kScoreColumns, a_desc, b_desc, kScoreInstruction, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(s_full + 8 * (t & 1));
+                umma_commit(k_empty + 8 * (t % kStages));  // the key tile is free once these products have read it
             };
-            bool ok = mbar_wait_idle(q_full, 0, 2) && mbar_wait_idle(kv_full, 0, 3);
+            bool ok = mbar_wait(q_full, 0, 2) && mbar_wait(k_full, 0, 3);
             if (ok) {
                 tcgen05_fence_after();
                 issue_scores(0);
             }
             for (int t = 0; t < pages && ok; ++t) {
                 if (t + 1 < pages) {
-                    if (!(ok = mbar_wait_idle(kv_full + 8 * ((t + 1) % kStages), ((t + 1) / kStages) & 1, 3))) break;
+                    if (!(ok = mbar_wait(k_full + 8 * ((t + 1) % kStages), ((t + 1) / kStages) & 1, 3))) break;
                     tcgen05_fence_after();
                     issue_scores(t + 1);
                 }
-                if (!(ok = mbar_wait_idle(p_full + 8 * (t & 1), (t >> 1) & 1, 4))) break;
+                if (!(ok = mbar_wait(p_full + 8 * (t & 1), (t >> 1) & 1, 4))) break;
+                if (!(ok = mbar_wait(v_full + 8 * (t % kStages), (t / kStages) & 1, 3))) break;
                 tcgen05_fence_after();
-                const uint32_t v_tile = stage_smem + (t % kStages) * kStageBytes + kKVTileBytes;
+                const uint32_t v_tile = v_smem + (t % kStages) * kKVTileBytes;
                 const uint32_t p_tile = tmem_scores + (t & 1) * kScoreColumns;  // the probabilities lie over the scores they came from
 #pragma unroll
                 for (int j = 0; j < kKeys / 16; ++j)  // 16 keys per instruction: 8 columns of P, 16 rows of V
                     umma_a_tmem(tmem_output, p_tile + 8 * j, umma_descriptor_mn(v_tile + j * 16 * 128, kKVBoxBytes),
                                 kOutputInstruction, (t > 0 || j > 0) ? 1u : 0u);
                 umma_commit(o_full + 8 * (t & 1));
-                umma_commit(kv_empty + 8 * (t % kStages));
+                umma_commit(v_empty + 8 * (t % kStages));
             }
         }
     } else {
@@ -362,13 +354,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     float x0, x1;
                     unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c * 8 + 2 * i]), __uint_as_float(s[c * 8 + 2 * i + 1])),
                                            scale2, offset2), x0, x1);
-#if defined(MB_PROBE_NO_EXP)
-                    const float e0 = x0 * 1e-3f, e1 = x1 * 1e-3f;
-#elif defined(MB_PROBE_HALF_EXP)
-                    const float e0 = fast_exp2(x0), e1 = x1 * 1e-3f;
-#else
                     const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-#endif
                     sums[i] = add_f32x2(sums[i], pack_f32x2(e0, e1));
                     packed[c * 4 + i] = pack_bf16(e0, e1);
                 }
@@ -440,7 +426,7 @@ MB_EXPORT int mb_prefill_attention_tcgen05(const void* q, int q_row_stride, int 
     if (q_row_stride % 8 || out_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
         return fail("prefill_attention_tcgen05: query and output rows must start on 16-byte boundaries");
     if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15)) return fail("prefill_attention_tcgen05: the cache pools must start on 16-byte boundaries");
-    if (sequences > 65535 || heads > 65535) return fail("prefill_attention_tcgen05: grid too large");
+    if (sequences > 65535 || (max_q_len + kQRows - 1) / kQRows > 65535) return fail("prefill_attention_tcgen05: grid too large");
     if ((long long)pool_pages * kv_heads * kKeys > 0x7fffffffLL) return fail("prefill_attention_tcgen05: the cache pool has too many rows for one map");
     CUtensorMap map_q, map_k, map_v;
     if (int status = make_map(&map_q, q, total_rows, heads * HD, q_row_stride, kQRows)) return status;
@@ -454,7 +440,7 @@ MB_EXPORT int mb_prefill_attention_tcgen05(const void* q, int q_row_stride, int 
         configured = true;
     }
     AttentionArgs args{(bf16*)out, out_row_stride, block_table, max_blocks, cu_q, kv_lens, heads, kv_heads, window, scale};
-    const dim3 grid((max_q_len + kQRows - 1) / kQRows, heads, sequences);
+    const dim3 grid(heads, (max_q_len + kQRows - 1) / kQRows, sequences);
     return launch_dependent("prefill_attention_tcgen05", prefill_attention_tcgen05_kernel, grid, dim3(kThreads), kSmemBytes, stream,
                             true, map_q, map_k, map_v, args);
 }

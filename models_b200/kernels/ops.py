@@ -89,13 +89,7 @@ def attention_tc_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> boo
 
 def prefill_attention_tc(head_dim: int):
     """The tcgen05 prefill attention, compiled for this head size (64 or 128) at first use."""
-    return load_library("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"],
-                        {"MB_HEAD_DIM": int(head_dim), **_attention_defines})
-
-
-# tuning knob for experiments: MODELS_B200_ATTENTION="IDLE_NS=200" rebuilds the tcgen05 attention with other constants
-_attention_defines = {"MB_" + k: int(v) for k, v in
-                      (item.split("=") for item in os.environ.get("MODELS_B200_ATTENTION", "").split(",") if item)}
+    return load_library("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": int(head_dim)})
 
 
 TCGEN05_ATTENTION_MIN_ROWS = 33  # shorter steps go to the mma.sync kernel, whose blocks take 64 query rows
