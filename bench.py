@@ -72,14 +72,21 @@ class ClockSampler:
     def __init__(self):
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.process = None
+        self.skip = 0
 
     def start(self):
         try:
             self.process = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.process = None
+            return
+        # the tool takes a moment to come up; the timed region starts once it is sampling
+        deadline = time.perf_counter() + 3.0
+        while time.perf_counter() < deadline and os.path.getsize(self.file.name) == 0:
+            time.sleep(0.02)
+        self.skip = os.path.getsize(self.file.name)  # what it printed before the timed region
 
     def stop(self):
         if self.process is not None:
@@ -89,7 +96,7 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.process.kill()
         self.file.flush()
-        self.file.seek(0)
+        self.file.seek(self.skip)
         clocks, max_clock, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.file.read().splitlines():
@@ -243,7 +250,7 @@ def device_prefill(model, tokens, repeats=3):
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--steps", type=int, default=256)  # the workload's 256 generated tokens
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=LLAMA_3_2_1B["num_hidden_layers"])
