@@ -163,7 +163,11 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
                         const int* __restrict__ kv_lens, int heads, int kv_heads, int head_chunks, int window,
                         float scale, int splits, float* __restrict__ partial_o, float* __restrict__ partial_ml) {
     grid_launch_dependents();
-    grid_dependency_wait();  // the newest keys and values come from the kernel before this one
+    // The query, and the keys and values of the newest position, come from the kernel before this one.
+    // Lengths and page tables were written before the step began, and every older position of the
+    // cache in an earlier step: a block may fetch its first page before it waits for that kernel,
+    // unless that page is the one that holds the newest position.
+    if (!kCluster) grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* q_smem = smem;                                 // 16 rows
     unsigned char* stage_smem = smem + kQRowsDecode * kRowBytes;  // 2 stages x (K tile, V tile)
@@ -197,12 +201,16 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+    if (empty && kCluster) grid_dependency_wait();
     if (!empty) {
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t stage_base = smem_u32(stage_smem);
+    const bool early = kCluster && t_begin != pos / kTile;  // the first page holds no position of this step
+    if (kCluster && !early) grid_dependency_wait();
     load_tile(stage_base, k_pool, table[t_begin], kv_head, kv_heads);
     load_tile(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads);
     cp_async_commit();
+    if (early) grid_dependency_wait();
     load_queries(q_smem, q + (size_t)q_row * q_row_stride + (size_t)head0 * HD, HD, kQRowsDecode, rows_here);
     __syncthreads();
     uint32_t a[kKSteps][4];

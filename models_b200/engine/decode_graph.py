@@ -9,6 +9,7 @@ point at the cache's spare page and store nothing, so padding changes no result.
 
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -51,9 +52,18 @@ class _Captured:
         torch.cuda.synchronize(engine.device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self.graph, pool=pool, stream=stream):
-            self.logits = engine.model.forward(self.batch, engine.runs)
-            self.argmax = ops.argmax_rows(self.logits)  # greedy choice of every row, for callers that want only that
+        # No garbage collection inside the capture: a finaliser that frees device or pinned memory (an
+        # older model's, say) is a call that a capture forbids, and it would invalidate this one.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, pool=pool, stream=stream):
+                self.logits = engine.model.forward(self.batch, engine.runs)
+                self.argmax = ops.argmax_rows(self.logits)  # greedy choice of every row, for callers that want only that
+        finally:
+            if collecting:
+                gc.enable()
         self.kernels = ops.launch_count() - before  # this package's kernels inside one replay
         ops.add_launches(-self.kernels)  # a capture launches nothing
         # views of the pinned buffer, for the quick per-step update

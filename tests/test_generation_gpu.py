@@ -302,3 +302,37 @@ def test_stepping_ahead_of_the_sampled_ids_changes_no_token(cuda_device, folders
         model.engine.cache.check()
         assert model.engine.cache.slots.held == 0
     model.close()
+
+
+def test_graph_capture_is_not_disturbed_by_garbage_collection(cuda_device, folders):
+    """Cyclic garbage that owns device and pinned memory, and a collector set to run at every
+    opportunity: collecting it inside a graph capture would free memory there, which a capture
+    forbids.  Generation (which captures at its first decode step) must work all the same."""
+    import gc
+
+    import models_b200
+    from models_b200 import SamplingOptions
+
+    class Knot:
+        def __init__(self):
+            self.me = self
+            self.device = torch.empty(1 << 18, device="cuda")
+            self.pinned = torch.empty(1 << 12).pin_memory()
+
+    old_model = models_b200.load_model(folders["A"], dtype="bfloat16", max_batch=2, context=64)
+    old_model.generate([1, 2, 3], SamplingOptions(temperature=0.0, max_tokens=4))
+    old_model.me = old_model  # an older model that nobody closed, reachable only from itself
+    del old_model
+    for _ in range(20):
+        Knot()
+    before = gc.get_threshold()
+    gc.set_threshold(1, 1, 1)
+    try:
+        model = models_b200.load_model(folders["B"], dtype="float32", max_batch=2, context=64)
+        got = model.generate([4, 5, 6], SamplingOptions(temperature=0.0, max_tokens=6))
+        assert gc.isenabled()
+    finally:
+        gc.set_threshold(*before)
+    expected, _ = plain_greedy(folders["B"], [4, 5, 6], 6, model.engine.spec.stop_token_ids)
+    assert got == expected
+    model.close()
