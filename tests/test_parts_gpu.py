@@ -288,6 +288,156 @@ def test_a_toy_mixer_with_its_own_state_registers_builds_and_steps(cuda_device):
         unregister_part("mixer", "test_running_mean")
 
 
+class LinearAnglePosition:
+    """A toy position encoding: pair i of position p is rotated by p * step * (i + 1).  It offers what
+    the attention mixer asks of any position part: rotary_dim, interleaved, and cos / sin tables."""
+
+    def __init__(self, spec, runtime):
+        self.spec, self.runtime = spec, runtime
+        self.rotary_dim, self.interleaved = spec.rotary_dim, False
+        angle = (torch.arange(max(1, runtime.max_positions), dtype=torch.float64)[:, None] * spec.step *
+                 torch.arange(1, spec.rotary_dim // 2 + 1, dtype=torch.float64)[None, :])
+        self.cos = torch.cos(angle).float().contiguous().to(runtime.device)
+        self.sin = torch.sin(angle).float().contiguous().to(runtime.device)
+
+    def parameters(self):
+        return []
+
+    def load(self, tensors):
+        pass
+
+
+class TopOneExperts:
+    """A toy feed-forward with routing: router logits in 32-bit, the best expert's gated feed-forward
+    for each token (the first of equal logits).  Plain tensor code: it shows the interface, not speed."""
+
+    def __init__(self, spec, runtime):
+        self.spec, self.runtime = spec, runtime
+
+    def parameters(self):
+        from models_b200.weights import ParamRequest
+
+        s, n = self.spec, self.spec.weights
+        out = [ParamRequest(n["router"], (s.experts, s.hidden_size))]
+        for e in range(s.experts):
+            out += [ParamRequest(n["gate"].format(e), (s.intermediate_size, s.hidden_size)),
+                    ParamRequest(n["up"].format(e), (s.intermediate_size, s.hidden_size)),
+                    ParamRequest(n["down"].format(e), (s.hidden_size, s.intermediate_size))]
+        return out
+
+    def load(self, tensors):
+        n, rt = self.spec.weights, self.runtime
+        self.router = rt.vector(tensors[n["router"]])  # read as 32-bit in both modes, like a norm's gain
+        self.experts = [tuple(rt.matrix(tensors[n[k].format(e)]).float() for k in ("gate", "up", "down"))
+                        for e in range(self.spec.experts)]
+
+    def forward(self, xn):
+        x = xn.float()
+        choice = torch.argmax(x @ self.router.t(), dim=1)
+        out = torch.zeros_like(x)
+        for e, (gate, up, down) in enumerate(self.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                h = x[rows]
+                out[rows] = (torch.nn.functional.silu(h @ gate.t()) * (h @ up.t())) @ down.t()
+        return out.to(xn.dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_register_and_run(cuda_device, dtype):
+    """Layer 0: the package's attention with a position encoding defined here; layer 1: the package's
+    attention and a feed-forward with routing defined here.  Both are registered from outside, built
+    from specs, loaded by tensor name and stepped (whole, then token by token) against plain code."""
+    from dataclasses import dataclass, field, replace
+
+    from models_b200.config.specs import BlockSpec, ModelSpec
+    from models_b200.engine import StepEntry
+    from models_b200.parts import register_part, unregister_part
+
+    @dataclass(frozen=True)
+    class LinearAngleSpec:
+        rotary_dim: int
+        step: float
+        kind: str = "test_linear_angles"
+
+    @dataclass(frozen=True)
+    class TopOneSpec:
+        hidden_size: int
+        intermediate_size: int
+        experts: int
+        weights: dict = field(default_factory=dict, hash=False, compare=False)
+        kind: str = "test_top1_experts"
+
+    register_part("position", "test_linear_angles", LinearAnglePosition)
+    register_part("feed_forward", "test_top1_experts", TopOneExperts)
+    try:
+        base = _specs(windows=(None, None))
+        toy_position = LinearAngleSpec(base.layers[0].mixer.head_dim, 0.013)
+        layer0 = replace(base.layers[0], mixer=replace(base.layers[0].mixer, position=toy_position))
+        toy_ffn = TopOneSpec(base.hidden_size, 72, 3, {"router": "layers.1.router", "gate": "layers.1.expert{}.gate",
+                                                        "up": "layers.1.expert{}.up", "down": "layers.1.expert{}.down"})
+        layer1 = replace(base.layers[1], feed_forward=toy_ffn)
+        spec = ModelSpec(base.architecture, base.vocab_size, base.hidden_size, base.max_positions, base.embedding,
+                         (layer0, layer1), base.schedule, base.final_norm, base.head)
+        engine, tensors = _engine(spec, dtype, seed=6, max_tokens=512)
+        assert "layers.1.expert2.down" in tensors and "layers.1.router" in tensors
+
+        def plain(tokens):
+            w = {k: v.float() for k, v in tensors.items()}
+            T = len(tokens)
+            x = P.embed(w["embed"], torch.tensor(tokens))
+            for i, layer in enumerate(spec.layers):
+                m, names = layer.mixer, layer.mixer.weights
+                xn = P.rms_norm(x, w[layer.mixer_norm.weights["weight"]], layer.mixer_norm.eps)
+                if i == 0:
+                    angle = (torch.arange(T, dtype=torch.float64)[:, None] * toy_position.step *
+                             torch.arange(1, m.head_dim // 2 + 1, dtype=torch.float64)[None, :])
+                    cos, sin = torch.cos(angle).float(), torch.sin(angle).float()
+                else:
+                    cos, sin = P.rope_cos_sin(torch.arange(T), P.rope_pair_frequencies(m.head_dim, m.position.theta), None)
+                q = P.rope_rotate_split_half(P.linear(xn, w[names["q"]]).reshape(T, m.num_heads, m.head_dim), cos, sin)
+                k = P.rope_rotate_split_half(P.linear(xn, w[names["k"]]).reshape(T, m.num_kv_heads, m.head_dim), cos, sin)
+                v = P.linear(xn, w[names["v"]]).reshape(T, m.num_kv_heads, m.head_dim)
+                x = x + P.linear(P.causal_gqa_attention(q, k, v), w[names["o"]])
+                xn = P.rms_norm(x, w[layer.feed_forward_norm.weights["weight"]], layer.feed_forward_norm.eps)
+                if i == 0:
+                    f = layer.feed_forward.weights
+                    x = x + P.feed_forward(xn, w[f["gate"]], w[f["up"]], w[f["down"]])
+                else:
+                    router_logits = xn @ w["layers.1.router"].t()
+                    choice = torch.argmax(router_logits, dim=1)
+                    top2 = torch.topk(router_logits, 2, dim=1).values
+                    margins.append(top2[:, 0] - top2[:, 1])
+                    delta = torch.zeros_like(x)
+                    for t in range(T):
+                        e = int(choice[t])
+                        delta[t] = P.feed_forward(xn[t:t + 1], w[f"layers.1.expert{e}.gate"], w[f"layers.1.expert{e}.up"],
+                                                  w[f"layers.1.expert{e}.down"])[0]
+                    x = x + delta
+            return P.linear(P.rms_norm(x, w["final_norm"], spec.final_norm.eps), w["head"])
+
+        tokens = _tokens(40, spec.vocab_size, 31)
+        margins = []
+        expected = plain(tokens)
+        # Routing is a discrete choice: where the two best router logits are closer than bfloat16's
+        # rounding of the inputs can move them, either expert is a right answer and the row is not
+        # compared (the routed layer is the last one, so such a row touches no other row).
+        clear = margins[0] > (0.0 if dtype == "float32" else 0.02)
+        assert int(clear.sum()) >= 30
+        tol = max(TOLERANCE[dtype], 1e-4)
+        slot = engine.open_slot()
+        out = engine.step([StepEntry(slot, tokens[:30], list(range(30)))])
+        assert scaled_error(out[clear[:30].cuda()], expected[:30][clear[:30]]) < tol
+        for i in range(30, 40):
+            out = engine.step([StepEntry(slot, [tokens[i]], [0])])
+            if clear[i]:
+                assert scaled_error(out[0], expected[i]) < tol, i
+        engine.release_slot(slot)
+    finally:
+        unregister_part("position", "test_linear_angles")
+        unregister_part("feed_forward", "test_top1_experts")
+
+
 def test_missing_kind_and_cpu_tensors_fail_loudly(cuda_device):
     from models_b200.kernels import ops
     from models_b200.parts import Runtime, build_part
