@@ -1,13 +1,15 @@
 // Prefill matrix products on the fifth-generation tensor cores: C[M, N] = A[M, K] . W[N, K]^T with
 // bfloat16 operands and float accumulation, for many activation rows (a whole prompt).
 //
-//   * Operand tiles travel by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a four-stage ring of
-//     shared memory: 128 rows of A and 256 rows of W, 64 columns of K per stage.
-//   * One thread issues tcgen05.mma (M = 128, N = 256, K = 16, operands from shared-memory
-//     descriptors); the accumulator lives in tensor memory, 256 columns, double-buffered, so the
-//     epilogue of one tile overlaps the products of the next.
-//   * Four epilogue warps read the accumulator back with tcgen05.ld and finish the layer's arithmetic
-//     in registers: store as bfloat16 / float, add into the float32 residual stream, or -- when W
+//   * Operand tiles travel by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared
+//     memory: 128 rows of A and 256 (or 128) rows of W, 64 columns of K per stage, four (six) stages.
+//   * One thread issues tcgen05.mma (M = 128, N = 256 or 128, K = 16, operands from shared-memory
+//     descriptors); the accumulator lives in tensor memory, double-buffered, so the epilogue of one
+//     tile overlaps the products of the next.
+//   * Eight epilogue warps (two per quarter of the tensor-memory lanes, half the columns each) read
+//     the accumulator back with tcgen05.ld and finish the layer's arithmetic in registers: store as
+//     bfloat16 / float, add into the float32 residual stream (a vector reduction at the memory side:
+//     the stream is not read back), or -- when W
 //     holds gate rows and up rows -- silu(gate) * up, so the gated activation never passes through
 //     memory.  (x = x + W.h: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1131-1138,
 //     1172-1178; SwiGLU: backend-java/.../ops/TensorOps.java:1407-1425.)
@@ -25,13 +27,25 @@ namespace mb {
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
 
-constexpr int kBlockM = 128, kBlockN = 256, kStages = 4;
-constexpr uint32_t kInstruction = instruction_descriptor(kBlockM, kBlockN);
+constexpr int kBlockM = 128;
 constexpr int kTileABytes = kBlockM * kBlockK * 2;      // 16 KB
-constexpr int kBoxBBytes = 128 * kBlockK * 2;           // 16 KB, two boxes per stage
-constexpr int kStageBytes = kTileABytes + 2 * kBoxBBytes;
-constexpr int kThreads = 192;                           // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
-constexpr int kAccumulatorColumns = 256, kTmemColumns = 512;
+constexpr int kBoxBBytes = 128 * kBlockK * 2;           // 16 KB: 128 rows of W; one or two boxes per stage
+constexpr int kRingBytes = 192 * 1024;
+// A tile is 128 rows by BN columns, BN = 256 (two boxes of W per stage, four stages) or 128 (one box,
+// six stages).  The narrow tile moves more bytes per product, but twice as many tiles spread a small
+// or oddly sized matrix more evenly over the multiprocessors.
+template <int BN>
+struct Tile {
+    static_assert(BN == 128 || BN == 256, "tile widths built: 128 and 256");
+    static constexpr int kBoxes = BN / 128;
+    static constexpr int kStageBytes = kTileABytes + kBoxes * kBoxBBytes;
+    static constexpr int kStages = kRingBytes / kStageBytes;
+    static constexpr uint32_t kInstruction = instruction_descriptor(kBlockM, BN);
+};
+constexpr int kMaxStages = 6;
+constexpr int kEpilogueWarps = 8;                       // two per quarter of the tensor-memory lanes: each takes half the columns
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;      // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue
+constexpr int kTmemColumns = 512;  // two accumulators of BN columns; all of it is taken either way
 
 struct GemmArgs {
     int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
@@ -40,20 +54,22 @@ struct GemmArgs {
     int ld_out;
 };
 
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmArgs args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle and the descriptors assume
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t barriers[2 * kStages + 4];
+    constexpr int kStages = Tile<BN>::kStages, kStageBytes = Tile<BN>::kStageBytes, kAccumulatorColumns = BN;
+    static_assert(EPI != EPI_SWIGLU || BN == 256, "the gated epilogue pairs 128 gate columns with 128 up columns");
+    __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 4];
     __shared__ uint32_t tmem_base_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t full_bar = smem_u32(&barriers[0]), empty_bar = smem_u32(&barriers[kStages]);
-    const uint32_t acc_full_bar = smem_u32(&barriers[2 * kStages]), acc_empty_bar = smem_u32(&barriers[2 * kStages + 2]);
+    const uint32_t full_bar = smem_u32(&barriers[0]), empty_bar = smem_u32(&barriers[kMaxStages]);
+    const uint32_t acc_full_bar = smem_u32(&barriers[2 * kMaxStages]), acc_empty_bar = smem_u32(&barriers[2 * kMaxStages + 2]);
 
-    // columns of output per tile: 256, or 128 gate/up pairs
-    constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : 256;
+    // columns of output per tile: BN, or 128 gate/up pairs
+    constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
     const int m_tiles = (args.m + kBlockM - 1) / kBlockM;
     const int n_tiles = (args.n + kOutCols - 1) / kOutCols;
     const int tiles = m_tiles * n_tiles;
@@ -66,7 +82,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full_bar + 8 * a, 1);
-            mbar_init(acc_empty_bar + 8 * a, 4);
+            mbar_init(acc_empty_bar + 8 * a, kEpilogueWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -89,15 +105,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % m_tiles) * kBlockM, n_tile = tile / m_tiles;
-                const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * 256;
-                const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * 256 + 128;
+                const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
+                const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
                     const uint32_t dst = smem_u32(smem) + stage * kStageBytes;
                     mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
                     tma_load_2d(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
                     tma_load_2d(dst + kTileABytes, &map_w, kb * kBlockK, w_row0, full_bar + 8 * stage);
-                    tma_load_2d(dst + kTileABytes + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * stage);
+                    if (Tile<BN>::kBoxes == 2)
+                        tma_load_2d(dst + kTileABytes + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * stage);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -122,7 +139,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint64_t a_desc = umma_descriptor(a_addr), b_desc = umma_descriptor(a_addr + kTileABytes);
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 16; ++ks)  // 32 bytes further along K per step: +2 in the address field
-                        umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
+                        umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, Tile<BN>::kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(empty_bar + 8 * stage);  // the stage is free once these products have read it
                     if (++stage == kStages) {
                         stage = 0;
@@ -138,8 +155,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue: 4 warps, one TMEM lane quarter each
-        const int quarter = warp & 3;
+        // ------------------------------------------------------------------ epilogue: 8 warps; a warp reads one quarter of
+        // the tensor-memory lanes (its index modulo 4) and half of the tile's columns
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        constexpr int kHalfCols = kOutCols / 2;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -153,14 +172,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t taddr = tmem_base + acc * kAccumulatorColumns + ((uint32_t)(quarter * 32) << 16);
             const int n0 = n_tile * kOutCols;
 #pragma unroll 1
-            for (int c = 0; c < kOutCols; c += 32) {
+            for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 32) {
                 float v[32];
-                tmem_load_32(taddr + c, v);
                 if (EPI == EPI_SWIGLU) {
                     float u[32];
-                    tmem_load_32(taddr + 128 + c, u);
+                    tmem_load_32_issue(taddr + c, v);
+                    tmem_load_32_issue(taddr + 128 + c, u);
+                    tmem_load_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                } else {
+                    tmem_load_32_issue(taddr + c, v);
+                    tmem_load_wait();
                 }
                 if (row < args.m) {
                     const int col = n0 + c;
@@ -182,12 +205,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (col + 32 <= args.n) {
 #pragma unroll
                             for (int i = 0; i < 32; i += 4) {
-                                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                                 if (EPI == EPI_RESIDUAL) {
-                                    const float4 x = *reinterpret_cast<const float4*>(dst + i);
-                                    o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+                                    // x += value without reading x here: the addition happens at the memory side.  Every
+                                    // element of x gets exactly one such addition per product, so the sum has one order.
+                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(v[i]),
+                                                 "f"(v[i + 1]), "f"(v[i + 2]), "f"(v[i + 3])
+                                                 : "memory");
+                                } else {
+                                    *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                                 }
-                                *reinterpret_cast<float4*>(dst + i) = o;
                             }
                         } else {
                             for (int i = 0; i < 32 && col + i < args.n; ++i) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
@@ -214,11 +240,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-template <int EPI>
-static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, cudaStream_t stream) {
-    constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : 256;
-    const size_t smem = (size_t)kStages * kStageBytes + 1024;
-    auto kernel = gemm_tcgen05_kernel<EPI>;
+template <int EPI, int BN>
+static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, cudaStream_t stream) {
+    constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
+    const size_t smem = (size_t)Tile<BN>::kStages * Tile<BN>::kStageBytes + 1024;
+    auto kernel = gemm_tcgen05_kernel<EPI, BN>;
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -230,6 +256,23 @@ static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const Gemm
     return launch_dependent("gemm_tcgen05", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_a, map_w, args);
 }
 
+// Which tile width finishes first: rounds of tiles over the multiprocessors times the cost of a tile, a
+// narrow tile counted at 0.75 of a wide one (it moves more bytes per product; measured 0.7 to 0.8).
+static bool narrow_tiles_are_faster(int m, int n, int multiprocessors) {
+    const long m_tiles = (m + kBlockM - 1) / kBlockM;
+    const long wide = m_tiles * ((n + 255) / 256), narrow = m_tiles * ((n + 127) / 128);
+    const long wide_rounds = (wide + multiprocessors - 1) / multiprocessors, narrow_rounds = (narrow + multiprocessors - 1) / multiprocessors;
+    return narrow_rounds * 75 < wide_rounds * 100;
+}
+
+template <int EPI>
+static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, int tile_width,
+                  cudaStream_t stream) {
+    const bool narrow = tile_width == 128 || (tile_width == 0 && narrow_tiles_are_faster(args.m, args.n, multiprocessors));
+    if (narrow) return launch_tile<EPI, 128>(map_a, map_w, args, multiprocessors, stream);
+    return launch_tile<EPI, 256>(map_a, map_w, args, multiprocessors, stream);
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -237,8 +280,10 @@ using namespace mb;
 // a: bfloat16 [m, k] (row stride lda); w: bfloat16 [n_w, k] (row stride ldw).
 // epilogue 0: out bfloat16 [m, n_w]; 1: out float32 [m, n_w]; 2: out float32 [m, n_w] += ; 3: w holds gate
 // rows [0, n_w/2) and up rows [n_w/2, n_w): out bfloat16 [m, n_w/2] = silu(gate) * up.
+// tile_width: 0 lets the launcher choose between 128 and 256 output columns per tile; the gated epilogue takes 256.
 MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ld_out, int m, int n_w, int k,
-                              int epilogue, int multiprocessors, cudaStream_t stream) {
+                              int epilogue, int multiprocessors, int tile_width, cudaStream_t stream) {
+    if (tile_width != 0 && tile_width != 128 && tile_width != 256) return fail("gemm_tcgen05: tile width %d is not built (128, 256)", tile_width);
     if (m <= 0 || n_w <= 0) return 0;
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8) return fail("gemm_tcgen05: k (%d) and the row strides (%d, %d) must be multiples of 8", k, lda, ldw);
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return fail("gemm_tcgen05: operands must start on 16-byte boundaries");
@@ -251,10 +296,12 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
     GemmArgs args{m, n, k, n, out, ld_out};
     switch (epilogue) {
-        case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, stream);
-        case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, stream);
-        case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(map_a, map_w, args, multiprocessors, stream);
-        case EPI_SWIGLU: return launch<EPI_SWIGLU>(map_a, map_w, args, multiprocessors, stream);
+        case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, stream);
+        case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, stream);
+        case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(map_a, map_w, args, multiprocessors, tile_width, stream);
+        case EPI_SWIGLU:
+            if (tile_width == 128) return fail("gemm_tcgen05: the gated epilogue takes tiles of 256 weight rows");
+            return launch_tile<EPI_SWIGLU, 256>(map_a, map_w, args, multiprocessors, stream);
     }
     return fail("gemm_tcgen05: unknown epilogue %d", epilogue);
 }

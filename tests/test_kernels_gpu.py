@@ -494,14 +494,17 @@ def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
     w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
     exact = a.double() @ w.double().t()
     scale = float(exact.abs().max())
-    out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_F32)
-    assert float((out.double().cpu() - exact).abs().max()) < 2e-5 * scale * math.sqrt(k)
-    out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_BF16)
-    assert out.dtype == torch.bfloat16 and float((out.double().cpu() - exact).abs().max()) < 1e-2 * scale
-    residual = torch.randn(m, n, generator=g)
-    rd = residual.cuda()
-    ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_RESIDUAL, out=rd)
-    assert float((rd.double().cpu() - (residual.double() + exact)).abs().max()) < 2e-5 * (scale + 4) * math.sqrt(k)
+    for tile_width in (0, 128, 256):  # the launcher's choice, and both tile widths by name
+        out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_F32, tile_width=tile_width)
+        assert float((out.double().cpu() - exact).abs().max()) < 2e-5 * scale * math.sqrt(k)
+        out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_BF16, tile_width=tile_width)
+        assert out.dtype == torch.bfloat16 and float((out.double().cpu() - exact).abs().max()) < 1e-2 * scale
+        residual = torch.randn(m, n, generator=g)
+        rd = residual.cuda()
+        ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_RESIDUAL, out=rd, tile_width=tile_width)
+        assert float((rd.double().cpu() - (residual.double() + exact)).abs().max()) < 2e-5 * (scale + 4) * math.sqrt(k)
+    with pytest.raises(ops.KernelError, match="256"):
+        ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_SWIGLU, tile_width=128)
     gated = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_SWIGLU)
     want = plain_llama.swiglu(exact[:, : n // 2], exact[:, n // 2:])
     assert gated.shape == (m, n // 2)
