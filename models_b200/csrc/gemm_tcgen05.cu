@@ -25,7 +25,7 @@ MB_DEFINE_LAST_ERROR()
 
 namespace mb {
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE = 4 };
 
 constexpr int kBlockM = 128;
 constexpr int kTileABytes = kBlockM * kBlockK * 2;      // 16 KB
@@ -50,8 +50,16 @@ constexpr int kTmemColumns = 512;  // two accumulators of BN columns; all of it 
 struct GemmArgs {
     int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
     int up_row_offset;    // EPI_SWIGLU: first up row of W
-    void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream
+    void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream; EPI_ROPE: the queries [m, heads * head_dim]
     int ld_out;
+    // EPI_ROPE: W is [q heads; k heads; v heads]
+    int heads, kv_heads, head_dim, page_size;
+    const int* positions;     // [m]
+    const int* slot_mapping;  // [m] flat cache position, < 0: do not store
+    const float* cos_table;   // [positions][head_dim / 2]
+    const float* sin_table;
+    bf16* k_pool;             // [pages][kv_heads][page_size][head_dim]
+    bf16* v_pool;
 };
 
 template <int EPI, int BN>
@@ -171,6 +179,61 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * kAccumulatorColumns + ((uint32_t)(quarter * 32) << 16);
             const int n0 = n_tile * kOutCols;
+            if (EPI == EPI_ROPE) {
+                // Whole heads lie inside this warp's half of the tile (head size 64 or 128).  Per head: the
+                // coordinates d and d + head/2 are a rotation pair (x0' = x0*c - x1*s, x1' = x0*s + x1*c,
+                // integrallis/models, backend-java/.../ops/TensorOps.java:1481-1486); queries go to the query
+                // buffer, keys (rotated) and values (as they are) straight into the paged cache
+                // (backend-java/.../llama/LlamaForwardPass.java:1070-1086).  Queries and keys pass through
+                // bfloat16 before the rotation, as they do when the product stores them.
+                const int hd = args.head_dim, half_head = hd / 2;
+                const bool live = row < args.m;
+                const int position = live ? args.positions[row] : 0;
+                const int slot = live ? args.slot_mapping[row] : -1;
+                for (int h0 = half * kHalfCols; h0 < (half + 1) * kHalfCols; h0 += hd) {
+                    const int head = (n0 + h0) / hd;
+                    if (head >= args.heads + 2 * args.kv_heads) break;
+                    const bool is_query = head < args.heads, is_key = !is_query && head < args.heads + args.kv_heads;
+                    bf16* dst = nullptr;
+                    if (is_query) {
+                        dst = reinterpret_cast<bf16*>(args.out) + (size_t)row * args.ld_out + (size_t)head * hd;
+                    } else if (slot >= 0) {
+                        const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
+                        const size_t page = slot / args.page_size, offset = slot % args.page_size;
+                        dst = (is_key ? args.k_pool : args.v_pool) + ((page * args.kv_heads + kv_head) * args.page_size + offset) * hd;
+                    }
+#pragma unroll 1
+                    for (int c = 0; c < half_head; c += 32) {
+                        float x0[32], x1[32];
+                        tmem_load_32_issue(taddr + h0 + c, x0);
+                        tmem_load_32_issue(taddr + h0 + half_head + c, x1);
+                        tmem_load_wait();
+                        if (!live || dst == nullptr) continue;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            float lo[8], hi[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                lo[j] = __bfloat162float(__float2bfloat16_rn(x0[i + j]));
+                                hi[j] = __bfloat162float(__float2bfloat16_rn(x1[i + j]));
+                            }
+                            if (is_query || is_key) {
+                                float cs[8], sn[8];
+                                load8(args.cos_table + (size_t)position * half_head + c + i, cs);
+                                load8(args.sin_table + (size_t)position * half_head + c + i, sn);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const float r0 = lo[j] * cs[j] - hi[j] * sn[j], r1 = lo[j] * sn[j] + hi[j] * cs[j];
+                                    lo[j] = r0;
+                                    hi[j] = r1;
+                                }
+                            }
+                            store8(dst + c + i, lo);
+                            store8(dst + half_head + c + i, hi);
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 32) {
                 float v[32];
@@ -294,7 +357,7 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     CUtensorMap map_a, map_w;
     if (int status = make_map(&map_a, a, m, k, lda)) return status;
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
-    GemmArgs args{m, n, k, n, out, ld_out};
+    GemmArgs args{m, n, k, n, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     switch (epilogue) {
         case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, stream);
         case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, stream);
@@ -304,6 +367,29 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
             return launch_tile<EPI_SWIGLU, 256>(map_a, map_w, args, multiprocessors, stream);
     }
     return fail("gemm_tcgen05: unknown epilogue %d", epilogue);
+}
+
+// The q/k/v product of an attention layer for a whole prompt, with the rotation of queries and keys and the paged
+// cache write folded into its epilogue.  w: bfloat16 [(heads + 2 kv_heads) * head_dim, k], rows ordered q heads, k
+// heads, v heads; q_out: bfloat16 [m, heads * head_dim].  Head sizes 64 and 128 (a tile half holds whole heads).
+MB_EXPORT int mb_gemm_tcgen05_qkv_rope(const void* a, int lda, const void* w, int ldw, void* q_out, int ld_q, int m, int k,
+                                       int heads, int kv_heads, int head_dim, const int* positions, const float* cos_table,
+                                       const float* sin_table, void* k_pool, void* v_pool, const int* slot_mapping,
+                                       int page_size, int multiprocessors, cudaStream_t stream) {
+    if (m <= 0) return 0;
+    if (head_dim != 64 && head_dim != 128) return fail("gemm_tcgen05_qkv_rope: head size %d is not built (64, 128)", head_dim);
+    if (heads <= 0 || kv_heads <= 0 || page_size <= 0) return fail("gemm_tcgen05_qkv_rope: heads, kv heads and page size must be positive");
+    if (k <= 0 || k % 8 || lda % 8 || ldw % 8) return fail("gemm_tcgen05_qkv_rope: k (%d) and the row strides (%d, %d) must be multiples of 8", k, lda, ldw);
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)q_out & 15) || ld_q % 8 || ((uintptr_t)k_pool & 15) ||
+        ((uintptr_t)v_pool & 15) || ((uintptr_t)cos_table & 15) || ((uintptr_t)sin_table & 15))
+        return fail("gemm_tcgen05_qkv_rope: operands, tables and pools must start on 16-byte boundaries");
+    const int n_w = (heads + 2 * kv_heads) * head_dim;
+    CUtensorMap map_a, map_w;
+    if (int status = make_map(&map_a, a, m, k, lda)) return status;
+    if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
+    GemmArgs args{m, n_w, k, n_w, q_out, ld_q, heads, kv_heads, head_dim, page_size, positions, slot_mapping, cos_table, sin_table,
+                  (bf16*)k_pool, (bf16*)v_pool};
+    return launch_tile<EPI_ROPE, 256>(map_a, map_w, args, multiprocessors, stream);
 }
 
 // 0 when no wait ever gave up; else 1 + (role << 8): 1 producer, 2 MMA (accumulator), 3 MMA (operands), 4 epilogue.

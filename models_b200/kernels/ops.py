@@ -42,7 +42,10 @@ def _p(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device, as the raw handle the launchers take (the two
+    calls below are what torch.cuda.current_stream() ends in, without its Python layers: this runs
+    once per kernel launch)."""
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 _launches = [0]
@@ -469,6 +472,43 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16
     _run(lib, lib.mb_gemm_tcgen05(_p(a), a.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), m, n_w, k,
                                   epilogue, _sm_count(a.device), tile_width, _stream()))
     return out
+
+
+def gemm_tcgen05_qkv_rope_takes(weight: torch.Tensor, rows: int, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether the prefill q/k/v product with folded rotation and cache write applies: a weight the
+    tcgen05 product takes for so many rows, heads of 64 or 128."""
+    return (head_dim in (64, 128) and weight.shape[0] == (heads + 2 * kv_heads) * head_dim and rows > WIDE_ROWS
+            and gemm_tcgen05_takes(weight, EPI_BF16, rows))
+
+
+def gemm_tcgen05_qkv_rope(a: torch.Tensor, weight: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                          positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
+                          v_pool: torch.Tensor, slot_mapping: torch.Tensor) -> torch.Tensor:
+    """The q/k/v product of an attention layer over a whole prompt with what follows it folded into
+    its epilogue: rotation of queries and keys (split-half pairs over the whole head) and the paged
+    cache write of keys and values.  Returns the rotated queries, bfloat16 [rows, heads * head_dim]."""
+    _cuda(a, weight, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    m, k = a.shape
+    if a.dtype != torch.bfloat16 or a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16 or weight.shape[1] != k:
+        raise KernelError(f"gemm_tcgen05_qkv_rope: activations {tuple(a.shape)} {a.dtype} do not fit the weight {tuple(weight.shape)}")
+    if not gemm_tcgen05_qkv_rope_takes(weight, m, heads, kv_heads, head_dim):
+        raise KernelError(f"gemm_tcgen05_qkv_rope does not take a {tuple(weight.shape)} {weight.dtype} weight with {m} rows "
+                          f"and heads of {head_dim}")
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    if positions.numel() < m or slot_mapping.numel() < m:
+        raise KernelError("positions and slot_mapping must hold one entry per row")
+    if cos.dtype != torch.float32 or cos.shape[-1] != head_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous():
+        raise KernelError(f"cos/sin tables must be contiguous float32 [positions, {head_dim // 2}]")
+    if (k_pool.dtype != torch.bfloat16 or k_pool.shape != v_pool.shape or k_pool.dim() != 4 or k_pool.shape[1] != kv_heads
+            or k_pool.shape[3] != head_dim or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
+        raise KernelError("cache pools must be contiguous bfloat16 [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((m, heads * head_dim), dtype=torch.bfloat16, device=a.device)
+    lib = gemm_tc()
+    _run(lib, lib.mb_gemm_tcgen05_qkv_rope(_p(a), a.stride(0), _p(weight), weight.stride(0), _p(q), q.stride(0), m, k, heads,
+                                           kv_heads, head_dim, _p(positions), _p(cos), _p(sin), _p(k_pool), _p(v_pool),
+                                           _p(slot_mapping), k_pool.shape[2], _sm_count(a.device), _stream()))
+    return q
 
 
 def wide_gemm_lib():

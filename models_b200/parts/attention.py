@@ -100,12 +100,22 @@ class AttentionMixer(Mixer):
         return self.b_o is None and xn.dtype == torch.bfloat16 and ops.gemm_tcgen05_takes(self.w_o, rows=xn.shape[0])
 
     def forward_into(self, x: torch.Tensor, xn: torch.Tensor, batch, run: RunContext) -> None:
-        """x += Wo . attention(...): the residual add rides in the output product."""
-        writes = run.writes_cache
-        qkv = linear(xn, self.w_qkv if writes else self.w_q, self.runtime.compute_dtype)
-        if self.b_qkv is not None:
-            ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
-        attended = self._rotate_store_attend(qkv, batch, run)
+        """x += Wo . attention(...): the residual add rides in the output product, and (whole heads of
+        64 or 128, split-half pairs over the whole head) rotation and cache write in the q/k/v product."""
+        writes, s, pos = run.writes_cache, self.spec, self.position
+        if (writes and self.b_qkv is None and pos is not None and pos.rotary_dim == s.head_dim and not pos.interleaved
+                and run.k_pool is not None and run.k_pool.dtype == torch.bfloat16
+                and ops.gemm_tcgen05_qkv_rope_takes(self.w_qkv, xn.shape[0], s.num_heads, s.num_kv_heads, s.head_dim)):
+            group = batch.groups[run.group]
+            q = ops.gemm_tcgen05_qkv_rope(xn, self.w_qkv, s.num_heads, s.num_kv_heads, s.head_dim, batch.positions, pos.cos,
+                                          pos.sin, run.k_pool, run.v_pool, group.slot_mapping)
+            attended = torch.empty((q.shape[0], self.q_width), dtype=q.dtype, device=q.device)
+            self.attend(q, attended, batch, group, run)
+        else:
+            qkv = linear(xn, self.w_qkv if writes else self.w_q, self.runtime.compute_dtype)
+            if self.b_qkv is not None:
+                ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
+            attended = self._rotate_store_attend(qkv, batch, run)
         ops.tensor_core_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x)
 
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:

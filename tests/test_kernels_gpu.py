@@ -483,6 +483,57 @@ def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads
     assert torch.equal(kd.cpu()[untouched], k_pool[untouched])  # pages of other sequences are left alone
 
 
+@pytest.mark.parametrize("rows,heads,kv_heads,head_dim,hidden", [(129, 8, 2, 64, 512), (300, 3, 3, 128, 264), (700, 5, 1, 64, 328),
+                                                               (257, 2, 2, 128, 1024)])
+def test_tcgen05_qkv_product_with_rotation_and_cache_write(cuda_device, rows, heads, kv_heads, head_dim, hidden):
+    """The prefill q/k/v product with rotation and paged cache write in its epilogue against the plain
+    parts: head counts that leave the last tile partly empty, rows that do not fill the last row tile,
+    padding rows that must store nothing, positions scattered over the table."""
+    from models_b200.kernels import ops
+
+    page = 64
+    g = torch.Generator().manual_seed(rows + head_dim)
+    n = (heads + 2 * kv_heads) * head_dim
+    w = (torch.randn(n, hidden, generator=g) * 0.05).bfloat16()
+    a = torch.randn(rows, hidden, generator=g).bfloat16()
+    positions = torch.randint(0, 900, (rows,), generator=g).int()
+    cos, sin = plain_llama.rope_cos_sin(torch.arange(900), plain_llama.rope_pair_frequencies(head_dim, 50000.0), None)
+    pages = -(-rows // page) + 3
+    k_pool, v_pool = _pools(pages, kv_heads, page, head_dim, torch.bfloat16, 3)
+    slots = (torch.randperm((pages - 1) * page, generator=g)[:rows] + page).int()  # distinct cache positions, none in page 0
+    slots[1] = -1  # padding rows store nothing
+    slots[rows - 1] = -1
+    kd, vd = k_pool.cuda(), v_pool.cuda()
+    q = ops.gemm_tcgen05_qkv_rope(a.cuda(), w.cuda(), heads, kv_heads, head_dim, positions.cuda(), cos.cuda(), sin.cuda(), kd, vd,
+                                  slots.cuda())
+    torch.cuda.synchronize()
+    assert ops.gemm_tcgen05_status() == 0
+    qkv = (a.float() @ w.float().t()).bfloat16().float()  # the product passes through bfloat16 before the rotation
+    c, s_ = cos[positions.long()], sin[positions.long()]
+    want_q = plain_llama.rope_rotate_split_half(qkv[:, : heads * head_dim].reshape(rows, heads, head_dim), c, s_)
+    want_k = plain_llama.rope_rotate_split_half(
+        qkv[:, heads * head_dim:(heads + kv_heads) * head_dim].reshape(rows, kv_heads, head_dim), c, s_)
+    want_v = qkv[:, (heads + kv_heads) * head_dim:].reshape(rows, kv_heads, head_dim)
+    scale = float(qkv.abs().max())
+    assert q.shape == (rows, heads * head_dim)
+    assert float((q.float().cpu() - want_q.reshape(rows, -1)).abs().max()) < 1.5e-2 * scale
+    ek, ev = k_pool.float().clone(), v_pool.float().clone()
+    for b in range(rows):
+        slot = int(slots[b])
+        if slot >= 0:
+            ek[slot // page, :, slot % page, :] = want_k[b]
+            ev[slot // page, :, slot % page, :] = want_v[b]
+    assert float((kd.float().cpu() - ek).abs().max()) < 1.5e-2 * max(scale, 4.0)
+    assert float((vd.float().cpu() - ev).abs().max()) < 1.5e-2 * max(scale, 4.0)
+    written = torch.zeros(pages * page, dtype=torch.bool)
+    written[slots[slots >= 0].long()] = True
+    untouched = ~written.reshape(pages, page)
+    assert torch.equal(kd.cpu().permute(0, 2, 1, 3)[untouched], k_pool.permute(0, 2, 1, 3)[untouched])  # nothing else was stored
+    assert torch.equal(vd.cpu().permute(0, 2, 1, 3)[untouched], v_pool.permute(0, 2, 1, 3)[untouched])
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tcgen05_qkv_rope(a.cuda(), w.cuda(), heads, kv_heads, 48, positions.cuda(), cos.cuda(), sin.cuda(), kd, vd, slots.cuda())
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (70, 144, 136), (300, 272, 200), (1, 512, 2048), (513, 1040, 328)])
 def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
     """The prefill matrix product (TMA, tcgen05.mma, accumulator in tensor memory) against float64,
