@@ -145,6 +145,53 @@ argmax_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
     cluster.sync();
 }
 
+// The candidates (probability, id) in shared memory, unused entries (-1, max int): sorted by probability
+// descending and id ascending (bitonic, all kMaxSorted entries), cut at the shortest prefix whose mass
+// reaches `nucleus` (crossing token included), then the inverse-CDF draw r = u * kept mass.
+__device__ void sort_and_pick(float* sorted_p, int* sorted_id, int k, float nucleus, float u, int* out) {
+    const int tid = threadIdx.x;
+    for (int size = 2; size <= kMaxSorted; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            const int partner = tid ^ stride;
+            if (partner > tid) {
+                const bool descending_block = (tid & size) == 0;
+                const float pa = sorted_p[tid], pb = sorted_p[partner];
+                const int ia = sorted_id[tid], ib = sorted_id[partner];
+                const bool a_first = pa > pb || (pa == pb && ia < ib);
+                if (a_first != descending_block) {
+                    sorted_p[tid] = pb; sorted_p[partner] = pa;
+                    sorted_id[tid] = ib; sorted_id[partner] = ia;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        float cumulative = 0.0f;
+        int cutoff = k;
+        for (int i = 0; i < k; ++i) {
+            cumulative += sorted_p[i];
+            if (cumulative >= nucleus) {
+                cutoff = i + 1;
+                break;
+            }
+        }
+        float total = 0.0f;
+        for (int i = 0; i < cutoff; ++i) total += sorted_p[i];
+        const float target = u * total;
+        float acc = 0.0f;
+        int pick = sorted_id[cutoff - 1];
+        for (int i = 0; i < cutoff; ++i) {
+            acc += sorted_p[i];
+            if (acc >= target) {
+                pick = sorted_id[i];
+                break;
+            }
+        }
+        *out = pick;
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, float* __restrict__ work,
                    int* __restrict__ counts, const float* __restrict__ temperature, const int* __restrict__ top_k,
@@ -287,47 +334,7 @@ sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
             }
             __syncthreads();
         }
-        // bitonic sort of kMaxSorted entries
-        for (int size = 2; size <= kMaxSorted; size <<= 1) {
-            for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                const int partner = tid ^ stride;
-                if (partner > tid) {
-                    const bool descending_block = (tid & size) == 0;
-                    const float pa = sorted_p[tid], pb = sorted_p[partner];
-                    const int ia = sorted_id[tid], ib = sorted_id[partner];
-                    const bool a_first = pa > pb || (pa == pb && ia < ib);
-                    if (a_first != descending_block) {
-                        sorted_p[tid] = pb; sorted_p[partner] = pa;
-                        sorted_id[tid] = ib; sorted_id[partner] = ia;
-                    }
-                }
-                __syncthreads();
-            }
-        }
-        if (tid == 0) {
-            float cumulative = 0.0f;
-            int cutoff = k;
-            for (int i = 0; i < k; ++i) {
-                cumulative += sorted_p[i];
-                if (cumulative >= nucleus) {
-                    cutoff = i + 1;
-                    break;
-                }
-            }
-            float total = 0.0f;
-            for (int i = 0; i < cutoff; ++i) total += sorted_p[i];
-            const float target = u * total;
-            float acc = 0.0f;
-            int pick = sorted_id[cutoff - 1];
-            for (int i = 0; i < cutoff; ++i) {
-                acc += sorted_p[i];
-                if (acc >= target) {
-                    pick = sorted_id[i];
-                    break;
-                }
-            }
-            out[r] = pick;
-        }
+        sort_and_pick(sorted_p, sorted_id, k, nucleus, u, out + r);
         return;
     }
 
@@ -383,6 +390,211 @@ sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
     if (tid == 0) out[r] = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
 }
 
+
+// The same pipeline for rows with at most kMaxSorted candidates, with the row spread over a cluster of
+// kSampleBlocks blocks: block b owns the ids [b * slice, (b + 1) * slice).  Every pass over the vocabulary
+// runs on all blocks at once; maxima, sums and the radix histograms meet through distributed shared memory
+// (always added in block order, so the result does not depend on timing); the candidates are gathered into
+// the first block's shared memory, which sorts them and draws.  grid (kSampleBlocks, rows).
+constexpr int kSampleBlocks = 8;
+
+__global__ void __launch_bounds__(kThreads)
+sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int vocab, float* __restrict__ work,
+                           int* __restrict__ counts, const float* __restrict__ temperature, const int* __restrict__ top_k,
+                           const float* __restrict__ top_p, const float* __restrict__ penalty,
+                           const int* __restrict__ history, int history_stride, const int* __restrict__ history_len,
+                           const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
+                           const float* __restrict__ uniforms, int* __restrict__ out) {
+    __shared__ Best best_scratch[32];
+    __shared__ float float_scratch[32];
+    __shared__ int int_scratch[32];
+    __shared__ int histogram[256];      // of this block's ids
+    __shared__ int histogram_all[256];  // of the whole row
+    __shared__ float sorted_p[kMaxSorted];  // the candidates: filled and used in the cluster's first block only
+    __shared__ int sorted_id[kMaxSorted];
+    __shared__ Best slot_best;
+    __shared__ float slot_sum;
+    __shared__ int slot_ties;
+    __shared__ int gathered;            // first block: candidates gathered so far
+    __shared__ int shared_int[4];
+
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int part = cluster.block_rank();
+    const int r = blockIdx.y, tid = threadIdx.x;
+    const int slice = (vocab + kSampleBlocks - 1) / kSampleBlocks;
+    const int begin = min(vocab, part * slice), end = min(vocab, begin + slice);
+    const float* row = logits + (size_t)r * row_stride;
+    float* w = work + (size_t)r * vocab;
+    const float temp = temperature[r];
+    const float pen = penalty[r];
+    const bool penalised = pen > 1.0f && history && history_len[r] > 0;
+
+    if (part == 0) {
+        if (tid == 0) gathered = 0;
+        for (int i = tid; i < kMaxSorted; i += kThreads) {
+            sorted_p[i] = -1.0f;
+            sorted_id[i] = 0x7fffffff;
+        }
+    }
+    if (penalised) {
+        int* cnt = counts + (size_t)r * vocab;
+        for (int i = begin + tid; i < end; i += kThreads) cnt[i] = 0;
+        __threadfence();
+        cluster.sync();
+        const int* h = history + (size_t)r * history_stride;
+        for (int j = part * kThreads + tid; j < history_len[r]; j += kSampleBlocks * kThreads) {
+            const int token = h[j];
+            if (token >= 0 && token < vocab) atomicAdd(&cnt[token], 1);
+        }
+        __threadfence();
+        cluster.sync();
+    }
+
+    // adjusted logits, and their first maximum
+    Best mine = {-CUDART_INF_F, 0x7fffffff};
+    for (int i = begin + tid; i < end; i += kThreads) {
+        float v = row[i];
+        if (penalised) {
+            const int c = counts[(size_t)r * vocab + i];
+            for (int n = 0; n < c; ++n) v = v > 0.0f ? v / pen : v * pen;
+        }
+        if (temp > 0.0f) v = v / temp;
+        w[i] = v;
+        if (v > mine.value) mine = {v, i};
+    }
+    {
+        const Best block = block_best(mine, best_scratch);
+        if (tid == 0) slot_best = block;
+    }
+    cluster.sync();
+    Best top = *cluster.map_shared_rank(&slot_best, 0);
+    for (int b = 1; b < kSampleBlocks; ++b) top = better(top, *cluster.map_shared_rank(&slot_best, b));
+    if (temp <= 0.0f) {
+        if (part == 0 && tid == 0) out[r] = top.index == 0x7fffffff ? 0 : top.index;
+        cluster.sync();  // nobody leaves while its shared memory may still be read
+        return;
+    }
+
+    // softmax over the whole vocabulary
+    float local = 0.0f;
+    for (int i = begin + tid; i < end; i += kThreads) {
+        const float e = expf(w[i] - top.value);
+        w[i] = e;
+        local += e;
+    }
+    {
+        const float block = block_sum(local, float_scratch);
+        if (tid == 0) slot_sum = block;
+    }
+    cluster.sync();
+    float sum = 0.0f;
+    for (int b = 0; b < kSampleBlocks; ++b) sum += *cluster.map_shared_rank(&slot_sum, b);
+    for (int i = begin + tid; i < end; i += kThreads) w[i] = w[i] / sum;
+    __syncthreads();
+
+    const float u = uniforms ? uniforms[r] : philox_uniform(seeds[r], counters[r]);
+    int k = top_k[r];
+    if (k <= 0 || k > vocab) k = vocab;
+    if (k > kMaxSorted) k = kMaxSorted;  // the host sends only rows that fit; never write past the arrays
+    const float nucleus = top_p[r];
+
+    // k-th largest probability by radix select over the float bit patterns (all are >= 0)
+    uint32_t kth_bits = 0;
+    int need_ties = 0, tie_count = 0;
+    if (k < vocab) {
+        uint32_t prefix = 0, mask = 0;
+        int remaining = k;
+        for (int pass = 3; pass >= 0; --pass) {
+            const int shift = pass * 8;
+            if (tid < 256) histogram[tid] = 0;
+            __syncthreads();
+            for (int i = begin + tid; i < end; i += kThreads) {
+                const uint32_t key = __float_as_uint(w[i]);
+                const bool counted = (key & mask) == prefix;
+                const uint32_t digit = (key >> shift) & 255u;
+                // lanes with the same digit add once: most of a row shares its leading digits
+                const unsigned peers = __match_any_sync(__activemask(), counted ? digit : 256u);
+                if (counted && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&histogram[digit], __popc(peers));
+            }
+            cluster.sync();
+            if (tid < 256) {
+                int total = 0;
+                for (int b = 0; b < kSampleBlocks; ++b) total += cluster.map_shared_rank(histogram, b)[tid];
+                histogram_all[tid] = total;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int cumulative = 0, digit = 0;
+                for (int b = 255; b >= 0; --b) {
+                    if (cumulative + histogram_all[b] >= remaining) {
+                        digit = b;
+                        break;
+                    }
+                    cumulative += histogram_all[b];
+                }
+                shared_int[0] = digit;
+                shared_int[1] = remaining - cumulative;
+                shared_int[2] = histogram_all[digit];
+            }
+            cluster.sync();  // every block has read every histogram before the next pass clears them
+            prefix |= (uint32_t)shared_int[0] << shift;
+            mask |= 255u << shift;
+            remaining = shared_int[1];
+            tie_count = shared_int[2];
+        }
+        kth_bits = prefix;
+        need_ties = remaining;
+    }
+
+    // gather the candidates into the first block
+    float* first_p = cluster.map_shared_rank(sorted_p, 0);
+    int* first_id = cluster.map_shared_rank(sorted_id, 0);
+    int* first_gathered = cluster.map_shared_rank(&gathered, 0);
+    const bool all_ties = (k == vocab) || tie_count == need_ties;
+    int my_ties = 0;
+    for (int i = begin + tid; i < end; i += kThreads) {
+        const uint32_t key = __float_as_uint(w[i]);
+        if (k == vocab || key > kth_bits || (all_ties && key == kth_bits)) {
+            const int at = atomicAdd(first_gathered, 1);
+            if (at < kMaxSorted) {
+                first_p[at] = w[i];
+                first_id[at] = i;
+            }
+        } else if (key == kth_bits) {
+            ++my_ties;
+        }
+    }
+    if (!all_ties) {
+        // more tokens tie at the k-th probability than fit: the lower ids go in.  Blocks own ascending id
+        // ranges, so a block's ties rank after all ties of the blocks before it.
+        __syncthreads();
+        int_scratch[0] = 0;
+        __syncthreads();
+        if (my_ties) atomicAdd(&int_scratch[0], my_ties);
+        __syncthreads();
+        if (tid == 0) slot_ties = int_scratch[0];
+        cluster.sync();  // all candidates above the k-th are in; the tie counts are known
+        int taken = 0;
+        for (int b = 0; b < part; ++b) taken += *cluster.map_shared_rank(&slot_ties, b);
+        const int base_count = *first_gathered;
+        for (int base = begin; base < end && taken < need_ties; base += kThreads) {
+            const int i = base + tid;
+            const bool tie = i < end && __float_as_uint(w[i]) == kth_bits;
+            int chunk_total;
+            const int rank = taken + block_flag_scan(tie, int_scratch, &chunk_total);
+            if (tie && rank < need_ties && base_count + rank < kMaxSorted) {
+                first_p[base_count + rank] = w[i];
+                first_id[base_count + rank] = i;
+            }
+            taken += chunk_total;
+        }
+    }
+    cluster.sync();  // the first block's arrays are complete; the others are done
+    if (part != 0) return;
+    sort_and_pick(sorted_p, sorted_id, k, nucleus, u, out + r);
+}
+
 }  // namespace mb
 
 using namespace mb;
@@ -412,15 +624,36 @@ MB_EXPORT int mb_argmax_rows(const float* logits, int row_stride, int rows, int 
 // Per-row arrays live on the device.  `uniforms` (optional) overrides the generator, for tests.
 // The host guarantees top_p == 1 for rows whose candidate count (top_k, or the vocabulary when
 // top_k <= 0) exceeds `mb_sample_max_sorted()`.
+// max_candidates: the host's bound on min(top_k, vocab) over the rows (0: unknown).  Rows that all keep at most
+// mb_sample_max_sorted() candidates take the kernel that spreads a row over a cluster of blocks.
 MB_EXPORT int mb_sample_rows(const float* logits, int row_stride, int rows, int vocab, float* work, int* counts,
                              const float* temperature, const int* top_k, const float* top_p, const float* penalty,
                              const int* history, int history_stride, const int* history_len,
                              const unsigned long long* seeds, const unsigned long long* counters,
-                             const float* uniforms, int* out, cudaStream_t stream) {
+                             const float* uniforms, int* out, int max_candidates, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0 || row_stride < vocab) return fail("sample_rows: vocab %d, row stride %d", vocab, row_stride);
     if (!work) return fail("sample_rows: needs rows * vocab floats of scratch");
     if (!uniforms && (!seeds || !counters)) return fail("sample_rows: needs seeds and counters, or uniforms");
+    if (max_candidates > 0 && max_candidates <= kMaxSorted) {
+        if (rows > 65535) return fail("sample_rows: %d rows exceed the grid limit 65535", rows);
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(kSampleBlocks, rows);
+        config.blockDim = dim3(kThreads);
+        config.stream = stream;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = kSampleBlocks;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        cudaError_t status = cudaLaunchKernelEx(&config, sample_rows_cluster_kernel, logits, row_stride, vocab, work, counts,
+                                                temperature, top_k, top_p, penalty, history, history_stride, history_len, seeds,
+                                                counters, uniforms, out);
+        if (status != cudaSuccess) return fail("sample_rows: launch failed: %s", cudaGetErrorString(status));
+        return check_launch("sample_rows");
+    }
     sample_rows_kernel<<<rows, kThreads, 0, stream>>>(logits, row_stride, vocab, work, counts, temperature, top_k, top_p,
                                                       penalty, history, history_stride, history_len, seeds, counters,
                                                       uniforms, out);

@@ -587,7 +587,11 @@ def sample_max_sorted() -> int:
 def sample_rows(logits: torch.Tensor, work: torch.Tensor, counts: Optional[torch.Tensor], temperature: torch.Tensor,
                 top_k: torch.Tensor, top_p: torch.Tensor, penalty: torch.Tensor, history: Optional[torch.Tensor],
                 history_len: Optional[torch.Tensor], seeds: Optional[torch.Tensor], counters: Optional[torch.Tensor],
-                uniforms: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                uniforms: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                max_candidates: int = 0) -> torch.Tensor:
+    """One token per row of `logits` by the sampling pipeline.  `max_candidates`: the caller's bound on
+    min(top_k, vocabulary) over the rows, 0 if it has none; when every row keeps at most
+    sample_max_sorted() candidates a row is spread over a cluster of blocks instead of one block."""
     _cuda(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters, uniforms)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("sample_rows takes float32 [rows, vocab] logits")
@@ -610,5 +614,5 @@ def sample_rows(logits: torch.Tensor, work: torch.Tensor, counts: Optional[torch
     _run(lib, lib.mb_sample_rows(_p(logits), logits.stride(0), rows, vocab, _p(work), _p(counts), _p(temperature),
                                  _p(top_k), _p(top_p), _p(penalty), _p(history),
                                  history.stride(0) if history is not None else 0, _p(history_len), _p(seeds),
-                                 _p(counters), _p(uniforms), _p(out), _stream()))
+                                 _p(counters), _p(uniforms), _p(out), int(max_candidates), _stream()))
     return out

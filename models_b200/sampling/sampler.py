@@ -70,7 +70,9 @@ class BatchSampler:
             history, history_len = host.to(self.device), lens.to(self.device)
             counts = torch.empty((rows, self.vocab), dtype=torch.int32, device=self.device)
         work = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.device)
-        out = ops.sample_rows(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters)
+        most = max(min(r.options.top_k, self.vocab) if r.options.top_k > 0 else self.vocab for r in requests)
+        out = ops.sample_rows(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters,
+                              max_candidates=most)
         for r in requests:
             if r.options.temperature > 0.0:
                 r.draws += 1

@@ -181,6 +181,54 @@ def test_sampling_kernel_follows_the_reference_pipeline(cuda_device, vocab):
         BatchSampler(5003, "cuda:0").check(SamplingOptions(top_k=2000, top_p=0.9))
 
 
+@pytest.mark.parametrize("vocab", [5003, 128256])
+def test_sampling_over_a_cluster_follows_the_reference_pipeline(cuda_device, vocab):
+    """Rows that keep at most 1,024 candidates are spread over a cluster of blocks: the same pipeline,
+    at vocabularies that do not divide by the cluster size, with more tokens tied at the k-th
+    probability than fit (the lower ids go in; they straddle two blocks' id ranges), a penalised
+    history, and greedy rows in the same batch."""
+    from models_b200.sampling import BatchSampler, RequestSampling, SamplingOptions, philox_uniform
+
+    g = torch.Generator().manual_seed(vocab + 1)
+    sampler = BatchSampler(vocab, "cuda:0")
+    cases = [
+        SamplingOptions(temperature=1.0, top_k=40, top_p=0.9, seed=1),
+        SamplingOptions(temperature=0.7, top_k=5, top_p=1.0, seed=2),
+        SamplingOptions(temperature=1.3, top_k=1000, top_p=0.5, seed=3),
+        SamplingOptions(temperature=0.0, repetition_penalty=1.5, seed=4),
+        SamplingOptions(temperature=1.1, top_k=50, top_p=1.0, seed=5),    # the row with the wide tie
+        SamplingOptions(temperature=1.0, top_k=12, top_p=0.8, repetition_penalty=1.3, seed=6),
+        SamplingOptions(temperature=0.0, seed=7),
+        SamplingOptions(temperature=0.6, top_k=1024, top_p=0.97, seed=8),
+    ]
+    prompt = [int(t) for t in torch.randint(0, vocab, (25,), generator=g)] + [3, 3, 3]
+    requests = [RequestSampling(o, prompt) for o in cases]
+    boundary = -(-vocab // 8)  # the first id of the second block
+    for step in range(5):
+        logits = torch.randn(len(cases), vocab, generator=g) * 3
+        logits[:, 3] = 6.0
+        logits[0, 10] = logits[0, 11] = logits[0, 12] = 5.0
+        logits[4, :] = torch.randn(vocab, generator=g).clamp(max=2.0)
+        logits[4, 7:37] = 9.0 + torch.arange(30).float() * 0.01  # 30 clear leaders ...
+        logits[4, boundary - 40:boundary + 40] = 8.0                # ... and 80 tokens tied for the other 20 places
+        draws = [r.draws for r in requests]
+        got = sampler.sample(logits.cuda(), requests).tolist()
+        for row, (o, r) in enumerate(zip(cases, requests)):
+            if o.temperature == 0.0:
+                adjusted = logits[row].clone()
+                if o.repetition_penalty > 1.0:
+                    for t in r.history:
+                        adjusted[t] = adjusted[t] / o.repetition_penalty if adjusted[t] > 0 else adjusted[t] * o.repetition_penalty
+                assert got[row] == plain_llama.plain_argmax(adjusted), (step, row)
+                continue
+            u = philox_uniform(r.seed, draws[row])
+            want, ids = expected_draw(logits[row].numpy(), r.history or [], o, u)
+            if row == 4:
+                assert sorted(ids)[30:] == list(range(boundary - 40, boundary - 20)), "the plain pipeline keeps the lower ids"
+            assert got[row] == want, (step, row, got[row], want)
+        BatchSampler.record(requests, got)
+
+
 def test_sampling_is_reproducible_and_follows_the_distribution(cuda_device):
     import models_b200
     from models_b200.sampling import BatchSampler, RequestSampling, SamplingOptions
