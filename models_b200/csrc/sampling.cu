@@ -146,14 +146,16 @@ argmax_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
 }
 
 // The candidates (probability, id) in shared memory, unused entries (-1, max int): sorted by probability
-// descending and id ascending (bitonic, all kMaxSorted entries), cut at the shortest prefix whose mass
+// descending and id ascending (bitonic over the smallest power of two that holds k), cut at the shortest prefix whose mass
 // reaches `nucleus` (crossing token included), then the inverse-CDF draw r = u * kept mass.
 __device__ void sort_and_pick(float* sorted_p, int* sorted_id, int k, float nucleus, float u, int* out) {
     const int tid = threadIdx.x;
-    for (int size = 2; size <= kMaxSorted; size <<= 1) {
+    int span = 32;  // the candidates lie in the first k entries: a power of two that holds them is all that is sorted
+    while (span < k) span <<= 1;
+    for (int size = 2; size <= span; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             const int partner = tid ^ stride;
-            if (partner > tid) {
+            if (partner > tid && partner < span) {
                 const bool descending_block = (tid & size) == 0;
                 const float pa = sorted_p[tid], pb = sorted_p[partner];
                 const int ia = sorted_id[tid], ib = sorted_id[partner];
@@ -176,9 +178,7 @@ __device__ void sort_and_pick(float* sorted_p, int* sorted_id, int k, float nucl
                 break;
             }
         }
-        float total = 0.0f;
-        for (int i = 0; i < cutoff; ++i) total += sorted_p[i];
-        const float target = u * total;
+        const float target = u * cumulative;  // the kept mass: the same additions in the same order
         float acc = 0.0f;
         int pick = sorted_id[cutoff - 1];
         for (int i = 0; i < cutoff; ++i) {
@@ -496,8 +496,57 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
     const float u = uniforms ? uniforms[r] : philox_uniform(seeds[r], counters[r]);
     int k = top_k[r];
     if (k <= 0 || k > vocab) k = vocab;
-    if (k > kMaxSorted) k = kMaxSorted;  // the host sends only rows that fit; never write past the arrays
     const float nucleus = top_p[r];
+
+    if (k == vocab && nucleus >= 1.0f && vocab > kMaxSorted) {
+        // Nothing is cut: the draw walks the whole vocabulary in id order (the same distribution as walking it by
+        // probability).  The blocks' masses are added in block order; the block whose range holds the target walks
+        // its ids, 1,024 at a time.
+        float mass = 0.0f;
+        for (int i = begin + tid; i < end; i += kThreads) mass += w[i];
+        {
+            const float block = block_sum(mass, float_scratch);
+            __syncthreads();
+            if (tid == 0) slot_sum = block;
+        }
+        cluster.sync();
+        float prefix[kSampleBlocks + 1];
+        prefix[0] = 0.0f;
+        for (int b = 0; b < kSampleBlocks; ++b) prefix[b + 1] = prefix[b] + *cluster.map_shared_rank(&slot_sum, b);
+        const float target = u * prefix[kSampleBlocks];
+        int owner = 0;  // the first block whose range reaches the target; else the last block that has ids
+        for (int b = 0; b < kSampleBlocks; ++b) {
+            if (min(vocab, b * slice) >= min(vocab, (b + 1) * slice)) continue;  // no ids
+            owner = b;
+            if (prefix[b + 1] >= target) break;
+        }
+        const float before = prefix[owner];
+        cluster.sync();  // every block has read every mass
+        if (part != owner) return;
+        if (tid == 0) {
+            shared_int[1] = 0x7fffffff;  // lowest id whose running mass reaches the target
+            shared_int[2] = -1;          // highest id with any mass, taken if rounding leaves the target unreached
+        }
+        __syncthreads();
+        int last_kept = -1;
+        for (int i = begin + tid; i < end; i += kThreads)
+            if (w[i] > 0.0f) last_kept = i;
+        if (last_kept >= 0) atomicMax(&shared_int[2], last_kept);
+        float running = before;
+        for (int base = begin; base < end; base += kThreads) {
+            const int i = base + tid;
+            const float v = i < end ? w[i] : 0.0f;
+            float chunk_total;
+            const float inclusive = running + block_float_scan(v, float_scratch, &chunk_total);
+            if (v > 0.0f && inclusive >= target) atomicMin(&shared_int[1], i);
+            running += chunk_total;  // the same value in every thread
+            if (running >= target) break;
+        }
+        __syncthreads();
+        if (tid == 0) out[r] = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
+        return;
+    }
+    if (k > kMaxSorted) k = kMaxSorted;  // the host sends only rows that fit; never write past the arrays
 
     // k-th largest probability by radix select over the float bit patterns (all are >= 0)
     uint32_t kth_bits = 0;
@@ -624,8 +673,9 @@ MB_EXPORT int mb_argmax_rows(const float* logits, int row_stride, int rows, int 
 // Per-row arrays live on the device.  `uniforms` (optional) overrides the generator, for tests.
 // The host guarantees top_p == 1 for rows whose candidate count (top_k, or the vocabulary when
 // top_k <= 0) exceeds `mb_sample_max_sorted()`.
-// max_candidates: the host's bound on min(top_k, vocab) over the rows (0: unknown).  Rows that all keep at most
-// mb_sample_max_sorted() candidates take the kernel that spreads a row over a cluster of blocks.
+// max_candidates: the host's bound on min(top_k, vocab) over the rows that cut anything (a row with top_k >= vocab and
+// top_p >= 1 cuts nothing and does not count); 0: unknown.  When it is at most mb_sample_max_sorted(), the rows take the
+// kernel that spreads a row over a cluster of blocks.
 MB_EXPORT int mb_sample_rows(const float* logits, int row_stride, int rows, int vocab, float* work, int* counts,
                              const float* temperature, const int* top_k, const float* top_p, const float* penalty,
                              const int* history, int history_stride, const int* history_len,

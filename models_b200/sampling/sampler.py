@@ -70,7 +70,9 @@ class BatchSampler:
             history, history_len = host.to(self.device), lens.to(self.device)
             counts = torch.empty((rows, self.vocab), dtype=torch.int32, device=self.device)
         work = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.device)
-        most = max(min(r.options.top_k, self.vocab) if r.options.top_k > 0 else self.vocab for r in requests)
+        # the largest candidate set among the rows that cut anything (1 if none does): it picks the kernel
+        most = max([min(r.options.top_k, self.vocab) for r in requests
+                    if r.options.top_k < self.vocab or r.options.top_p < 1.0] or [1])
         out = ops.sample_rows(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters,
                               max_candidates=most)
         for r in requests:

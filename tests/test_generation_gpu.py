@@ -200,6 +200,7 @@ def test_sampling_over_a_cluster_follows_the_reference_pipeline(cuda_device, voc
         SamplingOptions(temperature=1.0, top_k=12, top_p=0.8, repetition_penalty=1.3, seed=6),
         SamplingOptions(temperature=0.0, seed=7),
         SamplingOptions(temperature=0.6, top_k=1024, top_p=0.97, seed=8),
+        SamplingOptions(temperature=0.9, top_k=vocab, top_p=1.0, seed=9),  # nothing cut: drawn in id order
     ]
     prompt = [int(t) for t in torch.randint(0, vocab, (25,), generator=g)] + [3, 3, 3]
     requests = [RequestSampling(o, prompt) for o in cases]
@@ -225,8 +226,23 @@ def test_sampling_over_a_cluster_follows_the_reference_pipeline(cuda_device, voc
             want, ids = expected_draw(logits[row].numpy(), r.history or [], o, u)
             if row == 4:
                 assert sorted(ids)[30:] == list(range(boundary - 40, boundary - 20)), "the plain pipeline keeps the lower ids"
+            if o.top_k >= vocab:
+                # the walk in id order: the token at which the running mass (ascending id) reaches u
+                p = torch.softmax(logits[row].double() / o.temperature, 0)
+                running = torch.cumsum(p, 0)
+                at = int(torch.searchsorted(running, torch.tensor(float(u), dtype=torch.float64)))
+                assert abs(got[row] - at) <= 1 or abs(float(running[got[row]]) - float(u)) < 1e-4, (step, row, got[row], at)
+                continue
             assert got[row] == want, (step, row, got[row], want)
         BatchSampler.record(requests, got)
+    # the full-vocabulary draw follows the distribution
+    few = torch.full((1, vocab), -40.0)
+    few[0, [5, boundary + 3, vocab - 1]] = torch.tensor([1.0, 2.0, 0.0])
+    request = RequestSampling(SamplingOptions(temperature=1.0, top_k=vocab, top_p=1.0, seed=21), [0])
+    drawn = torch.tensor([sampler.sample(few.cuda(), [request]).item() for _ in range(600)])
+    expected = torch.softmax(torch.tensor([1.0, 2.0, 0.0]), 0)
+    seen = torch.tensor([(drawn == 5).sum(), (drawn == boundary + 3).sum(), (drawn == vocab - 1).sum()]).float() / 600
+    assert float(seen.sum()) == 1.0 and float((seen - expected).abs().max()) < 0.07, seen
 
 
 def test_sampling_is_reproducible_and_follows_the_distribution(cuda_device):
