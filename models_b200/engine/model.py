@@ -82,7 +82,7 @@ class DecoderModel:
         if batch.num_wanted == 0:
             return None
         if (pending is None and self.runtime.mode == "bfloat16" and getattr(self.final_norm, "foldable", False)
-                and ops.skinny_takes(self.head_weight, batch.num_wanted, with_norm=True)):
+                and ops.skinny_pays(self.head_weight, batch.num_wanted, with_norm=True)):
             # few wanted rows: gather, final norm and output product in one kernel
             return ops.skinny_gemm(self.head_weight, ops.EPI_F32, xf=x, gain=self.final_norm.weight,
                                    eps=self.final_norm.spec.eps, rows=batch.want_rows)

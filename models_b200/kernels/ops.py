@@ -350,6 +350,17 @@ def skinny_takes(weight: torch.Tensor, rows: int, with_norm: bool = False) -> bo
             and 0 < rows <= (SKINNY_NORM_ROWS if with_norm else SKINNY_ROWS))
 
 
+SKINNY_PAYS_ROWS = 8  # one 8-column MMA tile of activations: beyond it a block's activations crowd out its weight rings
+
+
+def skinny_pays(weight: torch.Tensor, rows: int, with_norm: bool = False) -> bool:
+    """Whether the decode matrix product is the one to use: it takes up to 32 rows, but with more than 8
+    its blocks hold twice the activations in shared memory, half as many of them fit a multiprocessor,
+    and a library product streams the weights faster (measured at 16 and 32 rows on every layer shape
+    of the 1B, 3B and 8B models)."""
+    return rows <= SKINNY_PAYS_ROWS and skinny_takes(weight, rows, with_norm)
+
+
 _multiprocessors = {}
 
 

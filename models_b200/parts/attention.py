@@ -75,7 +75,7 @@ class AttentionMixer(Mixer):
     def folds(self, rows: int, norm) -> bool:
         """Whether `forward_residual` applies: bfloat16 weights, few rows, no biases, a foldable norm."""
         return (self.b_qkv is None and self.b_o is None and getattr(norm, "foldable", False)
-                and ops.skinny_takes(self.w_qkv, rows, with_norm=True) and ops.skinny_takes(self.w_o, rows))
+                and ops.skinny_pays(self.w_qkv, rows, with_norm=True) and ops.skinny_pays(self.w_o, rows))
 
     def forward_residual(self, x: torch.Tensor, norm, batch, run: RunContext) -> None:
         """x += Wo . attention(rotate(Wqkv . norm(x))): the norm rides in the q/k/v product, the

@@ -52,7 +52,7 @@ class GatedFeedForward(Part):
     def folds(self, rows: int, norm) -> bool:
         """Whether `forward_residual` applies: bfloat16 weights, few rows, no biases, a foldable norm."""
         return (self.b_gate_up is None and self.b_down is None and getattr(norm, "foldable", False)
-                and ops.skinny_takes(self.w_gate_up, rows, with_norm=True) and ops.skinny_takes(self.w_down, rows))
+                and ops.skinny_pays(self.w_gate_up, rows, with_norm=True) and ops.skinny_pays(self.w_down, rows))
 
     def forward_residual(self, x: torch.Tensor, norm) -> None:
         """x += down(silu(gate(norm(x))) * up(norm(x))) in two kernels: norm, gate/up product and
@@ -75,7 +75,7 @@ class GatedFeedForward(Part):
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
-        if self.b_gate_up is None and ops.skinny_takes(self.w_gate_up, xn.shape[0]) and xn.dtype == torch.bfloat16:
+        if self.b_gate_up is None and ops.skinny_pays(self.w_gate_up, xn.shape[0]) and xn.dtype == torch.bfloat16:
             hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, x=xn)
             delta = linear(hidden, self.w_down, dtype)
             if self.b_down is not None:

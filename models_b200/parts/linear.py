@@ -28,7 +28,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> tor
     if weight.dtype != torch.bfloat16:
         raise ops.KernelError(f"matrices are bfloat16 or float32, got {weight.dtype}")
     a = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
-    if ops.skinny_takes(weight, a.shape[0]) and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 \
+    if ops.skinny_pays(weight, a.shape[0]) and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 \
             and out_dtype in (torch.bfloat16, torch.float32):
         # decode: few rows, the weights stream once through this package's own kernel
         return ops.skinny_gemm(weight, ops.EPI_F32 if out_dtype == torch.float32 else ops.EPI_BF16, x=a)
