@@ -2,7 +2,7 @@
 """Benchmark of models_b200 on one B200: decode tokens per second of Llama 3.2 1B (bfloat16, random
 weights, synthetic token ids), with prefill and roofline figures on the same JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 1b|3b|8b] [--batch B] [--layers L] [--impl ours|reference]
 
 A "step" is one decode step of the whole batch.  `value` is device-timed (CUDA events around K
 steps); `e2e` is the same rate through the Python entry point (`generate_batch`: host token ids in,
@@ -48,6 +48,22 @@ LLAMA_3_2_1B = {
 CONTEXT = 4096
 PROMPT_TOKENS = 512
 PREFILL_TOKENS = 2048
+
+# The other two workloads of the baseline file (--model 3b / 8b); the default run is the 1B one.
+LLAMA_3_2_3B = dict(LLAMA_3_2_1B, num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8,
+                    head_dim=128, intermediate_size=8192)
+LLAMA_3_1_8B = dict(LLAMA_3_2_1B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                    head_dim=128, intermediate_size=14336, tie_word_embeddings=False,
+                    rope_scaling=dict(LLAMA_3_2_1B["rope_scaling"], factor=8.0))
+WORKLOADS = {
+    # prompt: a length, or (shortest, longest) for unequal prompts; context: positions per sequence the cache is sized for
+    "1b": {"config": LLAMA_3_2_1B, "name": "Llama 3.2 1B (LlamaForCausalLM)", "batch": 8, "prompt": PROMPT_TOKENS,
+           "context": CONTEXT, "steps": 256, "prefill": PREFILL_TOKENS, "points": (1, 64)},
+    "3b": {"config": LLAMA_3_2_3B, "name": "Llama 3.2 3B (LlamaForCausalLM)", "batch": 16, "prompt": (128, 2048),
+           "context": 2048 + 192, "steps": 128, "prefill": PREFILL_TOKENS, "points": ()},
+    "8b": {"config": LLAMA_3_1_8B, "name": "Llama 3.1 8B-shaped (LlamaForCausalLM)", "batch": 64, "prompt": 1024,
+           "context": 1024 + 320, "steps": 256, "prefill": 16384, "points": ()},
+}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -141,21 +157,23 @@ def prefill_flops(c, layers, tokens):
     return gemm + attention
 
 
-def make_model(config, max_batch):
+def make_model(config, max_batch, context=CONTEXT):
     import models_b200
 
-    return models_b200.load_model(config=config, seed=0, dtype="bfloat16", max_batch=max_batch, context=CONTEXT)
+    return models_b200.load_model(config=config, seed=0, dtype="bfloat16", max_batch=max_batch, context=context)
 
 
 def random_prompts(n, length, vocab, seed):
+    """n prompts of `length` tokens each, or of lengths drawn from (shortest, longest)."""
     import numpy as np
 
     rng = np.random.default_rng(seed)
-    return [[int(t) for t in rng.integers(0, vocab, size=length)] for _ in range(n)]
+    lengths = [length] * n if isinstance(length, int) else [int(x) for x in rng.integers(length[0], length[1] + 1, size=n)]
+    return [[int(t) for t in rng.integers(0, vocab, size=m)] for m in lengths]
 
 
-def device_decode(model, batch, steps, warmup, sample_clocks=False):
-    """K decode steps of `batch` sequences after 512-token prompts, greedy, timed on the device.
+def device_decode(model, batch, steps, warmup, sample_clocks=False, prompt=PROMPT_TOKENS):
+    """K decode steps of `batch` sequences after their prompts (512 tokens each in the default run), greedy, timed on the device.
     As in generation, a step is queued with the ids of the step before it still on the device, and
     the host reads every step's ids while the next step runs."""
     import torch
@@ -167,7 +185,7 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False):
 
     engine = model.engine
     vocab = engine.spec.vocab_size
-    prompts = random_prompts(batch, PROMPT_TOKENS, vocab, 1)
+    prompts = random_prompts(batch, prompt, vocab, 1)
     stepper = EngineStepper(engine)
     greedy = [RequestSampling(SamplingOptions(temperature=0.0), p) for p in prompts]
     rows = list(range(batch))
@@ -201,13 +219,13 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False):
             "kv_tokens_per_step": kv_total / steps, "launches": launches, "clocks": clocks}
 
 
-def e2e_decode(model, batch, steps, warmup):
+def e2e_decode(model, batch, steps, warmup, prompt=PROMPT_TOKENS):
     """The same through generate_batch: host ids in, host ids out; rate over the decode steps
     (tokens after each request's first, as integrallis/models' TrialMeasurement counts them)."""
     from models_b200 import SamplingOptions
 
     vocab = model.metadata.vocab_size
-    prompts = random_prompts(batch, PROMPT_TOKENS, vocab, 2)
+    prompts = random_prompts(batch, prompt, vocab, 2)
     stamps = []
 
     def on_token(index, token):
@@ -250,14 +268,16 @@ def device_prefill(model, tokens, repeats=3):
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=256)  # the workload's 256 generated tokens
+    parser.add_argument("--steps", type=int, default=None, help="decode steps timed (default: the workload's generated tokens)")
     parser.add_argument("--warmup", type=int, default=8)
-    parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=LLAMA_3_2_1B["num_hidden_layers"])
+    parser.add_argument("--model", default="1b", choices=sorted(WORKLOADS),
+                        help="1b: the default run; 3b, 8b: the other two workloads of the baseline file")
+    parser.add_argument("--batch", type=int, default=None, help="sequences decoded together (default: the workload's)")
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both counts are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
     parser.add_argument("--only-prefill", action="store_true",
-                        help="run the 2,048-token prefill alone and print its figures (for profiling)")
+                        help="run the workload's prefill alone and print its figures (for profiling)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -269,27 +289,42 @@ def main() -> int:
         print(f"bench.py measures one GPU: this library runs on a single GPU and --gpus {args.gpus} is not built")
         return 2
     warmup = max(args.warmup, 3)
+    work = WORKLOADS[args.model]
+    batch = args.batch or work["batch"]
+    steps = args.steps or work["steps"]
+    layers = args.layers or work["config"]["num_hidden_layers"]
+    prompt, context, prefill_tokens = work["prompt"], work["context"], work["prefill"]
+    longest_prompt = prompt if isinstance(prompt, int) else prompt[1]
+    if longest_prompt + warmup + steps + 1 > context:
+        print(f"bench.py: {longest_prompt} prompt tokens + {warmup} + {steps} steps do not fit the context of {context}")
+        return 2
 
     import torch
 
-    config = dict(LLAMA_3_2_1B, num_hidden_layers=args.layers)
+    config = dict(work["config"], num_hidden_layers=layers)
     peak = peaks()
-    model = make_model(config, args.batch if (args.no_points or args.only_prefill) else max(64, args.batch))
     if args.only_prefill:
-        ms = device_prefill(model, PREFILL_TOKENS, repeats=1)
-        print(json.dumps({"prefill_ms": ms, "tokens": PREFILL_TOKENS}))
+        model = make_model(config, 1, max(context, prefill_tokens + 64))
+        ms = device_prefill(model, prefill_tokens, repeats=1)
+        print(json.dumps({"prefill_ms": ms, "tokens": prefill_tokens}))
         return 0
-    main_run = device_decode(model, args.batch, args.steps, warmup, sample_clocks=True)
-    e2e = e2e_decode(model, args.batch, args.steps, warmup)
-    bytes_per_step = decode_bytes(config, args.layers, main_run["kv_tokens_per_step"])
+    with_points = not args.no_points
+    # the prefill fits the decode cache when it is no longer than a sequence's context; else it gets a model of its own
+    prefill_fits = prefill_tokens + 64 <= context
+    sequences = max([batch] + (list(work["points"]) if with_points else []))
+    model = make_model(config, sequences, context)
+    main_run = device_decode(model, batch, steps, warmup, sample_clocks=True, prompt=prompt)
+    e2e = e2e_decode(model, batch, steps, warmup, prompt=prompt)
+    bytes_per_step = decode_bytes(config, layers, main_run["kv_tokens_per_step"])
     achieved = bytes_per_step / (main_run["ms_per_step"] / 1e3) / 1e9
+    weights_gb = decode_bytes(config, layers, 0) / 1e9
 
     line = {
-        "metric": "decode tok/s @ batch 8 (Llama 3.2 1B, bf16)",
+        "metric": f"decode tok/s @ batch {batch} ({work['name'].split(' (')[0]}, bf16)",
         "value": main_run["tokens_per_second"],
         "unit": "tokens/s",
         "n_gpus": 1,
-        "steps": args.steps,
+        "steps": steps,
         "warmup": warmup,
         "ms_per_step": main_run["ms_per_step"],
         "higher_is_better": True,
@@ -299,24 +334,24 @@ def main() -> int:
         "data": "synthetic: seeded uniform-random token ids, random weights N(0, 0.02)",
         "impl": "ours",
         "config": {
-            "model": "Llama 3.2 1B (LlamaForCausalLM)",
-            "layers": args.layers,
-            "layers_of_model": LLAMA_3_2_1B["num_hidden_layers"],
+            "model": work["name"],
+            "layers": layers,
+            "layers_of_model": work["config"]["num_hidden_layers"],
             "hidden_size": config["hidden_size"],
             "heads": config["num_attention_heads"],
             "kv_heads": config["num_key_value_heads"],
             "head_dim": config["head_dim"],
             "intermediate_size": config["intermediate_size"],
             "vocab_size": config["vocab_size"],
-            "tied_embeddings": True,
-            "global_batch": args.batch,
-            "context_len": CONTEXT,
-            "prompt_len": PROMPT_TOKENS,
-            "seq_len": PROMPT_TOKENS + warmup + args.steps,
+            "tied_embeddings": bool(config["tie_word_embeddings"]),
+            "global_batch": batch,
+            "context_len": context,
+            "prompt_len": prompt if isinstance(prompt, int) else f"{prompt[0]}..{prompt[1]} (unequal)",
+            "seq_len": longest_prompt + warmup + steps,
             "parallelism": "single GPU",
             "sampling": "greedy",
             "cache": "paged, 64 positions per page, bf16",
-            "l2": "each step reads ~2.5 GB of weights (> 126 MB L2); no flush needed",
+            "l2": f"each step reads ~{weights_gb:.1f} GB of weights (> 126 MB L2); no flush needed",
             "peaks": peak["source"],
         },
         "e2e": {"value": e2e["tokens_per_second"], "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
@@ -326,15 +361,21 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peak["hbm_gbs"], "bytes_per_step": bytes_per_step},
     }
-    if not args.no_points:
-        ms = device_prefill(model, PREFILL_TOKENS)
-        flops = prefill_flops(config, args.layers, PREFILL_TOKENS)
-        line["prefill"] = {"value": PREFILL_TOKENS / (ms / 1e3), "tokens": PREFILL_TOKENS, "ms": ms,
-                           "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+    if with_points:
         points = {}
-        for b in (1, 64):
-            points[f"decode_b{b}"] = device_decode(model, b, min(args.steps, 64), warmup)["tokens_per_second"]
-        line["points"] = points
+        for b in work["points"]:
+            points[f"decode_b{b}"] = device_decode(model, b, min(steps, 64), warmup, prompt=prompt)["tokens_per_second"]
+        if points:
+            line["points"] = points
+        if not prefill_fits:
+            model.close()
+            del model
+            torch.cuda.empty_cache()
+            model = make_model(config, 1, prefill_tokens + 64)
+        ms = device_prefill(model, prefill_tokens)
+        flops = prefill_flops(config, layers, prefill_tokens)
+        line["prefill"] = {"value": prefill_tokens / (ms / 1e3), "tokens": prefill_tokens, "ms": ms,
+                           "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
     print(json.dumps(line))
     return 0
 
