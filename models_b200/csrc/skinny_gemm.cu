@@ -18,13 +18,13 @@
 // Layout of the work.  A block of four warps owns 16 weight rows at a time and walks a sequence of
 // such row tiles; its warps split the
 // block's part of K.  Each warp streams its rows with cp.async through a private four-stage ring in
-// shared memory, 64 columns per stage, and the stages run on across row tiles, so loads stay in flight
+// shared memory, 128 columns per stage, and the stages run on across row tiles, so loads stay in flight
 // from the first tile to the last.  The activations of the block's part of K are staged once, as
 // bfloat16, in shared memory.  At the end of a row tile the warps' partial sums are added in warp
-// order.  When a matrix has too few row tiles to occupy the GPU, K is also split over the blocks of a
-// thread-block cluster (up to 8); their partial sums meet in the shared memory of the cluster's first
-// block (distributed shared memory) and are added there in block order, so no result depends on
-// timing.
+// order.  When the activations of all of K do not fit a block's shared memory (many rows, or a long
+// K), K is also split over the blocks of a thread-block cluster (up to 8); their partial sums meet in
+// the shared memory of the cluster's first block (distributed shared memory) and are added there in
+// block order, so no result depends on timing.
 //
 // The kernel is launched as a programmatic dependent of the kernel before it: its blocks may start
 // while that kernel drains, and they fill their weight rings (weights are never written) before they
@@ -443,8 +443,9 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     if (epilogue == EPI_SWIGLU) args.n = n / 2;
     // Planning.  A block's shared memory holds its activations (rows x k_unit bfloat16), the warps' rings
     // and the partial sums; as many blocks as fit stay resident per multiprocessor (at most four).
-    // With fewer row tiles than resident blocks, K is split over a cluster (a warp keeps at least 256
-    // columns); with more, blocks walk several row tiles.
+    // K is split over a cluster only when a block's activations would not fit otherwise: splitting it
+    // to fill idle multiprocessors was measured and lost to the cluster barrier it adds.  Blocks walk
+    // several row tiles when there are more tiles than resident blocks.
     const int rows_total = (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE) ? n / 2 : n;
     const int tiles = (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE) ? (rows_total + 7) / 8 : (rows_total + 15) / 16;
     const int cols = batch <= 8 ? 8 : (batch <= 16 ? 16 : 32);
@@ -459,7 +460,6 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     };
     int split = 1;
     while (split < 8 && smem_for(split) > 200 * 1024) split *= 2;
-    while (split < 8 && tiles * split * 2 <= resident_for(split * 2) && k / (split * 2) >= 256 * kWarps) split *= 2;
     if (smem_for(split) > 200 * 1024)
         return fail("skinny_gemm: %d activation rows of %d columns do not fit shared memory", batch, k);
     args.k_split = split;
