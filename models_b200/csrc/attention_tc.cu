@@ -38,6 +38,14 @@ constexpr int kChunks = HD / 8;           // 16-byte pieces of a row
 constexpr int kKSteps = HD / 16;
 constexpr int kThreads = 128;
 constexpr int kQRowsDecode = 16;
+// Pages of keys and values in shared memory per decode block.  Measured at 64 sequences of 1,280 positions: with heads
+// of 128 a third stage takes the kernel from 4.3 to 5.2 TB/s; with heads of 64 (pages half as large, five blocks per
+// multiprocessor with two stages, four with three) it loses a fifth.
+#ifndef MB_DECODE_STAGES
+#define MB_DECODE_STAGES (MB_HEAD_DIM >= 96 ? 3 : 2)
+#endif
+constexpr int kDecodeStages = MB_DECODE_STAGES;
+static_assert(kDecodeStages >= 2, "at least one page in flight while one is worked on");
 constexpr int kQRowsPrefill = 64;
 
 using bf16 = __nv_bfloat16;
@@ -170,7 +178,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     if (!kCluster) grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* q_smem = smem;                                 // 16 rows
-    unsigned char* stage_smem = smem + kQRowsDecode * kRowBytes;  // 2 stages x (K tile, V tile)
+    unsigned char* stage_smem = smem + kQRowsDecode * kRowBytes;  // kDecodeStages x (K tile, V tile)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
     const int split = blockIdx.x, seq = blockIdx.z;
     const int kv_head = blockIdx.y / head_chunks, chunk = blockIdx.y % head_chunks;
@@ -211,21 +219,33 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     load_tile(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads);
     cp_async_commit();
     if (early) grid_dependency_wait();
+    // kDecodeStages - 1 pages are in flight while one is worked on; every stage is one commit group, empty
+    // groups past the last page keep the count the waits rely on
+#pragma unroll
+    for (int ahead = 1; ahead < kDecodeStages - 1; ++ahead) {
+        if (t_begin + ahead < t_end) {
+            const uint32_t dst = stage_base + ahead * 2 * kTileBytes;
+            load_tile(dst, k_pool, table[t_begin + ahead], kv_head, kv_heads);
+            load_tile(dst + kTileBytes, v_pool, table[t_begin + ahead], kv_head, kv_heads);
+        }
+        cp_async_commit();
+    }
     load_queries(q_smem, q + (size_t)q_row * q_row_stride + (size_t)head0 * HD, HD, kQRowsDecode, rows_here);
     __syncthreads();
     uint32_t a[kKSteps][4];
     load_q_fragments(a, smem_u32(q_smem));
 
     for (int t = t_begin; t < t_end; ++t) {
-        const int stage = (t - t_begin) & 1;
-        if (t + 1 < t_end) {
-            const uint32_t next = stage_base + (stage ^ 1) * 2 * kTileBytes;
-            load_tile(next, k_pool, table[t + 1], kv_head, kv_heads);
-            load_tile(next + kTileBytes, v_pool, table[t + 1], kv_head, kv_heads);
+        const int stage = (t - t_begin) % kDecodeStages;
+        {
+            const int fetch = t + kDecodeStages - 1;  // its stage was freed by the barrier that ended page t - 1
+            if (fetch < t_end) {
+                const uint32_t next = stage_base + ((fetch - t_begin) % kDecodeStages) * 2 * kTileBytes;
+                load_tile(next, k_pool, table[fetch], kv_head, kv_heads);
+                load_tile(next + kTileBytes, v_pool, table[fetch], kv_head, kv_heads);
+            }
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+            cp_async_wait<kDecodeStages - 1>();  // everything but the newest kDecodeStages - 1 groups: page t is in
         }
         __syncthreads();
         const uint32_t k_tile = stage_base + stage * 2 * kTileBytes, v_tile = k_tile + kTileBytes;
@@ -536,7 +556,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
 }
 
 constexpr size_t decode_smem() {
-    const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 4 * (size_t)kTileBytes;
+    const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 2 * kDecodeStages * (size_t)kTileBytes;
     const size_t merge = (size_t)kQRowsDecode * kRowBytes + (4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
@@ -556,6 +576,9 @@ static int check_common(const char* what, int heads, int kv_heads, int page_size
 using namespace mb;
 
 MB_EXPORT int mb_attention_head_dim() { return HD; }
+
+// Shared memory of one decode block, for callers that plan how many blocks are resident at once.
+MB_EXPORT size_t mb_decode_block_bytes() { return decode_smem(); }
 
 // Scratch floats a decode call with `splits` > 1 needs: partial outputs and (maximum, sum) pairs.
 MB_EXPORT size_t mb_decode_scratch_floats(int sequences, int heads, int splits) {

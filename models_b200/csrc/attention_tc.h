@@ -13,6 +13,9 @@ extern "C" {
 const char* mb_last_error(void);
 int mb_attention_head_dim(void);
 
+/* Shared memory of one decode block in bytes, for callers that plan how many blocks are resident at once. */
+size_t mb_decode_block_bytes(void);
+
 /* Floats of scratch a decode call with `splits` > 1 needs (0 for one split). */
 size_t mb_decode_scratch_floats(int sequences, int heads, int splits);
 

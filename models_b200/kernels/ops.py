@@ -83,7 +83,13 @@ def attention_rows():
 
 def attention_tc(head_dim: int):
     """The tensor-core attention kernels, compiled for this head size at first use."""
-    return load_library("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": int(head_dim)})
+    return load_library("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": int(head_dim), **_attention_defines})
+
+
+# tuning knob for experiments: MODELS_B200_ATTENTION="DECODE_STAGES=4" rebuilds the attention kernels with another
+# number of page stages in the decode kernel
+_attention_defines = {"MB_" + k: int(v) for k, v in
+                      (item.split("=") for item in os.environ.get("MODELS_B200_ATTENTION", "").split(",") if item)}
 
 
 def attention_tc_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
@@ -250,6 +256,9 @@ def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, h
         raise KernelError("the tensor-core attention kernels take bfloat16 q, out and pools")
 
 
+_decode_block_bytes = {}
+
+
 def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64, multiprocessors: int = 148) -> int:
     """How many blocks share one sequence's keys: the largest power of two, at most 8 (they form one
     thread-block cluster), with which all blocks of the call are resident at once -- a second,
@@ -261,9 +270,11 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
     while rounded < sequences:
         rounded *= 2
     base = rounded * kv_heads * (-(-(heads // kv_heads) // 16))
-    row_bytes = head_dim * 2 + 16
-    block_bytes = 16 * row_bytes + 4 * 64 * row_bytes + 1024  # queries, two stages of a key and a value page
-    resident = max(1, (227 * 1024) // block_bytes)
+    if head_dim not in _decode_block_bytes:
+        lib = attention_tc(head_dim)
+        lib.mb_decode_block_bytes.restype = ctypes.c_size_t
+        _decode_block_bytes[head_dim] = int(lib.mb_decode_block_bytes()) + 1024
+    resident = max(1, (227 * 1024) // _decode_block_bytes[head_dim])
     limit = max(1, min(8, (resident * multiprocessors) // max(1, base)))
     splits = 1
     while splits * 2 <= limit:
