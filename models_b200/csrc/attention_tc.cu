@@ -38,14 +38,12 @@ constexpr int kChunks = HD / 8;           // 16-byte pieces of a row
 constexpr int kKSteps = HD / 16;
 constexpr int kThreads = 128;
 constexpr int kQRowsDecode = 16;
-// Pages of keys and values in shared memory per decode block.  Measured at 64 sequences of 1,280 positions: with heads
-// of 128 a third stage takes the kernel from 4.3 to 5.2 TB/s; with heads of 64 (pages half as large, five blocks per
-// multiprocessor with two stages, four with three) it loses a fifth.
-#ifndef MB_DECODE_STAGES
-#define MB_DECODE_STAGES (MB_HEAD_DIM >= 96 ? 3 : 2)
-#endif
-constexpr int kDecodeStages = MB_DECODE_STAGES;
-static_assert(kDecodeStages >= 2, "at least one page in flight while one is worked on");
+// Pages of keys and values in shared memory per decode block: two or three, chosen at launch (mb_decode_stages).
+// A third stage helps where a block has only a few pages -- all of them are then in flight at once; with four blocks
+// of three stages per sequence, batch 8 of the 1B model gains 2 % over eight blocks of two -- and at head sizes of 96
+// and more (64 sequences of 1,280 positions at head size 128: 4.3 -> 5.2 TB/s).  With heads of 64 and long loops it
+// costs a resident block per multiprocessor and loses (batch 64: 49.7 -> 46.6 k tokens/s), and eight blocks of three
+// stages per sequence no longer fit one round at batch 8 (9.2 -> 8.3 k tokens/s).
 constexpr int kQRowsPrefill = 64;
 
 using bf16 = __nv_bfloat16;
@@ -163,7 +161,7 @@ __device__ __forceinline__ float quad_sum(float v) {
 // kCluster: the `splits` blocks of one (sequence, kv head) form a thread-block cluster and combine
 // their partial results in the first block's shared memory (distributed shared memory) instead of
 // going through scratch memory and a second kernel; splits <= 8 then.
-template <bool kCluster>
+template <bool kCluster, int kDecodeStages>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __restrict__ out, int out_row_stride,
                         const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
@@ -555,8 +553,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
     }
 }
 
-constexpr size_t decode_smem() {
-    const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 2 * kDecodeStages * (size_t)kTileBytes;
+constexpr size_t decode_smem(int stages) {
+    const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 2 * stages * (size_t)kTileBytes;
     const size_t merge = (size_t)kQRowsDecode * kRowBytes + (4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
@@ -578,7 +576,10 @@ using namespace mb;
 MB_EXPORT int mb_attention_head_dim() { return HD; }
 
 // Shared memory of one decode block, for callers that plan how many blocks are resident at once.
-MB_EXPORT size_t mb_decode_block_bytes() { return decode_smem(); }
+// Page stages a decode call with `splits` blocks per sequence runs with (see the note on page stages above), and the
+// shared memory of one block with so many stages: for callers that plan how many blocks are resident at once.
+MB_EXPORT int mb_decode_stages(int splits) { return (HD >= 96 || splits >= 4) ? 3 : 2; }
+MB_EXPORT size_t mb_decode_block_bytes(int stages) { return decode_smem(stages); }
 
 // Scratch floats a decode call with `splits` > 1 needs: partial outputs and (maximum, sum) pairs.
 MB_EXPORT size_t mb_decode_scratch_floats(int sequences, int heads, int splits) {
@@ -595,12 +596,17 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     const int group = heads / kv_heads;
     const int head_chunks = (group + 15) / 16;
     if (sequences > 65535 || kv_heads * head_chunks > 65535) return fail("decode_attention: grid too large");
+    const int stages = mb_decode_stages(splits);
     static bool configured = false;
     if (!configured) {
-        cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
+        cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
         if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(decode_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem());
-        if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(), cudaGetErrorString(status));
+            status = cudaFuncSetAttribute(decode_attention_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(decode_attention_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
+        if (status == cudaSuccess)
+            status = cudaFuncSetAttribute(decode_attention_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
+        if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(3), cudaGetErrorString(status));
         configured = true;
     }
     const dim3 grid(splits, kv_heads * head_chunks, sequences);
@@ -610,7 +616,7 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
         cudaLaunchConfig_t config = {};
         config.gridDim = grid;
         config.blockDim = dim3(kThreads);
-        config.dynamicSmemBytes = decode_smem();
+        config.dynamicSmemBytes = decode_smem(stages);
         config.stream = stream;
         cudaLaunchAttribute attribute[2];
         attribute[0].id = cudaLaunchAttributeClusterDimension;
@@ -621,7 +627,8 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
         attribute[1].val.programmaticStreamSerializationAllowed = 1;
         config.attrs = attribute;
         config.numAttrs = dependent_launches_allowed() ? 2 : 1;
-        cudaError_t status = cudaLaunchKernelEx(&config, decode_attention_kernel<true>, (const bf16*)q, q_row_stride, (bf16*)out,
+        auto kernel = stages == 3 ? decode_attention_kernel<true, 3> : decode_attention_kernel<true, 2>;
+        cudaError_t status = cudaLaunchKernelEx(&config, kernel, (const bf16*)q, q_row_stride, (bf16*)out,
                                                 out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks,
                                                 cu_q, kv_lens, heads, kv_heads, head_chunks, window, scale, splits,
                                                 (float*)nullptr, (float*)nullptr);
@@ -630,7 +637,8 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     }
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)sequences * heads * splits * HD : nullptr;
-    if (int status = launch_dependent("decode_attention", decode_attention_kernel<false>, grid, dim3(kThreads), decode_smem(), stream, true,
+    auto kernel = stages == 3 ? decode_attention_kernel<false, 3> : decode_attention_kernel<false, 2>;
+    if (int status = launch_dependent("decode_attention", kernel, grid, dim3(kThreads), decode_smem(stages), stream, true,
                                       (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool,
                                       (const bf16*)v_pool, block_table, max_blocks, cu_q, kv_lens, heads, kv_heads, head_chunks,
                                       window, scale, splits, partial_o, partial_ml))

@@ -13,8 +13,10 @@ extern "C" {
 const char* mb_last_error(void);
 int mb_attention_head_dim(void);
 
-/* Shared memory of one decode block in bytes, for callers that plan how many blocks are resident at once. */
-size_t mb_decode_block_bytes(void);
+/* Page stages (2 or 3) a decode call with `splits` blocks per sequence runs with, and the shared memory in bytes of
+ * one block with so many stages: for callers that plan how many blocks are resident at once. */
+int mb_decode_stages(int splits);
+size_t mb_decode_block_bytes(int stages);
 
 /* Floats of scratch a decode call with `splits` > 1 needs (0 for one split). */
 size_t mb_decode_scratch_floats(int sequences, int heads, int splits);

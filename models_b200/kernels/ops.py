@@ -83,13 +83,7 @@ def attention_rows():
 
 def attention_tc(head_dim: int):
     """The tensor-core attention kernels, compiled for this head size at first use."""
-    return load_library("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": int(head_dim), **_attention_defines})
-
-
-# tuning knob for experiments: MODELS_B200_ATTENTION="DECODE_STAGES=4" rebuilds the attention kernels with another
-# number of page stages in the decode kernel
-_attention_defines = {"MB_" + k: int(v) for k, v in
-                      (item.split("=") for item in os.environ.get("MODELS_B200_ATTENTION", "").split(",") if item)}
+    return load_library("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": int(head_dim)})
 
 
 def attention_tc_takes(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
@@ -260,12 +254,14 @@ _decode_block_bytes = {}
 
 
 def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64, multiprocessors: int = 148) -> int:
-    """How many blocks share one sequence's keys: the largest power of two, at most 8 (they form one
-    thread-block cluster), with which all blocks of the call are resident at once -- a second,
-    partly filled round of blocks costs more than longer blocks do (measured: 16 sequences of 1,100
-    positions at head size 128 take 22 us with 2 splits, 29 with 4, 38 with 8).  It depends on the
-    batch size rounded up to a power of two only, never on the lengths, so a batch padded to such a
-    size is split like the unpadded one and a captured step keeps its split."""
+    """How many blocks share one sequence's keys: a power of two, at most 8 (they form one thread-block
+    cluster), with which all blocks of the call are resident at once -- a second, partly filled
+    round of blocks costs more than longer blocks do (measured: 16 sequences of 1,100 positions at
+    head size 128 take 22 us with 2 splits, 29 with 4, 38 with 8).  The kernel runs with three page
+    stages when there are four or more splits (or heads of 96 and more) and with two otherwise, and a
+    block's shared memory follows from that; so does the count.  It depends on the batch size rounded
+    up to a power of two only, never on the lengths, so a batch padded to such a size is split like
+    the unpadded one and a captured step keeps its split."""
     rounded = 1
     while rounded < sequences:
         rounded *= 2
@@ -273,13 +269,21 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
     if head_dim not in _decode_block_bytes:
         lib = attention_tc(head_dim)
         lib.mb_decode_block_bytes.restype = ctypes.c_size_t
-        _decode_block_bytes[head_dim] = int(lib.mb_decode_block_bytes()) + 1024
-    resident = max(1, (227 * 1024) // _decode_block_bytes[head_dim])
-    limit = max(1, min(8, (resident * multiprocessors) // max(1, base)))
-    splits = 1
-    while splits * 2 <= limit:
-        splits *= 2
-    return splits
+        _decode_block_bytes[head_dim] = {stages: int(lib.mb_decode_block_bytes(stages)) + 1024 for stages in (2, 3)}
+        _decode_block_bytes[head_dim]["wide"] = int(lib.mb_decode_stages(1)) == 3  # three stages whatever the split
+
+    def fitting(stages: int) -> int:
+        resident = max(1, (227 * 1024) // _decode_block_bytes[head_dim][stages])
+        limit = max(1, min(8, (resident * multiprocessors) // max(1, base)))
+        splits = 1
+        while splits * 2 <= limit:
+            splits *= 2
+        return splits
+
+    with_three = fitting(3)
+    if _decode_block_bytes[head_dim]["wide"] or with_three >= 4:
+        return with_three
+    return min(2, fitting(2))
 
 
 def decode_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
