@@ -69,12 +69,27 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
 def peaks():
+    """The roofline denominators: the driver's measured copy bandwidth and cuBLAS bf16 throughput (burst) when
+    MEASURED_PEAKS.json is there, else the stated fallback figures."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+
+    def number(raw, names, scale=1.0):
+        for name in names:
+            value = raw.get(name)
+            if isinstance(value, dict):
+                value = value.get("value", value.get("measured"))
+            if isinstance(value, (int, float)) and value > 0:
+                return float(value) * scale
+        return None
+
     if os.path.isfile(path):
         try:
             raw = json.load(open(path))
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
-        except (KeyError, ValueError, TypeError):
+            hbm = number(raw, ("hbm_gbs", "hbm_gb_s", "hbm_gbps")) or number(raw, ("hbm_tbs", "hbm_tb_s"), 1000.0)
+            bf16 = number(raw, ("bf16_tflops", "bf16_tflops_burst")) or number(raw, ("bf16_pflops",), 1000.0)
+            if hbm and bf16:
+                return {"hbm_gbs": hbm, "bf16_tflops": bf16, "source": "measured"}
+        except (OSError, ValueError, TypeError, AttributeError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
 
