@@ -94,6 +94,33 @@ def test_different_mixers_in_different_layers(cuda_device, dtype):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("head_dim,heads,kv_heads", [(64, 4, 2), (128, 3, 1)])
+def test_a_windowed_layer_at_the_head_sizes_of_the_tcgen05_kernels(cuda_device, head_dim, heads, kv_heads):
+    """The same mix -- one layer sees everything, the other a window of 100 -- at head sizes 64 and 128
+    in bfloat16, where a prompt takes the tcgen05 attention and the folded q/k/v product: a prompt in
+    two pieces (the second on top of cached positions whose early pages the window group has already
+    given back), then token by token across a page boundary."""
+    from models_b200.engine import StepEntry
+
+    spec = _specs(hidden=256, heads=heads, kv_heads=kv_heads, head_dim=head_dim, inter=328, vocab=331, windows=(None, 100))
+    engine, tensors = _engine(spec, "bfloat16", seed=7, max_tokens=2048)
+    assert len(engine.cache.groups) == 2
+    tokens = _tokens(470, spec.vocab_size, 5)
+    expected = _plain_forward(spec, tensors, tokens)
+    slot = engine.open_slot()
+    out = engine.step([StepEntry(slot, tokens[:260], [0, 99, 100, 259])])
+    assert scaled_error(out, expected[[0, 99, 100, 259]]) < TOLERANCE["bfloat16"]
+    out = engine.step([StepEntry(slot, tokens[260:440], [0, 60, 179])])  # 180 more on top of 260 cached
+    assert scaled_error(out, expected[[260, 320, 439]]) < TOLERANCE["bfloat16"]
+    full, windowed = engine.cache.groups
+    assert sum(p >= 0 for p in full.tables[slot]) == 7 and sum(p >= 0 for p in windowed.tables[slot]) <= 3
+    for i in range(440, 470):
+        out = engine.step([StepEntry(slot, [tokens[i]], [0])])
+        assert scaled_error(out[0], expected[i]) < TOLERANCE["bfloat16"], i
+    engine.release_slot(slot)
+    engine.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_schedule_names_a_layer_twice_and_shares_a_cache(cuda_device, dtype):
     from models_b200.config.specs import ScheduleEntry
