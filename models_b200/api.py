@@ -65,6 +65,10 @@ class ModelMetadata:
     kv_heads: int
 
 
+class _StreamAbandoned(Exception):
+    """Raised inside the generation of a stream nobody reads any more."""
+
+
 class TextGenerationModel:
     def __init__(self, engine, max_batch: int, name: str, cuda_graphs: bool = True, context: Optional[int] = None):
         from .engine.stepper import EngineStepper
@@ -138,20 +142,31 @@ class TextGenerationModel:
             return self._loop.run(prompts, options, on_token)
 
     def stream(self, prompt: Sequence[int], options: Optional[SamplingOptions] = None) -> Iterator[int]:
-        """Token ids as they are generated."""
+        """Token ids as they are generated.  An iterator that is closed or dropped before its end
+        stops the generation behind it at its next token; the sequence's slot goes back."""
         done = object()
         items: "queue.Queue" = queue.Queue()
-        handler = CallbackStream(items.put, lambda usage: items.put(done), lambda failure: items.put(failure))
+        abandoned = threading.Event()
+
+        def on_token(token: int) -> None:
+            if abandoned.is_set():
+                raise _StreamAbandoned()
+            items.put(token)
+
+        handler = CallbackStream(on_token, lambda usage: items.put(done), lambda failure: items.put(failure))
         worker = threading.Thread(target=self.generate, args=(prompt, options, handler), daemon=True)
         worker.start()
-        while True:
-            item = items.get()
-            if item is done:
-                break
-            if isinstance(item, BaseException):
-                raise item
-            yield item
-        worker.join()
+        try:
+            while True:
+                item = items.get()
+                if item is done:
+                    break
+                if isinstance(item, BaseException):
+                    raise item
+                yield item
+        finally:
+            abandoned.set()
+            worker.join()
 
     # ------------------------------------------------------------------ pipeline calls (one default sequence)
 

@@ -64,6 +64,10 @@ def test_greedy_generation_through_the_entry_point(cuda_device, folders, name, d
     model.generate(prompts[1], options, models_b200.CallbackStream(streamed.append, done.append, done.append))
     assert streamed == alone and len(done) == 1 and done[0].completion_tokens == len(alone)
     assert list(model.stream(prompts[1], options)) == alone
+    abandoned = model.stream(prompts[1], options)  # read two tokens, then drop the iterator: the generation stops
+    assert [next(abandoned), next(abandoned)] == alone[:2]
+    abandoned.close()
+    assert model.engine.cache.slots.held == 0
     errors = []
     model.generate([], options, models_b200.CallbackStream(on_error=errors.append))
     assert len(errors) == 1 and "empty" in str(errors[0])
