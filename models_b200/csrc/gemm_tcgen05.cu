@@ -15,6 +15,11 @@
 //     1172-1178; SwiGLU: backend-java/.../ops/TensorOps.java:1407-1425.)
 //   * Blocks are persistent (one per multiprocessor) and walk the output tiles with the row tile
 //     index running fastest, so neighbouring blocks share a weight tile through L2.
+//   * Where there are tiles enough, two blocks of a cluster share a tile of 256 rows by 256 columns
+//     (tcgen05 cta_group::2): each loads its own 128 rows of A and its half of W (plain TMA loads, no
+//     multicast; both blocks' bytes are counted on the leader's barrier), the leader issues products
+//     that read both blocks' shared memory, tcgen05.commit tells both blocks' barriers, and each block
+//     runs the epilogue of its rows from its own tensor memory.
 //
 // Every wait on an mbarrier is bounded: after about two seconds a role gives up, records where in
 // g_gemm_status and leaves its loop; all roles then meet at the final barrier, tensor memory is
@@ -62,14 +67,24 @@ struct GemmArgs {
     bf16* v_pool;
 };
 
-template <int EPI, int BN>
+// kPair 1: a block works on a tile alone.  kPair 2: the two blocks of a cluster share a tile of 256 rows by BN columns
+// (tcgen05 cta_group::2): each loads its 128 rows of A and its half of the BN rows of W, the leader issues the products
+// for both, each block's tensor memory holds the accumulator of its own 128 rows, and each block runs the epilogue of
+// its rows.  A block then moves 32 KB per 64 columns of K instead of 48 KB for the same work.
+template <int EPI, int BN, int kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmArgs args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment of the tiles is what the swizzle and the descriptors assume
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int kStages = Tile<BN>::kStages, kStageBytes = Tile<BN>::kStageBytes, kAccumulatorColumns = BN;
+    constexpr int kBoxes = Tile<BN>::kBoxes / kPair;  // boxes of W this block loads per stage
+    constexpr int kStageBytes = kTileABytes + kBoxes * kBoxBBytes, kStages = kRingBytes / kStageBytes, kAccumulatorColumns = BN;
+    constexpr uint32_t kInstruction = instruction_descriptor(kBlockM * kPair, BN);
     static_assert(EPI != EPI_SWIGLU || BN == 256, "the gated epilogue pairs 128 gate columns with 128 up columns");
+    static_assert(kPair == 1 || (kPair == 2 && BN == 256), "a pair of blocks shares a tile of 256 columns");
+    static_assert(kStages <= kMaxStages, "ring deeper than its barriers");
+    const int rank = kPair == 2 ? (int)cluster_rank() : 0;
+    const bool leader = rank == 0;
     __shared__ __align__(8) uint64_t barriers[2 * kMaxStages + 4];
     __shared__ uint32_t tmem_base_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -78,10 +93,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     // columns of output per tile: BN, or 128 gate/up pairs
     constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
-    const int m_tiles = (args.m + kBlockM - 1) / kBlockM;
+    const int m_tiles = (args.m + kBlockM * kPair - 1) / (kBlockM * kPair);
     const int n_tiles = (args.n + kOutCols - 1) / kOutCols;
     const int tiles = m_tiles * n_tiles;
     const int k_blocks = (args.k + kBlockK - 1) / kBlockK;
+    const int first_tile = blockIdx.x / kPair, tile_step = gridDim.x / kPair;  // a pair walks the tiles together
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -90,16 +106,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full_bar + 8 * a, 1);
-            mbar_init(acc_empty_bar + 8 * a, kEpilogueWarps);
+            mbar_init(acc_empty_bar + 8 * a, kEpilogueWarps * kPair);  // the leader's copy hears from both blocks' epilogues
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // one warp allocates all 512 columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    if (warp == 1) {  // one warp allocates all 512 columns of tensor memory (of a pair: the same warp of both blocks)
+        if (kPair == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (kPair == 2) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     grid_launch_dependents();
@@ -111,18 +133,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 1;  // the first pass over the ring finds every stage free
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * kBlockM, n_tile = tile / m_tiles;
+            for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+                const int m0 = (tile % m_tiles) * kBlockM * kPair + rank * kBlockM, n_tile = tile / m_tiles;
                 const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
                 const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
                     const uint32_t dst = smem_u32(smem) + stage * kStageBytes;
-                    mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
-                    tma_load_2d(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
-                    tma_load_2d(dst + kTileABytes, &map_w, kb * kBlockK, w_row0, full_bar + 8 * stage);
-                    if (Tile<BN>::kBoxes == 2)
-                        tma_load_2d(dst + kTileABytes + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * stage);
+                    if (kPair == 2) {
+                        // both blocks' bytes are counted on the leader's barrier; the leader announces them
+                        if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes);
+                        tma_load_2d_pair(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
+                        tma_load_2d_pair(dst + kTileABytes, &map_w, kb * kBlockK, leader ? w_row0 : w_row1, full_bar + 8 * stage);
+                    } else {
+                        mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
+                        tma_load_2d(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
+                        tma_load_2d(dst + kTileABytes, &map_w, kb * kBlockK, w_row0, full_bar + 8 * stage);
+                        if (kBoxes == 2)
+                            tma_load_2d(dst + kTileABytes + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * stage);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -132,11 +161,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && leader) {
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 1;  // both accumulators start free
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
                 if (!(ok = mbar_wait(acc_empty_bar + 8 * acc, acc_phase, 2))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * kAccumulatorColumns;
@@ -146,16 +175,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t a_addr = smem_u32(smem) + stage * kStageBytes;
                     const uint64_t a_desc = umma_descriptor(a_addr), b_desc = umma_descriptor(a_addr + kTileABytes);
 #pragma unroll
-                    for (int ks = 0; ks < kBlockK / 16; ++ks)  // 32 bytes further along K per step: +2 in the address field
-                        umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, Tile<BN>::kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(empty_bar + 8 * stage);  // the stage is free once these products have read it
+                    for (int ks = 0; ks < kBlockK / 16; ++ks) {  // 32 bytes further along K per step: +2 in the address field
+                        if (kPair == 2) umma_pair(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
+                        else umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    // the stage is free (in both blocks of a pair) once these products have read it
+                    if (kPair == 2) umma_commit_pair(empty_bar + 8 * stage);
+                    else umma_commit(empty_bar + 8 * stage);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
                 if (!ok) break;
-                umma_commit(acc_full_bar + 8 * acc);  // the accumulator is complete once all products are
+                // the accumulator (each block's half of it) is complete once all products are
+                if (kPair == 2) umma_commit_pair(acc_full_bar + 8 * acc);
+                else umma_commit(acc_full_bar + 8 * acc);
                 if (++acc == 2) {
                     acc = 0;
                     acc_phase ^= 1;
@@ -170,8 +205,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile % m_tiles) * kBlockM, n_tile = tile / m_tiles;
+        for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
+            const int m0 = (tile % m_tiles) * kBlockM * kPair + rank * kBlockM, n_tile = tile / m_tiles;
             ok = mbar_wait(acc_full_bar + 8 * acc, acc_phase, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -286,7 +321,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
+            if (lane == 0) {
+                if (kPair == 2) mbar_arrive_leader(acc_empty_bar + 8 * acc);
+                else mbar_arrive(acc_empty_bar + 8 * acc);
+            }
             if (++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1;
@@ -297,26 +335,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // every role has left its loop (done, or after a bounded wait gave up): free tensor memory
     tcgen05_fence_before();
     __syncthreads();
+    if (kPair == 2) cluster_sync_all();  // neither block leaves while the other may still signal its barriers
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+        if (kPair == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
     }
 }
 
-template <int EPI, int BN>
+template <int EPI, int BN, int kPair>
 static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, cudaStream_t stream) {
     constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
-    const size_t smem = (size_t)Tile<BN>::kStages * Tile<BN>::kStageBytes + 1024;
-    auto kernel = gemm_tcgen05_kernel<EPI, BN>;
+    const size_t smem = (size_t)kRingBytes + 1024;
+    auto kernel = gemm_tcgen05_kernel<EPI, BN, kPair>;
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
         configured = true;
     }
-    const int tiles = ((args.m + kBlockM - 1) / kBlockM) * ((args.n + kOutCols - 1) / kOutCols);
-    const int grid = tiles < multiprocessors ? tiles : multiprocessors;
-    return launch_dependent("gemm_tcgen05", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_a, map_w, args);
+    const int tiles = ((args.m + kBlockM * kPair - 1) / (kBlockM * kPair)) * ((args.n + kOutCols - 1) / kOutCols);
+    if (kPair == 1) {
+        const int grid = tiles < multiprocessors ? tiles : multiprocessors;
+        return launch_dependent("gemm_tcgen05", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_a, map_w, args);
+    }
+    // pairs of blocks: a cluster of two per tile in flight
+    const int pairs = tiles < multiprocessors / 2 ? tiles : multiprocessors / 2;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * (pairs < 1 ? 1 : pairs));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = 2;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = dependent_launches_allowed() ? 2 : 1;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, map_a, map_w, args);
+    if (status != cudaSuccess) return fail("gemm_tcgen05: launch of block pairs failed: %s", cudaGetErrorString(status));
+    return check_launch("gemm_tcgen05");
 }
 
 // Which tile width finishes first: rounds of tiles over the multiprocessors times the cost of a tile, a
@@ -328,12 +389,22 @@ static bool narrow_tiles_are_faster(int m, int n, int multiprocessors) {
     return narrow_rounds * 75 < wide_rounds * 100;
 }
 
+// Pairs of blocks (tiles of 256 x 256) move a third less through L2 and shared memory per product and win wherever
+// there are tiles enough to keep most pairs busy: measured at 2,048 rows, 96.8 against 108.2 us for the gate/up product
+// (1.42 PFLOP/s) and 54.4 against 60.0 us for the down product; with few tiles (512 rows of a 2048-wide matrix) the
+// smaller tiles of single blocks spread better.
+static bool pairs_are_faster(int m, int n) {
+    const long tiles = (long)((m + 255) / 256) * ((n + 255) / 256);
+    return tiles >= 48;
+}
+
 template <int EPI>
 static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, int tile_width,
-                  cudaStream_t stream) {
+                  int pair, cudaStream_t stream) {
+    if (pair == 2 || (pair == 0 && tile_width == 0 && pairs_are_faster(args.m, args.n))) return launch_tile<EPI, 256, 2>(map_a, map_w, args, multiprocessors, stream);
     const bool narrow = tile_width == 128 || (tile_width == 0 && narrow_tiles_are_faster(args.m, args.n, multiprocessors));
-    if (narrow) return launch_tile<EPI, 128>(map_a, map_w, args, multiprocessors, stream);
-    return launch_tile<EPI, 256>(map_a, map_w, args, multiprocessors, stream);
+    if (narrow) return launch_tile<EPI, 128, 1>(map_a, map_w, args, multiprocessors, stream);
+    return launch_tile<EPI, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }
 
 }  // namespace mb
@@ -344,9 +415,12 @@ using namespace mb;
 // epilogue 0: out bfloat16 [m, n_w]; 1: out float32 [m, n_w]; 2: out float32 [m, n_w] += ; 3: w holds gate
 // rows [0, n_w/2) and up rows [n_w/2, n_w): out bfloat16 [m, n_w/2] = silu(gate) * up.
 // tile_width: 0 lets the launcher choose between 128 and 256 output columns per tile; the gated epilogue takes 256.
+// pair: 2 runs tiles of 256 rows x 256 columns on pairs of blocks (tcgen05 cta_group::2); 1: one block per tile; 0: the launcher chooses.
 MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ld_out, int m, int n_w, int k,
-                              int epilogue, int multiprocessors, int tile_width, cudaStream_t stream) {
+                              int epilogue, int multiprocessors, int tile_width, int pair, cudaStream_t stream) {
     if (tile_width != 0 && tile_width != 128 && tile_width != 256) return fail("gemm_tcgen05: tile width %d is not built (128, 256)", tile_width);
+    if (pair < 0 || pair > 2) return fail("gemm_tcgen05: pair must be 0, 1 or 2, got %d", pair);
+    if (pair == 2 && tile_width == 128) return fail("gemm_tcgen05: pairs of blocks take tiles of 256 columns");
     if (m <= 0 || n_w <= 0) return 0;
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8) return fail("gemm_tcgen05: k (%d) and the row strides (%d, %d) must be multiples of 8", k, lda, ldw);
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return fail("gemm_tcgen05: operands must start on 16-byte boundaries");
@@ -359,12 +433,13 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
     GemmArgs args{m, n, k, n, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     switch (epilogue) {
-        case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, stream);
-        case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, stream);
-        case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(map_a, map_w, args, multiprocessors, tile_width, stream);
+        case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
+        case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
+        case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
         case EPI_SWIGLU:
             if (tile_width == 128) return fail("gemm_tcgen05: the gated epilogue takes tiles of 256 weight rows");
-            return launch_tile<EPI_SWIGLU, 256>(map_a, map_w, args, multiprocessors, stream);
+            if (pair == 2 || (pair == 0 && pairs_are_faster(m, 2 * n))) return launch_tile<EPI_SWIGLU, 256, 2>(map_a, map_w, args, multiprocessors, stream);
+            return launch_tile<EPI_SWIGLU, 256, 1>(map_a, map_w, args, multiprocessors, stream);
     }
     return fail("gemm_tcgen05: unknown epilogue %d", epilogue);
 }
@@ -389,7 +464,8 @@ MB_EXPORT int mb_gemm_tcgen05_qkv_rope(const void* a, int lda, const void* w, in
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
     GemmArgs args{m, n_w, k, n_w, q_out, ld_q, heads, kv_heads, head_dim, page_size, positions, slot_mapping, cos_table, sin_table,
                   (bf16*)k_pool, (bf16*)v_pool};
-    return launch_tile<EPI_ROPE, 256>(map_a, map_w, args, multiprocessors, stream);
+    if (pairs_are_faster(m, n_w)) return launch_tile<EPI_ROPE, 256, 2>(map_a, map_w, args, multiprocessors, stream);
+    return launch_tile<EPI_ROPE, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }
 
 // 0 when no wait ever gave up; else 1 + (role << 8): 1 producer, 2 MMA (accumulator), 3 MMA (operands), 4 epilogue.

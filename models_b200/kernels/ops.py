@@ -482,11 +482,12 @@ def gemm_tcgen05_takes(weight: torch.Tensor, epilogue: int = EPI_BF16, rows: Opt
 
 
 def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None,
-                 tile_width: int = 0) -> torch.Tensor:
+                 tile_width: int = 0, pair: int = 0) -> torch.Tensor:
     """a [m, k] . weight[n, k]^T on the tcgen05 tensor cores (bfloat16 in, float accumulation).
     Epilogues as for skinny_gemm: EPI_BF16 / EPI_F32 store, EPI_RESIDUAL adds into `out` (float32
     [m, n]), EPI_SWIGLU stores silu(gate) * up for weight = [gate rows; up rows].  tile_width 0 lets
-    the launcher choose between tiles of 128 and 256 output columns."""
+    the launcher choose between tiles of 128 and 256 output columns.  pair 2: tiles of 256 rows by
+    256 columns on pairs of blocks (tcgen05 cta_group::2)."""
     _cuda(a, weight, out)
     if a.dtype != torch.bfloat16 or a.dim() != 2 or a.stride(1) != 1 or a.shape[1] != weight.shape[1]:
         raise KernelError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit the weight {tuple(weight.shape)}")
@@ -502,7 +503,7 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16
         out = torch.empty((m, n), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=a.device)
     lib = gemm_tc()
     _run(lib, lib.mb_gemm_tcgen05(_p(a), a.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), m, n_w, k,
-                                  epilogue, _sm_count(a.device), tile_width, _stream()))
+                                  epilogue, _sm_count(a.device), tile_width, pair, _stream()))
     return out
 
 

@@ -484,7 +484,7 @@ def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads
 
 
 @pytest.mark.parametrize("rows,heads,kv_heads,head_dim,hidden", [(129, 8, 2, 64, 512), (300, 3, 3, 128, 264), (700, 5, 1, 64, 328),
-                                                               (257, 2, 2, 128, 1024)])
+                                                               (257, 2, 2, 128, 1024), (1500, 28, 4, 64, 136)])
 def test_tcgen05_qkv_product_with_rotation_and_cache_write(cuda_device, rows, heads, kv_heads, head_dim, hidden):
     """The prefill q/k/v product with rotation and paged cache write in its epilogue against the plain
     parts: head counts that leave the last tile partly empty, rows that do not fill the last row tile,
@@ -534,7 +534,8 @@ def test_tcgen05_qkv_product_with_rotation_and_cache_write(cuda_device, rows, he
         ops.gemm_tcgen05_qkv_rope(a.cuda(), w.cuda(), heads, kv_heads, 48, positions.cuda(), cos.cuda(), sin.cuda(), kd, vd, slots.cuda())
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (70, 144, 136), (300, 272, 200), (1, 512, 2048), (513, 1040, 328)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (70, 144, 136), (300, 272, 200), (1, 512, 2048), (513, 1040, 328),
+                                   (2100, 5136, 264)])
 def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
     """The prefill matrix product (TMA, tcgen05.mma, accumulator in tensor memory) against float64,
     at sizes that do not fill its 128 x 256 x 64 tiles; no bounded wait may have given up."""
@@ -545,21 +546,23 @@ def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
     w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
     exact = a.double() @ w.double().t()
     scale = float(exact.abs().max())
-    for tile_width in (0, 128, 256):  # the launcher's choice, and both tile widths by name
-        out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_F32, tile_width=tile_width)
+    # the launcher's choice; both tile widths of single blocks by name; pairs of blocks (cta_group::2)
+    for tile_width, pair in ((0, 0), (128, 1), (256, 1), (0, 2)):
+        out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_F32, tile_width=tile_width, pair=pair)
         assert float((out.double().cpu() - exact).abs().max()) < 2e-5 * scale * math.sqrt(k)
-        out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_BF16, tile_width=tile_width)
+        out = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_BF16, tile_width=tile_width, pair=pair)
         assert out.dtype == torch.bfloat16 and float((out.double().cpu() - exact).abs().max()) < 1e-2 * scale
         residual = torch.randn(m, n, generator=g)
         rd = residual.cuda()
-        ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_RESIDUAL, out=rd, tile_width=tile_width)
+        ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_RESIDUAL, out=rd, tile_width=tile_width, pair=pair)
         assert float((rd.double().cpu() - (residual.double() + exact)).abs().max()) < 2e-5 * (scale + 4) * math.sqrt(k)
     with pytest.raises(ops.KernelError, match="256"):
         ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_SWIGLU, tile_width=128)
-    gated = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_SWIGLU)
     want = plain_llama.swiglu(exact[:, : n // 2], exact[:, n // 2:])
-    assert gated.shape == (m, n // 2)
-    assert float((gated.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+    for pair in (1, 2):
+        gated = ops.gemm_tcgen05(a.cuda(), w.cuda(), ops.EPI_SWIGLU, pair=pair)
+        assert gated.shape == (m, n // 2)
+        assert float((gated.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
     # a strided view of wider activations is taken as it is
     wide = torch.randn(m, k + 24, generator=g).bfloat16().cuda()
     out = ops.gemm_tcgen05(wide[:, 8:8 + k], w.cuda(), ops.EPI_F32)
