@@ -14,7 +14,8 @@
 //     memory.  (x = x + W.h: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1131-1138,
 //     1172-1178; SwiGLU: backend-java/.../ops/TensorOps.java:1407-1425.)
 //   * Blocks are persistent (one per multiprocessor) and walk the output tiles with the row tile
-//     index running fastest, so neighbouring blocks share a weight tile through L2.
+//     index running fastest inside groups of 2,048 rows, so neighbouring blocks share a weight tile
+//     through L2 and a group of activation rows stays there while the weights stream past.
 //   * Where there are tiles enough, two blocks of a cluster share a tile of 256 rows by 256 columns
 //     (tcgen05 cta_group::2): each loads its own 128 rows of A and its half of W (plain TMA loads, no
 //     multicast; both blocks' bytes are counted on the leader's barrier), the leader issues products
@@ -51,6 +52,27 @@ constexpr int kMaxStages = 6;
 constexpr int kEpilogueWarps = 8;                       // two per quarter of the tensor-memory lanes: each takes half the columns
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;      // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue
 constexpr int kTmemColumns = 512;  // two accumulators of BN columns; all of it is taken either way
+
+// The order in which tiles are walked: row tiles run fastest inside a group of kGroupRows rows of A, then the column
+// tiles of W, then the next group.  Blocks that work at the same time then share a few tiles of W and one group of A,
+// which stays in L2 while all of W streams past it once; with row tiles simply running fastest, a prompt of 16,384
+// tokens re-read all of A (more than L2 holds) for every column tile.
+constexpr int kGroupRows = 2048;
+__device__ __forceinline__ void tile_coordinates(int tile, int m_tiles, int n_tiles, int group, int* m_tile, int* n_tile) {
+    const int per_group = group * n_tiles;
+    const int full_groups = m_tiles / group;
+    const int g = tile / per_group;
+    if (g < full_groups) {
+        const int within = tile - g * per_group;
+        *m_tile = g * group + within % group;
+        *n_tile = within / group;
+    } else {  // the last, smaller group
+        const int rest = m_tiles - full_groups * group;
+        const int within = tile - full_groups * per_group;
+        *m_tile = full_groups * group + within % rest;
+        *n_tile = within / rest;
+    }
+}
 
 struct GemmArgs {
     int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
@@ -134,7 +156,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 1;  // the first pass over the ring finds every stage free
             bool ok = true;
             for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
-                const int m0 = (tile % m_tiles) * kBlockM * kPair + rank * kBlockM, n_tile = tile / m_tiles;
+                int m_tile, n_tile;
+                tile_coordinates(tile, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+                const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
                 const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
                 const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
                 for (int kb = 0; kb < k_blocks; ++kb) {
@@ -206,7 +230,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t acc_phase = 0;
         bool ok = true;
         for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
-            const int m0 = (tile % m_tiles) * kBlockM * kPair + rank * kBlockM, n_tile = tile / m_tiles;
+            int m_tile, n_tile;
+            tile_coordinates(tile, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+            const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
             ok = mbar_wait(acc_full_bar + 8 * acc, acc_phase, 4);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
