@@ -53,6 +53,42 @@ constexpr int kEpilogueWarps = 8;                       // two per quarter of th
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;      // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue
 constexpr int kTmemColumns = 512;  // two accumulators of BN columns; all of it is taken either way
 
+// An epilogue warp's staging tile: 32 rows of 128 bytes.  A thread holds one row of the accumulator (a tensor-memory
+// lane), and storing from there would touch 32 lines per instruction; through the staging tile the rows are turned so
+// that neighbouring threads hold neighbouring bytes of a row and every store covers whole lines.  The 16-byte units
+// of a row are permuted by the row (unit ^ row % 8): the eight threads of a quarter-warp, which write the same unit of
+// eight rows or read eight units of one row, then fall on different banks.
+constexpr int kStagingBytes = 32 * 128;
+__device__ __forceinline__ uint32_t staged_address(uint32_t staging, int row, int unit) {
+    return staging + row * 128 + ((unit ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void stage_row(uint32_t staging, int row, const uint32_t (&packed)[32]) {
+    __syncwarp();  // the pass before has been read
+#pragma unroll
+    for (int unit = 0; unit < 8; ++unit)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(staged_address(staging, row, unit)), "r"(packed[4 * unit]),
+                     "r"(packed[4 * unit + 1]), "r"(packed[4 * unit + 2]), "r"(packed[4 * unit + 3])
+                     : "memory");
+    __syncwarp();
+}
+__device__ __forceinline__ uint4 staged_unit(uint32_t staging, int row, int unit) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(staged_address(staging, row, unit)) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&pair);
+}
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
 // The order in which tiles are walked: row tiles run fastest inside a group of kGroupRows rows of A, then the column
 // tiles of W, then the next group.  Blocks that work at the same time then share a few tiles of W and one group of A,
 // which stays in L2 while all of W streams past it once; with row tiles simply running fastest, a prompt of 16,384
@@ -225,6 +261,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ------------------------------------------------------------------ epilogue: 8 warps; a warp reads one quarter of
         // the tensor-memory lanes (its index modulo 4) and half of the tile's columns
         const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t staging = smem_u32(smem) + kRingBytes + (warp - 2) * kStagingBytes;
         constexpr int kHalfCols = kOutCols / 2;
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -257,31 +294,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const bool is_query = head < args.heads, is_key = !is_query && head < args.heads + args.kv_heads;
                     bf16* dst = nullptr;
                     if (is_query) {
-                        dst = reinterpret_cast<bf16*>(args.out) + (size_t)row * args.ld_out + (size_t)head * hd;
+                        if (live) dst = reinterpret_cast<bf16*>(args.out) + (size_t)row * args.ld_out + (size_t)head * hd;
                     } else if (slot >= 0) {
                         const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
                         const size_t page = slot / args.page_size, offset = slot % args.page_size;
                         dst = (is_key ? args.k_pool : args.v_pool) + ((page * args.kv_heads + kv_head) * args.page_size + offset) * hd;
                     }
+                    const unsigned long long dst_bits = reinterpret_cast<unsigned long long>(dst);
 #pragma unroll 1
                     for (int c = 0; c < half_head; c += 32) {
-                        float x0[32], x1[32];
-                        tmem_load_32_issue(taddr + h0 + c, x0);
-                        tmem_load_32_issue(taddr + h0 + half_head + c, x1);
-                        tmem_load_wait();
-                        if (!live || dst == nullptr) continue;
+                        // 32 coordinates of the lower half of the head and their partners of the upper half: a row's
+                        // 128 staged bytes are [lower 32 | upper 32] in bfloat16
+                        uint32_t packed[32];
+                        {
+                            float x0[32], x1[32];
+                            tmem_load_32_issue(taddr + h0 + c, x0);
+                            tmem_load_32_issue(taddr + h0 + half_head + c, x1);
+                            tmem_load_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            float lo[8], hi[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                lo[j] = __bfloat162float(__float2bfloat16_rn(x0[i + j]));
-                                hi[j] = __bfloat162float(__float2bfloat16_rn(x1[i + j]));
+                            for (int i = 0; i < 16; ++i) {
+                                packed[i] = pack_bf16(x0[2 * i], x0[2 * i + 1]);
+                                packed[16 + i] = pack_bf16(x1[2 * i], x1[2 * i + 1]);
                             }
+                        }
+                        stage_row(staging, lane, packed);
+                        // a quarter of a row per thread: 8 coordinates of the lower half with their 8 partners; four
+                        // threads cover a row, so the tables and the destinations are read and written in whole lines
+#pragma unroll
+                        for (int pass = 0; pass < 4; ++pass) {
+                            const int r = 8 * pass + (lane >> 2), unit = lane & 3;
+                            const int r_position = __shfl_sync(0xffffffffu, position, r);
+                            bf16* r_dst = reinterpret_cast<bf16*>(__shfl_sync(0xffffffffu, dst_bits, r));
+                            const uint4 lo_raw = staged_unit(staging, r, unit), hi_raw = staged_unit(staging, r, 4 + unit);
+                            if (r_dst == nullptr) continue;
+                            float lo[8], hi[8];
+                            unpack_bf16x8(lo_raw, lo);
+                            unpack_bf16x8(hi_raw, hi);
                             if (is_query || is_key) {
                                 float cs[8], sn[8];
-                                load8(args.cos_table + (size_t)position * half_head + c + i, cs);
-                                load8(args.sin_table + (size_t)position * half_head + c + i, sn);
+                                load8(args.cos_table + (size_t)r_position * half_head + c + 8 * unit, cs);
+                                load8(args.sin_table + (size_t)r_position * half_head + c + 8 * unit, sn);
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) {
                                     const float r0 = lo[j] * cs[j] - hi[j] * sn[j], r1 = lo[j] * sn[j] + hi[j] * cs[j];
@@ -289,58 +341,76 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     hi[j] = r1;
                                 }
                             }
-                            store8(dst + c + i, lo);
-                            store8(dst + half_head + c + i, hi);
+                            store8(r_dst + c + 8 * unit, lo);
+                            store8(r_dst + half_head + c + 8 * unit, hi);
                         }
                     }
                 }
-            } else
+            } else {
+                // 128 bytes of a row per pass: 32 columns of float, 64 of bfloat16
+                constexpr bool kWide = EPI == EPI_F32 || EPI == EPI_RESIDUAL;
+                constexpr int kPassCols = kWide ? 32 : 64, kUnitCols = kPassCols / 8;
 #pragma unroll 1
-            for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 32) {
-                float v[32];
-                if (EPI == EPI_SWIGLU) {
-                    float u[32];
-                    tmem_load_32_issue(taddr + c, v);
-                    tmem_load_32_issue(taddr + 128 + c, u);
-                    tmem_load_wait();
+                for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += kPassCols) {
+                    uint32_t packed[32];
+                    if (kWide) {
+                        float v[32];
+                        tmem_load_32_issue(taddr + c, v);
+                        tmem_load_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
-                } else {
-                    tmem_load_32_issue(taddr + c, v);
-                    tmem_load_wait();
-                }
-                if (row < args.m) {
-                    const int col = n0 + c;
-                    if (EPI == EPI_BF16 || EPI == EPI_SWIGLU) {
-                        bf16* dst = reinterpret_cast<bf16*>(args.out) + (size_t)row * args.ld_out + col;
-                        if (col + 32 <= args.n) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                float piece[8];
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) piece[j] = v[i + j];
-                                store8(dst + i, piece);
-                            }
-                        } else {
-                            for (int i = 0; i < 32 && col + i < args.n; ++i) dst[i] = __float2bfloat16_rn(v[i]);
-                        }
+                        for (int i = 0; i < 32; ++i) packed[i] = __float_as_uint(v[i]);
                     } else {
-                        float* dst = reinterpret_cast<float*>(args.out) + (size_t)row * args.ld_out + col;
-                        if (col + 32 <= args.n) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
+                        for (int part = 0; part < 2; ++part) {
+                            float v[32];
+                            if (EPI == EPI_SWIGLU) {
+                                float u[32];
+                                tmem_load_32_issue(taddr + c + 32 * part, v);
+                                tmem_load_32_issue(taddr + 128 + c + 32 * part, u);
+                                tmem_load_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                            } else {
+                                tmem_load_32_issue(taddr + c + 32 * part, v);
+                                tmem_load_wait();
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) packed[16 * part + i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+                        }
+                    }
+                    stage_row(staging, lane, packed);
+                    // eight threads per row and four rows per pass: every store covers whole lines of the output
+                    const int col = n0 + c + (lane & 7) * kUnitCols;
+#pragma unroll
+                    for (int pass = 0; pass < 8; ++pass) {
+                        const int r = 4 * pass + (lane >> 3);
+                        const int out_row = m0 + quarter * 32 + r;
+                        const uint4 value = staged_unit(staging, r, lane & 7);
+                        if (out_row >= args.m || col >= args.n) continue;
+                        if (kWide) {
+                            float* dst = reinterpret_cast<float*>(args.out) + (size_t)out_row * args.ld_out + col;
+                            const float v[4] = {__uint_as_float(value.x), __uint_as_float(value.y), __uint_as_float(value.z), __uint_as_float(value.w)};
+                            if (col + 4 <= args.n) {
                                 if (EPI == EPI_RESIDUAL) {
                                     // x += value without reading x here: the addition happens at the memory side.  Every
                                     // element of x gets exactly one such addition per product, so the sum has one order.
-                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(v[i]),
-                                                 "f"(v[i + 1]), "f"(v[i + 2]), "f"(v[i + 3])
+                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
                                                  : "memory");
                                 } else {
-                                    *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
                                 }
+                            } else {
+                                for (int i = 0; col + i < args.n; ++i) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
                             }
                         } else {
-                            for (int i = 0; i < 32 && col + i < args.n; ++i) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
+                            bf16* dst = reinterpret_cast<bf16*>(args.out) + (size_t)out_row * args.ld_out + col;
+                            if (col + 8 <= args.n) {
+                                *reinterpret_cast<uint4*>(dst) = value;
+                            } else {
+                                const uint32_t w[4] = {value.x, value.y, value.z, value.w};
+                                for (int i = 0; col + i < args.n; ++i)
+                                    dst[i] = __ushort_as_bfloat16((unsigned short)(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xffffu));
+                            }
                         }
                     }
                 }
@@ -372,7 +442,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int EPI, int BN, int kPair>
 static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, cudaStream_t stream) {
     constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
-    const size_t smem = (size_t)kRingBytes + 1024;
+    const size_t smem = (size_t)kRingBytes + kEpilogueWarps * kStagingBytes + 1024;
     auto kernel = gemm_tcgen05_kernel<EPI, BN, kPair>;
     static bool configured = false;
     if (!configured) {
