@@ -253,7 +253,7 @@ def e2e_decode(model, batch, steps, warmup, prompt=PROMPT_TOKENS):
     graphs = model.engine.decode_graphs
     h2d = 0  # the step's indices; the ids themselves stay on the device
     if graphs and graphs.captured:
-        layout = graphs.captured[graphs.rung(batch)].layout
+        layout = next(c for (size, _), c in graphs.captured.items() if size == graphs.rung(batch)).layout
         h2d = 4 * (layout.total - layout.tokens)
     return {"tokens_per_second": batch * (len(stamps) - 1) / seconds, "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": 4 * batch}

@@ -400,7 +400,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
                                 }
                             } else {
-                                for (int i = 0; col + i < args.n; ++i) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)  // (fixed indices: the values stay in registers)
+                                    if (col + i < args.n) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
                             }
                         } else {
                             bf16* dst = reinterpret_cast<bf16*>(args.out) + (size_t)out_row * args.ld_out + col;
@@ -408,8 +410,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 *reinterpret_cast<uint4*>(dst) = value;
                             } else {
                                 const uint32_t w[4] = {value.x, value.y, value.z, value.w};
-                                for (int i = 0; col + i < args.n; ++i)
-                                    dst[i] = __ushort_as_bfloat16((unsigned short)(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xffffu));
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (col + i < args.n) dst[i] = __ushort_as_bfloat16((unsigned short)(i & 1 ? w[i >> 1] >> 16 : w[i >> 1] & 0xffffu));
                             }
                         }
                     }
@@ -486,18 +489,21 @@ static bool narrow_tiles_are_faster(int m, int n, int multiprocessors) {
 }
 
 // Pairs of blocks (tiles of 256 x 256) move a third less through L2 and shared memory per product and win wherever
-// there are tiles enough to keep most pairs busy: measured at 2,048 rows, 96.8 against 108.2 us for the gate/up product
-// (1.42 PFLOP/s) and 54.4 against 60.0 us for the down product; with few tiles (512 rows of a 2048-wide matrix) the
-// smaller tiles of single blocks spread better.
-static bool pairs_are_faster(int m, int n) {
+// there are tiles enough to keep most pairs busy and work enough per pair to repay the two cluster barriers: measured
+// at 2,048 rows, 93.7 against 108 us for the gate/up product (1.47 PFLOP/s) and 49.9 against 54.8 us for the down
+// product (K = 8192), but 17.5 against 16.6 us for the output product (one round of tiles over K = 2048); with few
+// tiles (512 rows of a 2048-wide matrix) the smaller tiles of single blocks spread better.
+static bool pairs_are_faster(int m, int n, int k, int multiprocessors) {
     const long tiles = (long)((m + 255) / 256) * ((n + 255) / 256);
-    return tiles >= 48;
+    const long pairs = multiprocessors / 2 > 0 ? multiprocessors / 2 : 1;
+    const long rounds = (tiles + pairs - 1) / pairs;
+    return tiles >= 48 && rounds * k > 2048;
 }
 
 template <int EPI>
 static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, int tile_width,
                   int pair, cudaStream_t stream) {
-    if (pair == 2 || (pair == 0 && tile_width == 0 && pairs_are_faster(args.m, args.n))) return launch_tile<EPI, 256, 2>(map_a, map_w, args, multiprocessors, stream);
+    if (pair == 2 || (pair == 0 && tile_width == 0 && pairs_are_faster(args.m, args.n, args.k, multiprocessors))) return launch_tile<EPI, 256, 2>(map_a, map_w, args, multiprocessors, stream);
     const bool narrow = tile_width == 128 || (tile_width == 0 && narrow_tiles_are_faster(args.m, args.n, multiprocessors));
     if (narrow) return launch_tile<EPI, 128, 1>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI, 256, 1>(map_a, map_w, args, multiprocessors, stream);
@@ -534,7 +540,7 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
         case EPI_RESIDUAL: return launch<EPI_RESIDUAL>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
         case EPI_SWIGLU:
             if (tile_width == 128) return fail("gemm_tcgen05: the gated epilogue takes tiles of 256 weight rows");
-            if (pair == 2 || (pair == 0 && pairs_are_faster(m, 2 * n))) return launch_tile<EPI_SWIGLU, 256, 2>(map_a, map_w, args, multiprocessors, stream);
+            if (pair == 2 || (pair == 0 && pairs_are_faster(m, 2 * n, k, multiprocessors))) return launch_tile<EPI_SWIGLU, 256, 2>(map_a, map_w, args, multiprocessors, stream);
             return launch_tile<EPI_SWIGLU, 256, 1>(map_a, map_w, args, multiprocessors, stream);
     }
     return fail("gemm_tcgen05: unknown epilogue %d", epilogue);
@@ -560,7 +566,7 @@ MB_EXPORT int mb_gemm_tcgen05_qkv_rope(const void* a, int lda, const void* w, in
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
     GemmArgs args{m, n_w, k, n_w, q_out, ld_q, heads, kv_heads, head_dim, page_size, positions, slot_mapping, cos_table, sin_table,
                   (bf16*)k_pool, (bf16*)v_pool};
-    if (pairs_are_faster(m, n_w)) return launch_tile<EPI_ROPE, 256, 2>(map_a, map_w, args, multiprocessors, stream);
+    if (pairs_are_faster(m, n_w, k, multiprocessors)) return launch_tile<EPI_ROPE, 256, 2>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI_ROPE, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }
 

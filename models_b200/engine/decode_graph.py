@@ -30,8 +30,9 @@ def ladder(max_batch: int) -> List[int]:
 
 
 class _Captured:
-    def __init__(self, engine, size: int, blocks: int, pool):
+    def __init__(self, engine, size: int, blocks: int, pool, span: int = 0):
         self.size = size
+        self.span = span  # the class of context lengths the capture is for (ops.decode_span)
         cache = engine.cache
         self.layout = StepLayout(size, size, size, blocks, len(cache.groups))
         self.host = torch.zeros(self.layout.total, dtype=torch.int32)  # the step's indices, kept up to date in place
@@ -42,7 +43,7 @@ class _Captured:
         offsets = [int(o) for o in self.layout.offsets]
         self.host_np[offsets[5]:offsets[6]] = np.arange(size, dtype=np.int32)  # every row's logits, row by row
         self.dev.copy_(self.host)
-        self.batch = batch_from_buffer(self.dev, self.layout, [1] * size, 1, [])
+        self.batch = batch_from_buffer(self.dev, self.layout, [1] * size, max(1, span), [])
         stream = torch.cuda.Stream(device=engine.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
@@ -137,7 +138,7 @@ class DecodeGraphs:
         self.max_batch = max_batch
         self.blocks = blocks
         self.sizes = ladder(max_batch)
-        self.captured: Dict[int, _Captured] = {}
+        self.captured: Dict[tuple, _Captured] = {}  # (batch size, class of context lengths)
         self.last_argmax = None  # first maximum of every row of the last step's logits (device, int32)
         self.pool = torch.cuda.graph_pool_handle()
 
@@ -154,9 +155,11 @@ class DecodeGraphs:
         step then needs nothing from the host that depends on the step before it."""
         engine = self.engine
         size = self.rung(len(entries))
-        captured = self.captured.get(size)
+        # long contexts split their keys over more blocks, and the split is part of the captured launches
+        span = ops.decode_span(1 + max((engine.cache.lengths[e[0]] for e in entries), default=0))
+        captured = self.captured.get((size, span))
         if captured is None:
-            captured = self.captured[size] = _Captured(engine, size, self.blocks, self.pool)
+            captured = self.captured[(size, span)] = _Captured(engine, size, self.blocks, self.pool, span)
         if device_tokens is None:
             captured.update(engine.cache, [e[0] for e in entries], [e[1][0] for e in entries])
             captured.upload()

@@ -253,15 +253,40 @@ def _check_paged(q, out, k_pool, v_pool, block_table, cu_q, kv_lens, kv_heads, h
 _decode_block_bytes = {}
 
 
-def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64, multiprocessors: int = 148) -> int:
-    """How many blocks share one sequence's keys: a power of two, at most 8 (they form one thread-block
-    cluster), with which all blocks of the call are resident at once -- a second, partly filled
-    round of blocks costs more than longer blocks do (measured: 16 sequences of 1,100 positions at
-    head size 128 take 22 us with 2 splits, 29 with 4, 38 with 8).  The kernel runs with three page
-    stages when there are four or more splits (or heads of 96 and more) and with two otherwise, and a
-    block's shared memory follows from that; so does the count.  It depends on the batch size rounded
-    up to a power of two only, never on the lengths, so a batch padded to such a size is split like
-    the unpadded one and a captured step keeps its split."""
+LONG_KEYS = 1024  # up to so many cached positions the split depends on the batch size alone
+
+
+def decode_span(max_kv_len: int) -> int:
+    """The class of context lengths that share one split of the keys: 0 up to LONG_KEYS positions, else
+    the next power of two.  A captured decode step is valid for one class."""
+    if max_kv_len <= LONG_KEYS:
+        return 0
+    span = LONG_KEYS
+    while span < max_kv_len:
+        span *= 2
+    return span
+
+
+def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64, keys: int = 0,
+                  window: Optional[int] = None, multiprocessors: int = 148) -> int:
+    """How many blocks share one sequence's keys.
+
+    Up to LONG_KEYS cached positions (`keys`; 0: unknown, taken as short): a power of two, at most 8
+    (they form one thread-block cluster), with which all blocks of the call are resident at once -- a
+    second, partly filled round of blocks costs more than longer blocks do (measured: 16 sequences of
+    1,100 positions at head size 128 take 22 us with 2 splits, 29 with 4, 38 with 8).  The kernel runs
+    with three page stages when there are four or more splits (or heads of 96 and more) and with two
+    otherwise, and a block's shared memory follows from that; so does the count.  It depends on the
+    batch size rounded up to a power of two only, so a batch padded to such a size is split like the
+    unpadded one.
+
+    Longer contexts: what counts is that enough blocks are in flight to keep memory busy, and a
+    cluster's eight are too few for one or two sequences (one sequence of 32,768 positions, head size
+    64: 58 us with 8 splits, 26 us with 32).  The count is then the larger of what fills the
+    multiprocessors (256 blocks) and one block per 16 pages (64 pages for heads wider than 64, whose
+    pages are twice as large), at most 64, at most 2,048 blocks in all and at least 4 pages each; above
+    8 the partial results meet in scratch memory and a second kernel.  `keys` is rounded up to its class
+    (decode_span), so the count is the same for every length of a class."""
     rounded = 1
     while rounded < sequences:
         rounded *= 2
@@ -272,18 +297,27 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
         _decode_block_bytes[head_dim] = {stages: int(lib.mb_decode_block_bytes(stages)) + 1024 for stages in (2, 3)}
         _decode_block_bytes[head_dim]["wide"] = int(lib.mb_decode_stages(1)) == 3  # three stages whatever the split
 
-    def fitting(stages: int) -> int:
-        resident = max(1, (227 * 1024) // _decode_block_bytes[head_dim][stages])
-        limit = max(1, min(8, (resident * multiprocessors) // max(1, base)))
+    def power_of_two_up_to(limit: int) -> int:
         splits = 1
         while splits * 2 <= limit:
             splits *= 2
         return splits
 
+    def fitting(stages: int) -> int:
+        resident = max(1, (227 * 1024) // _decode_block_bytes[head_dim][stages])
+        return power_of_two_up_to(max(1, min(8, (resident * multiprocessors) // max(1, base))))
+
     with_three = fitting(3)
-    if _decode_block_bytes[head_dim]["wide"] or with_three >= 4:
-        return with_three
-    return min(2, fitting(2))
+    short = with_three if _decode_block_bytes[head_dim]["wide"] or with_three >= 4 else min(2, fitting(2))
+    span = decode_span(keys)
+    if span == 0:
+        return short
+    visible = min(span, window) if window else span
+    pages = -(-visible // 64)
+    by_length = pages // (16 if head_dim <= 64 else 64)
+    want = max(256 // base, by_length)
+    want = power_of_two_up_to(max(1, min(want, 64, 2048 // base, pages // 4)))
+    return want if want > 8 else short
 
 
 def decode_attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

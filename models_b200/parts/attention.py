@@ -152,7 +152,7 @@ class AttentionMixer(Mixer):
         args = (qkv, attended, run.k_pool, run.v_pool, group.block_table, batch.cu_q, batch.kv_lens)
         if ops.attention_tc_takes(qkv.dtype, s.head_dim, run.k_pool.shape[2]):
             if batch.max_q_len == 1:
-                splits = ops.decode_splits(batch.num_sequences, s.num_heads, s.num_kv_heads, s.head_dim)
+                splits = ops.decode_splits(batch.num_sequences, s.num_heads, s.num_kv_heads, s.head_dim, batch.max_kv_len, s.window)
                 ops.decode_attention(*args, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale, splits)
             else:
                 ops.prefill_attention(*args, batch.max_q_len, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)

@@ -103,8 +103,36 @@ def test_long_decoding_with_graphs_matches_plain(cuda_device, folders, dtype):
         else:
             out = engine.decode([sa], [a[3 + i]])
         assert scaled_error(out[0], ea[3 + i]) < TOLERANCE[dtype], ("a", i)
-    assert engine.decode_graphs is not None and set(engine.decode_graphs.captured) == {1, 2}
+    assert engine.decode_graphs is not None and set(engine.decode_graphs.captured) == {(1, 0), (2, 0)}
     engine.release_slot(sa)
+    engine.cache.check()
+
+
+def test_graph_decoding_across_a_context_class(cuda_device, tmp_path):
+    """A sequence grows from 2,040 to 2,060 positions while it decodes with CUDA graphs: past 2,048 its
+    keys are split over more blocks than a cluster holds, which takes a capture of its own; every
+    step's logits are compared with the plain implementation."""
+    import models_b200
+    from models_b200.engine import StepEntry
+    from models_b200.kernels import ops
+    from tiny import TINY_B
+
+    raw = dict(TINY_B, max_position_embeddings=4096)
+    folder = make_folder(raw, seed=77, tmp_path=tmp_path, std=0.08)
+    tokens = random_tokens(raw["vocab_size"], 2061, 5)
+    expected = plain_logits(folder, tokens)
+    model = models_b200.load_model(folder, dtype="bfloat16", max_batch=1, context=2112)
+    engine = model.engine
+    slot = engine.open_slot()
+    out = engine.step([StepEntry(slot, tokens[:2040], [2039])])
+    assert scaled_error(out[0], expected[2039]) < TOLERANCE["bfloat16"]
+    for i in range(2040, 2061):
+        out = engine.decode([slot], [tokens[i]])
+        assert scaled_error(out[0], expected[i]) < TOLERANCE["bfloat16"], i
+    spans = {span for _, span in engine.decode_graphs.captured}
+    assert spans == {ops.decode_span(2041), ops.decode_span(2049)} == {2048, 4096}
+    assert ops.decode_splits(1, raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], 2049) > 8
+    engine.release_slot(slot)
     engine.cache.check()
 
 

@@ -376,6 +376,50 @@ def test_attention_finds_one_far_key(cuda_device):
                                       atol=1e-2), (far, splits)
 
 
+def test_decode_attention_finds_one_far_key_in_a_long_context(cuda_device):
+    """5,000 cached positions split over 16 to 64 blocks (partial results through scratch memory): the one
+    key that stands out may lie in any split, also the first and the last, and in a split's last page."""
+    from models_b200.kernels import ops
+
+    heads, kv_heads, head_dim, page = 8, 2, 64, 64
+    total = 5000
+    pages = -(-total // page)
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(3)).to(torch.int32) + 1
+    table = order.reshape(1, pages)
+    for far in (0, 63, 2047, 2048, 3333, 4992, 4999):
+        k_pool = torch.zeros(pages + 1, kv_heads, page, head_dim)
+        v_pool = torch.randn(pages + 1, kv_heads, page, head_dim, generator=torch.Generator().manual_seed(far))
+        k_pool[table[0, far // page], :, far % page, :] = 4.0
+        q = torch.ones(1, heads * head_dim)
+        for splits in (16, 32, 64):
+            assert ops.decode_splits(1, heads, kv_heads, head_dim, total) > 8  # what the engine would choose is of this kind
+            out = torch.zeros(1, heads * head_dim, device="cuda", dtype=torch.bfloat16)
+            ops.decode_attention(q.bfloat16().cuda(), out, k_pool.bfloat16().cuda(), v_pool.bfloat16().cuda(), table.cuda(),
+                                 torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                                 torch.tensor([total], dtype=torch.int32).cuda(), heads, kv_heads, head_dim, None, 1.0, splits)
+            for h in range(heads):
+                expected = v_pool[table[0, far // page], h // (heads // kv_heads), far % page, :]
+                assert torch.allclose(out[0, h * head_dim:(h + 1) * head_dim].float().cpu(), expected.bfloat16().float(),
+                                      atol=1e-2), (far, splits, h)
+
+
+def test_decode_splits_follow_the_context_class(cuda_device):
+    """Short contexts: the split depends on the batch size alone and stays within a cluster.  Long ones:
+    more blocks for few sequences, the same count for every length of a class."""
+    from models_b200.kernels import ops
+
+    short = ops.decode_splits(1, 32, 8, 64)
+    assert short <= 8 and short == ops.decode_splits(1, 32, 8, 64, 1) == ops.decode_splits(1, 32, 8, 64, ops.LONG_KEYS)
+    assert ops.decode_span(ops.LONG_KEYS) == 0 and ops.decode_span(ops.LONG_KEYS + 1) == 2 * ops.LONG_KEYS
+    assert ops.decode_span(5000) == 8192 and ops.decode_span(8192) == 8192
+    for keys in (4097, 5000, 8192):
+        assert ops.decode_splits(1, 32, 8, 64, keys) == ops.decode_splits(1, 32, 8, 64, 8192) > 8
+    assert ops.decode_splits(1, 32, 8, 64, 32768) == 32
+    assert ops.decode_splits(8, 32, 8, 64, 65536) == 32  # 2,048 blocks at most
+    assert ops.decode_splits(64, 32, 8, 64, 16384) <= 8
+    assert ops.decode_splits(1, 32, 8, 64, 32768, window=512) == short  # a window's few pages need no more blocks
+
+
 def test_argmax_first_maximum(cuda_device):
     from models_b200.kernels import ops
 
