@@ -38,7 +38,8 @@ constexpr int kChunks = HD / 8;           // 16-byte pieces of a row
 constexpr int kKSteps = HD / 16;
 constexpr int kThreads = 128;
 constexpr int kQRowsDecode = 16;
-// Pages of keys and values in shared memory per decode block: two or three, chosen at launch (mb_decode_stages).
+// Pages of keys and values in shared memory per decode block: two or three, chosen at launch (mb_decode_stages; six for
+// a few blocks over long contexts, see decode_stages).
 // A third stage helps where a block has only a few pages -- all of them are then in flight at once; with four blocks
 // of three stages per sequence, batch 8 of the 1B model gains 2 % over eight blocks of two -- and at head sizes of 96
 // and more (64 sequences of 1,280 positions at head size 128: 4.3 -> 5.2 TB/s).  With heads of 64 and long loops it
@@ -579,6 +580,22 @@ MB_EXPORT int mb_attention_head_dim() { return HD; }
 // Page stages a decode call with `splits` blocks per sequence runs with (see the note on page stages above), and the
 // shared memory of one block with so many stages: for callers that plan how many blocks are resident at once.
 MB_EXPORT int mb_decode_stages(int splits) { return (HD >= 96 || splits >= 4) ? 3 : 2; }
+// More than a cluster's eight splits are for long contexts.  While the call's blocks are so few that at most two
+// share a multiprocessor, pages of 8 KB (heads up to 64) are fetched five ahead instead of two: one sequence of
+// 32,768 positions, 32 splits, 26.4 -> 24.2 us; of 131,072 positions 80.9 -> 71.4 us.  With more blocks the
+// shared memory is worth more as room for further blocks (8 sequences of 65,536 positions: 195 us with three
+// stages, 242 us with six), and pages of wider heads gain nothing from a deeper ring.
+constexpr int kLongStages = HD <= 64 ? 6 : 3;
+static int decode_stages(int splits, long blocks) {
+    static int multiprocessors = 0;
+    if (!multiprocessors) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+            multiprocessors = 148;
+    }
+    if (splits > 8 && blocks <= 2L * multiprocessors) return kLongStages;
+    return mb_decode_stages(splits);
+}
 MB_EXPORT size_t mb_decode_block_bytes(int stages) { return decode_smem(stages); }
 
 // Scratch floats a decode call with `splits` > 1 needs: partial outputs and (maximum, sum) pairs.
@@ -596,7 +613,7 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     const int group = heads / kv_heads;
     const int head_chunks = (group + 15) / 16;
     if (sequences > 65535 || kv_heads * head_chunks > 65535) return fail("decode_attention: grid too large");
-    const int stages = mb_decode_stages(splits);
+    const int stages = decode_stages(splits, (long)splits * kv_heads * head_chunks * sequences);
     static bool configured = false;
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
@@ -606,7 +623,9 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
             status = cudaFuncSetAttribute(decode_attention_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
         if (status == cudaSuccess)
             status = cudaFuncSetAttribute(decode_attention_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
-        if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(3), cudaGetErrorString(status));
+        if (status == cudaSuccess && kLongStages > 3)
+            status = cudaFuncSetAttribute(decode_attention_kernel<false, kLongStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(kLongStages));
+        if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(kLongStages), cudaGetErrorString(status));
         configured = true;
     }
     const dim3 grid(splits, kv_heads * head_chunks, sequences);
@@ -637,7 +656,8 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     }
     float* partial_o = scratch;
     float* partial_ml = scratch ? scratch + (size_t)sequences * heads * splits * HD : nullptr;
-    auto kernel = stages == 3 ? decode_attention_kernel<false, 3> : decode_attention_kernel<false, 2>;
+    auto kernel = stages == kLongStages ? decode_attention_kernel<false, kLongStages>
+                                        : (stages == 3 ? decode_attention_kernel<false, 3> : decode_attention_kernel<false, 2>);
     if (int status = launch_dependent("decode_attention", kernel, grid, dim3(kThreads), decode_smem(stages), stream, true,
                                       (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool,
                                       (const bf16*)v_pool, block_table, max_blocks, cu_q, kv_lens, heads, kv_heads, head_chunks,
