@@ -107,6 +107,55 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ x, const TD* __restr
     }
 }
 
+// Many rows (a prompt's): one warp per row and the row in registers, kVec groups of four elements per lane.  All of a
+// row's loads are in flight at once and nothing waits at a block barrier; with one block per row a step of 2,048
+// rows of 2,048 spent most of its time between its two passes.  width <= 128 * kVec.
+template <typename TD, typename TO, int kVec>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ x, const TD* __restrict__ delta, const float* __restrict__ weight,
+                        TO* __restrict__ out, const int* __restrict__ rows, int out_rows, int width, float eps, int write_x) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int out_row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (out_row >= out_rows) return;
+    const int in_row = rows ? rows[out_row] : out_row;
+    float* xr = x + (size_t)in_row * width;
+    const TD* dr = delta ? delta + (size_t)in_row * width : nullptr;
+    float4 v[kVec];
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+        const int d = (i * 32 + lane) * 4;
+        v[i] = d < width ? load4(xr + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (dr) {
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+            const int d = (i * 32 + lane) * 4;
+            if (d < width) {
+                const float4 e = load4(dr + d);
+                v[i].x += e.x; v[i].y += e.y; v[i].z += e.z; v[i].w += e.w;
+                if (write_x) store4(xr + d, v[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) sum_sq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    sum_sq = warp_sum(sum_sq);
+    const float rms = sqrtf(sum_sq / (float)width + eps);
+    const float scale = 1.0f / rms;
+    TO* o = out + (size_t)out_row * width;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+        const int d = (i * 32 + lane) * 4;
+        if (d < width) {
+            const float4 w = load4(weight + d);
+            store4(o + d, make_float4(v[i].x * scale * w.x, v[i].y * scale * w.y, v[i].z * scale * w.z, v[i].w * scale * w.w));
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------ rotary + cache
 
 // grid (tokens, heads + 2*kv_heads).  Query heads are rotated in place; key heads are rotated and
@@ -291,6 +340,8 @@ MB_EXPORT int mb_embed_gather(const void* table, int table_dtype, const int* tok
     return check_launch("embed_gather");
 }
 
+constexpr int kRowsPerWarpFrom = 256;  // from so many rows on, a warp per row (add_rmsnorm_rows_kernel)
+
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
                               int out_rows, int width, float eps, int write_x, cudaStream_t stream) {
@@ -304,6 +355,17 @@ static int launch_add_rmsnorm(float* x, const void* delta, const float* weight, 
     const int block = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
     const bool aligned = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)delta & 7) && !((uintptr_t)weight & 15) &&
                          !((uintptr_t)out & 7);
+    if (aligned && out_rows >= kRowsPerWarpFrom && width <= 4096) {
+        const int warps = 8, grid = (out_rows + warps - 1) / warps;
+#define MB_ROWS_KERNEL(kVec)                                                                                              \
+    return launch_dependent("add_rmsnorm", add_rmsnorm_rows_kernel<TD, TO, kVec>, dim3(grid), dim3(32 * warps), 0, stream, \
+                            true, x, (const TD*)delta, weight, (TO*)out, rows, out_rows, width, eps, write_x)
+        if (width <= 512) MB_ROWS_KERNEL(4);
+        if (width <= 1024) MB_ROWS_KERNEL(8);
+        if (width <= 2048) MB_ROWS_KERNEL(16);
+        MB_ROWS_KERNEL(32);
+#undef MB_ROWS_KERNEL
+    }
     if (aligned) {
         auto vec = add_rmsnorm_vec4_kernel<TD, TO>;
         if (smem > 48 * 1024) {

@@ -39,13 +39,15 @@ def test_embed_gather(cuda_device, dtype):
 
 
 @pytest.mark.parametrize("out_dtype", DTYPES)
-@pytest.mark.parametrize("width", [72, 2048, 5000])
-def test_add_rmsnorm(cuda_device, out_dtype, width):
+@pytest.mark.parametrize("width,count", [(72, 7), (2048, 7), (5000, 7), (72, 300), (264, 300), (1028, 261), (2048, 300),
+                                         (3080, 259), (4096, 257), (5000, 260)])
+def test_add_rmsnorm(cuda_device, out_dtype, width, count):
+    """Few rows: a block per row; from 256 rows on, a warp per row (widths up to 4,096)."""
     from models_b200.kernels import ops
 
     g = torch.Generator().manual_seed(1)
-    x = torch.randn(7, width, generator=g) * 3
-    delta = (torch.randn(7, width, generator=g)).to(out_dtype)
+    x = torch.randn(count, width, generator=g) * 3
+    delta = (torch.randn(count, width, generator=g)).to(out_dtype)
     weight = 1 + 0.1 * torch.randn(width, generator=g)
     eps = 3e-6
     xd = x.cuda()
@@ -54,7 +56,7 @@ def test_add_rmsnorm(cuda_device, out_dtype, width):
     close(xd, summed, torch.float32)
     close(out, plain_llama.rms_norm(summed, weight, eps), out_dtype)
     # without a delta, on chosen rows, x untouched
-    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32) if count < 256 else torch.randperm(count, generator=g)[:257].int()
     before = xd.clone()
     out = ops.add_rmsnorm(xd, None, weight.cuda(), eps, out_dtype, rows=rows.cuda())
     assert torch.equal(before, xd)
