@@ -25,6 +25,8 @@
 // Every wait on an mbarrier is bounded: after about two seconds a role gives up, records where in
 // g_gemm_status and leaves its loop; all roles then meet at the final barrier, tensor memory is
 // freed and the kernel returns.  mb_gemm_tc_status() reads the record.
+#include <algorithm>
+
 #include "tcgen05.cuh"
 
 MB_DEFINE_LAST_ERROR()
@@ -113,6 +115,7 @@ __device__ __forceinline__ void tile_coordinates(int tile, int m_tiles, int n_ti
 struct GemmArgs {
     int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
     int up_row_offset;    // EPI_SWIGLU: first up row of W
+    int k_splits;         // EPI_RESIDUAL: blocks that share an output tile, each with its own part of K (else 1)
     void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream; EPI_ROPE: the queries [m, heads * head_dim]
     int ld_out;
     // EPI_ROPE: W is [q heads; k heads; v heads]
@@ -153,8 +156,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
     const int m_tiles = (args.m + kBlockM * kPair - 1) / (kBlockM * kPair);
     const int n_tiles = (args.n + kOutCols - 1) / kOutCols;
-    const int tiles = m_tiles * n_tiles;
-    const int k_blocks = (args.k + kBlockK - 1) / kBlockK;
+    // A work item is an output tile, or with k_splits > 1 one of the parts of K of an output tile: the parts' sums meet
+    // in the residual stream, each added there by its own block.
+    const int k_splits = EPI == EPI_RESIDUAL ? args.k_splits : 1;
+    const int tiles = m_tiles * n_tiles * k_splits;
+    const int k_blocks_all = (args.k + kBlockK - 1) / kBlockK;
+    const int k_blocks_per_split = (k_blocks_all + k_splits - 1) / k_splits;  // the launcher leaves no part empty
     const int first_tile = blockIdx.x / kPair, tile_step = gridDim.x / kPair;  // a pair walks the tiles together
 
     if (threadIdx.x == 0) {
@@ -193,11 +200,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
                 int m_tile, n_tile;
-                tile_coordinates(tile, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+                tile_coordinates(tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+                const int kb_begin = (tile % k_splits) * k_blocks_per_split, kb_end = min(kb_begin + k_blocks_per_split, k_blocks_all);
                 const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
                 const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
                 const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
                     const uint32_t dst = smem_u32(smem) + stage * kStageBytes;
                     if (kPair == 2) {
@@ -229,15 +237,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!(ok = mbar_wait(acc_empty_bar + 8 * acc, acc_phase, 2))) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * kAccumulatorColumns;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                const int kb_begin = (tile % k_splits) * k_blocks_per_split, kb_end = min(kb_begin + k_blocks_per_split, k_blocks_all);
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!(ok = mbar_wait(full_bar + 8 * stage, phase, 3))) break;
                     tcgen05_fence_after();
                     const uint32_t a_addr = smem_u32(smem) + stage * kStageBytes;
                     const uint64_t a_desc = umma_descriptor(a_addr), b_desc = umma_descriptor(a_addr + kTileABytes);
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 16; ++ks) {  // 32 bytes further along K per step: +2 in the address field
-                        if (kPair == 2) umma_pair(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
-                        else umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > 0 || ks > 0) ? 1u : 0u);
+                        if (kPair == 2) umma_pair(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                        else umma(tmem_d, a_desc + 2 * ks, b_desc + 2 * ks, kInstruction, (kb > kb_begin || ks > 0) ? 1u : 0u);
                     }
                     // the stage is free (in both blocks of a pair) once these products have read it
                     if (kPair == 2) umma_commit_pair(empty_bar + 8 * stage);
@@ -268,7 +277,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
             int m_tile, n_tile;
-            tile_coordinates(tile, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+            tile_coordinates(tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
             const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
             ok = mbar_wait(acc_full_bar + 8 * acc, acc_phase, 4);
             ok = __all_sync(0xffffffffu, ok);
@@ -393,7 +402,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             if (col + 4 <= args.n) {
                                 if (EPI == EPI_RESIDUAL) {
                                     // x += value without reading x here: the addition happens at the memory side.  Every
-                                    // element of x gets exactly one such addition per product, so the sum has one order.
+                                    // element of x gets one such addition per product and part of K.
                                     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
                                                  : "memory");
                                 } else {
@@ -402,7 +411,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             } else {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i)  // (fixed indices: the values stay in registers)
-                                    if (col + i < args.n) dst[i] = EPI == EPI_RESIDUAL ? dst[i] + v[i] : v[i];
+                                    if (col + i < args.n) {
+                                        if (EPI == EPI_RESIDUAL) atomicAdd(dst + i, v[i]);  // other parts of K add to the same element
+                                        else dst[i] = v[i];
+                                    }
                             }
                         } else {
                             bf16* dst = reinterpret_cast<bf16*>(args.out) + (size_t)out_row * args.ld_out + col;
@@ -442,8 +454,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// Few tiles and a long K (a prompt of a few hundred tokens; the down product above all): with the residual epilogue,
+// parts of K go to blocks of their own, at least 8 steps of 64 each and at most 8 parts, and every part adds its sum
+// to the residual stream.  The order in which the parts of an element arrive is not fixed, so its last bit may differ
+// from run to run.  Measured at 256 rows, K = 8192, N = 2048: 40 us as 16 tiles, 15 us as 8 parts each, 14 us for
+// the library's kernel.  `units`: blocks (or pairs) that run at once.
+static int residual_k_splits(long tiles, int k, int units) {
+    const int k_blocks = (k + kBlockK - 1) / kBlockK;
+    const int want = (int)std::min<long>(std::min<long>(8, units / (tiles > 0 ? tiles : 1)), k_blocks / 8);
+    if (want <= 1) return 1;
+    const int per_split = (k_blocks + want - 1) / want;
+    return (k_blocks + per_split - 1) / per_split;  // no part is empty
+}
+
 template <int EPI, int BN, int kPair>
-static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, cudaStream_t stream) {
+static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& given, int multiprocessors, cudaStream_t stream) {
     constexpr int kOutCols = EPI == EPI_SWIGLU ? 128 : BN;
     const size_t smem = (size_t)kRingBytes + kEpilogueWarps * kStagingBytes + 1024;
     auto kernel = gemm_tcgen05_kernel<EPI, BN, kPair>;
@@ -453,7 +478,12 @@ static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const
         if (status != cudaSuccess) return fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
         configured = true;
     }
-    const int tiles = ((args.m + kBlockM * kPair - 1) / (kBlockM * kPair)) * ((args.n + kOutCols - 1) / kOutCols);
+    GemmArgs args = given;
+    int tiles = ((args.m + kBlockM * kPair - 1) / (kBlockM * kPair)) * ((args.n + kOutCols - 1) / kOutCols);
+    if (EPI == EPI_RESIDUAL) {
+        args.k_splits = residual_k_splits(tiles, args.k, kPair == 2 ? multiprocessors / 2 : multiprocessors);
+        tiles *= args.k_splits;
+    }
     if (kPair == 1) {
         const int grid = tiles < multiprocessors ? tiles : multiprocessors;
         return launch_dependent("gemm_tcgen05", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_a, map_w, args);
@@ -479,13 +509,22 @@ static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const
     return check_launch("gemm_tcgen05");
 }
 
-// Which tile width finishes first: rounds of tiles over the multiprocessors times the cost of a tile, a
-// narrow tile counted at 0.75 of a wide one (it moves more bytes per product; measured 0.7 to 0.8).
-static bool narrow_tiles_are_faster(int m, int n, int multiprocessors) {
+// Which tile width finishes first: rounds of tiles over the multiprocessors times the steps of a tile's loop over K,
+// a narrow tile's step counted at 0.75 of a wide one's (it moves more bytes per product; measured 0.7 to 0.8), plus
+// what a block costs before and after its loop (about 15 steps).  With the residual epilogue each width is taken
+// with the split of K it would run with.
+static bool narrow_tiles_are_faster(int m, int n, int k, int multiprocessors, bool residual) {
     const long m_tiles = (m + kBlockM - 1) / kBlockM;
-    const long wide = m_tiles * ((n + 255) / 256), narrow = m_tiles * ((n + 127) / 128);
-    const long wide_rounds = (wide + multiprocessors - 1) / multiprocessors, narrow_rounds = (narrow + multiprocessors - 1) / multiprocessors;
-    return narrow_rounds * 75 < wide_rounds * 100;
+    const long k_blocks = (k + kBlockK - 1) / kBlockK;
+    long cost[2];
+    for (int narrow = 0; narrow < 2; ++narrow) {
+        const long tiles = m_tiles * ((n + (narrow ? 127 : 255)) / (narrow ? 128 : 256));
+        const long splits = residual ? residual_k_splits(tiles, k, multiprocessors) : 1;
+        const long rounds = (tiles * splits + multiprocessors - 1) / multiprocessors;
+        const long steps = (k_blocks + splits - 1) / splits;
+        cost[narrow] = rounds * (steps * (narrow ? 75 : 100) + 1500);
+    }
+    return cost[1] < cost[0];
 }
 
 // Pairs of blocks (tiles of 256 x 256) move a third less through L2 and shared memory per product and win wherever
@@ -504,7 +543,7 @@ template <int EPI>
 static int launch(const CUtensorMap& map_a, const CUtensorMap& map_w, const GemmArgs& args, int multiprocessors, int tile_width,
                   int pair, cudaStream_t stream) {
     if (pair == 2 || (pair == 0 && tile_width == 0 && pairs_are_faster(args.m, args.n, args.k, multiprocessors))) return launch_tile<EPI, 256, 2>(map_a, map_w, args, multiprocessors, stream);
-    const bool narrow = tile_width == 128 || (tile_width == 0 && narrow_tiles_are_faster(args.m, args.n, multiprocessors));
+    const bool narrow = tile_width == 128 || (tile_width == 0 && narrow_tiles_are_faster(args.m, args.n, args.k, multiprocessors, EPI == EPI_RESIDUAL));
     if (narrow) return launch_tile<EPI, 128, 1>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }
@@ -533,7 +572,7 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     CUtensorMap map_a, map_w;
     if (int status = make_map(&map_a, a, m, k, lda)) return status;
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
-    GemmArgs args{m, n, k, n, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    GemmArgs args{m, n, k, n, 1, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     switch (epilogue) {
         case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
         case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
@@ -564,7 +603,7 @@ MB_EXPORT int mb_gemm_tcgen05_qkv_rope(const void* a, int lda, const void* w, in
     CUtensorMap map_a, map_w;
     if (int status = make_map(&map_a, a, m, k, lda)) return status;
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
-    GemmArgs args{m, n_w, k, n_w, q_out, ld_q, heads, kv_heads, head_dim, page_size, positions, slot_mapping, cos_table, sin_table,
+    GemmArgs args{m, n_w, k, n_w, 1, q_out, ld_q, heads, kv_heads, head_dim, page_size, positions, slot_mapping, cos_table, sin_table,
                   (bf16*)k_pool, (bf16*)v_pool};
     if (pairs_are_faster(m, n_w, k, multiprocessors)) return launch_tile<EPI_ROPE, 256, 2>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI_ROPE, 256, 1>(map_a, map_w, args, multiprocessors, stream);

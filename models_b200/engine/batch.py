@@ -77,8 +77,10 @@ def plan_layout(cache, entries, pad_sequences: int = 0, blocks: int = 0) -> Step
     return StepLayout(B, T, R, blocks or need_blocks, len(cache.groups))
 
 
-def pack_step(cache, entries, layout: StepLayout, buf: np.ndarray, state_pad_row: int = 0):
-    """Fills `buf` (int32, layout.total long) for the step; returns (q_lens, max_kv_len)."""
+def pack_step(cache, entries, layout: StepLayout, buf: np.ndarray, state_pad_row: int = 0, empty_padding: bool = False):
+    """Fills `buf` (int32, layout.total long) for the step; returns (q_lens, max_kv_len).  Sequences
+    beyond the entries are padding: of one token each, or with `empty_padding` of none -- the rows
+    that are left over then belong to no sequence (token 0, position 0, nothing stored, no logits)."""
     B, T, width, n_groups = layout.sequences, layout.tokens, layout.blocks, layout.groups
     offsets = layout.offsets
     buf[:] = 0
@@ -110,14 +112,19 @@ def pack_step(cache, entries, layout: StepLayout, buf: np.ndarray, state_pad_row
             mappings[g][row:row + n] = table[pos // page] * page + pos % page
         row += n
     for b in range(len(entries), B):  # padding sequences
-        q_lens.append(1)
+        q_lens.append(0 if empty_padding else 1)
         cu_q_a[b] = row
         kv_lens_a[b] = 1
         slots_a[b] = state_pad_row
-        for g in range(n_groups):
-            mappings[g][row] = -1
-        row += 1
+        if not empty_padding:
+            for g in range(n_groups):
+                mappings[g][row] = -1
+            row += 1
     cu_q_a[B] = row
+    if row > T:
+        raise ValueError(f"the step's {row} tokens do not fit the layout's {T} rows")
+    for g in range(n_groups):  # rows of no sequence
+        mappings[g][row:] = -1
     return q_lens, max_kv
 
 

@@ -1,10 +1,15 @@
-"""Decode steps as CUDA graphs: one token per live sequence, the whole model in one launch.
+"""Steps as CUDA graphs: the whole model in one launch.
 
 A decode step at small batch is a few hundred short kernels, so launching them costs more than
 running them.  For each batch size out of a short ladder the step is captured once over fixed
 device buffers; a step then copies its indices (tokens, positions, page tables) into those
 buffers and replays.  A batch smaller than its rung is padded with sequences of one token that
 point at the cache's spare page and store nothing, so padding changes no result.
+
+Short prompts are in the same position: a step of a few hundred tokens runs for a fraction of a
+millisecond and takes two to launch.  Steps of up to PROMPT_TOKENS[-1] tokens are captured by
+(batch size, token count) class, the token count rounded up to one of PROMPT_TOKENS; sequences
+that are missing are empty, and the rows left over belong to no sequence.
 """
 
 from __future__ import annotations
@@ -30,20 +35,27 @@ def ladder(max_batch: int) -> List[int]:
 
 
 class _Captured:
-    def __init__(self, engine, size: int, blocks: int, pool, span: int = 0):
+    """One captured step: `size` sequences of one token each, or with `tokens` a step of so many
+    rows shared by up to `size` sequences in any way."""
+
+    def __init__(self, engine, size: int, blocks: int, pool, span: int = 0, tokens: Optional[int] = None):
         self.size = size
         self.span = span  # the class of context lengths the capture is for (ops.decode_span)
         cache = engine.cache
-        self.layout = StepLayout(size, size, size, blocks, len(cache.groups))
+        prompts = tokens is not None
+        self.layout = StepLayout(size, tokens if prompts else size, size, blocks, len(cache.groups))
         self.host = torch.zeros(self.layout.total, dtype=torch.int32)  # the step's indices, kept up to date in place
         self.host_np = self.host.numpy()
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=engine.device)
         # a first layout that is valid to run: every row is padding
-        pack_step(cache, [], self.layout, self.host_np, cache.max_slots)
+        pack_step(cache, [], self.layout, self.host_np, cache.max_slots, empty_padding=prompts)
         offsets = [int(o) for o in self.layout.offsets]
-        self.host_np[offsets[5]:offsets[6]] = np.arange(size, dtype=np.int32)  # every row's logits, row by row
+        if not prompts:
+            self.host_np[offsets[5]:offsets[6]] = np.arange(size, dtype=np.int32)  # every row's logits, row by row
         self.dev.copy_(self.host)
-        self.batch = batch_from_buffer(self.dev, self.layout, [1] * size, max(1, span), [])
+        # the sizes kernels are launched with: one token each, or as if one sequence held every row
+        q_lens = [tokens] + [0] * (size - 1) if prompts else [1] * size
+        self.batch = batch_from_buffer(self.dev, self.layout, q_lens, max(1, span), [])
         stream = torch.cuda.Stream(device=engine.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
@@ -92,6 +104,12 @@ class _Captured:
         first = self.layout.tokens if skip_tokens else 0
         self.dev[first:].copy_(staging[first:], non_blocking=True)
         event.record()
+
+    def fill(self, cache, entries) -> int:
+        """The indices of a step of any shape that fits (prompts of unequal lengths), packed anew;
+        returns how many rows of logits the step wants."""
+        pack_step(cache, entries, self.layout, self.host_np, cache.max_slots, empty_padding=True)
+        return sum(len(want) for _, _, want in entries)
 
     def update(self, cache, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
         """The indices of one decode step, written in place: one token per slot, appended at each
@@ -171,3 +189,52 @@ class DecodeGraphs:
         ops.add_launches(captured.kernels)
         self.last_argmax = captured.argmax[: len(entries)]
         return captured.logits[: len(entries)]
+
+
+PROMPT_TOKENS = (16, 32, 64, 128, 256, 512)  # token counts at which prompt steps are captured
+EAGER_USES = 2  # a class of steps is captured when it comes up for the third time: a capture costs tens of steps
+
+
+class PromptGraphs:
+    """Steps that bring several tokens to their sequences, replayed from captures by class."""
+
+    def __init__(self, decode_graphs: DecodeGraphs):
+        self.decode_graphs = decode_graphs
+        self.engine = decode_graphs.engine
+        self.captured: Dict[tuple, _Captured] = {}  # (batch size, token count)
+        self.uses: Dict[tuple, int] = {}
+
+    def bucket(self, entries: Sequence) -> Optional[tuple]:
+        """The class of the step, or None for one that runs launch by launch: too many tokens or
+        sequences, more logits wanted than sequences (or none), a page table wider than the captures'."""
+        graphs, cache = self.decode_graphs, self.engine.cache
+        total = sum(len(tokens) for _, tokens, _ in entries)
+        wanted = sum(len(want) for _, _, want in entries)
+        if len(entries) > graphs.max_batch or total > PROMPT_TOKENS[-1] or wanted == 0:
+            return None
+        size = graphs.rung(len(entries))
+        if wanted > size:
+            return None
+        if any(-(-(cache.lengths[slot] + len(tokens)) // cache.page_size) > graphs.blocks for slot, tokens, _ in entries):
+            return None
+        return size, next(t for t in PROMPT_TOKENS if t >= total)
+
+    def step(self, entries: Sequence) -> Optional[torch.Tensor]:
+        """entries: (slot, tokens, wanted places); the cache already has room.  Returns the logits of
+        the wanted places (a copy: the capture's buffer is rewritten by its next replay), or None
+        when the step is not one for a capture -- the caller then runs it launch by launch."""
+        key = self.bucket(entries)
+        if key is None:
+            return None
+        captured = self.captured.get(key)
+        if captured is None:
+            self.uses[key] = self.uses.get(key, 0) + 1
+            if self.uses[key] <= EAGER_USES:
+                return None
+            graphs = self.decode_graphs
+            captured = self.captured[key] = _Captured(self.engine, key[0], graphs.blocks, graphs.pool, tokens=key[1])
+        wanted = captured.fill(self.engine.cache, entries)
+        captured.upload()
+        captured.graph.replay()
+        ops.add_launches(captured.kernels)
+        return captured.logits[:wanted].clone()

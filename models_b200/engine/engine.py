@@ -76,16 +76,20 @@ class Engine:
             self.runs.append(ctx)
         self.steps = 0
         self.decode_graphs = None
+        self.prompt_graphs = None
         self.last_argmax = None
         self._last_logits = None
 
     def enable_decode_graphs(self, max_batch: int, max_sequence: Optional[int] = None) -> None:
         """Captures decode steps of up to `max_batch` sequences of up to `max_sequence` positions
         as CUDA graphs (lazily, one per batch size of a ladder)."""
-        from .decode_graph import DecodeGraphs
+        from .decode_graph import DecodeGraphs, PromptGraphs
 
         longest = min(max_sequence or self.runtime.max_positions, self.runtime.max_positions)
         self.decode_graphs = DecodeGraphs(self, max_batch, -(-longest // self.cache.page_size))
+        # short prompt steps too, unless a part keeps state of its own per sequence: such a part may
+        # walk the sequences on the host, which a capture would freeze
+        self.prompt_graphs = None if self.state.tensors else PromptGraphs(self.decode_graphs)
 
     # ------------------------------------------------------------------ slots
 
@@ -141,9 +145,11 @@ class Engine:
         self.validate(entries)
         appends = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.append(appends)
-        batch = build_step_batch(self.cache, [(e.slot, e.tokens, e.want) for e in entries], self.device,
-                                 state_pad_row=self.cache.max_slots)
-        logits = self.model.forward(batch, self.runs)
+        packed = [(e.slot, e.tokens, e.want) for e in entries]
+        logits = self.prompt_graphs.step(packed) if self.prompt_graphs is not None else None
+        if logits is None:
+            batch = build_step_batch(self.cache, packed, self.device, state_pad_row=self.cache.max_slots)
+            logits = self.model.forward(batch, self.runs)
         self.cache.commit(appends)
         self.steps += 1
         return logits

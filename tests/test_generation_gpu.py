@@ -136,6 +136,73 @@ def test_graph_decoding_across_a_context_class(cuda_device, tmp_path):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_prompt_steps_replayed_from_captures_match_plain(cuda_device, folders, name, dtype):
+    """Batches of unequal prompts, one after another so that slots are used again; from the third
+    step of a class on, the step is a replayed capture with empty sequences and spare rows as
+    padding.  Every wanted row is compared with the plain implementation, and a prompt that
+    arrives in two pieces continues on what the first piece left."""
+    import models_b200
+    from models_b200.engine import StepEntry
+
+    vocab = TINY[name]["vocab_size"]
+    model = models_b200.load_model(folders[name], dtype=dtype, max_batch=4, context=128)
+    engine = model.engine
+    assert engine.prompt_graphs is not None
+    seed = 0
+    for round_ in range(6):
+        lengths = [(5, 9, 4), (11, 3, 8), (7, 7, 7, 1), (12, 2, 9), (2, 25, 4), (19, 6, 5)][round_]  # 17 to 32 tokens
+        prompts = []
+        for n in lengths:
+            seed += 1
+            prompts.append(random_tokens(vocab, n, 100 + seed))
+        slots = [engine.open_slot() for _ in prompts]
+        # the last row of every prompt, and where a row of logits is to spare the first prompt's first row
+        wants = [[len(p) - 1] for p in prompts]
+        if len(prompts) < 4:
+            wants[0] = [0, len(prompts[0]) - 1]
+        out = engine.step([StepEntry(s, p, w) for s, p, w in zip(slots, prompts, wants)])
+        assert out.shape[0] == sum(len(w) for w in wants)
+        if len(prompts) < 4:
+            assert scaled_error(out[0], plain_logits(folders[name], prompts[0])[0]) < TOLERANCE[dtype], round_
+            out = out[1:]
+        for b, p in enumerate(prompts):
+            assert scaled_error(out[b], plain_logits(folders[name], p)[-1]) < TOLERANCE[dtype], (round_, b)
+        # the first sequence goes on with four more tokens, alone
+        more = random_tokens(vocab, 4, 500 + round_)
+        out2 = engine.step([StepEntry(slots[0], more, [3])])
+        expected = plain_logits(folders[name], prompts[0] + more)
+        assert scaled_error(out2[0], expected[-1]) < TOLERANCE[dtype], round_
+        # what the first step returned was a copy: the second step did not rewrite it
+        assert scaled_error(out[0], plain_logits(folders[name], prompts[0])[-1]) < TOLERANCE[dtype]
+        for s in slots:
+            engine.release_slot(s)
+    engine.cache.check()
+    captured = set(engine.prompt_graphs.captured)
+    assert captured == {(4, 32), (1, 16)}, captured  # the classes that came up more than twice
+
+
+def test_prompt_captures_leave_large_and_unwanted_steps_alone(cuda_device, folders):
+    """Steps beyond the largest class, steps that want no logits and steps that want more rows than
+    they have sequences run launch by launch."""
+    import models_b200
+    from models_b200.engine import StepEntry
+    from models_b200.engine.decode_graph import PROMPT_TOKENS
+
+    name = "B"
+    model = models_b200.load_model(folders[name], dtype="bfloat16", max_batch=2, context=1024)
+    engine = model.engine
+    graphs = engine.prompt_graphs
+    slot = engine.open_slot()
+    assert graphs.bucket([(slot, [1] * (PROMPT_TOKENS[-1] + 1), [0])]) is None
+    assert graphs.bucket([(slot, [1] * 8, [])]) is None
+    assert graphs.bucket([(slot, [1] * 8, [0, 1, 2])]) is None
+    assert graphs.bucket([(slot, [1] * 8, [7])]) == (1, 16)
+    assert graphs.bucket([(slot, [1] * 17, [0])]) == (1, 32)
+    engine.release_slot(slot)
+
+
 def test_graph_and_eager_decode_agree(cuda_device, folders):
     import models_b200
     from models_b200.engine import StepEntry

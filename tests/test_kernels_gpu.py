@@ -581,10 +581,11 @@ def test_tcgen05_qkv_product_with_rotation_and_cache_write(cuda_device, rows, he
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (70, 144, 136), (300, 272, 200), (1, 512, 2048), (513, 1040, 328),
-                                   (2100, 5136, 264)])
+                                   (2100, 5136, 264), (200, 528, 4136), (520, 272, 1288)])
 def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
     """The prefill matrix product (TMA, tcgen05.mma, accumulator in tensor memory) against float64,
-    at sizes that do not fill its 128 x 256 x 64 tiles; no bounded wait may have given up."""
+    at sizes that do not fill its 128 x 256 x 64 tiles; no bounded wait may have given up.  With few
+    tiles and a long K the residual epilogue splits K over blocks (the last part shorter than the rest)."""
     from models_b200.kernels import ops
 
     g = torch.Generator().manual_seed(m + n + k)
