@@ -288,6 +288,8 @@ def main() -> int:
     parser.add_argument("--model", default="1b", choices=sorted(WORKLOADS),
                         help="1b: the default run; 3b, 8b: the other two workloads of the baseline file")
     parser.add_argument("--batch", type=int, default=None, help="sequences decoded together (default: the workload's)")
+    parser.add_argument("--prompt", type=int, default=None,
+                        help="prompt tokens per sequence (default: the workload's); the context grows to hold them")
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both counts are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 decode points and the prefill")
@@ -309,6 +311,8 @@ def main() -> int:
     steps = args.steps or work["steps"]
     layers = args.layers or work["config"]["num_hidden_layers"]
     prompt, context, prefill_tokens = work["prompt"], work["context"], work["prefill"]
+    if args.prompt:
+        prompt, context = args.prompt, max(context, args.prompt + warmup + steps + 64)
     longest_prompt = prompt if isinstance(prompt, int) else prompt[1]
     if longest_prompt + warmup + steps + 1 > context:
         print(f"bench.py: {longest_prompt} prompt tokens + {warmup} + {steps} steps do not fit the context of {context}")

@@ -207,7 +207,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
+    float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};  // maxima of raw scores
+    const float scale_log2 = scale * 1.4426950408889634f;  // positive
     if (empty && kCluster) grid_dependency_wait();
     if (!empty) {
     const int* table = block_table + (size_t)seq * max_blocks;
@@ -254,30 +255,34 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
             float s[2][4];
             scores_16_keys(s, a, k_tile, key0);
             float tile_max = -CUDART_INF_F;
+            if (abs0 < first || abs0 + 15 > pos) {  // an end of the visible range runs through these 16 keys
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int key = abs0 + nt * 8 + tid4 * 2 + (i & 1);
-                    s[nt][i] = (key >= first && key <= pos) ? s[nt][i] * scale : -CUDART_INF_F;
-                }
+                    for (int i = 0; i < 4; ++i) {
+                        const int key = abs0 + nt * 8 + tid4 * 2 + (i & 1);
+                        if (key < first || key > pos) s[nt][i] = -CUDART_INF_F;
+                    }
+            }
             // one token: both rows of a lane see the same keys, so one maximum test serves the mask
             float row_max[2] = {fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1])),
                                 fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]))};
             uint32_t p[4];
             float probs[2][4];
+            // scores stay raw; the scale (times log2 e) is folded into the exponent: 2^(s*c - m*c)
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 tile_max = quad_max(row_max[r]);
                 const float new_max = fmaxf(run_max[r], tile_max);  // finite: a visible key exists
-                const float correction = expf(run_max[r] - new_max);
+                const float correction = fast_exp2((run_max[r] - new_max) * scale_log2);
+                const float offset = -new_max * scale_log2;
                 run_max[r] = new_max;
                 float local = 0.0f;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        const float e = expf(s[nt][2 * r + c] - new_max);
+                        const float e = fast_exp2(fmaf(s[nt][2 * r + c], scale_log2, offset));
                         probs[nt][2 * r + c] = e;
                         local += e;
                     }
@@ -315,7 +320,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
             dst[1] = o[i][2 * r + 1];
         }
         if (tid4 == 0) {
-            merge_ml[(warp * 16 + row) * 2] = run_max[r];
+            merge_ml[(warp * 16 + row) * 2] = run_max[r] * scale_log2;  // from here on maxima are exponents of two
             merge_ml[(warp * 16 + row) * 2 + 1] = run_sum[r];
         }
     }
@@ -329,7 +334,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
         if (m != -CUDART_INF_F) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float weight = expf(merge_ml[(w * 16 + row) * 2] - m);  // exp(-inf) = 0 for a warp that saw nothing
+                const float weight = fast_exp2(merge_ml[(w * 16 + row) * 2] - m);  // 2^-inf = 0 for a warp that saw nothing
                 total += merge_ml[(w * 16 + row) * 2 + 1] * weight;
                 value += merge_o[(size_t)(w * 16 + row) * HD + d] * weight;
             }
@@ -364,7 +369,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
                 float total = 0.0f, value = 0.0f;
                 for (int r = 0; r < splits; ++r) {
                     const float* ml = cluster.map_shared_rank(block_ml, r);
-                    const float weight = expf(ml[row * 2] - m);  // 0 for a block that saw nothing
+                    const float weight = fast_exp2(ml[row * 2] - m);  // 0 for a block that saw nothing
                     if (weight > 0.0f) {
                         total += ml[row * 2 + 1] * weight;
                         value += cluster.map_shared_rank(block_o, r)[row * HD + d] * weight;
@@ -388,13 +393,13 @@ __global__ void combine_splits_kernel(const float* __restrict__ partial_o, const
     float m = -CUDART_INF_F;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, partial_ml[(base + s) * 2]);
     float total = 0.0f;
-    for (int s = 0; s < splits; ++s) total += partial_ml[(base + s) * 2 + 1] * expf(partial_ml[(base + s) * 2] - m);
+    for (int s = 0; s < splits; ++s) total += partial_ml[(base + s) * 2 + 1] * fast_exp2(partial_ml[(base + s) * 2] - m);
     const float inv = 1.0f / total;
     const int row = cu_q[seq];
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float value = 0.0f;
         for (int s = 0; s < splits; ++s) {
-            const float weight = expf(partial_ml[(base + s) * 2] - m);
+            const float weight = fast_exp2(partial_ml[(base + s) * 2] - m);
             if (weight > 0.0f) value += partial_o[(base + s) * HD + d] * weight;  // an empty split wrote no output
         }
         out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(value * inv);
