@@ -85,7 +85,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void load_tile(uint32_t dst, const bf16* __restrict__ pool, size_t page, int kv_head,
                                           int kv_heads) {
     const bf16* src = pool + (page * kv_heads + kv_head) * (size_t)(kTile * HD);
-    for (int i = threadIdx.x; i < kTile * kChunks; i += kThreads) {
+    static_assert((kTile * kChunks) % kThreads == 0, "every thread copies the same number of pieces");
+#pragma unroll
+    for (int j = 0; j < kTile * kChunks / kThreads; ++j) {  // (unrolled: the offsets are the same for every page)
+        const int i = threadIdx.x + j * kThreads;
+        const int row = i / kChunks, chunk = i % kChunks;
+        cp_async16(dst + row * kRowBytes + chunk * 16, src + row * HD + chunk * 8);
+    }
+}
+
+// The 16 rows of a page that one decode warp works on (rows 16 * warp ...), copied by that warp alone: what a warp
+// reads it has fetched itself, so the warps of a block need no barrier between pages.
+__device__ __forceinline__ void load_tile_rows(uint32_t dst, const bf16* __restrict__ pool, size_t page, int kv_head,
+                                               int kv_heads, int warp, int lane) {
+    const bf16* src = pool + (page * kv_heads + kv_head) * (size_t)(kTile * HD) + (size_t)warp * 16 * HD;
+    dst += warp * 16 * kRowBytes;
+#pragma unroll
+    for (int j = 0; j < 16 * kChunks / 32; ++j) {
+        const int i = lane + j * 32;
         const int row = i / kChunks, chunk = i % kChunks;
         cp_async16(dst + row * kRowBytes + chunk * 16, src + row * HD + chunk * 8);
     }
@@ -215,8 +232,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     const uint32_t stage_base = smem_u32(stage_smem);
     const bool early = kCluster && t_begin != pos / kTile;  // the first page holds no position of this step
     if (kCluster && !early) grid_dependency_wait();
-    load_tile(stage_base, k_pool, table[t_begin], kv_head, kv_heads);
-    load_tile(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads);
+    load_tile_rows(stage_base, k_pool, table[t_begin], kv_head, kv_heads, warp, lane);
+    load_tile_rows(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads, warp, lane);
     cp_async_commit();
     if (early) grid_dependency_wait();
     // kDecodeStages - 1 pages are in flight while one is worked on; every stage is one commit group, empty
@@ -225,8 +242,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     for (int ahead = 1; ahead < kDecodeStages - 1; ++ahead) {
         if (t_begin + ahead < t_end) {
             const uint32_t dst = stage_base + ahead * 2 * kTileBytes;
-            load_tile(dst, k_pool, table[t_begin + ahead], kv_head, kv_heads);
-            load_tile(dst + kTileBytes, v_pool, table[t_begin + ahead], kv_head, kv_heads);
+            load_tile_rows(dst, k_pool, table[t_begin + ahead], kv_head, kv_heads, warp, lane);
+            load_tile_rows(dst + kTileBytes, v_pool, table[t_begin + ahead], kv_head, kv_heads, warp, lane);
         }
         cp_async_commit();
     }
@@ -235,19 +252,23 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     uint32_t a[kKSteps][4];
     load_q_fragments(a, smem_u32(q_smem));
 
+    // the page table is read one page ahead of the fetch that needs it, so that no fetch waits for its entry
+    int page_ahead = t_begin + kDecodeStages - 1 < t_end ? table[t_begin + kDecodeStages - 1] : 0;
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) % kDecodeStages;
         {
             const int fetch = t + kDecodeStages - 1;  // its stage was freed by the barrier that ended page t - 1
+            const int page = page_ahead;
+            if (fetch + 1 < t_end) page_ahead = table[fetch + 1];
             if (fetch < t_end) {
                 const uint32_t next = stage_base + ((fetch - t_begin) % kDecodeStages) * 2 * kTileBytes;
-                load_tile(next, k_pool, table[fetch], kv_head, kv_heads);
-                load_tile(next + kTileBytes, v_pool, table[fetch], kv_head, kv_heads);
+                load_tile_rows(next, k_pool, page, kv_head, kv_heads, warp, lane);
+                load_tile_rows(next + kTileBytes, v_pool, page, kv_head, kv_heads, warp, lane);
             }
             cp_async_commit();
             cp_async_wait<kDecodeStages - 1>();  // everything but the newest kDecodeStages - 1 groups: page t is in
         }
-        __syncthreads();
+        __syncwarp();  // the warp's own rows: every lane's pieces have landed
         const uint32_t k_tile = stage_base + stage * 2 * kTileBytes, v_tile = k_tile + kTileBytes;
         const int key0 = warp * 16;
         const int abs0 = t * kTile + key0;
@@ -299,13 +320,14 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
             p[3] = pack_bf16(probs[1][2], probs[1][3]);
             accumulate_16_keys(o, p, v_tile, key0);
         }
-        __syncthreads();  // the stage is free for the load after next
+        __syncwarp();  // the warp's rows of the stage are free for the load after next
     }
     }  // !empty
     run_sum[0] = quad_sum(run_sum[0]);
     run_sum[1] = quad_sum(run_sum[1]);
 
-    // merge the four warps' partial results through shared memory (the stages are free now)
+    // merge the four warps' partial results through shared memory: the stages are free once every warp has left its loop
+    __syncthreads();
     float* merge_o = reinterpret_cast<float*>(stage_smem);         // [4 warps][16 rows][HD]
     float* merge_ml = merge_o + 4 * 16 * HD;                        // [4 warps][16 rows][2]
     float* block_o = merge_ml + 4 * 16 * 2;                         // [16 rows][HD]   (cluster: this block's result)
