@@ -148,7 +148,8 @@ argmax_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
 // The candidates (probability, id) in shared memory, unused entries (-1, max int): sorted by probability
 // descending and id ascending (bitonic over the smallest power of two that holds k), cut at the shortest prefix whose mass
 // reaches `nucleus` (crossing token included), then the inverse-CDF draw r = u * kept mass.
-__device__ void sort_and_pick(float* sorted_p, int* sorted_id, int k, float nucleus, float u, int* out) {
+// `grown`: where the picked id is stored a second time (the end of the row's history), or null.
+__device__ void sort_and_pick(float* sorted_p, int* sorted_id, int k, float nucleus, float u, int* out, int* grown) {
     const int tid = threadIdx.x;
     int span = 32;  // the candidates lie in the first k entries: a power of two that holds them is all that is sorted
     while (span < k) span <<= 1;
@@ -189,6 +190,7 @@ __device__ void sort_and_pick(float* sorted_p, int* sorted_id, int k, float nucl
             }
         }
         *out = pick;
+        if (grown) *grown = pick;
     }
 }
 
@@ -196,7 +198,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, float* __restrict__ work,
                    int* __restrict__ counts, const float* __restrict__ temperature, const int* __restrict__ top_k,
                    const float* __restrict__ top_p, const float* __restrict__ penalty,
-                   const int* __restrict__ history, int history_stride, const int* __restrict__ history_len,
+                   const int* __restrict__ history, int history_stride, const long long* __restrict__ history_rows, int append,
+                   const int* __restrict__ history_len,
                    const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
                    const float* __restrict__ uniforms, int* __restrict__ out) {
     __shared__ Best best_scratch[32];
@@ -212,13 +215,16 @@ sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
     float* w = work + (size_t)r * vocab;
     const float temp = temperature[r];
     const float pen = penalty[r];
-    const bool penalised = pen > 1.0f && history && history_len[r] > 0;
+    // the row's earlier tokens: a row of the `history` matrix, or the array whose address history_rows[r] holds (0: none)
+    int* h_row = history_rows ? reinterpret_cast<int*>(history_rows[r])
+                              : (history ? const_cast<int*>(history) + (size_t)r * history_stride : nullptr);
+    const bool penalised = pen > 1.0f && h_row && history_len[r] > 0;
 
     if (penalised) {
         int* cnt = counts + (size_t)r * vocab;
         for (int i = tid; i < vocab; i += kThreads) cnt[i] = 0;
         __syncthreads();
-        const int* h = history + (size_t)r * history_stride;
+        const int* h = h_row;
         for (int j = tid; j < history_len[r]; j += kThreads) {
             const int token = h[j];
             if (token >= 0 && token < vocab) atomicAdd(&cnt[token], 1);
@@ -240,7 +246,11 @@ sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
     }
     const Best top = block_best(mine, best_scratch);
     if (temp <= 0.0f) {
-        if (tid == 0) out[r] = top.index == 0x7fffffff ? 0 : top.index;
+        if (tid == 0) {
+            const int token = top.index == 0x7fffffff ? 0 : top.index;
+            out[r] = token;
+            if (append && h_row) h_row[history_len[r]] = token;  // the row's history grows on the device
+        }
         return;
     }
 
@@ -334,7 +344,7 @@ sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
             }
             __syncthreads();
         }
-        sort_and_pick(sorted_p, sorted_id, k, nucleus, u, out + r);
+        sort_and_pick(sorted_p, sorted_id, k, nucleus, u, out + r, (append && h_row) ? h_row + history_len[r] : nullptr);
         return;
     }
 
@@ -387,7 +397,11 @@ sample_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
         if (running >= target) break;
     }
     __syncthreads();
-    if (tid == 0) out[r] = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
+    if (tid == 0) {
+        const int token = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
+        out[r] = token;
+        if (append && h_row) h_row[history_len[r]] = token;
+    }
 }
 
 
@@ -402,7 +416,8 @@ __global__ void __launch_bounds__(kThreads)
 sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int vocab, float* __restrict__ work,
                            int* __restrict__ counts, const float* __restrict__ temperature, const int* __restrict__ top_k,
                            const float* __restrict__ top_p, const float* __restrict__ penalty,
-                           const int* __restrict__ history, int history_stride, const int* __restrict__ history_len,
+                           const int* __restrict__ history, int history_stride, const long long* __restrict__ history_rows, int append,
+                   const int* __restrict__ history_len,
                            const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ counters,
                            const float* __restrict__ uniforms, int* __restrict__ out) {
     __shared__ Best best_scratch[32];
@@ -428,7 +443,10 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
     float* w = work + (size_t)r * vocab;
     const float temp = temperature[r];
     const float pen = penalty[r];
-    const bool penalised = pen > 1.0f && history && history_len[r] > 0;
+    // the row's earlier tokens: a row of the `history` matrix, or the array whose address history_rows[r] holds (0: none)
+    int* h_row = history_rows ? reinterpret_cast<int*>(history_rows[r])
+                              : (history ? const_cast<int*>(history) + (size_t)r * history_stride : nullptr);
+    const bool penalised = pen > 1.0f && h_row && history_len[r] > 0;
 
     if (part == 0) {
         if (tid == 0) gathered = 0;
@@ -442,7 +460,7 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
         for (int i = begin + tid; i < end; i += kThreads) cnt[i] = 0;
         __threadfence();
         cluster.sync();
-        const int* h = history + (size_t)r * history_stride;
+        const int* h = h_row;
         for (int j = part * kThreads + tid; j < history_len[r]; j += kSampleBlocks * kThreads) {
             const int token = h[j];
             if (token >= 0 && token < vocab) atomicAdd(&cnt[token], 1);
@@ -471,7 +489,11 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
     Best top = *cluster.map_shared_rank(&slot_best, 0);
     for (int b = 1; b < kSampleBlocks; ++b) top = better(top, *cluster.map_shared_rank(&slot_best, b));
     if (temp <= 0.0f) {
-        if (part == 0 && tid == 0) out[r] = top.index == 0x7fffffff ? 0 : top.index;
+        if (part == 0 && tid == 0) {
+            const int token = top.index == 0x7fffffff ? 0 : top.index;
+            out[r] = token;
+            if (append && h_row) h_row[history_len[r]] = token;
+        }
         cluster.sync();  // nobody leaves while its shared memory may still be read
         return;
     }
@@ -543,7 +565,11 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
             if (running >= target) break;
         }
         __syncthreads();
-        if (tid == 0) out[r] = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
+        if (tid == 0) {
+            const int token = shared_int[1] != 0x7fffffff ? shared_int[1] : (shared_int[2] >= 0 ? shared_int[2] : 0);
+            out[r] = token;
+            if (append && h_row) h_row[history_len[r]] = token;
+        }
         return;
     }
     if (k > kMaxSorted) k = kMaxSorted;  // the host sends only rows that fit; never write past the arrays
@@ -641,7 +667,7 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
     }
     cluster.sync();  // the first block's arrays are complete; the others are done
     if (part != 0) return;
-    sort_and_pick(sorted_p, sorted_id, k, nucleus, u, out + r);
+    sort_and_pick(sorted_p, sorted_id, k, nucleus, u, out + r, (append && h_row) ? h_row + history_len[r] : nullptr);
 }
 
 }  // namespace mb
@@ -678,7 +704,7 @@ MB_EXPORT int mb_argmax_rows(const float* logits, int row_stride, int rows, int 
 // kernel that spreads a row over a cluster of blocks.
 MB_EXPORT int mb_sample_rows(const float* logits, int row_stride, int rows, int vocab, float* work, int* counts,
                              const float* temperature, const int* top_k, const float* top_p, const float* penalty,
-                             const int* history, int history_stride, const int* history_len,
+                             const int* history, int history_stride, const long long* history_rows, int append, const int* history_len,
                              const unsigned long long* seeds, const unsigned long long* counters,
                              const float* uniforms, int* out, int max_candidates, cudaStream_t stream) {
     if (rows <= 0) return 0;
@@ -699,13 +725,13 @@ MB_EXPORT int mb_sample_rows(const float* logits, int row_stride, int rows, int 
         config.attrs = attribute;
         config.numAttrs = 1;
         cudaError_t status = cudaLaunchKernelEx(&config, sample_rows_cluster_kernel, logits, row_stride, vocab, work, counts,
-                                                temperature, top_k, top_p, penalty, history, history_stride, history_len, seeds,
+                                                temperature, top_k, top_p, penalty, history, history_stride, history_rows, append, history_len, seeds,
                                                 counters, uniforms, out);
         if (status != cudaSuccess) return fail("sample_rows: launch failed: %s", cudaGetErrorString(status));
         return check_launch("sample_rows");
     }
     sample_rows_kernel<<<rows, kThreads, 0, stream>>>(logits, row_stride, vocab, work, counts, temperature, top_k, top_p,
-                                                      penalty, history, history_stride, history_len, seeds, counters,
+                                                      penalty, history, history_stride, history_rows, append, history_len, seeds, counters,
                                                       uniforms, out);
     return check_launch("sample_rows");
 }

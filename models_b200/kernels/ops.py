@@ -655,11 +655,15 @@ def sample_rows(logits: torch.Tensor, work: torch.Tensor, counts: Optional[torch
                 top_k: torch.Tensor, top_p: torch.Tensor, penalty: torch.Tensor, history: Optional[torch.Tensor],
                 history_len: Optional[torch.Tensor], seeds: Optional[torch.Tensor], counters: Optional[torch.Tensor],
                 uniforms: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                max_candidates: int = 0) -> torch.Tensor:
+                max_candidates: int = 0, history_rows: Optional[torch.Tensor] = None, append: bool = False) -> torch.Tensor:
     """One token per row of `logits` by the sampling pipeline.  `max_candidates`: the caller's bound on
     min(top_k, vocabulary) over the rows, 0 if it has none; when every row keeps at most
-    sample_max_sorted() candidates a row is spread over a cluster of blocks instead of one block."""
-    _cuda(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters, uniforms)
+    sample_max_sorted() candidates a row is spread over a cluster of blocks instead of one block.
+    The earlier tokens of the rows (for the repetition penalty) are the rows of `history`, or the int32
+    arrays whose device addresses `history_rows` (int64 per row, 0: none) holds; `history_len` counts
+    them either way.  With `append` the kernel stores each row's new id behind its history (the arrays
+    of `history_rows` need room for it)."""
+    _cuda(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters, uniforms, history_rows)
     if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
         raise KernelError("sample_rows takes float32 [rows, vocab] logits")
     rows, vocab = logits.shape
@@ -673,13 +677,18 @@ def sample_rows(logits: torch.Tensor, work: torch.Tensor, counts: Optional[torch
             raise KernelError(f"{name} must hold {rows} values of {dt}")
     _int32(history, "history")
     _int32(history_len, "history_len")
-    if history is not None and counts is None:
-        raise KernelError("a token history needs the counters scratch")
+    if (history is not None or history_rows is not None) and (counts is None or history_len is None):
+        raise KernelError("a token history needs its lengths and the counters scratch")
+    if history_rows is not None and (history is not None or history_rows.dtype != torch.int64 or history_rows.numel() < rows):
+        raise KernelError(f"history_rows must hold {rows} int64 addresses and comes instead of a history matrix")
+    if append and history_rows is None:
+        raise KernelError("appending needs history_rows: a row of a history matrix has no room of its own")
     if out is None:
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     lib = sampling()
     _run(lib, lib.mb_sample_rows(_p(logits), logits.stride(0), rows, vocab, _p(work), _p(counts), _p(temperature),
                                  _p(top_k), _p(top_p), _p(penalty), _p(history),
-                                 history.stride(0) if history is not None else 0, _p(history_len), _p(seeds),
+                                 history.stride(0) if history is not None else 0, _p(history_rows), 1 if append else 0,
+                                 _p(history_len), _p(seeds),
                                  _p(counters), _p(uniforms), _p(out), int(max_candidates), _stream()))
     return out

@@ -25,6 +25,10 @@ class RequestSampling:
         self.draws = 0
         # the reference penalises every earlier token, prompt included (GenerationLoop.java:165-169)
         self.history: Optional[List[int]] = list(prompt) if options.repetition_penalty > 1.0 else None
+        # the same tokens on the device (int32, room for every token the request may still get): the
+        # sampling kernel reads them there and stores each new id behind them, so a step sends no history
+        self.history_device: Optional[torch.Tensor] = None
+        self.history_sent = 0  # tokens of the history that the device array holds
 
 
 class BatchSampler:
@@ -57,56 +61,70 @@ class BatchSampler:
         if all(r.options.greedy for r in requests):
             return greedy(logits)[:rows] if greedy is not None else ops.argmax_rows(logits[:rows])
         logits = logits[:rows]
-        temperature, top_k, top_p, penalty, seeds, counters = self._parameters(requests)
-        history = history_len = counts = None
-        if any(r.history is not None for r in requests):
-            longest = max(len(r.history) if r.history is not None else 0 for r in requests)
-            host = torch.zeros((rows, max(1, longest)), dtype=torch.int32)
-            lens = torch.zeros((rows,), dtype=torch.int32)
-            for i, r in enumerate(requests):
+        penalised = any(r.history is not None for r in requests)
+        if penalised:
+            for r in requests:
                 if r.history is not None:
-                    host[i, :len(r.history)] = torch.tensor(r.history, dtype=torch.int32)
-                    lens[i] = len(r.history)
-            history, history_len = host.to(self.device), lens.to(self.device)
-            counts = torch.empty((rows, self.vocab), dtype=torch.int32, device=self.device)
+                    self._history_on_device(r)
+        temperature, top_k, top_p, penalty, seeds, counters, history_rows, history_len = self._parameters(requests)
+        counts = torch.empty((rows, self.vocab), dtype=torch.int32, device=self.device) if penalised else None
+        if not penalised:
+            history_rows = history_len = None
         work = torch.empty((rows, self.vocab), dtype=torch.float32, device=self.device)
         # the largest candidate set among the rows that cut anything (1 if none does): it picks the kernel
         most = max([min(r.options.top_k, self.vocab) for r in requests
                     if r.options.top_k < self.vocab or r.options.top_p < 1.0] or [1])
-        out = ops.sample_rows(logits, work, counts, temperature, top_k, top_p, penalty, history, history_len, seeds, counters,
-                              max_candidates=most)
+        out = ops.sample_rows(logits, work, counts, temperature, top_k, top_p, penalty, None, history_len, seeds, counters,
+                              max_candidates=most, history_rows=history_rows, append=history_rows is not None)
         for r in requests:
             if r.options.temperature > 0.0:
                 r.draws += 1
+            if r.history_device is not None:
+                r.history_sent += 1  # the kernel has stored this step's id behind the others
         return out
+
+    def _history_on_device(self, r: RequestSampling) -> None:
+        """The request's earlier tokens as a device array that the kernel extends by itself.  Sent once
+        (the prompt); sent again only if the host's list and the device's count ever disagree, which
+        happens when ids were recorded that this sampler did not draw."""
+        room = len(r.history) + max(1, int(r.options.max_tokens)) + 4  # a finished request may be sampled once more
+        if r.history_device is None or r.history_sent != len(r.history) or r.history_device.numel() < len(r.history) + 1:
+            host = torch.zeros((room,), dtype=torch.int32)
+            host[: len(r.history)] = torch.tensor(r.history, dtype=torch.int32)
+            r.history_device = host.to(self.device)
+            r.history_sent = len(r.history)
 
     def _parameters(self, requests: Sequence[RequestSampling]):
         """The per-row options on the device, sent as one asynchronous copy from pinned memory (a
         copy from ordinary memory would wait for every step that is still queued)."""
         rows = len(requests)
-        if self._staging is None or self._staging[0][0].numel() < 32 * rows:
-            size = 32 * max(64, rows)
+        if self._staging is None or self._staging[0][0].numel() < 48 * rows:
+            size = 48 * max(64, rows)
             self._staging = [(torch.empty((size,), dtype=torch.uint8).pin_memory(), torch.cuda.Event()) for _ in range(4)]
         host, event = self._staging[self._staging_next]
         self._staging_next = (self._staging_next + 1) % len(self._staging)
         event.synchronize()  # the copy that last read this buffer, four calls ago
-        device = torch.empty((32 * rows,), dtype=torch.uint8, device=self.device)
+        device = torch.empty((48 * rows,), dtype=torch.uint8, device=self.device)
 
         def views(buffer):
             floats = buffer[: 12 * rows].view(torch.float32).view(3, rows)
             ints = buffer[12 * rows: 16 * rows].view(torch.int32)
-            longs = buffer[16 * rows: 32 * rows].view(torch.int64).view(2, rows)
-            return floats, ints, longs
+            longs = buffer[16 * rows: 40 * rows].view(torch.int64).view(3, rows)
+            lens = buffer[40 * rows: 44 * rows].view(torch.int32)
+            return floats, ints, longs, lens
 
-        floats, ints, longs = views(host)
+        floats, ints, longs, lens = views(host)
         floats.copy_(torch.tensor([[r.options.temperature for r in requests], [r.options.top_p for r in requests],
                                    [r.options.repetition_penalty for r in requests]], dtype=torch.float32))
         ints.copy_(torch.tensor([min(r.options.top_k, self.vocab) for r in requests], dtype=torch.int32))
-        longs.copy_(torch.tensor([[r.seed for r in requests], [r.draws for r in requests]], dtype=torch.int64))
-        device.copy_(host[: 32 * rows], non_blocking=True)
+        longs.copy_(torch.tensor([[r.seed for r in requests], [r.draws for r in requests],
+                                  [r.history_device.data_ptr() if r.history_device is not None else 0 for r in requests]],
+                                 dtype=torch.int64))
+        lens.copy_(torch.tensor([r.history_sent if r.history_device is not None else 0 for r in requests], dtype=torch.int32))
+        device.copy_(host[: 48 * rows], non_blocking=True)
         event.record()
-        floats, ints, longs = views(device)
-        return floats[0], ints, floats[1], floats[2], longs[0], longs[1]
+        floats, ints, longs, lens = views(device)
+        return floats[0], ints, floats[1], floats[2], longs[0], longs[1], longs[2], lens
 
     @staticmethod
     def record(requests: Sequence[RequestSampling], tokens: Sequence[int]) -> None:

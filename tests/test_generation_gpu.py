@@ -255,6 +255,7 @@ def test_sampling_kernel_follows_the_reference_pipeline(cuda_device, vocab):
     ]
     prompt = [int(t) for t in torch.randint(0, vocab, (25,), generator=g)] + [3, 3, 3]
     requests = [RequestSampling(o, prompt) for o in cases]
+    first_arrays = {}
     for step in range(6):
         logits = torch.randn(len(cases), vocab, generator=g) * 3
         logits[:, 3] = 6.0  # a likely token that the history penalises three times
@@ -276,6 +277,13 @@ def test_sampling_kernel_follows_the_reference_pipeline(cuda_device, vocab):
             else:
                 assert got[row] == want, (step, row, got[row], want)
         BatchSampler.record(requests, got)
+        # the history lives on the device: sent once, then grown there by the kernel itself
+        for r in requests:
+            if r.history is not None:
+                if step == 0:
+                    first_arrays[id(r)] = r.history_device
+                assert r.history_device is first_arrays[id(r)]
+                assert r.history_device[: len(r.history)].tolist() == r.history
     with pytest.raises(ValueError, match="top_p"):
         BatchSampler(5003, "cuda:0").check(SamplingOptions(top_k=2000, top_p=0.9))
 
