@@ -440,7 +440,9 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
     const int slice = (vocab + kSampleBlocks - 1) / kSampleBlocks;
     const int begin = min(vocab, part * slice), end = min(vocab, begin + slice);
     const float* row = logits + (size_t)r * row_stride;
-    float* w = work + (size_t)r * vocab;
+    // the block's part of the row lives in shared memory from the first pass to the last: w[i] for begin <= i < end
+    extern __shared__ float slice_values[];
+    float* w = slice_values - begin;
     const float temp = temperature[r];
     const float pen = penalty[r];
     // the row's earlier tokens: a row of the `history` matrix, or the array whose address history_rows[r] holds (0: none)
@@ -554,15 +556,23 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
         for (int i = begin + tid; i < end; i += kThreads)
             if (w[i] > 0.0f) last_kept = i;
         if (last_kept >= 0) atomicMax(&shared_int[2], last_kept);
-        float running = before;
-        for (int base = begin; base < end; base += kThreads) {
-            const int i = base + tid;
-            const float v = i < end ? w[i] : 0.0f;
-            float chunk_total;
-            const float inclusive = running + block_float_scan(v, float_scratch, &chunk_total);
-            if (v > 0.0f && inclusive >= target) atomicMin(&shared_int[1], i);
-            running += chunk_total;  // the same value in every thread
-            if (running >= target) break;
+        // every thread takes a run of neighbouring ids; one scan over the runs' masses finds the run that holds
+        // the target, and its thread walks it
+        const int per_thread = (end - begin + kThreads - 1) / kThreads;
+        const int first = min(end, begin + tid * per_thread), last = min(end, first + per_thread);
+        float run_mass = 0.0f;
+        for (int i = first; i < last; ++i) run_mass += w[i];
+        float all_runs;
+        const float inclusive = before + block_float_scan(run_mass, float_scratch, &all_runs);
+        if (inclusive >= target) {  // this run or an earlier one holds the target: the lowest id that reaches it wins
+            float running = inclusive - run_mass;
+            for (int i = first; i < last; ++i) {
+                running += w[i];
+                if (w[i] > 0.0f && running >= target) {
+                    atomicMin(&shared_int[1], i);
+                    break;
+                }
+            }
         }
         __syncthreads();
         if (tid == 0) {
@@ -599,18 +609,37 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
                 histogram_all[tid] = total;
             }
             __syncthreads();
-            if (tid == 0) {
-                int cumulative = 0, digit = 0;
-                for (int b = 255; b >= 0; --b) {
-                    if (cumulative + histogram_all[b] >= remaining) {
-                        digit = b;
-                        break;
-                    }
-                    cumulative += histogram_all[b];
+            if (tid < 32) {
+                // the digit at which the count from the top reaches `remaining`: lane l takes bins 255 - 8l down to
+                // 248 - 8l, a scan over the lanes finds the lane, the lane finds the bin
+                int bins[8], mine_total = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    bins[j] = histogram_all[255 - 8 * tid - j];
+                    mine_total += bins[j];
                 }
-                shared_int[0] = digit;
-                shared_int[1] = remaining - cumulative;
-                shared_int[2] = histogram_all[digit];
+                int inclusive = mine_total;
+#pragma unroll
+                for (int offset = 1; offset < 32; offset <<= 1) {
+                    const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+                    if (tid >= offset) inclusive += other;
+                }
+                const unsigned reached = __ballot_sync(0xffffffffu, inclusive >= remaining);
+                const int lane_of_digit = reached ? __ffs(reached) - 1 : 31;
+                if (tid == lane_of_digit) {
+                    int cumulative = inclusive - mine_total, digit = 255 - 8 * tid - 7;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (cumulative + bins[j] >= remaining || j == 7) {
+                            digit = 255 - 8 * tid - j;
+                            break;
+                        }
+                        cumulative += bins[j];
+                    }
+                    shared_int[0] = digit;
+                    shared_int[1] = remaining - cumulative;
+                    shared_int[2] = histogram_all[digit];
+                }
             }
             cluster.sync();  // every block has read every histogram before the next pass clears them
             prefix |= (uint32_t)shared_int[0] << shift;
@@ -711,11 +740,21 @@ MB_EXPORT int mb_sample_rows(const float* logits, int row_stride, int rows, int 
     if (vocab <= 0 || row_stride < vocab) return fail("sample_rows: vocab %d, row stride %d", vocab, row_stride);
     if (!work) return fail("sample_rows: needs rows * vocab floats of scratch");
     if (!uniforms && (!seeds || !counters)) return fail("sample_rows: needs seeds and counters, or uniforms");
-    if (max_candidates > 0 && max_candidates <= kMaxSorted) {
+    // a block of the cluster kernel keeps its eighth of a row in shared memory; a vocabulary too large for that (more
+    // than 400,000 ids) takes the kernel that works in the scratch array
+    const size_t slice_bytes = (size_t)((vocab + kSampleBlocks - 1) / kSampleBlocks) * sizeof(float);
+    if (max_candidates > 0 && max_candidates <= kMaxSorted && slice_bytes <= 200 * 1024) {
+        static size_t reserved = 0;
+        if (slice_bytes > reserved) {
+            cudaError_t status = cudaFuncSetAttribute(sample_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slice_bytes);
+            if (status != cudaSuccess) return fail("sample_rows: cannot reserve %zu bytes of shared memory: %s", slice_bytes, cudaGetErrorString(status));
+            reserved = slice_bytes;
+        }
         if (rows > 65535) return fail("sample_rows: %d rows exceed the grid limit 65535", rows);
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(kSampleBlocks, rows);
         config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = slice_bytes;
         config.stream = stream;
         cudaLaunchAttribute attribute[1];
         attribute[0].id = cudaLaunchAttributeClusterDimension;
