@@ -61,17 +61,27 @@ class GatedFeedForward(Part):
         ops.skinny_gemm(self.w_down, ops.EPI_RESIDUAL, x=hidden, out=x)
 
     def adds(self, xn: torch.Tensor) -> bool:
-        """Whether `forward_into` applies (any number of rows): bfloat16 weights the tensor-core kernels
-        take, no biases."""
+        """Whether `forward_into` applies (any number of rows): bfloat16, no biases, and a down matrix that
+        the tcgen05 product takes."""
         return (self.b_gate_up is None and self.b_down is None and xn.dtype == torch.bfloat16
-                and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, xn.shape[0])
-                and ops.gemm_tcgen05_takes(self.w_down, rows=xn.shape[0]))
+                and ops.gemm_tcgen05_takes(self.w_down))
 
     def forward_into(self, x: torch.Tensor, xn: torch.Tensor) -> None:
-        """x += down(silu(gate(xn)) * up(xn)): the activation rides in the gate/up product, the residual
-        add in the down product; neither the gate/up matrix nor the down result passes through memory."""
-        hidden = ops.tensor_core_gemm(xn, self.w_gate_up, ops.EPI_SWIGLU)
-        ops.tensor_core_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+        """x += down(silu(gate(xn)) * up(xn)) with the residual add inside the down product, which splits
+        K over blocks where it has few tiles: at 9 to 128 rows it takes 8.8 us for the 1B sizes where a
+        library product takes 12.5 and leaves the add to another kernel (decode steps of 16 to 64 sequences
+        gain 5 to 6 % at the 1B sizes, 0 to 3 % at 8B sizes; 64 sequences at 3B sizes lose 4 %).  Where the gate/up product has
+        tiles enough (more than 128 rows) the activation rides in it as well, and neither the gate/up
+        matrix nor the down result passes through memory; with fewer rows a library product and the
+        activation kernel are quicker."""
+        rows = xn.shape[0]
+        if ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows) and rows > ops.WIDE_ROWS:
+            hidden = ops.gemm_tcgen05(xn, self.w_gate_up, ops.EPI_SWIGLU)
+        elif ops.skinny_pays(self.w_gate_up, rows):
+            hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, x=xn)
+        else:
+            hidden = ops.swiglu(linear(xn, self.w_gate_up, self.runtime.compute_dtype))
+        ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
