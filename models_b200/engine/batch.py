@@ -83,6 +83,11 @@ def pack_step(cache, entries, layout: StepLayout, buf: np.ndarray, state_pad_row
     that are left over then belong to no sequence (token 0, position 0, nothing stored, no logits)."""
     B, T, width, n_groups = layout.sequences, layout.tokens, layout.blocks, layout.groups
     offsets = layout.offsets
+    need = sum(len(tokens) for _, tokens, _ in entries) + (0 if empty_padding else max(0, B - len(entries)))
+    wanted_rows = sum(len(want) for _, _, want in entries)
+    if len(entries) > B or need > T or wanted_rows > layout.wanted:
+        raise ValueError(f"the step's {len(entries)} sequences, {need} tokens and {wanted_rows} wanted rows do not fit the "
+                         f"layout's {B}, {T} and {layout.wanted}")
     buf[:] = 0
     tokens_a, positions_a, cu_q_a, kv_lens_a, slots_a, want_a = (buf[offsets[i]:offsets[i + 1]] for i in range(6))
     tables = [buf[offsets[6 + 2 * g]:offsets[7 + 2 * g]].reshape(B, width) for g in range(n_groups)]
@@ -121,8 +126,6 @@ def pack_step(cache, entries, layout: StepLayout, buf: np.ndarray, state_pad_row
                 mappings[g][row] = -1
             row += 1
     cu_q_a[B] = row
-    if row > T:
-        raise ValueError(f"the step's {row} tokens do not fit the layout's {T} rows")
     for g in range(n_groups):  # rows of no sequence
         mappings[g][row:] = -1
     return q_lens, max_kv
