@@ -210,6 +210,13 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False, prompt=PROMP
         logits = stepper.decode_pending(slots, pending, rows)
         pending.result()
         pending = stepper.sample_start(logits, greedy)
+    graphs = engine.decode_graphs
+    if graphs is not None and batch <= graphs.max_batch:
+        # part of the warm-up: the captures of every class of context length that the timed steps will meet (a
+        # sequence that crosses such a boundary would otherwise pay for a capture inside the timed region)
+        longest = max(engine.length(s) for s in slots)
+        for kv in range(longest + 1, longest + steps + 2):
+            graphs.prepare(graphs.rung(batch), kv)
     sampler = ClockSampler() if sample_clocks else None
     if sampler:
         sampler.start()

@@ -156,7 +156,7 @@ class DecodeGraphs:
         self.max_batch = max_batch
         self.blocks = blocks
         self.sizes = ladder(max_batch)
-        self.captured: Dict[tuple, _Captured] = {}  # (batch size, class of context lengths)
+        self.captured: Dict[tuple, _Captured] = {}  # (batch size, launch class)
         self.last_argmax = None  # first maximum of every row of the last step's logits (device, int32)
         self.pool = torch.cuda.graph_pool_handle()
 
@@ -166,6 +166,24 @@ class DecodeGraphs:
                 return size
         raise ValueError(f"a decode batch of {n} exceeds the largest captured size {self.max_batch}")
 
+    def launch_class(self, size: int, max_kv_len: int) -> tuple:
+        """What the launches of a decode step of `size` sequences depend on besides the batch size: every
+        mixer's answer for the class of context lengths (long contexts split their keys over more
+        blocks, and the split is part of the captured launches).  Most steps share one class."""
+        span = ops.decode_span(max_kv_len)
+        mixers = [block.mixer for block in self.engine.model.blocks]
+        return tuple(m.decode_class(size, span) if hasattr(m, "decode_class") else 0 for m in mixers)
+
+    def prepare(self, size: int, max_kv_len: int) -> _Captured:
+        """The capture for `size` sequences (a rung) of up to `max_kv_len` positions, made if it is not
+        there yet: a capture costs tens of steps, so a caller that knows what is coming can have it made
+        before it counts."""
+        key = (size, self.launch_class(size, max_kv_len))
+        captured = self.captured.get(key)
+        if captured is None:
+            captured = self.captured[key] = _Captured(self.engine, size, self.blocks, self.pool, ops.decode_span(max_kv_len))
+        return captured
+
     def step(self, entries: Sequence, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """entries: (slot, [token], [0]) each; the cache already has room.  Returns logits
         [len(entries), vocab]; they live in the graph's output buffer until the next replay.
@@ -173,11 +191,7 @@ class DecodeGraphs:
         step then needs nothing from the host that depends on the step before it."""
         engine = self.engine
         size = self.rung(len(entries))
-        # long contexts split their keys over more blocks, and the split is part of the captured launches
-        span = ops.decode_span(1 + max((engine.cache.lengths[e[0]] for e in entries), default=0))
-        captured = self.captured.get((size, span))
-        if captured is None:
-            captured = self.captured[(size, span)] = _Captured(engine, size, self.blocks, self.pool, span)
+        captured = self.prepare(size, 1 + max((engine.cache.lengths[e[0]] for e in entries), default=0))
         if device_tokens is None:
             captured.update(engine.cache, [e[0] for e in entries], [e[1][0] for e in entries])
             captured.upload()

@@ -145,6 +145,14 @@ class AttentionMixer(Mixer):
         self.attend(qkv, attended, batch, group, run)
         return attended
 
+    def decode_class(self, sequences: int, max_kv_len: int):
+        """What of a decode step's launches depends on the context length: how many blocks share a
+        sequence's keys.  Steps of one class can replay one capture."""
+        s = self.spec
+        if self.runtime.compute_dtype != torch.bfloat16 or s.head_dim % 16 or s.head_dim > 256:
+            return 0  # the plain-arithmetic kernel: one launch shape for every length
+        return ops.decode_splits(sequences, s.num_heads, s.num_kv_heads, s.head_dim, max_kv_len, s.window)
+
     def attend(self, qkv, attended, batch, group, run):
         """Tensor-core kernels where they apply (bfloat16, head size a multiple of 16, pages of 64);
         otherwise the plain-arithmetic kernel, which takes every size and is the 32-bit path's."""

@@ -103,7 +103,7 @@ def test_long_decoding_with_graphs_matches_plain(cuda_device, folders, dtype):
         else:
             out = engine.decode([sa], [a[3 + i]])
         assert scaled_error(out[0], ea[3 + i]) < TOLERANCE[dtype], ("a", i)
-    assert engine.decode_graphs is not None and set(engine.decode_graphs.captured) == {(1, 0), (2, 0)}
+    assert engine.decode_graphs is not None and sorted(size for size, _ in engine.decode_graphs.captured) == [1, 2]
     engine.release_slot(sa)
     engine.cache.check()
 
@@ -129,7 +129,7 @@ def test_graph_decoding_across_a_context_class(cuda_device, tmp_path):
     for i in range(2040, 2061):
         out = engine.decode([slot], [tokens[i]])
         assert scaled_error(out[0], expected[i]) < TOLERANCE["bfloat16"], i
-    spans = {span for _, span in engine.decode_graphs.captured}
+    spans = {capture.span for capture in engine.decode_graphs.captured.values()}
     assert spans == {ops.decode_span(2041), ops.decode_span(2049)} == {2048, 4096}
     assert ops.decode_splits(1, raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], 2049) > 8
     engine.release_slot(slot)
