@@ -15,14 +15,14 @@ state changes (:933-960, :1008-1014).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Mapping, Optional, Sequence, Tuple
+from typing import Dict, List, Mapping, Optional, Sequence
 
 import torch
 
-from ..cache import CacheFull, KvCache, StateArea
+from ..cache import KvCache, StateArea
 from ..config.specs import ModelSpec
 from ..parts import RunContext, Runtime
-from .batch import StepBatch, build_step_batch
+from .batch import build_step_batch
 from .model import DecoderModel
 
 

@@ -22,8 +22,6 @@ import sys
 from pathlib import Path
 from typing import Dict, IO
 
-import numpy as np
-
 from .engine import Engine, StepEntry
 from .loading import engine_from_folder
 

@@ -8,7 +8,7 @@ their place is taken by `stop_token_ids`, checked on token ids.
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional, Tuple
 
 
