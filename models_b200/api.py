@@ -185,9 +185,10 @@ class TextGenerationModel:
         return self.engine.step([StepEntry(self._default_session(), list(tokens), [len(tokens) - 1])])[0]
 
     def forward(self, token: int):
-        """One more token on the default sequence; its logits."""
+        """One more token on the default sequence; its logits (the caller's own copy: a replayed step
+        writes its logits into a buffer that the next step writes again)."""
         self._require_open()
-        return self.engine.decode([self._default_session()], [token])[0]
+        return self.engine.decode([self._default_session()], [token])[0].clone()
 
     def checkpoint(self) -> int:
         return 0 if self._session is None else self.engine.length(self._session)

@@ -55,26 +55,33 @@ class CacheGroup:
         have = len(self.tables[slot])
         return max(0, -(-new_length // self.page_size) - have)
 
-    def extend(self, slot: int, new_length: int) -> None:
+    def extend(self, slot: int, new_length: int) -> int:
+        """Takes the pages `new_length` positions need beyond those held; returns how many it took."""
         table = self.tables[slot]
-        for _ in range(self.pages_needed(slot, new_length)):
+        need = self.pages_needed(slot, new_length)
+        for _ in range(need):
             table.append(self.pages.take())
+        return need
 
-    def drop_invisible(self, slot: int, length: int) -> None:
+    def drop_invisible(self, slot: int, length: int) -> int:
         """After `length` positions are stored, a window group frees the pages no later query sees:
-        the next query sits at position >= length and sees keys >= length - window + 1."""
+        the next query sits at position >= length and sees keys >= length - window + 1.  Returns how
+        many pages it gave back."""
         window = self.request.window
         if window is None:
-            return
+            return 0
         first_visible = length - window + 1
         table = self.tables[slot]
+        dropped = 0
         for block in range(len(table)):
             if (block + 1) * self.page_size <= first_visible:
                 if table[block] >= 0:
                     self.pages.give_back(table[block])
                     table[block] = -1
+                    dropped += 1
             else:
                 break
+        return dropped
 
     def truncate(self, slot: int, length: int) -> None:
         table = self.tables[slot]
@@ -112,6 +119,11 @@ class KvCache:
             raise ValueError(f"max_slots must be positive, got {self.max_slots}")
         self.slots = FreeList(self.max_slots, what="slot")
         self.lengths: Dict[int, int] = {}
+        # A stamp per open slot that changes whenever a page table of the slot does, and that no slot ever
+        # carries twice: whoever keeps a copy of a slot's page tables (a captured step does) compares stamps
+        # to know whether the copy still holds.  A slot id alone does not say so: it is handed out again.
+        self.table_stamps: Dict[int, int] = {}
+        self._last_stamp = 0
         self.groups: List[CacheGroup] = []
         self.run_location: Dict[int, Tuple[int, int]] = {}  # run -> (group index, index in the group's storage)
         by_key: Dict[KvRequest, CacheGroup] = {}
@@ -161,11 +173,16 @@ class KvCache:
 
     # ---------------------------------------------------------------- slots
 
+    def _stamp(self, slot: int) -> None:
+        self._last_stamp += 1
+        self.table_stamps[slot] = self._last_stamp
+
     def open_slot(self) -> int:
         slot = self.slots.take()
         self.lengths[slot] = 0
         for group in self.groups:
             group.tables[slot] = []
+        self._stamp(slot)
         return slot
 
     def release(self, slot: int) -> None:
@@ -173,6 +190,7 @@ class KvCache:
         for group in self.groups:
             group.release(slot)
         del self.lengths[slot]
+        del self.table_stamps[slot]
         self.slots.give_back(slot)
 
     def length(self, slot: int) -> int:
@@ -215,15 +233,15 @@ class KvCache:
             if n <= 0:
                 raise ValueError(f"slot {slot}: a step must bring at least one token, got {n}")
         self._check_append(appends)
-        for group in self.groups:
-            for slot, n in appends:
-                group.extend(slot, self.lengths[slot] + n)
+        for slot, n in appends:
+            if sum(group.extend(slot, self.lengths[slot] + n) for group in self.groups):
+                self._stamp(slot)
 
     def commit(self, appends: Sequence[Tuple[int, int]]) -> None:
         for slot, n in appends:
             self.lengths[slot] += n
-            for group in self.groups:
-                group.drop_invisible(slot, self.lengths[slot])
+            if sum(group.drop_invisible(slot, self.lengths[slot]) for group in self.groups):
+                self._stamp(slot)
 
     def rewind(self, slot: int, length: int) -> None:
         """Forgets the positions >= length.  A window group that already gave back pages the shorter
@@ -241,6 +259,7 @@ class KvCache:
         for group in self.groups:
             group.truncate(slot, length)
         self.lengths[slot] = length
+        self._stamp(slot)
 
     # ---------------------------------------------------------------- checks
 

@@ -34,6 +34,63 @@ def ladder(max_batch: int) -> List[int]:
     return sizes
 
 
+class DecodeRows:
+    """The indices of a captured decode step on the host, kept up to date in place from one step to the
+    next (host arithmetic only: it runs without a GPU).  `buffer` is the step's int32 buffer in the
+    order of `layout`; it must hold a valid all-padding step when this is made."""
+
+    def __init__(self, layout: StepLayout, buffer: np.ndarray):
+        off = [int(o) for o in layout.offsets]
+        size, blocks, n = layout.sequences, layout.blocks, buffer
+        self.tokens_h, self.positions_h = n[off[0]:off[1]], n[off[1]:off[2]]
+        self.kv_lens_h, self.slots_h = n[off[3]:off[4]], n[off[4]:off[5]]
+        self.tables_h = [n[off[6 + 2 * g]:off[7 + 2 * g]].reshape(size, blocks) for g in range(layout.groups)]
+        self.mappings_h = [n[off[7 + 2 * g]:off[8 + 2 * g]] for g in range(layout.groups)]
+        self.row_stamps = [0] * size  # the cache's table stamp of what each row of the page tables holds (0: nothing)
+        self.live = 0
+
+    def update(self, cache, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
+        """The indices of one decode step, written in place: one token per slot, appended at each
+        slot's length.  A row of the page tables is rewritten only when the cache's stamp of the slot's
+        tables differs from the one the row was written with (another sequence, a new page, a rewind).
+        `tokens` None: the token ids are already on the device."""
+        live, page = len(slots), cache.page_size
+        pad_row = cache.max_slots
+        lengths = [cache.lengths[s] for s in slots]
+        if tokens is not None:
+            self.tokens_h[:live] = tokens
+        self.positions_h[:live] = lengths
+        self.kv_lens_h[:live] = lengths
+        self.kv_lens_h[:live] += 1
+        self.slots_h[:live] = slots
+        if live < self.live:  # rows that fell out of the batch become padding
+            self.tokens_h[live:self.live] = 0
+            self.positions_h[live:self.live] = 0
+            self.kv_lens_h[live:self.live] = 1
+            self.slots_h[live:self.live] = pad_row
+            for g in range(len(self.tables_h)):
+                self.tables_h[g][live:self.live] = 0
+                self.mappings_h[g][live:self.live] = -1
+            for b in range(live, self.live):
+                self.row_stamps[b] = 0
+        self.live = live
+        for b, slot in enumerate(slots):
+            length = lengths[b]
+            block, offset = length // page, length % page
+            # a slot id is handed out again and so are pages, in any order: only the stamp says whether
+            # the row still holds this sequence's tables as they are now
+            stamp = cache.table_stamps[slot]
+            refresh = self.row_stamps[b] != stamp
+            self.row_stamps[b] = stamp
+            for g, group in enumerate(cache.groups):
+                table = group.tables[slot]
+                self.mappings_h[g][b] = table[block] * page + offset
+                if refresh:  # pages a window group gave back are never read: their stale ids may stay
+                    row = self.tables_h[g][b]
+                    row[:len(table)] = [p if p >= 0 else 0 for p in table]
+                    row[len(table):] = 0
+
+
 class _Captured:
     """One captured step: `size` sequences of one token each, or with `tokens` a step of so many
     rows shared by up to `size` sequences in any way."""
@@ -79,16 +136,7 @@ class _Captured:
                 gc.enable()
         self.kernels = ops.launch_count() - before  # this package's kernels inside one replay
         ops.add_launches(-self.kernels)  # a capture launches nothing
-        # views of the pinned buffer, for the quick per-step update
-        off = [int(o) for o in self.layout.offsets]
-        n = self.host_np
-        self.tokens_h, self.positions_h = n[off[0]:off[1]], n[off[1]:off[2]]
-        self.kv_lens_h, self.slots_h = n[off[3]:off[4]], n[off[4]:off[5]]
-        groups = len(cache.groups)
-        self.tables_h = [n[off[6 + 2 * g]:off[7 + 2 * g]].reshape(size, blocks) for g in range(groups)]
-        self.mappings_h = [n[off[7 + 2 * g]:off[8 + 2 * g]] for g in range(groups)]
-        self.row_owner = [(-1, -1)] * size  # (slot, blocks written) of each row of the page tables
-        self.live = 0
+        self.rows = DecodeRows(self.layout, self.host_np)  # the quick per-step update of the indices
         self.staging = [(torch.zeros_like(self.host).pin_memory(), torch.cuda.Event()) for _ in range(4)]
         self.staging_next = 0
 
@@ -112,42 +160,7 @@ class _Captured:
         return sum(len(want) for _, _, want in entries)
 
     def update(self, cache, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> None:
-        """The indices of one decode step, written in place: one token per slot, appended at each
-        slot's length.  Page-table rows are rewritten only when a sequence moved in or gained a page.
-        `tokens` None: the token ids are already on the device."""
-        live, page = len(slots), cache.page_size
-        pad_row = cache.max_slots
-        lengths = [cache.lengths[s] for s in slots]
-        if tokens is not None:
-            self.tokens_h[:live] = tokens
-        self.positions_h[:live] = lengths
-        self.kv_lens_h[:live] = lengths
-        self.kv_lens_h[:live] += 1
-        self.slots_h[:live] = slots
-        if live < self.live:  # rows that fell out of the batch become padding
-            self.tokens_h[live:self.live] = 0
-            self.positions_h[live:self.live] = 0
-            self.kv_lens_h[live:self.live] = 1
-            self.slots_h[live:self.live] = pad_row
-            for g in range(len(self.tables_h)):
-                self.tables_h[g][live:self.live] = 0
-                self.mappings_h[g][live:self.live] = -1
-            for b in range(live, self.live):
-                self.row_owner[b] = (-1, -1)
-        self.live = live
-        for b, slot in enumerate(slots):
-            length = lengths[b]
-            block, offset = length // page, length % page
-            blocks_held = len(cache.groups[0].tables[slot]) if cache.groups else 0  # the same in every group
-            refresh = self.row_owner[b] != (slot, blocks_held)
-            self.row_owner[b] = (slot, blocks_held)
-            for g, group in enumerate(cache.groups):
-                table = group.tables[slot]
-                self.mappings_h[g][b] = table[block] * page + offset
-                if refresh:  # pages a window group gave back are never read: their stale ids may stay
-                    row = self.tables_h[g][b]
-                    row[:len(table)] = [p if p >= 0 else 0 for p in table]
-                    row[len(table):] = 0
+        self.rows.update(cache, slots, tokens)
 
 
 class DecodeGraphs:

@@ -114,3 +114,78 @@ def test_random_schedule_of_batches_loses_nothing():
         cache.release(s)
     cache.check()
     assert cache.slots.held == 0 and all(g.pages.held == 0 for g in cache.groups)
+
+
+def test_table_stamps_change_with_the_tables_and_never_repeat():
+    cache = _cache(max_tokens=64 * 12, window=70)
+    seen = set()
+    a = cache.open_slot()
+    stamp = cache.table_stamps[a]
+    seen.add(stamp)
+    cache.append([(a, 10)])  # a first page
+    assert cache.table_stamps[a] != stamp
+    stamp = cache.table_stamps[a]
+    seen.add(stamp)
+    cache.commit([(a, 10)])
+    cache.append([(a, 1)])  # no new page: the tables are what they were
+    cache.commit([(a, 1)])
+    assert cache.table_stamps[a] == stamp
+    cache.append([(a, 60)])  # a second page
+    cache.commit([(a, 60)])
+    assert cache.table_stamps[a] not in seen
+    seen.add(cache.table_stamps[a])
+    cache.append([(a, 64)])
+    stamp = cache.table_stamps[a]
+    cache.commit([(a, 64)])  # 135 positions, window 70: the window group gives its first page back
+    assert cache.groups[1].tables[a][0] == -1 and cache.table_stamps[a] != stamp
+    seen.add(cache.table_stamps[a])
+    cache.rewind(a, 134)
+    assert cache.table_stamps[a] not in seen
+    seen.add(cache.table_stamps[a])
+    cache.release(a)
+    assert a not in cache.table_stamps
+    b = cache.open_slot()
+    assert b == a and cache.table_stamps[b] not in seen  # the same slot id, another tenant: another stamp
+
+
+def test_decode_rows_follow_the_tables_of_a_slot_that_is_used_again():
+    """Two requests of two pages end; two others get their slots, at the same rows, with as many pages --
+    the same pages in the other order.  The rows of a captured step must then hold the new tables."""
+    import numpy as np
+
+    from models_b200.engine.batch import StepLayout, pack_step
+    from models_b200.engine.decode_graph import DecodeRows
+
+    full = KvRequest(2, 16, None)
+    cache = KvCache([full], [None], 64 * 8, max_slots=2)
+    layout = StepLayout(2, 2, 2, 4, 1)
+    buffer = np.zeros(layout.total, dtype=np.int32)
+    pack_step(cache, [], layout, buffer, cache.max_slots)
+    rows = DecodeRows(layout, buffer)
+
+    def tenant_pair(prompt):
+        slots = [cache.open_slot(), cache.open_slot()]
+        appends = [(s, prompt) for s in slots]
+        cache.append(appends)
+        cache.commit(appends)
+        for _ in range(3):
+            step = [(s, 1) for s in slots]
+            cache.append(step)
+            rows.update(cache, slots, [1, 2])
+            for b, s in enumerate(slots):
+                table = cache.groups[0].tables[s]
+                assert rows.tables_h[0][b, :len(table)].tolist() == table, (b, table)
+                length = cache.lengths[s]
+                assert rows.mappings_h[0][b] == table[length // 64] * 64 + length % 64
+                assert rows.kv_lens_h[b] == length + 1 and rows.positions_h[b] == length
+            cache.commit(step)
+        return slots, [list(cache.groups[0].tables[s]) for s in slots]
+
+    first_slots, first_tables = tenant_pair(70)
+    for s in reversed(first_slots):
+        cache.release(s)
+    second_slots, second_tables = tenant_pair(70)
+    assert second_slots == first_slots and [len(t) for t in second_tables] == [len(t) for t in first_tables]
+    assert second_tables != first_tables  # the case that a (slot, page count) key cannot tell apart
+    rows.update(cache, second_slots[:1], [3])  # one row falls out: it becomes padding
+    assert rows.tables_h[0][1].tolist() == [0, 0, 0, 0] and rows.mappings_h[0][1] == -1 and rows.slots_h[1] == cache.max_slots
