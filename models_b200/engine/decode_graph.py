@@ -169,7 +169,7 @@ class DecodeGraphs:
         self.max_batch = max_batch
         self.blocks = blocks
         self.sizes = ladder(max_batch)
-        self.captured: Dict[tuple, _Captured] = {}  # (batch size, launch class)
+        self.captured: Dict[tuple, _Captured] = {}  # (batch size, launch class: page-table width and the mixers' classes)
         self.last_argmax = None  # first maximum of every row of the last step's logits (device, int32)
         self.pool = torch.cuda.graph_pool_handle()
 
@@ -179,13 +179,26 @@ class DecodeGraphs:
                 return size
         raise ValueError(f"a decode batch of {n} exceeds the largest captured size {self.max_batch}")
 
+    def table_width(self, max_kv_len: int) -> int:
+        """Pages per sequence in the page tables of the capture for this length: the next of 4, 8, 16, ...
+        that holds it, at most the engine's longest sequence.  The width is part of the captured launches
+        (the kernels stride the tables by it) and of what every step copies to the device, so short
+        sequences do not carry the longest one's tables."""
+        need = -(-max_kv_len // self.engine.cache.page_size)
+        width = 4
+        while width < need:
+            width *= 2
+        return min(width, self.blocks)
+
     def launch_class(self, size: int, max_kv_len: int) -> tuple:
-        """What the launches of a decode step of `size` sequences depend on besides the batch size: every
-        mixer's answer for the class of context lengths (long contexts split their keys over more
-        blocks, and the split is part of the captured launches).  Most steps share one class."""
+        """What the launches of a decode step of `size` sequences depend on besides the batch size: the
+        width of the page tables, and every mixer's answer for the class of context lengths (long
+        contexts split their keys over more blocks, and the split is part of the captured launches).
+        Most steps share one class."""
         span = ops.decode_span(max_kv_len)
         mixers = [block.mixer for block in self.engine.model.blocks]
-        return tuple(m.decode_class(size, span) if hasattr(m, "decode_class") else 0 for m in mixers)
+        return (self.table_width(max_kv_len),) + tuple(
+            m.decode_class(size, span) if hasattr(m, "decode_class") else 0 for m in mixers)
 
     def prepare(self, size: int, max_kv_len: int) -> _Captured:
         """The capture for `size` sequences (a rung) of up to `max_kv_len` positions, made if it is not
@@ -194,7 +207,7 @@ class DecodeGraphs:
         key = (size, self.launch_class(size, max_kv_len))
         captured = self.captured.get(key)
         if captured is None:
-            captured = self.captured[key] = _Captured(self.engine, size, self.blocks, self.pool, ops.decode_span(max_kv_len))
+            captured = self.captured[key] = _Captured(self.engine, size, key[1][0], self.pool, ops.decode_span(max_kv_len))
         return captured
 
     def step(self, entries: Sequence, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -228,7 +241,7 @@ class PromptGraphs:
     def __init__(self, decode_graphs: DecodeGraphs):
         self.decode_graphs = decode_graphs
         self.engine = decode_graphs.engine
-        self.captured: Dict[tuple, _Captured] = {}  # (batch size, token count)
+        self.captured: Dict[tuple, _Captured] = {}  # (batch size, token count, page-table width)
         self.uses: Dict[tuple, int] = {}
 
     def bucket(self, entries: Sequence) -> Optional[tuple]:
@@ -242,9 +255,10 @@ class PromptGraphs:
         size = graphs.rung(len(entries))
         if wanted > size:
             return None
-        if any(-(-(cache.lengths[slot] + len(tokens)) // cache.page_size) > graphs.blocks for slot, tokens, _ in entries):
+        longest = max(cache.lengths[slot] + len(tokens) for slot, tokens, _ in entries)
+        if -(-longest // cache.page_size) > graphs.blocks:
             return None
-        return size, next(t for t in PROMPT_TOKENS if t >= total)
+        return size, next(t for t in PROMPT_TOKENS if t >= total), graphs.table_width(longest)
 
     def step(self, entries: Sequence) -> Optional[torch.Tensor]:
         """entries: (slot, tokens, wanted places); the cache already has room.  Returns the logits of
@@ -259,7 +273,7 @@ class PromptGraphs:
             if self.uses[key] <= EAGER_USES:
                 return None
             graphs = self.decode_graphs
-            captured = self.captured[key] = _Captured(self.engine, key[0], graphs.blocks, graphs.pool, tokens=key[1])
+            captured = self.captured[key] = _Captured(self.engine, key[0], key[2], graphs.pool, tokens=key[1])
         wanted = captured.fill(self.engine.cache, entries)
         captured.upload()
         captured.graph.replay()

@@ -140,9 +140,15 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Appends each entry's tokens to its slot and returns float32 logits [wanted, vocab] in the
         order of the entries and of their `want` lists (None if nothing is wanted).  A refused step
-        (StepError, CacheFull) leaves every slot as it was."""
+        (StepError, CacheFull) leaves every slot as it was.  With graphs enabled a step of one token
+        per sequence that wants each token's logits is the captured decode step (the result is a copy)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self.validate(entries)
+        if self._fits_decode_graphs(entries) and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._decode_from_graph(entries).clone()
+        return self._step(entries)
+
+    def _step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         appends = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.append(appends)
         packed = [(e.slot, e.tokens, e.want) for e in entries]
@@ -152,48 +158,50 @@ class Engine:
             logits = self.model.forward(batch, self.runs)
         self.cache.commit(appends)
         self.steps += 1
+        self.last_argmax = None
         return logits
 
-    def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
-        """One more token for each slot; logits [len(slots), vocab] for these tokens.  The same as
-        `step` with single-token entries that each want place 0, replayed from a CUDA graph when
-        graphs are enabled and the batch fits them.  The result is overwritten by the next decode."""
-        entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+    def _fits_decode_graphs(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether the captured decode steps take this batch: graphs enabled, no more sequences than the
+        largest capture, no sequence longer than the captures' page tables."""
         graphs = self.decode_graphs
-        self.last_argmax = None
         if graphs is None or len(entries) > graphs.max_batch:
-            return self.step(entries)
-        self.validate(entries)
-        if any(-(-(self.cache.lengths[e.slot] + 1) // self.cache.page_size) > graphs.blocks for e in entries):
-            return self.step(entries)
+            return False
+        page = self.cache.page_size
+        return all(-(-(self.cache.lengths[e.slot] + 1) // page) <= graphs.blocks for e in entries)
+
+    def _decode_from_graph(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        graphs = self.decode_graphs
         appends = [(e.slot, 1) for e in entries]
         self.cache.append(appends)
-        logits = graphs.step([(e.slot, e.tokens, e.want) for e in entries])
+        logits = graphs.step([(e.slot, e.tokens, e.want) for e in entries], device_tokens=device_tokens)
         self.last_argmax = graphs.last_argmax  # the graph holds the greedy choice too
         self._last_logits = logits
         self.cache.commit(appends)
         self.steps += 1
         return logits
 
+    def decode(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
+        """One more token for each slot; logits [len(slots), vocab] for these tokens.  The same as
+        `step` with single-token entries that each want place 0, replayed from a CUDA graph when
+        graphs are enabled and the batch fits them; the result is then the graph's own buffer, which
+        the next decode overwrites."""
+        entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        self.validate(entries)
+        if not self._fits_decode_graphs(entries):
+            return self._step(entries)
+        return self._decode_from_graph(entries)
+
     def decode_device_tokens(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         """`decode` with the token ids still on the device (int32 [len(slots)], what a sampler just
         wrote): the step is queued without waiting for them, so the host can prepare it while the
         step before it runs.  Without decode graphs (or beyond their sizes) the ids are fetched and
         the step runs as `decode` does."""
-        graphs = self.decode_graphs
-        if (graphs is None or len(slots) > graphs.max_batch or
-                any(-(-(self.cache.lengths[s] + 1) // self.cache.page_size) > graphs.blocks for s in slots)):
-            return self.decode(slots, tokens.tolist())
         entries = [StepEntry(s, [0], [0]) for s in slots]  # ids come from the device; a sampler's ids are in range
         self.validate(entries)
-        appends = [(s, 1) for s in slots]
-        self.cache.append(appends)
-        logits = graphs.step([(e.slot, e.tokens, e.want) for e in entries], device_tokens=tokens)
-        self.last_argmax = graphs.last_argmax
-        self._last_logits = logits
-        self.cache.commit(appends)
-        self.steps += 1
-        return logits
+        if not self._fits_decode_graphs(entries):
+            return self.decode(slots, tokens.tolist())
+        return self._decode_from_graph(entries, device_tokens=tokens)
 
     def greedy_tokens(self, logits: torch.Tensor) -> torch.Tensor:
         """First maximum of every row of `logits` (device, int32): taken from the decode graph when

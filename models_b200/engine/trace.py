@@ -1,7 +1,9 @@
 """Trace replay: feeds given token ids through the engine step by step and writes logits.
 
 It samples nothing and owns no model code: every step goes through `Engine.step`, the function
-generation uses, with the engine's cache and kernels.  The nearest pieces of integrallis/models are
+generation uses, with the engine's cache and kernels -- and, as in generation, with steps replayed
+from CUDA graphs where the engine captures them (one token per sequence; short prompt steps from
+their third occurrence on).  `--graphs off` runs every step launch by launch instead.  The nearest pieces of integrallis/models are
 `verify`, which returns the logits of every consumed token
 (backend-java/.../llama/LlamaForwardPass.java:1199-1249), and its determinism audit
 (models-bench/.../DeterminismAuditCli.java:115-140).
@@ -85,9 +87,15 @@ def main(argv=None) -> int:
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", required=True, type=int,
                         help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+    parser.add_argument("--graphs", default="on", choices=["on", "off"],
+                        help="replay captured steps as generation does (default), or launch every kernel of every step")
     args = parser.parse_args(argv)
     if args.max_tokens <= 0:
         parser.error("--max-tokens must be positive")
     engine = engine_from_folder(args.model, args.dtype, args.max_tokens)
+    if args.graphs == "on":
+        # any number of live requests the cache has slots for, of any length it has pages for; captures
+        # are made when a batch size and a class of lengths first come up
+        engine.enable_decode_graphs(engine.cache.max_slots)
     TraceReplayer(engine, args.out).replay(sys.stdin, sys.stdout)
     return 0

@@ -180,7 +180,7 @@ def test_prompt_steps_replayed_from_captures_match_plain(cuda_device, folders, n
             engine.release_slot(s)
     engine.cache.check()
     captured = set(engine.prompt_graphs.captured)
-    assert captured == {(4, 32), (1, 16)}, captured  # the classes that came up more than twice
+    assert captured == {(4, 32, 2), (1, 16, 2)}, captured  # the classes that came up more than twice
 
 
 def test_prompt_captures_leave_large_and_unwanted_steps_alone(cuda_device, folders):
@@ -198,8 +198,8 @@ def test_prompt_captures_leave_large_and_unwanted_steps_alone(cuda_device, folde
     assert graphs.bucket([(slot, [1] * (PROMPT_TOKENS[-1] + 1), [0])]) is None
     assert graphs.bucket([(slot, [1] * 8, [])]) is None
     assert graphs.bucket([(slot, [1] * 8, [0, 1, 2])]) is None
-    assert graphs.bucket([(slot, [1] * 8, [7])]) == (1, 16)
-    assert graphs.bucket([(slot, [1] * 17, [0])]) == (1, 32)
+    assert graphs.bucket([(slot, [1] * 8, [7])]) == (1, 16, 4)
+    assert graphs.bucket([(slot, [1] * 17, [0])]) == (1, 32, 4)
     engine.release_slot(slot)
 
 
