@@ -119,12 +119,16 @@ class EmbeddingSpec:
 @dataclass(frozen=True)
 class HeadSpec:
     """Output projection to the vocabulary.  `tied`: it uses the embedding table and owns no
-    tensor (backend-java/.../llama/LlamaWeights.java:83-89)."""
+    tensor (backend-java/.../llama/LlamaWeights.java:83-89).  The logits are multiplied by
+    `logit_scale`, then with `softcap` c != 0 become c * tanh(logits / c)
+    (backend-java/.../llama/LlamaForwardPass.java:1751-1764)."""
 
     vocab_size: int
     hidden_size: int
     tied: bool
     weights: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    logit_scale: float = 1.0
+    softcap: float = 0.0
     kind: str = "linear_head"
 
 

@@ -15,7 +15,22 @@
 #define MB_F32 0
 #define MB_BF16 1
 
+// Gate activations of a gated feed-forward.  A launcher takes the code in bits 8 and up of its
+// epilogue argument (0, the default, is SiLU).
+#define MB_ACT_SILU 0
+#define MB_ACT_GELU_TANH 1
+#define MB_ACT_COUNT 2
+
 namespace mb {
+
+// act(gate): silu(z) = z / (1 + exp(-z)) (integrallis/models, backend-java/.../ops/TensorOps.java:1407-1425);
+// gelu_tanh(z) = 0.5 z (1 + tanh(0.7978845608 z (1 + 0.044715 z^2))) (:1427-1449).  `activation` is the
+// same for every thread of a launch, so the branch does not diverge.
+__device__ __forceinline__ float gate_activation(int activation, float z) {
+    if (activation == MB_ACT_GELU_TANH)
+        return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * z * (1.0f + 0.044715f * z * z)));
+    return z / (1.0f + expf(-z));
+}
 
 // One message per library and host thread; read by mb_last_error() after a non-zero return.
 inline char* error_buffer() {

@@ -115,6 +115,7 @@ __device__ __forceinline__ void tile_coordinates(int tile, int m_tiles, int n_ti
 struct GemmArgs {
     int m, n, k;          // n: output columns (for EPI_SWIGLU the gate count, half the weight rows)
     int up_row_offset;    // EPI_SWIGLU: first up row of W
+    int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int k_splits;         // EPI_RESIDUAL: blocks that share an output tile, each with its own part of K (else 1)
     void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream; EPI_ROPE: the queries [m, heads * head_dim]
     int ld_out;
@@ -378,7 +379,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 tmem_load_32_issue(taddr + 128 + c + 32 * part, u);
                                 tmem_load_wait();
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.0f + expf(-v[i])) * u[i];
+                                for (int i = 0; i < 32; ++i) v[i] = gate_activation(args.activation, v[i]) * u[i];
                             } else {
                                 tmem_load_32_issue(taddr + c + 32 * part, v);
                                 tmem_load_wait();
@@ -554,7 +555,8 @@ using namespace mb;
 
 // a: bfloat16 [m, k] (row stride lda); w: bfloat16 [n_w, k] (row stride ldw).
 // epilogue 0: out bfloat16 [m, n_w]; 1: out float32 [m, n_w]; 2: out float32 [m, n_w] += ; 3: w holds gate
-// rows [0, n_w/2) and up rows [n_w/2, n_w): out bfloat16 [m, n_w/2] = silu(gate) * up.
+// rows [0, n_w/2) and up rows [n_w/2, n_w): out bfloat16 [m, n_w/2] = act(gate) * up, the activation code (MB_ACT_*)
+// in bits 8 and up of `epilogue`.
 // tile_width: 0 lets the launcher choose between 128 and 256 output columns per tile; the gated epilogue takes 256.
 // pair: 2 runs tiles of 256 rows x 256 columns on pairs of blocks (tcgen05 cta_group::2); 1: one block per tile; 0: the launcher chooses.
 MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ld_out, int m, int n_w, int k,
@@ -562,6 +564,9 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     if (tile_width != 0 && tile_width != 128 && tile_width != 256) return fail("gemm_tcgen05: tile width %d is not built (128, 256)", tile_width);
     if (pair < 0 || pair > 2) return fail("gemm_tcgen05: pair must be 0, 1 or 2, got %d", pair);
     if (pair == 2 && tile_width == 128) return fail("gemm_tcgen05: pairs of blocks take tiles of 256 columns");
+    const int activation = epilogue >> 8;
+    epilogue &= 0xff;
+    if (activation < 0 || activation >= MB_ACT_COUNT) return fail("gemm_tcgen05: unknown gate activation code %d", activation);
     if (m <= 0 || n_w <= 0) return 0;
     if (k <= 0 || k % 8 || lda % 8 || ldw % 8) return fail("gemm_tcgen05: k (%d) and the row strides (%d, %d) must be multiples of 8", k, lda, ldw);
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return fail("gemm_tcgen05: operands must start on 16-byte boundaries");
@@ -572,7 +577,7 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     CUtensorMap map_a, map_w;
     if (int status = make_map(&map_a, a, m, k, lda)) return status;
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
-    GemmArgs args{m, n, k, n, 1, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    GemmArgs args{m, n, k, n, activation, 1, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     switch (epilogue) {
         case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
         case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);

@@ -8,7 +8,8 @@
 //   epilogue  BF16 / F32: store.  RESIDUAL: add into the float32 residual stream
 //             (x = x + W.h, backend-java/.../llama/LlamaForwardPass.java:1131-1138,1172-1178).
 //             SWIGLU: the 16 rows of a tile are 8 gate rows and the 8 up rows that match them, and
-//             silu(gate) * up is stored (backend-java/.../ops/TensorOps.java:1407-1425).
+//             act(gate) * up is stored (silu: backend-java/.../ops/TensorOps.java:1407-1425; the
+//             activation is an argument).
 //             ROPE: W is [q heads; k heads; v heads]; the 16 rows of a tile are 8 coordinates of a head
 //             and their rotation partners half a head further; query and key pairs are rotated by the
 //             token's position (x0' = x0*c - x1*s, x1' = x0*s + x1*c, backend-java/.../ops/TensorOps.java:1481-1486),
@@ -51,18 +52,9 @@ enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE = 4
 
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-#ifndef MB_SKINNY_DEPTH
-#define MB_SKINNY_DEPTH 4
-#endif
-#ifndef MB_SKINNY_STEP
-#define MB_SKINNY_STEP 128
-#endif
-#ifndef MB_SKINNY_RESIDENT
-#define MB_SKINNY_RESIDENT 4
-#endif
-constexpr int kMaxResident = MB_SKINNY_RESIDENT;  // most blocks per multiprocessor the planner counts on
-constexpr int kDepth = MB_SKINNY_DEPTH;  // stages of the weight ring
-constexpr int kStep = MB_SKINNY_STEP;    // columns per stage: 32 per piece, a lane takes 8 of each piece
+constexpr int kMaxResident = 4;  // most blocks per multiprocessor the planner counts on
+constexpr int kDepth = 4;        // stages of the weight ring
+constexpr int kStep = 128;       // columns per stage: 32 per piece, a lane takes 8 of each piece
 constexpr int kPieces = kStep / 32;
 static_assert(kStep % 32 == 0 && kPieces >= 1 && kDepth >= 2, "a stage is a whole number of 32-column pieces");
 
@@ -108,6 +100,7 @@ struct SkinnyArgs {
     float* out_f32;       // EPI_F32 output, or the residual stream for EPI_RESIDUAL
     int ld_out;
     int pair_offset;      // EPI_SWIGLU: the up tile starts pair_offset rows after the gate tile
+    int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int k_split;          // blocks of a cluster that share K
     int k_unit;           // columns per block, a multiple of 4 * kStep
     int k_warp;           // columns per warp, a multiple of kStep
@@ -338,7 +331,7 @@ skinny_gemm_kernel(const SkinnyArgs args) {
             if (EPI == EPI_BF16) args.out_bf16[at] = __float2bfloat16_rn(value);
             if (EPI == EPI_F32) args.out_f32[at] = value;
             if (EPI == EPI_RESIDUAL) args.out_f32[at] += value;
-            if (EPI == EPI_SWIGLU) args.out_bf16[at] = __float2bfloat16_rn(value / (1.0f + expf(-value)) * second);
+            if (EPI == EPI_SWIGLU) args.out_bf16[at] = __float2bfloat16_rn(gate_activation(args.activation, value) * second);
             if (EPI == EPI_ROPE) {
                 const int tiles_per_head = args.head_dim / 16, half = args.head_dim / 2;
                 const int head = tile / tiles_per_head, d0 = (tile % tiles_per_head) * 8 + row_in_tile;
@@ -422,11 +415,16 @@ MB_EXPORT int mb_skinny_max_rows(int with_norm) { return with_norm ? 16 : 32; }
 // w: bfloat16 [n, k] (row stride ldw).  Activations: x (bfloat16 [batch, k]) when gain is null,
 // else xf (float32 rows, optionally picked by `rows`) normalised with `gain` and `eps`.
 // epilogue 0: out bfloat16 [batch, n]; 1: out float32; 2: out float32 += ; 3: w holds gate rows
-// [0, n/2) and up rows [n/2, n), out bfloat16 [batch, n/2] = silu(gate) * up.
+// [0, n/2) and up rows [n/2, n), out bfloat16 [batch, n/2] = act(gate) * up with the activation code
+// (MB_ACT_*) in bits 8 and up of `epilogue`.
 static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, const float* xf,
                        int ldxf, const float* gain, float eps, const int* rows, void* out, int ld_out,
                        int epilogue, int multiprocessors, int dependent, SkinnyArgs args, cudaStream_t stream) {
     if (batch <= 0 || n <= 0) return 0;
+    const int activation = epilogue >> 8;
+    epilogue &= 0xff;
+    if (activation < 0 || activation >= MB_ACT_COUNT) return fail("skinny_gemm: unknown gate activation code %d", activation);
+    args.activation = activation;
     if (batch > 32) return fail("skinny_gemm: takes at most 32 activation rows, got %d", batch);
     if (k <= 0 || k % 8 || ldw % 8) return fail("skinny_gemm: k (%d) and the weight row stride (%d) must be multiples of 8", k, ldw);
     if ((uintptr_t)w & 15) return fail("skinny_gemm: the weight matrix must start on a 16-byte boundary");
@@ -487,7 +485,7 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
 MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, const float* xf,
                              int ldxf, const float* gain, float eps, const int* rows, void* out, int ld_out,
                              int epilogue, int multiprocessors, int dependent, cudaStream_t stream) {
-    if (epilogue == EPI_ROPE) return fail("skinny_gemm: the rotary epilogue has an entry point of its own");
+    if ((epilogue & 0xff) == EPI_ROPE) return fail("skinny_gemm: the rotary epilogue has an entry point of its own");
     return skinny_gemm(w, ldw, n, k, batch, x, ldx, xf, ldxf, gain, eps, rows, out, ld_out, epilogue, multiprocessors, dependent,
                        SkinnyArgs{}, stream);
 }

@@ -34,6 +34,7 @@ constexpr int kThreads = 192;                     // warp 0: TMA, warp 1: MMA, w
 struct WideArgs {
     int rows_total;       // output columns = weight rows (for EPI_SWIGLU: gate rows)
     int up_row_offset;    // EPI_SWIGLU: first up row of W
+    int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int batch, k;
     int tiles, splits, k_blocks_per_split;
     void* out;            // [batch, rows_total] bfloat16 / float32 (row stride ld_out)
@@ -223,7 +224,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                             const int b = c + i;
                             if (b >= args.batch) break;
                             float value = v[i];
-                            if (EPI == EPI_SWIGLU) value = value / (1.0f + expf(-value)) * u[i];
+                            if (EPI == EPI_SWIGLU) value = gate_activation(args.activation, value) * u[i];
                             const size_t at = (size_t)b * args.ld_out + row;
                             if (EPI == EPI_BF16 || EPI == EPI_SWIGLU) reinterpret_cast<bf16*>(args.out)[at] = __float2bfloat16_rn(value);
                             if (EPI == EPI_F32) reinterpret_cast<float*>(args.out)[at] = value;
@@ -284,6 +285,7 @@ using namespace mb;
 // The tickets must be zero before the first launch that uses them; every launch leaves them zero.
 MB_EXPORT void mb_wide_gemm_scratch(int n_w, int k, int batch, int epilogue, int multiprocessors, size_t* partial_floats,
                                     size_t* ticket_ints) {
+    epilogue &= 0xff;
     const int rows_total = epilogue == EPI_SWIGLU ? n_w / 2 : n_w;
     int tiles, splits, per_split;
     plan(rows_total, k, multiprocessors, &tiles, &splits, &per_split);
@@ -295,10 +297,13 @@ MB_EXPORT void mb_wide_gemm_scratch(int n_w, int k, int batch, int epilogue, int
 
 // x: bfloat16 [batch, k] (33..128 rows pay off; 1..128 are taken); w: bfloat16 [n_w, k].
 // epilogue 0: out bfloat16 [batch, n_w]; 1: float32; 2: float32 += ; 3: w = [gate rows; up rows], out
-// bfloat16 [batch, n_w/2] = silu(gate) * up.
+// bfloat16 [batch, n_w/2] = act(gate) * up, the activation code (MB_ACT_*) in bits 8 and up of `epilogue`.
 MB_EXPORT int mb_wide_gemm(const void* x, int ldx, const void* w, int ldw, void* out, int ld_out, int batch, int n_w, int k,
                            int epilogue, float* partial, int* tickets, int multiprocessors, cudaStream_t stream) {
     if (batch <= 0 || n_w <= 0) return 0;
+    const int activation = epilogue >> 8;
+    epilogue &= 0xff;
+    if (activation < 0 || activation >= MB_ACT_COUNT) return fail("wide_gemm: unknown gate activation code %d", activation);
     if (batch > 128) return fail("wide_gemm: takes at most 128 activation rows, got %d", batch);
     if (k <= 0 || k % 8 || ldx % 8 || ldw % 8) return fail("wide_gemm: k (%d) and the row strides (%d, %d) must be multiples of 8", k, ldx, ldw);
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail("wide_gemm: operands must start on 16-byte boundaries");
@@ -306,6 +311,7 @@ MB_EXPORT int mb_wide_gemm(const void* x, int ldx, const void* w, int ldw, void*
     WideArgs args{};
     args.rows_total = epilogue == EPI_SWIGLU ? n_w / 2 : n_w;
     args.up_row_offset = args.rows_total;
+    args.activation = activation;
     args.batch = batch;
     args.k = k;
     plan(args.rows_total, k, multiprocessors, &args.tiles, &args.splits, &args.k_blocks_per_split);

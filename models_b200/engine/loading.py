@@ -29,8 +29,8 @@ def engine_from_folder(folder, dtype: str = "bfloat16", max_tokens: int = 4096, 
 def engine_from_config(config, seed: int, dtype: str = "bfloat16", max_tokens: int = 4096,
                        max_slots: Optional[int] = None, device="cuda:0", std: float = 0.02,
                        gain_std: float = 0.1, max_sequence: Optional[int] = None) -> Engine:
-    """Random weights drawn on the device (values differ from the ones `write_random_model` draws
-    on the host for the same seed)."""
+    """Random weights drawn on the device: the values `write_random_model` writes for the same seed,
+    bit for bit, without the detour through a file."""
     import torch
 
     device = require_cuda(device)

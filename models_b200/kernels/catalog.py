@@ -10,6 +10,7 @@ LIBRARIES = [
     ("mb_attention_rows", ["attention_rows.cu"], {}),
     ("mb_gemm_f32", ["gemm_f32.cu"], {}),
     ("mb_sampling", ["sampling.cu"], {}),
+    ("mb_random_init", ["random_init.cu"], {}),
     ("mb_skinny_gemm", ["skinny_gemm.cu"], {}),
     ("mb_gemm_tcgen05", ["gemm_tcgen05.cu"], {}),
     ("mb_wide_gemm_tcgen05", ["wide_gemm_tcgen05.cu"], {}),

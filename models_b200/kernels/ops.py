@@ -112,6 +112,22 @@ def sampling():
     return load_library("mb_sampling", ["sampling.cu"])
 
 
+def random_init():
+    return load_library("mb_random_init", ["random_init.cu"])
+
+
+def random_normal(out: torch.Tensor, key, mean: float, std: float) -> torch.Tensor:
+    """Fills `out` (contiguous float32 or bfloat16) with mean + std * z, z standard normal from the
+    counter-based generator keyed by `key` (two 32-bit words): the values of weights/philox_normal.py."""
+    _cuda(out)
+    if not out.is_contiguous():
+        raise KernelError("random_normal fills a contiguous tensor")
+    lib = random_init()
+    _run(lib, lib.mb_random_normal(_p(out), _code(out.dtype), ctypes.c_size_t(out.numel()), ctypes.c_uint32(key[0]),
+                                   ctypes.c_uint32(key[1]), ctypes.c_float(mean), ctypes.c_float(std), _stream()))
+    return out
+
+
 # ------------------------------------------------------------------------------------ element-wise
 
 def embed_gather(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0) -> torch.Tensor:

@@ -14,11 +14,13 @@ _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "norm": {},
     "position": {},
     "block": {},
+    "embedding": {},
+    "head": {},
 }
 
 
 def register_part(sort: str, kind: str, factory: Callable, replace: bool = False) -> None:
-    """`factory(spec, runtime)` builds the part.  sort: mixer, feed_forward, norm, position, block."""
+    """`factory(spec, runtime)` builds the part.  sort: mixer, feed_forward, norm, position, block, embedding, head."""
     if sort not in _REGISTRIES:
         raise ValueError(f"unknown sort of part {sort!r}; known: {', '.join(_REGISTRIES)}")
     if kind in _REGISTRIES[sort] and not replace:

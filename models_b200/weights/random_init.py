@@ -4,12 +4,11 @@ seed.
 integrallis/models builds such models only in its tests (a seeded nano model,
 models-test/.../NanoGgufModel.java:42-49,91); here it is a product feature so that benchmarks
 and tests need no checkpoint.  Each tensor's values depend on (seed, tensor name) only, not on the
-order in which tensors are drawn.
+order in which tensors are drawn nor on where (host or GPU) they are drawn.
 """
 
 from __future__ import annotations
 
-import hashlib
 import json
 from pathlib import Path
 from typing import Dict, Mapping
@@ -17,29 +16,32 @@ from typing import Dict, Mapping
 import torch
 
 from .loader import ParamRequest
+from .philox_normal import normal_float32, tensor_key
 from .safetensors_io import write_safetensors
-
-
-def _tensor_seed(seed: int, name: str) -> int:
-    digest = hashlib.sha256(f"{int(seed)}:{name}".encode("utf-8")).digest()
-    return int.from_bytes(digest[:8], "little") & 0x7FFF_FFFF_FFFF_FFFF
 
 
 def random_tensors(requests: Mapping[str, ParamRequest], seed: int, std: float = 0.02, gain_std: float = 0.1,
                    dtype: torch.dtype = torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
-    """Matrices and biases N(0, std); norm gains 1 + N(0, gain_std).  Drawn in float32, then
-    rounded to `dtype`."""
+    """Matrices and biases N(0, std); norm gains 1 + N(0, gain_std).  Drawn in float32, then rounded
+    to `dtype`.  Values come from a counter-based generator keyed by (seed, tensor name)
+    (weights/philox_normal.py): on a CUDA device a kernel draws them in place, on the host numpy does,
+    and both give the same bits."""
     out = {}
     device = torch.device(device)
     for name, request in requests.items():
-        generator = torch.Generator(device=device)
-        generator.manual_seed(_tensor_seed(seed, name))
-        values = torch.randn(tuple(request.shape), generator=generator, dtype=torch.float32, device=device)
-        if request.kind == "gain":
-            values = 1.0 + values * gain_std
+        key = tensor_key(seed, name)
+        mean, scale = (1.0, gain_std) if request.kind == "gain" else (0.0, std)
+        shape = tuple(request.shape)
+        count = 1
+        for n in shape:
+            count *= n
+        if device.type == "cuda":
+            from ..kernels import ops
+
+            out[name] = ops.random_normal(torch.empty(shape, dtype=dtype, device=device), key, mean, scale)
         else:
-            values = values * std
-        out[name] = values.to(dtype)
+            values = torch.from_numpy(normal_float32(count, key, mean, scale)).reshape(shape)
+            out[name] = values.to(dtype)
     return out
 
 

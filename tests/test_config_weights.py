@@ -177,3 +177,26 @@ def test_sharded_folder_with_index(tmp_path):
     (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
     loaded = load_tensors(tmp_path, requests)
     assert all(torch.equal(loaded[n], tensors[n]) for n in names)
+
+
+def test_random_values_are_normal_and_keyed_by_seed_and_name():
+    """The generator behind random-weights mode: standard normal moments, a value for every index
+    whatever the count (element i does not depend on how many are drawn), other values under another key."""
+    import numpy as np
+
+    from models_b200.weights.philox_normal import normal_float32, tensor_key
+
+    key = tensor_key(3, "model.embed_tokens.weight")
+    assert key == tensor_key(3, "model.embed_tokens.weight") and key != tensor_key(4, "model.embed_tokens.weight")
+    assert key != tensor_key(3, "model.norm.weight")
+    z = normal_float32(1_000_003, key, 0.0, 1.0).astype(np.float64)
+    assert abs(z.mean()) < 5e-3 and abs(z.std() - 1.0) < 5e-3
+    assert abs(((z - z.mean()) ** 3).mean()) < 2e-2  # skewness 0
+    assert abs(((z - z.mean()) ** 4).mean() / z.var() ** 2 - 3.0) < 5e-2  # kurtosis 3: tails as a normal's
+    assert np.isfinite(z).all() and z.max() > 4.0 and z.min() < -4.0
+    assert abs(np.corrcoef(z[:-1], z[1:])[0, 1]) < 5e-3  # the two values of a pair, and neighbours, are uncorrelated
+    short = normal_float32(1001, key, 0.0, 1.0)
+    assert np.array_equal(short, z[:1001].astype(np.float32))
+    shifted = normal_float32(1001, key, 1.0, 0.1)
+    assert np.array_equal(shifted, (short * np.float32(0.1) + np.float32(1.0)).astype(np.float32))
+    assert not np.array_equal(short, normal_float32(1001, tensor_key(3, "model.norm.weight"), 0.0, 1.0))

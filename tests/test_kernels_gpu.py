@@ -647,3 +647,45 @@ def test_wide_decode_gemm_all_epilogues(cuda_device, batch, n, k):
     assert gated.shape == (batch, n // 2)
     assert float((gated.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
     assert ops.gemm_tcgen05_status() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("count", [1, 3, 4, 1001, 262147])
+def test_random_weights_are_the_same_bits_on_host_and_device(cuda_device, dtype, count):
+    """The counter-based normal generator of random-weights mode: the device kernel and its numpy twin
+    evaluate the same polynomials with the same roundings."""
+    from models_b200.weights.philox_normal import normal_float32, tensor_key
+
+    from models_b200.kernels import ops
+
+    torch_dtype = dtype
+    for mean, std, name in ((0.0, 0.02, "a.weight"), (1.0, 0.1, "b.weight"), (0.0, 1.0, "c")):
+        key = tensor_key(count, name)
+        device = ops.random_normal(torch.empty(count, dtype=torch_dtype, device="cuda"), key, mean, std)
+        host = torch.from_numpy(normal_float32(count, key, mean, std)).to(torch_dtype)
+        assert torch.equal(device.cpu(), host), (count, name)
+
+
+def test_a_random_model_is_the_same_from_a_file_and_on_the_device(cuda_device, tmp_path):
+    """`engine_from_config` (weights drawn on the GPU) and `write_random_model` (drawn on the host, written,
+    read back) give one model: the same tensors, so the same logits."""
+    from models_b200.config import config_from_dict
+    from models_b200.engine import StepEntry
+    from models_b200.engine.loading import engine_from_config, engine_from_folder
+    from tiny import TINY_B, make_folder, random_tokens
+
+    folder = make_folder(TINY_B, 9, tmp_path)
+    from_file = engine_from_folder(folder, "bfloat16", 256)
+    on_device = engine_from_config(config_from_dict(TINY_B), 9, "bfloat16", 256)
+    assert torch.equal(from_file.model.embedding, on_device.model.embedding)
+    assert torch.equal(from_file.model.head_weight, on_device.model.head_weight)
+    assert torch.equal(from_file.model.final_norm.weight, on_device.model.final_norm.weight)
+    for a, b in zip(from_file.model.blocks, on_device.model.blocks):
+        assert torch.equal(a.mixer.w_qkv, b.mixer.w_qkv) and torch.equal(a.feed_forward.w_down, b.feed_forward.w_down)
+        assert torch.equal(a.mixer_norm.weight, b.mixer_norm.weight)
+    tokens = random_tokens(TINY_B["vocab_size"], 50, 1)
+    outs = []
+    for engine in (from_file, on_device):
+        slot = engine.open_slot()
+        outs.append(engine.step([StepEntry(slot, tokens, [49])]))
+    assert torch.equal(outs[0], outs[1])
