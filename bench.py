@@ -14,6 +14,7 @@ do not find their inputs in the cache.
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -222,23 +223,33 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False, prompt=PROMP
         sampler.start()
     kv_total = 0
     launches_before = ops.launch_count()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]  # one after every step, on the step's stream
     torch.cuda.synchronize()
-    start.record()
-    for _ in range(steps):
+    marks[0].record()
+    for step in range(steps):
         kv_total += sum(engine.length(s) + 1 for s in slots)
         logits = stepper.decode_pending(slots, pending, rows)
         pending.result()
         pending = stepper.sample_start(logits, greedy)
-    end.record()
+        marks[step + 1].record()
     torch.cuda.synchronize()
-    seconds = start.elapsed_time(end) / 1e3
+    seconds = marks[0].elapsed_time(marks[-1]) / 1e3
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
     launches = ops.launch_count() - launches_before
     clocks = sampler.stop() if sampler else None
     for s in slots:
         engine.release_slot(s)
     return {"seconds": seconds, "tokens_per_second": batch * steps / seconds, "ms_per_step": 1e3 * seconds / steps,
+            "ms_per_step_p50": percentile(per_step, 0.50), "ms_per_step_p95": percentile(per_step, 0.95),
             "kv_tokens_per_step": kv_total / steps, "launches": launches, "clocks": clocks}
+
+
+def percentile(ordered, fraction):
+    """Nearest-rank percentile of an ascending list (integrallis/models, models-bench/.../BenchmarkStatistics.java:35-59)."""
+    if not ordered:
+        return None
+    rank = max(1, -(-int(round(fraction * 1000)) * len(ordered) // 1000))
+    return ordered[min(len(ordered), rank) - 1]
 
 
 def e2e_decode(model, batch, steps, warmup, prompt=PROMPT_TOKENS):
@@ -254,16 +265,22 @@ def e2e_decode(model, batch, steps, warmup, prompt=PROMPT_TOKENS):
         if index == 0:
             stamps.append(time.perf_counter())
 
-    model.generate_batch(prompts, SamplingOptions(temperature=0.0, max_tokens=warmup + 1))  # warm-up
-    model.generate_batch(prompts, SamplingOptions(temperature=0.0, max_tokens=steps + 1), on_token=on_token)
+    first = model.generate_batch(prompts, SamplingOptions(temperature=0.0, max_tokens=warmup + 1))  # warm-up
+    results = model.generate_batch(prompts, SamplingOptions(temperature=0.0, max_tokens=steps + 1), on_token=on_token)
     seconds = stamps[-1] - stamps[0]
+    # what was generated, as a hash (integrallis/models prints one per run, models-bench/.../SessionBatchProfileCli.java:287-293),
+    # and whether the warm-up run -- the same prompts, fewer tokens -- produced the same ids as far as it went
+    digest = hashlib.sha256()
+    for result in results:
+        digest.update(",".join(str(t) for t in result.tokens).encode() + b";")
+    repeated = all(a.tokens == b.tokens[: len(a.tokens)] for a, b in zip(first, results))
     graphs = model.engine.decode_graphs
     h2d = 0  # the step's indices; the ids themselves stay on the device
     if graphs and graphs.captured:
         layout = next(c for (size, _), c in graphs.captured.items() if size == graphs.rung(batch)).layout
         h2d = 4 * (layout.total - layout.tokens)
     return {"tokens_per_second": batch * (len(stamps) - 1) / seconds, "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": 4 * batch}
+            "d2h_bytes_per_step": 4 * batch, "tokens_hash": digest.hexdigest()[:16], "repeated": repeated}
 
 
 def device_prefill(model, tokens, repeats=3):
@@ -353,12 +370,17 @@ def main() -> int:
         "steps": steps,
         "warmup": warmup,
         "ms_per_step": main_run["ms_per_step"],
+        "ms_per_step_p50": main_run["ms_per_step_p50"],
+        "ms_per_step_p95": main_run["ms_per_step_p95"],
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic: seeded uniform-random token ids, random weights N(0, 0.02)",
         "impl": "ours",
+        "gpu": torch.cuda.get_device_name(0),
+        "tokens_hash": e2e["tokens_hash"],
+        "tokens_repeat_the_warmup_run": e2e["repeated"],
         "config": {
             "model": work["name"],
             "layers": layers,

@@ -1,12 +1,13 @@
 """The cache: a slot per sequence, keys and values per layer run, each sequence with its own length.
 
-Runs of the schedule whose mixers need the same thing (kv heads, head size, retention: all keys or
-a window of them) form a group; every group has storage and a page table of its own.  Storage of a
-group is one tensor [runs, 2 (keys, values), pages, kv_heads, page_size, head_dim]; a sequence holds
-whole pages of `page_size` positions, and `block_table[i]` names the page with positions
-[i*page_size, (i+1)*page_size).  A window group gives pages back as soon as no later query can see
-them.  Page 0 of every group is never handed out: padding rows of a fixed-size decode batch point
-at it.
+Runs of the schedule whose mixers need the same thing (kv heads, key and value head sizes, retention:
+all keys or a window of them) form a group; every group has storage, a page pool and a page table of
+its own.  Storage of a group is two tensors, keys [runs, pages, kv_heads, page_size, key size] and
+values [runs, pages, kv_heads, page_size, value size]; a sequence holds whole pages of `page_size`
+positions, and `block_table[i]` names the page with positions [i*page_size, (i+1)*page_size).  A
+window group gives pages back as soon as no later query can see them, and when the engine states
+the longest step it will be given, such a group is made with only the pages its window can hold.
+Page 0 of every group is never handed out: padding rows of a fixed-size decode batch point at it.
 
 integrallis/models' model for groups with different needs is LayeredKvCache, with a LayerSpec
 (keyDim, valueDim, LINEAR | RING, ringCapacity) per layer
@@ -31,11 +32,18 @@ PAGE_SIZE = 64
 @dataclass(frozen=True)
 class KvRequest:
     """What one attention-like mixer needs of the cache.  window None: every earlier position
-    stays; n: only the n positions that end at the newest query."""
+    stays; n: only the n positions that end at the newest query.  `head_dim` is the size of a key
+    head; a value head has `value_dim` (None: the same), as the reference's LayerSpec keeps keyDim and
+    valueDim apart (backend-java/.../cache/LayeredKvCache.java:35-64)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+
+    @property
+    def value_head_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 class CacheGroup:
@@ -46,7 +54,8 @@ class CacheGroup:
         self.num_pages = num_pages  # usable pages; storage has one more (page 0, padding)
         self.pages = FreeList(num_pages, first=1, what="cache page")
         self.tables: Dict[int, List[int]] = {}  # slot -> page per block, -1 where given back
-        self.storage = None  # [runs, 2, num_pages + 1, kv_heads, page_size, head_dim]
+        self.keys = None    # [runs, num_pages + 1, kv_heads, page_size, key head size]
+        self.values = None  # [runs, num_pages + 1, kv_heads, page_size, value head size]
 
     def run_index(self, run: int) -> int:
         return self.runs.index(run)
@@ -103,11 +112,16 @@ class KvCache:
     `requests[i]` is what run i of the schedule asks for (None: that run keeps no keys and values);
     `cache_from[i]` names the earlier run whose storage run i reads instead of owning some.
     `max_tokens` is the most positions that live sequences hold at any time, each sequence's count
-    rounded up to whole pages; every group gets that many positions.
+    rounded up to whole pages; a group that keeps every position gets that many.  A window group
+    needs, per sequence, the pages that hold its window and the tokens of the step in flight (a step's
+    keys are all stored before any page is given back): with `max_step_tokens` (the most tokens a step
+    brings to one sequence; the caller must then refuse longer steps) it gets
+    max_slots x (pages of window - 1 + max_step_tokens, and one more for the page boundary), if that is
+    less; without it, as many as the other groups.
     """
 
     def __init__(self, requests: Sequence[Optional[KvRequest]], cache_from: Sequence[Optional[int]], max_tokens: int,
-                 max_slots: Optional[int] = None, page_size: int = PAGE_SIZE):
+                 max_slots: Optional[int] = None, page_size: int = PAGE_SIZE, max_step_tokens: Optional[int] = None):
         if page_size <= 0 or page_size % 32:
             raise ValueError(f"page_size must be a positive multiple of 32, got {page_size}")
         if max_tokens <= 0:
@@ -132,7 +146,7 @@ class KvCache:
                 continue
             group = by_key.get(request)
             if group is None:
-                group = CacheGroup(request, [], self.num_pages, page_size)
+                group = CacheGroup(request, [], self.pages_for(request, max_step_tokens), page_size)
                 by_key[request] = group
                 self.groups.append(group)
             group.runs.append(run)
@@ -144,32 +158,45 @@ class KvCache:
                 raise ValueError(f"run {run} reads the cache of run {source}, which stores none")
             owner = self.groups[self.run_location[source][0]].request
             mine = requests[run]
-            if (owner.num_kv_heads, owner.head_dim) != (mine.num_kv_heads, mine.head_dim):
+            if ((owner.num_kv_heads, owner.head_dim, owner.value_head_dim) !=
+                    (mine.num_kv_heads, mine.head_dim, mine.value_head_dim)):
                 raise ValueError(
                     f"run {run} reads the cache of run {source} but asks for {mine.num_kv_heads} kv heads of "
-                    f"{mine.head_dim}, the owner stores {owner.num_kv_heads} of {owner.head_dim}")
+                    f"{mine.head_dim} (values {mine.value_head_dim}), the owner stores {owner.num_kv_heads} of "
+                    f"{owner.head_dim} (values {owner.value_head_dim})")
             self.run_location[run] = self.run_location[source]
 
     # ---------------------------------------------------------------- storage
 
+    def pages_for(self, request: KvRequest, max_step_tokens: Optional[int]) -> int:
+        """Usable pages of the group of `request`."""
+        if request.window is None or max_step_tokens is None:
+            return self.num_pages
+        if max_step_tokens <= 0:
+            raise ValueError(f"max_step_tokens must be positive, got {max_step_tokens}")
+        # positions a sequence holds at most while a step is in flight, wherever they start in a page
+        per_slot = -(-(request.window - 1 + max_step_tokens) // self.page_size) + 1
+        return min(self.num_pages, self.max_slots * per_slot)
+
     def allocate_storage(self, allocate: Callable[[Tuple[int, ...]], object]) -> int:
-        """Creates each group's tensor with `allocate(shape)`; returns the number of elements."""
+        """Creates each group's keys and values with `allocate(shape)`; returns the number of elements."""
         total = 0
         for group in self.groups:
             r = group.request
-            shape = (len(group.runs), 2, group.num_pages + 1, r.num_kv_heads, self.page_size, r.head_dim)
-            group.storage = allocate(shape)
-            n = 1
-            for s in shape:
-                n *= s
-            total += n
+            for name, width in (("keys", r.head_dim), ("values", r.value_head_dim)):
+                shape = (len(group.runs), group.num_pages + 1, r.num_kv_heads, self.page_size, width)
+                setattr(group, name, allocate(shape))
+                n = 1
+                for s in shape:
+                    n *= s
+                total += n
         return total
 
     def pools(self, run: int):
-        """(group index, keys pool, values pool) of a run: [pages, kv_heads, page_size, head_dim] each."""
+        """(group index, keys pool, values pool) of a run: [pages, kv_heads, page_size, key or value head size]."""
         g, i = self.run_location[run]
-        storage = self.groups[g].storage
-        return g, storage[i, 0], storage[i, 1]
+        group = self.groups[g]
+        return g, group.keys[i], group.values[i]
 
     # ---------------------------------------------------------------- slots
 
@@ -219,7 +246,9 @@ class KvCache:
             if need > group.pages.free:
                 raise CacheFull(
                     f"the step needs {need} more cache pages of {self.page_size} positions, {group.pages.free} are free "
-                    f"(the cache was sized for {self.num_pages * self.page_size} positions)")
+                    f"(the cache was sized for {self.num_pages * self.page_size} positions"
+                    + (f"; this group keeps a window of {group.request.window} and has {group.num_pages} pages)"
+                       if group.num_pages != self.num_pages else ")"))
 
     def append(self, appends: Sequence[Tuple[int, int]]) -> None:
         """Makes room for n more positions in each (slot, n).  Checks everything first: on CacheFull

@@ -304,6 +304,11 @@ class LlamaConfig:
             head=HeadSpec(self.vocab_size, self.hidden_size, self.tie_word_embeddings, head_names),
             stop_token_ids=self.eos_token_ids,
             bos_token_id=self.bos_token_id,
+            # older exports store the rotation frequencies as a buffer; they are recomputed from the configuration
+            ignored_tensors=("*.rotary_emb.inv_freq",),
+            # a tied model whose file also stores the output matrix: fine if it repeats the embedding table, an
+            # error if the two disagree (backend-java/.../llama/LlamaWeights.java:83-89 ties by absence)
+            duplicate_tensors={"lm_head.weight": "model.embed_tokens.weight"} if self.tie_word_embeddings else {},
         )
 
 

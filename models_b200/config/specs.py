@@ -145,6 +145,11 @@ class ModelSpec:
     head: HeadSpec
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
+    # Tensors a checkpoint of this architecture may hold that the model does not read: name patterns
+    # (fnmatch) of buffers that are recomputed, and names that must repeat another tensor exactly (a
+    # tied model's stored output matrix).  Anything else that is not asked for is an error.
+    ignored_tensors: Tuple[str, ...] = ()
+    duplicate_tensors: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
 
     def __post_init__(self):
         if not self.layers:

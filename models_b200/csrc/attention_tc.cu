@@ -16,161 +16,13 @@
 // head / group; dot first, then scale; only positions <= the query's are read; with a window of n
 // only the n positions that end at the query) and backend-java/.../ops/TensorOps.java:1247-1279
 // (softmax), here in its running form.  Probabilities are rounded to bfloat16 for the P.V product.
-#include "common.cuh"
+#include "attention_tiles.cuh"
 
 #include <cooperative_groups.h>
-#include <math_constants.h>
-
-#ifndef MB_HEAD_DIM
-#error "compile with -DMB_HEAD_DIM=<head size>"
-#endif
 
 MB_DEFINE_LAST_ERROR()
 
 namespace mb {
-
-constexpr int HD = MB_HEAD_DIM;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in 16..256");
-constexpr int kTile = 64;                 // keys per tile, one cache page
-constexpr int kRowBytes = HD * 2 + 16;    // padded shared-memory row
-constexpr int kTileBytes = kTile * kRowBytes;
-constexpr int kChunks = HD / 8;           // 16-byte pieces of a row
-constexpr int kKSteps = HD / 16;
-constexpr int kThreads = 128;
-constexpr int kQRowsDecode = 16;
-// Pages of keys and values in shared memory per decode block: two or three, chosen at launch (mb_decode_stages; six for
-// a few blocks over long contexts, see decode_stages).
-// A third stage helps where a block has only a few pages -- all of them are then in flight at once; with four blocks
-// of three stages per sequence, batch 8 of the 1B model gains 2 % over eight blocks of two -- and at head sizes of 96
-// and more (64 sequences of 1,280 positions at head size 128: 4.3 -> 5.2 TB/s).  With heads of 64 and long loops it
-// costs a resident block per multiprocessor and loses (batch 64: 49.7 -> 46.6 k tokens/s), and eight blocks of three
-// stages per sequence no longer fit one round at batch 8 (9.2 -> 8.3 k tokens/s).
-constexpr int kQRowsPrefill = 64;
-
-using bf16 = __nv_bfloat16;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// One page of one kv head -> a padded tile in shared memory (all threads of the block).
-__device__ __forceinline__ void load_tile(uint32_t dst, const bf16* __restrict__ pool, size_t page, int kv_head,
-                                          int kv_heads) {
-    const bf16* src = pool + (page * kv_heads + kv_head) * (size_t)(kTile * HD);
-    static_assert((kTile * kChunks) % kThreads == 0, "every thread copies the same number of pieces");
-#pragma unroll
-    for (int j = 0; j < kTile * kChunks / kThreads; ++j) {  // (unrolled: the offsets are the same for every page)
-        const int i = threadIdx.x + j * kThreads;
-        const int row = i / kChunks, chunk = i % kChunks;
-        cp_async16(dst + row * kRowBytes + chunk * 16, src + row * HD + chunk * 8);
-    }
-}
-
-// The 16 rows of a page that one decode warp works on (rows 16 * warp ...), copied by that warp alone: what a warp
-// reads it has fetched itself, so the warps of a block need no barrier between pages.
-__device__ __forceinline__ void load_tile_rows(uint32_t dst, const bf16* __restrict__ pool, size_t page, int kv_head,
-                                               int kv_heads, int warp, int lane) {
-    const bf16* src = pool + (page * kv_heads + kv_head) * (size_t)(kTile * HD) + (size_t)warp * 16 * HD;
-    dst += warp * 16 * kRowBytes;
-#pragma unroll
-    for (int j = 0; j < 16 * kChunks / 32; ++j) {
-        const int i = lane + j * 32;
-        const int row = i / kChunks, chunk = i % kChunks;
-        cp_async16(dst + row * kRowBytes + chunk * 16, src + row * HD + chunk * 8);
-    }
-}
-
-// Rows of queries -> padded rows in shared memory; rows >= valid are zero.
-__device__ __forceinline__ void load_queries(unsigned char* dst, const bf16* __restrict__ q_first_row, size_t row_stride,
-                                             int rows, int valid) {
-    for (int i = threadIdx.x; i < rows * kChunks; i += kThreads) {
-        const int row = i / kChunks, chunk = i % kChunks;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (row < valid) v = *reinterpret_cast<const uint4*>(q_first_row + (size_t)row * row_stride + chunk * 8);
-        *reinterpret_cast<uint4*>(dst + row * kRowBytes + chunk * 16) = v;
-    }
-}
-
-// Query fragments of one warp's 16 rows for every 16-wide step over the head.
-__device__ __forceinline__ void load_q_fragments(uint32_t (&a)[kKSteps][4], uint32_t q_rows_base) {
-    const int lane = threadIdx.x & 31;
-    const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
-#pragma unroll
-    for (int ks = 0; ks < kKSteps; ++ks) ldmatrix_x4(a[ks], q_rows_base + row * kRowBytes + (ks * 2 + (lane >> 4)) * 16);
-}
-
-// S[16 x 16 keys] for keys key0..key0+15 of a tile: two 8-key accumulators.
-__device__ __forceinline__ void scores_16_keys(float (&s)[2][4], const uint32_t (&a)[kKSteps][4], uint32_t k_tile, int key0) {
-    const int lane = threadIdx.x & 31;
-    const int key = key0 + (lane & 7) + ((lane >> 4) & 1) * 8;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) s[0][i] = s[1][i] = 0.0f;
-#pragma unroll
-    for (int ks = 0; ks < kKSteps; ++ks) {
-        uint32_t b[4];
-        ldmatrix_x4(b, k_tile + key * kRowBytes + (ks * 2 + ((lane >> 3) & 1)) * 16);
-        mma_bf16(s[0], a[ks], b[0], b[1]);
-        mma_bf16(s[1], a[ks], b[2], b[3]);
-    }
-}
-
-// O[16 x HD] += P[16 x 16 keys] . V[16 keys x HD]
-__device__ __forceinline__ void accumulate_16_keys(float (&o)[HD / 8][4], const uint32_t (&p)[4], uint32_t v_tile, int key0) {
-    const int lane = threadIdx.x & 31;
-    const int key = key0 + (lane & 7) + ((lane >> 3) & 1) * 8;
-#pragma unroll
-    for (int dp = 0; dp < HD / 16; ++dp) {
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, v_tile + key * kRowBytes + (dp * 2 + (lane >> 4)) * 16);
-        mma_bf16(o[2 * dp], p, b[0], b[1]);
-        mma_bf16(o[2 * dp + 1], p, b[2], b[3]);
-    }
-}
-
-// 2^x by the special-function unit (about two units in the last place; the probabilities it feeds are
-// rounded to bfloat16 afterwards).  2^-inf = 0.
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ float quad_max(float v) {
-    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
-    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-}
-__device__ __forceinline__ float quad_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    return v + __shfl_xor_sync(0xffffffffu, v, 2);
-}
 
 // ------------------------------------------------------------------------------------------ decode
 
@@ -613,14 +465,23 @@ MB_EXPORT int mb_decode_stages(int splits) { return (HD >= 96 || splits >= 4) ? 
 // shared memory is worth more as room for further blocks (8 sequences of 65,536 positions: 195 us with three
 // stages, 242 us with six), and pages of wider heads gain nothing from a deeper ring.
 constexpr int kLongStages = HD <= 64 ? 6 : 3;
-static int decode_stages(int splits, long blocks) {
-    static int multiprocessors = 0;
-    if (!multiprocessors) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&multiprocessors, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-            multiprocessors = 148;
-    }
-    if (splits > 8 && blocks <= 2L * multiprocessors) return kLongStages;
+constexpr int kMaxDevices = 64;  // per-device facts below are kept for devices 0..63
+
+// The current device, or -1 (with the message set) when it cannot be told or lies beyond the per-device tables.
+static int current_device(const char* what) {
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) { fail("%s: cudaGetDevice: %s", what, cudaGetErrorString(status)); return -1; }
+    if (device < 0 || device >= kMaxDevices) { fail("%s: device %d is outside 0..%d", what, device, kMaxDevices - 1); return -1; }
+    return device;
+}
+
+static int decode_stages(int splits, long blocks, int device) {
+    static int multiprocessors[kMaxDevices] = {0};  // of each device, asked once
+    if (!multiprocessors[device] &&
+        cudaDeviceGetAttribute(&multiprocessors[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        multiprocessors[device] = 1;  // unknown: the deep ring only for a handful of blocks
+    if (splits > 8 && blocks <= 2L * multiprocessors[device]) return kLongStages;
     return mb_decode_stages(splits);
 }
 MB_EXPORT size_t mb_decode_block_bytes(int stages) { return decode_smem(stages); }
@@ -640,8 +501,11 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     const int group = heads / kv_heads;
     const int head_chunks = (group + 15) / 16;
     if (sequences > 65535 || kv_heads * head_chunks > 65535) return fail("decode_attention: grid too large");
-    const int stages = decode_stages(splits, (long)splits * kv_heads * head_chunks * sequences);
-    static bool configured = false;
+    const int device = current_device("decode_attention");
+    if (device < 0) return 1;
+    const int stages = decode_stages(splits, (long)splits * kv_heads * head_chunks * sequences, device);
+    static bool configured_devices[kMaxDevices] = {false};  // the attribute is a device's, not the process's
+    bool& configured = configured_devices[device];
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
         if (status == cudaSuccess)
@@ -704,7 +568,10 @@ MB_EXPORT int mb_prefill_attention(const void* q, int q_row_stride, void* out, i
     if (sequences <= 0 || max_q_len <= 0) return 0;
     if (int status = check_common("prefill_attention", heads, kv_heads, page_size, q_row_stride, out_row_stride, q, out)) return status;
     if (sequences > 65535 || heads > 65535) return fail("prefill_attention: grid too large");
-    static bool configured = false;
+    const int device = current_device("prefill_attention");
+    if (device < 0) return 1;
+    static bool configured_devices[kMaxDevices] = {false};
+    bool& configured = configured_devices[device];
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(prefill_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem());
         if (status != cudaSuccess) return fail("prefill_attention: cannot reserve %zu bytes of shared memory: %s", prefill_smem(), cudaGetErrorString(status));
@@ -732,14 +599,14 @@ MB_EXPORT int mb_prefill_attention(const void* q, int q_row_stride, void* out, i
 // The array's name is usable in device code only; host code sees a stand-in for it, not a device
 // address.  So the entry point asks the runtime for the address once per device, with that device
 // current (cudaGetSymbolAddress), keeps it, and hands it to the kernels.  The first call on a
-// device does this set-up; make that first call outside any stream capture.
+// device does this set-up; make that first call outside any stream capture, and from one thread:
+// the per-device tables are plain statics, so two first calls on one device must not run at once.
 //
 // Every call uses the same array, and it keeps what the last call left.  Nothing in it has to be
 // zero at the start: each block writes its (maximum, sum) pair, and a partial output is read only
 // where that pair says the block saw keys.  Two calls that overlap on the GPU (different streams,
 // no ordering between them) race on the array; order them.
 constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB
-constexpr int kMaxDevices = 64;
 static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats];
 static float* g_static_scratch_address[kMaxDevices] = {nullptr};
 
@@ -756,13 +623,11 @@ MB_EXPORT int mb_decode_attention_static(const void* q, int q_row_stride, void* 
         return fail("decode_attention_static: %d sequences x %d heads x %d splits need %zu floats of scratch, the built-in "
                     "array holds %zu; use fewer splits or mb_decode_attention with scratch of your own",
                     sequences, heads, splits, need, (size_t)kStaticScratchFloats);
-    int device = -1;
-    cudaError_t status = cudaGetDevice(&device);
-    if (status != cudaSuccess) return fail("decode_attention_static: cudaGetDevice: %s", cudaGetErrorString(status));
-    if (device < 0 || device >= kMaxDevices) return fail("decode_attention_static: device %d is outside 0..%d", device, kMaxDevices - 1);
+    const int device = current_device("decode_attention_static");
+    if (device < 0) return 1;
     if (!g_static_scratch_address[device]) {
         float* address = nullptr;
-        status = cudaGetSymbolAddress((void**)&address, g_static_decode_scratch);
+        cudaError_t status = cudaGetSymbolAddress((void**)&address, g_static_decode_scratch);
         if (status != cudaSuccess || !address)
             return fail("decode_attention_static: cudaGetSymbolAddress on device %d: %s", device, cudaGetErrorString(status));
         g_static_scratch_address[device] = address;

@@ -262,11 +262,23 @@ __global__ void rope_cache_write_vec8_kernel(T* __restrict__ qkv, int row_stride
     }
 }
 
+// ------------------------------------------------------------------------------------ logits
+
+__global__ void logit_epilogue_kernel(float* __restrict__ logits, int ld, int vocab, size_t total, float scale, float softcap) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float* at = logits + (i / vocab) * ld + (i % vocab);
+        float value = *at * scale;
+        if (softcap != 0.0f) value = softcap * tanhf(value / softcap);
+        *at = value;
+    }
+}
+
 // ------------------------------------------------------------------------------------ gated activation
 
 // gate_up: [rows, 2*width] with the gate in columns [0, width) and up in [width, 2*width).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total, int activation) {
     grid_launch_dependents();
     grid_dependency_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -274,14 +286,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
         const size_t row = i / width, col = i % width;
         const float g = Num<T>::load(gate_up + row * 2 * width + col);
         const float u = Num<T>::load(gate_up + row * 2 * width + width + col);
-        const float silu = g / (1.0f + expf(-g));
-        Num<T>::store(out + i, silu * u);
+        Num<T>::store(out + i, gate_activation(activation, g) * u);
     }
 }
 
 // Eight elements per thread; width a multiple of 8, rows 16-byte (bf16) or 32-byte (float) aligned.
 template <typename T>
-__global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total8) {
+__global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width, size_t total8, int activation) {
     grid_launch_dependents();
     grid_dependency_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -292,7 +303,7 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gate_up, T* __restrict_
         load8(gate_up + row * 2 * width + col, g);
         load8(gate_up + row * 2 * width + width + col, u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) r[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+        for (int j = 0; j < 8; ++j) r[j] = gate_activation(activation, g[j]) * u[j];
         store8(out + row * width + col, r);
     }
 }
@@ -439,28 +450,39 @@ MB_EXPORT int mb_rope_cache_write(void* qkv, int dtype, int row_stride, const in
     return fail("rope_cache_write: unknown dtype code %d", dtype);
 }
 
-MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int dtype, int rows, int width, cudaStream_t stream) {
+// out [rows, width] = act(gate) * up for gate_up [rows, 2 * width]; activation: MB_ACT_*.
+MB_EXPORT int mb_swiglu(const void* gate_up, void* out, int dtype, int rows, int width, int activation, cudaStream_t stream) {
     const size_t total = (size_t)rows * width;
     if (total == 0) return 0;
+    if (activation < 0 || activation >= MB_ACT_COUNT) return fail("swiglu: unknown gate activation code %d", activation);
     if (width % 8 == 0 && !((uintptr_t)gate_up & 31) && !((uintptr_t)out & 31)) {
         const size_t total8 = total / 8;
         const size_t blocks = (total8 + 255) / 256;
         const int grid = (int)(blocks > 148 * 32 ? 148 * 32 : blocks);
         if (dtype == MB_F32)
             return launch_dependent("swiglu", swiglu_vec8_kernel<float>, dim3(grid), dim3(256), 0, stream, true, (const float*)gate_up,
-                                    (float*)out, width, total8);
+                                    (float*)out, width, total8, activation);
         if (dtype == MB_BF16)
             return launch_dependent("swiglu", swiglu_vec8_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, true,
-                                    (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total8);
+                                    (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total8, activation);
         return fail("swiglu: unknown dtype code %d", dtype);
     }
     if (dtype == MB_F32)
-        swiglu_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, width, total);
+        swiglu_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, width, total, activation);
     else if (dtype == MB_BF16)
-        swiglu_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total);
+        swiglu_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total, activation);
     else
         return fail("swiglu: unknown dtype code %d", dtype);
     return check_launch("swiglu");
+}
+
+// logits = logits * scale; with softcap c != 0 then c * tanh(logits / c)
+// (integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1751-1764).  In place, float32.
+MB_EXPORT int mb_logit_epilogue(float* logits, int ld, int rows, int vocab, float scale, float softcap, cudaStream_t stream) {
+    const size_t total = (size_t)rows * vocab;
+    if (total == 0) return 0;
+    logit_epilogue_kernel<<<grid_for(total, 256), 256, 0, stream>>>(logits, ld, vocab, total, scale, softcap);
+    return check_launch("logit_epilogue");
 }
 
 MB_EXPORT int mb_bias_add(void* x, int dtype, const float* bias, int rows, int width, cudaStream_t stream) {

@@ -117,6 +117,8 @@ struct GemmArgs {
     int up_row_offset;    // EPI_SWIGLU: first up row of W
     int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int k_splits;         // EPI_RESIDUAL: blocks that share an output tile, each with its own part of K (else 1)
+    float* partial;       // k_splits > 1: [tile][block of a pair][part of K][128 rows][tile columns] floats, or null
+    int* tickets;         // k_splits > 1 with `partial`: [tile][block of a pair][8 epilogue warps], zero before and after a launch
     void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream; EPI_ROPE: the queries [m, heads * head_dim]
     int ld_out;
     // EPI_ROPE: W is [q heads; k heads; v heads]
@@ -287,6 +289,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + acc * kAccumulatorColumns + ((uint32_t)(quarter * 32) << 16);
             const int n0 = n_tile * kOutCols;
+            // with K in parts and scratch given, the parts are summed in their order (see below)
+            const int mn_tile = tile / k_splits;
+            const bool ordered = EPI == EPI_RESIDUAL && k_splits > 1 && args.partial != nullptr;
+            float* my_partial = ordered ? args.partial + ((size_t)(mn_tile * kPair + rank) * k_splits + tile % k_splits) * (kBlockM * kOutCols)
+                                        : nullptr;
             if (EPI == EPI_ROPE) {
                 // Whole heads lie inside this warp's half of the tile (head size 64 or 128).  Per head: the
                 // coordinates d and d + head/2 are a rotation pair (x0' = x0*c - x1*s, x1' = x0*s + x1*c,
@@ -400,10 +407,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (kWide) {
                             float* dst = reinterpret_cast<float*>(args.out) + (size_t)out_row * args.ld_out + col;
                             const float v[4] = {__uint_as_float(value.x), __uint_as_float(value.y), __uint_as_float(value.z), __uint_as_float(value.w)};
-                            if (col + 4 <= args.n) {
+                            if (ordered) {
+                                // this part of K goes to scratch; the sum of the parts is taken below, in the order of the parts
+                                *reinterpret_cast<float4*>(my_partial + (size_t)(quarter * 32 + r) * kOutCols + c + (lane & 7) * 4) =
+                                    make_float4(v[0], v[1], v[2], v[3]);
+                            } else if (col + 4 <= args.n) {
                                 if (EPI == EPI_RESIDUAL) {
                                     // x += value without reading x here: the addition happens at the memory side.  Every
-                                    // element of x gets one such addition per product and part of K.
+                                    // element of x gets one such addition per product (and, unordered, per part of K).
                                     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3])
                                                  : "memory");
                                 } else {
@@ -437,6 +448,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (kPair == 2) mbar_arrive_leader(acc_empty_bar + 8 * acc);
                 else mbar_arrive(acc_empty_bar + 8 * acc);
             }
+            if (ordered) {
+                // The parts of K of this warp's rows and columns: whichever block's warp stores last adds all of
+                // them, in the order of the parts, and adds the sum into the stream -- the same additions in the
+                // same order whoever that is, so the result does not depend on timing.  Nobody waits.
+                __threadfence();
+                __syncwarp();
+                int* ticket_slot = args.tickets + (size_t)(mn_tile * kPair + rank) * kEpilogueWarps + (warp - 2);
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(ticket_slot, 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == k_splits - 1) {
+                    __threadfence();
+                    if (lane == 0) *ticket_slot = 0;  // as the next launch expects it
+                    const float* parts = args.partial + (size_t)(mn_tile * kPair + rank) * k_splits * (kBlockM * kOutCols);
+#pragma unroll 1
+                    for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 32) {
+                        const int col = n0 + c + (lane & 7) * 4;
+#pragma unroll 1
+                        for (int pass = 0; pass < 8; ++pass) {
+                            const int r = 4 * pass + (lane >> 3);
+                            const int out_row = m0 + quarter * 32 + r;
+                            if (out_row >= args.m || col >= args.n) continue;
+                            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                            const float* at = parts + (size_t)(quarter * 32 + r) * kOutCols + c + (lane & 7) * 4;
+                            for (int part = 0; part < k_splits; ++part) {
+                                const float4 p = __ldcg(reinterpret_cast<const float4*>(at + (size_t)part * (kBlockM * kOutCols)));
+                                sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+                            }
+                            float* dst = reinterpret_cast<float*>(args.out) + (size_t)out_row * args.ld_out + col;
+                            if (col + 4 <= args.n) {
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(sum.x), "f"(sum.y), "f"(sum.z), "f"(sum.w)
+                                             : "memory");
+                            } else {
+                                const float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    if (col + i < args.n) dst[i] += v[i];  // the only addition into this element
+                            }
+                        }
+                    }
+                }
+            }
             if (++acc == 2) {
                 acc = 0;
                 acc_phase ^= 1;
@@ -457,8 +510,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // Few tiles and a long K (a prompt of a few hundred tokens; the down product above all): with the residual epilogue,
 // parts of K go to blocks of their own, at least 8 steps of 64 each and at most 8 parts, and every part adds its sum
-// to the residual stream.  The order in which the parts of an element arrive is not fixed, so its last bit may differ
-// from run to run.  Measured at 256 rows, K = 8192, N = 2048: 40 us as 16 tiles, 15 us as 8 parts each, 14 us for
+// to the residual stream.  Given scratch memory, every part stores its sum there and the block that stores last adds
+// the parts in their order (a ticket per tile and epilogue warp; nobody waits), so a result is the same bits in every
+// run; without scratch each part adds into the stream as it finishes, in no fixed order, and an element's last bit may
+// differ from run to run.  Measured at 256 rows, K = 8192, N = 2048: 40 us as 16 tiles, 15 us as 8 parts each, 14 us for
 // the library's kernel.  `units`: blocks (or pairs) that run at once.
 static int residual_k_splits(long tiles, int k, int units) {
     const int k_blocks = (k + kBlockK - 1) / kBlockK;
@@ -559,8 +614,20 @@ using namespace mb;
 // in bits 8 and up of `epilogue`.
 // tile_width: 0 lets the launcher choose between 128 and 256 output columns per tile; the gated epilogue takes 256.
 // pair: 2 runs tiles of 256 rows x 256 columns on pairs of blocks (tcgen05 cta_group::2); 1: one block per tile; 0: the launcher chooses.
+// Scratch that always suffices for the ordered sum of the parts of K (residual epilogue): K is split only while
+// tiles x parts stay within the blocks that run at once, so there are at most `multiprocessors` partial tiles of at
+// most 128 x 256 floats, and eight tickets for each.
+MB_EXPORT void mb_gemm_tcgen05_scratch(int multiprocessors, size_t* partial_floats, size_t* ticket_ints) {
+    *partial_floats = (size_t)multiprocessors * kBlockM * 256;
+    *ticket_ints = (size_t)multiprocessors * kEpilogueWarps;
+}
+
+// partial, tickets: scratch for the residual epilogue when K is split over blocks (mb_gemm_tcgen05_scratch says how much;
+// the tickets zero before the first launch that uses them -- every launch leaves them zero); with both null the parts of K
+// add into the stream as they finish, in no fixed order.
 MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ld_out, int m, int n_w, int k,
-                              int epilogue, int multiprocessors, int tile_width, int pair, cudaStream_t stream) {
+                              int epilogue, int multiprocessors, int tile_width, int pair, float* partial, int* tickets,
+                              cudaStream_t stream) {
     if (tile_width != 0 && tile_width != 128 && tile_width != 256) return fail("gemm_tcgen05: tile width %d is not built (128, 256)", tile_width);
     if (pair < 0 || pair > 2) return fail("gemm_tcgen05: pair must be 0, 1 or 2, got %d", pair);
     if (pair == 2 && tile_width == 128) return fail("gemm_tcgen05: pairs of blocks take tiles of 256 columns");
@@ -577,7 +644,9 @@ MB_EXPORT int mb_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, vo
     CUtensorMap map_a, map_w;
     if (int status = make_map(&map_a, a, m, k, lda)) return status;
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
-    GemmArgs args{m, n, k, n, activation, 1, out, ld_out, 0, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    GemmArgs args{};
+    args.m = m; args.n = n; args.k = k; args.up_row_offset = n; args.activation = activation; args.k_splits = 1;
+    args.partial = partial; args.tickets = tickets; args.out = out; args.ld_out = ld_out;
     switch (epilogue) {
         case EPI_BF16: return launch<EPI_BF16>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
         case EPI_F32: return launch<EPI_F32>(map_a, map_w, args, multiprocessors, tile_width, pair, stream);
@@ -608,8 +677,11 @@ MB_EXPORT int mb_gemm_tcgen05_qkv_rope(const void* a, int lda, const void* w, in
     CUtensorMap map_a, map_w;
     if (int status = make_map(&map_a, a, m, k, lda)) return status;
     if (int status = make_map(&map_w, w, n_w, k, ldw)) return status;
-    GemmArgs args{m, n_w, k, n_w, 1, q_out, ld_q, heads, kv_heads, head_dim, page_size, positions, slot_mapping, cos_table, sin_table,
-                  (bf16*)k_pool, (bf16*)v_pool};
+    GemmArgs args{};
+    args.m = m; args.n = n_w; args.k = k; args.up_row_offset = n_w; args.activation = MB_ACT_SILU; args.k_splits = 1;
+    args.out = q_out; args.ld_out = ld_q; args.heads = heads; args.kv_heads = kv_heads; args.head_dim = head_dim;
+    args.page_size = page_size; args.positions = positions; args.slot_mapping = slot_mapping; args.cos_table = cos_table;
+    args.sin_table = sin_table; args.k_pool = (bf16*)k_pool; args.v_pool = (bf16*)v_pool;
     if (pairs_are_faster(m, n_w, k, multiprocessors)) return launch_tile<EPI_ROPE, 256, 2>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI_ROPE, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }

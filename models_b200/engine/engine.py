@@ -20,6 +20,7 @@ from typing import Dict, List, Mapping, Optional, Sequence
 import torch
 
 from ..cache import KvCache, StateArea
+from ..cache.kv_cache import PAGE_SIZE
 from ..config.specs import ModelSpec
 from ..parts import RunContext, Runtime
 from .batch import build_step_batch
@@ -49,11 +50,24 @@ def require_cuda(device) -> torch.device:
 class Engine:
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype: str = "bfloat16",
                  max_tokens: int = 4096, max_slots: Optional[int] = None, device="cuda:0",
-                 max_sequence: Optional[int] = None):
+                 max_sequence: Optional[int] = None, max_step_tokens: Optional[int] = None,
+                 page_size: int = PAGE_SIZE):
+        """`max_tokens`: the most positions live sequences hold at any time, each rounded up to whole
+        pages.  `max_sequence`: a cap on one sequence's positions below the model's.  `max_step_tokens`:
+        the most tokens a step may bring to one sequence (None: no limit); stating it lets cache groups
+        that keep only a window of positions be made with the pages a window needs instead of
+        `max_tokens`.  `page_size`: positions per cache page; the tensor-core attention kernels tile the
+        cache in pages of 64, so the bfloat16 mode takes no other size."""
         self.device = require_cuda(device)
         torch.cuda.set_device(self.device)
         self.spec = spec
-        page_tokens = -(-max_tokens // 64) * 64
+        if dtype == "bfloat16" and page_size != PAGE_SIZE:
+            raise ValueError(f"the bfloat16 attention kernels read cache pages of {PAGE_SIZE} positions; page_size "
+                             f"{page_size} runs in the float32 mode only")
+        if max_step_tokens is not None and max_step_tokens <= 0:
+            raise ValueError(f"max_step_tokens must be positive, got {max_step_tokens}")
+        self.max_step_tokens = max_step_tokens
+        page_tokens = -(-max_tokens // page_size) * page_size
         longest = min(spec.max_positions, page_tokens)
         if max_sequence is not None:
             longest = min(longest, max(1, max_sequence))
@@ -61,7 +75,7 @@ class Engine:
         self.model = DecoderModel(spec, self.runtime)
         self.model.load(tensors)
         cache_from = [entry.cache_from for entry in spec.schedule]
-        self.cache = KvCache(self.model.kv_requests(), cache_from, max_tokens, max_slots)
+        self.cache = KvCache(self.model.kv_requests(), cache_from, max_tokens, max_slots, page_size, max_step_tokens)
         dtype_t = self.runtime.compute_dtype
         self.cache_elements = self.cache.allocate_storage(
             lambda shape: torch.zeros(shape, dtype=dtype_t, device=self.device))
@@ -126,6 +140,9 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"slot {e.slot}: a step must bring at least one token")
+            if self.max_step_tokens is not None and n > self.max_step_tokens:
+                raise StepError(f"slot {e.slot}: {n} tokens in one step exceed the engine's max_step_tokens of "
+                                f"{self.max_step_tokens}; bring them in several steps")
             for t in e.tokens:
                 if not 0 <= int(t) < vocab:
                     raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary of {vocab}")
@@ -225,7 +242,7 @@ class Engine:
             "dtype": self.runtime.mode,
             "architecture": self.spec.architecture,
             "cache_groups": len(self.cache.groups),
-            "cache_pages": self.cache.num_pages,
+            "cache_pages": [group.num_pages for group in self.cache.groups],
             "page_size": self.cache.page_size,
             "cache_bytes": self.cache_elements * element,
             "state_bytes": self.state.bytes,

@@ -20,7 +20,7 @@ def engine_from_folder(folder, dtype: str = "bfloat16", max_tokens: int = 4096, 
     require_cuda(device)
     config = load_config(folder)
     spec = config.model_spec()
-    tensors = load_tensors(folder, parameter_requests(spec))
+    tensors = load_tensors(folder, parameter_requests(spec), spec.ignored_tensors, spec.duplicate_tensors)
     engine = Engine(spec, tensors, dtype, max_tokens, max_slots, device, max_sequence)
     engine.config = config
     return engine

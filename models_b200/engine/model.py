@@ -1,6 +1,7 @@
 """The decoder put together from parts, as its ModelSpec says: embedding, the scheduled runs of
-blocks, final norm, output projection (integrallis/models' layer order:
-backend-java/.../llama/LlamaForwardPass.java:1024-1196).
+blocks, final norm, output head (integrallis/models' layer order:
+backend-java/.../llama/LlamaForwardPass.java:1024-1196).  Every piece, the embedding and the head
+included, is built from its spec through the registry of parts; this file knows none of them.
 """
 
 from __future__ import annotations
@@ -10,9 +11,7 @@ from typing import Callable, Dict, List, Mapping, Optional
 import torch
 
 from ..config.specs import ModelSpec
-from ..kernels import ops
 from ..parts import RunContext, Runtime, build_part
-from ..parts.linear import linear
 from ..weights.loader import ParamRequest, check_names_and_shapes
 
 
@@ -33,32 +32,32 @@ class DecoderModel:
         self.runtime = runtime
         self.blocks = [build_part("block", layer, runtime) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
-        self.embedding = None
-        self.head_weight = None
+        self.embedding = build_part("embedding", spec.embedding, runtime)
+        self.head = build_part("head", spec.head, runtime)
+        # when set, called with (run index, a copy of the float32 residual stream after that run), for
+        # finding the layer where two computations part (the reference's LayerObserver,
+        # backend-java/.../llama/LlamaForwardPass.java:44-47,1179-1181)
         self.observer: Optional[Callable[[int, torch.Tensor], None]] = None
 
     # ------------------------------------------------------------------ weights
 
     def parameters(self) -> Dict[str, ParamRequest]:
-        s = self.spec
-        requests = [ParamRequest(s.embedding.weights["weight"], (s.embedding.vocab_size, s.embedding.hidden_size))]
+        requests = list(self.embedding.parameters())
         for block in self.blocks:
             requests += block.parameters()
         requests += self.final_norm.parameters()
-        if not s.head.tied:
-            requests.append(ParamRequest(s.head.weights["weight"], (s.head.vocab_size, s.head.hidden_size)))
+        requests += self.head.parameters()
         return _collect(requests)
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         requests = self.parameters()
         check_names_and_shapes(requests, {n: tuple(t.shape) for n, t in tensors.items()}, "model tensors")
-        rt, s = self.runtime, self.spec
-        self.embedding = rt.matrix(tensors[s.embedding.weights["weight"]])
+        self.embedding.load(tensors)
         for block in self.blocks:
             block.load(tensors)
         self.final_norm.load(tensors)
         # tied output: the embedding matrix stands in (backend-java/.../llama/LlamaWeights.java:83-89)
-        self.head_weight = self.embedding if s.head.tied else rt.matrix(tensors[s.head.weights["weight"]])
+        self.head.load(tensors, tied_to=getattr(self.embedding, "weight", None) if self.spec.head.tied else None)
 
     # ------------------------------------------------------------------ cache needs
 
@@ -73,7 +72,7 @@ class DecoderModel:
     def forward(self, batch, runs: List[RunContext]) -> Optional[torch.Tensor]:
         """Runs the tokens of `batch` through every scheduled run and returns float32 logits at
         batch.want_rows ([rows, vocab]), or None when no row is wanted."""
-        x = ops.embed_gather(self.embedding, batch.tokens, self.spec.embedding.scale)
+        x = self.embedding.forward(batch.tokens)
         pending = None
         for run, entry in zip(runs, self.spec.schedule):
             pending = self.blocks[entry.layer].forward(x, pending, batch, run)
@@ -81,13 +80,7 @@ class DecoderModel:
                 self.observer(run.run, x + pending.float() if pending is not None else x.clone())
         if batch.num_wanted == 0:
             return None
-        if (pending is None and self.runtime.mode == "bfloat16" and getattr(self.final_norm, "foldable", False)
-                and ops.skinny_pays(self.head_weight, batch.num_wanted, with_norm=True)):
-            # few wanted rows: gather, final norm and output product in one kernel
-            return ops.skinny_gemm(self.head_weight, ops.EPI_F32, xf=x, gain=self.final_norm.weight,
-                                   eps=self.final_norm.spec.eps, rows=batch.want_rows)
-        xn = self.final_norm.forward(x, pending, rows=batch.want_rows)
-        return linear(xn, self.head_weight, torch.float32)
+        return self.head.forward(x, pending, self.final_norm, batch.want_rows)
 
 
 def parameter_requests(spec: ModelSpec) -> Dict[str, ParamRequest]:

@@ -7,7 +7,6 @@ library that cannot be built, raises.
 from __future__ import annotations
 
 import ctypes
-import os
 from typing import Optional
 
 import torch
@@ -194,16 +193,43 @@ def rope_cache_write(qkv: torch.Tensor, positions: Optional[torch.Tensor], cos: 
                                       1 if write_cache else 0, _stream()))
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(gate) * up for a [rows, 2*width] tensor whose first half of columns is the gate."""
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # the codes of csrc/common.cuh (MB_ACT_*)
+
+
+def activation_code(activation: str) -> int:
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gate activation {activation!r} is not built (known: {', '.join(sorted(ACTIVATIONS))})")
+    return ACTIVATIONS[activation]
+
+
+def gated_epilogue(activation: str = "silu") -> int:
+    """The epilogue code of a gate/up product that stores act(gate) * up: EPI_SWIGLU with the
+    activation in the bits above it (silu gives EPI_SWIGLU itself)."""
+    return EPI_SWIGLU | (activation_code(activation) << 8)
+
+
+def swiglu(gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """act(gate) * up for a [rows, 2*width] tensor whose first half of columns is the gate."""
     _cuda(gate_up)
     if gate_up.dim() != 2 or not gate_up.is_contiguous() or gate_up.shape[1] % 2:
         raise KernelError("gate_up must be a contiguous [rows, 2*width] tensor")
     rows, width = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((rows, width), dtype=gate_up.dtype, device=gate_up.device)
     lib = elementwise()
-    _run(lib, lib.mb_swiglu(_p(gate_up), _p(out), _code(gate_up.dtype), rows, width, _stream()))
+    _run(lib, lib.mb_swiglu(_p(gate_up), _p(out), _code(gate_up.dtype), rows, width, activation_code(activation), _stream()))
     return out
+
+
+def logit_epilogue(logits: torch.Tensor, scale: float, softcap: float) -> torch.Tensor:
+    """In place on float32 logits [rows, vocab]: times `scale`, then softcap * tanh(logits / softcap)
+    unless softcap is 0."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("logit_epilogue takes float32 [rows, vocab] logits")
+    lib = elementwise()
+    _run(lib, lib.mb_logit_epilogue(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], ctypes.c_float(scale),
+                                    ctypes.c_float(softcap), _stream()))
+    return logits
 
 
 def bias_add(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
@@ -283,8 +309,11 @@ def decode_span(max_kv_len: int) -> int:
     return span
 
 
+SHARED_MEMORY_PER_SM = 227 * 1024  # what a block of sm_100a can be given
+
+
 def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64, keys: int = 0,
-                  window: Optional[int] = None, multiprocessors: int = 148) -> int:
+                  window: Optional[int] = None, multiprocessors: Optional[int] = None, page_size: int = 64) -> int:
     """How many blocks share one sequence's keys.
 
     Up to LONG_KEYS cached positions (`keys`; 0: unknown, taken as short): a power of two, at most 8
@@ -302,7 +331,10 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
     multiprocessors (256 blocks) and one block per 16 pages (64 pages for heads wider than 64, whose
     pages are twice as large), at most 64, at most 2,048 blocks in all and at least 4 pages each; above
     8 the partial results meet in scratch memory and a second kernel.  `keys` is rounded up to its class
-    (decode_span), so the count is the same for every length of a class."""
+    (decode_span), so the count is the same for every length of a class.  `multiprocessors`: those of
+    the device the call runs on (None: the current device's)."""
+    if multiprocessors is None:
+        multiprocessors = _sm_count(torch.device("cuda", torch.cuda.current_device()))
     rounded = 1
     while rounded < sequences:
         rounded *= 2
@@ -320,7 +352,7 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
         return splits
 
     def fitting(stages: int) -> int:
-        resident = max(1, (227 * 1024) // _decode_block_bytes[head_dim][stages])
+        resident = max(1, SHARED_MEMORY_PER_SM // _decode_block_bytes[head_dim][stages])
         return power_of_two_up_to(max(1, min(8, (resident * multiprocessors) // max(1, base))))
 
     with_three = fitting(3)
@@ -329,7 +361,7 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
     if span == 0:
         return short
     visible = min(span, window) if window else span
-    pages = -(-visible // 64)
+    pages = -(-visible // page_size)
     by_length = pages // (16 if head_dim <= 64 else 64)
     want = max(256 // base, by_length)
     want = power_of_two_up_to(max(1, min(want, 64, 2048 // base, pages // 4)))
@@ -405,13 +437,7 @@ EPI_BF16, EPI_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 
 
 def skinny():
-    return load_library("mb_skinny_gemm", ["skinny_gemm.cu"], _skinny_defines)
-
-
-# tuning knob for experiments: MODELS_B200_SKINNY="DEPTH=6,STEP=128" rebuilds the decode product with
-# another ring depth / stage width
-_skinny_defines = {"MB_SKINNY_" + k: int(v) for k, v in
-                   (item.split("=") for item in os.environ.get("MODELS_B200_SKINNY", "").split(",") if item)}
+    return load_library("mb_skinny_gemm", ["skinny_gemm.cu"])
 
 
 def skinny_takes(weight: torch.Tensor, rows: int, with_norm: bool = False) -> bool:
@@ -442,6 +468,11 @@ def _sm_count(device) -> int:
     return _multiprocessors[index]
 
 
+def multiprocessors(device) -> int:
+    """Multiprocessors of a CUDA device (asked of the driver once)."""
+    return _sm_count(torch.device(device))
+
+
 def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] = None, xf: Optional[torch.Tensor] = None,
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -465,12 +496,13 @@ def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] =
         batch = x.shape[0]
     if not skinny_takes(weight, batch, norm):
         raise KernelError(f"skinny_gemm does not take a {tuple(weight.shape)} {weight.dtype} weight with {batch} rows")
-    out_cols = n // 2 if epilogue == EPI_SWIGLU else n
-    if epilogue == EPI_RESIDUAL:
+    kind = epilogue & 0xFF  # a gated epilogue carries its activation above
+    out_cols = n // 2 if kind == EPI_SWIGLU else n
+    if kind == EPI_RESIDUAL:
         if out is None or out.dtype != torch.float32 or out.shape != (batch, n) or out.stride(1) != 1:
             raise KernelError("the residual epilogue adds into a float32 [rows, n] tensor")
     elif out is None:
-        out = torch.empty((batch, out_cols), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16,
+        out = torch.empty((batch, out_cols), dtype=torch.float32 if kind == EPI_F32 else torch.bfloat16,
                           device=weight.device)
     lib = skinny()
     _run(lib, lib.mb_skinny_gemm(_p(weight), weight.stride(0), n, k, batch, _p(x), x.stride(0) if x is not None else 0,
@@ -520,6 +552,7 @@ def gemm_tcgen05_takes(weight: torch.Tensor, epilogue: int = EPI_BF16, rows: Opt
     many rows: above 128 the prefill form; from 33 to 128 the wide decode form, and that only for
     matrices with a row tile per multiprocessor (with fewer it would have to split K, and a library
     product is quicker there)."""
+    epilogue &= 0xFF
     n = weight.shape[0] // 2 if epilogue == EPI_SWIGLU else weight.shape[0]
     if rows is not None:
         if rows < TCGEN05_MIN_ROWS:
@@ -531,13 +564,19 @@ def gemm_tcgen05_takes(weight: torch.Tensor, epilogue: int = EPI_BF16, rows: Opt
             and (epilogue != EPI_SWIGLU or weight.shape[0] % 2 == 0))
 
 
+_split_tickets = {}
+
+
 def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None,
-                 tile_width: int = 0, pair: int = 0) -> torch.Tensor:
+                 tile_width: int = 0, pair: int = 0, arrival_order: bool = False) -> torch.Tensor:
     """a [m, k] . weight[n, k]^T on the tcgen05 tensor cores (bfloat16 in, float accumulation).
     Epilogues as for skinny_gemm: EPI_BF16 / EPI_F32 store, EPI_RESIDUAL adds into `out` (float32
-    [m, n]), EPI_SWIGLU stores silu(gate) * up for weight = [gate rows; up rows].  tile_width 0 lets
+    [m, n]), EPI_SWIGLU stores act(gate) * up for weight = [gate rows; up rows].  tile_width 0 lets
     the launcher choose between tiles of 128 and 256 output columns.  pair 2: tiles of 256 rows by
-    256 columns on pairs of blocks (tcgen05 cta_group::2)."""
+    256 columns on pairs of blocks (tcgen05 cta_group::2).  Where the residual epilogue splits K over
+    blocks (few tiles, a long K) the parts are summed in their order through scratch memory, so a
+    result is the same bits in every run; `arrival_order` lets each part add into `out` as it finishes
+    instead (a little quicker, the last bit of an element then depends on timing)."""
     _cuda(a, weight, out)
     if a.dtype != torch.bfloat16 or a.dim() != 2 or a.stride(1) != 1 or a.shape[1] != weight.shape[1]:
         raise KernelError(f"gemm_tcgen05: activations {tuple(a.shape)} {a.dtype} do not fit the weight {tuple(weight.shape)}")
@@ -545,15 +584,27 @@ def gemm_tcgen05(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16
         raise KernelError(f"gemm_tcgen05 does not take a {tuple(weight.shape)} {weight.dtype} weight")
     m, k = a.shape
     n_w = weight.shape[0]
-    n = n_w // 2 if epilogue == EPI_SWIGLU else n_w
-    if epilogue == EPI_RESIDUAL:
+    kind = epilogue & 0xFF
+    n = n_w // 2 if kind == EPI_SWIGLU else n_w
+    if kind == EPI_RESIDUAL:
         if out is None or out.dtype != torch.float32 or out.shape != (m, n) or out.stride(1) != 1:
             raise KernelError("the residual epilogue adds into a float32 [m, n] tensor")
     elif out is None:
-        out = torch.empty((m, n), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=a.device)
+        out = torch.empty((m, n), dtype=torch.float32 if kind == EPI_F32 else torch.bfloat16, device=a.device)
     lib = gemm_tc()
+    sms = _sm_count(a.device)
+    partial = tickets = None
+    if kind == EPI_RESIDUAL and not arrival_order:
+        need_partial, need_tickets = ctypes.c_size_t(0), ctypes.c_size_t(0)
+        lib.mb_gemm_tcgen05_scratch(sms, ctypes.byref(need_partial), ctypes.byref(need_tickets))
+        partial = torch.empty((need_partial.value,), dtype=torch.float32, device=a.device)  # touched only where K is split
+        key = a.device.index if a.device.index is not None else torch.cuda.current_device()
+        tickets = _split_tickets.get(key)
+        if tickets is None:
+            # zero once; every launch leaves the tickets at zero
+            tickets = _split_tickets[key] = torch.zeros((need_tickets.value,), dtype=torch.int32, device=a.device)
     _run(lib, lib.mb_gemm_tcgen05(_p(a), a.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), m, n_w, k,
-                                  epilogue, _sm_count(a.device), tile_width, pair, _stream()))
+                                  epilogue, sms, tile_width, pair, _p(partial), _p(tickets), _stream()))
     return out
 
 
@@ -611,12 +662,13 @@ def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, o
         raise KernelError(f"wide_gemm does not take a {tuple(weight.shape)} {weight.dtype} weight")
     batch, k = x.shape
     n_w = weight.shape[0]
-    n = n_w // 2 if epilogue == EPI_SWIGLU else n_w
-    if epilogue == EPI_RESIDUAL:
+    kind = epilogue & 0xFF
+    n = n_w // 2 if kind == EPI_SWIGLU else n_w
+    if kind == EPI_RESIDUAL:
         if out is None or out.dtype != torch.float32 or out.shape != (batch, n) or out.stride(1) != 1:
             raise KernelError("the residual epilogue adds into a float32 [rows, n] tensor")
     elif out is None:
-        out = torch.empty((batch, n), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=x.device)
+        out = torch.empty((batch, n), dtype=torch.float32 if kind == EPI_F32 else torch.bfloat16, device=x.device)
     lib = wide_gemm_lib()
     sms = _sm_count(x.device)
     need_partial, need_tickets = ctypes.c_size_t(0), ctypes.c_size_t(0)

@@ -151,7 +151,8 @@ class AttentionMixer(Mixer):
         s = self.spec
         if self.runtime.compute_dtype != torch.bfloat16 or s.head_dim % 16 or s.head_dim > 256:
             return 0  # the plain-arithmetic kernel: one launch shape for every length
-        return ops.decode_splits(sequences, s.num_heads, s.num_kv_heads, s.head_dim, max_kv_len, s.window)
+        return ops.decode_splits(sequences, s.num_heads, s.num_kv_heads, s.head_dim, max_kv_len, s.window,
+                                 ops.multiprocessors(self.runtime.device))
 
     def attend(self, qkv, attended, batch, group, run):
         """Tensor-core kernels where they apply (bfloat16, head size a multiple of 16, pages of 64);
@@ -160,7 +161,8 @@ class AttentionMixer(Mixer):
         args = (qkv, attended, run.k_pool, run.v_pool, group.block_table, batch.cu_q, batch.kv_lens)
         if ops.attention_tc_takes(qkv.dtype, s.head_dim, run.k_pool.shape[2]):
             if batch.max_q_len == 1:
-                splits = ops.decode_splits(batch.num_sequences, s.num_heads, s.num_kv_heads, s.head_dim, batch.max_kv_len, s.window)
+                splits = ops.decode_splits(batch.num_sequences, s.num_heads, s.num_kv_heads, s.head_dim, batch.max_kv_len,
+                                           s.window, ops.multiprocessors(qkv.device), run.k_pool.shape[2])
                 ops.decode_attention(*args, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale, splits)
             else:
                 ops.prefill_attention(*args, batch.max_q_len, s.num_heads, s.num_kv_heads, s.head_dim, s.window, s.scale)

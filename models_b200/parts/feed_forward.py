@@ -1,6 +1,7 @@
-"""Dense gated feed-forward: down(silu(gate(xn)) * up(xn)) (integrallis/models,
-backend-java/.../llama/LlamaForwardPass.java:1150-1178; silu(z) = z / (1 + exp(-z)),
-backend-java/.../ops/TensorOps.java:1407-1425).  gate and up are one product over row-concatenated
+"""Dense gated feed-forward: down(act(gate(xn)) * up(xn)) (integrallis/models,
+backend-java/.../llama/LlamaForwardPass.java:1150-1178).  The activation is the spec's: "silu"
+(z / (1 + exp(-z)), backend-java/.../ops/TensorOps.java:1407-1425; Llama's) or "gelu_tanh"
+(:1427-1449); it is an argument of every kernel that applies it, fused or not.  gate and up are one product over row-concatenated
 weights, as the reference pairs them (dualMatmulDispatch,
 backend-java/.../llama/LlamaForwardPass.java:1153-1164).
 """
@@ -19,8 +20,10 @@ from .registry import register_part
 class GatedFeedForward(Part):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
-        if spec.activation != "silu":
-            raise ValueError(f"gated feed-forward activation {spec.activation!r} is not built (known: silu)")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"gated feed-forward activation {spec.activation!r} is not built "
+                             f"(known: {', '.join(sorted(ops.ACTIVATIONS))})")
+        self.gated = ops.gated_epilogue(spec.activation)  # the epilogue code of a gate/up product with this activation
 
     def parameters(self):
         s, n = self.spec, self.spec.weights
@@ -55,9 +58,9 @@ class GatedFeedForward(Part):
                 and ops.skinny_pays(self.w_gate_up, rows, with_norm=True) and ops.skinny_pays(self.w_down, rows))
 
     def forward_residual(self, x: torch.Tensor, norm) -> None:
-        """x += down(silu(gate(norm(x))) * up(norm(x))) in two kernels: norm, gate/up product and
+        """x += down(act(gate(norm(x))) * up(norm(x))) in two kernels: norm, gate/up product and
         activation in one, the down product and the residual add in the other."""
-        hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, xf=x, gain=norm.weight, eps=norm.spec.eps)
+        hidden = ops.skinny_gemm(self.w_gate_up, self.gated, xf=x, gain=norm.weight, eps=norm.spec.eps)
         ops.skinny_gemm(self.w_down, ops.EPI_RESIDUAL, x=hidden, out=x)
 
     def adds(self, xn: torch.Tensor) -> bool:
@@ -67,7 +70,7 @@ class GatedFeedForward(Part):
                 and ops.gemm_tcgen05_takes(self.w_down))
 
     def forward_into(self, x: torch.Tensor, xn: torch.Tensor) -> None:
-        """x += down(silu(gate(xn)) * up(xn)) with the residual add inside the down product, which splits
+        """x += down(act(gate(xn)) * up(xn)) with the residual add inside the down product, which splits
         K over blocks where it has few tiles: at 9 to 128 rows it takes 8.8 us for the 1B sizes where a
         library product takes 12.5 and leaves the add to another kernel (decode steps of 16 to 64 sequences
         gain 5 to 6 % at the 1B sizes, 0 to 3 % at 8B sizes; 64 sequences at 3B sizes lose 4 %).  Where the gate/up product has
@@ -76,29 +79,29 @@ class GatedFeedForward(Part):
         activation kernel are quicker."""
         rows = xn.shape[0]
         if ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows) and rows > ops.WIDE_ROWS:
-            hidden = ops.gemm_tcgen05(xn, self.w_gate_up, ops.EPI_SWIGLU)
+            hidden = ops.gemm_tcgen05(xn, self.w_gate_up, self.gated)
         elif ops.skinny_pays(self.w_gate_up, rows):
-            hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, x=xn)
+            hidden = ops.skinny_gemm(self.w_gate_up, self.gated, x=xn)
         else:
-            hidden = ops.swiglu(linear(xn, self.w_gate_up, self.runtime.compute_dtype))
+            hidden = ops.swiglu(linear(xn, self.w_gate_up, self.runtime.compute_dtype), self.spec.activation)
         ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype
         if self.b_gate_up is None and ops.skinny_pays(self.w_gate_up, xn.shape[0]) and xn.dtype == torch.bfloat16:
-            hidden = ops.skinny_gemm(self.w_gate_up, ops.EPI_SWIGLU, x=xn)
+            hidden = ops.skinny_gemm(self.w_gate_up, self.gated, x=xn)
             delta = linear(hidden, self.w_down, dtype)
             if self.b_down is not None:
                 ops.bias_add(delta, self.b_down)
             return delta
         if (self.b_gate_up is None and xn.dtype == torch.bfloat16
                 and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, xn.shape[0])):
-            hidden = ops.tensor_core_gemm(xn, self.w_gate_up, ops.EPI_SWIGLU)
+            hidden = ops.tensor_core_gemm(xn, self.w_gate_up, self.gated)
         else:
             gate_up = linear(xn, self.w_gate_up, dtype)
             if self.b_gate_up is not None:
                 ops.bias_add(gate_up, self.b_gate_up)
-            hidden = ops.swiglu(gate_up)
+            hidden = ops.swiglu(gate_up, self.spec.activation)
         delta = linear(hidden, self.w_down, dtype)
         if self.b_down is not None:
             ops.bias_add(delta, self.b_down)

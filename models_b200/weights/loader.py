@@ -8,10 +8,11 @@ and reported in one error: missing tensors, unexpected tensors, wrong shapes.
 
 from __future__ import annotations
 
+import fnmatch
 import json
 from dataclasses import dataclass
 from pathlib import Path
-from typing import Dict, List, Mapping, Tuple
+from typing import Dict, List, Mapping, Sequence, Tuple
 
 import torch
 
@@ -87,14 +88,31 @@ def check_names_and_shapes(requests: Mapping[str, ParamRequest], found: Mapping[
     raise WeightsError("\n".join(lines), missing, unexpected, wrong)
 
 
-def load_tensors(folder, requests: Mapping[str, ParamRequest]) -> Dict[str, torch.Tensor]:
+def load_tensors(folder, requests: Mapping[str, ParamRequest], ignored: Sequence[str] = (),
+                 duplicates: Mapping[str, str] = {}) -> Dict[str, torch.Tensor]:
     """Host tensors for every requested name.  bfloat16 stays bfloat16, a tensor stored in 32-bit
-    stays 32-bit, integer tables become int32."""
+    stays 32-bit, integer tables become int32.  A stored tensor that nobody asked for is an error,
+    listed with the missing ones and the wrong shapes, unless its name matches one of the `ignored`
+    patterns (buffers the model recomputes), or `duplicates` names the requested tensor it must
+    repeat bit for bit (then it is dropped; if it differs, that is the error)."""
     folder = Path(folder)
     files, by_name = _open_files(folder)
     try:
-        check_names_and_shapes(requests, {n: f.shape(n) for n, f in by_name.items()}, str(folder))
-        return {name: by_name[name].tensor(name) for name in requests}
+        found = {n: f.shape(n) for n, f in by_name.items()
+                 if n in requests or not any(fnmatch.fnmatchcase(n, pattern) for pattern in ignored)}
+        repeated = [n for n in found if n not in requests and duplicates.get(n) in found]
+        for name in repeated:
+            del found[name]
+        check_names_and_shapes(requests, found, str(folder))
+        tensors = {name: by_name[name].tensor(name) for name in requests}
+        for name in repeated:
+            original = duplicates[name]
+            copy = by_name[name].tensor(name)
+            if copy.shape != tensors[original].shape or copy.dtype != tensors[original].dtype or not torch.equal(copy, tensors[original]):
+                raise WeightsError(
+                    f"{folder}: {name} is stored although the model takes it from {original}, and the two differ "
+                    "(the configuration says they are tied)", unexpected=[name])
+        return tensors
     finally:
         for f in files:
             f.close()

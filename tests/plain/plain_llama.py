@@ -179,6 +179,20 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return (gate / (1.0 + torch.exp(-gate))) * up
 
 
+def gelu_glu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """0.5 g (1 + tanh(0.7978845608 g (1 + 0.044715 g^2))) * up (backend-java/.../ops/TensorOps.java:1427-1449;
+    the reference reads tanh from a table, this is the function the table samples)."""
+    inner = 0.7978845608028654 * gate * (1.0 + 0.044715 * gate * gate)
+    return 0.5 * gate * (1.0 + torch.tanh(inner)) * up
+
+
+def softcap_logits(logits: torch.Tensor, softcap: float) -> torch.Tensor:
+    """softcap * tanh(logits / softcap); 0 means none (backend-java/.../llama/LlamaForwardPass.java:1751-1764)."""
+    if softcap == 0.0:
+        return logits
+    return softcap * torch.tanh(logits / softcap)
+
+
 def feed_forward(xn, w_gate, w_up, w_down, b_gate=None, b_up=None, b_down=None):
     """d = Wd . (silu(Wg.xn) * (Wu.xn)) (backend-java/.../llama/LlamaForwardPass.java:1166-1178)."""
     return linear(swiglu(linear(xn, w_gate, b_gate), linear(xn, w_up, b_up)), w_down, b_down)

@@ -34,7 +34,8 @@ def test_groups_by_need_and_storage_shapes():
     assert cache.groups[0].runs == [0, 1] and cache.groups[1].runs == [2]
     shapes = []
     cache.allocate_storage(lambda shape: shapes.append(shape) or shape)
-    assert shapes == [(2, 2, 11, 2, 64, 16), (1, 2, 11, 2, 64, 16)]  # 10 pages and the spare page 0
+    # keys and values of each group: 10 pages and the spare page 0
+    assert shapes == [(2, 11, 2, 64, 16), (2, 11, 2, 64, 16), (1, 11, 2, 64, 16), (1, 11, 2, 64, 16)]
     shared = KvCache([KvRequest(2, 16), KvRequest(2, 16)], [None, 0], 128)
     assert shared.run_location[1] == shared.run_location[0] and shared.groups[0].runs == [0]
     with pytest.raises(ValueError, match="kv heads"):
@@ -189,3 +190,31 @@ def test_decode_rows_follow_the_tables_of_a_slot_that_is_used_again():
     assert second_tables != first_tables  # the case that a (slot, page count) key cannot tell apart
     rows.update(cache, second_slots[:1], [3])  # one row falls out: it becomes padding
     assert rows.tables_h[0][1].tolist() == [0, 0, 0, 0] and rows.mappings_h[0][1] == -1 and rows.slots_h[1] == cache.max_slots
+
+
+def test_key_and_value_sizes_apart_and_a_window_groups_own_budget():
+    """A group's keys and values have sizes of their own; a window group is made with the pages its
+    window (and the longest step) can hold, a group that keeps everything with the whole budget."""
+    narrow_values = KvRequest(2, 32, None, value_dim=8)
+    windowed = KvRequest(1, 16, 100)
+    cache = KvCache([narrow_values, windowed, narrow_values], [None, None, 0], 64 * 200, max_slots=4, max_step_tokens=30)
+    shapes = []
+    cache.allocate_storage(lambda shape: shapes.append(shape) or shape)
+    # window 100 and steps of up to 30 tokens: ceil(129 / 64) + 1 = 4 pages per sequence, 16 in all
+    assert [g.num_pages for g in cache.groups] == [200, 16]
+    assert shapes == [(1, 201, 2, 64, 32), (1, 201, 2, 64, 8), (1, 17, 1, 64, 16), (1, 17, 1, 64, 16)]
+    assert cache.pools(2)[1] is cache.pools(0)[1]  # run 2 reads run 0's storage
+    slots = [cache.open_slot() for _ in range(4)]
+    for s in slots:  # four sequences grow to 1,000 positions in steps of 30: the window group never runs out
+        for _ in range(34):
+            cache.append([(s, 30)])
+            cache.commit([(s, 30)])
+        assert sum(p >= 0 for p in cache.groups[1].tables[s]) <= 4
+    cache.check()
+    with pytest.raises(CacheFull, match="window of 100"):
+        cache.append([(s, 64 * 5) for s in slots])  # a step longer than promised does not fit the window group
+    cache.check()
+    with pytest.raises(ValueError, match="values 8"):
+        KvCache([narrow_values, KvRequest(2, 32, None)], [None, 0], 128)
+    unbounded = KvCache([windowed], [None], 64 * 200, max_slots=4)  # no promise about steps: the whole budget
+    assert unbounded.groups[0].num_pages == 200

@@ -200,3 +200,33 @@ def test_random_values_are_normal_and_keyed_by_seed_and_name():
     shifted = normal_float32(1001, key, 1.0, 0.1)
     assert np.array_equal(shifted, (short * np.float32(0.1) + np.float32(1.0)).astype(np.float32))
     assert not np.array_equal(short, normal_float32(1001, tensor_key(3, "model.norm.weight"), 0.0, 1.0))
+
+
+def test_recomputed_buffers_and_a_tied_models_stored_output_matrix(tmp_path):
+    """What a checkpoint may hold beyond the model's tensors: rotation-frequency buffers (ignored: they
+    are recomputed), and for a tied model the output matrix itself -- accepted when it repeats the
+    embedding table, refused when the two differ.  Any other unknown tensor is still an error."""
+    config = config_from_dict(TINY_A)
+    spec = config.model_spec()
+    requests = parameter_requests(spec)
+    tensors = random_tensors(requests, 1)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    folder = tmp_path / "with_extras"
+    folder.mkdir()
+    write_safetensors(folder / "model.safetensors", tensors)
+    loaded = load_tensors(folder, requests, spec.ignored_tensors, spec.duplicate_tensors)
+    assert set(loaded) == set(requests)
+    with pytest.raises(WeightsError, match="unexpected"):  # without the architecture's word for it, both are unknown
+        load_tensors(folder, requests)
+    tensors["lm_head.weight"][3, 5] += 1.0
+    write_safetensors(folder / "model.safetensors", tensors)
+    with pytest.raises(WeightsError, match="the two differ"):
+        load_tensors(folder, requests, spec.ignored_tensors, spec.duplicate_tensors)
+    del tensors["lm_head.weight"]
+    tensors["model.layers.0.self_attn.something_else"] = torch.ones(8)
+    write_safetensors(folder / "model.safetensors", tensors)
+    with pytest.raises(WeightsError, match="something_else"):
+        load_tensors(folder, requests, spec.ignored_tensors, spec.duplicate_tensors)
+    untied = config_from_dict(TINY_B).model_spec()
+    assert untied.duplicate_tensors == {}  # an untied model needs its output matrix; nothing stands in for it

@@ -178,3 +178,30 @@ def test_mid_size_models_all_ways(cuda_device, tmp_path, name, dtype):
     if dtype == "bfloat16":
         assert ops.gemm_tcgen05_status() == 0
     engine.cache.check()
+
+
+def test_the_same_prompt_gives_the_same_bits_every_time(cuda_device, tmp_path):
+    """A prompt of 256 tokens (the size at which the residual products split K over blocks) five times,
+    alone and next to another prompt, in bfloat16: every run's logits are equal bit for bit
+    (integrallis/models gates on exact-logit repeatability, models-bench/.../DeterminismAuditCli.java:115-140)."""
+    from models_b200.engine import StepEntry
+
+    raw = MID["D"]
+    folder = make_folder(raw, seed=33, tmp_path=tmp_path, std=0.03)
+    engine = _engine(folder, "bfloat16", max_tokens=4096)
+    tokens, other = random_tokens(raw["vocab_size"], 256, 9), random_tokens(raw["vocab_size"], 100, 10)
+    runs = []
+    for i in range(5):
+        slot = engine.open_slot()
+        runs.append(engine.step([StepEntry(slot, tokens, [0, 100, 255])]))
+        engine.release_slot(slot)
+    for other_run in runs[1:]:
+        assert torch.equal(runs[0], other_run)
+    assert scaled_error(runs[0][2], plain_logits(folder, tokens)[255]) < TOLERANCE["bfloat16"]
+    pairs = []
+    for i in range(3):
+        slots = [engine.open_slot(), engine.open_slot()]
+        pairs.append(engine.step([StepEntry(slots[0], other, [99]), StepEntry(slots[1], tokens, [255])]))
+        for slot in slots:
+            engine.release_slot(slot)
+    assert torch.equal(pairs[0], pairs[1]) and torch.equal(pairs[0], pairs[2])

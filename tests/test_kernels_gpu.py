@@ -677,8 +677,8 @@ def test_a_random_model_is_the_same_from_a_file_and_on_the_device(cuda_device, t
     folder = make_folder(TINY_B, 9, tmp_path)
     from_file = engine_from_folder(folder, "bfloat16", 256)
     on_device = engine_from_config(config_from_dict(TINY_B), 9, "bfloat16", 256)
-    assert torch.equal(from_file.model.embedding, on_device.model.embedding)
-    assert torch.equal(from_file.model.head_weight, on_device.model.head_weight)
+    assert torch.equal(from_file.model.embedding.weight, on_device.model.embedding.weight)
+    assert torch.equal(from_file.model.head.weight, on_device.model.head.weight)
     assert torch.equal(from_file.model.final_norm.weight, on_device.model.final_norm.weight)
     for a, b in zip(from_file.model.blocks, on_device.model.blocks):
         assert torch.equal(a.mixer.w_qkv, b.mixer.w_qkv) and torch.equal(a.feed_forward.w_down, b.feed_forward.w_down)
@@ -689,3 +689,84 @@ def test_a_random_model_is_the_same_from_a_file_and_on_the_device(cuda_device, t
         slot = engine.open_slot()
         outs.append(engine.step([StepEntry(slot, tokens, [49])]))
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gated_products_take_their_activation_as_an_argument(cuda_device, activation):
+    """act(gate) * up with the gate's activation as an argument of every kernel that applies it: the
+    stand-alone kernel (float32 and bfloat16), the decode product (with and without the folded norm),
+    the wide tcgen05 product and the prefill tcgen05 product."""
+    from models_b200.kernels import ops
+
+    act = {"silu": P_swiglu, "gelu_tanh": plain_llama.gelu_glu}[activation]
+    g = torch.Generator().manual_seed(5)
+    n, k = 272, 264
+    w = (torch.randn(2 * n, k, generator=g) * 0.2).to(torch.bfloat16)
+    gain = 1.0 + 0.1 * torch.randn(k, generator=g)
+    for dtype in DTYPES:
+        both = (torch.randn(37, 2 * 203, generator=g) * 2).to(dtype)
+        expected = act(both[:, :203].float(), both[:, 203:].float())
+        close(ops.swiglu(both.cuda(), activation), expected, dtype)
+    code = ops.gated_epilogue(activation)
+    for rows in (5, 16, 64, 300):
+        x = (torch.randn(rows, k, generator=g)).to(torch.bfloat16)
+        product = x.float() @ w.float().t()
+        expected = act(product[:, :n], product[:, n:])
+        if rows <= 32:
+            close(ops.skinny_gemm(w.cuda(), code, x=x.cuda()), expected, torch.bfloat16)
+        if rows <= 16:
+            xf = torch.randn(rows, k, generator=g)
+            normed = plain_llama.rms_norm(xf, gain, 1e-5).to(torch.bfloat16).float() @ w.float().t()
+            got = ops.skinny_gemm(w.cuda(), code, xf=xf.cuda(), gain=gain.cuda(), eps=1e-5)
+            want = act(normed[:, :n], normed[:, n:])
+            # as for silu in the test of all epilogues: two roundings to bfloat16 (rows, result) around a product of two sums
+            assert float((got.double().cpu() - want.double()).abs().max()) < 2e-2 * float(want.abs().max())
+        if rows <= 128:
+            close(ops.wide_gemm(x.cuda(), w.cuda(), code), expected, torch.bfloat16)
+        close(ops.gemm_tcgen05(x.cuda(), w.cuda(), code), expected, torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="not built"):
+        ops.gated_epilogue("relu")
+    assert ops.gemm_tcgen05_status() == 0
+
+
+def P_swiglu(gate, up):
+    return plain_llama.swiglu(gate, up)
+
+
+def test_logit_epilogue(cuda_device):
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(5, 203, generator=g) * 3
+    wide = torch.zeros(5, 256)
+    wide[:, :203] = logits
+    view = wide.cuda()[:, :203]  # rows wider than the vocabulary: the stride is an argument
+    close(ops.logit_epilogue(view, 2.0, 5.0), plain_llama.softcap_logits(logits * 2.0, 5.0), torch.float32)
+    close(ops.logit_epilogue(logits.clone().cuda(), 0.5, 0.0), logits * 0.5, torch.float32)
+
+
+def test_split_k_residual_product_is_the_same_bits_every_time(cuda_device):
+    """Few tiles and a long K: the residual product splits K over blocks.  The parts are summed in their
+    order, so ten runs give one result, bit for bit, and it is the plain product; letting the parts add
+    in as they finish is still there as an option and gives the same numbers within rounding."""
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(11)
+    for m, n, k in ((256, 2048, 8192), (200, 520, 4096), (129, 264, 2048)):
+        a = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
+        x0 = torch.randn(m, n, generator=g).cuda()
+        expected = x0.double().cpu() + a.double().cpu() @ w.double().cpu().t()
+        results = []
+        for _ in range(10):
+            x = x0.clone()
+            ops.gemm_tcgen05(a, w, ops.EPI_RESIDUAL, out=x)
+            results.append(x)
+        for other in results[1:]:
+            assert torch.equal(results[0], other), (m, n, k)
+        close(results[0], expected, torch.float32, scale=float(expected.abs().max()) * 1e3)  # bfloat16 inputs, float sums
+        loose = ops.gemm_tcgen05(a, w, ops.EPI_RESIDUAL, out=x0.clone(), arrival_order=True)
+        close(loose, expected, torch.float32, scale=float(expected.abs().max()) * 1e3)
+    tickets = ops._split_tickets[torch.cuda.current_device()]
+    assert int(tickets.abs().sum()) == 0  # every launch leaves them as it found them
+    assert ops.gemm_tcgen05_status() == 0

@@ -473,3 +473,239 @@ def test_missing_kind_and_cpu_tensors_fail_loudly(cuda_device):
         build_part("mixer", type("S", (), {"kind": "nope"})(), Runtime(torch.device("cuda:0"), "float32"))
     with pytest.raises(ops.KernelError, match="no CPU path"):
         ops.swiglu(torch.zeros(2, 4))
+
+
+class HalvedEvenLogitsHead:
+    """A toy output head, defined here and registered from outside the package: the package's linear
+    head, after which every even-numbered token's logit is halved.  It offers what the model asks of
+    any head: parameters(), load(tensors, tied_to), forward(x, pending, norm, want_rows)."""
+
+    def __init__(self, spec, runtime):
+        from models_b200.parts.head import LinearHead
+
+        self.spec, self.inner = spec, LinearHead(spec, runtime)
+
+    def parameters(self):
+        return self.inner.parameters()
+
+    def load(self, tensors, tied_to=None):
+        self.inner.load(tensors, tied_to)
+
+    def forward(self, x, pending, norm, want_rows):
+        logits = self.inner.forward(x, pending, norm, want_rows)
+        logits[:, ::2] *= 0.5
+        return logits
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_heads_with_a_logit_epilogue_and_a_toy_head_from_outside(cuda_device, dtype):
+    """The output head is a part like the others: its logit scale and softcap are fields of its spec,
+    and another kind of head is registered without a change to the package."""
+    import dataclasses
+
+    from models_b200.engine import StepEntry
+    from models_b200.parts import register_part, unregister_part
+
+    base = _specs(windows=(None, None))
+    tokens = _tokens(40, base.vocab_size, 3)
+    capped = dataclasses.replace(base, head=dataclasses.replace(base.head, logit_scale=30.0, softcap=4.0))
+    register_part("head", "test_halved_even", HalvedEvenLogitsHead)
+    try:
+        toy = dataclasses.replace(base, head=dataclasses.replace(base.head, kind="test_halved_even"))
+        for spec, name in ((base, "plain"), (capped, "capped"), (toy, "toy")):
+            engine, tensors = _engine(spec, dtype, seed=6)
+            expected = _plain_forward(base, tensors, tokens)
+            # the cap's slope is at most 1, so it passes an error on no larger than it was: errors are
+            # measured against the size of the logits that go into the cap
+            size = float(expected.abs().max()) * (30.0 if name == "capped" else 1.0)
+            if name == "capped":
+                expected = P.softcap_logits(expected * 30.0, 4.0)
+                assert size > 8.0 and float(expected.abs().max()) > 3.9  # the cap bends these logits; it is not a no-op here
+            if name == "toy":
+                expected[:, ::2] *= 0.5
+            slot = engine.open_slot()
+            out = engine.step([StepEntry(slot, tokens[:30], [0, 29])])  # two wanted rows: the folded few-row path
+            for row, place in enumerate((0, 29)):
+                assert float((out[row].cpu() - expected[place]).abs().max()) < TOLERANCE[dtype] * size, (name, place)
+            out = engine.step([StepEntry(slot, tokens[30:], list(range(10)))])  # ten rows: norm, then the product
+            assert float((out.cpu() - expected[30:]).abs().max()) < TOLERANCE[dtype] * size, name
+    finally:
+        unregister_part("head", "test_halved_even")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_layer_observer_sees_the_stream_after_every_run(cuda_device, tmp_path, dtype):
+    """DecoderModel.observer is called once per scheduled run with the float32 residual stream after
+    it, for a whole prompt (the deltas still pending are added in) and for a decode step whose norms
+    and residual adds ride inside the matrix products."""
+    from models_b200.engine import StepEntry
+    from models_b200.engine.loading import engine_from_folder
+    from tiny import TINY_B, make_folder, random_tokens
+
+    folder = make_folder(TINY_B, 17, tmp_path, std=0.05)
+    config, weights = P.read_model_folder(folder)
+    tokens = random_tokens(TINY_B["vocab_size"], 31, 2)
+    _, hidden = P.forward(config, weights, tokens, return_hidden=True)
+    engine = engine_from_folder(folder, dtype, 256)
+    seen = []
+    engine.model.observer = lambda run, x: seen.append((run, x))
+    slot = engine.open_slot()
+    engine.step([StepEntry(slot, tokens[:30], [29])])
+    assert [run for run, _ in seen] == [0, 1, 2]
+    for run, x in seen:
+        assert x.dtype == torch.float32 and scaled_error(x, hidden[run][:30]) < TOLERANCE[dtype], run
+    seen.clear()
+    engine.step([StepEntry(slot, tokens[30:], [0])])
+    assert [run for run, _ in seen] == [0, 1, 2]
+    for run, x in seen:
+        assert scaled_error(x[0], hidden[run][30]) < TOLERANCE[dtype], run
+    engine.model.observer = None
+
+
+class NarrowValueMixer:
+    """A toy attention with keys of one size and values of another, defined here: one head, queries and
+    keys of `key_dim`, values of `value_dim`, no rotation, plain torch arithmetic over its own pages.
+    It shows that the cache gives a mixer keys and values of sizes of their own."""
+
+    def __init__(self, spec, runtime):
+        self.spec, self.runtime = spec, runtime
+
+    def parameters(self):
+        from models_b200.weights import ParamRequest
+
+        s, n = self.spec, self.spec.weights
+        return [ParamRequest(n["q"], (s.key_dim, s.hidden_size)), ParamRequest(n["k"], (s.key_dim, s.hidden_size)),
+                ParamRequest(n["v"], (s.value_dim, s.hidden_size)), ParamRequest(n["o"], (s.hidden_size, s.value_dim))]
+
+    def load(self, tensors):
+        n = self.spec.weights
+        self.w = {name: self.runtime.matrix(tensors[n[name]]).float() for name in ("q", "k", "v", "o")}
+
+    def kv_request(self):
+        from models_b200.cache import KvRequest
+
+        return KvRequest(1, self.spec.key_dim, None, value_dim=self.spec.value_dim)
+
+    def state_request(self):
+        return None
+
+    def forward(self, xn, batch, run):
+        s = self.spec
+        x = xn.float()
+        q, k, v = x @ self.w["q"].t(), x @ self.w["k"].t(), x @ self.w["v"].t()
+        assert run.k_pool.shape[1:] == (1, 64, s.key_dim) and run.v_pool.shape[1:] == (1, 64, s.value_dim)
+        mapping = batch.groups[run.group].slot_mapping.long()
+        keep = mapping >= 0
+        run.k_pool.view(-1, s.key_dim)[mapping[keep]] = k[keep].to(run.k_pool.dtype)
+        run.v_pool.view(-1, s.value_dim)[mapping[keep]] = v[keep].to(run.v_pool.dtype)
+        out = torch.zeros(x.shape[0], s.value_dim, device=x.device)
+        cu, lens, table = batch.cu_q.tolist(), batch.kv_lens.tolist(), batch.groups[run.group].block_table
+        positions = batch.positions.tolist()
+        for b in range(batch.num_sequences):
+            where = torch.arange(lens[b], device=x.device)
+            flat = table[b][where // 64].long() * 64 + where % 64
+            keys, values = run.k_pool.view(-1, s.key_dim)[flat].float(), run.v_pool.view(-1, s.value_dim)[flat].float()
+            for row in range(cu[b], cu[b + 1]):
+                scores = (keys[: positions[row] + 1] @ q[row]) / math.sqrt(s.key_dim)
+                out[row] = torch.softmax(scores, 0) @ values[: positions[row] + 1]
+        return (out @ self.w["o"].t()).to(xn.dtype)
+
+
+def test_a_toy_mixer_with_keys_and_values_of_different_sizes(cuda_device):
+    from dataclasses import dataclass, field
+
+    from models_b200.config.specs import BlockSpec, ModelSpec, ScheduleEntry
+    from models_b200.engine import StepEntry
+    from models_b200.parts import register_part, unregister_part
+
+    @dataclass(frozen=True)
+    class NarrowValueSpec:
+        hidden_size: int
+        key_dim: int
+        value_dim: int
+        weights: dict = field(default_factory=dict, hash=False, compare=False)
+        kind: str = "test_narrow_value"
+
+    register_part("mixer", "test_narrow_value", NarrowValueMixer)
+    try:
+        base = _specs(windows=(None, None))
+        names = {n: f"layers.1.toy_{n}" for n in ("q", "k", "v", "o")}
+        toy = BlockSpec(NarrowValueSpec(base.hidden_size, 24, 8, names), base.layers[1].feed_forward,
+                        base.layers[1].mixer_norm, base.layers[1].feed_forward_norm)
+        spec = ModelSpec(base.architecture, base.vocab_size, base.hidden_size, base.max_positions, base.embedding,
+                         (base.layers[0], toy), (ScheduleEntry(0), ScheduleEntry(1)), base.final_norm, base.head)
+        engine, tensors = _engine(spec, "float32", seed=8, max_tokens=512)
+        assert len(engine.cache.groups) == 2  # the toy mixer's keys and values are a group of their own
+        toy_group = engine.cache.groups[1]
+        assert toy_group.keys.shape[-1] == 24 and toy_group.values.shape[-1] == 8
+
+        def plain(tokens):
+            w = {k: v.float() for k, v in tensors.items()}
+            T = len(tokens)
+            x = P.embed(w["embed"], torch.tensor(tokens))
+            l0 = spec.layers[0]
+            m = l0.mixer
+            xn = P.rms_norm(x, w["layers.0.norm1"], l0.mixer_norm.eps)
+            cos, sin = P.rope_cos_sin(torch.arange(T), P.rope_pair_frequencies(m.head_dim, m.position.theta), None)
+            q = P.rope_rotate_split_half(P.linear(xn, w["layers.0.q"]).reshape(T, m.num_heads, m.head_dim), cos, sin)
+            k = P.rope_rotate_split_half(P.linear(xn, w["layers.0.k"]).reshape(T, m.num_kv_heads, m.head_dim), cos, sin)
+            v = P.linear(xn, w["layers.0.v"]).reshape(T, m.num_kv_heads, m.head_dim)
+            x = x + P.linear(P.causal_gqa_attention(q, k, v), w["layers.0.o"])
+            x = x + P.feed_forward(P.rms_norm(x, w["layers.0.norm2"], l0.feed_forward_norm.eps), w["layers.0.gate"],
+                                   w["layers.0.up"], w["layers.0.down"])
+            xn = P.rms_norm(x, w["layers.1.norm1"], toy.mixer_norm.eps)
+            q, k, v = (P.linear(xn, w[names[n]]) for n in ("q", "k", "v"))
+            scores = (q @ k.t()) / math.sqrt(24)
+            scores = scores.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            x = x + P.linear(torch.softmax(scores, -1) @ v, w[names["o"]])
+            x = x + P.feed_forward(P.rms_norm(x, w["layers.1.norm2"], toy.feed_forward_norm.eps), w["layers.1.gate"],
+                                   w["layers.1.up"], w["layers.1.down"])
+            return P.linear(P.rms_norm(x, w["final_norm"], spec.final_norm.eps), w["head"])
+
+        a, b = _tokens(90, spec.vocab_size, 31), _tokens(20, spec.vocab_size, 32)
+        ea, eb = plain(a), plain(b)
+        sa, sb = engine.open_slot(), engine.open_slot()
+        out = engine.step([StepEntry(sa, a[:70], [0, 69]), StepEntry(sb, b[:5], [4])])  # across a page
+        assert scaled_error(out[0], ea[0]) < 1e-4 and scaled_error(out[1], ea[69]) < 1e-4 and scaled_error(out[2], eb[4]) < 1e-4
+        for i in range(15):
+            out = engine.step([StepEntry(sa, [a[70 + i]], [0]), StepEntry(sb, [b[5 + i]], [0])])
+            assert scaled_error(out[0], ea[70 + i]) < 1e-4 and scaled_error(out[1], eb[5 + i]) < 1e-4
+        engine.release_slot(sa)
+        engine.release_slot(sb)
+        engine.cache.check()
+    finally:
+        unregister_part("mixer", "test_narrow_value")
+
+
+def test_a_window_layer_with_a_budget_of_its_own_and_other_page_sizes(cuda_device):
+    """With the longest step stated, the layer that keeps a window of 24 positions gets pages for its
+    window only, and a sequence still decodes far past what those pages hold.  A step longer than stated
+    is refused.  Pages of 32 positions run in float32 (the plain-arithmetic attention takes any page
+    size); bfloat16, whose tensor-core kernels tile pages of 64, refuses them by name."""
+    from models_b200.engine import Engine, StepEntry, StepError, parameter_requests
+    from models_b200.weights import random_tensors
+
+    spec = _specs(windows=(None, 24))
+    tensors = random_tensors(parameter_requests(spec), 12, std=0.05)
+    tokens = _tokens(400, spec.vocab_size, 41)
+    expected = _plain_forward(spec, tensors, tokens)
+    for dtype, page_size in (("float32", 64), ("bfloat16", 64), ("float32", 32)):
+        engine = Engine(spec, tensors, dtype, max_tokens=1024, max_slots=2, max_step_tokens=40, page_size=page_size)
+        full, windowed = engine.cache.groups
+        per_slot = -(-(24 - 1 + 40) // page_size) + 1
+        assert full.num_pages == 1024 // page_size and windowed.num_pages == 2 * per_slot
+        slot = engine.open_slot()
+        with pytest.raises(StepError, match="max_step_tokens"):
+            engine.step([StepEntry(slot, tokens[:41], [40])])
+        assert engine.length(slot) == 0
+        at = 0
+        while at < 400:  # prompts of 40, then single tokens: 400 positions through a window group of a few pages
+            n = 40 if at < 200 else 1
+            out = engine.step([StepEntry(slot, tokens[at:at + n], [n - 1])])
+            assert scaled_error(out[0], expected[at + n - 1]) < TOLERANCE[dtype], (dtype, page_size, at)
+            at += n
+        assert sum(p >= 0 for p in windowed.tables[slot]) <= per_slot
+        engine.release_slot(slot)
+        engine.cache.check()
+    with pytest.raises(ValueError, match="pages of 64"):
+        Engine(spec, tensors, "bfloat16", max_tokens=1024, page_size=32)
