@@ -32,6 +32,8 @@
 // Compiled per head size: -DMB_HEAD_DIM=<multiple of 16, at most 128>.
 #include "attention_tiles.cuh"
 
+#include <string.h>
+
 MB_DEFINE_LAST_ERROR()
 
 namespace mb {
@@ -39,10 +41,14 @@ namespace mb {
 constexpr int kStepWarps = 8;
 constexpr int kStepThreads = kStepWarps * 32;
 constexpr int kCols = 8;              // activation rows of a step = columns of the MMA
-constexpr int kStageCols = 64;        // columns of K per ring stage
-constexpr int kStageBytes = 2 * 2 * 32 * 16;  // [2 row halves][2 pieces][32 lanes][16 bytes]
-constexpr int kDepth = 8;             // ring stages per warp
-constexpr int kSliceCols = kStepWarps * kStageCols;  // K is padded to a multiple of this
+constexpr int kTeams = 2;             // a block's warps work as two teams, each on a row tile of its own
+constexpr int kTeamWarps = kStepWarps / kTeams;  // the warps of a team split K
+constexpr int kTeamThreads = kTeamWarps * 32;
+constexpr int kStageCols = 128;       // columns of K per ring stage
+constexpr int kPieces = kStageCols / 32;  // 32 columns per piece, a lane takes 8 of each piece
+constexpr int kStageBytes = 2 * kPieces * 32 * 16;  // [2 row halves][pieces][32 lanes][16 bytes]
+constexpr int kDepth = 4;             // ring stages per warp
+constexpr int kSliceCols = kTeamWarps * kStageCols;  // K is padded to a multiple of this
 constexpr int kMaxStageCols = 4096;   // most columns of one (sub-)phase: its activations must fit shared memory
 constexpr int kMaxGroups = 4;
 constexpr int kAttnWarps = HD <= 64 ? 8 : 4;  // warps that work in the attention phase (their page rings must fit)
@@ -77,9 +83,11 @@ struct Phase {
     const float* sin_table;
 };
 
-// What changes from step to step; passed by value.
+constexpr int kMaxPhases = 250;  // what fits a launch's 32 KB of parameters beside the step's own record
+
+// What changes from step to step.
 struct Step {
-    const Phase* phases;
+    const Phase* phases;  // host memory, copied into the launch's parameters
     int num_phases;
     int batch;            // sequences = rows, 1..8
     int hidden;
@@ -99,10 +107,13 @@ struct Step {
     int ld_h;
     float* attn_o;        // [batch][heads][splits][HD] partial outputs of the split keys
     float* attn_ml;       // [batch][heads][splits][2] their (maximum as an exponent of two, sum)
+    int* attn_tickets;    // [batch][kv heads x head chunks] arrivals of a sequence's splits; zero before and after a step
+    bf16* a;              // [batch][ld_q] the attention's output rows
     float* logits;        // [batch][ld_logits]
     int ld_logits;
     unsigned int* barrier;  // arrival counter, zero at launch
     int* status;            // set to 1 + (phase << 8) by a block whose bounded wait ran out
+    long long* timeline;    // null, or [num_phases][6] clock readings of block 0: phase entered, barrier passed, activations staged, done, first tile's products done, its sums met
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -132,7 +143,7 @@ __device__ __forceinline__ void cp_async_wait_mem() {
 //   activations  [8 rows][k_pad * 2 + 64]   (row stride = 64 mod 128: the eight rows a quarter-warp reads fall on
 //                different banks); the attention phase has its query tile and page rings here instead
 //   rings        [8 warps][kDepth][kStageBytes]
-//   partial      [2 buffers][8 warps][16 rows][8 columns] floats
+//   partial      [2 teams][2 buffers][4 warps][16 rows][8 columns] floats
 //   sums         [8] sums of squares of the rows, then [8 warps][8] the warps' parts of them
 constexpr int kAttnBytes = kQRowsDecode * kRowBytes + kAttnWarps * kAttnStages * kAttnStageBytes;
 constexpr int kMergeBytes = kQRowsDecode * kRowBytes + kAttnWarps * 16 * (HD + 2) * (int)sizeof(float);
@@ -140,40 +151,72 @@ constexpr int kActivationBytes = kCols * (kMaxStageCols * 2 + 64);
 constexpr int max3(int a, int b, int c) { return a > b ? (a > c ? a : c) : (b > c ? b : c); }
 constexpr int kFrontBytes = (max3(kAttnBytes, kMergeBytes, kActivationBytes) + 127) / 128 * 128;
 constexpr int kRingBytes = kStepWarps * kDepth * kStageBytes;
-constexpr int kPartialFloats = kStepWarps * 16 * kCols;
-constexpr int kSmemBytes = kFrontBytes + kRingBytes + (2 * kPartialFloats + kCols + kStepWarps * kCols) * (int)sizeof(float);
+constexpr int kPartialFloats = kTeamWarps * 16 * kCols;  // one buffer of one team
+constexpr int kSmemBytes = kFrontBytes + kRingBytes + (kTeams * 2 * kPartialFloats + kCols + kStepWarps * kCols) * (int)sizeof(float);
+
+// A launch's parameters: the step and the phases, by value.  They reach the kernel through the constant bank, so
+// walking the phases costs no trip to memory (a phase's record read from global memory at every phase boundary cost
+// about a microsecond of latency per phase, in the consumer and again in the producer of the weight stream).
+struct StepParams {
+    Step step;
+    Phase phases[kMaxPhases];
+};
 
 // Where a warp's weight stream stands: the phases, the block's tiles of a phase and the warp's steps over its slice
 // of K, flattened into one sequence of stages.  The producer runs kDepth - 1 stages ahead of the consumer.
 struct Stream {
     int phase;        // index of the phase the next stage belongs to; num_phases when the stream has ended
     int tile;         // row tile of that stage
-    int step;         // 64-column step within the warp's slice
+    int step;         // 128-column step within the warp's slice
     int steps;        // steps of the slice in this phase
     int kind, rows, tiles, pair_offset, ldw;
     int k0, k1;       // the warp's columns [k0, k1) of the (sub-)phase
     const bf16* w;
+    const bf16* row[2];  // of the current tile: this lane's two weight rows (MMA rows group_id and group_id + 8)
 };
 
+// The first row tile of a team in a phase, and the distance to its next: the teams of all blocks take the tiles in turn.
+__device__ __forceinline__ int first_tile(int team) { return team * gridDim.x + blockIdx.x; }
+__device__ __forceinline__ int tile_stride() { return kTeams * gridDim.x; }
+
+// This lane's two weight rows of a tile: 16 consecutive rows, or 8 rows and their partners.
+__device__ __forceinline__ void stream_rows(Stream& s, int lane) {
+    const int group_id = lane >> 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        int row;
+        if (s.kind == PH_GATE_UP) {
+            row = min(s.rows - 1, s.tile * 8 + group_id) + h * s.pair_offset;
+        } else if (s.kind == PH_QKV) {  // tile = (head, eighth of its first half); the partner lies half a head further
+            constexpr int tiles_per_head = HD / 16;
+            row = (s.tile / tiles_per_head) * HD + (s.tile % tiles_per_head) * 8 + group_id + h * (HD / 2);
+        } else {
+            row = min(s.rows - 1, s.tile * 16 + group_id + 8 * h);
+        }
+        s.row[h] = s.w + (size_t)row * s.ldw;
+    }
+}
+
 __device__ __forceinline__ int slice_steps(const Phase& p, int warp, int* k0, int* k1) {
-    const int per_warp = p.k_pad / kStepWarps;
-    *k0 = min(p.k_len, warp * per_warp);
+    const int per_warp = p.k_pad / kTeamWarps;
+    *k0 = min(p.k_len, (warp % kTeamWarps) * per_warp);
     *k1 = min(p.k_len, *k0 + per_warp);
     return (*k1 - *k0 + kStageCols - 1) / kStageCols;
 }
 
 // Moves the stream to the first stage at or after phase `from` (a matrix phase in which this block has a tile and
 // this warp a slice of K).
-__device__ __forceinline__ void stream_seek(Stream& s, const Step& step, int from, int warp) {
+__device__ __forceinline__ void stream_seek(Stream& s, const Step& step, const Phase* phases, int from, int warp) {
     for (int ph = from; ph < step.num_phases; ++ph) {
-        const Phase& p = step.phases[ph];
-        if (p.kind == PH_EMBED || p.kind == PH_ATTN || (int)blockIdx.x >= p.tiles) continue;
+        const Phase& p = phases[ph];
+        if (p.kind == PH_EMBED || p.kind == PH_ATTN || first_tile(warp / kTeamWarps) >= p.tiles) continue;
         int k0, k1;
         const int steps = slice_steps(p, warp, &k0, &k1);
         if (steps == 0) continue;
-        s.phase = ph; s.tile = blockIdx.x; s.step = 0; s.steps = steps;
+        s.phase = ph; s.tile = first_tile(warp / kTeamWarps); s.step = 0; s.steps = steps;
         s.kind = p.kind; s.rows = p.rows; s.tiles = p.tiles; s.pair_offset = p.pair_offset; s.ldw = p.ldw;
         s.k0 = k0; s.k1 = k1; s.w = p.w;
+        stream_rows(s, threadIdx.x & 31);
         return;
     }
     s.phase = step.num_phases;
@@ -181,36 +224,26 @@ __device__ __forceinline__ void stream_seek(Stream& s, const Step& step, int fro
 
 // Issues the loads of the stream's next stage into ring slot `slot` and moves the stream on.  Always one commit
 // group, also when the stream has ended: the consumer's waits count groups.
-__device__ __forceinline__ void stream_produce(Stream& s, const Step& step, uint32_t ring, int slot, int warp, int lane) {
+__device__ __forceinline__ void stream_produce(Stream& s, const Step& step, const Phase* phases, uint32_t ring, int slot, int warp, int lane) {
     if (s.phase < step.num_phases) {
-        const int group_id = lane >> 2, tid4 = lane & 3;
+        const int tid4 = lane & 3;
         const uint32_t stage = ring + slot * kStageBytes;
         const int kc = s.k0 + s.step * kStageCols + 8 * tid4;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            // MMA rows group_id and group_id + 8: 16 consecutive weight rows, or 8 rows and their partners
-            int row;
-            if (s.kind == PH_GATE_UP) {
-                row = min(s.rows - 1, s.tile * 8 + group_id) + h * s.pair_offset;
-            } else if (s.kind == PH_QKV) {  // tile = (head, eighth of its first half); the partner lies half a head further
-                constexpr int tiles_per_head = HD / 16;
-                row = (s.tile / tiles_per_head) * HD + (s.tile % tiles_per_head) * 8 + group_id + h * (HD / 2);
-            } else {
-                row = min(s.rows - 1, s.tile * 16 + group_id + 8 * h);
-            }
-            const bf16* w_row = s.w + (size_t)row * s.ldw;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < kPieces; ++c) {
                 const int kk = kc + 32 * c;
-                const uint32_t dst = stage + ((h * 2 + c) * 32 + lane) * 16;
-                if (kk < s.k1) cp_async16_mem(dst, w_row + kk);
+                const uint32_t dst = stage + ((h * kPieces + c) * 32 + lane) * 16;
+                if (kk < s.k1) cp_async16_mem(dst, s.row[h] + kk);
                 else sts128_zero(dst);
             }
         }
         if (++s.step == s.steps) {
             s.step = 0;
-            s.tile += gridDim.x;
-            if (s.tile >= s.tiles) stream_seek(s, step, s.phase + 1, warp);
+            s.tile += tile_stride();
+            if (s.tile >= s.tiles) stream_seek(s, step, phases, s.phase + 1, warp);
+            else stream_rows(s, lane);
         }
     }
     cp_async_commit_mem();
@@ -286,42 +319,17 @@ __device__ __forceinline__ void stage_normed(const Step& step, const Phase& p, u
     }
 }
 
-// Rows of a bfloat16 buffer (the gated activations), columns [k_begin, k_begin + k_len).
-__device__ __forceinline__ void stage_bf16(const Step& step, const Phase& p, uint32_t smem_base, const bf16* from, int ld) {
+// Rows of a bfloat16 buffer (the gated activations or the attention's output), columns [k_begin, k_begin + k_len).
+// Plain loads, not cp.async: waiting for these copies must not wait for the weight ring's newest stages too.
+__device__ __forceinline__ void stage_bf16(const Step& step, const Phase& p, unsigned char* smem, const bf16* from, int ld) {
     const int x_stride = p.k_pad * 2 + 64;
     const int chunks = p.k_len / 8;
-    for (int b = 0; b < step.batch; ++b) {
-        const bf16* src = from + (size_t)b * ld + p.k_begin;
-        for (int c = threadIdx.x; c < chunks; c += kStepThreads) cp_async16_mem(smem_base + b * x_stride + c * 16, src + c * 8);
-    }
-}
-
-// The attention's output rows, combined from the partial results of the split keys while they are staged: with
-// (m_s, l_s, o_s) of split s, m = max m_s, out = sum o_s 2^(m_s - m) / sum l_s 2^(m_s - m).
-__device__ __forceinline__ void stage_attention(const Step& step, const Phase& p, unsigned char* smem) {
-    const int x_stride = p.k_pad * 2 + 64;
-    const int splits = step.splits[p.group];
-    const int quads = HD / 4;
-    const int total = step.batch * p.heads * quads;
+    const int total = step.batch * chunks;
+#pragma unroll 8
     for (int i = threadIdx.x; i < total; i += kStepThreads) {
-        const int quad = i % quads, head = (i / quads) % p.heads, b = i / (quads * p.heads);
-        const size_t slot = (size_t)(b * p.heads + head) * splits;
-        float m = -CUDART_INF_F;
-        for (int s = 0; s < splits; ++s) m = fmaxf(m, __ldcg(step.attn_ml + (slot + s) * 2));
-        float sum = 0.0f;
-        float4 value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int s = 0; s < splits; ++s) {
-            const float weight = fast_exp2(__ldcg(step.attn_ml + (slot + s) * 2) - m);  // 0 for a split that saw nothing
-            if (weight > 0.0f) {
-                sum += __ldcg(step.attn_ml + (slot + s) * 2 + 1) * weight;
-                const float4 o = __ldcg(reinterpret_cast<const float4*>(step.attn_o + (slot + s) * HD + quad * 4));
-                value.x += o.x * weight; value.y += o.y * weight; value.z += o.z * weight; value.w += o.w * weight;
-            }
-        }
-        const float inv = 1.0f / sum;
-        const int col = head * HD + quad * 4 - p.k_begin;  // (the output product is never split: k_begin is 0)
-        *reinterpret_cast<uint2*>(smem + b * x_stride + col * 2) =
-            make_uint2(pack_bf16(value.x * inv, value.y * inv), pack_bf16(value.z * inv, value.w * inv));
+        const int b = i / chunks, c = i % chunks;
+        *reinterpret_cast<uint4*>(smem + b * x_stride + c * 16) =
+            __ldcg(reinterpret_cast<const uint4*>(from + (size_t)b * ld + p.k_begin + c * 8));
     }
 }
 
@@ -367,7 +375,23 @@ __device__ __forceinline__ void attention_item(const Step& step, const Phase& p,
     float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
-    // the query rows of this kv head's group
+    // the first pages are asked for before anything else; then the query rows of this kv head's group
+    const int* table = step.block_tables[p.group] + (size_t)seq * step.max_blocks;
+    const uint32_t ring = rings + warp * kAttnStages * kAttnStageBytes;
+    auto fetch = [&](int t, int stage) {
+        const size_t page = table[t];
+        const size_t at = ((page * p.kv_heads + kv_head) * kTile + sub * 16) * (size_t)HD;
+        load_rows16(ring + stage * kAttnStageBytes, p.k_pool + at, lane);
+        load_rows16(ring + stage * kAttnStageBytes + 16 * kRowBytes, p.v_pool + at, lane);
+    };
+    const int t0 = t_begin + lane_page;
+    if (works && t_begin < t_end) {
+#pragma unroll
+        for (int ahead = 0; ahead < kAttnStages - 1; ++ahead) {
+            if (t0 + ahead * kPagesAtOnce < t_end) fetch(t0 + ahead * kPagesAtOnce, ahead);
+            cp_async_commit();
+        }
+    }
     for (int i = threadIdx.x; i < kQRowsDecode * kChunks; i += kStepThreads) {
         const int row = i / kChunks, c = i % kChunks;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -376,20 +400,6 @@ __device__ __forceinline__ void attention_item(const Step& step, const Phase& p,
     }
     __syncthreads();
     if (works && t_begin < t_end) {
-        const int* table = step.block_tables[p.group] + (size_t)seq * step.max_blocks;
-        const uint32_t ring = rings + warp * kAttnStages * kAttnStageBytes;
-        auto fetch = [&](int t, int stage) {
-            const size_t page = table[t];
-            const size_t at = ((page * p.kv_heads + kv_head) * kTile + sub * 16) * (size_t)HD;
-            load_rows16(ring + stage * kAttnStageBytes, p.k_pool + at, lane);
-            load_rows16(ring + stage * kAttnStageBytes + 16 * kRowBytes, p.v_pool + at, lane);
-        };
-        const int t0 = t_begin + lane_page;
-#pragma unroll
-        for (int ahead = 0; ahead < kAttnStages - 1; ++ahead) {
-            if (t0 + ahead * kPagesAtOnce < t_end) fetch(t0 + ahead * kPagesAtOnce, ahead);
-            cp_async_commit();
-        }
         uint32_t a[kKSteps][4];
         load_q_fragments(a, smem_u32(q_smem));
         int round = 0;
@@ -485,11 +495,50 @@ __device__ __forceinline__ void attention_item(const Step& step, const Phase& p,
                 value += merge_o[(size_t)(w * 16 + row) * HD + d] * weight;
             }
         }
-        const size_t slot = (size_t)(seq * p.heads + head0 + row) * splits + split;
-        step.attn_o[slot * HD + d] = value;
-        if (d == 0) {
-            step.attn_ml[slot * 2] = m;
-            step.attn_ml[slot * 2 + 1] = total;
+        if (splits == 1) {
+            step.a[(size_t)seq * step.ld_q + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(value * (1.0f / total));
+        } else {
+            const size_t slot = (size_t)(seq * p.heads + head0 + row) * splits + split;
+            step.attn_o[slot * HD + d] = value;
+            if (d == 0) {
+                step.attn_ml[slot * 2] = m;
+                step.attn_ml[slot * 2 + 1] = total;
+            }
+        }
+    }
+    if (splits > 1) {
+        // whichever split's block stores last combines them all, in the order of the splits (the same additions whoever
+        // that is): with (m_s, l_s, o_s) of split s, m = max m_s, out = sum o_s 2^(m_s - m) / sum l_s 2^(m_s - m)
+        __shared__ int last_split;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int* ticket = step.attn_tickets + seq * (p.kv_heads * ((group + 15) / 16)) + kv_head * ((group + 15) / 16) + chunk;
+            last_split = atomicAdd(ticket, 1) == splits - 1;
+            if (last_split) *ticket = 0;  // as the next step expects it
+            __threadfence();
+        }
+        __syncthreads();
+        if (last_split) {
+            for (int i = threadIdx.x; i < rows_here * (HD / 4); i += kStepThreads) {
+                const int row = i / (HD / 4), quad = i % (HD / 4);
+                const size_t slot = (size_t)(seq * p.heads + head0 + row) * splits;
+                float m = -CUDART_INF_F;
+                for (int sp = 0; sp < splits; ++sp) m = fmaxf(m, __ldcg(step.attn_ml + (slot + sp) * 2));
+                float sum = 0.0f;
+                float4 value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int sp = 0; sp < splits; ++sp) {
+                    const float weight = fast_exp2(__ldcg(step.attn_ml + (slot + sp) * 2) - m);  // 0 for a split that saw nothing
+                    if (weight > 0.0f) {
+                        sum += __ldcg(step.attn_ml + (slot + sp) * 2 + 1) * weight;
+                        const float4 o4 = __ldcg(reinterpret_cast<const float4*>(step.attn_o + (slot + sp) * HD + quad * 4));
+                        value.x += o4.x * weight; value.y += o4.y * weight; value.z += o4.z * weight; value.w += o4.w * weight;
+                    }
+                }
+                const float inv = 1.0f / sum;
+                *reinterpret_cast<uint2*>(step.a + (size_t)seq * step.ld_q + (size_t)(head0 + row) * HD + quad * 4) =
+                    make_uint2(pack_bf16(value.x * inv, value.y * inv), pack_bf16(value.z * inv, value.w * inv));
+            }
         }
     }
     __syncthreads();  // the next item reuses the shared memory
@@ -498,29 +547,38 @@ __device__ __forceinline__ void attention_item(const Step& step, const Phase& p,
 // ------------------------------------------------------------------------------------ the kernel
 
 __global__ void __launch_bounds__(kStepThreads, 1)
-decode_step_kernel(const Step step) {
+decode_step_kernel(const __grid_constant__ StepParams params) {
+    const Step& step = params.step;
+    const Phase* phases = params.phases;
     extern __shared__ __align__(128) unsigned char smem[];
     const uint32_t smem_base = smem_u32(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
     const uint32_t ring = smem_base + kFrontBytes + warp * kDepth * kStageBytes;
-    float* partial = reinterpret_cast<float*>(smem + kFrontBytes + kRingBytes);  // two buffers
-    float* sq_total = partial + 2 * kPartialFloats;                              // [kCols]
+    const int team = warp / kTeamWarps, team_warp = warp % kTeamWarps, team_thread = threadIdx.x % kTeamThreads;
+    float* partial = reinterpret_cast<float*>(smem + kFrontBytes + kRingBytes) + team * 2 * kPartialFloats;  // this team's two buffers
+    float* sq_total = reinterpret_cast<float*>(smem + kFrontBytes + kRingBytes) + kTeams * 2 * kPartialFloats;  // [kCols]
     float* sq_warp = sq_total + kCols;                                           // [warps][kCols]
 
     // the weight stream starts at once: weights depend on nothing
     Stream stream;
-    stream_seek(stream, step, 0, warp);
+    stream_seek(stream, step, phases, 0, warp);
     int produce_slot = 0, consume_slot = 0;
     for (int s = 0; s < kDepth - 1; ++s) {
-        stream_produce(stream, step, ring, produce_slot, warp, lane);
+        stream_produce(stream, step, phases, ring, produce_slot, warp, lane);
         produce_slot = (produce_slot + 1) % kDepth;
     }
 
     unsigned int epoch = 0;
     int tile_parity = 0;
+    const bool timed = step.timeline != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
     for (int ph = 0; ph < step.num_phases; ++ph) {
-        const Phase& p = step.phases[ph];
+        const Phase& p = phases[ph];
+        if (timed) {
+            if (ph > 0) step.timeline[(ph - 1) * 6 + 3] = clock64();
+            step.timeline[ph * 6] = clock64();
+        }
         if (p.barrier_before && !grid_barrier(step, ++epoch, ph)) break;
+        if (timed) step.timeline[ph * 6 + 1] = step.timeline[ph * 6 + 2] = clock64();
 
         if (p.kind == PH_EMBED) {
             // x = E[token] * scale, a row per block (backend-java/.../llama/LlamaForwardPass.java:1024-1025)
@@ -552,101 +610,123 @@ decode_step_kernel(const Step step) {
             for (int c = live + threadIdx.x; c < chunks_padded; c += kStepThreads) sts128_zero(smem_base + b * x_stride + c * 16);
         }
         if (p.gain) stage_normed(step, p, smem, sq_total, sq_warp);
-        else if (p.kind == PH_OUT) stage_attention(step, p, smem);
-        else stage_bf16(step, p, smem_base, step.h, step.ld_h);
-        if (!p.gain && p.kind != PH_OUT) {
-            // the copies of this staging are the newest groups: wait for all (the ring's older groups have long landed)
-            cp_async_commit_mem();
-            cp_async_wait_mem<0>();
-        }
+        else if (p.kind == PH_OUT) stage_bf16(step, p, smem, step.a, step.ld_q);
+        else stage_bf16(step, p, smem, step.h, step.ld_h);
         __syncthreads();
+        if (timed) step.timeline[ph * 6 + 2] = clock64();
 
-        // ---- this block's row tiles; the ring keeps running across them
+        // ---- the row tiles of this warp's team; the ring keeps running across them
         const bool paired = p.kind == PH_GATE_UP || p.kind == PH_QKV;
         const int tile_rows = paired ? 8 : 16;
+        const int rows_total = p.kind == PH_QKV ? p.rows / 2 : p.rows;  // rows, or pairs
         int k0, k1;
         const int steps = slice_steps(p, warp, &k0, &k1);
         const uint32_t x_lane = smem_base + group_id * x_stride + (k0 + 8 * tid4) * 2;
-        for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x) {
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // the thread of the team that finishes output (row_in_tile, col) of every tile, and what it needs besides the
+        // sums: fetched before a tile's products so that it is there when they are done
+        const bool finisher = team_thread < tile_rows * kCols;
+        const int row_in_tile = team_thread % tile_rows, col = team_thread / tile_rows;
+        const bool live_col = finisher && col < step.batch;
+        int position = 0, cache_slot = -1;
+        float inv_rms = 1.0f;
+        if (live_col) {
+            if (p.gain) inv_rms = 1.0f / sqrtf(sq_total[col] / (float)p.k_len + p.eps);
+            if (p.kind == PH_QKV) {
+                position = step.positions[col];
+                cache_slot = step.slot_mappings[p.group][col];
+            }
+        }
+        for (int tile = first_tile(team); tile < p.tiles; tile += tile_stride()) {
+            const int row = tile * tile_rows + row_in_tile;
+            const bool live = live_col && row < rows_total;
+            float before = 0.0f, rope_cos = 1.0f, rope_sin = 0.0f;
+            float* x_at = nullptr;
+            constexpr int tiles_per_head = HD / 16, half_head = HD / 2;
+            const int head = tile / tiles_per_head, d0 = (tile % tiles_per_head) * 8 + row_in_tile;  // of a q/k/v tile
+            if (live) {
+                if (p.kind == PH_OUT || p.kind == PH_DOWN) {
+                    x_at = step.x + (size_t)col * step.hidden + row;  // this thread alone owns the element in this phase
+                    before = __ldcg(x_at);
+                } else if (p.kind == PH_QKV && head < p.heads + p.kv_heads) {
+                    rope_cos = p.cos_table[(size_t)position * half_head + d0];
+                    rope_sin = p.sin_table[(size_t)position * half_head + d0];
+                }
+            }
+            float acc[2 * kPieces][4];  // independent chains of products, added at the end
+#pragma unroll
+            for (int i = 0; i < 2 * kPieces; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
             for (int s = 0; s < steps; ++s) {
-                stream_produce(stream, step, ring, produce_slot, warp, lane);
-                produce_slot = (produce_slot + 1) % kDepth;
+                stream_produce(stream, step, phases, ring, produce_slot, warp, lane);
+                produce_slot = produce_slot + 1 == kDepth ? 0 : produce_slot + 1;
                 cp_async_wait_mem<kDepth - 1>();  // this lane's pieces of the stage have landed; nobody else reads them
                 const uint32_t stage = ring + consume_slot * kStageBytes;
-                consume_slot = (consume_slot + 1) % kDepth;
-                uint4 wv[2][2];
+                consume_slot = consume_slot + 1 == kDepth ? 0 : consume_slot + 1;
+                uint4 wv[2][kPieces];
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) wv[h][c] = lds128(stage + ((h * 2 + c) * 32 + lane) * 16);
+                    for (int c = 0; c < kPieces; ++c) wv[h][c] = lds128(stage + ((h * kPieces + c) * 32 + lane) * 16);
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < kPieces; ++c) {
                     const uint4 xv = lds128(x_lane + (s * kStageCols + 32 * c) * 2);
-                    mma_16816(acc, wv[0][c].x, wv[1][c].x, wv[0][c].y, wv[1][c].y, xv.x, xv.y);
-                    mma_16816(acc, wv[0][c].z, wv[1][c].z, wv[0][c].w, wv[1][c].w, xv.z, xv.w);
+                    mma_16816(acc[2 * c], wv[0][c].x, wv[1][c].x, wv[0][c].y, wv[1][c].y, xv.x, xv.y);
+                    mma_16816(acc[2 * c + 1], wv[0][c].z, wv[1][c].z, wv[0][c].w, wv[1][c].w, xv.z, xv.w);
                 }
             }
             // the warps' partial sums: c0, c1 = (MMA row group_id, activation rows 2 * tid4, + 1); c2, c3 = row + 8
+            if (timed && tile == (int)blockIdx.x) step.timeline[ph * 6 + 4] = clock64();
             float* mine = partial + tile_parity * kPartialFloats;
             tile_parity ^= 1;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) mine[(warp * 16 + group_id + 8 * (i >> 1)) * kCols + tid4 * 2 + (i & 1)] = acc[i];
-            __syncthreads();
-            if (threadIdx.x < tile_rows * kCols) {
-                const int row_in_tile = threadIdx.x % tile_rows, col = threadIdx.x / tile_rows;
-                const int row = tile * tile_rows + row_in_tile;
-                const int rows_total = p.kind == PH_QKV ? p.rows / 2 : p.rows;  // rows, or pairs
-                if (row < rows_total && col < step.batch) {
-                    float value = 0.0f, second = 0.0f;  // second: the partner row of a pair
+            for (int i = 0; i < 4; ++i)
+            {
+                float sum = 0.0f;
 #pragma unroll
-                    for (int w = 0; w < kStepWarps; ++w) {
-                        value += mine[(w * 16 + row_in_tile) * kCols + col];
-                        if (paired) second += mine[(w * 16 + row_in_tile + 8) * kCols + col];
+                for (int chain = 0; chain < 2 * kPieces; ++chain) sum += acc[chain][i];
+                mine[(team_warp * 16 + group_id + 8 * (i >> 1)) * kCols + tid4 * 2 + (i & 1)] = sum;
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(kTeamThreads) : "memory");  // the team's warps meet; the other team runs on
+            if (live) {
+                float value = 0.0f, second = 0.0f;  // second: the partner row of a pair
+#pragma unroll
+                for (int w = 0; w < kTeamWarps; ++w) {
+                    value += mine[(w * 16 + row_in_tile) * kCols + col];
+                    if (paired) second += mine[(w * 16 + row_in_tile + 8) * kCols + col];
+                }
+                value *= inv_rms;
+                second *= inv_rms;
+                if (p.kind == PH_HEAD) {
+                    step.logits[(size_t)col * step.ld_logits + row] = value;
+                } else if (p.kind == PH_OUT || p.kind == PH_DOWN) {
+                    __stcg(x_at, before + value);
+                } else if (p.kind == PH_GATE_UP) {
+                    step.h[(size_t)col * step.ld_h + row] = __float2bfloat16_rn(gate_activation(p.activation, value) * second);
+                } else {  // PH_QKV
+                    // queries and keys pass through bfloat16 before the rotation, as they do when a product stores them
+                    float x0 = __bfloat162float(__float2bfloat16_rn(value)), x1 = __bfloat162float(__float2bfloat16_rn(second));
+                    if (head < p.heads + p.kv_heads) {
+                        const float r0 = x0 * rope_cos - x1 * rope_sin, r1 = x0 * rope_sin + x1 * rope_cos;
+                        x0 = r0;
+                        x1 = r1;
                     }
-                    if (p.gain) {
-                        const float inv_rms = 1.0f / sqrtf(sq_total[col] / (float)p.k_len + p.eps);
-                        value *= inv_rms;
-                        second *= inv_rms;
-                    }
-                    if (p.kind == PH_HEAD) {
-                        step.logits[(size_t)col * step.ld_logits + row] = value;
-                    } else if (p.kind == PH_OUT || p.kind == PH_DOWN) {
-                        step.x[(size_t)col * step.hidden + row] += value;  // this block alone owns the row in this phase
-                    } else if (p.kind == PH_GATE_UP) {
-                        step.h[(size_t)col * step.ld_h + row] = __float2bfloat16_rn(gate_activation(p.activation, value) * second);
-                    } else {  // PH_QKV
-                        constexpr int tiles_per_head = HD / 16, half = HD / 2;
-                        const int head = tile / tiles_per_head, d0 = (tile % tiles_per_head) * 8 + row_in_tile;
-                        // queries and keys pass through bfloat16 before the rotation, as they do when a product stores them
-                        float x0 = __bfloat162float(__float2bfloat16_rn(value)), x1 = __bfloat162float(__float2bfloat16_rn(second));
-                        if (head < p.heads + p.kv_heads) {
-                            const size_t at_table = (size_t)step.positions[col] * half + d0;
-                            const float c = p.cos_table[at_table], sn = p.sin_table[at_table];
-                            const float r0 = x0 * c - x1 * sn, r1 = x0 * sn + x1 * c;
-                            x0 = r0;
-                            x1 = r1;
-                        }
-                        if (head < p.heads) {
-                            bf16* q = step.q + (size_t)col * step.ld_q + (size_t)head * HD;
-                            q[d0] = __float2bfloat16_rn(x0);
-                            q[d0 + half] = __float2bfloat16_rn(x1);
-                        } else {
-                            const int slot = step.slot_mappings[p.group][col];
-                            if (slot >= 0) {
-                                const bool is_key = head < p.heads + p.kv_heads;
-                                const int kv_head = head - p.heads - (is_key ? 0 : p.kv_heads);
-                                const size_t page = slot / kTile, offset = slot % kTile;
-                                bf16* dst = (is_key ? p.k_pool : p.v_pool) + ((page * p.kv_heads + kv_head) * kTile + offset) * HD;
-                                dst[d0] = __float2bfloat16_rn(x0);
-                                dst[d0 + half] = __float2bfloat16_rn(x1);
-                            }
-                        }
+                    if (head < p.heads) {
+                        bf16* q = step.q + (size_t)col * step.ld_q + (size_t)head * HD;
+                        q[d0] = __float2bfloat16_rn(x0);
+                        q[d0 + half_head] = __float2bfloat16_rn(x1);
+                    } else if (cache_slot >= 0) {
+                        const bool is_key = head < p.heads + p.kv_heads;
+                        const int kv_head = head - p.heads - (is_key ? 0 : p.kv_heads);
+                        const size_t page = cache_slot / kTile, offset = cache_slot % kTile;
+                        bf16* dst = (is_key ? p.k_pool : p.v_pool) + ((page * p.kv_heads + kv_head) * kTile + offset) * HD;
+                        dst[d0] = __float2bfloat16_rn(x0);
+                        dst[d0 + half_head] = __float2bfloat16_rn(x1);
                     }
                 }
             }
+            if (timed && tile == (int)blockIdx.x) step.timeline[ph * 6 + 5] = clock64();
         }
     }
+    if (timed) step.timeline[(step.num_phases - 1) * 6 + 3] = clock64();
     cp_async_wait_mem<0>();  // nothing of this block is in flight when it leaves
 }
 
@@ -661,13 +741,19 @@ MB_EXPORT int mb_decode_step_max_columns() { return kMaxStageCols; }
 MB_EXPORT int mb_decode_step_slice_columns() { return kSliceCols; }
 MB_EXPORT int mb_decode_step_max_groups() { return kMaxGroups; }
 
-// Runs one decode step.  `step` (host memory) is copied; its `phases` point to device memory.  The barrier counter is
+// Runs one decode step.  `step` and its `phases` (both host memory) are copied into the launch's parameters.  The barrier counter is
 // set to zero on the stream first.  Blocks: one per multiprocessor, launched cooperatively (all resident, or the
 // launch fails).
+MB_EXPORT int mb_decode_step_max_phases() { return kMaxPhases; }
+
 MB_EXPORT int mb_decode_step(const Step* given, int multiprocessors, cudaStream_t stream) {
-    const Step step = *given;
+    static thread_local StepParams params;  // (32 KB: not on the stack)
+    params.step = *given;
+    const Step& step = params.step;
+    if (step.num_phases < 1 || step.num_phases > kMaxPhases || !step.phases)
+        return fail("decode_step: takes 1 to %d phases, got %d", kMaxPhases, step.num_phases);
+    memcpy(params.phases, step.phases, sizeof(Phase) * step.num_phases);
     if (step.batch < 1 || step.batch > kCols) return fail("decode_step: takes 1 to %d sequences, got %d", kCols, step.batch);
-    if (step.num_phases < 1 || !step.phases) return fail("decode_step: no phases");
     if (step.hidden % 8 || ((uintptr_t)step.x & 15) || ((uintptr_t)step.q & 15) || ((uintptr_t)step.h & 15) || step.ld_q % 8 || step.ld_h % 8)
         return fail("decode_step: rows of the residual stream, queries and gated activations must start on 16-byte boundaries");
     if (!step.barrier || !step.status) return fail("decode_step: needs a barrier counter and a status word");
@@ -694,7 +780,7 @@ MB_EXPORT int mb_decode_step(const Step* given, int multiprocessors, cudaStream_
     attribute[0].val.cooperative = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    status = cudaLaunchKernelEx(&config, decode_step_kernel, step);
+    status = cudaLaunchKernelEx(&config, decode_step_kernel, params);
     if (status != cudaSuccess) return fail("decode_step: launch failed: %s", cudaGetErrorString(status));
     return check_launch("decode_step");
 }

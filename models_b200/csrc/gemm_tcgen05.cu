@@ -118,7 +118,7 @@ struct GemmArgs {
     int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int k_splits;         // EPI_RESIDUAL: blocks that share an output tile, each with its own part of K (else 1)
     float* partial;       // k_splits > 1: [tile][block of a pair][part of K][128 rows][tile columns] floats, or null
-    int* tickets;         // k_splits > 1 with `partial`: [tile][block of a pair][8 epilogue warps], zero before and after a launch
+    int* tickets;         // k_splits > 1 with `partial`: [tile][block of a pair][8 epilogue warps][arrived, finished], zero before and after a launch
     void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream; EPI_ROPE: the queries [m, heads * head_dim]
     int ld_out;
     // EPI_ROPE: W is [q heads; k heads; v heads]
@@ -449,45 +449,72 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 else mbar_arrive(acc_empty_bar + 8 * acc);
             }
             if (ordered) {
-                // The parts of K of this warp's rows and columns: whichever block's warp stores last adds all of
-                // them, in the order of the parts, and adds the sum into the stream -- the same additions in the
-                // same order whoever that is, so the result does not depend on timing.  Nobody waits.
+                // The parts of K of this warp's rows and columns lie in scratch memory once the same warp of every
+                // block that shares the tile has stored its own.  Each of them then sums a share of the rows over all
+                // parts, in the order of the parts -- the same additions in the same order whenever it runs -- and adds
+                // the sum into the stream.  The blocks of a tile run at the same time (K is split only while all work
+                // items fit one round of blocks), so the wait is short; it is bounded all the same.
                 __threadfence();
                 __syncwarp();
-                int* ticket_slot = args.tickets + (size_t)(mn_tile * kPair + rank) * kEpilogueWarps + (warp - 2);
-                int ticket = 0;
-                if (lane == 0) ticket = atomicAdd(ticket_slot, 1);
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                if (ticket == k_splits - 1) {
-                    __threadfence();
-                    if (lane == 0) *ticket_slot = 0;  // as the next launch expects it
+                int* arrived = args.tickets + ((size_t)(mn_tile * kPair + rank) * kEpilogueWarps + (warp - 2)) * 2;
+                int* finished = arrived + 1;
+                bool all_stored = true;
+                if (lane == 0) {
+                    atomicAdd(arrived, 1);
+                    int seen = 0;
+                    const long long start = clock64();
+                    do {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(arrived) : "memory");
+                    } while (seen < k_splits && clock64() - start < kWaitCycles);
+                    all_stored = seen >= k_splits;
+                    if (!all_stored) atomicCAS(&g_gemm_status, 0, 1 + (5 << 8));  // role 5: the parts of K
+                }
+                all_stored = __shfl_sync(0xffffffffu, all_stored, 0);
+                if (all_stored) {
+                    const int split = tile % k_splits;
                     const float* parts = args.partial + (size_t)(mn_tile * kPair + rank) * k_splits * (kBlockM * kOutCols);
+                    constexpr int kChunks = kHalfCols / 32;
 #pragma unroll 1
-                    for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 32) {
-                        const int col = n0 + c + (lane & 7) * 4;
-#pragma unroll 1
-                        for (int pass = 0; pass < 8; ++pass) {
-                            const int r = 4 * pass + (lane >> 3);
-                            const int out_row = m0 + quarter * 32 + r;
-                            if (out_row >= args.m || col >= args.n) continue;
-                            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                            const float* at = parts + (size_t)(quarter * 32 + r) * kOutCols + c + (lane & 7) * 4;
-                            for (int part = 0; part < k_splits; ++part) {
-                                const float4 p = __ldcg(reinterpret_cast<const float4*>(at + (size_t)part * (kBlockM * kOutCols)));
-                                sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+                    for (int pass = split; pass < 8; pass += k_splits) {  // four rows per pass, dealt out over the parts' blocks
+                        const int r = 4 * pass + (lane >> 3);
+                        const int out_row = m0 + quarter * 32 + r;
+                        if (out_row >= args.m) continue;
+                        float4 sum[kChunks];
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ++ch) sum[ch] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        const float* at = parts + (size_t)(quarter * 32 + r) * kOutCols + half * kHalfCols + (lane & 7) * 4;
+#pragma unroll 4
+                        for (int part = 0; part < k_splits; ++part) {
+#pragma unroll
+                            for (int ch = 0; ch < kChunks; ++ch) {
+                                if (n0 + half * kHalfCols + ch * 32 + (lane & 7) * 4 < args.n) {
+                                    const float4 p = __ldcg(reinterpret_cast<const float4*>(at + (size_t)part * (kBlockM * kOutCols) + ch * 32));
+                                    sum[ch].x += p.x; sum[ch].y += p.y; sum[ch].z += p.z; sum[ch].w += p.w;
+                                }
                             }
+                        }
+#pragma unroll
+                        for (int ch = 0; ch < kChunks; ++ch) {
+                            const int col = n0 + half * kHalfCols + ch * 32 + (lane & 7) * 4;
+                            if (col >= args.n) continue;
                             float* dst = reinterpret_cast<float*>(args.out) + (size_t)out_row * args.ld_out + col;
                             if (col + 4 <= args.n) {
-                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(sum.x), "f"(sum.y), "f"(sum.z), "f"(sum.w)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(sum[ch].x), "f"(sum[ch].y),
+                                             "f"(sum[ch].z), "f"(sum[ch].w)
                                              : "memory");
                             } else {
-                                const float v[4] = {sum.x, sum.y, sum.z, sum.w};
+                                const float v[4] = {sum[ch].x, sum[ch].y, sum[ch].z, sum[ch].w};
 #pragma unroll
                                 for (int i = 0; i < 4; ++i)
                                     if (col + i < args.n) dst[i] += v[i];  // the only addition into this element
                             }
                         }
                     }
+                }
+                __syncwarp();
+                if (lane == 0 && atomicAdd(finished, 1) == k_splits - 1) {  // everyone has read: as the next launch expects them
+                    *arrived = 0;
+                    *finished = 0;
                 }
             }
             if (++acc == 2) {
@@ -510,9 +537,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // Few tiles and a long K (a prompt of a few hundred tokens; the down product above all): with the residual epilogue,
 // parts of K go to blocks of their own, at least 8 steps of 64 each and at most 8 parts, and every part adds its sum
-// to the residual stream.  Given scratch memory, every part stores its sum there and the block that stores last adds
-// the parts in their order (a ticket per tile and epilogue warp; nobody waits), so a result is the same bits in every
-// run; without scratch each part adds into the stream as it finishes, in no fixed order, and an element's last bit may
+// to the residual stream.  Given scratch memory, every part stores its sum there, and once all parts of a tile are
+// stored each of its blocks adds a share of the rows over the parts, in their order, so a result is the same bits in
+// every run; without scratch each part adds into the stream as it finishes, in no fixed order, and an element's last bit may
 // differ from run to run.  Measured at 256 rows, K = 8192, N = 2048: 40 us as 16 tiles, 15 us as 8 parts each, 14 us for
 // the library's kernel.  `units`: blocks (or pairs) that run at once.
 static int residual_k_splits(long tiles, int k, int units) {
@@ -619,7 +646,7 @@ using namespace mb;
 // most 128 x 256 floats, and eight tickets for each.
 MB_EXPORT void mb_gemm_tcgen05_scratch(int multiprocessors, size_t* partial_floats, size_t* ticket_ints) {
     *partial_floats = (size_t)multiprocessors * kBlockM * 256;
-    *ticket_ints = (size_t)multiprocessors * kEpilogueWarps;
+    *ticket_ints = (size_t)multiprocessors * kEpilogueWarps * 2;
 }
 
 // partial, tickets: scratch for the residual epilogue when K is split over blocks (mb_gemm_tcgen05_scratch says how much;

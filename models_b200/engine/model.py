@@ -38,6 +38,7 @@ class DecoderModel:
         # finding the layer where two computations part (the reference's LayerObserver,
         # backend-java/.../llama/LlamaForwardPass.java:44-47,1179-1181)
         self.observer: Optional[Callable[[int, torch.Tensor], None]] = None
+        self.fused_decode = None  # the whole decode step as one kernel, where the model's parts allow it (set by `load`)
 
     # ------------------------------------------------------------------ weights
 
@@ -58,6 +59,10 @@ class DecoderModel:
         self.final_norm.load(tensors)
         # tied output: the embedding matrix stands in (backend-java/.../llama/LlamaWeights.java:83-89)
         self.head.load(tensors, tied_to=getattr(self.embedding, "weight", None) if self.spec.head.tied else None)
+        if self.runtime.mode == "bfloat16" and self.runtime.device.type == "cuda":
+            from .fused_decode import FusedDecode
+
+            self.fused_decode = FusedDecode(self)
 
     # ------------------------------------------------------------------ cache needs
 
@@ -72,6 +77,10 @@ class DecoderModel:
     def forward(self, batch, runs: List[RunContext]) -> Optional[torch.Tensor]:
         """Runs the tokens of `batch` through every scheduled run and returns float32 logits at
         batch.want_rows ([rows, vocab]), or None when no row is wanted."""
+        if self.fused_decode is not None and self.fused_decode.takes(batch):
+            logits = self.fused_decode.run(batch, runs)  # one token for each of a few sequences: the step as one kernel
+            if logits is not None:
+                return logits
         x = self.embedding.forward(batch.tokens)
         pending = None
         for run, entry in zip(runs, self.spec.schedule):

@@ -21,6 +21,11 @@ LIBRARIES = [
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 48}),
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 64}),
     ("mb_attention_tc", ["attention_tc.cu"], {"MB_HEAD_DIM": 128}),
+    ("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": 16}),
+    ("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": 32}),
+    ("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": 48}),
+    ("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": 64}),
+    ("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": 128}),
     ("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": 64}),
     ("mb_prefill_attention_tcgen05", ["prefill_attention_tcgen05.cu"], {"MB_HEAD_DIM": 128}),
 ]

@@ -703,6 +703,18 @@ def gemm_tcgen05_status() -> int:
     return int(gemm_tc().mb_gemm_tc_status()) or int(wide_gemm_lib().mb_wide_gemm_status())
 
 
+# ------------------------------------------------------------------------------------ the fused decode step
+
+def decode_step_lib(head_dim: int):
+    """The whole-step decode kernel, compiled for this head size at first use."""
+    return load_library("mb_decode_step", ["decode_step.cu"], {"MB_HEAD_DIM": int(head_dim)})
+
+
+def decode_step(lib, step, sms: int) -> None:
+    """Launches csrc/decode_step.cu with the ctypes record `step` (engine/fused_decode.py builds it)."""
+    _run(lib, lib.mb_decode_step(ctypes.byref(step), sms, _stream()))
+
+
 # ------------------------------------------------------------------------------------ sampling
 
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:

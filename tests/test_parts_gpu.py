@@ -709,3 +709,62 @@ def test_a_window_layer_with_a_budget_of_its_own_and_other_page_sizes(cuda_devic
         engine.cache.check()
     with pytest.raises(ValueError, match="pages of 64"):
         Engine(spec, tensors, "bfloat16", max_tokens=1024, page_size=32)
+
+
+@pytest.mark.parametrize("shape", ["heads of 16, a window, a wide feed-forward", "heads of 128", "heads of 64, four to a kv head"])
+def test_the_fused_decode_step_against_the_part_by_part_path_and_plain(cuda_device, shape):
+    """Steps of one token for each of 1 to 8 sequences can run as one kernel where the model's parts allow it
+    (it is off unless asked for).  The same engine runs the same steps part by part: both must agree with the
+    plain functions and with each other within rounding.  The first model has a windowed layer (two cache
+    groups, each with page tables of its own), a feed-forward wider than a block can stage at once (the
+    down product then runs as column ranges one after the other) and sizes that fill no tile; the others
+    have the head sizes whose attention warps are laid out differently."""
+    from models_b200.engine import StepEntry
+
+    spec = {
+        "heads of 16, a window, a wide feed-forward":
+            _specs(hidden=72, heads=6, kv_heads=2, head_dim=16, inter=4200, vocab=203, windows=(None, 24, None)),
+        "heads of 128": _specs(hidden=264, heads=2, kv_heads=1, head_dim=128, inter=520, vocab=331, windows=(None, None)),
+        "heads of 64, four to a kv head": _specs(hidden=136, heads=8, kv_heads=2, head_dim=64, inter=264, vocab=203, windows=(None, 70)),
+    }[shape]
+    engine, tensors = _engine(spec, "bfloat16", seed=21, max_tokens=2048)
+    fused = engine.model.fused_decode
+    assert fused is not None and fused.why_not is None and not fused.enabled
+    lengths = [90, 1, 64, 30, 127, 5, 70, 12]
+    sequences = [_tokens(n + 10, spec.vocab_size, 300 + i) for i, n in enumerate(lengths)]
+    expected = [_plain_forward(spec, tensors, s) for s in sequences]
+    for batch in (1, 3, 8):
+        results = {}
+        for mode in ("one kernel", "part by part"):
+            fused.enabled = mode == "one kernel"
+            slots = [engine.open_slot() for _ in range(batch)]
+            engine.step([StepEntry(slots[b], sequences[b][:lengths[b]], []) for b in range(batch)])
+            rows = []
+            for i in range(10):
+                out = engine.step([StepEntry(slots[b], [sequences[b][lengths[b] + i]], [0]) for b in range(batch)])
+                for b in range(batch):
+                    err = scaled_error(out[b], expected[b][lengths[b] + i])
+                    assert err < TOLERANCE["bfloat16"], (mode, batch, i, b, err)
+                rows.append(out)
+            results[mode] = torch.stack(rows)
+            for slot in slots:
+                engine.release_slot(slot)
+        assert scaled_error(results["one kernel"], results["part by part"]) < 1e-2, batch
+    assert fused.phases is not None and fused.status() == 0
+    layers = len(spec.layers)
+    down_ranges = 2 if shape.startswith("heads of 16") else 1
+    assert fused.num_phases == 1 + layers * (4 + down_ranges) + 1  # embed; per layer q/k/v, attention, output, gate/up, down; head
+    engine.cache.check()
+
+
+def test_what_the_fused_decode_step_leaves_to_the_parts(cuda_device, tmp_path):
+    """Biases, float32 and parts of another kind keep the part-by-part path, and say why."""
+    from models_b200.engine.loading import engine_from_folder
+    from tiny import TINY_A, TINY_C, make_folder
+
+    biased = engine_from_folder(make_folder(TINY_C, 1, tmp_path), "bfloat16", 256)
+    assert "biases" in biased.model.fused_decode.why_not
+    exact = engine_from_folder(make_folder(TINY_A, 2, tmp_path), "float32", 256)
+    assert exact.model.fused_decode is None
+    plain = engine_from_folder(make_folder(TINY_A, 2, tmp_path), "bfloat16", 256)
+    assert plain.model.fused_decode.why_not is None
