@@ -111,7 +111,7 @@ struct Step {
     bf16* a;              // [batch][ld_q] the attention's output rows
     float* logits;        // [batch][ld_logits]
     int ld_logits;
-    unsigned int* barrier;  // arrival counter, zero at launch
+    unsigned int* barrier;  // arrival counter: zero at launch, and zero again when the step is done
     int* status;            // set to 1 + (phase << 8) by a block whose bounded wait ran out
     long long* timeline;    // null, or [num_phases][6] clock readings of block 0: phase entered, barrier passed, activations staged, done, first tile's products done, its sums met
 };
@@ -229,14 +229,21 @@ __device__ __forceinline__ void stream_produce(Stream& s, const Step& step, cons
         const int tid4 = lane & 3;
         const uint32_t stage = ring + slot * kStageBytes;
         const int kc = s.k0 + s.step * kStageCols + 8 * tid4;
+        const uint32_t dst0 = stage + lane * 16;
+        if (s.k0 + (s.step + 1) * kStageCols <= s.k1) {  // the whole stage lies inside the slice (all but the last stage at most)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int c = 0; c < kPieces; ++c) {
-                const int kk = kc + 32 * c;
-                const uint32_t dst = stage + ((h * kPieces + c) * 32 + lane) * 16;
-                if (kk < s.k1) cp_async16_mem(dst, s.row[h] + kk);
-                else sts128_zero(dst);
+                for (int c = 0; c < kPieces; ++c) cp_async16_mem(dst0 + (h * kPieces + c) * 512, s.row[h] + kc + 32 * c);
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int c = 0; c < kPieces; ++c) {
+                    const int kk = kc + 32 * c;
+                    if (kk < s.k1) cp_async16_mem(dst0 + (h * kPieces + c) * 512, s.row[h] + kk);
+                    else sts128_zero(dst0 + (h * kPieces + c) * 512);
+                }
             }
         }
         if (++s.step == s.steps) {
@@ -260,9 +267,11 @@ __device__ __forceinline__ bool grid_barrier(const Step& step, unsigned int epoc
         const unsigned int target = epoch * gridDim.x;
         unsigned int seen = 0;
         long polls = 0;
-        do {
+        for (;;) {
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(step.barrier) : "memory");
-        } while (seen < target && ++polls < kSpinLimit);
+            if (seen >= target || ++polls >= kSpinLimit) break;
+            __nanosleep(32);  // 148 pollers of one word: leave the arrivals some room
+        }
         barrier_ok = seen >= target;
         if (seen < target) atomicExch(step.status, 1 + (phase << 8));
         __threadfence();
@@ -601,7 +610,19 @@ decode_step_kernel(const __grid_constant__ StepParams params) {
             continue;
         }
 
-        // ---- a matrix phase: activations of its columns -> shared memory, bfloat16
+        // ---- a matrix phase.  First what the finishing threads need from memory besides the sums (a position's
+        // rotation, a cache slot): asked for now, there when the first tile is done
+        const bool paired = p.kind == PH_GATE_UP || p.kind == PH_QKV;
+        const int tile_rows = paired ? 8 : 16;
+        const bool finisher = team_thread < tile_rows * kCols;
+        const int row_in_tile = team_thread % tile_rows, col = team_thread / tile_rows;
+        const bool live_col = finisher && col < step.batch;
+        int position = 0, cache_slot = -1;
+        if (live_col && p.kind == PH_QKV) {
+            position = step.positions[col];
+            cache_slot = step.slot_mappings[p.group][col];
+        }
+        // ---- activations of its columns -> shared memory, bfloat16
         const int x_stride = p.k_pad * 2 + 64;
         const int chunks_padded = p.k_pad / 8, chunks = p.k_len / 8;
         __syncthreads();  // whoever still reads the front of shared memory (the phase before) is done
@@ -616,26 +637,13 @@ decode_step_kernel(const __grid_constant__ StepParams params) {
         if (timed) step.timeline[ph * 6 + 2] = clock64();
 
         // ---- the row tiles of this warp's team; the ring keeps running across them
-        const bool paired = p.kind == PH_GATE_UP || p.kind == PH_QKV;
-        const int tile_rows = paired ? 8 : 16;
         const int rows_total = p.kind == PH_QKV ? p.rows / 2 : p.rows;  // rows, or pairs
         int k0, k1;
         const int steps = slice_steps(p, warp, &k0, &k1);
         const uint32_t x_lane = smem_base + group_id * x_stride + (k0 + 8 * tid4) * 2;
-        // the thread of the team that finishes output (row_in_tile, col) of every tile, and what it needs besides the
-        // sums: fetched before a tile's products so that it is there when they are done
-        const bool finisher = team_thread < tile_rows * kCols;
-        const int row_in_tile = team_thread % tile_rows, col = team_thread / tile_rows;
-        const bool live_col = finisher && col < step.batch;
-        int position = 0, cache_slot = -1;
+        // the thread of the team that finishes output (row_in_tile, col) of every tile
         float inv_rms = 1.0f;
-        if (live_col) {
-            if (p.gain) inv_rms = 1.0f / sqrtf(sq_total[col] / (float)p.k_len + p.eps);
-            if (p.kind == PH_QKV) {
-                position = step.positions[col];
-                cache_slot = step.slot_mappings[p.group][col];
-            }
-        }
+        if (live_col && p.gain) inv_rms = 1.0f / sqrtf(sq_total[col] / (float)p.k_len + p.eps);
         for (int tile = first_tile(team); tile < p.tiles; tile += tile_stride()) {
             const int row = tile * tile_rows + row_in_tile;
             const bool live = live_col && row < rows_total;
@@ -728,6 +736,10 @@ decode_step_kernel(const __grid_constant__ StepParams params) {
     }
     if (timed) step.timeline[(step.num_phases - 1) * 6 + 3] = clock64();
     cp_async_wait_mem<0>();  // nothing of this block is in flight when it leaves
+    // one more arrival, without a wait: whoever arrives last puts the counter back to zero for the next step (when a
+    // wait ran out the count is short and stays: the status word says so, and the host clears both)
+    __syncthreads();
+    if (threadIdx.x == 0 && atomicAdd(step.barrier, 1u) == (epoch + 1) * gridDim.x - 1) *step.barrier = 0u;
 }
 
 }  // namespace mb
@@ -741,11 +753,11 @@ MB_EXPORT int mb_decode_step_max_columns() { return kMaxStageCols; }
 MB_EXPORT int mb_decode_step_slice_columns() { return kSliceCols; }
 MB_EXPORT int mb_decode_step_max_groups() { return kMaxGroups; }
 
-// Runs one decode step.  `step` and its `phases` (both host memory) are copied into the launch's parameters.  The barrier counter is
-// set to zero on the stream first.  Blocks: one per multiprocessor, launched cooperatively (all resident, or the
-// launch fails).
 MB_EXPORT int mb_decode_step_max_phases() { return kMaxPhases; }
 
+// Runs one decode step.  `step` and its `phases` (both host memory) are copied into the launch's parameters.  The
+// barrier counter must be zero; a step leaves it zero (unless a bounded wait ran out: then the status word is set).
+// Blocks: one per multiprocessor, launched cooperatively (all resident, or the launch fails).
 MB_EXPORT int mb_decode_step(const Step* given, int multiprocessors, cudaStream_t stream) {
     static thread_local StepParams params;  // (32 KB: not on the stack)
     params.step = *given;
@@ -768,8 +780,7 @@ MB_EXPORT int mb_decode_step(const Step* given, int multiprocessors, cudaStream_
         if (status != cudaSuccess || resident < 1) return fail("decode_step: a block does not fit a multiprocessor");
         configured[device] = true;
     }
-    cudaError_t status = cudaMemsetAsync(step.barrier, 0, sizeof(unsigned int), stream);
-    if (status != cudaSuccess) return fail("decode_step: cannot clear the barrier counter: %s", cudaGetErrorString(status));
+    cudaError_t status = cudaSuccess;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(multiprocessors);
     config.blockDim = dim3(kStepThreads);

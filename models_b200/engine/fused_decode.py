@@ -280,5 +280,12 @@ class FusedDecode:
                 for i in range(self.num_phases)]
 
     def status(self) -> int:
-        """0 unless a bounded wait inside the kernel ever gave up (1 + (phase << 8))."""
-        return 0 if self.scratch is None else int(self.scratch["status"].item())
+        """0 unless a bounded wait inside the kernel ever gave up (1 + (phase << 8)); the barrier counter, which such a
+        step leaves short, is then cleared so that the next step starts clean."""
+        if self.scratch is None:
+            return 0
+        status = int(self.scratch["status"].item())
+        if status:
+            self.scratch["barrier"].zero_()
+            self.scratch["status"].zero_()
+        return status
