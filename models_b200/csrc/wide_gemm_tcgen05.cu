@@ -1,22 +1,26 @@
-// Decode matrix products for wide batches (33 to 128 activation rows) on the tcgen05 tensor cores.
+// Decode matrix products for wide batches (9 to 128 activation rows) on the tcgen05 tensor cores.
 //
 // With this many rows the weights still have to stream exactly once, but the arithmetic no longer
 // fits the register-fed MMAs of the narrow decode kernel.  So the operands swap sides: a tile of 128
-// WEIGHT rows is the 128-row operand of tcgen05.mma and the activations are the N = 64 or 128 side;
-// both travel by TMA (the activations, a few hundred KB, are re-read from L2 for every weight tile)
-// and the accumulator [128 weight rows x batch] lives in tensor memory.
+// WEIGHT rows is the 128-row operand of tcgen05.mma and the activations are the N = 32, 64 or 128
+// side; both travel by TMA (the activations, a few hundred KB, are re-read from L2 for every weight
+// tile) and the accumulator [128 weight rows x batch] lives in tensor memory.
 //
-//   * Work units are (weight row tile, K split).  Matrices with few row tiles split K so that every
-//     multiprocessor streams; blocks are persistent and walk the units round-robin, the TMA ring runs
-//     on across units.
-//   * Split K without waiting: every split stores its partial accumulator to scratch memory and takes
-//     a ticket (atomic counter per row tile and warp quarter); the split that draws the last ticket
-//     adds all partials in split order -- the same order whoever comes last -- and runs the epilogue.
-//     Nobody waits for anybody, and the counter is back at zero when the tile is done.
-//   * Epilogues as in the other product kernels: store bf16 / f32, add into the float32 residual
-//     stream, or silu(gate) * up when the unit carries a gate tile and its up tile (two accumulators).
-//     The accumulator is transposed with respect to the output ([weight row][batch row]); a warp's 32
-//     lanes hold 32 neighbouring output columns of one batch row, so stores stay coalesced.
+//   * A block works on ONE tile, or on one part of K of one tile: a layer's matrices have 16 to 128
+//     row tiles, too few to keep every multiprocessor streaming, so K is split over the 2, 4 or 8
+//     blocks of a thread-block CLUSTER.  Their partial accumulators meet in distributed shared
+//     memory: every block copies its accumulator from tensor memory into its own shared memory, the
+//     cluster meets at its hardware barrier, and each block then finishes a share of the tile's rows,
+//     adding the parts in the order of the blocks' ranks -- the same order in every run, no scratch
+//     memory, no atomics, nobody polls.
+//   * What surrounds the product rides in it, as in the narrow decode kernel (csrc/skinny_gemm.cu):
+//     store bf16 / f32; add into the float32 residual stream (x = x + W.h, integrallis/models,
+//     backend-java/.../llama/LlamaForwardPass.java:1131-1138,1172-1178); act(gate) * up, a tile then
+//     being 64 gate rows and the 64 up rows that match them (backend-java/.../ops/TensorOps.java:1407-1449);
+//     and for the q/k/v product the rotation of query and key pairs (x0' = x0*c - x1*s, x1' = x0*s +
+//     x1*c, :1481-1486) with the paged cache write of keys and values (backend-java/.../llama/LlamaForwardPass.java:1070-1086).
+//   * The kernel is a programmatic dependent of the kernel before it: its first weight tiles are
+//     asked for before it waits for that kernel (weights depend on nothing), the activations after.
 //
 // Every mbarrier wait is bounded as in gemm_tcgen05.cu; mb_wide_gemm_status() reads the record.
 #include "tcgen05.cuh"
@@ -25,59 +29,89 @@ MB_DEFINE_LAST_ERROR()
 
 namespace mb {
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE = 4 };
 
 constexpr int kTileRows = 128;                    // weight rows per tile (UMMA M)
 constexpr int kTileBytes = kTileRows * kBlockK * 2;
 constexpr int kThreads = 192;                     // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr int kFinishThreads = 128;
 
 struct WideArgs {
-    int rows_total;       // output columns = weight rows (for EPI_SWIGLU: gate rows)
+    int rows_total;       // output columns = weight rows (EPI_SWIGLU: gate rows)
     int up_row_offset;    // EPI_SWIGLU: first up row of W
     int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int batch, k;
-    int tiles, splits, k_blocks_per_split;
-    void* out;            // [batch, rows_total] bfloat16 / float32 (row stride ld_out)
+    int splits;           // blocks of a cluster that share a tile, each with its own part of K
+    int k_blocks_per_split;
+    void* out;            // [batch, rows_total] bfloat16 / float32 (row stride ld_out); EPI_ROPE: the queries
     int ld_out;
-    float* partial;       // splits > 1: [tile][split][accumulators][batch columns][128 rows] floats
-    int* tickets;         // splits > 1: [tile][4 warp quarters], zero before the launch and after it
+    // EPI_ROPE: W is [q heads; k heads; v heads], head_dim divides 128
+    int heads, kv_heads, head_dim, page_size;
+    const int* positions;     // [batch]
+    const int* slot_mapping;  // [batch] flat cache position, < 0: do not store
+    const float* cos_table;   // [positions][head_dim / 2]
+    const float* sin_table;
+    bf16* k_pool;             // [pages][kv_heads][page_size][head_dim]
+    bf16* v_pool;
 };
 
-template <int EPI, int kBatchN>
+// kStages: eight where every block has a multiprocessor to itself anyway (few tiles: the ring is then all that keeps
+// loads in flight); four where there are more blocks than multiprocessors: two then share one, and one streams while the
+// other starts or finishes.
+template <int kBatchN, int kStageCount>
 struct WidePlan {
-    static constexpr int kAccumulators = EPI == EPI_SWIGLU ? 2 : 1;   // gate and up
-    static constexpr int kStageBytes = kAccumulators * kTileBytes + kBatchN * kBlockK * 2;
-    static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-    static constexpr int kUnitColumns = kAccumulators * kBatchN;        // tensor-memory columns per unit
-    static constexpr int kTmemColumns = 2 * kUnitColumns <= 128 ? 128 : (2 * kUnitColumns <= 256 ? 256 : 512);
-    static_assert(2 * kUnitColumns <= 512, "two units of accumulators must fit tensor memory");
+    static constexpr int kStageBytes = kTileBytes + kBatchN * kBlockK * 2;
+    static constexpr int kStages = kStageCount * kStageBytes <= 200 * 1024 ? kStageCount : 200 * 1024 / kStageBytes;
+    static constexpr int kTmemColumns = kBatchN < 32 ? 32 : kBatchN;
+    static constexpr int kPartialBytes = kBatchN * kTileRows * (int)sizeof(float);  // [batch column][128 rows], over the ring
 };
 
-template <int EPI, int kBatchN>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&pair);
+}
+// Four floats at the same place of the shared memory of block `rank` of this cluster (distributed shared memory).
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_shared_f32x4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+template <int EPI, int kBatchN, int kStageCount>
+__global__ void __launch_bounds__(kThreads, kStageCount > 4 ? 1 : 2)
 wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const WideArgs args) {
-    using Plan = WidePlan<EPI, kBatchN>;
-    constexpr int kStages = Plan::kStages, kAccumulators = Plan::kAccumulators;
+    using Plan = WidePlan<kBatchN, kStageCount>;
+    constexpr int kStages = Plan::kStages;
     constexpr uint32_t kInstruction = instruction_descriptor(kTileRows, kBatchN);
+    constexpr bool kPaired = EPI == EPI_SWIGLU || EPI == EPI_ROPE;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t barriers[2 * kStages + 4];
+    __shared__ __align__(8) uint64_t barriers[2 * kStages + 1];
+    static_assert(Plan::kPartialBytes <= kStages * Plan::kStageBytes, "the accumulator's copy reuses the ring");
     __shared__ uint32_t tmem_base_slot;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full_bar = smem_u32(&barriers[0]), empty_bar = smem_u32(&barriers[kStages]);
-    const uint32_t acc_full_bar = smem_u32(&barriers[2 * kStages]), acc_empty_bar = smem_u32(&barriers[2 * kStages + 2]);
-    const int units = args.tiles * args.splits;
+    const uint32_t acc_full_bar = smem_u32(&barriers[2 * kStages]);
+    const int splits = args.splits;
+    const int rank = splits > 1 ? (int)cluster_rank() : 0;
+    const int tile = blockIdx.x / splits;
     const int k_blocks = (args.k + kBlockK - 1) / kBlockK;
+    const int kb_begin = rank * args.k_blocks_per_split;
+    const int kb_end = min(k_blocks, kb_begin + args.k_blocks_per_split);  // (the launcher leaves no part empty)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar + 8 * s, 1);
             mbar_init(empty_bar + 8 * s, 1);
         }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(acc_full_bar + 8 * a, 1);
-            mbar_init(acc_empty_bar + 8 * a, 4);
-        }
+        mbar_init(acc_full_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -89,251 +123,316 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     grid_launch_dependents();
-    grid_dependency_wait();  // the activations come from the kernel before this one
+    bool ok = true;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            // the weight rows of MMA rows 0..127: 128 consecutive rows, or 64 gate rows and the 64 up rows that match them
+            auto load_weights = [&](uint32_t dst, int kb, uint32_t bar) {
+                if (EPI == EPI_SWIGLU) {
+                    tma_load_2d(dst, &map_w, kb * kBlockK, tile * 64, bar);
+                    tma_load_2d(dst + kTileBytes / 2, &map_w, kb * kBlockK, args.up_row_offset + tile * 64, bar);
+                } else {
+                    tma_load_2d(dst, &map_w, kb * kBlockK, tile * kTileRows, bar);
+                }
+            };
+            // the first weight tiles go out before this kernel waits for the one before it; the activations after
+            const int early = min(kStages, kb_end - kb_begin);
+            for (int s = 0; s < early; ++s) {
+                mbar_expect_tx(full_bar + 8 * s, Plan::kStageBytes);
+                load_weights(smem_u32(smem) + s * Plan::kStageBytes, kb_begin + s, full_bar + 8 * s);
+            }
+            grid_dependency_wait();
+            for (int s = 0; s < early; ++s)
+                tma_load_2d(smem_u32(smem) + s * Plan::kStageBytes + kTileBytes, &map_x, (kb_begin + s) * kBlockK, 0, full_bar + 8 * s);
             int stage = 0;
-            uint32_t phase = 1;
-            bool ok = true;
-            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-                const int tile = unit / args.splits, split = unit % args.splits;
-                const int kb_begin = split * args.k_blocks_per_split;
-                const int kb_end = min(k_blocks, kb_begin + args.k_blocks_per_split);
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
-                    const uint32_t dst = smem_u32(smem) + stage * Plan::kStageBytes;
-                    mbar_expect_tx(full_bar + 8 * stage, Plan::kStageBytes);
-                    tma_load_2d(dst, &map_w, kb * kBlockK, tile * kTileRows, full_bar + 8 * stage);
-                    if (kAccumulators == 2)
-                        tma_load_2d(dst + kTileBytes, &map_w, kb * kBlockK, args.up_row_offset + tile * kTileRows, full_bar + 8 * stage);
-                    tma_load_2d(dst + kAccumulators * kTileBytes, &map_x, kb * kBlockK, 0, full_bar + 8 * stage);
-                    if (++stage == kStages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
+            uint32_t phase = 0;  // the second pass over the ring waits for the first pass's products
+            for (int kb = kb_begin + early; kb < kb_end; ++kb) {
+                if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
+                const uint32_t dst = smem_u32(smem) + stage * Plan::kStageBytes;
+                mbar_expect_tx(full_bar + 8 * stage, Plan::kStageBytes);
+                load_weights(dst, kb, full_bar + 8 * stage);
+                tma_load_2d(dst + kTileBytes, &map_x, kb * kBlockK, 0, full_bar + 8 * stage);
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            int stage = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 1;
-            bool ok = true;
-            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-                const int split = unit % args.splits;
-                const int kb_begin = split * args.k_blocks_per_split;
-                const int kb_end = min(k_blocks, kb_begin + args.k_blocks_per_split);
-                if (!(ok = mbar_wait(acc_empty_bar + 8 * acc, acc_phase, 2))) break;
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!(ok = mbar_wait(full_bar + 8 * stage, phase, 3))) break;
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * Plan::kUnitColumns;
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    if (!(ok = mbar_wait(full_bar + 8 * stage, phase, 3))) break;
-                    tcgen05_fence_after();
-                    const uint32_t base = smem_u32(smem) + stage * Plan::kStageBytes;
-                    const uint64_t x_desc = umma_descriptor(base + kAccumulators * kTileBytes);
+                const uint32_t base = smem_u32(smem) + stage * Plan::kStageBytes;
+                const uint64_t w_desc = umma_descriptor(base), x_desc = umma_descriptor(base + kTileBytes);
 #pragma unroll
-                    for (int a = 0; a < kAccumulators; ++a) {
-                        const uint64_t w_desc = umma_descriptor(base + a * kTileBytes);
-#pragma unroll
-                        for (int ks = 0; ks < kBlockK / 16; ++ks)
-                            umma(tmem_d + a * kBatchN, w_desc + 2 * ks, x_desc + 2 * ks, kInstruction, (kb > kb_begin || ks > 0) ? 1u : 0u);
-                    }
-                    umma_commit(empty_bar + 8 * stage);
-                    if (++stage == kStages) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
-                }
-                if (!ok) break;
-                umma_commit(acc_full_bar + 8 * acc);
-                if (++acc == 2) {
-                    acc = 0;
-                    acc_phase ^= 1;
+                for (int ks = 0; ks < kBlockK / 16; ++ks)
+                    umma(tmem_base, w_desc + 2 * ks, x_desc + 2 * ks, kInstruction, (kb > kb_begin || ks > 0) ? 1u : 0u);
+                umma_commit(empty_bar + 8 * stage);
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
                 }
             }
+            if (ok) umma_commit(acc_full_bar);
         }
     } else {
-        // ------------------------------------------------------------------ epilogue: 4 warps, 32 weight rows each
+        // ------------------------------------------------------------------ the accumulator -> this block's shared memory
+        grid_dependency_wait();  // (what the finishing below reads and adds into comes from the kernel before this one)
         const int quarter = warp & 3;
-        int acc = 0;
-        uint32_t acc_phase = 0;
-        bool ok = true;
-        for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-            const int tile = unit / args.splits, split = unit % args.splits;
-            ok = mbar_wait(acc_full_bar + 8 * acc, acc_phase, 4);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+        ok = mbar_wait(acc_full_bar, 0, 4);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
             tcgen05_fence_after();
-            const int row = tile * kTileRows + quarter * 32 + lane;   // output column = weight row
-            const uint32_t taddr = tmem_base + acc * Plan::kUnitColumns + ((uint32_t)(quarter * 32) << 16);
-            bool finish = true;  // this warp runs the epilogue of its 32 rows
-            // this warp's slice of a partial: [accumulator][batch column][32 rows of this quarter]
-            const size_t slice = (size_t)kAccumulators * kBatchN * 32;
-            float* partial = args.partial + ((size_t)(tile * args.splits) * 4 + quarter) * slice;  // split 0; split s: + s * 4 * slice
-            if (args.splits > 1) {
-                float* mine = partial + (size_t)split * 4 * slice;
+            // every product has read the ring: it now holds the accumulator, [batch column][128 rows]
+            float* partial = reinterpret_cast<float*>(smem);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-                for (int c = 0; c < kAccumulators * kBatchN; c += 32) {
-                    float v[32];
-                    tmem_load_32(taddr + c, v);
+            for (int c = 0; c < kBatchN; c += 32) {
+                float v[32];
+                tmem_load_32(taddr + c, v);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mine[(size_t)(c + i) * 32 + lane] = v[i];
-                }
-                __threadfence();
-                __syncwarp();
-                int ticket = 0;
-                if (lane == 0) ticket = atomicAdd(args.tickets + tile * 4 + quarter, 1);
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                finish = ticket == args.splits - 1;
-                if (finish) {
-                    __threadfence();
-                    if (lane == 0) args.tickets[tile * 4 + quarter] = 0;  // ready for the next launch
-                }
-            }
-            // the accumulator has been read (or will not be needed): hand it back early
-            if (args.splits > 1) {
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
-            }
-            if (finish) {
-#pragma unroll 1
-                for (int c = 0; c < kBatchN; c += 32) {
-                    float v[32], u[32];
-                    if (args.splits > 1) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = u[i] = 0.0f;
-                        for (int s = 0; s < args.splits; ++s) {  // split order, whoever finishes
-                            const float* from = partial + (size_t)s * 4 * slice;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                v[i] += __ldcg(from + (size_t)(c + i) * 32 + lane);
-                                if (kAccumulators == 2) u[i] += __ldcg(from + (size_t)(kBatchN + c + i) * 32 + lane);
-                            }
-                        }
-                    } else {
-                        tmem_load_32(taddr + c, v);
-                        if (kAccumulators == 2) tmem_load_32(taddr + kBatchN + c, u);
-                    }
-                    if (row < args.rows_total) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int b = c + i;
-                            if (b >= args.batch) break;
-                            float value = v[i];
-                            if (EPI == EPI_SWIGLU) value = gate_activation(args.activation, value) * u[i];
-                            const size_t at = (size_t)b * args.ld_out + row;
-                            if (EPI == EPI_BF16 || EPI == EPI_SWIGLU) reinterpret_cast<bf16*>(args.out)[at] = __float2bfloat16_rn(value);
-                            if (EPI == EPI_F32) reinterpret_cast<float*>(args.out)[at] = value;
-                            if (EPI == EPI_RESIDUAL) reinterpret_cast<float*>(args.out)[at] += value;
-                        }
-                    }
-                }
-            }
-            if (args.splits == 1) {
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty_bar + 8 * acc);
-            }
-            if (++acc == 2) {
-                acc = 0;
-                acc_phase ^= 1;
+                for (int i = 0; i < 32; ++i) partial[(c + i) * kTileRows + quarter * 32 + lane] = v[i];
             }
         }
     }
 
+    // ---- the parts of K meet: every block of the cluster has its accumulator in its shared memory
     tcgen05_fence_before();
-    __syncthreads();
+    if (splits > 1) cluster_sync_all();
+    else __syncthreads();
+
+    if (warp >= 2) {
+        // ------------------------------------------------------------------ finishing: a share of the tile's rows (or pairs of rows) per
+        // block, four neighbouring rows per thread and step (they are neighbours in shared memory and in the output)
+        const int t = threadIdx.x - 64;
+        const uint32_t partial_addr = smem_u32(smem);
+        constexpr int kUnits = kPaired ? 64 : 128;     // rows, or pairs of rows, of a tile
+        const int per_block = kUnits / splits;         // splits is 1, 2, 4 or 8: a multiple of 4
+        const int quads = per_block / 4;
+        const int first = rank * per_block;
+        auto sum_parts = [&](int mma_row, int col) {   // rows mma_row .. mma_row + 3 of batch column col, over all parts of K
+            const uint32_t at = partial_addr + (uint32_t)(col * kTileRows + mma_row) * 4u;
+            if (splits == 1) return ld_shared_f32x4(at);
+            float4 parts[8];  // all loads first (they are independent), then the sums in the order of the ranks
+#pragma unroll
+            for (int r = 0; r < 8; ++r) parts[r] = r < splits ? ld_cluster_f32x4(at, (uint32_t)r) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                v.x += parts[r].x; v.y += parts[r].y; v.z += parts[r].z; v.w += parts[r].w;
+            }
+            return v;
+        };
+        for (int item = t; item < quads * args.batch; item += kFinishThreads) {
+            const int unit = first + (item % quads) * 4, col = item / quads;  // neighbouring threads: neighbouring rows of one batch row
+            if (!kPaired) {
+                const int row = tile * kTileRows + unit;
+                if (row >= args.rows_total) continue;  // (the number of rows is a multiple of 8: four rows are all inside or all outside)
+                const float4 value = sum_parts(unit, col);
+                const size_t at = (size_t)col * args.ld_out + row;
+                if (EPI == EPI_BF16)
+                    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.out) + at) = make_uint2(pack_bf16(value.x, value.y), pack_bf16(value.z, value.w));
+                if (EPI == EPI_F32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at) = value;
+                if (EPI == EPI_RESIDUAL) {  // this thread alone owns the elements
+                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at);
+                    const float4 before = *dst;
+                    *dst = make_float4(before.x + value.x, before.y + value.y, before.z + value.z, before.w + value.w);
+                }
+            } else if (EPI == EPI_SWIGLU) {
+                const int row = tile * 64 + unit;
+                if (row >= args.rows_total) continue;
+                const float4 gate = sum_parts(unit, col), up = sum_parts(unit + 64, col);
+                const int a = args.activation;
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.out) + (size_t)col * args.ld_out + row) =
+                    make_uint2(pack_bf16(gate_activation(a, gate.x) * up.x, gate_activation(a, gate.y) * up.y),
+                               pack_bf16(gate_activation(a, gate.z) * up.z, gate_activation(a, gate.w) * up.w));
+            } else {  // EPI_ROPE: pairs `unit`.. of the tile are coordinates d and d + head/2 of one of its heads
+                const int hd = args.head_dim, half = hd / 2;
+                const int head_in_tile = unit / half, d0 = unit % half;
+                const int head = tile * (kTileRows / hd) + head_in_tile;
+                if (head >= args.heads + 2 * args.kv_heads) continue;
+                const int mma_row = head_in_tile * hd + d0;
+                const float4 first_half = sum_parts(mma_row, col), second_half = sum_parts(mma_row + half, col);
+                // queries and keys pass through bfloat16 before the rotation, as they do when a product stores them
+                float x0[4] = {first_half.x, first_half.y, first_half.z, first_half.w};
+                float x1[4] = {second_half.x, second_half.y, second_half.z, second_half.w};
+                if (head < args.heads + args.kv_heads) {
+                    const size_t at_table = (size_t)args.positions[col] * half + d0;
+                    const float4 c4 = *reinterpret_cast<const float4*>(args.cos_table + at_table);
+                    const float4 s4 = *reinterpret_cast<const float4*>(args.sin_table + at_table);
+                    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float a0 = __bfloat162float(__float2bfloat16_rn(x0[i])), a1 = __bfloat162float(__float2bfloat16_rn(x1[i]));
+                        x0[i] = a0 * c[i] - a1 * sn[i];
+                        x1[i] = a0 * sn[i] + a1 * c[i];
+                    }
+                }
+                bf16* dst = nullptr;
+                if (head < args.heads) {
+                    dst = reinterpret_cast<bf16*>(args.out) + (size_t)col * args.ld_out + (size_t)head * hd;
+                } else {
+                    const int slot = args.slot_mapping[col];
+                    if (slot >= 0) {
+                        const bool is_key = head < args.heads + args.kv_heads;
+                        const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
+                        const size_t page = slot / args.page_size, offset = slot % args.page_size;
+                        dst = (is_key ? args.k_pool : args.v_pool) + ((page * args.kv_heads + kv_head) * args.page_size + offset) * hd;
+                    }
+                }
+                if (dst) {
+                    *reinterpret_cast<uint2*>(dst + d0) = make_uint2(pack_bf16(x0[0], x0[1]), pack_bf16(x0[2], x0[3]));
+                    *reinterpret_cast<uint2*>(dst + d0 + half) = make_uint2(pack_bf16(x1[0], x1[1]), pack_bf16(x1[2], x1[3]));
+                }
+            }
+        }
+    }
+
+    // a cluster's blocks leave together: each has read the others' shared memory until now
+    if (splits > 1) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Plan::kTmemColumns));
     }
 }
 
-template <int EPI, int kBatchN>
-static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const WideArgs& args, int grid, cudaStream_t stream) {
-    using Plan = WidePlan<EPI, kBatchN>;
+template <int EPI, int kBatchN, int kStageCount>
+static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const WideArgs& args, int tiles, cudaStream_t stream) {
+    using Plan = WidePlan<kBatchN, kStageCount>;
     const size_t smem = (size_t)Plan::kStages * Plan::kStageBytes + 1024;
-    auto kernel = wide_gemm_kernel<EPI, kBatchN>;
-    static bool configured = false;
-    if (!configured) {
+    auto kernel = wide_gemm_kernel<EPI, kBatchN, kStageCount>;
+    static bool configured[64] = {false};  // the attribute is a device's
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail("wide_gemm: cannot tell the current device");
+    if (!configured[device]) {
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("wide_gemm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(status));
-        configured = true;
+        configured[device] = true;
     }
-    return launch_dependent("wide_gemm", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_w, map_x, args);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(tiles * args.splits);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = args.splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = dependent_launches_allowed() ? 2 : 1;
+    cudaError_t status = cudaLaunchKernelEx(&config, kernel, map_w, map_x, args);
+    if (status != cudaSuccess) return fail("wide_gemm: launch failed: %s", cudaGetErrorString(status));
+    return check_launch("wide_gemm");
 }
 
-static void plan(int rows_total, int k, int multiprocessors, int* tiles, int* splits, int* per_split) {
+// How many blocks share a tile's K: as many (1, 2, 4 or 8: a cluster) as it takes for every multiprocessor to have a
+// block, while a block keeps at least four 64-column steps of K.
+static void plan(int tiles, int k, int multiprocessors, int* splits, int* per_split) {
     const int k_blocks = (k + kBlockK - 1) / kBlockK;
-    *tiles = (rows_total + kTileRows - 1) / kTileRows;
     int s = 1;
-    // split K until every multiprocessor has a unit, keeping at least four stages of K per unit
-    while (s < 16 && *tiles * s < multiprocessors && k_blocks / (s * 2) >= 4) s *= 2;
+    while (s < 8 && tiles * s * 2 <= multiprocessors + multiprocessors / 4 && k_blocks / (s * 2) >= 4) s *= 2;
     *per_split = (k_blocks + s - 1) / s;
-    *splits = (k_blocks + *per_split - 1) / *per_split;
+    while (s > 1 && (s - 1) * *per_split >= k_blocks) {  // no part may be empty: fewer, as a power of two
+        s /= 2;
+        *per_split = (k_blocks + s - 1) / s;
+    }
+    *splits = s;
+}
+
+template <int EPI>
+static int launch_n(const CUtensorMap& map_w, const void* x, int ldx, const WideArgs& args, int tiles, int multiprocessors,
+                    cudaStream_t stream) {
+    const int batch_n = args.batch <= 32 ? 32 : (args.batch <= 64 ? 64 : 128);
+    CUtensorMap map_x;
+    if (int status = make_map(&map_x, x, args.batch, args.k, ldx, batch_n)) return status;
+    // a block per multiprocessor at most, and no cluster (a cluster of eight blocks that each fill a multiprocessor
+    // finds room for only some of the clusters at a time): the deeper ring
+    const bool deep = args.splits == 1 && tiles <= multiprocessors;
+    if (batch_n == 32) return deep ? launch<EPI, 32, 8>(map_w, map_x, args, tiles, stream) : launch<EPI, 32, 4>(map_w, map_x, args, tiles, stream);
+    if (batch_n == 64) return deep ? launch<EPI, 64, 8>(map_w, map_x, args, tiles, stream) : launch<EPI, 64, 4>(map_w, map_x, args, tiles, stream);
+    return deep ? launch<EPI, 128, 8>(map_w, map_x, args, tiles, stream) : launch<EPI, 128, 4>(map_w, map_x, args, tiles, stream);
+}
+
+static int check_operands(const char* what, const void* x, int ldx, const void* w, int ldw, int batch, int k) {
+    if (batch > 128) return fail("%s: takes at most 128 activation rows, got %d", what, batch);
+    if (k <= 0 || k % 8 || ldx % 8 || ldw % 8) return fail("%s: k (%d) and the row strides (%d, %d) must be multiples of 8", what, k, ldx, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail("%s: operands must start on 16-byte boundaries", what);
+    return 0;
 }
 
 }  // namespace mb
 
 using namespace mb;
 
-// Scratch a call needs: floats of partial accumulators and ints of tickets (both 0 when K is not split).
-// The tickets must be zero before the first launch that uses them; every launch leaves them zero.
-MB_EXPORT void mb_wide_gemm_scratch(int n_w, int k, int batch, int epilogue, int multiprocessors, size_t* partial_floats,
-                                    size_t* ticket_ints) {
-    epilogue &= 0xff;
-    const int rows_total = epilogue == EPI_SWIGLU ? n_w / 2 : n_w;
-    int tiles, splits, per_split;
-    plan(rows_total, k, multiprocessors, &tiles, &splits, &per_split);
-    const int batch_n = batch <= 64 ? 64 : 128;
-    const int accumulators = epilogue == EPI_SWIGLU ? 2 : 1;
-    *partial_floats = splits > 1 ? (size_t)tiles * splits * accumulators * batch_n * kTileRows : 0;
-    *ticket_ints = splits > 1 ? (size_t)tiles * 4 : 0;
-}
-
-// x: bfloat16 [batch, k] (33..128 rows pay off; 1..128 are taken); w: bfloat16 [n_w, k].
+// x: bfloat16 [batch, k] (up to 128 rows); w: bfloat16 [n_w, k].
 // epilogue 0: out bfloat16 [batch, n_w]; 1: float32; 2: float32 += ; 3: w = [gate rows; up rows], out
 // bfloat16 [batch, n_w/2] = act(gate) * up, the activation code (MB_ACT_*) in bits 8 and up of `epilogue`.
 MB_EXPORT int mb_wide_gemm(const void* x, int ldx, const void* w, int ldw, void* out, int ld_out, int batch, int n_w, int k,
-                           int epilogue, float* partial, int* tickets, int multiprocessors, cudaStream_t stream) {
+                           int epilogue, int multiprocessors, cudaStream_t stream) {
     if (batch <= 0 || n_w <= 0) return 0;
     const int activation = epilogue >> 8;
     epilogue &= 0xff;
     if (activation < 0 || activation >= MB_ACT_COUNT) return fail("wide_gemm: unknown gate activation code %d", activation);
-    if (batch > 128) return fail("wide_gemm: takes at most 128 activation rows, got %d", batch);
-    if (k <= 0 || k % 8 || ldx % 8 || ldw % 8) return fail("wide_gemm: k (%d) and the row strides (%d, %d) must be multiples of 8", k, ldx, ldw);
-    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail("wide_gemm: operands must start on 16-byte boundaries");
-    if (epilogue == EPI_SWIGLU && (n_w % 2 || (n_w / 2) % 8)) return fail("wide_gemm: the gated epilogue needs gate and up halves that are multiples of 8 rows, got %d rows", n_w);
+    if (int status = check_operands("wide_gemm", x, ldx, w, ldw, batch, k)) return status;
+    if (epilogue == EPI_SWIGLU && n_w % 2) return fail("wide_gemm: the gated epilogue needs an even number of weight rows, got %d", n_w);
     WideArgs args{};
     args.rows_total = epilogue == EPI_SWIGLU ? n_w / 2 : n_w;
     args.up_row_offset = args.rows_total;
     args.activation = activation;
     args.batch = batch;
     args.k = k;
-    plan(args.rows_total, k, multiprocessors, &args.tiles, &args.splits, &args.k_blocks_per_split);
-    if (args.splits > 1 && (!partial || !tickets)) return fail("wide_gemm: %d splits of K need scratch memory", args.splits);
     args.out = out;
     args.ld_out = ld_out;
-    args.partial = partial;
-    args.tickets = tickets;
-    const int batch_n = batch <= 64 ? 64 : 128;
-    CUtensorMap map_w, map_x;
-    if (int status = make_map(&map_w, w, n_w, k, ldw, kTileRows)) return status;
-    if (int status = make_map(&map_x, x, batch, k, ldx, batch_n)) return status;
-    const int units = args.tiles * args.splits;
-    const int grid = units < multiprocessors ? units : multiprocessors;
-#define MB_WIDE(EPI) \
-    if (epilogue == EPI) return batch_n == 64 ? launch<EPI, 64>(map_w, map_x, args, grid, stream) : launch<EPI, 128>(map_w, map_x, args, grid, stream);
-    MB_WIDE(EPI_BF16)
-    MB_WIDE(EPI_F32)
-    MB_WIDE(EPI_RESIDUAL)
-    MB_WIDE(EPI_SWIGLU)
-#undef MB_WIDE
+    const int tiles = epilogue == EPI_SWIGLU ? (args.rows_total + 63) / 64 : (args.rows_total + kTileRows - 1) / kTileRows;
+    plan(tiles, k, multiprocessors, &args.splits, &args.k_blocks_per_split);
+    CUtensorMap map_w;
+    // (the gated tile is two boxes of 64 rows; rows past the matrix are zeros and their results are not stored)
+    if (int status = make_map(&map_w, w, n_w, k, ldw, epilogue == EPI_SWIGLU ? 64 : kTileRows)) return status;
+    switch (epilogue) {
+        case EPI_BF16: return launch_n<EPI_BF16>(map_w, x, ldx, args, tiles, multiprocessors, stream);
+        case EPI_F32: return launch_n<EPI_F32>(map_w, x, ldx, args, tiles, multiprocessors, stream);
+        case EPI_RESIDUAL: return launch_n<EPI_RESIDUAL>(map_w, x, ldx, args, tiles, multiprocessors, stream);
+        case EPI_SWIGLU: return launch_n<EPI_SWIGLU>(map_w, x, ldx, args, tiles, multiprocessors, stream);
+    }
     return fail("wide_gemm: unknown epilogue %d", epilogue);
+}
+
+// The q/k/v product of an attention layer on up to 128 rows with what follows it folded in: rotation of queries and
+// keys (split-half pairs over the whole head) and the paged cache write of keys and values.  w: bfloat16 [(heads + 2 *
+// kv_heads) * head_dim, k]; head_dim divides 128; q_out: bfloat16 [batch, heads * head_dim] (row stride ld_q).
+MB_EXPORT int mb_wide_qkv_rope(const void* x, int ldx, const void* w, int ldw, void* q_out, int ld_q, int batch, int k, int heads,
+                               int kv_heads, int head_dim, const int* positions, const float* cos_table, const float* sin_table,
+                               void* k_pool, void* v_pool, const int* slot_mapping, int page_size, int multiprocessors,
+                               cudaStream_t stream) {
+    if (batch <= 0) return 0;
+    if (head_dim < 16 || kTileRows % head_dim) return fail("wide_qkv_rope: the head size must divide 128, got %d", head_dim);
+    if (!positions || !cos_table || !sin_table || !k_pool || !v_pool || !slot_mapping || page_size <= 0)
+        return fail("wide_qkv_rope: needs positions, cos/sin tables, cache pools, a slot mapping and a page size");
+    if (int status = check_operands("wide_qkv_rope", x, ldx, w, ldw, batch, k)) return status;
+    WideArgs args{};
+    args.rows_total = (heads + 2 * kv_heads) * head_dim;
+    args.batch = batch;
+    args.k = k;
+    args.out = q_out;
+    args.ld_out = ld_q;
+    args.heads = heads; args.kv_heads = kv_heads; args.head_dim = head_dim; args.page_size = page_size;
+    args.positions = positions; args.slot_mapping = slot_mapping; args.cos_table = cos_table; args.sin_table = sin_table;
+    args.k_pool = (bf16*)k_pool; args.v_pool = (bf16*)v_pool;
+    const int tiles = (args.rows_total + kTileRows - 1) / kTileRows;
+    plan(tiles, k, multiprocessors, &args.splits, &args.k_blocks_per_split);
+    CUtensorMap map_w;
+    if (int status = make_map(&map_w, w, args.rows_total, k, ldw, kTileRows)) return status;
+    return launch_n<EPI_ROPE>(map_w, x, ldx, args, tiles, multiprocessors, stream);
 }
 
 MB_EXPORT int mb_wide_gemm_status() {

@@ -543,22 +543,18 @@ def gemm_tc():
     return load_library("mb_gemm_tcgen05", ["gemm_tcgen05.cu"])
 
 
-TCGEN05_MIN_ROWS = 33  # fewer rows take the narrow decode product
+TCGEN05_MIN_ROWS = 9  # fewer rows take the narrow decode product
 WIDE_ROWS = 128  # most activation rows of the wide decode product
 
 
 def gemm_tcgen05_takes(weight: torch.Tensor, epilogue: int = EPI_BF16, rows: Optional[int] = None) -> bool:
-    """Whether a tcgen05 matrix product takes this weight and, if `rows` is given, pays off for so
-    many rows: above 128 the prefill form; from 33 to 128 the wide decode form, and that only for
-    matrices with a row tile per multiprocessor (with fewer it would have to split K, and a library
-    product is quicker there)."""
+    """Whether a tcgen05 matrix product takes this weight and, if `rows` is given, is the one to use for
+    so many rows: above 128 the prefill form; from 9 to 128 the wide decode form (fewer rows take the
+    narrow decode product)."""
     epilogue &= 0xFF
     n = weight.shape[0] // 2 if epilogue == EPI_SWIGLU else weight.shape[0]
-    if rows is not None:
-        if rows < TCGEN05_MIN_ROWS:
-            return False
-        if rows <= WIDE_ROWS and n < 128 * _sm_count(weight.device):
-            return False
+    if rows is not None and rows < TCGEN05_MIN_ROWS:
+        return False
     return (weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.stride(1) == 1 and weight.shape[1] % 8 == 0
             and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0 and n % 8 == 0
             and (epilogue != EPI_SWIGLU or weight.shape[0] % 2 == 0))
@@ -649,12 +645,11 @@ def wide_gemm_lib():
     return load_library("mb_wide_gemm_tcgen05", ["wide_gemm_tcgen05.cu"])
 
 
-_tickets = {}
-
-
 def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Up to 128 activation rows times weight^T on the tcgen05 tensor cores with the weights as the
-    128-row operand (decode at wide batches).  Epilogues as for skinny_gemm."""
+    128-row operand (decode at wide batches); K is split over the blocks of a cluster where a matrix has
+    few row tiles, their sums meeting in distributed shared memory in a fixed order.  Epilogues as for
+    skinny_gemm."""
     _cuda(x, weight, out)
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != weight.shape[1] or x.shape[0] > WIDE_ROWS:
         raise KernelError(f"wide_gemm: activations {tuple(x.shape)} {x.dtype} do not fit the weight {tuple(weight.shape)}")
@@ -670,20 +665,45 @@ def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, o
     elif out is None:
         out = torch.empty((batch, n), dtype=torch.float32 if kind == EPI_F32 else torch.bfloat16, device=x.device)
     lib = wide_gemm_lib()
-    sms = _sm_count(x.device)
-    need_partial, need_tickets = ctypes.c_size_t(0), ctypes.c_size_t(0)
-    lib.mb_wide_gemm_scratch(n_w, k, batch, epilogue, sms, ctypes.byref(need_partial), ctypes.byref(need_tickets))
-    partial = tickets = None
-    if need_partial.value:
-        partial = torch.empty((need_partial.value,), dtype=torch.float32, device=x.device)
-        key = x.device.index if x.device.index is not None else torch.cuda.current_device()
-        tickets = _tickets.get(key)
-        if tickets is None or tickets.numel() < need_tickets.value:
-            # zero once; every launch leaves the tickets at zero
-            tickets = _tickets[key] = torch.zeros((max(4096, need_tickets.value),), dtype=torch.int32, device=x.device)
     _run(lib, lib.mb_wide_gemm(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), batch, n_w, k,
-                               epilogue, _p(partial), _p(tickets), sms, _stream()))
+                               epilogue, _sm_count(x.device), _stream()))
     return out
+
+
+def wide_qkv_rope_takes(weight: torch.Tensor, rows: int, heads: int, kv_heads: int, head_dim: int) -> bool:
+    """Whether the wide q/k/v product with folded rotation and cache write applies: a bfloat16 weight the
+    tcgen05 products take, 9 to 128 rows, a head size that divides 128."""
+    return (head_dim >= 16 and 128 % head_dim == 0 and weight.shape[0] == (heads + 2 * kv_heads) * head_dim
+            and SKINNY_PAYS_ROWS < rows <= WIDE_ROWS and gemm_tcgen05_takes(weight, EPI_BF16))
+
+
+def wide_qkv_rope(x: torch.Tensor, weight: torch.Tensor, heads: int, kv_heads: int, head_dim: int, positions: torch.Tensor,
+                  cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                  slot_mapping: torch.Tensor) -> torch.Tensor:
+    """The q/k/v product of an attention layer on 9 to 128 rows with what follows it folded in: rotation of
+    queries and keys (split-half pairs over the whole head) and the paged cache write of keys and values.
+    Returns the rotated queries, bfloat16 [rows, heads * head_dim]."""
+    _cuda(x, weight, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    batch, k = x.shape
+    if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16 or weight.shape[1] != k:
+        raise KernelError(f"wide_qkv_rope: activations {tuple(x.shape)} {x.dtype} do not fit the weight {tuple(weight.shape)}")
+    if not wide_qkv_rope_takes(weight, batch, heads, kv_heads, head_dim):
+        raise KernelError(f"wide_qkv_rope does not take a {tuple(weight.shape)} {weight.dtype} weight with {batch} rows and heads of {head_dim}")
+    _int32(positions, "positions")
+    _int32(slot_mapping, "slot_mapping")
+    if positions.numel() < batch or slot_mapping.numel() < batch:
+        raise KernelError("positions and slot_mapping must hold one entry per row")
+    if cos.dtype != torch.float32 or cos.shape[-1] != head_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous():
+        raise KernelError(f"cos/sin tables must be contiguous float32 [positions, {head_dim // 2}]")
+    if (k_pool.dtype != torch.bfloat16 or k_pool.shape != v_pool.shape or k_pool.dim() != 4 or k_pool.shape[1] != kv_heads
+            or k_pool.shape[3] != head_dim or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
+        raise KernelError("cache pools must be contiguous bfloat16 [pages, kv_heads, page_size, head_dim]")
+    q = torch.empty((batch, heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    lib = wide_gemm_lib()
+    _run(lib, lib.mb_wide_qkv_rope(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(q), q.stride(0), batch, k, heads, kv_heads,
+                                   head_dim, _p(positions), _p(cos), _p(sin), _p(k_pool), _p(v_pool), _p(slot_mapping),
+                                   k_pool.shape[2], _sm_count(x.device), _stream()))
+    return q
 
 
 def tensor_core_gemm(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:

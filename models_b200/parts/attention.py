@@ -103,12 +103,19 @@ class AttentionMixer(Mixer):
         """x += Wo . attention(...): the residual add rides in the output product, and (whole heads of
         64 or 128, split-half pairs over the whole head) rotation and cache write in the q/k/v product."""
         writes, s, pos = run.writes_cache, self.spec, self.position
-        if (writes and self.b_qkv is None and pos is not None and pos.rotary_dim == s.head_dim and not pos.interleaved
-                and run.k_pool is not None and run.k_pool.dtype == torch.bfloat16
-                and ops.gemm_tcgen05_qkv_rope_takes(self.w_qkv, xn.shape[0], s.num_heads, s.num_kv_heads, s.head_dim)):
+        rows = xn.shape[0]
+        folds_rotation = (writes and self.b_qkv is None and pos is not None and pos.rotary_dim == s.head_dim and not pos.interleaved
+                          and run.k_pool is not None and run.k_pool.dtype == torch.bfloat16)
+        if folds_rotation and ops.gemm_tcgen05_qkv_rope_takes(self.w_qkv, rows, s.num_heads, s.num_kv_heads, s.head_dim):
             group = batch.groups[run.group]
             q = ops.gemm_tcgen05_qkv_rope(xn, self.w_qkv, s.num_heads, s.num_kv_heads, s.head_dim, batch.positions, pos.cos,
                                           pos.sin, run.k_pool, run.v_pool, group.slot_mapping)
+            attended = torch.empty((q.shape[0], self.q_width), dtype=q.dtype, device=q.device)
+            self.attend(q, attended, batch, group, run)
+        elif folds_rotation and ops.wide_qkv_rope_takes(self.w_qkv, rows, s.num_heads, s.num_kv_heads, s.head_dim):
+            group = batch.groups[run.group]  # 9 to 128 rows: the wide decode product, rotation and cache write in it too
+            q = ops.wide_qkv_rope(xn, self.w_qkv, s.num_heads, s.num_kv_heads, s.head_dim, batch.positions, pos.cos, pos.sin,
+                                  run.k_pool, run.v_pool, group.slot_mapping)
             attended = torch.empty((q.shape[0], self.q_width), dtype=q.dtype, device=q.device)
             self.attend(q, attended, batch, group, run)
         else:

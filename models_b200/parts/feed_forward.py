@@ -70,21 +70,21 @@ class GatedFeedForward(Part):
                 and ops.gemm_tcgen05_takes(self.w_down))
 
     def forward_into(self, x: torch.Tensor, xn: torch.Tensor) -> None:
-        """x += down(act(gate(xn)) * up(xn)) with the residual add inside the down product, which splits
-        K over blocks where it has few tiles: at 9 to 128 rows it takes 8.8 us for the 1B sizes where a
-        library product takes 12.5 and leaves the add to another kernel (decode steps of 16 to 64 sequences
-        gain 5 to 6 % at the 1B sizes, 0 to 3 % at 8B sizes; 64 sequences at 3B sizes lose 4 %).  Where the gate/up product has
-        tiles enough (more than 128 rows) the activation rides in it as well, and neither the gate/up
-        matrix nor the down result passes through memory; with fewer rows a library product and the
-        activation kernel are quicker."""
+        """x += down(act(gate(xn)) * up(xn)) with the activation inside the gate/up product and the residual
+        add inside the down product: neither the gate/up matrix nor the down result passes through memory.
+        Up to 128 rows both are the wide decode product (weights as the 128-row operand, K split over a
+        cluster where the matrix has few tiles), above that the prefill product."""
         rows = xn.shape[0]
-        if ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows) and rows > ops.WIDE_ROWS:
-            hidden = ops.gemm_tcgen05(xn, self.w_gate_up, self.gated)
+        if ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows):
+            hidden = ops.tensor_core_gemm(xn, self.w_gate_up, self.gated)  # the wide decode form up to 128 rows, the prefill form above
         elif ops.skinny_pays(self.w_gate_up, rows):
             hidden = ops.skinny_gemm(self.w_gate_up, self.gated, x=xn)
         else:
             hidden = ops.swiglu(linear(xn, self.w_gate_up, self.runtime.compute_dtype), self.spec.activation)
-        ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+        if rows < ops.TCGEN05_MIN_ROWS:
+            ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+        else:
+            ops.tensor_core_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype

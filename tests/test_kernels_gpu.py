@@ -620,11 +620,12 @@ def test_tcgen05_gemm_all_epilogues(cuda_device, m, n, k):
         ops.gemm_tcgen05(a.cuda(), torch.zeros(n + 4, k, dtype=torch.bfloat16, device="cuda"), ops.EPI_BF16)
 
 
-@pytest.mark.parametrize("batch", [33, 64, 100, 128])
+@pytest.mark.parametrize("batch", [9, 17, 33, 64, 100, 128])
 @pytest.mark.parametrize("n,k", [(144, 136), (2048, 2048), (272, 8192), (1040, 328)])
 def test_wide_decode_gemm_all_epilogues(cuda_device, batch, n, k):
-    """The wide decode product (weights as the 128-row tcgen05 operand, K split with tickets) against
-    float64; a second call must find its tickets reset and give the same bits."""
+    """The wide decode product (weights as the 128-row tcgen05 operand, K split over the blocks of a
+    cluster whose sums meet in distributed shared memory) against float64; a second call gives the
+    same bits."""
     from models_b200.kernels import ops
 
     g = torch.Generator().manual_seed(batch + n + k)
@@ -769,4 +770,44 @@ def test_split_k_residual_product_is_the_same_bits_every_time(cuda_device):
         close(loose, expected, torch.float32, scale=float(expected.abs().max()) * 1e3)
     tickets = ops._split_tickets[torch.cuda.current_device()]
     assert int(tickets.abs().sum()) == 0  # every launch leaves them as it found them
+    assert ops.gemm_tcgen05_status() == 0
+
+
+@pytest.mark.parametrize("batch", [9, 40, 64, 128])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 8, 64, 2048), (6, 3, 128, 264)])
+def test_wide_qkv_product_with_rotation_and_cache_write(cuda_device, batch, heads, kv_heads, head_dim, hidden):
+    """The q/k/v product of a decode step of 9 to 128 sequences with rotation and cache write folded in,
+    against the plain functions: queries rotated by each row's own position, keys rotated and values
+    as they are at each row's cache position, rows without a position of their own storing nothing."""
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(batch * 7 + head_dim)
+    rows_w = (heads + 2 * kv_heads) * head_dim
+    w = (torch.randn(rows_w, hidden, generator=g) * 0.05).bfloat16()
+    x = torch.randn(batch, hidden, generator=g).bfloat16()
+    positions = torch.randint(0, 300, (batch,), generator=g).int()
+    freqs = plain_llama.rope_pair_frequencies(head_dim, 10000.0)
+    cos, sin = plain_llama.rope_cos_sin(torch.arange(300), freqs, None)
+    pages, page = 2 * batch + 1, 64
+    k_pool = torch.zeros(pages, kv_heads, page, head_dim, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    slots = torch.randperm(pages * page - page, generator=g)[:batch].int() + page
+    slots[batch // 2] = -1  # a padding row: nothing is stored for it
+    kd, vd = k_pool.cuda(), v_pool.cuda()
+    q = ops.wide_qkv_rope(x.cuda(), w.cuda(), heads, kv_heads, head_dim, positions.cuda(), cos.cuda(), sin.cuda(), kd, vd, slots.cuda())
+    full = (x.double() @ w.double().t()).float()
+    qe = full[:, : heads * head_dim].bfloat16().float().reshape(batch, heads, head_dim)
+    ke = full[:, heads * head_dim:(heads + kv_heads) * head_dim].bfloat16().float().reshape(batch, kv_heads, head_dim)
+    ve = full[:, (heads + kv_heads) * head_dim:].reshape(batch, kv_heads, head_dim)
+    c, s = cos[positions.long()], sin[positions.long()]
+    qe, ke = plain_llama.rope_rotate_split_half(qe, c, s), plain_llama.rope_rotate_split_half(ke, c, s)
+    close(q.reshape(batch, heads, head_dim), qe, torch.bfloat16)
+    kflat, vflat = kd.cpu().permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim), vd.cpu().permute(0, 2, 1, 3).reshape(-1, kv_heads, head_dim)
+    for b in range(batch):
+        if slots[b] < 0:
+            continue
+        close(kflat[slots[b]], ke[b], torch.bfloat16, scale=float(ke.abs().max()))
+        close(vflat[slots[b]], ve[b], torch.bfloat16, scale=float(ve.abs().max()))
+    stored = (kflat.abs().sum(dim=(1, 2)) > 0).sum()
+    assert int(stored) == batch - 1  # exactly the rows with a cache position wrote
     assert ops.gemm_tcgen05_status() == 0

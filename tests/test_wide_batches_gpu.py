@@ -111,17 +111,21 @@ def test_batches_of_33_64_and_16_one_after_another(cuda_device, folders, name, d
     model.close()
 
 
-def test_the_wide_product_is_the_output_matrix_of_the_wide_vocabulary(cuda_device, folders):
-    """What the test above relies on: at 33 to 128 wanted rows the output matrix of the 19,000-token
-    model goes through the wide tcgen05 product, and the 1,000-token model's does not."""
+def test_which_product_takes_how_many_rows(cuda_device, folders):
+    """What the tests above rely on: 1 to 8 rows take the narrow decode product, 9 to 128 the wide tcgen05
+    product (every matrix of a layer and the output matrix), more the prefill tcgen05 product."""
     import torch
 
     from models_b200.kernels import ops
 
     wide = torch.empty((WIDE_V["vocab_size"], WIDE_V["hidden_size"]), dtype=torch.bfloat16, device="cuda")
     narrow = torch.empty((MID_D["vocab_size"], MID_D["hidden_size"]), dtype=torch.bfloat16, device="cuda")
-    assert ops.gemm_tcgen05_takes(wide, ops.EPI_F32, rows=64) and ops.gemm_tcgen05_takes(wide, ops.EPI_F32, rows=33)
-    assert not ops.gemm_tcgen05_takes(narrow, ops.EPI_F32, rows=64)
+    for weight in (wide, narrow):
+        assert ops.skinny_pays(weight, 8) and not ops.skinny_pays(weight, 9)
+        assert not ops.gemm_tcgen05_takes(weight, ops.EPI_F32, rows=8)
+        assert all(ops.gemm_tcgen05_takes(weight, ops.EPI_F32, rows=rows) for rows in (9, 33, 64, 128, 129, 2048))
+    odd = torch.empty((203, 136), dtype=torch.bfloat16, device="cuda")  # a vocabulary that is no multiple of 8: a library product
+    assert not ops.gemm_tcgen05_takes(odd, ops.EPI_F32, rows=64)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
