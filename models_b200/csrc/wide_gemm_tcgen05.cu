@@ -53,6 +53,18 @@ struct WideArgs {
     const float* sin_table;
     bf16* k_pool;             // [pages][kv_heads][page_size][head_dim]
     bf16* v_pool;
+    // The RMSNorm around a product, without a kernel of its own.  A product whose activations are x * gain (not yet
+    // divided by the root mean square) gets the rows' sums of squares in parts and scales its results by
+    // 1 / sqrt(sum / width + eps) (integrallis/models, backend-java/.../ops/TensorOps.java:45-58).  A residual product
+    // writes, beside the new x, x * gain of the NEXT norm as bfloat16 and its blocks' parts of the sums of squares.
+    const float* ssq_parts;   // [ssq_count][128]: parts of the sums of squares of the activation rows, or null
+    int ssq_count;
+    int norm_width;
+    float eps;
+    const float* emit_gain;   // EPI_RESIDUAL: gain of the next norm [rows_total], or null
+    bf16* emit_rows;          // [batch][ld_emit]: x * gain
+    int ld_emit;
+    float* emit_ssq;          // [tiles * splits][128]: this block's part of each row's sum of squares
 };
 
 // kStages: eight where every block has a multiprocessor to itself anyway (few tiles: the ring is then all that keeps
@@ -96,6 +108,8 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __shared__ __align__(8) uint64_t barriers[2 * kStages + 1];
     static_assert(Plan::kPartialBytes <= kStages * Plan::kStageBytes, "the accumulator's copy reuses the ring");
     __shared__ uint32_t tmem_base_slot;
+    __shared__ float inv_rms[kFinishThreads];  // of the activation rows, when the product carries a norm
+    __shared__ __align__(16) float ssq_warp[4][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full_bar = smem_u32(&barriers[0]), empty_bar = smem_u32(&barriers[kStages]);
     const uint32_t acc_full_bar = smem_u32(&barriers[2 * kStages]);
@@ -185,6 +199,25 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         // ------------------------------------------------------------------ the accumulator -> this block's shared memory
         grid_dependency_wait();  // (what the finishing below reads and adds into comes from the kernel before this one)
         const int quarter = warp & 3;
+        if (args.ssq_parts) {
+            // while the products run: 1 / rms of every activation row from the parts of its sum of squares.  Every lane
+            // takes four rows, every warp a quarter of the parts (in their order, eight loads in flight at a time); the
+            // warps' sums are then added in the order of the warps.
+            const int per_warp = (args.ssq_count + 3) / 4;
+            const int p_begin = min(args.ssq_count, quarter * per_warp), p_end = min(args.ssq_count, p_begin + per_warp);
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4* parts = reinterpret_cast<const float4*>(args.ssq_parts) + lane;
+#pragma unroll 8
+            for (int p = p_begin; p < p_end; ++p) {
+                const float4 v = __ldcg(parts + (size_t)p * 32);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            *reinterpret_cast<float4*>(&ssq_warp[quarter][4 * lane]) = sum;
+            asm volatile("bar.sync 1, %0;" ::"r"(kFinishThreads) : "memory");
+            const int col = threadIdx.x - 64;
+            const float total = ssq_warp[0][col] + ssq_warp[1][col] + ssq_warp[2][col] + ssq_warp[3][col];
+            inv_rms[col] = col < args.batch ? 1.0f / sqrtf(total / (float)args.norm_width + args.eps) : 0.0f;
+        }
         ok = mbar_wait(acc_full_bar, 0, 4);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
@@ -229,25 +262,49 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             }
             return v;
         };
-        for (int item = t; item < quads * args.batch; item += kFinishThreads) {
-            const int unit = first + (item % quads) * 4, col = item / quads;  // neighbouring threads: neighbouring rows of one batch row
+        const bool scaled = args.ssq_parts != nullptr;
+        const int total = quads * args.batch;
+        for (int base = 0; base < total; base += kFinishThreads) {  // (whole warps stay in the loop: the sums below use shuffles)
+            const int item = base + t;
+            const bool active = item < total;
+            const int unit = first + (item % quads) * 4, col = active ? item / quads : 0;  // neighbouring threads: neighbouring rows of one batch row
+            const float scale = scaled ? inv_rms[col] : 1.0f;
             if (!kPaired) {
                 const int row = tile * kTileRows + unit;
-                if (row >= args.rows_total) continue;  // (the number of rows is a multiple of 8: four rows are all inside or all outside)
-                const float4 value = sum_parts(unit, col);
+                const bool live = active && row < args.rows_total;  // (the number of rows is a multiple of 8: four rows are all inside or all outside)
+                float4 value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (live) value = sum_parts(unit, col);
+                value.x *= scale; value.y *= scale; value.z *= scale; value.w *= scale;
                 const size_t at = (size_t)col * args.ld_out + row;
-                if (EPI == EPI_BF16)
+                if (live && EPI == EPI_BF16)
                     *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.out) + at) = make_uint2(pack_bf16(value.x, value.y), pack_bf16(value.z, value.w));
-                if (EPI == EPI_F32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at) = value;
+                if (live && EPI == EPI_F32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at) = value;
                 if (EPI == EPI_RESIDUAL) {  // this thread alone owns the elements
-                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at);
-                    const float4 before = *dst;
-                    *dst = make_float4(before.x + value.x, before.y + value.y, before.z + value.z, before.w + value.w);
+                    float squares = 0.0f;
+                    if (live) {
+                        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at);
+                        const float4 before = *dst;
+                        const float4 x = make_float4(before.x + value.x, before.y + value.y, before.z + value.z, before.w + value.w);
+                        *dst = x;
+                        if (args.emit_gain) {
+                            const float4 g = *reinterpret_cast<const float4*>(args.emit_gain + row);
+                            *reinterpret_cast<uint2*>(args.emit_rows + (size_t)col * args.ld_emit + row) =
+                                make_uint2(pack_bf16(x.x * g.x, x.y * g.y), pack_bf16(x.z * g.z, x.w * g.w));
+                            squares = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+                        }
+                    }
+                    if (args.emit_gain) {
+                        // the `quads` neighbouring threads of one batch row add their squares (a fixed tree); their first writes the part
+                        for (int offset = quads >> 1; offset > 0; offset >>= 1) squares += __shfl_down_sync(0xffffffffu, squares, offset);
+                        if (active && item % quads == 0) args.emit_ssq[(size_t)(tile * splits + rank) * 128 + col] = squares;
+                    }
                 }
             } else if (EPI == EPI_SWIGLU) {
                 const int row = tile * 64 + unit;
-                if (row >= args.rows_total) continue;
-                const float4 gate = sum_parts(unit, col), up = sum_parts(unit + 64, col);
+                if (!active || row >= args.rows_total) continue;
+                float4 gate = sum_parts(unit, col), up = sum_parts(unit + 64, col);
+                gate.x *= scale; gate.y *= scale; gate.z *= scale; gate.w *= scale;
+                up.x *= scale; up.y *= scale; up.z *= scale; up.w *= scale;
                 const int a = args.activation;
                 *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(args.out) + (size_t)col * args.ld_out + row) =
                     make_uint2(pack_bf16(gate_activation(a, gate.x) * up.x, gate_activation(a, gate.y) * up.y),
@@ -256,12 +313,12 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 const int hd = args.head_dim, half = hd / 2;
                 const int head_in_tile = unit / half, d0 = unit % half;
                 const int head = tile * (kTileRows / hd) + head_in_tile;
-                if (head >= args.heads + 2 * args.kv_heads) continue;
+                if (!active || head >= args.heads + 2 * args.kv_heads) continue;
                 const int mma_row = head_in_tile * hd + d0;
                 const float4 first_half = sum_parts(mma_row, col), second_half = sum_parts(mma_row + half, col);
                 // queries and keys pass through bfloat16 before the rotation, as they do when a product stores them
-                float x0[4] = {first_half.x, first_half.y, first_half.z, first_half.w};
-                float x1[4] = {second_half.x, second_half.y, second_half.z, second_half.w};
+                float x0[4] = {first_half.x * scale, first_half.y * scale, first_half.z * scale, first_half.w * scale};
+                float x1[4] = {second_half.x * scale, second_half.y * scale, second_half.z * scale, second_half.w * scale};
                 if (head < args.heads + args.kv_heads) {
                     const size_t at_table = (size_t)args.positions[col] * half + d0;
                     const float4 c4 = *reinterpret_cast<const float4*>(args.cos_table + at_table);
@@ -336,7 +393,7 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Wide
 }
 
 // How many blocks share a tile's K: as many (1, 2, 4 or 8: a cluster) as it takes for every multiprocessor to have a
-// block, while a block keeps at least four 64-column steps of K.
+// block, while a block keeps at least four 64-column steps of K (eight were measured too: a little slower).
 static void plan(int tiles, int k, int multiprocessors, int* splits, int* per_split) {
     const int k_blocks = (k + kBlockK - 1) / kBlockK;
     int s = 1;
@@ -377,8 +434,14 @@ using namespace mb;
 // x: bfloat16 [batch, k] (up to 128 rows); w: bfloat16 [n_w, k].
 // epilogue 0: out bfloat16 [batch, n_w]; 1: float32; 2: float32 += ; 3: w = [gate rows; up rows], out
 // bfloat16 [batch, n_w/2] = act(gate) * up, the activation code (MB_ACT_*) in bits 8 and up of `epilogue`.
+// ssq_parts (or null): [ssq_count][128] parts of the sums of squares of the rows that x is the gained copy of; the
+// results are then scaled by 1 / sqrt(sum / norm_width + eps).  emit_gain (or null, epilogue 2 only): the next norm's
+// gain; the new x times it goes to emit_rows (bfloat16, row stride ld_emit), the blocks' parts of the new rows' sums of
+// squares to emit_ssq [parts][128], and *parts_written says how many parts there are.
 MB_EXPORT int mb_wide_gemm(const void* x, int ldx, const void* w, int ldw, void* out, int ld_out, int batch, int n_w, int k,
-                           int epilogue, int multiprocessors, cudaStream_t stream) {
+                           int epilogue, int multiprocessors, const float* ssq_parts, int ssq_count, int norm_width, float eps,
+                           const float* emit_gain, void* emit_rows, int ld_emit, float* emit_ssq, int* parts_written,
+                           cudaStream_t stream) {
     if (batch <= 0 || n_w <= 0) return 0;
     const int activation = epilogue >> 8;
     epilogue &= 0xff;
@@ -395,6 +458,13 @@ MB_EXPORT int mb_wide_gemm(const void* x, int ldx, const void* w, int ldw, void*
     args.ld_out = ld_out;
     const int tiles = epilogue == EPI_SWIGLU ? (args.rows_total + 63) / 64 : (args.rows_total + kTileRows - 1) / kTileRows;
     plan(tiles, k, multiprocessors, &args.splits, &args.k_blocks_per_split);
+    args.ssq_parts = ssq_parts; args.ssq_count = ssq_count; args.norm_width = norm_width; args.eps = eps;
+    if (emit_gain) {
+        if (epilogue != EPI_RESIDUAL || !emit_rows || !emit_ssq || ld_emit % 4 || ((uintptr_t)emit_gain & 15) || ((uintptr_t)emit_rows & 7))
+            return fail("wide_gemm: the next norm's rows are written by the residual epilogue, into aligned buffers");
+        args.emit_gain = emit_gain; args.emit_rows = (bf16*)emit_rows; args.ld_emit = ld_emit; args.emit_ssq = emit_ssq;
+    }
+    if (parts_written) *parts_written = tiles * args.splits;
     CUtensorMap map_w;
     // (the gated tile is two boxes of 64 rows; rows past the matrix are zeros and their results are not stored)
     if (int status = make_map(&map_w, w, n_w, k, ldw, epilogue == EPI_SWIGLU ? 64 : kTileRows)) return status;
@@ -413,7 +483,7 @@ MB_EXPORT int mb_wide_gemm(const void* x, int ldx, const void* w, int ldw, void*
 MB_EXPORT int mb_wide_qkv_rope(const void* x, int ldx, const void* w, int ldw, void* q_out, int ld_q, int batch, int k, int heads,
                                int kv_heads, int head_dim, const int* positions, const float* cos_table, const float* sin_table,
                                void* k_pool, void* v_pool, const int* slot_mapping, int page_size, int multiprocessors,
-                               cudaStream_t stream) {
+                               const float* ssq_parts, int ssq_count, int norm_width, float eps, cudaStream_t stream) {
     if (batch <= 0) return 0;
     if (head_dim < 16 || kTileRows % head_dim) return fail("wide_qkv_rope: the head size must divide 128, got %d", head_dim);
     if (!positions || !cos_table || !sin_table || !k_pool || !v_pool || !slot_mapping || page_size <= 0)
@@ -428,6 +498,7 @@ MB_EXPORT int mb_wide_qkv_rope(const void* x, int ldx, const void* w, int ldw, v
     args.heads = heads; args.kv_heads = kv_heads; args.head_dim = head_dim; args.page_size = page_size;
     args.positions = positions; args.slot_mapping = slot_mapping; args.cos_table = cos_table; args.sin_table = sin_table;
     args.k_pool = (bf16*)k_pool; args.v_pool = (bf16*)v_pool;
+    args.ssq_parts = ssq_parts; args.ssq_count = ssq_count; args.norm_width = norm_width; args.eps = eps;
     const int tiles = (args.rows_total + kTileRows - 1) / kTileRows;
     plan(tiles, k, multiprocessors, &args.splits, &args.k_blocks_per_split);
     CUtensorMap map_w;

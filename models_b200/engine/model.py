@@ -11,7 +11,7 @@ from typing import Callable, Dict, List, Mapping, Optional
 import torch
 
 from ..config.specs import ModelSpec
-from ..parts import RunContext, Runtime, build_part
+from ..parts import RunContext, Runtime, as_delta, build_part
 from ..weights.loader import ParamRequest, check_names_and_shapes
 
 
@@ -83,13 +83,25 @@ class DecoderModel:
                 return logits
         x = self.embedding.forward(batch.tokens)
         pending = None
-        for run, entry in zip(runs, self.spec.schedule):
-            pending = self.blocks[entry.layer].forward(x, pending, batch, run)
+        schedule = self.spec.schedule
+        for index, (run, entry) in enumerate(zip(runs, schedule)):
+            block = self.blocks[entry.layer]
+            if getattr(block, "takes_next_norm", False):
+                # the norm that reads the stream after this run: the next run's first norm, or the final one
+                following = self.blocks[schedule[index + 1].layer] if index + 1 < len(schedule) else None
+                next_norm = getattr(following, "mixer_norm", None) if following is not None else self.final_norm
+                pending = block.forward(x, pending, batch, run, next_norm)
+            else:
+                pending = block.forward(x, as_delta(pending), batch, run)
             if self.observer is not None:
-                self.observer(run.run, x + pending.float() if pending is not None else x.clone())
+                delta = as_delta(pending)
+                self.observer(run.run, x + delta.float() if delta is not None else x.clone())
         if batch.num_wanted == 0:
             return None
-        return self.head.forward(x, pending, self.final_norm, batch.want_rows)
+        if getattr(self.head, "takes_prenormed", False):
+            every_row = batch.max_q_len == 1 and batch.num_wanted == batch.num_tokens
+            return self.head.forward(x, pending, self.final_norm, batch.want_rows, every_row)
+        return self.head.forward(x, as_delta(pending), self.final_norm, batch.want_rows)
 
 
 def parameter_requests(spec: ModelSpec) -> Dict[str, ParamRequest]:

@@ -645,12 +645,33 @@ def wide_gemm_lib():
     return load_library("mb_wide_gemm_tcgen05", ["wide_gemm_tcgen05.cu"])
 
 
-def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+SSQ_COLUMNS = 128  # columns of a table of parts of sums of squares: one per activation row
+
+
+def _norm_args(norm_parts):
+    """(ssq_parts, count, width, eps) of a product whose activations still lack the division by the root mean
+    square, as the C launchers take them."""
+    if norm_parts is None:
+        return None, 0, 0, ctypes.c_float(0.0)
+    ssq, count, width, eps = norm_parts
+    if ssq.dtype != torch.float32 or not ssq.is_contiguous() or ssq.dim() != 2 or ssq.shape[1] != SSQ_COLUMNS or ssq.shape[0] < count:
+        raise KernelError(f"parts of sums of squares must be a contiguous float32 [parts, {SSQ_COLUMNS}] table")
+    return _p(ssq), int(count), int(width), ctypes.c_float(eps)
+
+
+def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None,
+              norm_parts=None, emit_gain: Optional[torch.Tensor] = None):
     """Up to 128 activation rows times weight^T on the tcgen05 tensor cores with the weights as the
     128-row operand (decode at wide batches); K is split over the blocks of a cluster where a matrix has
     few row tiles, their sums meeting in distributed shared memory in a fixed order.  Epilogues as for
-    skinny_gemm."""
-    _cuda(x, weight, out)
+    skinny_gemm.
+
+    The RMSNorm before a product can ride in it: `x` is then the rows times the norm's gain, and
+    `norm_parts` = (parts of the rows' sums of squares [parts, 128], how many parts, the rows' width, eps);
+    the results are scaled by 1 / rms.  The residual epilogue can prepare the NEXT norm the same way: with
+    `emit_gain` (that norm's gain) it returns (out, rows of the new `out` times the gain as bfloat16, parts of
+    their sums of squares, how many parts)."""
+    _cuda(x, weight, out, emit_gain)
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] != weight.shape[1] or x.shape[0] > WIDE_ROWS:
         raise KernelError(f"wide_gemm: activations {tuple(x.shape)} {x.dtype} do not fit the weight {tuple(weight.shape)}")
     if not gemm_tcgen05_takes(weight, epilogue) or x.stride(0) % 8 or x.data_ptr() % 16:
@@ -664,9 +685,20 @@ def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, o
             raise KernelError("the residual epilogue adds into a float32 [rows, n] tensor")
     elif out is None:
         out = torch.empty((batch, n), dtype=torch.float32 if kind == EPI_F32 else torch.bfloat16, device=x.device)
+    emit_rows = emit_ssq = None
+    written = ctypes.c_int(0)
+    if emit_gain is not None:
+        if kind != EPI_RESIDUAL or emit_gain.dtype != torch.float32 or emit_gain.numel() != n:
+            raise KernelError("the next norm's rows come from the residual epilogue, with a float32 gain of the output's width")
+        emit_rows = torch.empty((batch, n), dtype=torch.bfloat16, device=x.device)
+        emit_ssq = torch.empty((8 * -(-n // 128), SSQ_COLUMNS), dtype=torch.float32, device=x.device)
+    ssq, count, width, eps = _norm_args(norm_parts)
     lib = wide_gemm_lib()
     _run(lib, lib.mb_wide_gemm(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), batch, n_w, k,
-                               epilogue, _sm_count(x.device), _stream()))
+                               epilogue, _sm_count(x.device), ssq, count, width, eps, _p(emit_gain), _p(emit_rows),
+                               emit_rows.stride(0) if emit_rows is not None else 0, _p(emit_ssq), ctypes.byref(written), _stream()))
+    if emit_gain is not None:
+        return out, emit_rows, emit_ssq, written.value
     return out
 
 
@@ -679,10 +711,10 @@ def wide_qkv_rope_takes(weight: torch.Tensor, rows: int, heads: int, kv_heads: i
 
 def wide_qkv_rope(x: torch.Tensor, weight: torch.Tensor, heads: int, kv_heads: int, head_dim: int, positions: torch.Tensor,
                   cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                  slot_mapping: torch.Tensor) -> torch.Tensor:
+                  slot_mapping: torch.Tensor, norm_parts=None) -> torch.Tensor:
     """The q/k/v product of an attention layer on 9 to 128 rows with what follows it folded in: rotation of
     queries and keys (split-half pairs over the whole head) and the paged cache write of keys and values.
-    Returns the rotated queries, bfloat16 [rows, heads * head_dim]."""
+    Returns the rotated queries, bfloat16 [rows, heads * head_dim].  `norm_parts` as for wide_gemm."""
     _cuda(x, weight, positions, cos, sin, k_pool, v_pool, slot_mapping)
     batch, k = x.shape
     if x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16 or weight.shape[1] != k:
@@ -699,10 +731,11 @@ def wide_qkv_rope(x: torch.Tensor, weight: torch.Tensor, heads: int, kv_heads: i
             or k_pool.shape[3] != head_dim or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
         raise KernelError("cache pools must be contiguous bfloat16 [pages, kv_heads, page_size, head_dim]")
     q = torch.empty((batch, heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    ssq, count, width, eps = _norm_args(norm_parts)
     lib = wide_gemm_lib()
     _run(lib, lib.mb_wide_qkv_rope(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(q), q.stride(0), batch, k, heads, kv_heads,
                                    head_dim, _p(positions), _p(cos), _p(sin), _p(k_pool), _p(v_pool), _p(slot_mapping),
-                                   k_pool.shape[2], _sm_count(x.device), _stream()))
+                                   k_pool.shape[2], _sm_count(x.device), ssq, count, width, eps, _stream()))
     return q
 
 

@@ -15,7 +15,7 @@ import torch
 from ..cache.kv_cache import KvRequest
 from ..kernels import ops
 from ..weights.loader import ParamRequest
-from .base import Mixer, RunContext
+from .base import Mixer, Prenormed, RunContext
 from .linear import linear
 from .registry import build_part, register_part
 
@@ -124,6 +124,30 @@ class AttentionMixer(Mixer):
                 ops.bias_add(qkv, self.b_qkv if writes else self.b_q)
             attended = self._rotate_store_attend(qkv, batch, run)
         ops.tensor_core_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x)
+
+    def chains(self, rows: int, run: RunContext, next_norm) -> bool:
+        """Whether `forward_chain` applies: 9 to 128 rows on the wide decode products, rotation and cache write
+        folded into the q/k/v product, no biases, and a next norm whose gain a residual product can apply."""
+        s, pos = self.spec, self.position
+        return (self.b_qkv is None and self.b_o is None and run.writes_cache and pos is not None
+                and pos.rotary_dim == s.head_dim and not pos.interleaved and run.k_pool is not None
+                and run.k_pool.dtype == torch.bfloat16 and getattr(next_norm, "foldable", False)
+                and ops.wide_qkv_rope_takes(self.w_qkv, rows, s.num_heads, s.num_kv_heads, s.head_dim)
+                and ops.gemm_tcgen05_takes(self.w_o, ops.EPI_RESIDUAL, rows))
+
+    def forward_chain(self, x: torch.Tensor, scaled, batch, run: RunContext, next_norm) -> Prenormed:
+        """x += Wo . attention(rotate(Wqkv . norm(x))) for 9 to 128 rows, in three kernels and with no kernel for
+        either norm: `scaled` is the normalised rows, or a Prenormed whose division by the root mean square the
+        q/k/v product does itself; the output product adds into x and prepares the rows of `next_norm`."""
+        s, pos = self.spec, self.position
+        group = batch.groups[run.group]
+        rows, parts = (scaled.rows, scaled.norm_parts()) if isinstance(scaled, Prenormed) else (scaled, None)
+        q = ops.wide_qkv_rope(rows, self.w_qkv, s.num_heads, s.num_kv_heads, s.head_dim, batch.positions, pos.cos, pos.sin,
+                              run.k_pool, run.v_pool, group.slot_mapping, norm_parts=parts)
+        attended = torch.empty((q.shape[0], self.q_width), dtype=q.dtype, device=q.device)
+        self.attend(q, attended, batch, group, run)
+        _, gained, ssq, count = ops.wide_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
+        return Prenormed(gained, ssq, count, x.shape[1], next_norm.spec.eps, next_norm)
 
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:
         dtype = self.runtime.compute_dtype

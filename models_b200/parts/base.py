@@ -15,6 +15,8 @@ Interfaces (duck-typed; the base classes below only document them):
                 forward(xn, batch, run) -> delta [T, width] in the compute dtype.
   FeedForward   forward(xn) -> delta [T, width] in the compute dtype.
   Block         forward(x, pending, batch, run) -> new pending delta; adds `pending` into x first.
+                A block that sets `takes_next_norm` is also given `next_norm` (the norm that will read the
+                stream after it) and may then return a `Prenormed` in place of a delta.
 """
 
 from __future__ import annotations
@@ -77,6 +79,30 @@ class RunContext:
     v_pool: Optional[torch.Tensor] = None
     writes_cache: bool = True
     state: Optional[torch.Tensor] = None
+
+
+@dataclass
+class Prenormed:
+    """What a block may hand on in place of a delta that is still to be added: the residual stream is up to
+    date, and the rows of the NEXT norm are half done -- `rows` holds x times that norm's gain (bfloat16) and
+    `ssq` the parts of every row's sum of squares ([parts, 128] float32, `count` of them valid).  A product
+    that takes them divides by the root mean square in its own epilogue, so the norm needs no kernel."""
+
+    rows: torch.Tensor
+    ssq: torch.Tensor
+    count: int
+    width: int
+    eps: float
+    norm: object  # the norm part whose gain and eps went into `rows`: only that norm's consumer may use them
+
+    def norm_parts(self):
+        return self.ssq, self.count, self.width, self.eps
+
+
+def as_delta(pending):
+    """The delta that is still to be added into the residual stream, or None (also for a Prenormed: the
+    stream it belongs to is up to date)."""
+    return None if isinstance(pending, Prenormed) else pending
 
 
 class Part:

@@ -13,11 +13,13 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import Part, RunContext
+from .base import Part, Prenormed, RunContext, as_delta
 from .registry import build_part, register_part
 
 
 class PreNormBlock(Part):
+    takes_next_norm = True  # `forward` is told which norm reads the stream next, and may hand it a Prenormed
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
@@ -33,8 +35,20 @@ class PreNormBlock(Part):
         for part in self.parts:
             part.load(tensors)
 
-    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], batch, run: RunContext) -> Optional[torch.Tensor]:
+    def forward(self, x: torch.Tensor, pending, batch, run: RunContext, next_norm=None):
         rows = x.shape[0]
+        mixer_chains = getattr(self.mixer, "chains", None)
+        ffn_chains = getattr(self.feed_forward, "chains", None)
+        if (self.runtime.mode == "bfloat16" and mixer_chains and ffn_chains and ffn_chains(rows)
+                and mixer_chains(rows, run, self.feed_forward_norm) and getattr(self.mixer_norm, "foldable", False)):
+            # 9 to 128 rows (decode at wide batches): five kernels a layer, the norms riding in the products around them
+            if isinstance(pending, Prenormed) and pending.norm is self.mixer_norm:
+                scaled = pending
+            else:
+                scaled = self.mixer_norm.forward(x, as_delta(pending))
+            half_way = self.mixer.forward_chain(x, scaled, batch, run, self.feed_forward_norm)
+            return self.feed_forward.forward_chain(x, half_way, next_norm)
+        pending = as_delta(pending)  # (a Prenormed means: nothing left to add)
         mixer_folds = getattr(self.mixer, "folds", None)
         ffn_folds = getattr(self.feed_forward, "folds", None)
         if (self.runtime.mode == "bfloat16" and mixer_folds and ffn_folds and mixer_folds(rows, self.mixer_norm)

@@ -12,7 +12,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import ParamRequest
-from .base import Part
+from .base import Part, Prenormed
 from .linear import linear
 from .registry import register_part
 
@@ -85,6 +85,25 @@ class GatedFeedForward(Part):
             ops.gemm_tcgen05(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
         else:
             ops.tensor_core_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+
+    def chains(self, rows: int) -> bool:
+        """Whether `forward_chain` applies: 9 to 128 rows on the wide decode products, no biases."""
+        return (self.b_gate_up is None and self.b_down is None and ops.SKINNY_PAYS_ROWS < rows <= ops.WIDE_ROWS
+                and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows)
+                and ops.gemm_tcgen05_takes(self.w_down, ops.EPI_RESIDUAL, rows))
+
+    def forward_chain(self, x: torch.Tensor, scaled, next_norm):
+        """x += down(act(gate(norm(x))) * up(norm(x))) for 9 to 128 rows in two kernels: `scaled` is the normalised
+        rows, or a Prenormed whose division by the root mean square the gate/up product does itself; the down
+        product adds into x and, given a `next_norm` whose gain it can apply, prepares that norm's rows (the
+        return value; else None)."""
+        rows, parts = (scaled.rows, scaled.norm_parts()) if isinstance(scaled, Prenormed) else (scaled, None)
+        hidden = ops.wide_gemm(rows, self.w_gate_up, self.gated, norm_parts=parts)
+        if next_norm is None or not getattr(next_norm, "foldable", False):
+            ops.wide_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+            return None
+        _, gained, ssq, count = ops.wide_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
+        return Prenormed(gained, ssq, count, x.shape[1], next_norm.spec.eps, next_norm)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:
         dtype = self.runtime.compute_dtype

@@ -19,12 +19,14 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import ParamRequest
-from .base import Part
+from .base import Part, Prenormed, as_delta
 from .linear import linear
 from .registry import register_part
 
 
 class LinearHead(Part):
+    takes_prenormed = True  # `forward` may be given a Prenormed as `pending`, and is told when every row is wanted
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if spec.softcap < 0.0:
@@ -42,17 +44,26 @@ class LinearHead(Part):
         else:
             self.weight = self.runtime.matrix(tensors[self.spec.weights["weight"]])
 
-    def forward(self, x: torch.Tensor, pending: Optional[torch.Tensor], norm, want_rows: torch.Tensor) -> torch.Tensor:
-        """x: the float32 residual stream, `pending` a delta not yet added into it (or None); `norm` the
-        final norm part; `want_rows` int32 rows of x whose logits are wanted."""
+    def forward(self, x: torch.Tensor, pending, norm, want_rows: torch.Tensor, every_row: bool = False) -> torch.Tensor:
+        """x: the float32 residual stream, `pending` a delta not yet added into it (or None, or a Prenormed
+        for `norm`); `norm` the final norm part; `want_rows` int32 rows of x whose logits are wanted
+        (`every_row`: all of them, in order)."""
         rows = want_rows.numel()
+        s = self.spec
+        if (every_row and isinstance(pending, Prenormed) and pending.norm is norm and self.runtime.mode == "bfloat16"
+                and ops.SKINNY_PAYS_ROWS < rows <= ops.WIDE_ROWS and ops.gemm_tcgen05_takes(self.weight, ops.EPI_F32, rows)):
+            # the last layer prepared the final norm's rows: the output product divides by the root mean square itself
+            logits = ops.wide_gemm(pending.rows, self.weight, ops.EPI_F32, norm_parts=pending.norm_parts())
+            if s.logit_scale != 1.0 or s.softcap != 0.0:
+                ops.logit_epilogue(logits, s.logit_scale, s.softcap)
+            return logits
+        pending = as_delta(pending)
         if (pending is None and self.runtime.mode == "bfloat16" and getattr(norm, "foldable", False)
                 and ops.skinny_pays(self.weight, rows, with_norm=True)):
             # few wanted rows: gather, final norm and output product in one kernel
             logits = ops.skinny_gemm(self.weight, ops.EPI_F32, xf=x, gain=norm.weight, eps=norm.spec.eps, rows=want_rows)
         else:
             logits = linear(norm.forward(x, pending, rows=want_rows), self.weight, torch.float32)
-        s = self.spec
         if s.logit_scale != 1.0 or s.softcap != 0.0:
             ops.logit_epilogue(logits, s.logit_scale, s.softcap)
         return logits
