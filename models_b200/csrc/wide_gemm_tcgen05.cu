@@ -240,14 +240,17 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (splits > 1) cluster_sync_all();
     else __syncthreads();
 
-    if (warp >= 2) {
+    {
         // ------------------------------------------------------------------ finishing: a share of the tile's rows (or pairs of rows) per
-        // block, four neighbouring rows per thread and step (they are neighbours in shared memory and in the output)
-        const int t = threadIdx.x - 64;
+        // block, four neighbouring rows per thread and step (they are neighbours in shared memory and in the output);
+        // all six warps take part (the loading and the issuing warp have nothing left to do)
+        if (warp < 2) grid_dependency_wait();  // (their lanes read what the kernel before this one wrote, too)
+        const int t = threadIdx.x;
         const uint32_t partial_addr = smem_u32(smem);
         constexpr int kUnits = kPaired ? 64 : 128;     // rows, or pairs of rows, of a tile
-        const int per_block = kUnits / splits;         // splits is 1, 2, 4 or 8: a multiple of 4
+        const int per_block = kUnits / splits;         // splits is 1, 2, 4 or 8: a multiple of 4, and a power of two
         const int quads = per_block / 4;
+        const int quad_shift = 31 - __clz(quads);
         const int first = rank * per_block;
         auto sum_parts = [&](int mma_row, int col) {   // rows mma_row .. mma_row + 3 of batch column col, over all parts of K
             const uint32_t at = partial_addr + (uint32_t)(col * kTileRows + mma_row) * 4u;
@@ -264,10 +267,10 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         };
         const bool scaled = args.ssq_parts != nullptr;
         const int total = quads * args.batch;
-        for (int base = 0; base < total; base += kFinishThreads) {  // (whole warps stay in the loop: the sums below use shuffles)
+        for (int base = 0; base < total; base += kThreads) {  // (whole warps stay in the loop: the sums below use shuffles)
             const int item = base + t;
             const bool active = item < total;
-            const int unit = first + (item % quads) * 4, col = active ? item / quads : 0;  // neighbouring threads: neighbouring rows of one batch row
+            const int unit = first + (item & (quads - 1)) * 4, col = active ? item >> quad_shift : 0;  // neighbouring threads: neighbouring rows of one batch row
             const float scale = scaled ? inv_rms[col] : 1.0f;
             if (!kPaired) {
                 const int row = tile * kTileRows + unit;
@@ -296,7 +299,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     if (args.emit_gain) {
                         // the `quads` neighbouring threads of one batch row add their squares (a fixed tree); their first writes the part
                         for (int offset = quads >> 1; offset > 0; offset >>= 1) squares += __shfl_down_sync(0xffffffffu, squares, offset);
-                        if (active && item % quads == 0) args.emit_ssq[(size_t)(tile * splits + rank) * 128 + col] = squares;
+                        if (active && (item & (quads - 1)) == 0) args.emit_ssq[(size_t)(tile * splits + rank) * 128 + col] = squares;
                     }
                 }
             } else if (EPI == EPI_SWIGLU) {

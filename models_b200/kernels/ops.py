@@ -648,15 +648,17 @@ def wide_gemm_lib():
 SSQ_COLUMNS = 128  # columns of a table of parts of sums of squares: one per activation row
 
 
-def _norm_args(norm_parts):
-    """(ssq_parts, count, width, eps) of a product whose activations still lack the division by the root mean
-    square, as the C launchers take them."""
+def _norm_args(norm_parts, rows: int, columns: Optional[int] = None):
+    """(ssq_parts, count, row stride, width, eps) of a product whose activations still lack the division by the
+    root mean square, as the C launchers take them.  The table is [parts, columns] float32 with a column per
+    activation row (`columns` given: exactly so many)."""
     if norm_parts is None:
-        return None, 0, 0, ctypes.c_float(0.0)
+        return None, 0, 0, 0, ctypes.c_float(0.0)
     ssq, count, width, eps = norm_parts
-    if ssq.dtype != torch.float32 or not ssq.is_contiguous() or ssq.dim() != 2 or ssq.shape[1] != SSQ_COLUMNS or ssq.shape[0] < count:
-        raise KernelError(f"parts of sums of squares must be a contiguous float32 [parts, {SSQ_COLUMNS}] table")
-    return _p(ssq), int(count), int(width), ctypes.c_float(eps)
+    if (ssq.dtype != torch.float32 or ssq.dim() != 2 or ssq.stride(1) != 1 or ssq.shape[1] < rows or ssq.shape[0] < count or count <= 0
+            or (columns is not None and (ssq.shape[1] != columns or ssq.stride(0) != columns))):
+        raise KernelError(f"parts of sums of squares must be a float32 [parts, {columns or 'rows'}] table with a column per row")
+    return _p(ssq), int(count), ssq.stride(0), int(width), ctypes.c_float(eps)
 
 
 def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None,
@@ -692,7 +694,7 @@ def wide_gemm(x: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, o
             raise KernelError("the next norm's rows come from the residual epilogue, with a float32 gain of the output's width")
         emit_rows = torch.empty((batch, n), dtype=torch.bfloat16, device=x.device)
         emit_ssq = torch.empty((8 * -(-n // 128), SSQ_COLUMNS), dtype=torch.float32, device=x.device)
-    ssq, count, width, eps = _norm_args(norm_parts)
+    ssq, count, _, width, eps = _norm_args(norm_parts, batch, SSQ_COLUMNS)
     lib = wide_gemm_lib()
     _run(lib, lib.mb_wide_gemm(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(out), out.stride(0), batch, n_w, k,
                                epilogue, _sm_count(x.device), ssq, count, width, eps, _p(emit_gain), _p(emit_rows),
@@ -731,7 +733,7 @@ def wide_qkv_rope(x: torch.Tensor, weight: torch.Tensor, heads: int, kv_heads: i
             or k_pool.shape[3] != head_dim or not k_pool.is_contiguous() or not v_pool.is_contiguous()):
         raise KernelError("cache pools must be contiguous bfloat16 [pages, kv_heads, page_size, head_dim]")
     q = torch.empty((batch, heads * head_dim), dtype=torch.bfloat16, device=x.device)
-    ssq, count, width, eps = _norm_args(norm_parts)
+    ssq, count, _, width, eps = _norm_args(norm_parts, batch, SSQ_COLUMNS)
     lib = wide_gemm_lib()
     _run(lib, lib.mb_wide_qkv_rope(_p(x), x.stride(0), _p(weight), weight.stride(0), _p(q), q.stride(0), batch, k, heads, kv_heads,
                                    head_dim, _p(positions), _p(cos), _p(sin), _p(k_pool), _p(v_pool), _p(slot_mapping),
@@ -739,10 +741,16 @@ def wide_qkv_rope(x: torch.Tensor, weight: torch.Tensor, heads: int, kv_heads: i
     return q
 
 
-def tensor_core_gemm(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """The tcgen05 product for this many rows: up to 128 the wide decode form, above the prefill form."""
+def tensor_core_gemm(a: torch.Tensor, weight: torch.Tensor, epilogue: int = EPI_BF16, out: Optional[torch.Tensor] = None,
+                     norm_parts=None, emit_gain: Optional[torch.Tensor] = None):
+    """The tcgen05 product for this many rows: up to 128 the wide decode form, above the prefill form.  The norms
+    around a product ride in the wide form only (`norm_parts`, `emit_gain`, see wide_gemm): over a whole prompt a
+    norm kernel runs at the speed of memory, and a residual epilogue that does its work, one tile per block with
+    nothing to hide behind, was measured to cost as much (4 us each at 2,048 rows of 2,048)."""
     if a.shape[0] <= WIDE_ROWS:
-        return wide_gemm(a, weight, epilogue, out)
+        return wide_gemm(a, weight, epilogue, out, norm_parts=norm_parts, emit_gain=emit_gain)
+    if norm_parts is not None or emit_gain is not None:
+        raise KernelError("the norms ride in the products of up to 128 rows only")
     return gemm_tcgen05(a, weight, epilogue, out)
 
 

@@ -650,6 +650,52 @@ def test_wide_decode_gemm_all_epilogues(cuda_device, batch, n, k):
     assert ops.gemm_tcgen05_status() == 0
 
 
+@pytest.mark.parametrize("rows", [9, 33, 64, 100, 128])
+@pytest.mark.parametrize("width,inner", [(264, 520), (2048, 2048), (272, 4136)])
+def test_the_norm_rides_in_the_products_around_it(cuda_device, rows, width, inner):
+    """x = x + h . Wd^T with the next RMSNorm half done in the same kernel (x * gain as bfloat16, and parts of
+    every row's sum of squares), then a product that divides by the root mean square in its own epilogue:
+    against float64 of the same steps (y = x / sqrt(mean(x^2) + eps) * gain, integrallis/models,
+    backend-java/.../ops/TensorOps.java:45-58).  These are the wide decode products (9 to 128 rows); over more
+    rows the norms keep kernels of their own, and the products say so."""
+    from models_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(rows + width + inner)
+    eps = 3e-5
+    h = torch.randn(rows, inner, generator=g).bfloat16()
+    w_down = (torch.randn(width, inner, generator=g) * 0.05).bfloat16()
+    w_next = (torch.randn(144, width, generator=g) * 0.05).bfloat16()
+    gain = (1.0 + 0.2 * torch.randn(width, generator=g)).float()
+    x = (3.0 * torch.randn(rows, width, generator=g)).float()
+    xd = x.cuda()
+    out, gained, ssq, count = ops.tensor_core_gemm(h.cuda(), w_down.cuda(), ops.EPI_RESIDUAL, out=xd, emit_gain=gain.cuda())
+    assert out is xd and gained.shape == (rows, width) and gained.dtype == torch.bfloat16
+    exact_x = x.double() + h.double() @ w_down.double().t()
+    scale = float(exact_x.abs().max())
+    assert float((xd.double().cpu() - exact_x).abs().max()) < 2e-5 * scale * math.sqrt(inner)
+    # the gained rows are the kernel's own new x times the gain, rounded once
+    assert torch.equal(gained.cpu(), (xd.cpu() * gain).bfloat16())
+    squares = ssq[:count, :rows].double().sum(0).cpu()
+    want_squares = (xd.double().cpu() ** 2).sum(1)
+    assert float(((squares - want_squares) / want_squares).abs().max()) < 1e-5
+    parts = (ssq, count, width, eps)
+    inv_rms = 1.0 / torch.sqrt(want_squares / width + eps)
+    normed = gained.double().cpu() * inv_rms[:, None]
+    exact = normed @ w_next.double().t()
+    got = ops.tensor_core_gemm(gained, w_next.cuda(), ops.EPI_F32, norm_parts=parts)
+    assert float((got.double().cpu() - exact).abs().max()) < 2e-5 * float(exact.abs().max()) * math.sqrt(width)
+    got = ops.tensor_core_gemm(gained, w_next.cuda(), ops.EPI_SWIGLU, norm_parts=parts)
+    want = plain_llama.swiglu(exact[:, :72], exact[:, 72:])
+    assert float((got.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
+    # the same bits in a second run (ordered sums everywhere)
+    xd2 = x.cuda()
+    _, gained2, ssq2, count2 = ops.tensor_core_gemm(h.cuda(), w_down.cuda(), ops.EPI_RESIDUAL, out=xd2, emit_gain=gain.cuda())
+    assert torch.equal(xd, xd2) and torch.equal(gained, gained2) and count == count2 and torch.equal(ssq[:count, :rows], ssq2[:count, :rows])
+    assert ops.gemm_tcgen05_status() == 0
+    with pytest.raises(ops.KernelError, match="128 rows"):
+        ops.tensor_core_gemm(torch.zeros(129, width, dtype=torch.bfloat16, device="cuda"), w_next.cuda(), ops.EPI_F32, norm_parts=parts)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("count", [1, 3, 4, 1001, 262147])
 def test_random_weights_are_the_same_bits_on_host_and_device(cuda_device, dtype, count):
@@ -775,10 +821,13 @@ def test_split_k_residual_product_is_the_same_bits_every_time(cuda_device):
 
 @pytest.mark.parametrize("batch", [9, 40, 64, 128])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 8, 64, 2048), (6, 3, 128, 264)])
-def test_wide_qkv_product_with_rotation_and_cache_write(cuda_device, batch, heads, kv_heads, head_dim, hidden):
+@pytest.mark.parametrize("normed", [False, True])
+def test_wide_qkv_product_with_rotation_and_cache_write(cuda_device, batch, heads, kv_heads, head_dim, hidden, normed):
     """The q/k/v product of a decode step of 9 to 128 sequences with rotation and cache write folded in,
     against the plain functions: queries rotated by each row's own position, keys rotated and values
-    as they are at each row's cache position, rows without a position of their own storing nothing."""
+    as they are at each row's cache position, rows without a position of their own storing nothing.
+    `normed`: the division by the rows' root mean square happens in the product's epilogue, from parts
+    of their sums of squares."""
     from models_b200.kernels import ops
 
     g = torch.Generator().manual_seed(batch * 7 + head_dim)
@@ -794,8 +843,14 @@ def test_wide_qkv_product_with_rotation_and_cache_write(cuda_device, batch, head
     slots = torch.randperm(pages * page - page, generator=g)[:batch].int() + page
     slots[batch // 2] = -1  # a padding row: nothing is stored for it
     kd, vd = k_pool.cuda(), v_pool.cuda()
-    q = ops.wide_qkv_rope(x.cuda(), w.cuda(), heads, kv_heads, head_dim, positions.cuda(), cos.cuda(), sin.cuda(), kd, vd, slots.cuda())
-    full = (x.double() @ w.double().t()).float()
+    parts, inv_rms = None, torch.ones(batch, dtype=torch.float64)
+    if normed:
+        ssq = torch.rand(7, ops.SSQ_COLUMNS, generator=g) * hidden  # (two more parts than are counted)
+        parts = (ssq.cuda(), 5, hidden, 2e-5)
+        inv_rms = 1.0 / torch.sqrt(ssq[:5, :batch].double().sum(0) / hidden + 2e-5)
+    q = ops.wide_qkv_rope(x.cuda(), w.cuda(), heads, kv_heads, head_dim, positions.cuda(), cos.cuda(), sin.cuda(), kd, vd, slots.cuda(),
+                          norm_parts=parts)
+    full = ((x.double() @ w.double().t()) * inv_rms[:, None]).float()
     qe = full[:, : heads * head_dim].bfloat16().float().reshape(batch, heads, head_dim)
     ke = full[:, heads * head_dim:(heads + kv_heads) * head_dim].bfloat16().float().reshape(batch, kv_heads, head_dim)
     ve = full[:, (heads + kv_heads) * head_dim:].reshape(batch, kv_heads, head_dim)
