@@ -24,7 +24,8 @@
 // Formula: integrallis/models, backend-java/.../llama/LlamaForwardPass.java:1543-1670 (kvHead = head /
 // group; dot first, then scale; only positions <= the query's are read; with a window of n only the n
 // positions that end at the query) and backend-java/.../ops/TensorOps.java:1247-1279 (softmax), in its
-// running form.  Probabilities are rounded to bfloat16 for the P . V product.
+// running form.  Probabilities enter the P . V product as bfloat16: scaled up by 1 + 2^-9 and truncated, which errs
+// like rounding to nearest (the sum takes the same scaled values, and the factor is divided out at the end).
 //
 // Every mbarrier wait is bounded (about two seconds); a role that gives up records where, all roles
 // meet at the final barrier, tensor memory is freed and the kernel returns.
@@ -51,8 +52,14 @@ constexpr int kQBytes = kBoxes * kQBoxBytes;
 constexpr int kKVBoxBytes = kKeys * 128;  // [64 keys][64 columns]
 constexpr int kKVTileBytes = kBoxes * kKVBoxBytes;
 constexpr int kStages = HD == 64 ? 3 : 2;      // of the key ring and of the value ring, each
-constexpr int kPColumns = kKeys / 2;           // probabilities of one page: bfloat16 pairs in 32-bit columns
-constexpr int kThreads = 192;
+// Of every four pairs of probabilities, so many are exponentiated by arithmetic (soft_exp2_x2) instead of the
+// special-function unit, which gives 16 results a clock and multiprocessor and is the busiest pipe of this kernel
+// (66 % of its cycles at heads of 64).  Measured at 2,048 / 8,192 tokens, heads of 64: none 477 / 726 TFLOP/s, one
+// 498 / 737, two 461 / 700, three 424 / 634: past one pair the added instructions cost more than the unit gains.
+constexpr int kSoftPairs = HD == 64 ? 1 : 0;
+constexpr int kCols = kKeys;                   // keys of a page per softmax thread: a thread takes its whole row
+constexpr int kSoftmaxWarps = 4;
+constexpr int kThreads = 64 + 32 * kSoftmaxWarps;
 constexpr int kScoreColumns = 64;
 constexpr int kTmemColumns = 256;  // two score buffers and the output: 2 * 64 + HD
 static_assert(2 * kScoreColumns + HD <= kTmemColumns, "tensor memory budget");
@@ -118,14 +125,42 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
     return d;
 }
 
+// 2^x for two floats at once without the special-function unit: x = n + f with n the nearest integer (the
+// magic-number addition leaves n in the low mantissa bits) and f in [-0.5, 0.5]; 2^f by a cubic (relative error 1e-4,
+// a twentieth of the rounding to bfloat16 that follows); n is added into the exponent bits.  x below -126 counts as -126.
+__device__ __forceinline__ void soft_exp2_x2(uint64_t x2, float& e0, float& e1) {
+    float x0, x1;
+    unpack_f32x2(x2, x0, x1);
+    const uint64_t x = pack_f32x2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f), minus_magic = pack_f32x2(-12582912.0f, -12582912.0f);
+    const uint64_t minus_one = pack_f32x2(-1.0f, -1.0f), one = pack_f32x2(1.0f, 1.0f);
+    const uint64_t c1 = pack_f32x2(0.69328290f, 0.69328290f), c2 = pack_f32x2(0.24221095f, 0.24221095f), c3 = pack_f32x2(0.05500893f, 0.05500893f);
+    const uint64_t r = add_f32x2(x, magic);
+    const uint64_t f = fma_f32x2(add_f32x2(r, minus_magic), minus_one, x);
+    const uint64_t p = fma_f32x2(fma_f32x2(fma_f32x2(c3, f, c2), f, c1), f, one);
+    float r0, r1, p0, p1;
+    unpack_f32x2(r, r0, r1);
+    unpack_f32x2(p, p0, p1);
+    e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(r0) << 23));
+    e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(r1) << 23));
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
+// The upper halves of two floats as a pair of bfloat16 (one byte permutation; a conversion instruction would
+// queue behind the exponentials on the special-function unit).  This truncates: the softmax below feeds it
+// probabilities scaled up by 1 + 2^-9, which centres the truncation error on zero like rounding to nearest.
+__device__ __forceinline__ uint32_t upper_halves(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
+constexpr float kTruncationLift = 0.0028150156f;  // log2(1 + 2^-9)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // tcgen05.mma with the 128 x 16 A operand in tensor memory (lane = row, two bfloat16 per 32-bit column)
@@ -198,9 +233,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         mbar_init(q_full, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full + 8 * b, 1);
-            mbar_init(p_full + 8 * b, 4);  // one arrival per softmax warp
+            mbar_init(p_full + 8 * b, kSoftmaxWarps);  // one arrival per softmax warp
             mbar_init(o_full + 8 * b, 1);
         }
+
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -281,6 +317,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int quarter = warp & 3;  // the quarter of the tensor-memory lanes this warp may read
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t my_output = tmem_output + lane_base;
         const int row_pos = row < valid ? pos0 + row : -1;  // a row beyond the sequence sees nothing
         const int row_first = (window > 0 && row_pos - window + 1 > 0) ? row_pos - window + 1 : 0;
         const float scale_log2 = args.scale * 1.4426950408889634f;
@@ -297,25 +334,27 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            uint32_t s[kKeys];
-            tmem_load_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base, &s[0]);
-            tmem_load_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base + 32, &s[32]);
+            uint32_t s[kCols];
+            const uint32_t my_scores = tmem_scores + (t & 1) * kScoreColumns + lane_base;
+#pragma unroll
+            for (int c = 0; c < kCols; c += 32) tmem_load_32_raw(my_scores + c, &s[c]);
             tmem_wait_loads();
             const int key_base = (t_begin + t) * kKeys;
-            if (!(key_base + kKeys - 1 <= row_pos && key_base >= row_first)) {  // not the whole page is visible to this row
+            if (!(key_base + kCols - 1 <= row_pos && key_base >= row_first)) {  // not the whole page is visible to this row
 #pragma unroll
-                for (int i = 0; i < kKeys; ++i) {
+                for (int i = 0; i < kCols; ++i) {
                     const int key = key_base + i;
                     if (!(key <= row_pos && key >= row_first)) s[i] = __float_as_uint(-CUDART_INF_F);
                 }
             }
-            float part[8];
+            float part[8];  // eight chains, two more scores a step
 #pragma unroll
-            for (int i = 0; i < 8; ++i) part[i] = __uint_as_float(s[i]);
+            for (int i = 0; i < 8; ++i) part[i] = fmaxf(__uint_as_float(s[i]), __uint_as_float(s[8 + i]));
 #pragma unroll
-            for (int i = 8; i < kKeys; ++i) part[i & 7] = fmaxf(part[i & 7], __uint_as_float(s[i]));
-            const float page_max = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])),
-                                         fmaxf(fmaxf(part[4], part[5]), fmaxf(part[6], part[7])));
+            for (int i = 16; i < kCols; i += 16)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) part[j] = max3(part[j], __uint_as_float(s[i + j]), __uint_as_float(s[i + 8 + j]));
+            const float page_max = max3(max3(part[0], part[1], part[2]), max3(part[3], part[4], part[5]), fmaxf(part[6], part[7]));
             // scores stay raw; the scale (times log2 e) is folded into the exponent: 2^(s*c - base*c)
             float factor = 1.0f;
             if (base == -CUDART_INF_F) {
@@ -324,49 +363,56 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 factor = fast_exp2((base - page_max) * scale_log2);
                 base = page_max;
             }
-            if (__any_sync(0xffffffffu, factor != 1.0f)) {
-                // the output so far moves to the new base; the product of the page before must have landed
-                ok = mbar_wait(o_full + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, 6);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tcgen05_fence_after();
-                run_sum *= factor;
-#pragma unroll
-                for (int c = 0; c < HD; c += 32) {
-                    uint32_t r[32];
-                    tmem_load_32_raw(tmem_output + lane_base + c, r);
-                    tmem_wait_loads();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-                    tmem_store_32_raw(tmem_output + lane_base + c, r);
-                }
-                tmem_wait_stores();
-            }
+            run_sum *= factor;
             // a row that has seen nothing yet keeps -inf; subtract 0 then so that the exponent is -inf, not NaN
-            const float offset = base == -CUDART_INF_F ? 0.0f : -base * scale_log2;
+            const float offset = base == -CUDART_INF_F ? 0.0f : fmaf(-base, scale_log2, kTruncationLift);
             const uint64_t offset2 = pack_f32x2(offset, offset);
             uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};  // eight partial sums, two per register pair
-            uint32_t packed[kPColumns];
+            uint32_t packed[kCols / 2];
 #pragma unroll
-            for (int c = 0; c < kKeys / 8; ++c) {
+            for (int c = 0; c < kCols / 8; ++c) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    float x0, x1;
-                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[c * 8 + 2 * i]), __uint_as_float(s[c * 8 + 2 * i + 1])),
-                                           scale2, offset2), x0, x1);
-                    const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+                    const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(s[c * 8 + 2 * i]), __uint_as_float(s[c * 8 + 2 * i + 1])), scale2, offset2);
+                    float e0, e1;
+                    if (i < kSoftPairs) {
+                        soft_exp2_x2(x2, e0, e1);
+                    } else {
+                        float x0, x1;
+                        unpack_f32x2(x2, x0, x1);
+                        e0 = fast_exp2(x0);
+                        e1 = fast_exp2(x1);
+                    }
                     sums[i] = add_f32x2(sums[i], pack_f32x2(e0, e1));
-                    packed[c * 4 + i] = pack_bf16(e0, e1);
+                    packed[c * 4 + i] = upper_halves(e0, e1);
                 }
             }
             // the row's probabilities go where its scores were: the next product takes them from tensor memory
-            tmem_store_32_raw(tmem_scores + (t & 1) * kScoreColumns + lane_base, packed);
-            tmem_wait_stores();
+            tmem_store_32_raw(my_scores, packed);
             {
                 float lo, hi;
                 unpack_f32x2(add_f32x2(add_f32x2(sums[0], sums[1]), add_f32x2(sums[2], sums[3])), lo, hi);
                 run_sum += lo + hi;
             }
+            if (__any_sync(0xffffffffu, factor != 1.0f)) {
+                // the output so far moves to the new base (the product of the page before must have landed) before the
+                // product of this page adds to it; the scores' registers are free by now
+                ok = mbar_wait(o_full + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, 6);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c = 0; c < HD; c += 32) {
+                    uint32_t r[32];
+                    tmem_load_32_raw(my_output + c, r);
+                    tmem_wait_loads();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+                    tmem_store_32_raw(my_output + c, r);
+                }
+                tmem_wait_stores();
+            }
+            tmem_wait_stores();
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * (t & 1));
@@ -377,12 +423,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         }
         if (ok) {
             tcgen05_fence_after();
-            const float inv = 1.0f / run_sum;
+            const float inv = exp2f(kTruncationLift) / run_sum;  // the sum holds the lifted probabilities, the products their truncations
             bf16* dst = args.out + (size_t)(q_begin + t0 + row) * args.out_row_stride + (size_t)head * HD;
 #pragma unroll
             for (int c = 0; c < HD; c += 32) {
                 uint32_t r[32];
-                tmem_load_32_raw(tmem_output + lane_base + c, r);
+                tmem_load_32_raw(my_output + c, r);
                 tmem_wait_loads();
                 if (row < valid) {
 #pragma unroll
