@@ -237,9 +237,15 @@ def device_decode(model, batch, steps, warmup, sample_clocks=False, prompt=PROMP
     per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
     launches = ops.launch_count() - launches_before
     clocks = sampler.stop() if sampler else None
+    # which form of each product the step ran: the launchers' names of the last capture this batch size replayed
+    kernels = {}
+    if graphs is not None and batch <= graphs.max_batch:
+        key = (graphs.rung(batch), graphs.launch_class(graphs.rung(batch), max(engine.length(s) for s in slots)))
+        for name in getattr(graphs.captured.get(key), "kernel_names", []):
+            kernels[name] = kernels.get(name, 0) + 1
     for s in slots:
         engine.release_slot(s)
-    return {"seconds": seconds, "tokens_per_second": batch * steps / seconds, "ms_per_step": 1e3 * seconds / steps,
+    return {"seconds": seconds, "kernels": kernels, "tokens_per_second": batch * steps / seconds, "ms_per_step": 1e3 * seconds / steps,
             "ms_per_step_p50": percentile(per_step, 0.50), "ms_per_step_p95": percentile(per_step, 0.95),
             "kv_tokens_per_step": kv_total / steps, "launches": launches, "clocks": clocks}
 
@@ -405,6 +411,7 @@ def main() -> int:
         "e2e": {"value": e2e["tokens_per_second"], "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": e2e["d2h_bytes_per_step"]},
         "gpu_launches": main_run["launches"],
+        "kernels": main_run["kernels"],
         "clocks": main_run["clocks"],
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peak["hbm_gbs"], "bytes_per_step": bytes_per_step},

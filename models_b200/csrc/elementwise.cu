@@ -367,7 +367,8 @@ static int launch_add_rmsnorm(float* x, const void* delta, const float* weight, 
     const bool aligned = width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)delta & 7) && !((uintptr_t)weight & 15) &&
                          !((uintptr_t)out & 7);
     if (aligned && out_rows >= kRowsPerWarpFrom && width <= 4096) {
-        const int warps = 8, grid = (out_rows + warps - 1) / warps;
+        const int warps = out_rows >= 2048 ? 8 : (out_rows >= 1024 ? 4 : 2);  // a few hundred rows: smaller blocks, so that every multiprocessor has some
+        const int grid = (out_rows + warps - 1) / warps;
 #define MB_ROWS_KERNEL(kVec)                                                                                              \
     return launch_dependent("add_rmsnorm", add_rmsnorm_rows_kernel<TD, TO, kVec>, dim3(grid), dim3(32 * warps), 0, stream, \
                             true, x, (const TD*)delta, weight, (TO*)out, rows, out_rows, width, eps, write_x)

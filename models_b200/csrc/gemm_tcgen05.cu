@@ -710,6 +710,9 @@ MB_EXPORT int mb_gemm_tcgen05_qkv_rope(const void* a, int lda, const void* w, in
     args.page_size = page_size; args.positions = positions; args.slot_mapping = slot_mapping; args.cos_table = cos_table;
     args.sin_table = sin_table; args.k_pool = (bf16*)k_pool; args.v_pool = (bf16*)v_pool;
     if (pairs_are_faster(m, n_w, k, multiprocessors)) return launch_tile<EPI_ROPE, 256, 2>(map_a, map_w, args, multiprocessors, stream);
+    // a prompt of a few hundred tokens has few tiles of 256 columns: tiles of 128 (a half of which still holds a whole
+    // head of 64) put twice the blocks to work, and what a block can load a second is what bounds it
+    if (head_dim == 64 && narrow_tiles_are_faster(m, n_w, k, multiprocessors, false)) return launch_tile<EPI_ROPE, 128, 1>(map_a, map_w, args, multiprocessors, stream);
     return launch_tile<EPI_ROPE, 256, 1>(map_a, map_w, args, multiprocessors, stream);
 }
 

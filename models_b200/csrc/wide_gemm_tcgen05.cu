@@ -73,7 +73,9 @@ struct WideArgs {
 template <int kBatchN, int kStageCount>
 struct WidePlan {
     static constexpr int kStageBytes = kTileBytes + kBatchN * kBlockK * 2;
-    static constexpr int kStages = kStageCount * kStageBytes <= 200 * 1024 ? kStageCount : 200 * 1024 / kStageBytes;
+    // (two blocks share a multiprocessor in the four-stage form: at 128 activation rows that leaves room for three stages each)
+    static constexpr int kWanted = kStageCount == 4 && 4 * kStageBytes > 110 * 1024 ? 3 : kStageCount;
+    static constexpr int kStages = kWanted * kStageBytes <= 200 * 1024 ? kWanted : 200 * 1024 / kStageBytes;
     static constexpr int kTmemColumns = kBatchN < 32 ? 32 : kBatchN;
     static constexpr int kPartialBytes = kBatchN * kTileRows * (int)sizeof(float);  // [batch column][128 rows], over the ring
 };

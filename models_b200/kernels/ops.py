@@ -59,10 +59,29 @@ def add_launches(n: int) -> None:
     _launches[0] += n
 
 
+_recorded = [None]  # a list while launches are being recorded (see `recording`), else None
+
+
+class recording:
+    """`with ops.recording() as names:` collects, in order, which launcher of this module ran each of this
+    package's kernels (the function's name says which form of a product it is).  For reports, not for hot loops."""
+
+    def __enter__(self):
+        self.before, _recorded[0] = _recorded[0], []
+        return _recorded[0]
+
+    def __exit__(self, *exc):
+        _recorded[0] = self.before
+        return False
+
+
 def _run(lib, status: int):
     if status != 0:
         raise KernelError(lib.mb_last_error().decode("utf-8", "replace"))
     _launches[0] += 1
+    if _recorded[0] is not None:
+        import sys
+        _recorded[0].append(sys._getframe(1).f_code.co_name)
 
 
 def _int32(t: Optional[torch.Tensor], name: str):
