@@ -32,6 +32,13 @@ __device__ __forceinline__ float gate_activation(int activation, float z) {
     return z / (1.0f + expf(-z));
 }
 
+// The cluster barrier a block passes before it leaves, so that its shared memory outlives the other blocks' reads
+// of it.  The arrival is relaxed: nothing this block wrote has to be visible to the others any more (they have read
+// what they needed), and a releasing arrival would wait here for the block's last global stores to be performed.
+__device__ __forceinline__ void cluster_leave_together() {
+    asm volatile("barrier.cluster.arrive.relaxed;\n\tbarrier.cluster.wait;" ::: "memory");
+}
+
 // One message per library and host thread; read by mb_last_error() after a non-zero return.
 inline char* error_buffer() {
     static thread_local char buffer[1024] = {0};

@@ -364,7 +364,7 @@ skinny_gemm_kernel(const SkinnyArgs args) {
         }
     }
     // a cluster's blocks leave together: the first block reads the others' shared memory until the end
-    if (args.k_split > 1) cg::this_cluster().sync();
+    if (args.k_split > 1) cluster_leave_together();
 }
 
 template <int NT, int PRO, int EPI>

@@ -357,7 +357,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
 
     // a cluster's blocks leave together: each has read the others' shared memory until now
-    if (splits > 1) cluster_sync_all();
+    if (splits > 1) cluster_leave_together();
     else __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
