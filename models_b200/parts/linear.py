@@ -2,13 +2,12 @@
 backend-java/.../ops/TensorOps.java:61-63), chosen by the weight's storage.
 
 bfloat16 weights: with up to 8 activation rows (decode) this package's own weight-streaming kernel
-(csrc/skinny_gemm.cu; it takes up to 32 rows but pays off up to 8); with more than 128 rows (prefill)
-its tcgen05 kernel csrc/gemm_tcgen05.cu; with 33 to 128 rows its tcgen05 kernel with the weights as the
-128-row operand (csrc/wide_gemm_tcgen05.cu) where the matrix has a row tile per multiprocessor (an
-output matrix over a large vocabulary).  What is left -- 9 to 128 rows against a smaller matrix, and
-widths that are no multiple of 8 -- falls to a library product (bfloat16 inputs, float accumulation), the
-place where the reference too calls a library (its matmul is VectorUtil.batchDotProduct of an external
-artifact).
+(csrc/skinny_gemm.cu; it takes up to 32 rows but pays off up to 8); with 9 to 128 rows its tcgen05 kernel
+with the weights as the 128-row operand and K split over a thread-block cluster
+(csrc/wide_gemm_tcgen05.cu); with more rows (prefill) its tcgen05 kernel csrc/gemm_tcgen05.cu.  What is
+left -- a matrix whose sizes are no multiples of 8, which TMA cannot address -- falls to a library product
+(bfloat16 inputs, float accumulation), the place where the reference too calls a library (its matmul is
+VectorUtil.batchDotProduct of an external artifact).
 float32 weights: this package's own true-32-bit kernel, in both modes -- a matrix stored in 32-bit is
 multiplied in 32-bit.
 """
