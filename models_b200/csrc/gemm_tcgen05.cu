@@ -193,7 +193,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     grid_launch_dependents();
-    grid_dependency_wait();  // the activations come from the kernel before this one
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -201,6 +200,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 1;  // the first pass over the ring finds every stage free
             bool ok = true;
+            auto announce = [&](int at) {  // both blocks' bytes of a pair are counted on the leader's barrier; the leader announces them
+                if (kPair == 2) {
+                    if (leader) mbar_expect_tx(full_bar + 8 * at, 2 * kStageBytes);
+                } else {
+                    mbar_expect_tx(full_bar + 8 * at, kStageBytes);
+                }
+            };
+            auto load_weights = [&](int at, int kb, int w_row0, int w_row1) {
+                const uint32_t dst = smem_u32(smem) + at * kStageBytes + kTileABytes;
+                if (kPair == 2) {
+                    tma_load_2d_pair(dst, &map_w, kb * kBlockK, leader ? w_row0 : w_row1, full_bar + 8 * at);
+                } else {
+                    tma_load_2d(dst, &map_w, kb * kBlockK, w_row0, full_bar + 8 * at);
+                    if (kBoxes == 2) tma_load_2d(dst + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * at);
+                }
+            };
+            auto load_activations = [&](int at, int kb, int m0) {
+                const uint32_t dst = smem_u32(smem) + at * kStageBytes;
+                if (kPair == 2) tma_load_2d_pair(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * at);
+                else tma_load_2d(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * at);
+            };
+            // The weights depend on nothing: the first tile's first stages of them are asked for before this kernel waits
+            // for the one before it; the activations, which that kernel wrote, after.
+            int early = 0;
+            if (first_tile < tiles) {
+                int m_tile, n_tile;
+                tile_coordinates(first_tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
+                const int kb_begin = (first_tile % k_splits) * k_blocks_per_split, kb_end = min(kb_begin + k_blocks_per_split, k_blocks_all);
+                const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
+                const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
+                early = min(kStages, kb_end - kb_begin);
+                for (int s = 0; s < early; ++s) {
+                    announce(s);
+                    load_weights(s, kb_begin + s, w_row0, w_row1);
+                }
+                grid_dependency_wait();
+                const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
+                for (int s = 0; s < early; ++s) load_activations(s, kb_begin + s, m0);
+                stage = early;
+                if (stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
             for (int tile = first_tile; tile < tiles && ok; tile += tile_step) {
                 int m_tile, n_tile;
                 tile_coordinates(tile / k_splits, m_tiles, n_tiles, kGroupRows / (kBlockM * kPair), &m_tile, &n_tile);
@@ -208,21 +251,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int m0 = m_tile * kBlockM * kPair + rank * kBlockM;
                 const int w_row0 = EPI == EPI_SWIGLU ? n_tile * 128 : n_tile * BN;
                 const int w_row1 = EPI == EPI_SWIGLU ? args.up_row_offset + n_tile * 128 : n_tile * BN + 128;
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                for (int kb = kb_begin + (tile == first_tile ? early : 0); kb < kb_end; ++kb) {
                     if (!(ok = mbar_wait(empty_bar + 8 * stage, phase, 1))) break;
-                    const uint32_t dst = smem_u32(smem) + stage * kStageBytes;
-                    if (kPair == 2) {
-                        // both blocks' bytes are counted on the leader's barrier; the leader announces them
-                        if (leader) mbar_expect_tx(full_bar + 8 * stage, 2 * kStageBytes);
-                        tma_load_2d_pair(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
-                        tma_load_2d_pair(dst + kTileABytes, &map_w, kb * kBlockK, leader ? w_row0 : w_row1, full_bar + 8 * stage);
-                    } else {
-                        mbar_expect_tx(full_bar + 8 * stage, kStageBytes);
-                        tma_load_2d(dst, &map_a, kb * kBlockK, m0, full_bar + 8 * stage);
-                        tma_load_2d(dst + kTileABytes, &map_w, kb * kBlockK, w_row0, full_bar + 8 * stage);
-                        if (kBoxes == 2)
-                            tma_load_2d(dst + kTileABytes + kBoxBBytes, &map_w, kb * kBlockK, w_row1, full_bar + 8 * stage);
-                    }
+                    announce(stage);
+                    load_activations(stage, kb, m0);
+                    load_weights(stage, kb, w_row0, w_row1);
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1;
@@ -272,6 +305,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ------------------------------------------------------------------ epilogue: 8 warps; a warp reads one quarter of
         // the tensor-memory lanes (its index modulo 4) and half of the tile's columns
+        grid_dependency_wait();  // what the epilogues read and add into comes from the kernels before this one
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const uint32_t staging = smem_u32(smem) + kRingBytes + (warp - 2) * kStagingBytes;
         constexpr int kHalfCols = kOutCols / 2;
