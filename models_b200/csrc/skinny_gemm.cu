@@ -47,7 +47,7 @@ namespace mb {
 
 using bf16 = __nv_bfloat16;
 
-enum { PRO_NONE = 0, PRO_NORM = 1 };
+enum { PRO_NONE = 0, PRO_NORM = 1, PRO_PRE = 2 };
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_ROPE = 4 };
 
 constexpr int kWarps = 4;
@@ -89,12 +89,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 struct SkinnyArgs {
     const bf16* w;
     int ldw, n, k, batch;
-    const bf16* x;        // PRO_NONE: [batch, k]
+    const bf16* x;        // PRO_NONE, PRO_PRE: [batch, k]
     int ldx;
     const float* xf;      // PRO_NORM: float rows
     int ldxf;
     const float* gain;    // PRO_NORM: [k]
     float eps;
+    // PRO_PRE: x holds the rows times the norm's gain, not yet divided by their root mean square; the rows' sums of
+    // squares come in parts ([ssq_count][128], a column per row) and the results are scaled by 1 / sqrt(sum / k + eps)
+    // (integrallis/models, backend-java/.../ops/TensorOps.java:45-58)
+    const float* ssq_parts;
+    int ssq_count;
+    // EPI_RESIDUAL, optional: beside the new x, write x times the NEXT norm's gain as bfloat16 and, per row tile, the
+    // tile's part of every row's sum of squares ([row tiles][128])
+    const float* emit_gain;   // [n]
+    bf16* emit_rows;          // [batch][ld_emit]
+    int ld_emit;
+    float* emit_ssq;
     const int* rows;      // optional: activation row b is xf row rows[b]
     bf16* out_bf16;
     float* out_f32;       // EPI_F32 output, or the residual stream for EPI_RESIDUAL
@@ -157,9 +168,26 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     const int steps = (k_end - k_begin + kStep - 1) / kStep;
     const int stages_total = tiles_mine * steps;
 
+    // where this lane reads its activations: row group_id (and 8, 16, ... further), its warp's columns of K, the lane's 8 of every 32
+    const int x_stride = Plan::x_stride(args.k_unit);
+    const uint32_t x_lane = smem_base + group_id * x_stride + ((k_begin - part_begin) + 8 * tid4) * 2;
+    // Activations that arrive as bfloat16 are not staged ahead of the products: every lane fetches exactly the pieces that
+    // it will read itself (no barrier, not even within the warp), those of a step of K together with the step's weights.
+    auto issue_activations = [&](int step) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int c = 0; c < kPieces; ++c) {
+                const int row = nt * 8 + group_id, col = k_begin + step * kStep + 32 * c + 8 * tid4;
+                const uint32_t dst = x_lane + nt * 8 * x_stride + (step * kStep + 32 * c) * 2;
+                if (row < args.batch && col < k_end) cp_async16(dst, args.x + (size_t)row * args.ldx + col);
+                else sts128_zero(dst);
+            }
+    };
     // ---- weights: this lane's pieces of each stage go to ring[stage][half][piece][lane]
     const uint32_t ring = smem_base + Plan::ring_offset(args.k_unit) + warp * kDepth * Plan::kStageBytes;
-    auto issue = [&](int stage_index) {
+    auto issue = [&](int stage_index, bool with_activations) {
+        if (PRO != PRO_NORM && with_activations && stage_index < steps) issue_activations(stage_index);  // (the first row tile's steps)
         const int tile = cluster_id + (stage_index / steps) * clusters, step = stage_index % steps;
         const uint32_t stage = ring + (stage_index % kDepth) * Plan::kStageBytes;
         const int kc = k_begin + step * kStep + 8 * tid4;
@@ -187,28 +215,40 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     };
     grid_launch_dependents();  // the next kernel's blocks may be scheduled as this one's leave
     for (int s = 0; s < kDepth - 1; ++s) {
-        if (s < stages_total) issue(s);
+        if (s < stages_total) issue(s, false);  // weights depend on nothing: they are asked for before the wait
         cp_async_commit();
     }
     grid_dependency_wait();  // from here on the results of the kernel before this one are visible
 
     // ---- activations of this block's part of K -> shared memory, bfloat16
-    const int x_stride = Plan::x_stride(args.k_unit);
     float* partial = reinterpret_cast<float*>(smem + Plan::partial_offset(args.k_unit));  // two buffers
     float* sq_total = partial + 2 * Plan::kPartialFloats;  // [COLS]
     float* sq_warp = sq_total + COLS;                      // [kWarps][COLS]
     const int chunks = (part_end - part_begin + 7) / 8;
     const int chunks_padded = args.k_unit / 8;  // the last steps may read past the part: zeros there
-    for (int b = 0; b < COLS; ++b) {
-        const int live_chunks = b < args.batch ? max(chunks, 0) : 0;
-        for (int c = live_chunks + threadIdx.x; c < chunks_padded; c += kThreads) sts128_zero(smem_base + b * x_stride + c * 16);
-    }
-    if (PRO == PRO_NONE) {
-        for (int b = 0; b < args.batch; ++b) {
-            const bf16* src = args.x + (size_t)b * args.ldx + part_begin;
-            for (int c = threadIdx.x; c < chunks; c += kThreads) cp_async16(smem_base + b * x_stride + c * 16, src + c * 8);
+    float parts_sum[COLS <= 16 ? COLS : 1];  // PRO_PRE: this thread's share of the parts of every row's sum of squares
+    if (PRO != PRO_NORM) {
+        // the activations of the steps whose weights are under way already; the rest follow step by step
+        for (int s = 0; s < kDepth - 1 && s < steps; ++s) issue_activations(s);
+        cp_async_commit();
+        if (PRO == PRO_PRE) {
+            // asked for now, added up when the first row tile is finished (in the order of the parts, then of the lanes and warps)
+#pragma unroll
+            for (int c = 0; c < (COLS <= 16 ? COLS : 1); ++c) parts_sum[c] = 0.0f;
+            for (int part = threadIdx.x; part < args.ssq_count; part += kThreads) {
+#pragma unroll
+                for (int c = 0; c < (COLS <= 16 ? COLS : 1); c += 4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(args.ssq_parts + (size_t)part * 128 + c));
+                    parts_sum[c] += v.x; parts_sum[c + 1] += v.y; parts_sum[c + 2] += v.z; parts_sum[c + 3] += v.w;
+                }
+            }
         }
+        cp_async_wait<0>();
     } else {
+        for (int b = 0; b < COLS; ++b) {
+            const int live_chunks = b < args.batch ? max(chunks, 0) : 0;
+            for (int c = live_chunks + threadIdx.x; c < chunks_padded; c += kThreads) sts128_zero(smem_base + b * x_stride + c * 16);
+        }
 #pragma unroll
         for (int b0 = 0; b0 < COLS; b0 += 8) {  // eight rows at a time: all their loads are issued before any is used
             if (b0 >= args.batch) break;
@@ -246,10 +286,10 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                 if (lane == 0) sq_warp[warp * COLS + b0 + j] = total;
             }
         }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
     }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
     if (PRO == PRO_NORM && threadIdx.x < COLS) {
         float s = 0.0f;
         if (threadIdx.x < (args.batch + 7) / 8 * 8)
@@ -259,7 +299,6 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     bool sq_gathered = args.k_split == 1;
 
     // ---- row tile after row tile; the ring keeps running across them
-    const uint32_t x_lane = smem_base + group_id * x_stride + ((k_begin - part_begin) + 8 * tid4) * 2;
     int stage_index = 0;
     for (int local = 0; local < tiles_mine; ++local) {
         const int tile = cluster_id + local * clusters;
@@ -267,7 +306,7 @@ skinny_gemm_kernel(const SkinnyArgs args) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
         for (int step = 0; step < steps; ++step, ++stage_index) {
-            if (stage_index + kDepth - 1 < stages_total) issue(stage_index + kDepth - 1);
+            if (stage_index + kDepth - 1 < stages_total) issue(stage_index + kDepth - 1, true);
             cp_async_commit();
             cp_async_wait<kDepth - 1>();  // this lane's pieces of the stage have landed; nobody else reads them
             const uint32_t stage = ring + (stage_index % kDepth) * Plan::kStageBytes;
@@ -294,6 +333,13 @@ skinny_gemm_kernel(const SkinnyArgs args) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
                 mine[(warp * 16 + group_id + 8 * (i >> 1)) * COLS + nt * 8 + tid4 * 2 + (i & 1)] = acc[nt][i];
+        if (PRO == PRO_PRE && local == 0) {
+#pragma unroll
+            for (int c = 0; c < (COLS <= 16 ? COLS : 1); ++c) {
+                const float total = warp_sum(parts_sum[c]);
+                if (lane == 0) sq_warp[warp * COLS + c] = total;
+            }
+        }
         if (args.k_split > 1) {
             cg::this_cluster().sync();
             if (rank != 0) continue;
@@ -313,7 +359,11 @@ skinny_gemm_kernel(const SkinnyArgs args) {
         for (int i = threadIdx.x; i < kTileRows * COLS; i += kThreads) {
             const int row_in_tile = i % kTileRows, col = i / kTileRows;  // neighbouring threads store neighbouring output columns
             const int row = tile * kTileRows + row_in_tile;
-            if (row >= rows_total || col >= args.batch) continue;
+            const bool emits = EPI == EPI_RESIDUAL && args.emit_gain != nullptr;
+            float squares = 0.0f;  // of the new x, where the next norm's rows are prepared
+            if (row >= rows_total || col >= args.batch) {
+                if (!emits) continue;  // (with them, whole warps stay for the sums below)
+            } else {
             float value = 0.0f, second = 0.0f;  // second: the up row that matches a gate row
             for (int r = 0; r < args.k_split; ++r) {
                 const float* from = args.k_split > 1 ? cg::this_cluster().map_shared_rank(mine, r) : mine;
@@ -327,10 +377,24 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                 value *= inv_rms;
                 second *= inv_rms;
             }
+            if (PRO == PRO_PRE) {
+                float sum = 0.0f;
+                for (int w = 0; w < kWarps; ++w) sum += sq_warp[w * COLS + col];
+                const float inv_rms = 1.0f / sqrtf(sum / (float)args.k + args.eps);
+                value *= inv_rms;
+                second *= inv_rms;
+            }
             const size_t at = (size_t)col * args.ld_out + row;
             if (EPI == EPI_BF16) args.out_bf16[at] = __float2bfloat16_rn(value);
             if (EPI == EPI_F32) args.out_f32[at] = value;
-            if (EPI == EPI_RESIDUAL) args.out_f32[at] += value;
+            if (EPI == EPI_RESIDUAL) {
+                const float x_new = args.out_f32[at] + value;
+                args.out_f32[at] = x_new;
+                if (emits) {
+                    args.emit_rows[(size_t)col * args.ld_emit + row] = __float2bfloat16_rn(x_new * args.emit_gain[row]);
+                    squares = x_new * x_new;
+                }
+            }
             if (EPI == EPI_SWIGLU) args.out_bf16[at] = __float2bfloat16_rn(gate_activation(args.activation, value) * second);
             if (EPI == EPI_ROPE) {
                 const int tiles_per_head = args.head_dim / 16, half = args.head_dim / 2;
@@ -360,6 +424,16 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                         dst[d0 + half] = __float2bfloat16_rn(x1);
                     }
                 }
+            }
+            }
+            if (emits) {
+                // the sixteen threads of a batch column (one per row of the tile) add their squares, a fixed tree; their
+                // first writes the tile's part
+                squares += __shfl_xor_sync(0xffffffffu, squares, 8);
+                squares += __shfl_xor_sync(0xffffffffu, squares, 4);
+                squares += __shfl_xor_sync(0xffffffffu, squares, 2);
+                squares += __shfl_xor_sync(0xffffffffu, squares, 1);
+                if ((lane & 15) == 0 && col < args.batch) args.emit_ssq[(size_t)tile * 128 + col] = squares;
             }
         }
     }
@@ -401,7 +475,7 @@ template <int PRO, int EPI>
 static int launch_nt(const SkinnyArgs& args, cudaStream_t stream) {
     if (args.batch <= 8) return launch<1, PRO, EPI>(args, stream);
     if (args.batch <= 16) return launch<2, PRO, EPI>(args, stream);
-    if (PRO == PRO_NORM) return fail("skinny_gemm: the norm prologue takes at most 16 rows, got %d", args.batch);
+    if (PRO != PRO_NONE) return fail("skinny_gemm: the norm prologues take at most 16 rows, got %d", args.batch);
     if (args.batch <= 32) return launch<4, PRO_NONE, EPI>(args, stream);
     return fail("skinny_gemm: takes at most 32 activation rows, got %d", args.batch);
 }
@@ -466,8 +540,13 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     const int resident_clusters = resident_for(split) / split;
     args.clusters = tiles < resident_clusters ? tiles : resident_clusters;
     if (args.clusters < 1) args.clusters = 1;
+    const int prologue = norm ? PRO_NORM : (args.ssq_parts ? PRO_PRE : PRO_NONE);
+    if (prologue == PRO_PRE && (batch > 16 || args.ssq_count <= 0 || ((uintptr_t)args.ssq_parts & 15)))
+        return fail("skinny_gemm: parts of sums of squares come with at most 16 rows, a count, and 16-byte alignment");
+    if (args.emit_gain && (epilogue != EPI_RESIDUAL || !args.emit_rows || !args.emit_ssq))
+        return fail("skinny_gemm: the next norm's rows are written by the residual epilogue, with buffers for them");
 #define MB_CASE(PRO, EPI) \
-    if ((norm ? PRO_NORM : PRO_NONE) == PRO && epilogue == EPI) return launch_nt<PRO, EPI>(args, stream);
+    if (prologue == PRO && epilogue == EPI) return launch_nt<PRO, EPI>(args, stream);
     MB_CASE(PRO_NONE, EPI_BF16)
     MB_CASE(PRO_NONE, EPI_F32)
     MB_CASE(PRO_NONE, EPI_RESIDUAL)
@@ -477,17 +556,31 @@ static int skinny_gemm(const void* w, int ldw, int n, int k, int batch, const vo
     MB_CASE(PRO_NONE, EPI_SWIGLU)
     MB_CASE(PRO_NORM, EPI_ROPE)
     MB_CASE(PRO_NONE, EPI_ROPE)
+    MB_CASE(PRO_PRE, EPI_BF16)
+    MB_CASE(PRO_PRE, EPI_F32)
+    MB_CASE(PRO_PRE, EPI_SWIGLU)
+    MB_CASE(PRO_PRE, EPI_ROPE)
 #undef MB_CASE
-    return fail("skinny_gemm: no kernel for prologue %d with epilogue %d", norm ? 1 : 0, epilogue);
+    return fail("skinny_gemm: no kernel for prologue %d with epilogue %d", prologue, epilogue);
 }
 
 // `dependent` != 0 launches the kernel as a programmatic dependent of the kernel before it in the stream.
+// ssq_parts (or null; then x is the rows times their norm's gain): [ssq_count][128] parts of the rows' sums of squares;
+// the results are scaled by 1 / sqrt(sum / k + eps).  emit_gain (or null; residual epilogue only): the next norm's gain;
+// the new rows times it go to emit_rows (bfloat16, row stride ld_emit), a part of their sums of squares per tile of 16
+// weight rows to emit_ssq ([(n + 15) / 16][128]), and *parts_written says how many parts there are.
 MB_EXPORT int mb_skinny_gemm(const void* w, int ldw, int n, int k, int batch, const void* x, int ldx, const float* xf,
                              int ldxf, const float* gain, float eps, const int* rows, void* out, int ld_out,
-                             int epilogue, int multiprocessors, int dependent, cudaStream_t stream) {
+                             int epilogue, int multiprocessors, int dependent, const float* ssq_parts, int ssq_count,
+                             const float* emit_gain, void* emit_rows, int ld_emit, float* emit_ssq, int* parts_written,
+                             cudaStream_t stream) {
     if ((epilogue & 0xff) == EPI_ROPE) return fail("skinny_gemm: the rotary epilogue has an entry point of its own");
+    SkinnyArgs args{};
+    args.ssq_parts = ssq_parts; args.ssq_count = ssq_count;
+    args.emit_gain = emit_gain; args.emit_rows = (bf16*)emit_rows; args.ld_emit = ld_emit; args.emit_ssq = emit_ssq;
+    if (parts_written) *parts_written = (n + 15) / 16;
     return skinny_gemm(w, ldw, n, k, batch, x, ldx, xf, ldxf, gain, eps, rows, out, ld_out, epilogue, multiprocessors, dependent,
-                       SkinnyArgs{}, stream);
+                       args, stream);
 }
 
 // The q/k/v product of an attention layer with rotation and cache write folded in.  w: [(heads + 2 *
@@ -497,7 +590,7 @@ MB_EXPORT int mb_skinny_qkv_rope(const void* w, int ldw, int k, int batch, const
                                  const float* gain, float eps, void* q_out, int ld_q, int heads, int kv_heads, int head_dim,
                                  const int* positions, const float* cos_table, const float* sin_table, void* k_pool,
                                  void* v_pool, const int* slot_mapping, int page_size, int multiprocessors, int dependent,
-                                 cudaStream_t stream) {
+                                 const float* ssq_parts, int ssq_count, cudaStream_t stream) {
     if (head_dim <= 0 || head_dim % 16) return fail("skinny_qkv_rope: head_dim %d must be a multiple of 16", head_dim);
     if (!positions || !cos_table || !sin_table || !k_pool || !v_pool || !slot_mapping || page_size <= 0)
         return fail("skinny_qkv_rope: needs positions, cos/sin tables, cache pools, a slot mapping and a page size");
@@ -505,6 +598,7 @@ MB_EXPORT int mb_skinny_qkv_rope(const void* w, int ldw, int k, int batch, const
     args.heads = heads; args.kv_heads = kv_heads; args.head_dim = head_dim; args.page_size = page_size;
     args.positions = positions; args.slot_mapping = slot_mapping; args.cos_table = cos_table; args.sin_table = sin_table;
     args.k_pool = (bf16*)k_pool; args.v_pool = (bf16*)v_pool;
+    args.ssq_parts = ssq_parts; args.ssq_count = ssq_count;
     return skinny_gemm(w, ldw, (heads + 2 * kv_heads) * head_dim, k, batch, x, ldx, xf, ldxf, gain, eps, nullptr, q_out, ld_q,
                        EPI_ROPE, multiprocessors, dependent, args, stream);
 }

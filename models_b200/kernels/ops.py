@@ -494,12 +494,14 @@ def multiprocessors(device) -> int:
 
 def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] = None, xf: Optional[torch.Tensor] = None,
                 gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, norm_parts=None, emit_gain: Optional[torch.Tensor] = None):
     """Few activation rows times weight^T ([n, k] bfloat16).  Activations: `x` (bfloat16 [rows, k]), or
     `xf` (the float32 residual rows, optionally gathered by `rows`) normalised on the fly with `gain`
     and `eps`.  Epilogues: EPI_BF16 / EPI_F32 store [rows, n]; EPI_RESIDUAL adds into `out` (float32
-    [rows, n]); EPI_SWIGLU takes weight = [gate rows; up rows] and stores silu(gate) * up [rows, n/2]."""
-    _cuda(weight, x, xf, gain, rows, out)
+    [rows, n]); EPI_SWIGLU takes weight = [gate rows; up rows] and stores act(gate) * up [rows, n/2].
+    `norm_parts` and `emit_gain` as for wide_gemm: `x` is then the rows times a norm's gain, divided by their
+    root mean square in the epilogue; a residual product can prepare the next norm's rows the same way."""
+    _cuda(weight, x, xf, gain, rows, out, emit_gain)
     n, k = weight.shape
     norm = gain is not None
     if norm:
@@ -523,26 +525,49 @@ def skinny_gemm(weight: torch.Tensor, epilogue: int, x: Optional[torch.Tensor] =
     elif out is None:
         out = torch.empty((batch, out_cols), dtype=torch.float32 if kind == EPI_F32 else torch.bfloat16,
                           device=weight.device)
+    if norm and norm_parts is not None:
+        raise KernelError("a product normalises float32 rows itself or takes rows with parts of their sums of squares, not both")
+    ssq, count, _, _, part_eps = _norm_args(norm_parts, batch, SSQ_COLUMNS)
+    if norm_parts is not None and norm_parts[2] != k:
+        raise KernelError("the norm's width is the product's k")
+    emit_rows = emit_ssq = None
+    written = ctypes.c_int(0)
+    if emit_gain is not None:
+        if kind != EPI_RESIDUAL or emit_gain.dtype != torch.float32 or emit_gain.numel() != n:
+            raise KernelError("the next norm's rows come from the residual epilogue, with a float32 gain of the output's width")
+        emit_rows = torch.empty((batch, n), dtype=torch.bfloat16, device=weight.device)
+        emit_ssq = torch.empty((-(-n // 16), SSQ_COLUMNS), dtype=torch.float32, device=weight.device)
     lib = skinny()
     _run(lib, lib.mb_skinny_gemm(_p(weight), weight.stride(0), n, k, batch, _p(x), x.stride(0) if x is not None else 0,
-                                 _p(xf), xf.stride(0) if xf is not None else 0, _p(gain), ctypes.c_float(eps), _p(rows),
-                                 _p(out), out.stride(0), epilogue, _sm_count(weight.device), 1, _stream()))
+                                 _p(xf), xf.stride(0) if xf is not None else 0, _p(gain),
+                                 part_eps if norm_parts is not None else ctypes.c_float(eps), _p(rows),
+                                 _p(out), out.stride(0), epilogue, _sm_count(weight.device), 1, ssq, count, _p(emit_gain),
+                                 _p(emit_rows), emit_rows.stride(0) if emit_rows is not None else 0, _p(emit_ssq),
+                                 ctypes.byref(written), _stream()))
+    if emit_gain is not None:
+        return out, emit_rows, emit_ssq, written.value
     return out
 
 
-def skinny_qkv_rope(weight: torch.Tensor, xf: torch.Tensor, gain: torch.Tensor, eps: float, heads: int, kv_heads: int,
-                    head_dim: int, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_pool: torch.Tensor,
-                    v_pool: torch.Tensor, slot_mapping: torch.Tensor) -> torch.Tensor:
+def skinny_qkv_rope(weight: torch.Tensor, xf: Optional[torch.Tensor], gain: Optional[torch.Tensor], eps: float, heads: int,
+                    kv_heads: int, head_dim: int, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                    k_pool: torch.Tensor, v_pool: torch.Tensor, slot_mapping: torch.Tensor, x: Optional[torch.Tensor] = None,
+                    norm_parts=None) -> torch.Tensor:
     """The q/k/v product of an attention layer on few rows with everything around it folded in: RMSNorm
     of the float32 residual rows `xf` before it, rotation of queries and keys (split-half pairs over
     the whole head) and the paged cache write of keys and values after it.  Returns the rotated
-    queries, bfloat16 [rows, heads * head_dim]."""
-    _cuda(weight, xf, gain, positions, cos, sin, k_pool, v_pool, slot_mapping)
-    batch, k = xf.shape
+    queries, bfloat16 [rows, heads * head_dim].  In place of `xf` and `gain`: `x`, the rows times the gain as
+    bfloat16, with `norm_parts` (as for wide_gemm); the division by the root mean square then happens in the epilogue."""
+    _cuda(weight, xf, x, gain, positions, cos, sin, k_pool, v_pool, slot_mapping)
+    if (xf is None) == (x is None) or (x is not None and norm_parts is None):
+        raise KernelError("skinny_qkv_rope takes float32 rows with a gain, or gained bfloat16 rows with parts of their sums of squares")
+    batch, k = (xf if xf is not None else x).shape
     if weight.shape != ((heads + 2 * kv_heads) * head_dim, k) or not skinny_takes(weight, batch, True):
         raise KernelError(f"skinny_qkv_rope does not take a {tuple(weight.shape)} {weight.dtype} weight with {batch} rows")
-    if xf.dtype != torch.float32 or xf.stride(1) != 1 or gain.dtype != torch.float32 or gain.numel() != k:
+    if xf is not None and (xf.dtype != torch.float32 or xf.stride(1) != 1 or gain.dtype != torch.float32 or gain.numel() != k):
         raise KernelError("skinny_qkv_rope needs float32 residual rows and gain")
+    if x is not None and (x.dtype != torch.bfloat16 or x.stride(1) != 1 or x.stride(0) % 8 or x.data_ptr() % 16 or norm_parts[2] != k):
+        raise KernelError("skinny_qkv_rope needs aligned bfloat16 rows of the weight's width")
     _int32(positions, "positions")
     _int32(slot_mapping, "slot_mapping")
     if cos.dtype != torch.float32 or cos.shape[-1] != head_dim // 2 or cos.shape != sin.shape or not cos.is_contiguous():
@@ -550,11 +575,13 @@ def skinny_qkv_rope(weight: torch.Tensor, xf: torch.Tensor, gain: torch.Tensor, 
     if k_pool.dtype != torch.bfloat16 or k_pool.shape != v_pool.shape or k_pool.shape[1] != kv_heads or k_pool.shape[3] != head_dim:
         raise KernelError("cache pools must be bfloat16 [pages, kv_heads, page_size, head_dim]")
     q = torch.empty((batch, heads * head_dim), dtype=torch.bfloat16, device=weight.device)
+    ssq, count, _, _, part_eps = _norm_args(norm_parts, batch, SSQ_COLUMNS)
     lib = skinny()
-    _run(lib, lib.mb_skinny_qkv_rope(_p(weight), weight.stride(0), k, batch, None, 0, _p(xf), xf.stride(0), _p(gain),
-                                     ctypes.c_float(eps), _p(q), q.stride(0), heads, kv_heads, head_dim, _p(positions),
-                                     _p(cos), _p(sin), _p(k_pool), _p(v_pool), _p(slot_mapping), k_pool.shape[2],
-                                     _sm_count(weight.device), 1, _stream()))
+    _run(lib, lib.mb_skinny_qkv_rope(_p(weight), weight.stride(0), k, batch, _p(x), x.stride(0) if x is not None else 0, _p(xf),
+                                     xf.stride(0) if xf is not None else 0, _p(gain),
+                                     part_eps if norm_parts is not None else ctypes.c_float(eps), _p(q), q.stride(0), heads,
+                                     kv_heads, head_dim, _p(positions), _p(cos), _p(sin), _p(k_pool), _p(v_pool),
+                                     _p(slot_mapping), k_pool.shape[2], _sm_count(weight.device), 1, ssq, count, _stream()))
     return q
 
 

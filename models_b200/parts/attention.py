@@ -126,27 +126,42 @@ class AttentionMixer(Mixer):
         ops.tensor_core_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x)
 
     def chains(self, rows: int, run: RunContext, next_norm) -> bool:
-        """Whether `forward_chain` applies: 9 to 128 rows on the wide decode products, rotation and cache write
-        folded into the q/k/v product, no biases, and a next norm whose gain a residual product can apply."""
+        """Whether `forward_chain` applies: up to 128 rows (the narrow decode products up to 8, the wide ones above),
+        rotation and cache write folded into the q/k/v product, no biases, and a next norm whose gain a residual
+        product can apply."""
         s, pos = self.spec, self.position
-        return (self.b_qkv is None and self.b_o is None and run.writes_cache and pos is not None
+        if not (self.b_qkv is None and self.b_o is None and run.writes_cache and pos is not None
                 and pos.rotary_dim == s.head_dim and not pos.interleaved and run.k_pool is not None
-                and run.k_pool.dtype == torch.bfloat16 and getattr(next_norm, "foldable", False)
-                and ops.wide_qkv_rope_takes(self.w_qkv, rows, s.num_heads, s.num_kv_heads, s.head_dim)
+                and run.k_pool.dtype == torch.bfloat16 and getattr(next_norm, "foldable", False)):
+            return False
+        if rows <= ops.SKINNY_PAYS_ROWS:
+            return s.head_dim % 16 == 0 and ops.skinny_pays(self.w_qkv, rows, with_norm=True) and ops.skinny_pays(self.w_o, rows)
+        return (ops.wide_qkv_rope_takes(self.w_qkv, rows, s.num_heads, s.num_kv_heads, s.head_dim)
                 and ops.gemm_tcgen05_takes(self.w_o, ops.EPI_RESIDUAL, rows))
 
-    def forward_chain(self, x: torch.Tensor, scaled, batch, run: RunContext, next_norm) -> Prenormed:
-        """x += Wo . attention(rotate(Wqkv . norm(x))) for 9 to 128 rows, in three kernels and with no kernel for
+    def forward_chain(self, x: torch.Tensor, scaled, batch, run: RunContext, next_norm, norm=None) -> Prenormed:
+        """x += Wo . attention(rotate(Wqkv . norm(x))) for up to 128 rows, in three kernels and with no kernel for
         either norm: `scaled` is the normalised rows, or a Prenormed whose division by the root mean square the
-        q/k/v product does itself; the output product adds into x and prepares the rows of `next_norm`."""
+        q/k/v product does itself, or None (few rows only): the product then normalises x with `norm` itself.  The
+        output product adds into x and prepares the rows of `next_norm`."""
         s, pos = self.spec, self.position
         group = batch.groups[run.group]
         rows, parts = (scaled.rows, scaled.norm_parts()) if isinstance(scaled, Prenormed) else (scaled, None)
-        q = ops.wide_qkv_rope(rows, self.w_qkv, s.num_heads, s.num_kv_heads, s.head_dim, batch.positions, pos.cos, pos.sin,
-                              run.k_pool, run.v_pool, group.slot_mapping, norm_parts=parts)
+        tables = (batch.positions, pos.cos, pos.sin, run.k_pool, run.v_pool, group.slot_mapping)
+        few = x.shape[0] <= ops.SKINNY_PAYS_ROWS
+        if few and rows is None:
+            q = ops.skinny_qkv_rope(self.w_qkv, x, norm.weight, norm.spec.eps, s.num_heads, s.num_kv_heads, s.head_dim, *tables)
+        elif few:
+            q = ops.skinny_qkv_rope(self.w_qkv, None, None, 0.0, s.num_heads, s.num_kv_heads, s.head_dim, *tables, x=rows,
+                                    norm_parts=parts)
+        else:
+            q = ops.wide_qkv_rope(rows, self.w_qkv, s.num_heads, s.num_kv_heads, s.head_dim, *tables, norm_parts=parts)
         attended = torch.empty((q.shape[0], self.q_width), dtype=q.dtype, device=q.device)
         self.attend(q, attended, batch, group, run)
-        _, gained, ssq, count = ops.wide_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
+        if few:
+            _, gained, ssq, count = ops.skinny_gemm(self.w_o, ops.EPI_RESIDUAL, x=attended, out=x, emit_gain=next_norm.weight)
+        else:
+            _, gained, ssq, count = ops.wide_gemm(attended, self.w_o, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
         return Prenormed(gained, ssq, count, x.shape[1], next_norm.spec.eps, next_norm)
 
     def forward(self, xn: torch.Tensor, batch, run: RunContext) -> torch.Tensor:

@@ -39,14 +39,19 @@ class PreNormBlock(Part):
         rows = x.shape[0]
         mixer_chains = getattr(self.mixer, "chains", None)
         ffn_chains = getattr(self.feed_forward, "chains", None)
-        if (self.runtime.mode == "bfloat16" and mixer_chains and ffn_chains and ffn_chains(rows)
+        # (a single row gains nothing from prepared rows: normalising one row inside a product costs less than the parts)
+        if (rows >= 2 and self.runtime.mode == "bfloat16" and mixer_chains and ffn_chains and ffn_chains(rows)
                 and mixer_chains(rows, run, self.feed_forward_norm) and getattr(self.mixer_norm, "foldable", False)):
-            # 9 to 128 rows (decode at wide batches): five kernels a layer, the norms riding in the products around them
+            # up to 128 rows (decode): five kernels a layer, the norms riding in the products around them
             if isinstance(pending, Prenormed) and pending.norm is self.mixer_norm:
                 scaled = pending
+            elif rows <= ops.SKINNY_PAYS_ROWS:
+                if as_delta(pending) is not None:
+                    ops.residual_add(x, as_delta(pending))
+                scaled = None  # few rows: the q/k/v product normalises x itself
             else:
                 scaled = self.mixer_norm.forward(x, as_delta(pending))
-            half_way = self.mixer.forward_chain(x, scaled, batch, run, self.feed_forward_norm)
+            half_way = self.mixer.forward_chain(x, scaled, batch, run, self.feed_forward_norm, norm=self.mixer_norm)
             return self.feed_forward.forward_chain(x, half_way, next_norm)
         pending = as_delta(pending)  # (a Prenormed means: nothing left to add)
         mixer_folds = getattr(self.mixer, "folds", None)

@@ -87,9 +87,13 @@ class GatedFeedForward(Part):
             ops.tensor_core_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
 
     def chains(self, rows: int) -> bool:
-        """Whether `forward_chain` applies: 9 to 128 rows on the wide decode products, no biases."""
-        return (self.b_gate_up is None and self.b_down is None and ops.SKINNY_PAYS_ROWS < rows <= ops.WIDE_ROWS
-                and ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows)
+        """Whether `forward_chain` applies: up to 128 rows (the narrow decode products up to 8, the wide ones above),
+        no biases."""
+        if self.b_gate_up is not None or self.b_down is not None or rows > ops.WIDE_ROWS:
+            return False
+        if rows <= ops.SKINNY_PAYS_ROWS:
+            return ops.skinny_pays(self.w_gate_up, rows, with_norm=True) and ops.skinny_pays(self.w_down, rows)
+        return (ops.gemm_tcgen05_takes(self.w_gate_up, ops.EPI_SWIGLU, rows)
                 and ops.gemm_tcgen05_takes(self.w_down, ops.EPI_RESIDUAL, rows))
 
     def forward_chain(self, x: torch.Tensor, scaled, next_norm):
@@ -98,11 +102,15 @@ class GatedFeedForward(Part):
         product adds into x and, given a `next_norm` whose gain it can apply, prepares that norm's rows (the
         return value; else None)."""
         rows, parts = (scaled.rows, scaled.norm_parts()) if isinstance(scaled, Prenormed) else (scaled, None)
-        hidden = ops.wide_gemm(rows, self.w_gate_up, self.gated, norm_parts=parts)
+        if x.shape[0] <= ops.SKINNY_PAYS_ROWS:
+            product = lambda a, w, epilogue, **more: ops.skinny_gemm(w, epilogue, x=a, **more)  # noqa: E731
+        else:
+            product = ops.wide_gemm
+        hidden = product(rows, self.w_gate_up, self.gated, norm_parts=parts)
         if next_norm is None or not getattr(next_norm, "foldable", False):
-            ops.wide_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
+            product(hidden, self.w_down, ops.EPI_RESIDUAL, out=x)
             return None
-        _, gained, ssq, count = ops.wide_gemm(hidden, self.w_down, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
+        _, gained, ssq, count = product(hidden, self.w_down, ops.EPI_RESIDUAL, out=x, emit_gain=next_norm.weight)
         return Prenormed(gained, ssq, count, x.shape[1], next_norm.spec.eps, next_norm)
 
     def forward(self, xn: torch.Tensor) -> torch.Tensor:

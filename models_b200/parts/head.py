@@ -51,9 +51,13 @@ class LinearHead(Part):
         rows = want_rows.numel()
         s = self.spec
         if (every_row and isinstance(pending, Prenormed) and pending.norm is norm and self.runtime.mode == "bfloat16"
-                and ops.SKINNY_PAYS_ROWS < rows <= ops.WIDE_ROWS and ops.gemm_tcgen05_takes(self.weight, ops.EPI_F32, rows)):
+                and (ops.skinny_pays(self.weight, rows, with_norm=True)
+                     or (ops.SKINNY_PAYS_ROWS < rows <= ops.WIDE_ROWS and ops.gemm_tcgen05_takes(self.weight, ops.EPI_F32, rows)))):
             # the last layer prepared the final norm's rows: the output product divides by the root mean square itself
-            logits = ops.wide_gemm(pending.rows, self.weight, ops.EPI_F32, norm_parts=pending.norm_parts())
+            if rows <= ops.SKINNY_PAYS_ROWS:
+                logits = ops.skinny_gemm(self.weight, ops.EPI_F32, x=pending.rows, norm_parts=pending.norm_parts())
+            else:
+                logits = ops.wide_gemm(pending.rows, self.weight, ops.EPI_F32, norm_parts=pending.norm_parts())
             if s.logit_scale != 1.0 or s.softcap != 0.0:
                 ops.logit_epilogue(logits, s.logit_scale, s.softcap)
             return logits

@@ -486,8 +486,11 @@ def test_skinny_gemm_all_prologues_and_epilogues(cuda_device, batch, n, k):
 
 @pytest.mark.parametrize("batch", [1, 5, 16])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,hidden", [(4, 2, 16, 64), (3, 1, 32, 96), (32, 8, 64, 2048), (6, 3, 48, 72)])
-def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads, kv_heads, head_dim, hidden):
-    """The folded decode kernel (norm, q/k/v product, rotation, cache write) against the plain parts."""
+@pytest.mark.parametrize("prepared", [False, True])
+def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads, kv_heads, head_dim, hidden, prepared):
+    """The folded decode kernel (norm, q/k/v product, rotation, cache write) against the plain parts.
+    `prepared`: the rows arrive as x times the gain in bfloat16 with parts of their sums of squares (as the
+    product before leaves them) instead of as float32 rows that the kernel normalises itself."""
     from models_b200.kernels import ops
 
     page = 64
@@ -506,8 +509,17 @@ def test_skinny_qkv_with_norm_rotation_and_cache_write(cuda_device, batch, heads
     if batch > 1:
         slots[1] = -1  # a padding row stores nothing
     kd, vd = k_pool.cuda(), v_pool.cuda()
-    q = ops.skinny_qkv_rope(w.cuda(), xf.cuda(), gain.cuda(), eps, heads, kv_heads, head_dim, positions.cuda(), cos.cuda(),
-                            sin.cuda(), kd, vd, slots.cuda())
+    if prepared:
+        squares = (xf.double() ** 2).sum(1)
+        share = torch.rand(5, batch, generator=g).double()
+        ssq = torch.zeros(7, ops.SSQ_COLUMNS)  # five parts that add up to the rows' sums of squares, two that do not count
+        ssq[:5, :batch] = (share / share.sum(0) * squares).float()
+        ssq[5:] = 1e6
+        q = ops.skinny_qkv_rope(w.cuda(), None, None, 0.0, heads, kv_heads, head_dim, positions.cuda(), cos.cuda(), sin.cuda(),
+                                kd, vd, slots.cuda(), x=(xf * gain).bfloat16().cuda(), norm_parts=(ssq.cuda(), 5, hidden, eps))
+    else:
+        q = ops.skinny_qkv_rope(w.cuda(), xf.cuda(), gain.cuda(), eps, heads, kv_heads, head_dim, positions.cuda(), cos.cuda(),
+                                sin.cuda(), kd, vd, slots.cuda())
     qkv = plain_llama.rms_norm(xf, gain, eps) @ w.float().t()
     c, s_ = cos[positions.long()], sin[positions.long()]
     want_q = plain_llama.rope_rotate_split_half(qkv[:, : heads * head_dim].reshape(batch, heads, head_dim), c, s_)
@@ -650,15 +662,20 @@ def test_wide_decode_gemm_all_epilogues(cuda_device, batch, n, k):
     assert ops.gemm_tcgen05_status() == 0
 
 
-@pytest.mark.parametrize("rows", [9, 33, 64, 100, 128])
+@pytest.mark.parametrize("rows", [1, 5, 8, 9, 33, 64, 100, 128])
 @pytest.mark.parametrize("width,inner", [(264, 520), (2048, 2048), (272, 4136)])
 def test_the_norm_rides_in_the_products_around_it(cuda_device, rows, width, inner):
     """x = x + h . Wd^T with the next RMSNorm half done in the same kernel (x * gain as bfloat16, and parts of
     every row's sum of squares), then a product that divides by the root mean square in its own epilogue:
     against float64 of the same steps (y = x / sqrt(mean(x^2) + eps) * gain, integrallis/models,
-    backend-java/.../ops/TensorOps.java:45-58).  These are the wide decode products (9 to 128 rows); over more
-    rows the norms keep kernels of their own, and the products say so."""
+    backend-java/.../ops/TensorOps.java:45-58).  These are the decode products (the narrow ones up to 8 rows, the
+    wide ones from 9 to 128); over more rows the norms keep kernels of their own, and the products say so."""
     from models_b200.kernels import ops
+
+    def product(a, w, epilogue, **more):
+        if rows <= ops.SKINNY_PAYS_ROWS:
+            return ops.skinny_gemm(w, epilogue, x=a, **more)
+        return ops.tensor_core_gemm(a, w, epilogue, **more)
 
     g = torch.Generator().manual_seed(rows + width + inner)
     eps = 3e-5
@@ -668,7 +685,7 @@ def test_the_norm_rides_in_the_products_around_it(cuda_device, rows, width, inne
     gain = (1.0 + 0.2 * torch.randn(width, generator=g)).float()
     x = (3.0 * torch.randn(rows, width, generator=g)).float()
     xd = x.cuda()
-    out, gained, ssq, count = ops.tensor_core_gemm(h.cuda(), w_down.cuda(), ops.EPI_RESIDUAL, out=xd, emit_gain=gain.cuda())
+    out, gained, ssq, count = product(h.cuda(), w_down.cuda(), ops.EPI_RESIDUAL, out=xd, emit_gain=gain.cuda())
     assert out is xd and gained.shape == (rows, width) and gained.dtype == torch.bfloat16
     exact_x = x.double() + h.double() @ w_down.double().t()
     scale = float(exact_x.abs().max())
@@ -682,14 +699,14 @@ def test_the_norm_rides_in_the_products_around_it(cuda_device, rows, width, inne
     inv_rms = 1.0 / torch.sqrt(want_squares / width + eps)
     normed = gained.double().cpu() * inv_rms[:, None]
     exact = normed @ w_next.double().t()
-    got = ops.tensor_core_gemm(gained, w_next.cuda(), ops.EPI_F32, norm_parts=parts)
+    got = product(gained, w_next.cuda(), ops.EPI_F32, norm_parts=parts)
     assert float((got.double().cpu() - exact).abs().max()) < 2e-5 * float(exact.abs().max()) * math.sqrt(width)
-    got = ops.tensor_core_gemm(gained, w_next.cuda(), ops.EPI_SWIGLU, norm_parts=parts)
+    got = product(gained, w_next.cuda(), ops.EPI_SWIGLU, norm_parts=parts)
     want = plain_llama.swiglu(exact[:, :72], exact[:, 72:])
     assert float((got.double().cpu() - want).abs().max()) < 1e-2 * float(want.abs().max())
     # the same bits in a second run (ordered sums everywhere)
     xd2 = x.cuda()
-    _, gained2, ssq2, count2 = ops.tensor_core_gemm(h.cuda(), w_down.cuda(), ops.EPI_RESIDUAL, out=xd2, emit_gain=gain.cuda())
+    _, gained2, ssq2, count2 = product(h.cuda(), w_down.cuda(), ops.EPI_RESIDUAL, out=xd2, emit_gain=gain.cuda())
     assert torch.equal(xd, xd2) and torch.equal(gained, gained2) and count == count2 and torch.equal(ssq[:count, :rows], ssq2[:count, :rows])
     assert ops.gemm_tcgen05_status() == 0
     with pytest.raises(ops.KernelError, match="128 rows"):
