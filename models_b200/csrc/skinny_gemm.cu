@@ -226,22 +226,19 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     float* sq_warp = sq_total + COLS;                      // [kWarps][COLS]
     const int chunks = (part_end - part_begin + 7) / 8;
     const int chunks_padded = args.k_unit / 8;  // the last steps may read past the part: zeros there
-    float parts_sum[COLS <= 16 ? COLS : 1];  // PRO_PRE: this thread's share of the parts of every row's sum of squares
+    constexpr int kHeld = COLS <= 16 ? COLS / 4 : 1;
+    float4 parts_held[kHeld];  // PRO_PRE: the thread's first part of every row's sum of squares, asked for early, used late
     if (PRO != PRO_NORM) {
         // the activations of the steps whose weights are under way already; the rest follow step by step
         for (int s = 0; s < kDepth - 1 && s < steps; ++s) issue_activations(s);
         cp_async_commit();
         if (PRO == PRO_PRE) {
-            // asked for now, added up when the first row tile is finished (in the order of the parts, then of the lanes and warps)
+            // asked for now, looked at only when the first row tile is finished: the products do not wait for them
 #pragma unroll
-            for (int c = 0; c < (COLS <= 16 ? COLS : 1); ++c) parts_sum[c] = 0.0f;
-            for (int part = threadIdx.x; part < args.ssq_count; part += kThreads) {
-#pragma unroll
-                for (int c = 0; c < (COLS <= 16 ? COLS : 1); c += 4) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4*>(args.ssq_parts + (size_t)part * 128 + c));
-                    parts_sum[c] += v.x; parts_sum[c + 1] += v.y; parts_sum[c + 2] += v.z; parts_sum[c + 3] += v.w;
-                }
-            }
+            for (int c = 0; c < kHeld; ++c)
+                parts_held[c] = (int)threadIdx.x < args.ssq_count
+                                    ? __ldcg(reinterpret_cast<const float4*>(args.ssq_parts + (size_t)threadIdx.x * 128 + 4 * c))
+                                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         }
         cp_async_wait<0>();
     } else {
@@ -298,6 +295,9 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     }
     bool sq_gathered = args.k_split == 1;
 
+    int my_position = 0;  // EPI_ROPE: the position of the batch column of this thread's first finishing item
+    if (EPI == EPI_ROPE && (int)threadIdx.x / kTileRows < args.batch) my_position = args.positions[threadIdx.x / kTileRows];
+
     // ---- row tile after row tile; the ring keeps running across them
     int stage_index = 0;
     for (int local = 0; local < tiles_mine; ++local) {
@@ -334,10 +334,34 @@ skinny_gemm_kernel(const SkinnyArgs args) {
             for (int i = 0; i < 4; ++i)
                 mine[(warp * 16 + group_id + 8 * (i >> 1)) * COLS + nt * 8 + tid4 * 2 + (i & 1)] = acc[nt][i];
         if (PRO == PRO_PRE && local == 0) {
+            // every row's sum of squares: the parts in their order within a thread, then a fixed tree over lanes and warps
 #pragma unroll
-            for (int c = 0; c < (COLS <= 16 ? COLS : 1); ++c) {
-                const float total = warp_sum(parts_sum[c]);
-                if (lane == 0) sq_warp[warp * COLS + c] = total;
+            for (int c = 0; c < kHeld; ++c) {
+                float4 sum = parts_held[c];
+                for (int part = threadIdx.x + kThreads; part < args.ssq_count; part += kThreads) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(args.ssq_parts + (size_t)part * 128 + 4 * c));
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                const float4 total = make_float4(warp_sum(sum.x), warp_sum(sum.y), warp_sum(sum.z), warp_sum(sum.w));
+                if (lane == 0) *reinterpret_cast<float4*>(&sq_warp[warp * COLS + 4 * c]) = total;
+            }
+        }
+        // What this thread's first item of the finishing below reads from memory is asked for before the block meets:
+        // the residual stream's old value, or the rotation's cosine and sine (the position was read before the loop).
+        float early_a = 0.0f, early_b = 0.0f;
+        {
+            const int row_in_tile = threadIdx.x % kTileRows, col = threadIdx.x / kTileRows;
+            const int row = tile * kTileRows + row_in_tile;
+            if (rank == 0 && row < rows_total && col < args.batch) {
+                if (EPI == EPI_RESIDUAL) early_a = args.out_f32[(size_t)col * args.ld_out + row];
+                if (EPI == EPI_ROPE) {
+                    const int tiles_per_head = args.head_dim / 16;
+                    if (tile / tiles_per_head < args.heads + args.kv_heads) {
+                        const size_t at_table = (size_t)my_position * (args.head_dim / 2) + (tile % tiles_per_head) * 8 + row_in_tile;
+                        early_a = args.cos_table[at_table];
+                        early_b = args.sin_table[at_table];
+                    }
+                }
             }
         }
         if (args.k_split > 1) {
@@ -388,7 +412,7 @@ skinny_gemm_kernel(const SkinnyArgs args) {
             if (EPI == EPI_BF16) args.out_bf16[at] = __float2bfloat16_rn(value);
             if (EPI == EPI_F32) args.out_f32[at] = value;
             if (EPI == EPI_RESIDUAL) {
-                const float x_new = args.out_f32[at] + value;
+                const float x_new = (i == (int)threadIdx.x ? early_a : args.out_f32[at]) + value;
                 args.out_f32[at] = x_new;
                 if (emits) {
                     args.emit_rows[(size_t)col * args.ld_emit + row] = __float2bfloat16_rn(x_new * args.emit_gain[row]);
@@ -402,8 +426,9 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                 // queries and keys pass through bfloat16 before the rotation, as they do when the product stores them
                 float x0 = __bfloat162float(__float2bfloat16_rn(value)), x1 = __bfloat162float(__float2bfloat16_rn(second));
                 if (head < args.heads + args.kv_heads) {
-                    const size_t at_table = (size_t)args.positions[col] * half + d0;
-                    const float c = args.cos_table[at_table], sn = args.sin_table[at_table];
+                    const bool early = i == (int)threadIdx.x;
+                    const size_t at_table = early ? 0 : (size_t)args.positions[col] * half + d0;
+                    const float c = early ? early_a : args.cos_table[at_table], sn = early ? early_b : args.sin_table[at_table];
                     const float r0 = x0 * c - x1 * sn, r1 = x0 * sn + x1 * c;
                     x0 = r0;
                     x1 = r1;
