@@ -403,6 +403,11 @@ static void plan(int tiles, int k, int multiprocessors, int* splits, int* per_sp
     const int k_blocks = (k + kBlockK - 1) / kBlockK;
     int s = 1;
     while (s < 8 && tiles * s * 2 <= multiprocessors + multiprocessors / 4 && k_blocks / (s * 2) >= 4) s *= 2;
+    // Blocks of a cluster run with the four-stage ring, two to a multiprocessor: while there is at most one for each,
+    // half of what could be in flight is not, so K is split once more where a block still keeps eight steps (the down
+    // products of the 3B and 8B layer shapes: +5 % and +2 % tokens a second at batch 16 and 64).  A matrix with a tile
+    // per multiprocessor is not split at all: its blocks run alone with the eight-stage ring.
+    if (s > 1 && s < 8 && tiles * s <= multiprocessors && k_blocks / (s * 2) >= 8) s *= 2;
     *per_split = (k_blocks + s - 1) / s;
     while (s > 1 && (s - 1) * *per_split >= k_blocks) {  // no part may be empty: fewer, as a power of two
         s /= 2;
