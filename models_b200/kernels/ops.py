@@ -346,9 +346,13 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
 
     Longer contexts: what counts is that enough blocks are in flight to keep memory busy, and a
     cluster's eight are too few for one or two sequences (one sequence of 32,768 positions, head size
-    64: 58 us with 8 splits, 26 us with 32).  The count is then the larger of what fills the
-    multiprocessors (256 blocks) and one block per 16 pages (64 pages for heads wider than 64, whose
-    pages are twice as large), at most 64, at most 2,048 blocks in all and at least 4 pages each; above
+    64: 58 us with 8 splits, 26 us with 32).  Up to four sequences the count is what makes one round of
+    blocks (at most 400: they then run with the deep page ring, and a second, partly filled round costs
+    more than it gives: 2 sequences of 32,768 positions take 29 us with 16 splits, 39 with 32; 4
+    sequences 57 us with 8, 65 with 16).  Larger batches have blocks enough anyway; there the count is
+    one block per 16 pages (64 pages for heads wider than 64, whose pages are twice as large) within
+    2,048 blocks in all (8 sequences of 65,536 positions: 175 us with 32 splits, 184 with 16; 16
+    sequences of 16,384: 94 us with 16, 100 with 8).  Always at most 64 and at least 4 pages each; above
     8 the partial results meet in scratch memory and a second kernel.  `keys` is rounded up to its class
     (decode_span), so the count is the same for every length of a class.  `multiprocessors`: those of
     the device the call runs on (None: the current device's)."""
@@ -382,7 +386,8 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
     visible = min(span, window) if window else span
     pages = -(-visible // page_size)
     by_length = pages // (16 if head_dim <= 64 else 64)
-    want = max(256 // base, by_length)
+    one_round = power_of_two_up_to(max(1, 400 // base))
+    want = one_round if one_round >= 8 else max(one_round, by_length)
     want = power_of_two_up_to(max(1, min(want, 64, 2048 // base, pages // 4)))
     return want if want > 8 else short
 
