@@ -183,6 +183,39 @@ def test_prompt_steps_replayed_from_captures_match_plain(cuda_device, folders, n
     assert captured == {(4, 32, 2), (1, 16, 2)}, captured  # the classes that came up more than twice
 
 
+def test_long_prompt_steps_replayed_from_captures_match_the_launched_ones(cuda_device, tmp_path):
+    """Prompt steps of several hundred tokens (the larger classes of captures, many pages per sequence, two
+    sequences of unequal length): the replayed step's logits against the same step launched kernel by kernel
+    on an engine without captures, in bfloat16 bit for bit (the kernels and their launch shapes are the same),
+    then a few decoded tokens on top."""
+    import models_b200
+    from models_b200.engine import StepEntry
+
+    from tiny import MID, make_folder
+
+    raw = MID["D"]  # heads of 64: the tcgen05 products and attention of a real prompt step
+    folder = make_folder(raw, seed=41, tmp_path=tmp_path, std=0.03)
+    vocab = raw["vocab_size"]
+    fast = models_b200.load_model(folder, dtype="bfloat16", max_batch=2, context=1024)
+    slow = models_b200.load_model(folder, dtype="bfloat16", max_batch=2, context=1024, cuda_graphs=False)
+    for round_ in range(4):  # the third and fourth rounds are replays
+        prompts = [random_tokens(vocab, 430 + 7 * round_, 900 + round_), random_tokens(vocab, 200 - 3 * round_, 950 + round_)]
+        outs = []
+        for model in (fast, slow):
+            engine = model.engine
+            slots = [engine.open_slot() for _ in prompts]
+            rows = [engine.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])]
+            for step in range(3):
+                rows.append(engine.decode(slots, [5 + step, 9 + step]).clone())
+            outs.append(torch.cat(rows))
+            for s in slots:
+                engine.release_slot(s)
+        assert torch.equal(outs[0], outs[1]), round_
+    assert any(tokens == 640 for _, tokens, _ in fast.engine.prompt_graphs.captured), fast.engine.prompt_graphs.captured
+    fast.close()
+    slow.close()
+
+
 def test_prompt_captures_leave_large_and_unwanted_steps_alone(cuda_device, folders):
     """Steps beyond the largest class, steps that want no logits and steps that want more rows than
     they have sequences run launch by launch."""
