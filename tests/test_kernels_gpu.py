@@ -663,7 +663,7 @@ def test_wide_decode_gemm_all_epilogues(cuda_device, batch, n, k):
 
 
 @pytest.mark.parametrize("rows", [1, 5, 8, 9, 33, 64, 100, 128])
-@pytest.mark.parametrize("width,inner", [(264, 520), (2048, 2048), (272, 4136)])
+@pytest.mark.parametrize("width,inner", [(264, 520), (2048, 2048), (272, 4136), (3088, 264), (1040, 8200)])
 def test_the_norm_rides_in_the_products_around_it(cuda_device, rows, width, inner):
     """x = x + h . Wd^T with the next RMSNorm half done in the same kernel (x * gain as bfloat16, and parts of
     every row's sum of squares), then a product that divides by the root mean square in its own epilogue:
