@@ -117,6 +117,8 @@ struct GemmArgs {
     int up_row_offset;    // EPI_SWIGLU: first up row of W
     int activation;       // EPI_SWIGLU: the gate's activation (MB_ACT_*)
     int k_splits;         // EPI_RESIDUAL: blocks that share an output tile, each with its own part of K (else 1)
+    int cluster_sum;      // k_splits > 1 on single blocks: the parts' blocks are one thread-block cluster and their sums meet
+                          // in distributed shared memory (no scratch, no tickets)
     float* partial;       // k_splits > 1: [tile][block of a pair][part of K][128 rows][tile columns] floats, or null
     int* tickets;         // k_splits > 1 with `partial`: [tile][block of a pair][8 epilogue warps][arrived, finished], zero before and after a launch
     void* out;            // bfloat16 [m, n], float [m, n], or the float residual stream; EPI_ROPE: the queries [m, heads * head_dim]
@@ -135,6 +137,19 @@ struct GemmArgs {
 // (tcgen05 cta_group::2): each loads its 128 rows of A and its half of the BN rows of W, the leader issues the products
 // for both, each block's tensor memory holds the accumulator of its own 128 rows, and each block runs the epilogue of
 // its rows.  A block then moves 32 KB per 64 columns of K instead of 48 KB for the same work.
+// Four floats at the same place of the shared memory of block `rank` of this cluster (distributed shared memory).
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+    return v;
+}
+// Where 16-byte piece `piece` of row `row` of a block's partial tile [128 rows][BN floats] lies: the pieces of a row are
+// permuted by the row's low bits, so that threads that hold a row each (and write the same piece of neighbouring rows at
+// once) do not meet in a bank.
+__device__ __forceinline__ uint32_t partial_piece(int row, int piece, int bn) { return (uint32_t)(row * bn * 4 + ((piece ^ (row & 7)) << 4)); }
+
 template <int EPI, int BN, int kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmArgs args) {
@@ -325,7 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int n0 = n_tile * kOutCols;
             // with K in parts and scratch given, the parts are summed in their order (see below)
             const int mn_tile = tile / k_splits;
-            const bool ordered = EPI == EPI_RESIDUAL && k_splits > 1 && args.partial != nullptr;
+            const bool ordered = EPI == EPI_RESIDUAL && k_splits > 1 && args.partial != nullptr && !args.cluster_sum;
             float* my_partial = ordered ? args.partial + ((size_t)(mn_tile * kPair + rank) * k_splits + tile % k_splits) * (kBlockM * kOutCols)
                                         : nullptr;
             if (EPI == EPI_ROPE) {
@@ -408,6 +423,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         float v[32];
                         tmem_load_32_issue(taddr + c, v);
                         tmem_load_wait();
+                        if (EPI == EPI_RESIDUAL && kPair == 1 && args.cluster_sum) {
+                            // this block's part of the sum goes to its own shared memory (the ring: every product has read
+                            // it); the cluster's blocks add the parts below
+                            const int tile_row = quarter * 32 + lane;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4*>(smem + partial_piece(tile_row, c / 4 + j, BN)) =
+                                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                            continue;
+                        }
 #pragma unroll
                         for (int i = 0; i < 32; ++i) packed[i] = __float_as_uint(v[i]);
                     } else {
@@ -558,6 +583,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     }
 
+    if (EPI == EPI_RESIDUAL && kPair == 1 && args.cluster_sum) {
+        // ---- the parts of K meet.  Every block of the cluster has its part of the tile in its shared memory; block r adds
+        // rows r, r + k_splits, ... over all parts, in the order of the parts (the same bits in every run), and adds the
+        // sums into the stream.  A block works on exactly one item here: the grid has a block per item.
+        cluster_sync_all();
+        if (warp >= 2) {
+            const int parts = args.k_splits, mine = (int)cluster_rank();
+            int m_tile, n_tile;
+            tile_coordinates((int)blockIdx.x / parts, m_tiles, n_tiles, kGroupRows / kBlockM, &m_tile, &n_tile);
+            constexpr int kPieces = BN / 4;  // 16-byte pieces of a row
+            const uint32_t base = smem_u32(smem);
+            for (int item = (threadIdx.x - 64); item < ((kBlockM - mine + parts - 1) / parts) * kPieces; item += kThreads - 64) {
+                const int tile_row = mine + (item / kPieces) * parts, piece = item % kPieces;  // neighbouring threads: neighbouring pieces of a row
+                const int out_row = m_tile * kBlockM + tile_row, col = n_tile * BN + piece * 4;
+                if (out_row >= args.m || col >= args.n) continue;
+                const uint32_t at = base + partial_piece(tile_row, piece, BN);
+                float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int part = 0; part < parts; ++part) {
+                    const float4 v = ld_cluster_f32x4(at, (uint32_t)part);
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                float* dst = reinterpret_cast<float*>(args.out) + (size_t)out_row * args.ld_out + col;
+                if (col + 4 <= args.n) {
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(sum.x), "f"(sum.y), "f"(sum.z), "f"(sum.w)
+                                 : "memory");
+                } else {
+                    const float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (col + i < args.n) dst[i] += v[i];  // the only addition into this element
+                }
+            }
+        }
+        cluster_leave_together();  // nobody leaves while its shared memory may still be read
+    }
     // every role has left its loop (done, or after a bounded wait gave up): free tensor memory
     tcgen05_fence_before();
     __syncthreads();
@@ -601,6 +661,39 @@ static int launch_tile(const CUtensorMap& map_a, const CUtensorMap& map_w, const
         args.k_splits = residual_k_splits(tiles, args.k, kPair == 2 ? multiprocessors / 2 : multiprocessors);
         tiles *= args.k_splits;
     }
+    if (kPair == 1 && EPI == EPI_RESIDUAL && args.k_splits > 1) {
+        // The parts' blocks of a tile form a cluster, each block with a multiprocessor to itself: clusters of more than
+        // four, and clusters of three that would need nearly every multiprocessor, do not find their places at once
+        // (measured: 256 rows of the down product 29 us with clusters of eight, 20 with four; 768 rows 47 us with
+        // clusters of three on 144 blocks, 33 with two).
+        const int whole_tiles = tiles / args.k_splits;
+        int parts = args.k_splits < 4 ? args.k_splits : 4;
+        if (parts == 3 && whole_tiles * 3 > multiprocessors * 85 / 100) parts = 2;
+        args.k_splits = parts;
+        tiles = whole_tiles * parts;
+    }
+    if (kPair == 1 && EPI == EPI_RESIDUAL && args.k_splits > 1 && tiles <= multiprocessors) {
+        // the blocks that share a tile's K are one cluster (K is split only while there is a multiprocessor for every
+        // item): their sums meet in distributed shared memory, in the order of the parts
+        args.cluster_sum = 1;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(tiles);
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = smem;
+        config.stream = stream;
+        cudaLaunchAttribute attribute[2];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = args.k_splits;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = dependent_launches_allowed() ? 2 : 1;
+        cudaError_t status = cudaLaunchKernelEx(&config, kernel, map_a, map_w, args);
+        if (status != cudaSuccess) return fail("gemm_tcgen05: launch of a cluster per tile failed: %s", cudaGetErrorString(status));
+        return check_launch("gemm_tcgen05");
+    }
     if (kPair == 1) {
         const int grid = tiles < multiprocessors ? tiles : multiprocessors;
         return launch_dependent("gemm_tcgen05", kernel, dim3(grid), dim3(kThreads), smem, stream, true, map_a, map_w, args);
@@ -636,7 +729,7 @@ static bool narrow_tiles_are_faster(int m, int n, int k, int multiprocessors, bo
     long cost[2];
     for (int narrow = 0; narrow < 2; ++narrow) {
         const long tiles = m_tiles * ((n + (narrow ? 127 : 255)) / (narrow ? 128 : 256));
-        const long splits = residual ? residual_k_splits(tiles, k, multiprocessors) : 1;
+        const long splits = residual ? std::min(4, residual_k_splits(tiles, k, multiprocessors)) : 1;  // (single blocks: clusters of four at most)
         const long rounds = (tiles * splits + multiprocessors - 1) / multiprocessors;
         const long steps = (k_blocks + splits - 1) / splits;
         cost[narrow] = rounds * (steps * (narrow ? 75 : 100) + 1500);
