@@ -235,24 +235,41 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
         namespace cg = cooperative_groups;
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
-        if (cluster.block_rank() == 0) {
-            for (int i = threadIdx.x; i < rows_here * HD; i += kThreads) {
-                const int row = i / HD, d = i % HD;
-                float m = -CUDART_INF_F;
-                for (int r = 0; r < splits; ++r) m = fmaxf(m, cluster.map_shared_rank(block_ml, r)[row * 2]);
-                float total = 0.0f, value = 0.0f;
-                for (int r = 0; r < splits; ++r) {
+        // every block of the cluster combines a share of the (head, coordinate) results: all reads of the other blocks'
+        // shared memory are asked for at once, then the parts are weighed in the order of the blocks
+        const int rank = (int)cluster.block_rank();
+        const int items = rows_here * HD, share = (items + splits - 1) / splits;
+        for (int i = rank * share + threadIdx.x; i < min(items, (rank + 1) * share); i += kThreads) {
+            const int row = i / HD, d = i % HD;
+            float part_m[8], part_l[8], part_o[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < splits) {
                     const float* ml = cluster.map_shared_rank(block_ml, r);
-                    const float weight = fast_exp2(ml[row * 2] - m);  // 0 for a block that saw nothing
-                    if (weight > 0.0f) {
-                        total += ml[row * 2 + 1] * weight;
-                        value += cluster.map_shared_rank(block_o, r)[row * HD + d] * weight;
-                    }
+                    part_m[r] = ml[row * 2];
+                    part_l[r] = ml[row * 2 + 1];
+                    part_o[r] = cluster.map_shared_rank(block_o, r)[row * HD + d];
+                } else {
+                    part_m[r] = -CUDART_INF_F;
+                    part_l[r] = 0.0f;
+                    part_o[r] = 0.0f;
                 }
-                out[(size_t)q_row * out_row_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(value * (1.0f / total));
             }
+            float m = part_m[0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) m = fmaxf(m, part_m[r]);
+            float total = 0.0f, value = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const float weight = fast_exp2(part_m[r] - m);  // 0 for a block that saw nothing
+                if (weight > 0.0f) {
+                    total += part_l[r] * weight;
+                    value += part_o[r] * weight;
+                }
+            }
+            out[(size_t)q_row * out_row_stride + (size_t)(head0 + row) * HD + d] = __float2bfloat16_rn(value * (1.0f / total));
         }
-        cluster.sync();  // the other blocks' shared memory has been read; they may leave
+        cluster_leave_together();  // the other blocks' shared memory has been read; they may leave
     }
 }
 
