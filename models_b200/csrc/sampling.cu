@@ -142,7 +142,7 @@ argmax_rows_kernel(const float* __restrict__ logits, int row_stride, int vocab, 
         for (int r = 1; r < kArgmaxBlocks; ++r) total = better(total, *cluster.map_shared_rank(&block_result, r));
         out[blockIdx.y] = total.index == 0x7fffffff ? 0 : total.index;
     }
-    cluster.sync();
+    cluster_leave_together();  // (the first block has read the others' results)
 }
 
 // The candidates (probability, id) in shared memory, unused entries (-1, max int): sorted by probability
