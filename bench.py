@@ -289,7 +289,7 @@ def e2e_decode(model, batch, steps, warmup, prompt=PROMPT_TOKENS):
             "d2h_bytes_per_step": 4 * batch, "tokens_hash": digest.hexdigest()[:16], "repeated": repeated}
 
 
-def device_prefill(model, tokens, repeats=3):
+def device_prefill(model, tokens, repeats=5):
     import torch
 
     from models_b200.engine import StepEntry
