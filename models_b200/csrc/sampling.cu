@@ -473,7 +473,24 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
 
     // adjusted logits, and their first maximum
     Best mine = {-CUDART_INF_F, 0x7fffffff};
-    for (int i = begin + tid; i < end; i += kThreads) {
+    int scalar_from = begin;
+    if (!penalised && !(begin & 3) && !((uintptr_t)row & 15)) {
+        // four logits a load where the block's part starts on a 16-byte boundary (every thread still walks ascending ids,
+        // so the first maximum stays the first)
+        const int whole = begin + ((end - begin) & ~3);
+        for (int i = begin + 4 * tid; i < whole; i += 4 * kThreads) {
+            const float4 q = *reinterpret_cast<const float4*>(row + i);
+            float v4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float v = temp > 0.0f ? v4[j] / temp : v4[j];
+                w[i + j] = v;
+                if (v > mine.value) mine = {v, i + j};
+            }
+        }
+        scalar_from = whole;
+    }
+    for (int i = scalar_from + tid; i < end; i += kThreads) {
         float v = row[i];
         if (penalised) {
             const int c = counts[(size_t)r * vocab + i];
@@ -587,6 +604,8 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
     // k-th largest probability by radix select over the float bit patterns (all are >= 0)
     uint32_t kth_bits = 0;
     int need_ties = 0, tie_count = 0;
+    int sort_span = 32;  // what sort_and_pick sorts for this k
+    while (sort_span < k) sort_span <<= 1;
     if (k < vocab) {
         uint32_t prefix = 0, mask = 0;
         int remaining = k;
@@ -646,6 +665,13 @@ sample_rows_cluster_kernel(const float* __restrict__ logits, int row_stride, int
             mask |= 255u << shift;
             remaining = shared_int[1];
             tie_count = shared_int[2];
+            // Everything above the chosen digit is in for certain (k - remaining ids), and the digit's own ids number
+            // tie_count.  If all of them together fit what the sort below takes anyway, the remaining passes are not
+            // needed: all ids from the digit's lower bound up become candidates and the sort cuts at k.
+            if (pass > 0 && k - remaining + tie_count <= sort_span) {
+                remaining = tie_count;  // (all of the digit's ids are gathered: see `all_ties` below)
+                break;
+            }
         }
         kth_bits = prefix;
         need_ties = remaining;
