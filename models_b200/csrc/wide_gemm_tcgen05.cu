@@ -237,6 +237,19 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
     }
 
+    // What a thread's first item of the finishing below reads from memory -- the residual stream's old values and the
+    // next norm's gain -- is asked for before the parts meet (the item depends only on the thread and the block).
+    float4 early_before = make_float4(0.0f, 0.0f, 0.0f, 0.0f), early_gain = early_before;
+    if (EPI == EPI_RESIDUAL) {
+        if (warp < 2) grid_dependency_wait();
+        const int quads = 128 / splits / 4, item = threadIdx.x;
+        const int row = tile * kTileRows + rank * (128 / splits) + (item & (quads - 1)) * 4, col = item / quads;
+        if (col < args.batch && row < args.rows_total) {
+            early_before = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(args.out) + (size_t)col * args.ld_out + row);
+            if (args.emit_gain) early_gain = *reinterpret_cast<const float4*>(args.emit_gain + row);
+        }
+    }
+
     // ---- the parts of K meet: every block of the cluster has its accumulator in its shared memory
     tcgen05_fence_before();
     if (splits > 1) cluster_sync_all();
@@ -288,11 +301,11 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     float squares = 0.0f;
                     if (live) {
                         float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + at);
-                        const float4 before = *dst;
+                        const float4 before = base == 0 ? early_before : *dst;
                         const float4 x = make_float4(before.x + value.x, before.y + value.y, before.z + value.z, before.w + value.w);
                         *dst = x;
                         if (args.emit_gain) {
-                            const float4 g = *reinterpret_cast<const float4*>(args.emit_gain + row);
+                            const float4 g = base == 0 ? early_gain : *reinterpret_cast<const float4*>(args.emit_gain + row);
                             *reinterpret_cast<uint2*>(args.emit_rows + (size_t)col * args.ld_emit + row) =
                                 make_uint2(pack_bf16(x.x * g.x, x.y * g.y), pack_bf16(x.z * g.z, x.w * g.w));
                             squares = x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
