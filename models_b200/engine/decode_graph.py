@@ -237,6 +237,7 @@ class DecodeGraphs:
 # host needs to launch them one by one.
 PROMPT_TOKENS = (16, 32, 64, 128, 256, 384, 512, 640, 768, 896, 1024, 1280, 1536, 1792, 2048)
 EAGER_USES = 2  # a class of steps is captured when it comes up for the third time: a capture costs tens of steps
+MAX_PROMPT_CAPTURES = 64  # classes beyond so many run launch by launch: every capture keeps its graph and its outputs
 
 
 class PromptGraphs:
@@ -274,7 +275,7 @@ class PromptGraphs:
         captured = self.captured.get(key)
         if captured is None:
             self.uses[key] = self.uses.get(key, 0) + 1
-            if self.uses[key] <= EAGER_USES:
+            if self.uses[key] <= EAGER_USES or len(self.captured) >= MAX_PROMPT_CAPTURES:
                 return None
             graphs = self.decode_graphs
             captured = self.captured[key] = _Captured(self.engine, key[0], key[2], graphs.pool, tokens=key[1])
