@@ -45,8 +45,12 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     // unless that page is the one that holds the newest position.
     if (!kCluster) grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char* q_smem = smem;                                 // 16 rows
-    unsigned char* stage_smem = smem + kQRowsDecode * kRowBytes;  // kDecodeStages x (K tile, V tile)
+    unsigned char* stage_smem = smem;  // kDecodeStages x (K tile, V tile)
+    // The 16 query rows pass through the last stage, which no page is fetched into before they are in registers: a
+    // block's shared memory is its stages alone, and a fourth block with three stages fits a multiprocessor (heads of 64).
+    // Every warp has a copy of them in the 16 key rows of that stage which only itself will ever write, so no warp waits
+    // for another before the walk over the pages begins.
+    unsigned char* q_smem = smem + (kDecodeStages - 1) * 2 * kTileBytes + (threadIdx.x >> 5) * 16 * kRowBytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, group_id = lane >> 2, tid4 = lane & 3;
     const int split = blockIdx.x, seq = blockIdx.z;
     const int kv_head = blockIdx.y / head_chunks, chunk = blockIdx.y % head_chunks;
@@ -99,10 +103,19 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
         }
         cp_async_commit();
     }
-    load_queries(q_smem, q + (size_t)q_row * q_row_stride + (size_t)head0 * HD, HD, kQRowsDecode, rows_here);
-    __syncthreads();
+    {
+        const bf16* q_first_row = q + (size_t)q_row * q_row_stride + (size_t)head0 * HD;  // (heads lie HD apart in a row of q)
+        for (int i = lane; i < kQRowsDecode * kChunks; i += 32) {
+            const int row = i / kChunks, chunk = i % kChunks;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (row < rows_here) v = *reinterpret_cast<const uint4*>(q_first_row + (size_t)row * HD + chunk * 8);
+            *reinterpret_cast<uint4*>(q_smem + row * kRowBytes + chunk * 16) = v;
+        }
+    }
+    __syncwarp();
     uint32_t a[kKSteps][4];
     load_q_fragments(a, smem_u32(q_smem));
+    __syncwarp();  // the warp has its queries in registers: its rows of the last stage are free for pages
 
     // the page table is read one page ahead of the fetch that needs it, so that no fetch waits for its entry
     int page_ahead = t_begin + kDecodeStages - 1 < t_end ? table[t_begin + kDecodeStages - 1] : 0;
@@ -451,8 +464,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __r
 }
 
 constexpr size_t decode_smem(int stages) {
-    const size_t tiles = (size_t)kQRowsDecode * kRowBytes + 2 * stages * (size_t)kTileBytes;
-    const size_t merge = (size_t)kQRowsDecode * kRowBytes + (4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
+    const size_t tiles = 2 * stages * (size_t)kTileBytes;  // (the queries lie in the last stage)
+    const size_t merge = (4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
 constexpr size_t prefill_smem() { return (size_t)kQRowsPrefill * kRowBytes + 4 * (size_t)kTileBytes; }
@@ -493,12 +506,21 @@ static int current_device(const char* what) {
     return device;
 }
 
-static int decode_stages(int splits, long blocks, int device) {
+static int multiprocessor_count(int device) {
     static int multiprocessors[kMaxDevices] = {0};  // of each device, asked once
     if (!multiprocessors[device] &&
         cudaDeviceGetAttribute(&multiprocessors[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
         multiprocessors[device] = 1;  // unknown: the deep ring only for a handful of blocks
-    if (splits > 8 && blocks <= 2L * multiprocessors[device]) return kLongStages;
+    return multiprocessors[device];
+}
+
+static int decode_stages(int splits, long blocks, int device) {
+    const int sms = multiprocessor_count(device);
+    if (splits > 8 && blocks <= 2L * sms) return kLongStages;
+    // Few splits mean long walks per block (64 sequences: ten pages each), and with two stages a block waits for every
+    // page: a third stage, as long as all blocks of the call still fit the multiprocessors at once with it.
+    const long resident_with_three = (long)((227 * 1024) / (decode_smem(3) + 1024)) * sms;
+    if (splits < 4 && blocks <= resident_with_three) return 3;
     return mb_decode_stages(splits);
 }
 MB_EXPORT size_t mb_decode_block_bytes(int stages) { return decode_smem(stages); }
@@ -526,11 +548,11 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
     if (!configured) {
         cudaError_t status = cudaFuncSetAttribute(decode_attention_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
         if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(decode_attention_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
+            status = cudaFuncSetAttribute(decode_attention_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (status == cudaSuccess)
             status = cudaFuncSetAttribute(decode_attention_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
         if (status == cudaSuccess)
-            status = cudaFuncSetAttribute(decode_attention_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
+            status = cudaFuncSetAttribute(decode_attention_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (status == cudaSuccess && kLongStages > 3)
             status = cudaFuncSetAttribute(decode_attention_kernel<false, kLongStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(kLongStages));
         if (status != cudaSuccess) return fail("decode_attention: cannot reserve %zu bytes of shared memory: %s", decode_smem(kLongStages), cudaGetErrorString(status));
@@ -544,6 +566,22 @@ MB_EXPORT int mb_decode_attention(const void* q, int q_row_stride, void* out, in
         config.gridDim = grid;
         config.blockDim = dim3(kThreads);
         config.dynamicSmemBytes = decode_smem(stages);
+        {
+            // The blocks of a cluster are placed on as few multiprocessors as will hold them, where they share what one
+            // multiprocessor can load.  Asking for as much shared memory as still lets all blocks of the call be resident
+            // at once spreads them (8 sequences, 256 blocks: 0.792 ms per decode step at four blocks to a multiprocessor,
+            // 0.762 at two; one sequence, 64 blocks: 0.722 and 0.703 with one; 16 sequences, 512 blocks, need all four).
+            const long blocks = (long)splits * kv_heads * head_chunks * sequences;
+            const int sms = multiprocessor_count(device);
+            long share = (blocks + sms - 1) / sms;  // blocks a multiprocessor has to hold
+            // (clusters of eight do not find eight multiprocessors of their own at once while the kernel before them still
+            // holds some: they are packed at least two to a multiprocessor, three when there are more blocks than
+            // multiprocessors -- 4 sequences: 0.746 ms per step with three, 0.777 with two)
+            if (splits > 4) share = blocks <= sms ? 2 : (share < 3 ? 3 : share);
+            const size_t room = (size_t)(227 * 1024) / (size_t)(share < 1 ? 1 : share) - 1024;
+            const size_t want = room < (size_t)200 * 1024 ? room : (size_t)200 * 1024;
+            if (want > config.dynamicSmemBytes) config.dynamicSmemBytes = want;
+        }
         config.stream = stream;
         cudaLaunchAttribute attribute[2];
         attribute[0].id = cudaLaunchAttributeClusterDimension;

@@ -380,6 +380,9 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
 
     with_three = fitting(3)
     short = with_three if _decode_block_bytes[head_dim]["wide"] or with_three >= 4 else min(2, fitting(2))
+    # (eight blocks to a sequence only for a handful of sequences: with more, a block is left with a page or two, and the
+    # cluster's meeting costs more than the shorter walk saves -- batch 8: 0.772 ms per step with four, 0.810 with eight)
+    short = min(short, max(4, 256 // max(1, base)))
     span = decode_span(keys)
     if span == 0:
         return short
