@@ -485,9 +485,9 @@ using namespace mb;
 
 MB_EXPORT int mb_attention_head_dim() { return HD; }
 
-// Shared memory of one decode block, for callers that plan how many blocks are resident at once.
-// Page stages a decode call with `splits` blocks per sequence runs with (see the note on page stages above), and the
-// shared memory of one block with so many stages: for callers that plan how many blocks are resident at once.
+// Page stages a decode call with `splits` blocks per sequence runs with at least (see the note on page stages above;
+// a call whose blocks all fit the multiprocessors with three stages gets three), and the shared memory of one block
+// with so many stages: for callers that plan how many blocks are resident at once.
 MB_EXPORT int mb_decode_stages(int splits) { return (HD >= 96 || splits >= 4) ? 3 : 2; }
 // More than a cluster's eight splits are for long contexts.  While the call's blocks are so few that at most two
 // share a multiprocessor, pages of 8 KB (heads up to 64) are fetched five ahead instead of two: one sequence of

@@ -339,8 +339,9 @@ def decode_splits(sequences: int, heads: int, kv_heads: int, head_dim: int = 64,
     (they form one thread-block cluster), with which all blocks of the call are resident at once -- a
     second, partly filled round of blocks costs more than longer blocks do (measured: 16 sequences of
     1,100 positions at head size 128 take 22 us with 2 splits, 29 with 4, 38 with 8).  The kernel runs
-    with three page stages when there are four or more splits (or heads of 96 and more) and with two
-    otherwise, and a block's shared memory follows from that; so does the count.  It depends on the
+    with three page stages when there are four or more splits (or heads of 96 and more, or blocks so
+    few that all of them fit the multiprocessors with three) and with two otherwise, and a block's shared
+    memory follows from that; so does the count.  It depends on the
     batch size rounded up to a power of two only, so a batch padded to such a size is split like the
     unpadded one.
 
