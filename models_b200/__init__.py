@@ -11,5 +11,5 @@ __version__ = "0.1.0"
 from .config import ConfigError, LlamaConfig, config_from_dict, load_config, register_architecture
 from .weights import WeightsError, load_tensors, write_random_model
 from .api import CallbackStream, ModelMetadata, TextGenerationModel, TokenStream, load_model
-from .engine.generation import GenerationResult, GenerationUsage
+from .engine.generation import GenerationResult, GenerationUsage, PromptCacheMetrics
 from .sampling import SamplingOptions

@@ -11,6 +11,12 @@ The reference serves one request at a time; batching is this library's own: requ
 start together in one prefill step and decode together, a finished request gives its slot back at
 once, and no request joins a batch that has started.  The loop only decides; it talks to the model
 through a small `Stepper`, so its decisions can be tested with a scripted one.
+
+Prompt-prefix reuse between requests (models-runtime/.../GenerationLoop.java:217-248), when asked
+for: a request that comes alone keeps its sequence in the cache when it ends; if the next request
+that comes alone begins with tokens that sequence holds, the sequence is cut back to the shared
+prefix (at most the prompt less one token, so that a step always runs) and only the rest of the
+prompt goes through the model.  Anything else that runs in between gives the kept sequence back first.
 """
 
 from __future__ import annotations
@@ -28,6 +34,29 @@ class GenerationUsage:
 
     prompt_tokens: int
     completion_tokens: int
+
+
+@dataclass(frozen=True)
+class PromptCacheMetrics:
+    """What the last request took from the sequence kept before it, in tokens
+    (models-runtime/.../PromptCacheMetrics.java:19-38): `supported` is whether reuse was possible for
+    that request at all; without it no activity is reported."""
+
+    supported: bool
+    input_tokens: int
+    cache_read_input_tokens: int  # found in the kept sequence
+    cache_write_input_tokens: int  # run through the model
+
+    def __post_init__(self):
+        read, written = self.cache_read_input_tokens, self.cache_write_input_tokens
+        if self.input_tokens < 0 or read < 0 or written < 0 or read + written > self.input_tokens:
+            raise ValueError("cache token counts must be non-negative and not exceed input_tokens")
+        if not self.supported and (read or written):
+            raise ValueError("an unsupported prompt cache cannot report cache activity")
+
+    @property
+    def hit_rate(self) -> float:
+        return self.cache_read_input_tokens / self.input_tokens if self.input_tokens else 0.0
 
 
 @dataclass
@@ -66,15 +95,57 @@ class _Live:
     slot: int = -1
     tokens: List[int] = field(default_factory=list)
     last: int = -1
+    start: int = 0  # tokens of the prompt that the slot already holds
+    keep: bool = False  # the sequence stays in the cache when the request ends
 
 
 class GenerationLoop:
-    def __init__(self, stepper: Stepper, max_batch: int, stop_token_ids: Iterable[int] = ()):
+    def __init__(self, stepper: Stepper, max_batch: int, stop_token_ids: Iterable[int] = (), reuse_prefix: bool = False):
         if max_batch <= 0:
             raise ValueError(f"max_batch must be positive, got {max_batch}")
         self.stepper = stepper
         self.max_batch = max_batch
         self.stop_token_ids = frozenset(int(t) for t in stop_token_ids)
+        # a sequence can only be cut back by a stepper that says how
+        self.reuse_prefix = bool(reuse_prefix) and hasattr(stepper, "rewind")
+        self._kept: Optional[tuple] = None  # (slot, the tokens it holds) of the last request that came alone
+        self.last_prompt_cache = PromptCacheMetrics(False, 0, 0, 0)
+
+    # ------------------------------------------------------------------ the kept sequence
+
+    def drop_kept(self) -> None:
+        """Gives the kept sequence's slot back (the next request starts from nothing)."""
+        if self._kept is not None:
+            slot = self._kept[0]
+            self._kept = None
+            self.stepper.release_slot(slot)
+
+    @staticmethod
+    def shared_prefix(held: Sequence[int], prompt: Sequence[int]) -> int:
+        """Tokens of `prompt` that a sequence holding `held` need not run again: the common prefix, but
+        at most the prompt less one token (models-runtime/.../GenerationLoop.java:240-248)."""
+        shared = 0
+        limit = min(len(held), len(prompt))
+        while shared < limit and held[shared] == prompt[shared]:
+            shared += 1
+        return min(shared, len(prompt) - 1)
+
+    def _resume(self, request: _Live) -> None:
+        """Lets a request that comes alone go on from the kept sequence where their tokens agree."""
+        request.keep = True
+        reused = 0
+        if self._kept is not None:
+            slot, held = self._kept
+            shared = self.shared_prefix(held, request.prompt)
+            if shared > 0:
+                try:
+                    self.stepper.rewind(slot, shared)
+                    self._kept = None
+                    request.slot, request.start, reused = slot, shared, shared
+                except Exception:  # a window that has let go of what the shorter sequence needs, a model with state
+                    pass
+            self.drop_kept()
+        self.last_prompt_cache = PromptCacheMetrics(True, len(request.prompt), reused, len(request.prompt) - reused)
 
     # ------------------------------------------------------------------ planning
 
@@ -125,13 +196,26 @@ class GenerationLoop:
             # the last emitted token is never fed back, so a sequence needs prompt + limit - 1 positions
             limits.append(min(o.max_tokens, self.stepper.max_positions - len(p) + 1))
         results: List[Optional[GenerationResult]] = [None] * len(prompts)
-        for batch in self.plan_batches(prompts, limits):
-            self._run_batch([_Live(i, prompts[i], RequestSampling(options[i], prompts[i]), limits[i]) for i in batch],
-                            results, on_token)
+        batches = self.plan_batches(prompts, limits)
+        alone = self.reuse_prefix and len(prompts) == 1
+        if not alone:
+            self.drop_kept()
+            self.last_prompt_cache = PromptCacheMetrics(False, sum(len(p) for p in prompts), 0, 0)
+        for batch in batches:
+            live = [_Live(i, prompts[i], RequestSampling(options[i], prompts[i]), limits[i]) for i in batch]
+            if alone:
+                self._resume(live[0])
+            self._run_batch(live, results, on_token)
         return results  # type: ignore[return-value]
 
     def _finish(self, request: _Live, reason: str, results) -> None:
-        self.stepper.release_slot(request.slot)
+        if request.keep:
+            # what went through the model: the prompt and every emitted token that another one followed; after a stop
+            # token all of them (the stop token was sampled from the last one's logits)
+            fed = request.tokens if reason == "stop" else request.tokens[:-1]
+            self._kept = (request.slot, request.prompt + fed)
+        else:
+            self.stepper.release_slot(request.slot)
         request.slot = -1
         results[request.index] = GenerationResult(
             request.tokens, GenerationUsage(len(request.prompt), len(request.tokens)), reason)
@@ -164,8 +248,9 @@ class GenerationLoop:
         rows: List[Optional[_Live]] = list(live)  # aligned with the rows of `pending`; None: finished
         try:
             for r in live:
-                r.slot = stepper.open_slot()
-            logits = stepper.prefill([r.slot for r in live], [r.prompt for r in live])
+                if r.slot < 0:
+                    r.slot = stepper.open_slot()
+            logits = stepper.prefill([r.slot for r in live], [r.prompt[r.start:] for r in live])
             pending = stepper.sample_start(logits, [r.sampling for r in live])
             samplings = [r.sampling for r in live]
             while any(r is not None for r in rows):
@@ -197,8 +282,9 @@ class GenerationLoop:
             return self._run_batch_pipelined(live, results, on_token)
         try:
             for r in live:
-                r.slot = stepper.open_slot()
-            logits = stepper.prefill([r.slot for r in live], [r.prompt for r in live])
+                if r.slot < 0:
+                    r.slot = stepper.open_slot()
+            logits = stepper.prefill([r.slot for r in live], [r.prompt[r.start:] for r in live])
             while live:
                 sampled = stepper.sample(logits, [r.sampling for r in live])
                 live = [r for r, token in zip(live, sampled) if self._take(r, int(token), results, on_token)]

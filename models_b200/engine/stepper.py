@@ -28,6 +28,10 @@ class EngineStepper:
     def release_slot(self, slot: int) -> None:
         self.engine.release_slot(slot)
 
+    def rewind(self, slot: int, length: int) -> None:
+        """Cuts the sequence back to its first `length` positions (raises where the cache cannot)."""
+        self.engine.rewind(slot, length)
+
     def check_options(self, options: SamplingOptions) -> None:
         self.sampler.check(options)
 

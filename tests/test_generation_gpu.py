@@ -555,3 +555,52 @@ def test_graph_capture_is_not_disturbed_by_garbage_collection(cuda_device, folde
     expected, _ = plain_greedy(folders["B"], [4, 5, 6], 6, model.engine.spec.stop_token_ids)
     assert got == expected
     model.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_next_request_goes_on_from_the_prefix_it_shares_with_the_last(cuda_device, folders, dtype):
+    """Prompt-prefix reuse between requests (models-runtime/.../GenerationLoop.java:217-248): a second turn that
+    repeats the first prompt and its reply runs only what is new; a prompt that parts from the kept sequence inside
+    its first page cuts the sequence back across a page; tokens are those of the plain implementation each time."""
+    import models_b200
+    from models_b200 import PromptCacheMetrics, SamplingOptions
+
+    raw = TINY["B"]
+    model = models_b200.load_model(folders["B"], dtype=dtype, max_batch=4, context=256, reuse_prefix=True)
+    stops = model.engine.spec.stop_token_ids
+    options = SamplingOptions(temperature=0.0, max_tokens=12)
+
+    def agrees(prompt, got):
+        expected, margins = plain_greedy(folders["B"], prompt, 12, stops)
+        if dtype == "float32":
+            assert got == expected
+        else:
+            for i, (g, e) in enumerate(zip(got, expected)):
+                if g != e:
+                    assert margins[i] < 0.05, (i, margins[i])
+                    break
+
+    first = random_tokens(raw["vocab_size"], 100, 5)
+    reply = model.generate(first, options)
+    agrees(first, reply)
+    assert model.last_prompt_cache == PromptCacheMetrics(True, 100, 0, 100)
+    held = model.engine.cache.slots.held
+    assert held == 1
+    second = first + reply + random_tokens(raw["vocab_size"], 9, 6)
+    agrees(second, model.generate(second, options))
+    # all of the first prompt and every reply token that went through the model (the last one did not, unless a stop
+    # token followed it)
+    reused = model.last_prompt_cache.cache_read_input_tokens
+    assert reused in (100 + len(reply) - 1, 100 + len(reply)) and model.last_prompt_cache.cache_write_input_tokens == len(second) - reused
+    third = first[:30] + random_tokens(raw["vocab_size"], 50, 7)
+    agrees(third, model.generate(third, options))
+    assert model.last_prompt_cache == PromptCacheMetrics(True, 80, 30, 50)
+    model.engine.cache.check()
+    # a batch in between gives the kept sequence back; so does closing the model
+    model.generate_batch([first[:20], first[:33]], options)
+    assert model.engine.cache.slots.held == 0 and model.last_prompt_cache.supported is False
+    agrees(third, model.generate(third, options))
+    assert model.engine.cache.slots.held == 1
+    model.close()
+    assert model.engine.cache.slots.held == 0
+    model.engine.cache.check()

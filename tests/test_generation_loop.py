@@ -204,3 +204,178 @@ def test_a_failing_step_ahead_gives_the_slots_back():
     with pytest.raises(RuntimeError, match="boom"):
         GenerationLoop(stepper, 4, [EOS]).run([[1], [2]], SamplingOptions(temperature=0.0))
     assert not stepper.held
+
+
+# ------------------------------------------------------------------ prompt-prefix reuse between requests
+# (the cases of models-runtime/src/test/.../GenerationLoopTest.java:563-617, and what batching adds to them)
+
+class RewindableStepper(ScriptedStepper):
+    """Keeps, per slot, the tokens it holds; every request 'generates' token 7."""
+
+    def __init__(self, **more):
+        super().__init__({}, **more)
+        self.tokens = {}
+        self.prefills, self.rewinds, self.releases = [], [], 0
+        self.refuse_rewind = False
+
+    def open_slot(self):
+        slot = super().open_slot()
+        self.tokens[slot] = []
+        return slot
+
+    def release_slot(self, slot):
+        super().release_slot(slot)
+        del self.tokens[slot]
+        self.releases += 1
+
+    def rewind(self, slot, length):
+        if self.refuse_rewind:
+            raise ValueError("this cache cannot be cut back")
+        assert 0 <= length <= len(self.tokens[slot])
+        self.rewinds.append(length)
+        del self.tokens[slot][length:]
+
+    def prefill(self, slots, prompts):
+        for s, p in zip(slots, prompts):
+            self.prefills.append((len(self.tokens[s]), list(p)))
+            self.tokens[s].extend(p)
+        return list(slots)
+
+    def decode(self, slots, tokens):
+        for s, t in zip(slots, tokens):
+            self.tokens[s].append(t)
+        return list(slots)
+
+    def sample(self, logits, requests):
+        return [7 for _ in logits]
+
+
+def test_the_longest_shared_prefix_is_kept_and_only_the_rest_runs():
+    from models_b200.engine.generation import PromptCacheMetrics
+
+    stepper = RewindableStepper()
+    loop = GenerationLoop(stepper, 4, [EOS], reuse_prefix=True)
+    one = SamplingOptions(temperature=0.0, max_tokens=1)
+    assert loop.run([[2, 3, 4]], one)[0].tokens == [7]
+    assert loop.last_prompt_cache == PromptCacheMetrics(True, 3, 0, 3)
+    assert loop.run([[2, 3, 4, 5]], one)[0].tokens == [7]
+    assert stepper.prefills == [(0, [2, 3, 4]), (3, [5])] and stepper.rewinds == [3]
+    assert loop.last_prompt_cache == PromptCacheMetrics(True, 4, 3, 1) and loop.last_prompt_cache.hit_rate == 0.75
+    assert len(stepper.held) == 1 and stepper.releases == 0  # the one sequence is still there, nothing was given back
+    loop.drop_kept()
+    assert not stepper.held
+
+
+def test_nothing_shared_starts_from_nothing_and_an_identical_prompt_runs_its_last_token_again():
+    from models_b200.engine.generation import PromptCacheMetrics
+
+    stepper = RewindableStepper()
+    loop = GenerationLoop(stepper, 4, [EOS], reuse_prefix=True)
+    one = SamplingOptions(temperature=0.0, max_tokens=1)
+    loop.run([[2, 3, 4]], one)
+    loop.run([[5]], one)
+    assert stepper.prefills == [(0, [2, 3, 4]), (0, [5])] and stepper.rewinds == [] and stepper.releases == 1
+    assert loop.last_prompt_cache == PromptCacheMetrics(True, 1, 0, 1)
+    loop.run([[5]], one)
+    assert stepper.prefills[-1] == (0, [5]) and stepper.releases == 2  # a prompt of one token has no prefix to keep
+    loop.run([[2, 3, 4]], one)
+    loop.run([[2, 3, 4]], one)
+    assert stepper.prefills[-1] == (2, [4]) and stepper.rewinds == [2]
+    assert loop.last_prompt_cache == PromptCacheMetrics(True, 3, 2, 1)
+    assert len(stepper.held) == 1
+
+
+def test_generated_tokens_that_went_through_the_model_count_as_held():
+    stepper = RewindableStepper()
+    loop = GenerationLoop(stepper, 4, [EOS], reuse_prefix=True)
+    result = loop.run([[2, 3]], SamplingOptions(temperature=0.0, max_tokens=3))[0]
+    assert result.tokens == [7, 7, 7] and result.finish_reason == "length"
+    slot = next(iter(stepper.tokens))
+    assert stepper.tokens[slot] == [2, 3, 7, 7]  # the last emitted token never ran
+    # the next turn of a conversation: the old prompt, the whole reply, and something new
+    loop.run([[2, 3, 7, 7, 7, 9]], SamplingOptions(temperature=0.0, max_tokens=1))
+    assert stepper.rewinds == [4] and stepper.prefills[-1] == (4, [7, 9])
+    assert loop.last_prompt_cache.cache_read_input_tokens == 4
+
+
+def test_batches_and_refused_rewinds_give_the_kept_sequence_back():
+    from models_b200.engine.generation import PromptCacheMetrics
+
+    stepper = RewindableStepper()
+    loop = GenerationLoop(stepper, 4, [EOS], reuse_prefix=True)
+    one = SamplingOptions(temperature=0.0, max_tokens=1)
+    loop.run([[2, 3, 4]], one)
+    loop.run([[2, 3, 4], [2, 3, 5]], one)  # two requests together: no reuse, and the kept slot goes back first
+    assert not stepper.held and stepper.rewinds == []
+    assert loop.last_prompt_cache == PromptCacheMetrics(False, 6, 0, 0)
+    loop.run([[2, 3, 4]], one)
+    stepper.refuse_rewind = True
+    loop.run([[2, 3, 4, 5]], one)
+    assert stepper.prefills[-1] == (0, [2, 3, 4, 5]) and len(stepper.held) == 1
+    assert loop.last_prompt_cache == PromptCacheMetrics(True, 4, 0, 4)
+    # a loop that was not asked to, or a stepper that cannot cut a sequence back, keeps nothing
+    plain = GenerationLoop(RewindableStepper(), 4, [EOS])
+    plain.run([[2, 3, 4]], one)
+    assert not plain.stepper.held and plain.last_prompt_cache.supported is False
+    assert GenerationLoop(ScriptedStepper({}), 4, [EOS], reuse_prefix=True).reuse_prefix is False
+    with pytest.raises(ValueError):
+        PromptCacheMetrics(False, 3, 1, 0)
+
+
+def test_a_failing_step_gives_a_resumed_sequence_back_too():
+    class Failing(RewindableStepper):
+        fail = False
+
+        def prefill(self, slots, prompts):
+            if self.fail:
+                raise RuntimeError("device lost")
+            return super().prefill(slots, prompts)
+
+    stepper = Failing()
+    loop = GenerationLoop(stepper, 4, [EOS], reuse_prefix=True)
+    one = SamplingOptions(temperature=0.0, max_tokens=1)
+    loop.run([[2, 3, 4]], one)
+    stepper.fail = True
+    with pytest.raises(RuntimeError):
+        loop.run([[2, 3, 4, 5]], one)
+    assert not stepper.held
+    stepper.fail = False
+    loop.run([[2, 3, 4, 5]], one)
+    assert stepper.prefills[-1] == (0, [2, 3, 4, 5])
+
+
+def test_the_loop_that_runs_a_step_ahead_keeps_a_prefix_of_what_the_cache_holds():
+    class AheadRewindable(RewindableStepper):
+        """Generates 7, 7, then a stop token; ids are read a step late."""
+
+        def script(self, slot):
+            return [7, 7, EOS, 1, 1][self.generated[slot]]
+
+        def open_slot(self):
+            slot = super().open_slot()
+            self.generated = getattr(self, "generated", {})
+            self.generated[slot] = 0
+            return slot
+
+        def prefill(self, slots, prompts):
+            for s in slots:
+                self.generated[s] = 0
+            return super().prefill(slots, prompts)
+
+        def sample_start(self, logits, requests):
+            return AheadStepper.Pending([self.script(s) if s in self.held else -1 for s in logits], self.calls)
+
+        def decode_pending(self, slots, pending, rows):
+            for s in slots:
+                self.generated[s] += 1
+            return self.decode(slots, [pending.values[i] for i in rows])
+
+    stepper = AheadRewindable()
+    loop = GenerationLoop(stepper, 4, [EOS], reuse_prefix=True)
+    result = loop.run([[2, 3]], SamplingOptions(temperature=0.0, max_tokens=8))[0]
+    assert result.tokens == [7, 7] and result.finish_reason == "stop"
+    slot = next(iter(stepper.tokens))
+    assert stepper.tokens[slot] == [2, 3, 7, 7, EOS]  # the step ahead carried the stop token through the model
+    loop.run([[2, 3, 7, 7, 9, 9]], SamplingOptions(temperature=0.0, max_tokens=1))
+    assert stepper.rewinds == [4] and stepper.prefills[-1] == (4, [9, 9])  # the stop token's position is cut off
+    assert stepper.tokens[slot][:6] == [2, 3, 7, 7, 9, 9]
