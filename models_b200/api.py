@@ -71,7 +71,7 @@ class _StreamAbandoned(Exception):
 
 class TextGenerationModel:
     def __init__(self, engine, max_batch: int, name: str, cuda_graphs: bool = True, context: Optional[int] = None,
-                 reuse_prefix: bool = False):
+                 reuse_prefix: bool = False, continuous: bool = False):
         from .engine.stepper import EngineStepper
 
         self.engine = engine
@@ -80,7 +80,8 @@ class TextGenerationModel:
         if cuda_graphs:
             engine.enable_decode_graphs(max_batch, context)
         self._stepper = EngineStepper(engine)
-        self._loop = GenerationLoop(self._stepper, max_batch, engine.spec.stop_token_ids, reuse_prefix=reuse_prefix)
+        self._loop = GenerationLoop(self._stepper, max_batch, engine.spec.stop_token_ids, reuse_prefix=reuse_prefix,
+                                    continuous=continuous)
         self._lock = threading.Lock()  # one generation at a time, as the reference serialises on its backend
         self._session: Optional[int] = None
         self._closed = False
@@ -239,13 +240,14 @@ class TextGenerationModel:
 
 def load_model(path=None, *, config=None, seed: Optional[int] = None, dtype: str = "bfloat16", max_batch: int = 8,
                context: Optional[int] = None, device="cuda:0", cuda_graphs: bool = True,
-               reuse_prefix: bool = False) -> TextGenerationModel:
+               reuse_prefix: bool = False, continuous: bool = False) -> TextGenerationModel:
     """A model ready to generate.  `path`: a folder with config.json and model.safetensors; or
     `config` (a typed configuration or a config.json dict) with `seed` for random weights.
     `context`: most positions per sequence (default: the model's, at most 4096); the cache is sized
     for `max_batch` sequences of that length.  `reuse_prefix`: a request that comes alone keeps its
     sequence in the cache when it ends, and the next such request runs only what follows their common
-    prefix (models-runtime/.../GenerationLoop.java:217-248)."""
+    prefix (models-runtime/.../GenerationLoop.java:217-248).  `continuous`: when there are more requests than
+    run together, one that waits joins the running ones as soon as another ends, instead of waiting for all of them."""
     from .config import config_from_dict, load_config
     from .engine.loading import engine_from_config, engine_from_folder
 
@@ -266,4 +268,4 @@ def load_model(path=None, *, config=None, seed: Optional[int] = None, dtype: str
     else:
         engine = engine_from_config(typed, seed, dtype, max_tokens, device=device, max_sequence=context)
         name = f"{typed.architecture}-random-{seed}"
-    return TextGenerationModel(engine, max_batch, name, cuda_graphs, context, reuse_prefix)
+    return TextGenerationModel(engine, max_batch, name, cuda_graphs, context, reuse_prefix, continuous)

@@ -17,6 +17,11 @@ for: a request that comes alone keeps its sequence in the cache when it ends; if
 that comes alone begins with tokens that sequence holds, the sequence is cut back to the shared
 prefix (at most the prompt less one token, so that a step always runs) and only the rest of the
 prompt goes through the model.  Anything else that runs in between gives the kept sequence back first.
+
+Continuous batching, when asked for: a request that waits takes the place of one that has ended
+while the others of the batch still run.  Its prompt runs as a step of its own between two of their
+decode steps, and from then on it decodes with them; requests are admitted in their order, none
+overtakes another, and never more than fit the cache at their longest.
 """
 
 from __future__ import annotations
@@ -97,10 +102,12 @@ class _Live:
     last: int = -1
     start: int = 0  # tokens of the prompt that the slot already holds
     keep: bool = False  # the sequence stays in the cache when the request ends
+    pages: int = 0  # cache pages the request needs at its longest
 
 
 class GenerationLoop:
-    def __init__(self, stepper: Stepper, max_batch: int, stop_token_ids: Iterable[int] = (), reuse_prefix: bool = False):
+    def __init__(self, stepper: Stepper, max_batch: int, stop_token_ids: Iterable[int] = (), reuse_prefix: bool = False,
+                 continuous: bool = False):
         if max_batch <= 0:
             raise ValueError(f"max_batch must be positive, got {max_batch}")
         self.stepper = stepper
@@ -108,6 +115,8 @@ class GenerationLoop:
         self.stop_token_ids = frozenset(int(t) for t in stop_token_ids)
         # a sequence can only be cut back by a stepper that says how
         self.reuse_prefix = bool(reuse_prefix) and hasattr(stepper, "rewind")
+        # rows of logits from two steps have to be put together, which only the stepper can do
+        self.continuous = bool(continuous) and hasattr(stepper, "concat")
         self._kept: Optional[tuple] = None  # (slot, the tokens it holds) of the last request that came alone
         self.last_prompt_cache = PromptCacheMetrics(False, 0, 0, 0)
 
@@ -201,12 +210,30 @@ class GenerationLoop:
         if not alone:
             self.drop_kept()
             self.last_prompt_cache = PromptCacheMetrics(False, sum(len(p) for p in prompts), 0, 0)
+        if self.continuous and len(batches) > 1:
+            waiting = [_Live(i, prompts[i], RequestSampling(options[i], prompts[i]), limits[i],
+                             pages=self._pages(len(prompts[i]) + limits[i] - 1)) for i in range(len(prompts))]
+            while waiting:  # (one pass: whoever waits is admitted as soon as the running ones leave room)
+                self._run_batch(self._admit(waiting, []), results, on_token, waiting)
+            return results  # type: ignore[return-value]
         for batch in batches:
             live = [_Live(i, prompts[i], RequestSampling(options[i], prompts[i]), limits[i]) for i in batch]
             if alone:
                 self._resume(live[0])
             self._run_batch(live, results, on_token)
         return results  # type: ignore[return-value]
+
+    def _admit(self, waiting: List[_Live], running: Sequence[_Live]) -> List[_Live]:
+        """Takes from the head of the queue the requests that fit beside the running ones: at most max_batch
+        together, and no more pages than the cache has when every one of them is at its longest.  In order: a
+        request that does not fit yet holds back those behind it."""
+        budget = self.stepper.capacity_tokens // self.stepper.page_size
+        used = sum(r.pages for r in running)
+        admitted: List[_Live] = []
+        while waiting and len(running) + len(admitted) < self.max_batch and used + waiting[0].pages <= budget:
+            used += waiting[0].pages
+            admitted.append(waiting.pop(0))
+        return admitted
 
     def _finish(self, request: _Live, reason: str, results) -> None:
         if request.keep:
@@ -237,15 +264,17 @@ class GenerationLoop:
         r.last = token
         return True
 
-    def _run_batch_pipelined(self, live: List[_Live], results, on_token) -> None:
+    def _run_batch_pipelined(self, live: List[_Live], results, on_token, waiting: Optional[List[_Live]] = None) -> None:
         """The same decisions, one step ahead of the ids: the next decode step is queued for every
         request that has room for another token before the last ids have reached the host, with
         the ids taken on the device.  A request whose pending token turns out to be a stop token
         has then been stepped once more than needed; that step's row is dropped, nothing of it is
         emitted, and the slot goes back as always.  The rows of such a step are sampled with the
-        others (their ids are never read).  Tokens, order and counts are those of the unpipelined loop."""
+        others (their ids are never read).  Tokens, order and counts are those of the unpipelined loop.
+        `waiting`: requests that join as others end (continuous batching)."""
         stepper = self.stepper
         rows: List[Optional[_Live]] = list(live)  # aligned with the rows of `pending`; None: finished
+        live = list(live)  # everyone who may hold a slot, for the failure path
         try:
             for r in live:
                 if r.slot < 0:
@@ -264,6 +293,16 @@ class GenerationLoop:
                         rows[i] = None
                 samplings = [samplings[i] for i in ahead]
                 rows = [rows[i] for i in ahead]
+                joiners = self._admit(waiting, [r for r in rows if r is not None]) if waiting else []
+                if joiners:
+                    # their prompts run as a step of its own, behind the step that is already queued for the others
+                    live.extend(joiners)
+                    for r in joiners:
+                        r.slot = stepper.open_slot()
+                    joined = stepper.prefill([r.slot for r in joiners], [r.prompt for r in joiners])
+                    next_logits = joined if next_logits is None else stepper.concat(next_logits, joined)
+                    rows.extend(joiners)
+                    samplings.extend(r.sampling for r in joiners)
                 if any(r is not None for r in rows):
                     pending = stepper.sample_start(next_logits, samplings)
         except BaseException:
@@ -276,10 +315,11 @@ class GenerationLoop:
                     r.slot = -1
             raise
 
-    def _run_batch(self, live: List[_Live], results, on_token) -> None:
+    def _run_batch(self, live: List[_Live], results, on_token, waiting: Optional[List[_Live]] = None) -> None:
         stepper = self.stepper
         if hasattr(stepper, "decode_pending") and hasattr(stepper, "sample_start"):
-            return self._run_batch_pipelined(live, results, on_token)
+            return self._run_batch_pipelined(live, results, on_token, waiting)
+        started = list(live)  # everyone who may hold a slot, for the failure path
         try:
             for r in live:
                 if r.slot < 0:
@@ -288,10 +328,18 @@ class GenerationLoop:
             while live:
                 sampled = stepper.sample(logits, [r.sampling for r in live])
                 live = [r for r, token in zip(live, sampled) if self._take(r, int(token), results, on_token)]
+                joiners = self._admit(waiting, live) if waiting else []
                 if live:
                     logits = stepper.decode([r.slot for r in live], [r.last for r in live])
+                if joiners:
+                    started.extend(joiners)
+                    for r in joiners:
+                        r.slot = stepper.open_slot()
+                    joined = stepper.prefill([r.slot for r in joiners], [r.prompt for r in joiners])
+                    logits = stepper.concat(logits, joined) if live else joined
+                    live = live + joiners
         except BaseException:
-            for r in live:
+            for r in started:
                 if r.slot >= 0:
                     try:
                         stepper.release_slot(r.slot)

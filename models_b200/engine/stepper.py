@@ -32,6 +32,10 @@ class EngineStepper:
         """Cuts the sequence back to its first `length` positions (raises where the cache cannot)."""
         self.engine.rewind(slot, length)
 
+    def concat(self, first: torch.Tensor, second: torch.Tensor) -> torch.Tensor:
+        """The rows of two steps' logits as one tensor (a copy: a replayed step's logits are its graph's own buffer)."""
+        return torch.cat([first, second], dim=0)
+
     def check_options(self, options: SamplingOptions) -> None:
         self.sampler.check(options)
 

@@ -604,3 +604,38 @@ def test_the_next_request_goes_on_from_the_prefix_it_shares_with_the_last(cuda_d
     model.close()
     assert model.engine.cache.slots.held == 0
     model.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_waiting_requests_join_the_running_ones(cuda_device, folders, dtype):
+    """Continuous batching through the entry point: five requests of unequal prompts and lengths, two at a time; a
+    request that waits starts as soon as another ends (its prompt as a step of its own between two decode steps of
+    the others, slots used again at once).  Every request's tokens are those of the plain implementation."""
+    import models_b200
+    from models_b200 import SamplingOptions
+
+    raw = TINY["B"]
+    model = models_b200.load_model(folders["B"], dtype=dtype, max_batch=2, context=256, continuous=True)
+    stops = model.engine.spec.stop_token_ids
+    prompts = [random_tokens(raw["vocab_size"], n, 50 + n) for n in (70, 5, 130, 33, 64)]
+    lengths = [4, 19, 9, 3, 12]
+    options = [SamplingOptions(temperature=0.0, max_tokens=n) for n in lengths]
+    prefills = []
+    real = model._stepper.prefill
+    model._stepper.prefill = lambda slots, ps: (prefills.append([len(p) for p in ps]), real(slots, ps))[1]
+    results = model.generate_batch(prompts, options)
+    assert prefills[0] == [70, 5] and sorted(n for step in prefills[1:] for n in step) == [33, 64, 130]
+    assert len(prefills) >= 3  # the others came in as places became free, not as one second batch
+    for prompt, limit, result in zip(prompts, lengths, results):
+        expected, margins = plain_greedy(folders["B"], prompt, limit, stops)
+        if dtype == "float32":
+            assert result.tokens == expected
+        else:
+            for i, (g, e) in enumerate(zip(result.tokens, expected)):
+                if g != e:
+                    assert margins[i] < 0.05, (i, margins[i])
+                    break
+        assert result.usage.prompt_tokens == len(prompt)
+    model.engine.cache.check()
+    assert model.engine.cache.slots.held == 0
+    model.close()

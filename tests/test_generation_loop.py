@@ -379,3 +379,69 @@ def test_the_loop_that_runs_a_step_ahead_keeps_a_prefix_of_what_the_cache_holds(
     loop.run([[2, 3, 7, 7, 9, 9]], SamplingOptions(temperature=0.0, max_tokens=1))
     assert stepper.rewinds == [4] and stepper.prefills[-1] == (4, [9, 9])  # the stop token's position is cut off
     assert stepper.tokens[slot][:6] == [2, 3, 7, 7, 9, 9]
+
+
+# ------------------------------------------------------------------ continuous batching
+
+class JoiningStepper(ScriptedStepper):
+    def concat(self, first, second):
+        return list(first) + list(second)
+
+    def prefill(self, slots, prompts):
+        self.most_held = max(getattr(self, "most_held", 0), len(self.held))
+        return super().prefill(slots, prompts)
+
+
+class JoiningAheadStepper(AheadStepper, JoiningStepper):
+    pass
+
+
+@pytest.mark.parametrize("kind", [JoiningStepper, JoiningAheadStepper])
+def test_a_waiting_request_joins_as_soon_as_another_ends(kind):
+    scripts = {1: [10, EOS], 2: [20, 21, 22, 23, 24, 25, EOS], 3: [30, 31, EOS], 4: [40, EOS], 5: [50, 51, 52, EOS]}
+    prompts = [[1, 0], [2], [3, 0, 0], [4], [5]]
+    options = SamplingOptions(temperature=0.0, max_tokens=10)
+    one_after_another = GenerationLoop(kind(scripts), 2, [EOS]).run(prompts, options)
+    stepper = kind(scripts)
+    emitted = []
+    results = GenerationLoop(stepper, 2, [EOS], continuous=True).run(prompts, options, on_token=lambda i, t: emitted.append((i, t)))
+    assert [(r.tokens, r.finish_reason, r.usage) for r in results] == [(r.tokens, r.finish_reason, r.usage) for r in one_after_another]
+    assert [r.tokens for r in results] == [[10], [20, 21, 22, 23, 24, 25], [30, 31], [40], [50, 51, 52]]
+    assert [t for i, t in emitted if i == 1] == [20, 21, 22, 23, 24, 25]
+    prefills = [c[2] for c in stepper.calls if c[0] == "prefill"]
+    # the first two start together; each of the others comes alone, in order, while request 1 is still running
+    assert prefills == [[[1, 0], [2]], [[3, 0, 0]], [[4]], [[5]]]
+    assert stepper.most_held <= 2 and not stepper.held and sorted(stepper.free) == list(range(64))
+    kinds = [c[0] for c in stepper.calls if c[0] != "result"]
+    assert kinds.index("prefill", 1) < len(kinds) - 1 and "decode" in kinds[kinds.index("prefill", 1):]  # decoding goes on after a join
+    # without the option (or with a stepper that cannot put two steps' logits together) batches follow one another
+    plain = kind(scripts)
+    GenerationLoop(plain, 2, [EOS]).run(prompts, options)
+    assert [c[2] for c in plain.calls if c[0] == "prefill"] == [[[1, 0], [2]], [[3, 0, 0], [4]], [[5]]]
+    assert GenerationLoop(ScriptedStepper(scripts), 2, [EOS], continuous=True).continuous is False
+
+
+def test_joiners_wait_for_pages_and_none_overtakes_another():
+    # three pages in all; request 2 needs two of them, request 3 one: 3 could run beside 1, but waits behind 2
+    scripts = {1: [10, 11, 12, EOS], 2: [20, EOS], 3: [30, EOS]}
+    stepper = JoiningStepper(scripts, capacity_tokens=3 * 64)
+    prompts = [[1] * 70, [2] * 100, [3]]
+    results = GenerationLoop(stepper, 4, [EOS], continuous=True).run(prompts, SamplingOptions(temperature=0.0, max_tokens=8))
+    assert [r.tokens for r in results] == [[10, 11, 12], [20], [30]]
+    prefills = [[p[0] for p in c[2]] for c in stepper.calls if c[0] == "prefill"]
+    assert prefills == [[1], [2, 3]]  # request 1 alone (2 pages of 3); when it ends, 2 and 3 start together
+    assert not stepper.held
+
+
+@pytest.mark.parametrize("kind", [JoiningStepper, JoiningAheadStepper])
+def test_a_failing_join_gives_every_slot_back(kind):
+    class Failing(kind):
+        def prefill(self, slots, prompts):
+            if any(p[0] == 3 for p in prompts):
+                raise RuntimeError("boom")
+            return super().prefill(slots, prompts)
+
+    stepper = Failing({1: [10, EOS], 2: [20, 21, 22, 23, EOS], 3: [30, EOS]})
+    with pytest.raises(RuntimeError, match="boom"):
+        GenerationLoop(stepper, 2, [EOS], continuous=True).run([[1], [2], [3]], SamplingOptions(temperature=0.0, max_tokens=8))
+    assert not stepper.held and sorted(stepper.free) == list(range(64))
