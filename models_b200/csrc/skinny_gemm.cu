@@ -214,8 +214,11 @@ skinny_gemm_kernel(const SkinnyArgs args) {
         }
     };
     grid_launch_dependents();  // the next kernel's blocks may be scheduled as this one's leave
-    for (int s = 0; s < kDepth - 1; ++s) {
-        if (s < stages_total) issue(s, false);  // weights depend on nothing: they are asked for before the wait
+    // Weights depend on nothing: every stage of the ring is asked for before the wait.  (All of them, not all but one:
+    // a warp of the q/k/v or output product has four steps in all, and its last step's weights would otherwise be
+    // asked for after the wait and arrive from memory on the critical path.)
+    for (int s = 0; s < kDepth; ++s) {
+        if (s < stages_total) issue(s, false);
         cp_async_commit();
     }
     grid_dependency_wait();  // from here on the results of the kernel before this one are visible
@@ -230,7 +233,7 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     float4 parts_held[kHeld];  // PRO_PRE: the thread's first part of every row's sum of squares, asked for early, used late
     if (PRO != PRO_NORM) {
         // the activations of the steps whose weights are under way already; the rest follow step by step
-        for (int s = 0; s < kDepth - 1 && s < steps; ++s) issue_activations(s);
+        for (int s = 0; s < kDepth && s < steps; ++s) issue_activations(s);
         cp_async_commit();
         if (PRO == PRO_PRE) {
             // asked for now, looked at only when the first row tile is finished: the products do not wait for them
@@ -306,8 +309,6 @@ skinny_gemm_kernel(const SkinnyArgs args) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
         for (int step = 0; step < steps; ++step, ++stage_index) {
-            if (stage_index + kDepth - 1 < stages_total) issue(stage_index + kDepth - 1, true);
-            cp_async_commit();
             cp_async_wait<kDepth - 1>();  // this lane's pieces of the stage have landed; nobody else reads them
             const uint32_t stage = ring + (stage_index % kDepth) * Plan::kStageBytes;
             uint4 wv[2][kPieces];
@@ -324,6 +325,9 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                     mma_bf16(acc[nt], wv[0][c].z, wv[1][c].z, wv[0][c].w, wv[1][c].w, xv.z, xv.w);
                 }
             }
+            // the stage has been read (by this lane, in program order): its slot takes the stage a ring's length further on
+            if (stage_index + kDepth < stages_total) issue(stage_index + kDepth, true);
+            cp_async_commit();
         }
 
         // the warps' partial sums of this row tile: c0,c1 = (MMA row groupID, activation rows 2*tid4, +1); c2,c3 = row +8
