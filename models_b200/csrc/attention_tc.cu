@@ -41,8 +41,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     grid_launch_dependents();
     // The query, and the keys and values of the newest position, come from the kernel before this one.
     // Lengths and page tables were written before the step began, and every older position of the
-    // cache in an earlier step: a block may fetch its first page before it waits for that kernel,
-    // unless that page is the one that holds the newest position.
+    // cache in an earlier step: a block may fetch its first pages before it waits for that kernel,
+    // up to the one that holds the newest position.
     if (!kCluster) grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* stage_smem = smem;  // kDecodeStages x (K tile, V tile)
@@ -86,16 +86,18 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     if (!empty) {
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t stage_base = smem_u32(stage_smem);
-    const bool early = kCluster && t_begin != pos / kTile;  // the first page holds no position of this step
-    if (kCluster && !early) grid_dependency_wait();
-    load_tile_rows(stage_base, k_pool, table[t_begin], kv_head, kv_heads, warp, lane);
-    load_tile_rows(stage_base + kTileBytes, v_pool, table[t_begin], kv_head, kv_heads, warp, lane);
-    cp_async_commit();
-    if (early) grid_dependency_wait();
     // kDecodeStages - 1 pages are in flight while one is worked on; every stage is one commit group, empty
-    // groups past the last page keep the count the waits rely on
+    // groups past the last page keep the count the waits rely on.  Of these first pages, those that hold no
+    // position of this step (all but the sequence's last page) are asked for before the wait for the kernel
+    // before this one, the others after it.
+    const int newest = pos / kTile;
+    bool waited = !kCluster;  // (without a cluster the block has waited above)
 #pragma unroll
-    for (int ahead = 1; ahead < kDecodeStages - 1; ++ahead) {
+    for (int ahead = 0; ahead < kDecodeStages - 1; ++ahead) {
+        if (!waited && (t_begin + ahead >= t_end || t_begin + ahead == newest)) {
+            grid_dependency_wait();
+            waited = true;
+        }
         if (t_begin + ahead < t_end) {
             const uint32_t dst = stage_base + ahead * 2 * kTileBytes;
             load_tile_rows(dst, k_pool, table[t_begin + ahead], kv_head, kv_heads, warp, lane);
@@ -103,6 +105,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
         }
         cp_async_commit();
     }
+    if (!waited) grid_dependency_wait();
     {
         const bf16* q_first_row = q + (size_t)q_row * q_row_stride + (size_t)head0 * HD;  // (heads lie HD apart in a row of q)
         for (int i = lane; i < kQRowsDecode * kChunks; i += 32) {
