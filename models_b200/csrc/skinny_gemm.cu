@@ -221,6 +221,29 @@ skinny_gemm_kernel(const SkinnyArgs args) {
         if (s < stages_total) issue(s, false);
         cp_async_commit();
     }
+    // What depends on no kernel of this step is asked for before the wait as well: the step's indices (written before the
+    // step began) and weights -- the position, cache slot, cosine and sine of this thread's first finishing item, the next
+    // norm's gain for it, and this norm's gain on its way into L2.
+    int my_position = 0, my_slot = -1;   // EPI_ROPE: of the batch column of this thread's first finishing item
+    float first_a = 0.0f, first_b = 0.0f;  // EPI_ROPE: its cosine and sine in the first row tile; EPI_RESIDUAL: the next norm's gain
+    {
+        const int row_in_tile = threadIdx.x % kTileRows, col = threadIdx.x / kTileRows;
+        if (EPI == EPI_ROPE && col < args.batch) {
+            my_position = args.positions[col];
+            my_slot = args.slot_mapping[col];
+            const int tiles_per_head = args.head_dim / 16;
+            if (tiles_mine > 0 && cluster_id / tiles_per_head < args.heads + args.kv_heads) {
+                const size_t at_table = (size_t)my_position * (args.head_dim / 2) + (cluster_id % tiles_per_head) * 8 + row_in_tile;
+                first_a = args.cos_table[at_table];
+                first_b = args.sin_table[at_table];
+            }
+        }
+        if (EPI == EPI_RESIDUAL && args.emit_gain != nullptr && tiles_mine > 0 && cluster_id * kTileRows + row_in_tile < rows_total)
+            first_a = args.emit_gain[cluster_id * kTileRows + row_in_tile];
+        if (PRO == PRO_NORM)
+            for (int c = threadIdx.x * 32; c < part_end - part_begin; c += kThreads * 32)  // a line of 128 bytes each
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(args.gain + part_begin + c));
+    }
     grid_dependency_wait();  // from here on the results of the kernel before this one are visible
 
     // ---- activations of this block's part of K -> shared memory, bfloat16
@@ -298,8 +321,6 @@ skinny_gemm_kernel(const SkinnyArgs args) {
     }
     bool sq_gathered = args.k_split == 1;
 
-    int my_position = 0;  // EPI_ROPE: the position of the batch column of this thread's first finishing item
-    if (EPI == EPI_ROPE && (int)threadIdx.x / kTileRows < args.batch) my_position = args.positions[threadIdx.x / kTileRows];
 
     // ---- row tile after row tile; the ring keeps running across them
     int stage_index = 0;
@@ -360,7 +381,10 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                 if (EPI == EPI_RESIDUAL) early_a = args.out_f32[(size_t)col * args.ld_out + row];
                 if (EPI == EPI_ROPE) {
                     const int tiles_per_head = args.head_dim / 16;
-                    if (tile / tiles_per_head < args.heads + args.kv_heads) {
+                    if (local == 0) {
+                        early_a = first_a;
+                        early_b = first_b;
+                    } else if (tile / tiles_per_head < args.heads + args.kv_heads) {
                         const size_t at_table = (size_t)my_position * (args.head_dim / 2) + (tile % tiles_per_head) * 8 + row_in_tile;
                         early_a = args.cos_table[at_table];
                         early_b = args.sin_table[at_table];
@@ -419,7 +443,8 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                 const float x_new = (i == (int)threadIdx.x ? early_a : args.out_f32[at]) + value;
                 args.out_f32[at] = x_new;
                 if (emits) {
-                    args.emit_rows[(size_t)col * args.ld_emit + row] = __float2bfloat16_rn(x_new * args.emit_gain[row]);
+                    const float gain = (local == 0 && i == (int)threadIdx.x) ? first_a : args.emit_gain[row];
+                    args.emit_rows[(size_t)col * args.ld_emit + row] = __float2bfloat16_rn(x_new * gain);
                     squares = x_new * x_new;
                 }
             }
@@ -442,7 +467,7 @@ skinny_gemm_kernel(const SkinnyArgs args) {
                     q[d0] = __float2bfloat16_rn(x0);
                     q[d0 + half] = __float2bfloat16_rn(x1);
                 } else {
-                    const int slot = args.slot_mapping[col];
+                    const int slot = i == (int)threadIdx.x ? my_slot : args.slot_mapping[col];
                     if (slot >= 0) {
                         const bool is_key = head < args.heads + args.kv_heads;
                         const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
