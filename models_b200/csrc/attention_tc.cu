@@ -43,7 +43,6 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     // Lengths and page tables were written before the step began, and every older position of the
     // cache in an earlier step: a block may fetch its first pages before it waits for that kernel,
     // up to the one that holds the newest position.
-    if (!kCluster) grid_dependency_wait();
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* stage_smem = smem;  // kDecodeStages x (K tile, V tile)
     // The 16 query rows pass through the last stage, which no page is fetched into before they are in registers: a
@@ -69,6 +68,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
 
     const bool empty = t_begin >= t_end;  // nothing for this split
     if (empty && !kCluster) {  // an empty partial
+        grid_dependency_wait();  // (the scratch memory may still be read by a kernel before this one)
         if (threadIdx.x < rows_here) {
             float* ml = partial_ml + ((size_t)(seq * heads + head0 + threadIdx.x) * splits + split) * 2;
             ml[0] = -CUDART_INF_F;
@@ -82,7 +82,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float run_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, run_sum[2] = {0.0f, 0.0f};  // maxima of raw scores
     const float scale_log2 = scale * 1.4426950408889634f;  // positive
-    if (empty && kCluster) grid_dependency_wait();
+    if (empty) grid_dependency_wait();
     if (!empty) {
     const int* table = block_table + (size_t)seq * max_blocks;
     const uint32_t stage_base = smem_u32(stage_smem);
@@ -91,7 +91,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_row_stride, bf16* __re
     // position of this step (all but the sequence's last page) are asked for before the wait for the kernel
     // before this one, the others after it.
     const int newest = pos / kTile;
-    bool waited = !kCluster;  // (without a cluster the block has waited above)
+    bool waited = false;
 #pragma unroll
     for (int ahead = 0; ahead < kDecodeStages - 1; ++ahead) {
         if (!waited && (t_begin + ahead >= t_end || t_begin + ahead == newest)) {
