@@ -141,6 +141,37 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     grid_launch_dependents();
     bool ok = true;
 
+    // What a thread's first item of the finishing below reads from memory -- the residual stream's old values and the
+    // next norm's gain, or the rotation's cosines and sines and the cache slot -- is asked for long before the parts
+    // meet (the item depends only on the thread and the block): by the warps that will copy the accumulator while
+    // they wait for it, by the others when their own work is done.  Callers have waited for the kernel before this one.
+    float4 early_before = make_float4(0.0f, 0.0f, 0.0f, 0.0f), early_gain = early_before;  // EPI_ROPE: cosines, sines
+    int early_slot = -1;
+    auto load_early = [&]() {
+        if (EPI == EPI_RESIDUAL) {
+            const int quads = 128 / splits / 4, item = threadIdx.x;
+            const int row = tile * kTileRows + rank * (128 / splits) + (item & (quads - 1)) * 4, col = item / quads;
+            if (col < args.batch && row < args.rows_total) {
+                early_before = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(args.out) + (size_t)col * args.ld_out + row);
+                if (args.emit_gain) early_gain = *reinterpret_cast<const float4*>(args.emit_gain + row);
+            }
+        }
+        if (EPI == EPI_ROPE) {
+            const int quads = 64 / splits / 4, item = threadIdx.x;
+            const int unit = rank * (64 / splits) + (item & (quads - 1)) * 4, col = item / quads;
+            const int hd = args.head_dim, half = hd / 2;
+            const int head = tile * (kTileRows / hd) + unit / half, d0 = unit % half;
+            if (col < args.batch && head < args.heads + 2 * args.kv_heads) {
+                early_slot = args.slot_mapping[col];
+                if (head < args.heads + args.kv_heads) {
+                    const size_t at_table = (size_t)args.positions[col] * half + d0;
+                    early_before = *reinterpret_cast<const float4*>(args.cos_table + at_table);
+                    early_gain = *reinterpret_cast<const float4*>(args.sin_table + at_table);
+                }
+            }
+        }
+    };
+
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -200,6 +231,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     } else {
         // ------------------------------------------------------------------ the accumulator -> this block's shared memory
         grid_dependency_wait();  // (what the finishing below reads and adds into comes from the kernel before this one)
+        load_early();
         const int quarter = warp & 3;
         if (args.ssq_parts) {
             // while the products run: 1 / rms of every activation row from the parts of its sum of squares.  Every lane
@@ -237,17 +269,9 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
     }
 
-    // What a thread's first item of the finishing below reads from memory -- the residual stream's old values and the
-    // next norm's gain -- is asked for before the parts meet (the item depends only on the thread and the block).
-    float4 early_before = make_float4(0.0f, 0.0f, 0.0f, 0.0f), early_gain = early_before;
-    if (EPI == EPI_RESIDUAL) {
-        if (warp < 2) grid_dependency_wait();
-        const int quads = 128 / splits / 4, item = threadIdx.x;
-        const int row = tile * kTileRows + rank * (128 / splits) + (item & (quads - 1)) * 4, col = item / quads;
-        if (col < args.batch && row < args.rows_total) {
-            early_before = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(args.out) + (size_t)col * args.ld_out + row);
-            if (args.emit_gain) early_gain = *reinterpret_cast<const float4*>(args.emit_gain + row);
-        }
+    if (warp < 2 && (EPI == EPI_RESIDUAL || EPI == EPI_ROPE)) {
+        grid_dependency_wait();
+        load_early();
     }
 
     // ---- the parts of K meet: every block of the cluster has its accumulator in its shared memory
@@ -338,9 +362,9 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 float x0[4] = {first_half.x * scale, first_half.y * scale, first_half.z * scale, first_half.w * scale};
                 float x1[4] = {second_half.x * scale, second_half.y * scale, second_half.z * scale, second_half.w * scale};
                 if (head < args.heads + args.kv_heads) {
-                    const size_t at_table = (size_t)args.positions[col] * half + d0;
-                    const float4 c4 = *reinterpret_cast<const float4*>(args.cos_table + at_table);
-                    const float4 s4 = *reinterpret_cast<const float4*>(args.sin_table + at_table);
+                    const size_t at_table = base == 0 ? 0 : (size_t)args.positions[col] * half + d0;
+                    const float4 c4 = base == 0 ? early_before : *reinterpret_cast<const float4*>(args.cos_table + at_table);
+                    const float4 s4 = base == 0 ? early_gain : *reinterpret_cast<const float4*>(args.sin_table + at_table);
                     const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -353,7 +377,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 if (head < args.heads) {
                     dst = reinterpret_cast<bf16*>(args.out) + (size_t)col * args.ld_out + (size_t)head * hd;
                 } else {
-                    const int slot = args.slot_mapping[col];
+                    const int slot = base == 0 ? early_slot : args.slot_mapping[col];
                     if (slot >= 0) {
                         const bool is_key = head < args.heads + args.kv_heads;
                         const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
