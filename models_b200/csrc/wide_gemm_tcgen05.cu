@@ -145,6 +145,9 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     // next norm's gain, or the rotation's cosines and sines and the cache slot -- is asked for long before the parts
     // meet (the item depends only on the thread and the block): by the warps that will copy the accumulator while
     // they wait for it, by the others when their own work is done.  Callers have waited for the kernel before this one.
+    // (With 32 batch columns only the first two warps have such an item, and the step measured slower with the rotation's
+    // part: there the residual product's threads ask where they always did, and the rotation reads in its loop.)
+    constexpr bool kEarlyForAll = kBatchN >= 64;
     float4 early_before = make_float4(0.0f, 0.0f, 0.0f, 0.0f), early_gain = early_before;  // EPI_ROPE: cosines, sines
     int early_slot = -1;
     auto load_early = [&]() {
@@ -156,7 +159,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 if (args.emit_gain) early_gain = *reinterpret_cast<const float4*>(args.emit_gain + row);
             }
         }
-        if (EPI == EPI_ROPE) {
+        if (EPI == EPI_ROPE && kEarlyForAll) {
             const int quads = 64 / splits / 4, item = threadIdx.x;
             const int unit = rank * (64 / splits) + (item & (quads - 1)) * 4, col = item / quads;
             const int hd = args.head_dim, half = hd / 2;
@@ -231,7 +234,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     } else {
         // ------------------------------------------------------------------ the accumulator -> this block's shared memory
         grid_dependency_wait();  // (what the finishing below reads and adds into comes from the kernel before this one)
-        load_early();
+        if (kEarlyForAll) load_early();
         const int quarter = warp & 3;
         if (args.ssq_parts) {
             // while the products run: 1 / rms of every activation row from the parts of its sum of squares.  Every lane
@@ -269,8 +272,13 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
     }
 
-    if (warp < 2 && (EPI == EPI_RESIDUAL || EPI == EPI_ROPE)) {
-        grid_dependency_wait();
+    if (kEarlyForAll) {
+        if (warp < 2 && (EPI == EPI_RESIDUAL || EPI == EPI_ROPE)) {
+            grid_dependency_wait();
+            load_early();
+        }
+    } else if (EPI == EPI_RESIDUAL) {
+        if (warp < 2) grid_dependency_wait();
         load_early();
     }
 
@@ -362,9 +370,10 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 float x0[4] = {first_half.x * scale, first_half.y * scale, first_half.z * scale, first_half.w * scale};
                 float x1[4] = {second_half.x * scale, second_half.y * scale, second_half.z * scale, second_half.w * scale};
                 if (head < args.heads + args.kv_heads) {
-                    const size_t at_table = base == 0 ? 0 : (size_t)args.positions[col] * half + d0;
-                    const float4 c4 = base == 0 ? early_before : *reinterpret_cast<const float4*>(args.cos_table + at_table);
-                    const float4 s4 = base == 0 ? early_gain : *reinterpret_cast<const float4*>(args.sin_table + at_table);
+                    const bool early = kEarlyForAll && base == 0;
+                    const size_t at_table = early ? 0 : (size_t)args.positions[col] * half + d0;
+                    const float4 c4 = early ? early_before : *reinterpret_cast<const float4*>(args.cos_table + at_table);
+                    const float4 s4 = early ? early_gain : *reinterpret_cast<const float4*>(args.sin_table + at_table);
                     const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -377,7 +386,7 @@ wide_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 if (head < args.heads) {
                     dst = reinterpret_cast<bf16*>(args.out) + (size_t)col * args.ld_out + (size_t)head * hd;
                 } else {
-                    const int slot = base == 0 ? early_slot : args.slot_mapping[col];
+                    const int slot = (kEarlyForAll && base == 0) ? early_slot : args.slot_mapping[col];
                     if (slot >= 0) {
                         const bool is_key = head < args.heads + args.kv_heads;
                         const int kv_head = head - args.heads - (is_key ? 0 : args.kv_heads);
